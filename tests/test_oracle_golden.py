@@ -1,0 +1,194 @@
+"""Pins the CPU oracle: the reference's own known-answer tests (transcribed into
+tests/golden/reference_kat.json) and real-oneDNN outputs (tests/golden/onednn_*.npz)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import itex_oracle as o
+
+
+@pytest.fixture(scope="module")
+def kat(golden_dir):
+    with open(os.path.join(golden_dir, "reference_kat.json")) as f:
+        return json.load(f)
+
+
+def scale_per_slice(shape, axis, values):
+    out = np.take(values, np.remainder(np.arange(np.prod(shape)), len(values))).reshape(shape)
+    if axis is not None:
+        ss = [1] * len(shape)
+        ss[axis] = shape[axis]
+        out = out * np.arange(1, shape[axis] + 1).reshape(ss)
+    return out
+
+
+def test_quantize_axis_exact(kat):
+    k = kat["quantize_axis"]
+    shape = np.array(k["shape"])
+    values = np.array(k["values"], np.float32)
+    expected = scale_per_slice(shape, None, np.array(k["quant_values"], np.int32))
+    for axis in k["axes"]:
+        x = scale_per_slice(shape, axis, values).astype(np.float32)
+        if axis is None:
+            mn, mx = k["min_per_slice"], k["max_per_slice"]
+            axes = [-1]
+        else:
+            mn = [k["min_per_slice"] * (i + 1) for i in range(shape[axis])]
+            mx = [k["max_per_slice"] * (i + 1) for i in range(shape[axis])]
+            axes = [axis]
+        for ax in axes:
+            q, omin, omax = o.quantize_v2(x, mn, mx, T=k["T"], mode=k["mode"], round_mode=k["round_mode"],
+                                          narrow_range=k["narrow_range"], axis=ax)
+            assert q.dtype == np.int8
+            np.testing.assert_array_equal(q.astype(np.int32), expected)
+            np.testing.assert_allclose(np.asarray(omax), np.abs(mn))  # |min| = 1.0*(i+1) dominates
+
+
+def test_quantize_min_first_variants(kat):
+    for name, kwargs in (("quantize_min_first", {}), ("quantize_asymmetric_legacy", {}),
+                         ("quantize_asymmetric_classic", {"classic_asymmetric_algorithm": True})):
+        k = kat[name]
+        q, _, _ = o.quantize_v2(np.array(k["x"], np.float32), k["min"], k["max"], T=k["T"], mode="MIN_FIRST",
+                                round_mode="HALF_AWAY_FROM_ZERO", **kwargs)
+        np.testing.assert_allclose(q.astype(np.float32), k["expected"], atol=k["atol"])
+    # bf16 input takes the same path (quantized_ops_test.py:70-90)
+    k = kat["quantize_min_first"]
+    q, _, _ = o.quantize_v2(o.to_bf16_rne(np.array(k["x"], np.float32)), k["min"], k["max"], T=k["T"],
+                            mode="MIN_FIRST", round_mode="HALF_AWAY_FROM_ZERO")
+    np.testing.assert_allclose(q.astype(np.float32), k["expected"], atol=k["atol"])
+
+
+def test_dequantize_axis(kat):
+    k = kat["dequantize_axis"]
+    shape = np.array(k["shape"])
+    q = scale_per_slice(shape, None, np.array(k["values"], np.int32)).astype(np.int8)
+    for axis in k["axes"]:
+        expected = scale_per_slice(shape, axis, np.array(k["dequant_values"], np.float32))
+        if axis is None:
+            mn, mx, ax = k["min_per_slice"], k["max_per_slice"], -1
+        else:
+            mn = [k["min_per_slice"] * (i + 1) for i in range(shape[axis])]
+            mx = [k["max_per_slice"] * (i + 1) for i in range(shape[axis])]
+            ax = axis
+        y = o.dequantize(q, mn, mx, T=k["T"], mode=k["mode"], narrow_range=True, axis=ax)
+        np.testing.assert_allclose(y, expected, rtol=k["rtol"], atol=k["atol"])
+
+
+def test_dequantize_scaled_closed_form(kat):
+    k = kat["dequantize_scaled"]
+    for c in k["cases"]:
+        for narrow in (False, True):
+            q = np.array(c["q"], np.int8)
+            vmin = -127 if narrow else -128
+            sf = max(c["min"] / vmin, c["max"] / 127)
+            y = o.dequantize(q, c["min"], c["max"], T=k["T"], narrow_range=narrow)
+            np.testing.assert_allclose(y, q.astype(np.float32) * sf, rtol=k["rtol"], atol=k["atol"])
+    k = kat["dequantize_min_first"]
+    y = o.dequantize(np.array(k["q"], np.uint8), k["min"], k["max"], T=k["T"], mode="MIN_FIRST")
+    np.testing.assert_allclose(y, k["expected"], atol=k["atol"])
+
+
+def _matmul_case(kat):
+    k = kat["matmul_min_first"]
+    x = np.array(k["x_f32"], np.float32)
+    y = np.array(k["y_f32"], np.float32)
+    b = np.array(k["bias_f32"], np.float32)
+    qx, xmin, xmax = o.quantize_v2(x, x.min(), x.max(), T="quint8", mode="MIN_FIRST",
+                                   round_mode="HALF_AWAY_FROM_ZERO")
+    qy, ymin, ymax = o.quantize_v2(y, y.min(), y.max(), T="qint8", mode="SCALED", narrow_range=True)
+    return k, x, y, b, qx, xmin, xmax, qy, ymin, ymax
+
+
+def test_matmul_reference_sanity_cases(kat):
+    """quantized_matmul_op_test.py: the four QuantizedMatMulWithBias* ops vs fp32 math at 0.2."""
+    k, x, y, b, qx, xmin, xmax, qy, ymin, ymax = _matmul_case(kat)
+    tol = dict(rtol=k["rtol"], atol=k["atol"])
+    f = x @ y + b
+    # ...AndReluAndRequantize
+    fr = np.maximum(f, 0)
+    out, mn, mx = o.quantized_matmul_with_bias(qx, qy, b, xmin, xmax, ymin, ymax, fr.min(), fr.max(),
+                                               toutput="quint8", relu=True)
+    np.testing.assert_allclose(o.dequantize(out, mn, mx, T="quint8", narrow_range=True), fr, **tol)
+    # ...AndDequantize
+    out, _, _ = o.quantized_matmul_with_bias(qx, qy, b, xmin, xmax, ymin, ymax, f.min(), f.max(), toutput="float")
+    np.testing.assert_allclose(out, f, **tol)
+    # WithBias / WithBiasAndRelu -> qint32; dequantize linearly over [min_out, max_out]
+    for relu in (False, True):
+        out, mn, mx = o.quantized_matmul_with_bias(qx, qy, b, xmin, xmax, ymin, ymax, toutput="qint32", relu=relu)
+        deq = out.astype(np.float64) * (float(mx) / (2 ** 31 - 1))
+        np.testing.assert_allclose(deq, np.maximum(f, 0) if relu else f, **tol)
+
+
+def test_matmul_against_onednn(golden_dir):
+    g = np.load(os.path.join(golden_dir, "onednn_matmul.npz"))
+    n_exact = 0
+    for tout in ("float", "quint8", "bfloat16"):
+        for mode in ("SCALED", "MIN_FIRST"):
+            for sbm in ("literal", "intended"):
+                for relu in (0, 1):
+                    ref = g["y_%s_%s_%s_%d" % (tout, mode, sbm, relu)]
+                    out, _, _ = o.quantized_matmul_with_bias(
+                        g["a"], g["b"], g["bias"], g["min_a"], g["max_a"], g["min_b"], g["max_b"],
+                        g["min_freezed"], g["max_freezed"], toutput=tout, relu=bool(relu),
+                        input_quant_mode=mode, scaled_bias_mode=sbm)
+                    if tout == "quint8":
+                        np.testing.assert_array_equal(out, ref)
+                    else:
+                        np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-6)
+                    n_exact += int(np.array_equal(out, ref))
+    assert n_exact >= 16  # the restated epilogue order reproduces oneDNN bit for bit on most cases
+
+
+def test_conv_against_onednn(golden_dir):
+    g = np.load(os.path.join(golden_dir, "onednn_conv.npz"))
+    for name in ("c3s1", "c3s2", "c1s1"):
+        s = int(g[name + "_stride"])
+        for tout in ("quint8", "float"):
+            out, mn, mx = o.quantized_conv2d(
+                g[name + "_x"], g[name + "_f"], g[name + "_bias"], g["min_input"], g["max_input"],
+                g[name + "_min_f"], g[name + "_max_f"], g["min_out"], g["max_out"],
+                strides=(1, s, s, 1), padding="SAME", out_type=tout, relu=True)
+            ref = g["%s_y_%s" % (name, tout)]
+            assert out.shape == ref.shape
+            if tout == "quint8":
+                np.testing.assert_array_equal(out, ref)
+                assert mn == g["min_out"] and mx == g["max_out"]
+            else:
+                np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_conv_reference_style_vs_fp32():
+    """native_quantized_conv_test.py:33-198 pattern: random 1x6x6x4 . 3x3x4x4, SAME, SCALED
+    inputs, compared with the fp32 convolution at rtol=atol=0.3."""
+    rng = np.random.default_rng(7)
+    x = rng.uniform(0, 1, (1, 6, 6, 4)).astype(np.float32)
+    w = rng.uniform(-1, 1, (3, 3, 4, 4)).astype(np.float32)
+    b = rng.uniform(-1, 1, 4).astype(np.float32)
+    qx, xmin, xmax = o.quantize_v2(x, x.min(), x.max(), T="quint8")
+    qw, wmin, wmax = o.quantize_v2(w, w.min(), w.max(), T="qint8")
+    xp = np.zeros((1, 8, 8, 4), np.float32)
+    xp[:, 1:7, 1:7] = x
+    f = np.zeros((1, 6, 6, 4), np.float32)
+    for i in range(3):
+        for j in range(3):
+            f += np.tensordot(xp[:, i:i + 6, j:j + 6], w[i, j], axes=([3], [0]))
+    f = np.maximum(f + b, 0)
+    out, mn, mx = o.quantized_conv2d(qx, qw, b, xmin, xmax, wmin, wmax, f.min(), f.max(), out_type="quint8")
+    np.testing.assert_allclose(o.dequantize(out, mn, mx, T="quint8"), f, rtol=0.3, atol=0.3)
+
+
+def test_fp8_cast_and_delayed_scaling():
+    # saturation and RNE on e4m3 (float8.h kSaturate=true): 448 is max, 464 is the tie to 448|480(sat)
+    v = np.array([0.0, 1.0, 447.0, 448.0, 460.0, 1e9, -1e9, 0.0625 + 0.0078125 / 2], np.float32)
+    back = o.fp8_to_f32(o.fp8_cast_sat(v))
+    assert back[3] == 448 and back[4] == 448 and back[5] == 448 and back[6] == -448
+    hist = np.zeros((16, 3), np.float32)
+    scale = np.ones(3, np.float32)
+    hist[0] = [3.7, 0.0, 1000.0]
+    nh, sf, sfi = o.fp8_amax_and_scale_update(hist, scale)
+    # 448/3.7=121.08 -> 2^6; amax 0 keeps the old scale; 448/1000 -> exp=-2 -> 1/4
+    np.testing.assert_array_equal(sf, [64.0, 1.0, 0.25])
+    np.testing.assert_array_equal(sfi, [1 / 64.0, 1.0, 4.0])
+    assert (nh[0] == 0).all() and (nh[15] == hist[0]).all()
