@@ -1,0 +1,340 @@
+/*
+ * itexb200.h - C-ABI of libitexb200, the B200 (sm_100a) implementation of the
+ * quantized-inference hot path of intel/intel-extension-for-tensorflow (ITEX).
+ *
+ * Three layers, all plain C (no exceptions cross this boundary, every function
+ * returns an itexb_status_t unless noted, caller owns every pointer it passes):
+ *
+ *   1. Device runtime   itexb_rt_*      - what ITEX's StreamExecutor callbacks do
+ *   2. Kernel launches  itexb_quantize / itexb_dequantize / itexb_gemm / itexb_conv2d /
+ *                       itexb_fp8_*     - raw device pointers + POD descriptors
+ *   3. Op layer         itexb_op_*      - ITEX's op names, attrs, input/output order,
+ *                       HostMemory conventions and error behaviour; this is what a
+ *                       TensorFlow PluggableDevice shim binds its create/compute/delete
+ *                       callbacks to.
+ *
+ * Citations name files of the reference project by their path inside it.
+ */
+#ifndef ITEXB200_H_
+#define ITEXB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ITEXB_API __attribute__((visibility("default")))
+
+/* Status codes carry TensorFlow's TF_Code values so a shim can forward them to
+ * TF_SetStatus unchanged (the reference reports errors through
+ * OP_REQUIRES -> TF_OpKernelContext_Failure, itex/core/utils/op_kernel.cc:511-532). */
+typedef enum itexb_status {
+  ITEXB_OK = 0,
+  ITEXB_INVALID_ARGUMENT = 3,
+  ITEXB_NOT_FOUND = 5,
+  ITEXB_RESOURCE_EXHAUSTED = 8,
+  ITEXB_FAILED_PRECONDITION = 9,
+  ITEXB_ABORTED = 10,
+  ITEXB_UNIMPLEMENTED = 12,
+  ITEXB_INTERNAL = 13
+} itexb_status_t;
+
+/* Element types, numbered like TensorFlow's DataType enum (the attr values T, T1,
+ * Toutput, Tbias, dtype ... arrive as these numbers).  FP8 has no TF number on this
+ * path: the reference carries e4m3/e5m2 bytes in DT_INT8 tensors and names the
+ * format in a string attr (itex/core/ops/fp8_ops.cc:22-61). */
+typedef enum itexb_dtype {
+  ITEXB_DT_INVALID = 0,
+  ITEXB_DT_FLOAT = 1,
+  ITEXB_DT_INT32 = 3,
+  ITEXB_DT_UINT8 = 4,
+  ITEXB_DT_INT8 = 6,
+  ITEXB_DT_QINT8 = 11,
+  ITEXB_DT_QUINT8 = 12,
+  ITEXB_DT_QINT32 = 13,
+  ITEXB_DT_BFLOAT16 = 14,
+  ITEXB_DT_HALF = 19,
+  ITEXB_DT_FP8_E4M3 = 101,
+  ITEXB_DT_FP8_E5M2 = 102
+} itexb_dtype_t;
+
+/* Thread-local text of the last non-OK status returned on the calling thread. */
+ITEXB_API const char* itexb_last_error(void);
+ITEXB_API const char* itexb_version(void);
+/* Number of kernel launches this library has issued (all threads) since load. */
+ITEXB_API uint64_t itexb_launch_count(void);
+
+/* ------------------------------------------------------------------------- */
+/* 1. Device runtime.  Replaces the StreamExecutor callback table the reference
+ *    fills in itex/core/devices/gpu/gpu_device_plugin.cc:26-376 (listed at
+ *    itex/core/wrapper/itex_gpu_wrapper.cc:190-228): device memory through the
+ *    plugin's own caching allocator, pinned host memory, streams, events,
+ *    async/sync copies, memset, host callbacks.  itexb_stream_t is a cudaStream_t
+ *    (NULL = the legacy default stream); itexb_event_t is a cudaEvent_t.          */
+/* ------------------------------------------------------------------------- */
+typedef void* itexb_stream_t;
+typedef void* itexb_event_t;
+
+typedef struct itexb_allocator_stats {
+  int64_t num_allocs;       /* calls served */
+  int64_t bytes_in_use;     /* handed out and not yet freed */
+  int64_t peak_bytes_in_use;
+  int64_t bytes_reserved;   /* held from the driver (in use + cached) */
+  int64_t largest_alloc_size;
+  int64_t bytes_limit;      /* 0 = no limit (env ITEXB_LIMIT_MEMORY_MB, like ITEX_LIMIT_MEMORY_SIZE_IN_MB) */
+} itexb_allocator_stats_t;
+
+ITEXB_API int itexb_rt_device_count(int* count);
+ITEXB_API int itexb_rt_set_device(int ordinal);
+ITEXB_API int itexb_rt_device_memory_usage(int ordinal, int64_t* free_bytes, int64_t* total_bytes);
+ITEXB_API int itexb_rt_allocate(int ordinal, size_t bytes, void** ptr);      /* 256-byte aligned */
+ITEXB_API int itexb_rt_deallocate(int ordinal, void* ptr);
+ITEXB_API int itexb_rt_host_allocate(size_t bytes, void** ptr);              /* pinned */
+ITEXB_API int itexb_rt_host_deallocate(void* ptr);
+ITEXB_API int itexb_rt_allocator_stats(int ordinal, itexb_allocator_stats_t* stats);
+ITEXB_API int itexb_rt_trim(int ordinal);                                    /* return cached blocks to the driver */
+ITEXB_API int itexb_rt_create_stream(int ordinal, itexb_stream_t* stream);
+ITEXB_API int itexb_rt_destroy_stream(itexb_stream_t stream);
+ITEXB_API int itexb_rt_stream_dependency(itexb_stream_t dependent, itexb_stream_t other);
+ITEXB_API int itexb_rt_stream_status(itexb_stream_t stream);                 /* OK, or INTERNAL when the stream is in error */
+ITEXB_API int itexb_rt_create_event(itexb_event_t* event);
+ITEXB_API int itexb_rt_destroy_event(itexb_event_t event);
+ITEXB_API int itexb_rt_record_event(itexb_stream_t stream, itexb_event_t event);
+ITEXB_API int itexb_rt_wait_for_event(itexb_stream_t stream, itexb_event_t event);
+ITEXB_API int itexb_rt_event_status(itexb_event_t event, int* complete);
+ITEXB_API int itexb_rt_event_elapsed_ms(itexb_event_t start, itexb_event_t stop, float* ms);
+ITEXB_API int itexb_rt_memcpy_h2d(void* dst_dev, const void* src_host, size_t bytes, itexb_stream_t stream);
+ITEXB_API int itexb_rt_memcpy_d2h(void* dst_host, const void* src_dev, size_t bytes, itexb_stream_t stream);
+ITEXB_API int itexb_rt_memcpy_d2d(void* dst_dev, const void* src_dev, size_t bytes, itexb_stream_t stream);
+ITEXB_API int itexb_rt_sync_memcpy_h2d(void* dst_dev, const void* src_host, size_t bytes);
+ITEXB_API int itexb_rt_sync_memcpy_d2h(void* dst_host, const void* src_dev, size_t bytes);
+ITEXB_API int itexb_rt_sync_memcpy_d2d(void* dst_dev, const void* src_dev, size_t bytes);
+ITEXB_API int itexb_rt_mem_zero(void* dev, size_t bytes, itexb_stream_t stream);
+ITEXB_API int itexb_rt_memset(void* dev, uint8_t value, size_t bytes, itexb_stream_t stream);
+ITEXB_API int itexb_rt_memset32(void* dev, uint32_t pattern, size_t bytes, itexb_stream_t stream);
+ITEXB_API int itexb_rt_block_host_until_done(itexb_stream_t stream);
+ITEXB_API int itexb_rt_block_host_for_event(itexb_event_t event);
+ITEXB_API int itexb_rt_synchronize_all_activity(int ordinal);
+ITEXB_API int itexb_rt_host_callback(itexb_stream_t stream, void (*fn)(void* arg), void* arg);
+
+/* ------------------------------------------------------------------------- */
+/* 2. Kernel launches (device pointers; asynchronous on `stream`).            */
+/* ------------------------------------------------------------------------- */
+
+/* How the affine quantize kernel combines its per-slice constants. */
+typedef enum itexb_quant_kind {
+  ITEXB_QUANT_SCALED = 0,          /* q = sat(rne(x*s))                     SCALED      */
+  ITEXB_QUANT_MIN_FIRST_LEGACY = 1,/* q = sat(rne(x*s + shift*s))           legacy MIN_FIRST, shift = -min */
+  ITEXB_QUANT_MIN_FIRST_CLASSIC = 2/* q = sat(rne(x*s + zp))                classic asymmetric */
+} itexb_quant_kind_t;
+
+/* Replaces the dnnl::reorder / dnnl::binary the reference executes in
+ * QuantizeV2Op::Compute (itex/core/kernels/common/quantize_op.h:256-314,394).
+ * x: FLOAT | BFLOAT16 | HALF, q: QINT8 | QUINT8, n elements.  The tensor is viewed
+ * as [outer, nslice, inner]; slice of element i is (i / inner) % nslice.  With
+ * nslice == 1 and scale == NULL the host scalars are used.  `shift` carries the
+ * second constant of kinds 1 and 2 (NULL -> shift_host).                       */
+ITEXB_API int itexb_quantize(const void* x, int x_dtype, void* q, int q_dtype, int64_t n,
+                             int64_t inner, int64_t nslice, int kind,
+                             const float* scale, const float* shift,
+                             float scale_host, float shift_host, itexb_stream_t stream);
+
+/* Replaces the dnnl::reorder of DequantizeOp::Compute
+ * (itex/core/kernels/common/dequantize_op.h:143-169): y = ydtype((float(q) - zp) * s). */
+ITEXB_API int itexb_dequantize(const void* q, int q_dtype, void* y, int y_dtype, int64_t n,
+                               int64_t inner, int64_t nslice, const float* scale, const float* zp,
+                               float scale_host, float zp_host, itexb_stream_t stream);
+
+/* min and max of a FLOAT|BFLOAT16 tensor into minmax[0], minmax[1] (device), for graphs
+ * that derive a dynamic range on the device.  minmax must be initialised by
+ * itexb_minmax_init first (+inf, -inf).  No counterpart kernel in the reference: there
+ * the range arrives as a HostMemory input (itex/core/kernels/gpu/quantize_op.cc:25-31). */
+ITEXB_API int itexb_minmax_init(float* minmax, itexb_stream_t stream);
+ITEXB_API int itexb_minmax(const void* x, int x_dtype, int64_t n, float* minmax, itexb_stream_t stream);
+/* QuantizeV2 SCALED whose range is read on the device from minmax[0..1] (already
+ * adjusted like AdjustInputMinMaxRange + GetScaleAndZeropointAndAlignMinMax would);
+ * writes the scale it used and the aligned range to out3 = {scale, out_min, out_max}. */
+ITEXB_API int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_dtype, int64_t n,
+                                     const float* minmax, float ensure_minimum_range, float* out3,
+                                     itexb_stream_t stream);
+
+/* Weight pre-pack: [k,n] row-major (the TF layout of `b`) -> [n,k_pad] row-major with k
+ * padded by zeros to a multiple of 16, the K-major layout the MMA kernel stages with TMA.
+ * Plays the role of the cached weight reorder of
+ * itex/core/kernels/common/quantized_matmul_common.h:241-275.  1-byte elements.        */
+ITEXB_API int itexb_pack_weights_kn(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad,
+                                    itexb_stream_t stream);
+/* Column sums of an int8 [k,n] weight (MIN_FIRST compensation,
+ * quantized_matmul_common.h:569-574). */
+ITEXB_API int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, int64_t n, itexb_stream_t stream);
+
+/* What the GEMM / conv epilogue does with an accumulator acc[m][n]:
+ *   f = float(acc) * scale[n or 0]     (scale == NULL and scale_count == 0: no multiply)
+ *   f = f + bias[n]                    (bias != NULL)
+ *   f = f + sum_scale * float(summand[m][n])   (summand != NULL)
+ *   f = max(f, 0)                      (relu)
+ *   out = convert(f): QUINT8/QINT8/QINT32 saturate then round-to-nearest-even;
+ *         FLOAT/BFLOAT16/HALF plain conversion; FP8_E4M3 saturating RNE of f*out_scale[0]
+ *         with amax[0] = max(amax[0], max|f|).
+ * Separate fp32 multiply and add (no FMA), the order oneDNN's int8 primitives use for
+ * "scale on DNNL_ARG_WEIGHTS, bias after" (itex/core/utils/onednn/onednn_post_op_util.cc:283-295).
+ * raw_acc = 1 with out_dtype QINT32 stores the exact int32 accumulator instead.        */
+typedef struct itexb_epilogue {
+  const float* scale;      /* device, scale_count entries */
+  int32_t scale_count;     /* 0, 1 or n */
+  const float* alpha_a;    /* optional device scalars: scale used is alpha_a[0]*alpha_b[0] */
+  const float* alpha_b;    /*   (FP8: a_scale_inv[i], b_scale_inv[j]); overrides `scale` */
+  const float* bias;       /* device fp32 [n] or NULL */
+  const void* summand;     /* device [m][n] or NULL */
+  int32_t summand_dtype;   /* QUINT8 | QINT8 | FLOAT | BFLOAT16 */
+  int64_t ld_summand;      /* elements */
+  float sum_scale;
+  int32_t relu;
+  int32_t raw_acc;
+  const float* out_scale;  /* FP8 output only: device scalar c_scale */
+  float* amax;             /* FP8 output only: device scalar, atomically maxed */
+} itexb_epilogue_t;
+
+/* out[m][n] = epilogue( sum_k a[m][k] * b[n][k] ).
+ * Replaces dnnl::inner_product_forward (quantized_matmul_common.h:223-226,92) and, for
+ * FP8, the dequantize + dnnl::matmul (+ quantize) chain of
+ * itex/core/kernels/gpu/fp8/fp8_matmul_gpu.h:34-162.
+ * a: [m,k] row-major, lda elements (multiple of 16, base 16-byte aligned);
+ * b: packed [n,k] row-major, ldb likewise.  a_dtype QUINT8|QINT8 with b_dtype QINT8
+ * (int32 accumulation, exact), or both FP8_E4M3|FP8_E5M2 (fp32 accumulation).
+ * status_word: optional device int32 that the kernel sets non-zero if one of its
+ * bounded waits expired (0 stays 0 on success).                                        */
+typedef struct itexb_gemm_params {
+  int32_t m, n, k;
+  int32_t a_dtype, b_dtype, out_dtype;
+  const void* a; int64_t lda;
+  const void* b; int64_t ldb;
+  void* out;     int64_t ldo;
+  itexb_epilogue_t ep;
+  int32_t* status_word;
+} itexb_gemm_params_t;
+ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
+
+/* NHWC x (packed) HWIO convolution as an implicit GEMM with the same epilogue.
+ * Replaces dnnl::convolution_forward (itex/core/kernels/common/conv_ops.h:953-957,801).
+ * x: [n,h,w,c] QUINT8|QINT8; filter packed by itexb_pack_filter_hwio to
+ * [co][kh*kw*c_pad]; out: [n,oh,ow,co].  Padding is zero fill; pad_top/pad_left as
+ * computed by GetWindowedOutputSizeVerboseV2 (itex/core/utils/common_shape_fns.cc:42-81). */
+typedef struct itexb_conv_params {
+  int32_t n, h, w, c;
+  int32_t kh, kw, co;
+  int32_t stride_h, stride_w, dil_h, dil_w;
+  int32_t pad_top, pad_left;
+  int32_t oh, ow;
+  int32_t c_pad;           /* channels per tap in the packed filter (multiple of 16) */
+  int32_t x_dtype, out_dtype;
+  const void* x;
+  const void* filter_packed;
+  void* out;
+  itexb_epilogue_t ep;     /* scale_count 0, 1 or co; summand laid out like out */
+  int32_t* status_word;
+  void* workspace;         /* device scratch of itexb_conv2d_workspace_bytes() or NULL if 0 */
+} itexb_conv_params_t;
+ITEXB_API int itexb_pack_filter_hwio(const void* f_hwio, void* f_packed, int32_t kh, int32_t kw, int32_t c,
+                                     int32_t co, int32_t c_pad, itexb_stream_t stream);
+ITEXB_API size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p);
+ITEXB_API int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream);
+
+/* FP8 pointwise ops.  Replace the SYCL PointWiseKernel launched by
+ * functor::Fp8Quantize / Fp8Dequantize (itex/core/kernels/gpu/fp8/fp8_quantize_gpu.h:36-72,
+ * vectorized_pointwise.h:27-88).  scale / scale_inv / amax point at the meta element
+ * (base + fp8_meta_index).  y = fp8(float(x)*scale[0]) saturating RNE; amax[0] is
+ * atomically raised to max|x|.                                                          */
+ITEXB_API int itexb_fp8_quantize(const void* x, int x_dtype, void* y, int fp8_dtype, int64_t n,
+                                 const float* scale, float* amax, itexb_stream_t stream);
+ITEXB_API int itexb_fp8_dequantize(const void* x, int fp8_dtype, void* y, int y_dtype, int64_t n,
+                                   const float* scale_inv, itexb_stream_t stream);
+/* Delayed-scaling update of itex/python/fp8/autocast.py:44-121 for `n` meta slots on the
+ * device: amax = max over the `history_len` rows (algo 0 "max") or row 0 (algo 1
+ * "most_recent"); scale from amax; roll rows by -1 and zero row 0; scale_inv = 1/scale. */
+ITEXB_API int itexb_fp8_amax_and_scale_update(float* amax_history, float* scale, float* scale_inv,
+                                              int32_t history_len, int32_t n, float fp8_max, float margin,
+                                              int32_t algo, itexb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* 3. Op layer.  One kernel object per graph node, created from the node's op name
+ *    and attrs, computed many times, possibly from several threads (each instance
+ *    serialises itself like the reference's mu_compute_,
+ *    quantized_matmul_common.h:62, conv_ops.h:786).  Mirrors the three callbacks
+ *    the reference registers with TF_NewKernelBuilder (itex/core/utils/op_kernel.h:710-714,
+ *    op_kernel.cc:887-918).                                                             */
+/* ------------------------------------------------------------------------- */
+#define ITEXB_MAX_DIMS 8
+
+typedef struct itexb_tensor {
+  int32_t dtype;                 /* itexb_dtype_t */
+  int32_t rank;
+  int64_t dims[ITEXB_MAX_DIMS];
+  void* data;                    /* device memory, or host memory for HostMemory args */
+  int32_t on_host;               /* 1: `data` is host memory */
+  int32_t reserved;
+} itexb_tensor_t;
+
+typedef enum itexb_attr_type {
+  ITEXB_ATTR_INT = 0, ITEXB_ATTR_FLOAT = 1, ITEXB_ATTR_BOOL = 2, ITEXB_ATTR_STRING = 3,
+  ITEXB_ATTR_TYPE = 4, ITEXB_ATTR_INT_LIST = 5, ITEXB_ATTR_STRING_LIST = 6
+} itexb_attr_type_t;
+
+typedef struct itexb_attr {
+  const char* name;
+  int32_t type;                  /* itexb_attr_type_t */
+  int64_t i;                     /* INT, BOOL, TYPE (itexb_dtype_t) */
+  float f;                       /* FLOAT */
+  const char* s;                 /* STRING */
+  const int64_t* list_i;         /* INT_LIST */
+  const char* const* list_s;     /* STRING_LIST */
+  int32_t list_len;
+} itexb_attr_t;
+
+typedef struct itexb_op itexb_op_t;
+
+/* The op's view of one Compute call: what TF_GetInput / TF_AllocateOutput /
+ * TF_AllocateTemp / TF_GetStream give the reference's kernels
+ * (itex/core/utils/op_kernel.cc:117,338,441; op_kernel.h:404-407).
+ * allocate_output must set out->data for a tensor whose dtype/rank/dims/on_host the
+ * op has filled in; allocate_temp memory only needs to live until the work the op has
+ * enqueued on `stream` has run (the default context frees it stream-ordered).        */
+typedef struct itexb_op_context {
+  void* user;
+  int32_t num_inputs;
+  const itexb_tensor_t* inputs;
+  int32_t device_ordinal;
+  itexb_stream_t stream;
+  int (*allocate_output)(void* user, int index, itexb_tensor_t* out);
+  int (*allocate_temp)(void* user, size_t bytes, int on_host, void** ptr);
+} itexb_op_context_t;
+
+/* Names of the ops this library implements, NULL-terminated. */
+ITEXB_API const char* const* itexb_op_list(void);
+/* Input names and which inputs/outputs are HostMemory for an op (the lists of
+ * itex/core/kernels/gpu/quantize_op.cc:25-46, gpu/quantized_matmul.cc:53-102,
+ * gpu/quantized_conv_ops.cc:72-140).  Bit i of the masks = argument i.             */
+ITEXB_API int itexb_op_signature(const char* op_name, int* num_inputs, int* num_outputs,
+                                 uint32_t* host_input_mask, uint32_t* host_output_mask);
+ITEXB_API int itexb_op_create(const char* op_name, const itexb_attr_t* attrs, int num_attrs, itexb_op_t** op);
+ITEXB_API int itexb_op_compute(itexb_op_t* op, itexb_op_context_t* ctx);
+ITEXB_API void itexb_op_delete(itexb_op_t* op);
+
+/* A ready-made context over the runtime above: outputs and temps come from
+ * itexb_rt_allocate / itexb_rt_host_allocate.  Outputs stay valid until
+ * itexb_simple_context_reset or _destroy.                                           */
+typedef struct itexb_simple_context itexb_simple_context_t;
+ITEXB_API int itexb_simple_context_create(int device_ordinal, itexb_stream_t stream, itexb_simple_context_t** c);
+ITEXB_API itexb_op_context_t* itexb_simple_context_begin(itexb_simple_context_t* c, const itexb_tensor_t* inputs,
+                                                         int num_inputs);
+ITEXB_API int itexb_simple_context_num_outputs(itexb_simple_context_t* c);
+ITEXB_API const itexb_tensor_t* itexb_simple_context_output(itexb_simple_context_t* c, int index);
+ITEXB_API int itexb_simple_context_reset(itexb_simple_context_t* c);
+ITEXB_API void itexb_simple_context_destroy(itexb_simple_context_t* c);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* ITEXB200_H_ */

@@ -1,0 +1,145 @@
+// NHWC x HWIO int8 convolution for sm_100a, lowered onto the tcgen05 GEMM kernel.
+//
+// Two lowerings share the MMA main loop and the fused epilogue:
+//   * pointwise (1x1, stride 1, no padding, channels a multiple of 16): the input IS the
+//     [n*h*w, c] A operand; nothing is staged.
+//   * general: a gather kernel writes the [n*oh*ow, kh*kw*c_pad] patch matrix (zero fill
+//     for padding) into caller-provided scratch, 16 bytes per thread, then the GEMM runs
+//     on it.  Scratch traffic is kh*kw times the input; the caller sizes it with
+//     itexb_conv2d_workspace_bytes().
+#include <algorithm>
+
+#include "common.h"
+#include "gemm_sm100.h"
+
+namespace itexb {
+namespace {
+
+struct GatherArgs {
+  const uint8_t* x;
+  uint8_t* ws;
+  int n, h, w, c, kh, kw, oh, ow, c_pad;
+  int stride_h, stride_w, dil_h, dil_w, pad_top, pad_left;
+  long long m;       // n*oh*ow
+  int chunks;        // 16-byte chunks per patch row = kh*kw*c_pad/16
+};
+
+// One thread per 16-byte chunk of the patch matrix (c % 16 == 0 and c_pad == c).
+__global__ void __launch_bounds__(256) GatherPatchesVecKernel(GatherArgs a) {
+  const long long total = a.m * a.chunks;
+  const int cpt = a.c_pad >> 4;  // chunks per tap
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const long long pix = i / a.chunks;
+    const int ch = int(i - pix * a.chunks);
+    const int tap = ch / cpt, cc = ch - tap * cpt;
+    const int ky = tap / a.kw, kx = tap - ky * a.kw;
+    const int ox = int(pix % a.ow);
+    const int oy = int((pix / a.ow) % a.oh);
+    const int b = int(pix / ((long long)a.ow * a.oh));
+    const int iy = oy * a.stride_h + ky * a.dil_h - a.pad_top;
+    const int ix = ox * a.stride_w + kx * a.dil_w - a.pad_left;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (iy >= 0 && iy < a.h && ix >= 0 && ix < a.w)
+      v = __ldg(reinterpret_cast<const uint4*>(a.x + (((long long)b * a.h + iy) * a.w + ix) * a.c + cc * 16));
+    reinterpret_cast<uint4*>(a.ws)[i] = v;
+  }
+}
+
+// One thread per byte: any channel count (e.g. 3), channels >= c are zero.
+__global__ void __launch_bounds__(256) GatherPatchesScalarKernel(GatherArgs a) {
+  const long long kp = (long long)a.chunks * 16;
+  const long long total = a.m * kp;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const long long pix = i / kp;
+    const int kk = int(i - pix * kp);
+    const int tap = kk / a.c_pad, ci = kk - tap * a.c_pad;
+    const int ky = tap / a.kw, kx = tap - ky * a.kw;
+    const int ox = int(pix % a.ow);
+    const int oy = int((pix / a.ow) % a.oh);
+    const int b = int(pix / ((long long)a.ow * a.oh));
+    const int iy = oy * a.stride_h + ky * a.dil_h - a.pad_top;
+    const int ix = ox * a.stride_w + kx * a.dil_w - a.pad_left;
+    uint8_t v = 0;
+    if (ci < a.c && iy >= 0 && iy < a.h && ix >= 0 && ix < a.w) v = a.x[(((long long)b * a.h + iy) * a.w + ix) * a.c + ci];
+    a.ws[i] = v;
+  }
+}
+
+bool IsPointwise(const itexb_conv_params_t& p) {
+  return p.kh == 1 && p.kw == 1 && p.stride_h == 1 && p.stride_w == 1 && p.pad_top == 0 && p.pad_left == 0 &&
+         p.oh == p.h && p.ow == p.w && p.c % 16 == 0 && p.c_pad == p.c;
+}
+
+int Validate(const itexb_conv_params_t& p) {
+  ITEXB_REQUIRE(p.n >= 0 && p.h > 0 && p.w > 0 && p.c > 0 && p.kh > 0 && p.kw > 0 && p.co > 0, ITEXB_INVALID_ARGUMENT,
+                "conv2d: bad tensor dimensions");
+  ITEXB_REQUIRE(p.stride_h > 0 && p.stride_w > 0 && p.dil_h > 0 && p.dil_w > 0, ITEXB_INVALID_ARGUMENT,
+                "conv2d: strides and dilations must be positive");
+  ITEXB_REQUIRE(p.oh > 0 && p.ow > 0, ITEXB_INVALID_ARGUMENT, "conv2d: empty output");
+  ITEXB_REQUIRE(p.c_pad >= p.c && p.c_pad % 16 == 0, ITEXB_INVALID_ARGUMENT,
+                "conv2d: c_pad must be a multiple of 16 and >= c (got %d for c=%d)", p.c_pad, p.c);
+  ITEXB_REQUIRE(IsInt8(p.x_dtype), ITEXB_INVALID_ARGUMENT, "conv2d: input type %s is not qint8/quint8", DtypeName(p.x_dtype));
+  return ValidateEpilogue("conv2d", p.ep, p.out_dtype, false, p.co);
+}
+
+}  // namespace
+}  // namespace itexb
+
+using namespace itexb;
+
+extern "C" size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p) {
+  if (p == nullptr || IsPointwise(*p)) return 0;
+  return size_t(p->n) * p->oh * p->ow * size_t(p->kh) * p->kw * p->c_pad;
+}
+
+extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream) {
+  ITEXB_REQUIRE(p != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d: params is NULL");
+  ITEXB_RETURN_IF_ERROR(Validate(*p));
+  if (p->n == 0) return ITEXB_OK;
+  ITEXB_REQUIRE(p->x && p->filter_packed && p->out, ITEXB_INVALID_ARGUMENT, "conv2d: NULL tensor");
+  cudaStream_t st = AsCuda(stream);
+  const long long m = (long long)p->n * p->oh * p->ow;
+  ITEXB_REQUIRE(m < (1ll << 31), ITEXB_INVALID_ARGUMENT, "conv2d: more than 2^31 output pixels");
+  const int kp = p->kh * p->kw * p->c_pad;
+  const void* a_ptr = p->x;
+  if (!IsPointwise(*p)) {
+    ITEXB_REQUIRE(p->workspace != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d: workspace of %zu bytes is required",
+                  itexb_conv2d_workspace_bytes(p));
+    ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0, ITEXB_INVALID_ARGUMENT,
+                  "conv2d: workspace must be 16-byte aligned");
+    GatherArgs a{};
+    a.x = static_cast<const uint8_t*>(p->x);
+    a.ws = static_cast<uint8_t*>(p->workspace);
+    a.n = p->n; a.h = p->h; a.w = p->w; a.c = p->c; a.kh = p->kh; a.kw = p->kw; a.oh = p->oh; a.ow = p->ow; a.c_pad = p->c_pad;
+    a.stride_h = p->stride_h; a.stride_w = p->stride_w; a.dil_h = p->dil_h; a.dil_w = p->dil_w;
+    a.pad_top = p->pad_top; a.pad_left = p->pad_left;
+    a.m = m;
+    a.chunks = kp / 16;
+    const bool vec = p->c % 16 == 0 && p->c_pad == p->c && (reinterpret_cast<uintptr_t>(p->x) & 15) == 0;
+    const long long work = vec ? m * a.chunks : m * (long long)kp;
+    const int blocks = int(std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)SmCount() * 32)));
+    if (vec) GatherPatchesVecKernel<<<blocks, 256, 0, st>>>(a);
+    else GatherPatchesScalarKernel<<<blocks, 256, 0, st>>>(a);
+    ITEXB_RETURN_IF_ERROR(CheckLaunch("GatherPatchesKernel"));
+    a_ptr = p->workspace;
+  } else {
+    ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->x) & 15) == 0, ITEXB_INVALID_ARGUMENT, "conv2d: input must be 16-byte aligned");
+  }
+  ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->filter_packed) & 15) == 0, ITEXB_INVALID_ARGUMENT,
+                "conv2d: packed filter must be 16-byte aligned");
+  CUtensorMap ta, tb;
+  const int bn = PickBN(p->co);
+  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, kp, kp, 128));
+  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->filter_packed, p->co, kp, kp, bn));
+  GemmArgs g{};
+  g.m = int(m); g.n = p->co; g.k = kp;
+  g.out_dtype = p->out_dtype;
+  g.out = p->out; g.ldo = p->co;
+  g.ep = p->ep;
+  if (g.ep.summand != nullptr && g.ep.ld_summand == 0) g.ep.ld_summand = p->co;
+  g.status_word = p->status_word;
+  g.idesc = MakeInstrDesc(p->x_dtype, ITEXB_DT_QINT8, bn);
+  const int osz = p->ep.raw_acc ? 4 : DtypeSize(p->out_dtype);
+  g.vec_store = ((reinterpret_cast<uintptr_t>(p->out) & 15) == 0 && ((long long)p->co * osz) % 16 == 0) ? 1 : 0;
+  return LaunchGemm(ta, tb, g, bn, false, st);
+}

@@ -1,0 +1,38 @@
+// Internal interface of the tcgen05 GEMM / implicit-GEMM convolution kernels.
+#ifndef ITEXB_CSRC_GEMM_SM100_H_
+#define ITEXB_CSRC_GEMM_SM100_H_
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "itexb200.h"
+
+namespace itexb {
+
+// Kernel argument block (by value in parameter space).
+struct GemmArgs {
+  int m, n, k;          // k in bytes = elements (8-bit operands)
+  int out_dtype;
+  void* out;
+  long long ldo;        // elements
+  itexb_epilogue_t ep;
+  int* status_word;     // set non-zero when a bounded wait expired
+  unsigned idesc;       // tcgen05 instruction descriptor
+  int vec_store;        // output rows are 16-byte aligned
+  // Implicit-GEMM convolution (conv_taps > 0): row m of A is output pixel m of an NHWC
+  // tensor, k-block kb reads filter tap kb / kb_per_tap, channel block kb % kb_per_tap.
+  int conv_taps, kb_per_tap, kw, oh, ow;
+  int stride_h, stride_w, dil_h, dil_w, pad_top, pad_left;
+};
+
+// 2-D tiled tensor map over a K-major 8-bit operand: dims {k, rows}, row pitch `ld` bytes,
+// box {128 bytes, box_rows}, 128-byte swizzle, zero fill outside.
+int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
+unsigned MakeInstrDesc(int a_dtype, int b_dtype, int bn);
+int PickBN(int n);
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st);
+int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n);
+
+}  // namespace itexb
+
+#endif  // ITEXB_CSRC_GEMM_SM100_H_

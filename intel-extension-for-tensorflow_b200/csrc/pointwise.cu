@@ -1,0 +1,738 @@
+// HBM-bound element-wise kernels of libitexb200 for sm_100a: QuantizeV2, Dequantize,
+// FP8 quantize / dequantize, device-side range reduction, delayed-scaling update and
+// the one-time weight / filter packers.
+//
+// Layout rule shared by the streaming kernels: a thread owns 16 consecutive elements,
+// so the 1-byte side moves as one 16-byte vector and the wide side as 2-4 of them;
+// a warp therefore touches 512 contiguous bytes of int8 and 1-2 KiB of fp16/fp32 per
+// instruction group.  fp32 multiply and add are kept separate (the library is built
+// with -fmad=false) so results match a CPU that does not contract.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <algorithm>
+#include <cfloat>
+
+#include "common.h"
+
+namespace itexb {
+namespace {
+
+constexpr int kVec = 16;        // elements per thread
+constexpr int kThreads = 256;
+
+// ---- scalar conversions -----------------------------------------------------------
+template <typename T> __device__ __forceinline__ float ToFloat(T v);
+template <> __device__ __forceinline__ float ToFloat<float>(float v) { return v; }
+template <> __device__ __forceinline__ float ToFloat<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float ToFloat<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T FromFloat(float v);
+template <> __device__ __forceinline__ float FromFloat<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 FromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half FromFloat<__half>(float v) { return __float2half_rn(v); }
+
+// Saturate to [lo, hi] then round to nearest even.  NaN converts to 0.
+template <bool SIGNED> __device__ __forceinline__ int SatRne8(float f) {
+  constexpr float lo = SIGNED ? -128.f : 0.f;
+  constexpr float hi = SIGNED ? 127.f : 255.f;
+  f = f < lo ? lo : (f > hi ? hi : f);
+  return __float2int_rn(f);
+}
+
+// ---- 16-element vector load / store -----------------------------------------------
+template <typename T> struct Vec16 { float v[kVec]; };
+
+template <typename T> __device__ __forceinline__ void Load16(const T* p, float (&out)[kVec]);
+template <> __device__ __forceinline__ void Load16<float>(const float* p, float (&out)[kVec]) {
+  const float4* p4 = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 t = __ldcs(p4 + i);
+    out[4 * i + 0] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w;
+  }
+}
+template <> __device__ __forceinline__ void Load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&out)[kVec]) {
+  const uint4* p4 = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 t = __ldcs(p4 + i);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      out[8 * i + 2 * j + 0] = __uint_as_float(w[j] << 16);
+      out[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+}
+template <> __device__ __forceinline__ void Load16<__half>(const __half* p, float (&out)[kVec]) {
+  const uint4* p4 = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 t = __ldcs(p4 + i);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+      float2 f = __half22float2(h);
+      out[8 * i + 2 * j + 0] = f.x;
+      out[8 * i + 2 * j + 1] = f.y;
+    }
+  }
+}
+
+template <typename T> __device__ __forceinline__ void Store16(T* p, const float (&in)[kVec]);
+template <> __device__ __forceinline__ void Store16<float>(float* p, const float (&in)[kVec]) {
+  float4* p4 = reinterpret_cast<float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) __stcs(p4 + i, make_float4(in[4 * i], in[4 * i + 1], in[4 * i + 2], in[4 * i + 3]));
+}
+template <> __device__ __forceinline__ void Store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&in)[kVec]) {
+  uint4* p4 = reinterpret_cast<uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(in[8 * i + 2 * j], in[8 * i + 2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    __stcs(p4 + i, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+template <> __device__ __forceinline__ void Store16<__half>(__half* p, const float (&in)[kVec]) {
+  uint4* p4 = reinterpret_cast<uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 h = __floats2half2_rn(in[8 * i + 2 * j], in[8 * i + 2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    __stcs(p4 + i, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+__device__ __forceinline__ void StoreBytes16(void* p, const int (&q)[kVec]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    w[j] = uint32_t(q[4 * j] & 0xff) | (uint32_t(q[4 * j + 1] & 0xff) << 8) | (uint32_t(q[4 * j + 2] & 0xff) << 16) |
+           (uint32_t(q[4 * j + 3] & 0xff) << 24);
+  __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
+}
+
+template <bool SIGNED> __device__ __forceinline__ void LoadBytes16(const void* p, float (&out)[kVec]) {
+  uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t byte = (w[j] >> (8 * b)) & 0xff;
+      out[4 * j + b] = SIGNED ? float(int(int8_t(byte))) : float(byte);
+    }
+}
+
+struct SliceArgs {
+  const float* scale;
+  const float* shift;
+  float scale_host;
+  float shift_host;
+  long long inner;
+  long long nslice;
+};
+
+__device__ __forceinline__ void SliceConsts(const SliceArgs& a, long long i, float* s, float* sh) {
+  if (a.nslice <= 1) {
+    *s = a.scale ? __ldg(a.scale) : a.scale_host;
+    *sh = a.shift ? __ldg(a.shift) : a.shift_host;
+  } else {
+    const long long c = (i / a.inner) % a.nslice;
+    *s = __ldg(a.scale + c);
+    *sh = a.shift ? __ldg(a.shift + c) : a.shift_host;
+  }
+}
+
+template <int KIND> __device__ __forceinline__ float QuantAffine(float x, float s, float sh) {
+  float f = __fmul_rn(x, s);
+  if (KIND == ITEXB_QUANT_MIN_FIRST_LEGACY) f = __fadd_rn(f, __fmul_rn(sh, s));
+  if (KIND == ITEXB_QUANT_MIN_FIRST_CLASSIC) f = __fadd_rn(f, sh);
+  return f;
+}
+
+// q = sat(rne(affine(x)))
+// VEC: pointers 16-byte aligned; a 16-element group shares one slice when UNIFORM.
+template <typename TX, bool SIGNED, int KIND, bool UNIFORM>
+__global__ void __launch_bounds__(kThreads) QuantizeKernel(const TX* __restrict__ x, uint8_t* __restrict__ q, long long n,
+                                                           SliceArgs a) {
+  const long long g = (long long)blockIdx.x * kThreads + threadIdx.x;
+  const long long i0 = g * kVec;
+  if (i0 >= n) return;
+  if (i0 + kVec <= n) {
+    float v[kVec];
+    int r[kVec];
+    Load16<TX>(x + i0, v);
+    if (UNIFORM) {
+      float s, sh;
+      SliceConsts(a, i0, &s, &sh);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) r[j] = SatRne8<SIGNED>(QuantAffine<KIND>(v[j], s, sh));
+    } else {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        float s, sh;
+        SliceConsts(a, i0 + j, &s, &sh);
+        r[j] = SatRne8<SIGNED>(QuantAffine<KIND>(v[j], s, sh));
+      }
+    }
+    StoreBytes16(q + i0, r);
+  } else {
+    for (long long i = i0; i < n; ++i) {
+      float s, sh;
+      SliceConsts(a, i, &s, &sh);
+      q[i] = uint8_t(SatRne8<SIGNED>(QuantAffine<KIND>(ToFloat<TX>(x[i]), s, sh)));
+    }
+  }
+}
+
+// Same arithmetic, one element per thread: used when a pointer is not 16-byte aligned.
+template <typename TX, bool SIGNED, int KIND>
+__global__ void __launch_bounds__(kThreads) QuantizeScalarKernel(const TX* __restrict__ x, uint8_t* __restrict__ q, long long n,
+                                                                 SliceArgs a) {
+  long long i = (long long)blockIdx.x * kThreads + threadIdx.x;
+  const long long stride = (long long)gridDim.x * kThreads;
+  for (; i < n; i += stride) {
+    float s, sh;
+    SliceConsts(a, i, &s, &sh);
+    q[i] = uint8_t(SatRne8<SIGNED>(QuantAffine<KIND>(ToFloat<TX>(x[i]), s, sh)));
+  }
+}
+
+// y = T((float(q) - zp) * s)
+template <typename TY, bool SIGNED, bool UNIFORM>
+__global__ void __launch_bounds__(kThreads) DequantizeKernel(const uint8_t* __restrict__ q, TY* __restrict__ y, long long n,
+                                                             SliceArgs a) {
+  const long long g = (long long)blockIdx.x * kThreads + threadIdx.x;
+  const long long i0 = g * kVec;
+  if (i0 >= n) return;
+  if (i0 + kVec <= n) {
+    float v[kVec];
+    LoadBytes16<SIGNED>(q + i0, v);
+    if (UNIFORM) {
+      float s, zp;
+      SliceConsts(a, i0, &s, &zp);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) v[j] = __fmul_rn(__fsub_rn(v[j], zp), s);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        float s, zp;
+        SliceConsts(a, i0 + j, &s, &zp);
+        v[j] = __fmul_rn(__fsub_rn(v[j], zp), s);
+      }
+    }
+    Store16<TY>(y + i0, v);
+  } else {
+    for (long long i = i0; i < n; ++i) {
+      float s, zp;
+      SliceConsts(a, i, &s, &zp);
+      const float f = SIGNED ? float(int(int8_t(q[i]))) : float(q[i]);
+      y[i] = FromFloat<TY>(__fmul_rn(__fsub_rn(f, zp), s));
+    }
+  }
+}
+
+template <typename TY, bool SIGNED>
+__global__ void __launch_bounds__(kThreads) DequantizeScalarKernel(const uint8_t* __restrict__ q, TY* __restrict__ y,
+                                                                   long long n, SliceArgs a) {
+  long long i = (long long)blockIdx.x * kThreads + threadIdx.x;
+  const long long stride = (long long)gridDim.x * kThreads;
+  for (; i < n; i += stride) {
+    float s, zp;
+    SliceConsts(a, i, &s, &zp);
+    const float f = SIGNED ? float(int(int8_t(q[i]))) : float(q[i]);
+    y[i] = FromFloat<TY>(__fmul_rn(__fsub_rn(f, zp), s));
+  }
+}
+
+inline bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline int GridFor(long long n_groups) { return int((n_groups + kThreads - 1) / kThreads); }
+
+template <typename TX, bool SIGNED, int KIND>
+int LaunchQuantize(const void* x, void* q, long long n, const SliceArgs& a, cudaStream_t st) {
+  const TX* xp = static_cast<const TX*>(x);
+  uint8_t* qp = static_cast<uint8_t*>(q);
+  if (!Aligned16(x) || !Aligned16(q)) {
+    const int blocks = int(std::min<long long>((n + kThreads - 1) / kThreads, (long long)SmCount() * 16));
+    QuantizeScalarKernel<TX, SIGNED, KIND><<<blocks, kThreads, 0, st>>>(xp, qp, n, a);
+    return CheckLaunch("QuantizeScalarKernel");
+  }
+  const long long groups = (n + kVec - 1) / kVec;
+  const bool uniform = a.nslice <= 1 || (a.inner % kVec) == 0;
+  if (uniform)
+    QuantizeKernel<TX, SIGNED, KIND, true><<<GridFor(groups), kThreads, 0, st>>>(xp, qp, n, a);
+  else
+    QuantizeKernel<TX, SIGNED, KIND, false><<<GridFor(groups), kThreads, 0, st>>>(xp, qp, n, a);
+  return CheckLaunch("QuantizeKernel");
+}
+
+template <typename TX, bool SIGNED>
+int DispatchQuantKind(int kind, const void* x, void* q, long long n, const SliceArgs& a, cudaStream_t st) {
+  switch (kind) {
+    case ITEXB_QUANT_SCALED: return LaunchQuantize<TX, SIGNED, ITEXB_QUANT_SCALED>(x, q, n, a, st);
+    case ITEXB_QUANT_MIN_FIRST_LEGACY: return LaunchQuantize<TX, SIGNED, ITEXB_QUANT_MIN_FIRST_LEGACY>(x, q, n, a, st);
+    case ITEXB_QUANT_MIN_FIRST_CLASSIC: return LaunchQuantize<TX, SIGNED, ITEXB_QUANT_MIN_FIRST_CLASSIC>(x, q, n, a, st);
+    default: return SetError(ITEXB_INVALID_ARGUMENT, "quantize: unknown kind %d", kind);
+  }
+}
+
+template <typename TY, bool SIGNED>
+int LaunchDequantize(const void* q, void* y, long long n, const SliceArgs& a, cudaStream_t st) {
+  const uint8_t* qp = static_cast<const uint8_t*>(q);
+  TY* yp = static_cast<TY*>(y);
+  if (!Aligned16(q) || !Aligned16(y)) {
+    const int blocks = int(std::min<long long>((n + kThreads - 1) / kThreads, (long long)SmCount() * 16));
+    DequantizeScalarKernel<TY, SIGNED><<<blocks, kThreads, 0, st>>>(qp, yp, n, a);
+    return CheckLaunch("DequantizeScalarKernel");
+  }
+  const long long groups = (n + kVec - 1) / kVec;
+  const bool uniform = a.nslice <= 1 || (a.inner % kVec) == 0;
+  if (uniform)
+    DequantizeKernel<TY, SIGNED, true><<<GridFor(groups), kThreads, 0, st>>>(qp, yp, n, a);
+  else
+    DequantizeKernel<TY, SIGNED, false><<<GridFor(groups), kThreads, 0, st>>>(qp, yp, n, a);
+  return CheckLaunch("DequantizeKernel");
+}
+
+int CheckSliceArgs(const char* who, int64_t n, int64_t inner, int64_t nslice, const float* scale) {
+  ITEXB_REQUIRE(n >= 0, ITEXB_INVALID_ARGUMENT, "%s: negative element count", who);
+  ITEXB_REQUIRE(nslice >= 1 && inner >= 1, ITEXB_INVALID_ARGUMENT, "%s: inner and nslice must be >= 1", who);
+  ITEXB_REQUIRE(nslice == 1 || scale != nullptr, ITEXB_INVALID_ARGUMENT,
+                "%s: a device scale vector is required when nslice > 1", who);
+  return ITEXB_OK;
+}
+
+// ---- float atomics on ordered bit patterns -----------------------------------------
+__device__ __forceinline__ void AtomicMaxFloat(float* addr, float v) {
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+__device__ __forceinline__ void AtomicMinFloat(float* addr, float v) {
+  if (v >= 0.f) atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+__device__ __forceinline__ float WarpMax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float WarpMin(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__global__ void MinMaxInitKernel(float* mm) {
+  mm[0] = __int_as_float(0x7f800000);
+  mm[1] = __int_as_float(0xff800000);
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(kThreads) MinMaxKernel(const TX* __restrict__ x, long long n, float* __restrict__ mm,
+                                                         bool vec) {
+  float lo = __int_as_float(0x7f800000), hi = __int_as_float(0xff800000);
+  const long long stride = (long long)gridDim.x * kThreads;
+  if (vec) {
+    const long long groups = n / kVec;
+    for (long long g = (long long)blockIdx.x * kThreads + threadIdx.x; g < groups; g += stride) {
+      float v[kVec];
+      Load16<TX>(x + g * kVec, v);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) { lo = fminf(lo, v[j]); hi = fmaxf(hi, v[j]); }
+    }
+    for (long long i = groups * kVec + (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+      const float f = ToFloat<TX>(x[i]);
+      lo = fminf(lo, f); hi = fmaxf(hi, f);
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+      const float f = ToFloat<TX>(x[i]);
+      lo = fminf(lo, f); hi = fmaxf(hi, f);
+    }
+  }
+  __shared__ float s_lo[kThreads / 32], s_hi[kThreads / 32];
+  lo = WarpMin(lo); hi = WarpMax(hi);
+  if ((threadIdx.x & 31) == 0) { s_lo[threadIdx.x >> 5] = lo; s_hi[threadIdx.x >> 5] = hi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    lo = threadIdx.x < kThreads / 32 ? s_lo[threadIdx.x] : __int_as_float(0x7f800000);
+    hi = threadIdx.x < kThreads / 32 ? s_hi[threadIdx.x] : __int_as_float(0xff800000);
+    lo = WarpMin(lo); hi = WarpMax(hi);
+    if (threadIdx.x == 0) { AtomicMinFloat(mm, lo); AtomicMaxFloat(mm + 1, hi); }
+  }
+}
+
+// Host math of QuantizeV2 SCALED restated on the device for a device-resident range:
+// AdjustInputMinMaxRange then GetScaleAndZeropointAndAlignMinMax (quantize branch).
+__device__ __forceinline__ void DynamicScale(const float* mm, float emr, bool is_signed, float* scale, float* omin,
+                                             float* omax) {
+  const float min_in = mm[0], max_in = mm[1];
+  const float adj_min = fminf(0.f, min_in);
+  const float eps = __fmul_rn(fmaxf(1.f, fmaxf(fabsf(min_in), fabsf(max_in))), emr);
+  const float adj_max = fmaxf(0.f, fmaxf(max_in, __fadd_rn(adj_min, eps)));
+  const float abs_range = fmaxf(fabsf(adj_min), fabsf(adj_max));
+  *scale = __fdiv_rn(is_signed ? 127.f : 255.f, abs_range);
+  *omin = is_signed ? -abs_range : 0.f;
+  *omax = abs_range;
+}
+
+template <typename TX, bool SIGNED>
+__global__ void __launch_bounds__(kThreads) QuantizeDynamicKernel(const TX* __restrict__ x, uint8_t* __restrict__ q,
+                                                                  long long n, const float* __restrict__ mm, float emr,
+                                                                  float* __restrict__ out3) {
+  float s, omin, omax;
+  DynamicScale(mm, emr, SIGNED, &s, &omin, &omax);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && out3 != nullptr) { out3[0] = s; out3[1] = omin; out3[2] = omax; }
+  const long long i0 = ((long long)blockIdx.x * kThreads + threadIdx.x) * kVec;
+  if (i0 >= n) return;
+  if (i0 + kVec <= n) {
+    float v[kVec];
+    int r[kVec];
+    Load16<TX>(x + i0, v);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) r[j] = SatRne8<SIGNED>(__fmul_rn(v[j], s));
+    StoreBytes16(q + i0, r);
+  } else {
+    for (long long i = i0; i < n; ++i) q[i] = uint8_t(SatRne8<SIGNED>(__fmul_rn(ToFloat<TX>(x[i]), s)));
+  }
+}
+
+// ---- FP8 ----------------------------------------------------------------------------
+template <bool E4M3> __device__ __forceinline__ uint8_t FloatToFp8Sat(float f) {
+  return (uint8_t)__nv_cvt_float_to_fp8(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
+}
+template <bool E4M3> __device__ __forceinline__ float Fp8ToFloat(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, E4M3 ? __NV_E4M3 : __NV_E5M2);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// y = fp8(float(x) * scale[0]); amax[0] = max(amax[0], max|x|)
+template <typename TX, bool E4M3>
+__global__ void __launch_bounds__(kThreads) Fp8QuantizeKernel(const TX* __restrict__ x, uint8_t* __restrict__ y, long long n,
+                                                              const float* __restrict__ scale, float* __restrict__ amax,
+                                                              bool vec) {
+  const float s = __ldg(scale);
+  float m = 0.f;
+  const long long stride = (long long)gridDim.x * kThreads;
+  if (vec) {
+    const long long groups = n / kVec;
+    for (long long g = (long long)blockIdx.x * kThreads + threadIdx.x; g < groups; g += stride) {
+      float v[kVec];
+      int r[kVec];
+      Load16<TX>(x + g * kVec, v);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        m = fmaxf(m, fabsf(v[j]));
+        r[j] = FloatToFp8Sat<E4M3>(__fmul_rn(v[j], s));
+      }
+      StoreBytes16(y + g * kVec, r);
+    }
+    for (long long i = groups * kVec + (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+      const float f = ToFloat<TX>(x[i]);
+      m = fmaxf(m, fabsf(f));
+      y[i] = FloatToFp8Sat<E4M3>(__fmul_rn(f, s));
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+      const float f = ToFloat<TX>(x[i]);
+      m = fmaxf(m, fabsf(f));
+      y[i] = FloatToFp8Sat<E4M3>(__fmul_rn(f, s));
+    }
+  }
+  if (amax == nullptr) return;
+  __shared__ float s_m[kThreads / 32];
+  m = WarpMax(m);
+  if ((threadIdx.x & 31) == 0) s_m[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = threadIdx.x < kThreads / 32 ? s_m[threadIdx.x] : 0.f;
+    m = WarpMax(m);
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));  // m >= 0
+  }
+}
+
+template <typename TY, bool E4M3>
+__global__ void __launch_bounds__(kThreads) Fp8DequantizeKernel(const uint8_t* __restrict__ x, TY* __restrict__ y, long long n,
+                                                                const float* __restrict__ scale_inv, bool vec) {
+  const float s = __ldg(scale_inv);
+  const long long stride = (long long)gridDim.x * kThreads;
+  long long start = 0;
+  if (vec) {
+    const long long groups = n / kVec;
+    for (long long g = (long long)blockIdx.x * kThreads + threadIdx.x; g < groups; g += stride) {
+      uint4 t = __ldcs(reinterpret_cast<const uint4*>(x + g * kVec));
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+      float v[kVec];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) v[4 * j + b] = __fmul_rn(Fp8ToFloat<E4M3>(uint8_t((w[j] >> (8 * b)) & 0xff)), s);
+      Store16<TY>(y + g * kVec, v);
+    }
+    start = groups * kVec;
+  }
+  for (long long i = start + (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+    y[i] = FromFloat<TY>(__fmul_rn(Fp8ToFloat<E4M3>(x[i]), s));
+}
+
+// One thread per meta slot.  floor(log2(.)) is taken on the fp32-rounded logarithm like
+// the TensorFlow expression it restates; 2^|exp| is exact for integer exponents.
+__global__ void Fp8AmaxScaleUpdateKernel(float* __restrict__ hist, float* __restrict__ scale, float* __restrict__ scale_inv,
+                                         int hlen, int n, float fp8_max, float margin, int algo) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  float amax = hist[j];
+  if (algo == 0)
+    for (int r = 1; r < hlen; ++r) amax = fmaxf(amax, hist[(long long)r * n + j]);
+  const float old = scale[j];
+  const float ratio = __fdiv_rn(fp8_max, amax);
+  const float lg = float(log2(double(ratio)));
+  const float e = __fsub_rn(floorf(lg), margin);
+  float sf = rintf(exp2f(fabsf(e)));
+  sf = (amax > 0.f) ? sf : old;
+  sf = (isfinite(amax)) ? sf : old;
+  sf = (e < 0.f) ? __fdiv_rn(1.f, sf) : sf;
+  // roll(-1, axis 0): row r takes row r+1, last row takes row 0; then row 0 is zeroed.
+  const float first = hist[j];
+  for (int r = 0; r + 1 < hlen; ++r) hist[(long long)r * n + j] = hist[(long long)(r + 1) * n + j];
+  hist[(long long)(hlen - 1) * n + j] = first;
+  hist[j] = 0.f;
+  scale[j] = sf;
+  scale_inv[j] = __fdiv_rn(1.f, sf);
+}
+
+// ---- one-time packers ---------------------------------------------------------------
+// [k,n] -> [n,k_pad] through a 64x64 shared tile (+4 bytes of row padding against bank conflicts).
+__global__ void __launch_bounds__(256) PackWeightsKnKernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                           long long k, long long n, long long k_pad) {
+  __shared__ uint8_t tile[64][68];
+  const long long k0 = (long long)blockIdx.y * 64, n0 = (long long)blockIdx.x * 64;
+  for (int t = threadIdx.x; t < 64 * 64; t += 256) {
+    const int r = t >> 6, c = t & 63;  // r: k, c: n (coalesced along n)
+    const long long kk = k0 + r, nn = n0 + c;
+    tile[r][c] = (kk < k && nn < n) ? src[kk * n + nn] : uint8_t(0);
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < 64 * 64; t += 256) {
+    const int r = t >> 6, c = t & 63;  // r: n, c: k (coalesced along k)
+    const long long nn = n0 + r, kk = k0 + c;
+    if (nn < n && kk < k_pad) dst[nn * k_pad + kk] = tile[c][r];
+  }
+}
+
+__global__ void ColsumS8Kernel(const int8_t* __restrict__ b, int32_t* __restrict__ colsum, long long k, long long n) {
+  const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  int s = 0;
+  for (long long i = 0; i < k; ++i) s += int(b[i * n + j]);
+  colsum[j] = s;
+}
+
+// HWIO [kh,kw,c,co] -> [co][kh*kw][c_pad]
+__global__ void PackFilterKernel(const uint8_t* __restrict__ f, uint8_t* __restrict__ dst, int taps, int c, int co, int c_pad) {
+  const long long total = (long long)co * taps * c_pad;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int ci = int(i % c_pad);
+    const int t = int((i / c_pad) % taps);
+    const int o = int(i / ((long long)c_pad * taps));
+    dst[i] = ci < c ? f[((long long)t * c + ci) * co + o] : uint8_t(0);
+  }
+}
+
+}  // namespace
+}  // namespace itexb
+
+using namespace itexb;
+
+extern "C" {
+
+int itexb_quantize(const void* x, int x_dtype, void* q, int q_dtype, int64_t n, int64_t inner, int64_t nslice, int kind,
+                   const float* scale, const float* shift, float scale_host, float shift_host, itexb_stream_t stream) {
+  ITEXB_RETURN_IF_ERROR(CheckSliceArgs("quantize", n, inner, nslice, scale));
+  ITEXB_REQUIRE(IsInt8(q_dtype), ITEXB_INVALID_ARGUMENT, "quantize: output type %s is not qint8/quint8", DtypeName(q_dtype));
+  if (n == 0) return ITEXB_OK;
+  ITEXB_REQUIRE(x != nullptr && q != nullptr, ITEXB_INVALID_ARGUMENT, "quantize: NULL tensor");
+  SliceArgs a{scale, shift, scale_host, shift_host, (long long)inner, (long long)nslice};
+  cudaStream_t st = AsCuda(stream);
+  const bool sg = IsSigned8(q_dtype);
+  switch (x_dtype) {
+    case ITEXB_DT_FLOAT:
+      return sg ? DispatchQuantKind<float, true>(kind, x, q, n, a, st) : DispatchQuantKind<float, false>(kind, x, q, n, a, st);
+    case ITEXB_DT_BFLOAT16:
+      return sg ? DispatchQuantKind<__nv_bfloat16, true>(kind, x, q, n, a, st)
+                : DispatchQuantKind<__nv_bfloat16, false>(kind, x, q, n, a, st);
+    case ITEXB_DT_HALF:
+      return sg ? DispatchQuantKind<__half, true>(kind, x, q, n, a, st) : DispatchQuantKind<__half, false>(kind, x, q, n, a, st);
+    default:
+      return SetError(ITEXB_INVALID_ARGUMENT, "quantize: input type %s is not float/bfloat16/half", DtypeName(x_dtype));
+  }
+}
+
+int itexb_dequantize(const void* q, int q_dtype, void* y, int y_dtype, int64_t n, int64_t inner, int64_t nslice,
+                     const float* scale, const float* zp, float scale_host, float zp_host, itexb_stream_t stream) {
+  ITEXB_RETURN_IF_ERROR(CheckSliceArgs("dequantize", n, inner, nslice, scale));
+  ITEXB_REQUIRE(IsInt8(q_dtype), ITEXB_INVALID_ARGUMENT, "dequantize: input type %s is not qint8/quint8", DtypeName(q_dtype));
+  if (n == 0) return ITEXB_OK;
+  ITEXB_REQUIRE(q != nullptr && y != nullptr, ITEXB_INVALID_ARGUMENT, "dequantize: NULL tensor");
+  SliceArgs a{scale, zp, scale_host, zp_host, (long long)inner, (long long)nslice};
+  cudaStream_t st = AsCuda(stream);
+  const bool sg = IsSigned8(q_dtype);
+  switch (y_dtype) {
+    case ITEXB_DT_FLOAT:
+      return sg ? LaunchDequantize<float, true>(q, y, n, a, st) : LaunchDequantize<float, false>(q, y, n, a, st);
+    case ITEXB_DT_BFLOAT16:
+      return sg ? LaunchDequantize<__nv_bfloat16, true>(q, y, n, a, st) : LaunchDequantize<__nv_bfloat16, false>(q, y, n, a, st);
+    case ITEXB_DT_HALF:
+      return sg ? LaunchDequantize<__half, true>(q, y, n, a, st) : LaunchDequantize<__half, false>(q, y, n, a, st);
+    default:
+      return SetError(ITEXB_INVALID_ARGUMENT, "dequantize: output type %s is not float/bfloat16/half", DtypeName(y_dtype));
+  }
+}
+
+int itexb_minmax_init(float* minmax, itexb_stream_t stream) {
+  ITEXB_REQUIRE(minmax != nullptr, ITEXB_INVALID_ARGUMENT, "minmax_init: NULL pointer");
+  MinMaxInitKernel<<<1, 1, 0, AsCuda(stream)>>>(minmax);
+  return CheckLaunch("MinMaxInitKernel");
+}
+
+int itexb_minmax(const void* x, int x_dtype, int64_t n, float* minmax, itexb_stream_t stream) {
+  ITEXB_REQUIRE(minmax != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "minmax: bad arguments");
+  if (n == 0) return ITEXB_OK;
+  const bool vec = Aligned16(x);
+  const long long work = vec ? (n + kVec - 1) / kVec : n;
+  const int blocks = int(std::max<long long>(1, std::min<long long>((work + kThreads - 1) / kThreads, (long long)SmCount() * 8)));
+  cudaStream_t st = AsCuda(stream);
+  if (x_dtype == ITEXB_DT_FLOAT)
+    MinMaxKernel<float><<<blocks, kThreads, 0, st>>>(static_cast<const float*>(x), n, minmax, vec);
+  else if (x_dtype == ITEXB_DT_BFLOAT16)
+    MinMaxKernel<__nv_bfloat16><<<blocks, kThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, minmax, vec);
+  else
+    return SetError(ITEXB_INVALID_ARGUMENT, "minmax: input type %s is not float/bfloat16", DtypeName(x_dtype));
+  return CheckLaunch("MinMaxKernel");
+}
+
+int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_dtype, int64_t n, const float* minmax,
+                           float ensure_minimum_range, float* out3, itexb_stream_t stream) {
+  ITEXB_REQUIRE(IsInt8(q_dtype), ITEXB_INVALID_ARGUMENT, "quantize_dynamic: output type %s is not qint8/quint8",
+                DtypeName(q_dtype));
+  ITEXB_REQUIRE(minmax != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "quantize_dynamic: bad arguments");
+  ITEXB_REQUIRE(Aligned16(x) && Aligned16(q), ITEXB_INVALID_ARGUMENT, "quantize_dynamic: tensors must be 16-byte aligned");
+  if (n == 0) return ITEXB_OK;
+  const int grid = GridFor((n + kVec - 1) / kVec);
+  cudaStream_t st = AsCuda(stream);
+  const bool sg = IsSigned8(q_dtype);
+  uint8_t* qp = static_cast<uint8_t*>(q);
+  if (x_dtype == ITEXB_DT_FLOAT) {
+    auto xp = static_cast<const float*>(x);
+    if (sg) QuantizeDynamicKernel<float, true><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
+    else QuantizeDynamicKernel<float, false><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
+  } else if (x_dtype == ITEXB_DT_BFLOAT16) {
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    if (sg) QuantizeDynamicKernel<__nv_bfloat16, true><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
+    else QuantizeDynamicKernel<__nv_bfloat16, false><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
+  } else {
+    return SetError(ITEXB_INVALID_ARGUMENT, "quantize_dynamic: input type %s is not float/bfloat16", DtypeName(x_dtype));
+  }
+  return CheckLaunch("QuantizeDynamicKernel");
+}
+
+int itexb_pack_weights_kn(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad, itexb_stream_t stream) {
+  ITEXB_REQUIRE(b_kn != nullptr && b_nk != nullptr && k > 0 && n > 0 && k_pad >= k, ITEXB_INVALID_ARGUMENT,
+                "pack_weights_kn: bad arguments");
+  dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k_pad + 63) / 64));
+  PackWeightsKnKernel<<<grid, 256, 0, AsCuda(stream)>>>(static_cast<const uint8_t*>(b_kn), static_cast<uint8_t*>(b_nk), k, n, k_pad);
+  return CheckLaunch("PackWeightsKnKernel");
+}
+
+int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, int64_t n, itexb_stream_t stream) {
+  ITEXB_REQUIRE(b_kn != nullptr && colsum != nullptr && k > 0 && n > 0, ITEXB_INVALID_ARGUMENT, "colsum_s8: bad arguments");
+  ColsumS8Kernel<<<(unsigned)((n + 127) / 128), 128, 0, AsCuda(stream)>>>(b_kn, colsum, k, n);
+  return CheckLaunch("ColsumS8Kernel");
+}
+
+int itexb_pack_filter_hwio(const void* f_hwio, void* f_packed, int32_t kh, int32_t kw, int32_t c, int32_t co, int32_t c_pad,
+                           itexb_stream_t stream) {
+  ITEXB_REQUIRE(f_hwio != nullptr && f_packed != nullptr && kh > 0 && kw > 0 && c > 0 && co > 0 && c_pad >= c,
+                ITEXB_INVALID_ARGUMENT, "pack_filter_hwio: bad arguments");
+  const long long total = (long long)co * kh * kw * c_pad;
+  const int blocks = int(std::min<long long>((total + 255) / 256, (long long)SmCount() * 8));
+  PackFilterKernel<<<blocks, 256, 0, AsCuda(stream)>>>(static_cast<const uint8_t*>(f_hwio), static_cast<uint8_t*>(f_packed),
+                                                      kh * kw, c, co, c_pad);
+  return CheckLaunch("PackFilterKernel");
+}
+
+int itexb_fp8_quantize(const void* x, int x_dtype, void* y, int fp8_dtype, int64_t n, const float* scale, float* amax,
+                       itexb_stream_t stream) {
+  ITEXB_REQUIRE(IsFp8(fp8_dtype), ITEXB_INVALID_ARGUMENT, "fp8_quantize: fp8_dtype must be E4M3 or E5M2");
+  ITEXB_REQUIRE(scale != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "fp8_quantize: bad arguments");
+  if (n == 0) return ITEXB_OK;
+  const bool vec = Aligned16(x) && Aligned16(y);
+  const long long work = vec ? (n + kVec - 1) / kVec : n;
+  const int blocks = int(std::max<long long>(1, std::min<long long>((work + kThreads - 1) / kThreads, (long long)SmCount() * 16)));
+  cudaStream_t st = AsCuda(stream);
+  uint8_t* yp = static_cast<uint8_t*>(y);
+  const bool e4 = fp8_dtype == ITEXB_DT_FP8_E4M3;
+#define ITEXB_FP8Q(TX)                                                                                         \
+  do {                                                                                                         \
+    if (e4) Fp8QuantizeKernel<TX, true><<<blocks, kThreads, 0, st>>>(static_cast<const TX*>(x), yp, n, scale, amax, vec); \
+    else Fp8QuantizeKernel<TX, false><<<blocks, kThreads, 0, st>>>(static_cast<const TX*>(x), yp, n, scale, amax, vec);   \
+  } while (0)
+  if (x_dtype == ITEXB_DT_FLOAT) ITEXB_FP8Q(float);
+  else if (x_dtype == ITEXB_DT_BFLOAT16) ITEXB_FP8Q(__nv_bfloat16);
+  else if (x_dtype == ITEXB_DT_HALF) ITEXB_FP8Q(__half);
+  else return SetError(ITEXB_INVALID_ARGUMENT, "fp8_quantize: input type %s is not float/bfloat16/half", DtypeName(x_dtype));
+#undef ITEXB_FP8Q
+  return CheckLaunch("Fp8QuantizeKernel");
+}
+
+int itexb_fp8_dequantize(const void* x, int fp8_dtype, void* y, int y_dtype, int64_t n, const float* scale_inv,
+                         itexb_stream_t stream) {
+  ITEXB_REQUIRE(IsFp8(fp8_dtype), ITEXB_INVALID_ARGUMENT, "fp8_dequantize: fp8_dtype must be E4M3 or E5M2");
+  ITEXB_REQUIRE(scale_inv != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "fp8_dequantize: bad arguments");
+  if (n == 0) return ITEXB_OK;
+  const bool vec = Aligned16(x) && Aligned16(y);
+  const long long work = vec ? (n + kVec - 1) / kVec : n;
+  const int blocks = int(std::max<long long>(1, std::min<long long>((work + kThreads - 1) / kThreads, (long long)SmCount() * 16)));
+  cudaStream_t st = AsCuda(stream);
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  const bool e4 = fp8_dtype == ITEXB_DT_FP8_E4M3;
+#define ITEXB_FP8D(TY)                                                                                        \
+  do {                                                                                                        \
+    if (e4) Fp8DequantizeKernel<TY, true><<<blocks, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv, vec); \
+    else Fp8DequantizeKernel<TY, false><<<blocks, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv, vec);   \
+  } while (0)
+  if (y_dtype == ITEXB_DT_FLOAT) ITEXB_FP8D(float);
+  else if (y_dtype == ITEXB_DT_BFLOAT16) ITEXB_FP8D(__nv_bfloat16);
+  else if (y_dtype == ITEXB_DT_HALF) ITEXB_FP8D(__half);
+  else return SetError(ITEXB_INVALID_ARGUMENT, "fp8_dequantize: output type %s is not float/bfloat16/half", DtypeName(y_dtype));
+#undef ITEXB_FP8D
+  return CheckLaunch("Fp8DequantizeKernel");
+}
+
+int itexb_fp8_amax_and_scale_update(float* amax_history, float* scale, float* scale_inv, int32_t history_len, int32_t n,
+                                    float fp8_max, float margin, int32_t algo, itexb_stream_t stream) {
+  ITEXB_REQUIRE(amax_history && scale && scale_inv && history_len >= 1 && n >= 1, ITEXB_INVALID_ARGUMENT,
+                "fp8_amax_and_scale_update: bad arguments");
+  ITEXB_REQUIRE(algo == 0 || algo == 1, ITEXB_INVALID_ARGUMENT,
+                "We only support the fp8 recipe with 'max' or 'most_recent' amax_compute_algo");
+  Fp8AmaxScaleUpdateKernel<<<(n + 63) / 64, 64, 0, AsCuda(stream)>>>(amax_history, scale, scale_inv, history_len, n, fp8_max,
+                                                                    margin, algo);
+  return CheckLaunch("Fp8AmaxScaleUpdateKernel");
+}
+
+}  // extern "C"
