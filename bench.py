@@ -1,0 +1,324 @@
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch of
+synthetic input: _ITEXQuantizeV2 (fp32 -> quint8, SCALED, HALF_TO_EVEN) followed by
+_ITEXQuantizedMatMulWithBiasAndDequantize (u8 x s8 -> fp32, bias and dequantize fused),
+both called through the C-ABI op layer of libitexb200.so.  The metric is int8 GEMM
+throughput: 2*M*N*K operations per step over the time of the whole step.
+
+Multi-GPU (launched by torch.distributed.run): the batch (rows of the activation matrix)
+is sharded, weights are replicated, there is no data-path collective; per-GPU work is
+fixed, so scaling is weak and `value` is the sum over ranks.
+
+--impl reference times the CPU path the reference would run (oneDNN int8 inner product,
+reached through torch.ops.onednn, plus the oracle's quantize) on the host cores, on a
+bounded row sample of the same workload.
+"""
+import argparse
+import ctypes
+import importlib
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+WORKLOADS = {
+    # name: (M per GPU, N, K)
+    "int8_gemm_8192": (8192, 8192, 8192),
+    "int8_gemm_4096": (4096, 4096, 4096),
+    "bert_ffn1": (12288, 4096, 1024),
+}
+
+
+def load_package():
+    if "itex_b200" in sys.modules:
+        return sys.modules["itex_b200"]
+    pkg_dir = os.path.join(ROOT, "intel-extension-for-tensorflow_b200")
+    spec = importlib.util.spec_from_file_location("itex_b200", os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["itex_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.stop_flag = threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([s.strip() for s in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def synth_weights(n, k, seed):
+    """int8 weights [K,N] from N(0, 0.02), symmetric per-tensor (the named op honours one weight range)."""
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.02))
+    amax = float(np.abs(w).max())
+    q = np.clip(np.rint(w * (127.0 / amax)), -127, 127).astype(np.int8)
+    bias = (rng.standard_normal(n, dtype=np.float32) * np.float32(0.1))
+    return q, -amax, amax, bias
+
+
+def cpu_reference_step(x_rows, qw_kn, wmin, wmax, bias, state):
+    """One CPU step on a row sample: quantize + int8 matmul + bias + dequantize.
+    Returns (fp32 output, label of what ran)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import itex_oracle as o
+    import oracle_c as oc
+    import torch
+    mn, mx = float(x_rows.min()), float(x_rows.max())
+    amin, amax = o.adjust_input_min_max(mn, mx)
+    scale, absr = o.scaled_scale(amin, amax, "quint8", True)
+    qa = oc.quantize_scaled(x_rows, scale, False)
+    out_scale = o.matmul_output_scale(0.0, absr, wmin, wmax, "float")
+    if "bias_s" not in state:
+        state["bias_s"] = o.matmul_scaled_bias(bias, qw_kn[:1], 0.0, absr, wmin, wmax, "SCALED", "float", out_scale)
+        state["w_nk"] = np.ascontiguousarray(qw_kn.T)
+        try:
+            state["pw"] = torch.ops.onednn.qlinear_prepack(torch.from_numpy(state["w_nk"]), None)
+            state["ws"] = torch.full((qw_kn.shape[1],), float(out_scale))
+            state["wz"] = torch.zeros(qw_kn.shape[1], dtype=torch.int64)
+            state["label"] = "oneDNN int8 inner product via torch.ops.onednn.qlinear_pointwise + C oracle quantize"
+        except Exception:
+            state["pw"] = None
+            state["label"] = "C/OpenMP oracle port (oracle/itex_oracle_c.c)"
+    if state["pw"] is not None:
+        y = torch.ops.onednn.qlinear_pointwise(torch.from_numpy(qa), 1.0, 0, state["pw"], state["ws"], state["wz"],
+                                               torch.from_numpy(state["bias_s"]), 1.0, 0, torch.float32, "none", [], "")
+        return y.numpy(), state["label"]
+    return oc.gemm_fused(qa, state["w_nk"], out_scale, state["bias_s"], False, "float"), state["label"]
+
+
+def run_reference(args, m, n, k):
+    """The reference arm: CPU only, rank 0 only."""
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    m_s = min(m, 512)
+    rng = np.random.default_rng(1234)
+    x = rng.uniform(-1, 1, (m_s, k)).astype(np.float32)
+    qw, wmin, wmax, bias = synth_weights(n, k, 1235)
+    state = {}
+    for _ in range(max(args.warmup, 1)):
+        _, label = cpu_reference_step(x, qw, wmin, wmax, bias, state)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_step(x, qw, wmin, wmax, bias, state)
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = 2.0 * m_s * n * k / dt / 1e12
+    sample = "%d of %d rows per step (%s), %d host threads" % (m_s, m, label, cores)
+    line = {"impl": "reference", "metric": "int8_quantized_gemm_tops", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "s8xu8->s32", "data": "synthetic",
+            "config": {"workload": args.workload, "m_per_gpu": m, "n": n, "k": k, "cpu_sample_rows": m_s},
+            "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    m, n, k = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, m, n, k)
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    itex = load_package()
+    ops = importlib.import_module("itex_b200.ops")
+    K = importlib.import_module("itex_b200.kernels")
+    dev = torch.device("cuda", local)
+
+    # ---- synthetic inputs, resident in HBM (seed depends on the rank: each GPU has its own batch shard)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    x = torch.rand((m, k), device=dev, generator=gen) * 2 - 1
+    qw, wmin, wmax, bias_h = synth_weights(n, k, 1235)
+    w = torch.from_numpy(qw).to(dev)
+    bias = torch.from_numpy(bias_h).to(dev)
+    xmin, xmax = float(x.min()), float(x.max())  # the graph's frozen activation range
+    q_op = ops.Op("_ITEXQuantizeV2", T="quint8", mode="SCALED", round_mode="HALF_TO_EVEN", narrow_range=False, axis=-1,
+                  ensure_minimum_range=0.01, dtype="float")
+    mm_op = ops.Op("_ITEXQuantizedMatMulWithBiasAndDequantize", T1="quint8", T2="qint8", Tbias="float", Toutput="float",
+                   transpose_a=False, transpose_b=False, input_quant_mode="SCALED", is_weight_const=True)
+
+    def step(x_dev):
+        q, qmin, qmax = q_op(x_dev, xmin, xmax)
+        return mm_op(q, w, bias, qmin, qmax, wmin, wmax, 0.0, 0.0), q, qmin, qmax
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # clocks are sampled from the warm-up on (one nvidia-smi query takes longer than a step),
+    # so the record covers the device under this load, the timed region included
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_warm = time.perf_counter()
+    n_warm = 0
+    while n_warm < args.warmup or time.perf_counter() - t_warm < 1.0:
+        out, q, qmin, qmax = step(x)
+        n_warm += 1
+        if n_warm % 50 == 0:
+            torch.cuda.synchronize()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream
+    launches0 = K.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    g1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        q, qmin, qmax = q_op(x, xmin, xmax)
+        g0[i].record()
+        out = mm_op(q, w, bias, qmin, qmax, wmin, wmax, 0.0, 0.0)
+        g1[i].record()
+    e1.record()
+    barrier()
+    launches = K.launch_count() - launches0
+    sampler.stop_flag.set()
+    sampler.join()
+    ms_total = e0.elapsed_time(e1)
+    gemm_ms = sum(a.elapsed_time(b) for a, b in zip(g0, g1)) / args.steps
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    ops_per_step = 2.0 * m * n * k * world
+    value = ops_per_step / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public op API with host buffers (pinned), every step H2D in, D2H out
+    x_host = torch.empty((m, k), dtype=torch.float32, pin_memory=True)
+    x_host.copy_(x.cpu())
+    out_host = torch.empty((m, n), dtype=torch.float32, pin_memory=True)
+    x_stage = torch.empty_like(x)
+
+    def e2e_step():
+        x_stage.copy_(x_host, non_blocking=True)
+        o, _, _, _ = step(x_stage)
+        out_host.copy_(o, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    te = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / args.e2e_steps
+    e2e_value = ops_per_step / (e2e_ms * 1e-3) / 1e12
+    checksum = float(out_host[::997, ::991].double().sum())
+
+    if rank == 0:
+        peaks = measured_peaks()
+        gemm_tops = 2.0 * m * n * k / (gemm_ms * 1e-3) / 1e12
+        int8_peak = 2.0 * peaks["bf16_tflops"]
+        line = {
+            "metric": "int8_quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "s8xu8->s32", "data": "synthetic",
+            "config": {"workload": args.workload, "m_per_gpu": m, "n": n, "k": k, "ops": ["_ITEXQuantizeV2", "_ITEXQuantizedMatMulWithBiasAndDequantize"],
+                       "output": "float32", "l2": "inputs larger than L2 (%.0f MB touched per step)" % ((m * k * 5 + n * k + m * n * 4) / 1e6),
+                       "parallelism": "batch-sharded x%d, no collective" % world},
+            "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,int8> (tcgen05.mma kind::i8)", "achieved": gemm_tops,
+                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
+                         "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s); int8 MMA rate is twice bf16" % peaks["source"],
+                         "gemm_ms": gemm_ms, "traffic": None},
+            "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k * 4 * world,
+                    "d2h_bytes_per_step": m * n * 4 * world, "checksum": checksum},
+            "gpu_launches": int(launches), "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            m_s = min(m, 512)
+            xs = x[:m_s].cpu().numpy()
+            state = {}
+            ref, label = cpu_reference_step(xs, qw, wmin, wmax, bias_h, state)
+            reps, t_cpu = 0, time.perf_counter()
+            while reps < 3 or (time.perf_counter() - t_cpu < 5.0 and reps < 50):
+                cpu_reference_step(xs, qw, wmin, wmax, bias_h, state)
+                reps += 1
+            dt = (time.perf_counter() - t_cpu) / reps
+            # the CPU sample also checks the GPU result of the same rows (range = that of the full batch)
+            line["cpu_baseline"] = {"value": 2.0 * m_s * n * k / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+                                    "sample": "%d of %d rows per step (%s), %d host threads, %d reps" % (m_s, m, label, cores, reps)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -175,6 +175,7 @@ ITEXB_API int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, in
  *   f = f + bias[n]                    (bias != NULL)
  *   f = f + sum_scale * float(summand[m][n])   (summand != NULL)
  *   f = max(f, 0)                      (relu)
+ *   f = float(mid_dtype(f))            (mid_dtype != 0)
  *   out = convert(f): QUINT8/QINT8/QINT32 saturate then round-to-nearest-even;
  *         FLOAT/BFLOAT16/HALF plain conversion; FP8_E4M3 saturating RNE of f*out_scale[0]
  *         with amax[0] = max(amax[0], max|f|).
@@ -188,13 +189,15 @@ typedef struct itexb_epilogue {
   const float* alpha_b;    /*   (FP8: a_scale_inv[i], b_scale_inv[j]); overrides `scale` */
   const float* bias;       /* device fp32 [n] or NULL */
   const void* summand;     /* device [m][n] or NULL */
-  int32_t summand_dtype;   /* QUINT8 | QINT8 | FLOAT | BFLOAT16 */
+  int32_t summand_dtype;   /* QUINT8 | QINT8 | FLOAT | BFLOAT16 | HALF */
   int64_t ld_summand;      /* elements */
   float sum_scale;
   int32_t relu;
   int32_t raw_acc;
   const float* out_scale;  /* FP8 output only: device scalar c_scale */
   float* amax;             /* FP8 output only: device scalar, atomically maxed */
+  int32_t mid_dtype;       /* 0, or BFLOAT16 | HALF: round f to that type before the final
+                              conversion (FP8 output of a matmul whose sum type is 16-bit) */
 } itexb_epilogue_t;
 
 /* out[m][n] = epilogue( sum_k a[m][k] * b[n][k] ).

@@ -20,7 +20,7 @@ LIB = os.path.join(OUT_DIR, "libitexb200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false",  # separate fp32 multiply and add, like the CPU reference path
-    "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function,-ffp-contract=off",
     "-I" + os.path.join(ROOT, "include"), "-I" + CSRC,
 ]
 

@@ -171,6 +171,7 @@ __device__ __forceinline__ float LoadSummand(const void* p, int dt, long long id
     case ITEXB_DT_QUINT8: case ITEXB_DT_UINT8: return float(static_cast<const uint8_t*>(p)[idx]);
     case ITEXB_DT_QINT8: case ITEXB_DT_INT8: return float(int(static_cast<const int8_t*>(p)[idx]));
     case ITEXB_DT_BFLOAT16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+    case ITEXB_DT_HALF: return __half2float(static_cast<const __half*>(p)[idx]);
     default: return static_cast<const float*>(p)[idx];
   }
 }
@@ -485,6 +486,13 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
             }
+            if (g.ep.mid_dtype == ITEXB_DT_BFLOAT16) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+            } else if (g.ep.mid_dtype == ITEXB_DT_HALF) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __half2float(__float2half_rn(v[j]));
+            }
             StoreRow32(g, v, row, col0, ncols, vec, &thread_amax, out_scale);
           }
         }
@@ -622,7 +630,7 @@ int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype,
                   "%s: raw_acc needs int8 operands and a qint32 output", who);
   if (ep.summand != nullptr) {
     const int sd = ep.summand_dtype;
-    ITEXB_REQUIRE(IsInt8(sd) || sd == ITEXB_DT_FLOAT || sd == ITEXB_DT_BFLOAT16, ITEXB_INVALID_ARGUMENT,
+    ITEXB_REQUIRE(IsInt8(sd) || sd == ITEXB_DT_FLOAT || sd == ITEXB_DT_BFLOAT16 || sd == ITEXB_DT_HALF, ITEXB_INVALID_ARGUMENT,
                   "%s: unsupported summand type %s", who, DtypeName(sd));
   }
   return ITEXB_OK;

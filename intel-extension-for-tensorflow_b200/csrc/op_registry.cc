@@ -1,0 +1,338 @@
+// Op registry, attribute access, per-instance caches and the C-ABI of the op layer
+// (itexb_op_* and itexb_simple_context_* of include/itexb200.h).
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+
+#include "op_kernel.h"
+
+namespace itexb {
+
+// ---- AttrMap --------------------------------------------------------------------------
+const itexb_attr_t* AttrMap::Find(const char* name) const {
+  for (int i = 0; i < n_; ++i)
+    if (attrs_[i].name != nullptr && std::strcmp(attrs_[i].name, name) == 0) return &attrs_[i];
+  return nullptr;
+}
+int AttrMap::Missing(const char* name, const char* want) const {
+  return SetError(ITEXB_INVALID_ARGUMENT, "attr '%s' of type %s is missing or has another type", name, want);
+}
+int AttrMap::GetString(const char* name, std::string* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_STRING || a->s == nullptr) return Missing(name, "string");
+  *v = a->s;
+  return ITEXB_OK;
+}
+int AttrMap::GetInt(const char* name, int64_t* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_INT) return Missing(name, "int");
+  *v = a->i;
+  return ITEXB_OK;
+}
+int AttrMap::GetFloat(const char* name, float* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_FLOAT) return Missing(name, "float");
+  *v = a->f;
+  return ITEXB_OK;
+}
+int AttrMap::GetBool(const char* name, bool* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_BOOL) return Missing(name, "bool");
+  *v = a->i != 0;
+  return ITEXB_OK;
+}
+int AttrMap::GetType(const char* name, int* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_TYPE) return Missing(name, "type");
+  *v = int(a->i);
+  return ITEXB_OK;
+}
+int AttrMap::GetIntList(const char* name, std::vector<int64_t>* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_INT_LIST) return Missing(name, "list(int)");
+  v->assign(a->list_i, a->list_i + a->list_len);
+  return ITEXB_OK;
+}
+int AttrMap::GetStringList(const char* name, std::vector<std::string>* v) const {
+  const itexb_attr_t* a = Find(name);
+  if (a == nullptr || a->type != ITEXB_ATTR_STRING_LIST) return Missing(name, "list(string)");
+  v->clear();
+  for (int i = 0; i < a->list_len; ++i) v->emplace_back(a->list_s[i]);
+  return ITEXB_OK;
+}
+
+// ---- registry -------------------------------------------------------------------------
+namespace {
+struct Entry {
+  OpSignature sig;
+  OpFactory factory;
+};
+std::map<std::string, Entry>& Registry() {
+  static std::map<std::string, Entry>* r = new std::map<std::string, Entry>();
+  return *r;
+}
+}  // namespace
+
+void RegisterOp(const char* name, const OpSignature& sig, OpFactory factory) { Registry()[name] = Entry{sig, std::move(factory)}; }
+
+// ---- context helpers ------------------------------------------------------------------
+int RequireInputs(const itexb_op_context_t* ctx, int n, const char* op) {
+  ITEXB_REQUIRE(ctx != nullptr && ctx->inputs != nullptr, ITEXB_INVALID_ARGUMENT, "%s: context has no inputs", op);
+  ITEXB_REQUIRE(ctx->num_inputs == n, ITEXB_INVALID_ARGUMENT, "%s expects %d inputs, got %d", op, n, ctx->num_inputs);
+  ITEXB_REQUIRE(ctx->allocate_output != nullptr, ITEXB_INVALID_ARGUMENT, "%s: context has no allocate_output", op);
+  return ITEXB_OK;
+}
+int HostFloats(const itexb_op_context_t* ctx, int i, const char* op, const char* arg, const float** data, int64_t* count) {
+  const itexb_tensor_t& t = ctx->inputs[i];
+  ITEXB_REQUIRE(t.on_host, ITEXB_INVALID_ARGUMENT, "%s: input '%s' (#%d) is a HostMemory argument but was passed in device memory",
+                op, arg, i);
+  ITEXB_REQUIRE(t.dtype == ITEXB_DT_FLOAT, ITEXB_INVALID_ARGUMENT, "%s: input '%s' must be float, is %s", op, arg,
+                DtypeName(t.dtype));
+  *count = NumElements(t);
+  ITEXB_REQUIRE(*count >= 1 && t.data != nullptr, ITEXB_INVALID_ARGUMENT, "%s: input '%s' is empty", op, arg);
+  *data = static_cast<const float*>(t.data);
+  return ITEXB_OK;
+}
+int RequireDevice(const itexb_op_context_t* ctx, int i, const char* op, const char* arg) {
+  ITEXB_REQUIRE(!ctx->inputs[i].on_host, ITEXB_INVALID_ARGUMENT, "%s: input '%s' (#%d) must be in device memory", op, arg, i);
+  return ITEXB_OK;
+}
+int AllocateOutput(itexb_op_context_t* ctx, int index, int dtype, const int64_t* dims, int rank, bool on_host,
+                   itexb_tensor_t* out) {
+  ITEXB_REQUIRE(rank <= ITEXB_MAX_DIMS, ITEXB_INVALID_ARGUMENT, "output rank %d exceeds %d", rank, ITEXB_MAX_DIMS);
+  std::memset(out, 0, sizeof(*out));
+  out->dtype = dtype;
+  out->rank = rank;
+  for (int i = 0; i < rank; ++i) out->dims[i] = dims[i];
+  out->on_host = on_host ? 1 : 0;
+  int st = ctx->allocate_output(ctx->user, index, out);
+  if (st != ITEXB_OK) return st;
+  ITEXB_REQUIRE(out->data != nullptr || NumElements(*out) == 0, ITEXB_RESOURCE_EXHAUSTED, "allocate_output(%d) returned no memory",
+                index);
+  return ITEXB_OK;
+}
+int AllocateTemp(itexb_op_context_t* ctx, size_t bytes, bool on_host, void** ptr) {
+  ITEXB_REQUIRE(ctx->allocate_temp != nullptr, ITEXB_INVALID_ARGUMENT, "context has no allocate_temp");
+  int st = ctx->allocate_temp(ctx->user, bytes, on_host ? 1 : 0, ptr);
+  if (st != ITEXB_OK) return st;
+  ITEXB_REQUIRE(*ptr != nullptr, ITEXB_RESOURCE_EXHAUSTED, "allocate_temp(%zu) returned no memory", bytes);
+  return ITEXB_OK;
+}
+
+// ---- DeviceVectorCache ------------------------------------------------------------------
+DeviceVectorCache::~DeviceVectorCache() {
+  for (Slot& s : slots_) {
+    if (s.ev) (void)cudaEventDestroy(s.ev);
+    if (s.pinned) (void)cudaFreeHost(s.pinned);
+    if (s.dev) (void)itexb_rt_deallocate(ordinal_, s.dev);
+  }
+}
+
+int DeviceVectorCache::Get(int ordinal, cudaStream_t stream, const float* host, size_t n, const float** dev) {
+  ITEXB_REQUIRE(n > 0, ITEXB_INVALID_ARGUMENT, "DeviceVectorCache: empty vector");
+  if (cur_ >= 0 && last_.size() == n && std::memcmp(last_.data(), host, n * sizeof(float)) == 0) {
+    *dev = slots_[cur_].dev;
+    return ITEXB_OK;
+  }
+  ordinal_ = ordinal;
+  const int next = (cur_ + 1) % kSlots;
+  Slot& s = slots_[next];
+  if (s.used) ITEXB_CUDA(cudaEventSynchronize(s.ev));  // only if the host is 4 uploads ahead
+  if (s.cap < n) {
+    if (s.pinned) ITEXB_CUDA(cudaFreeHost(s.pinned));
+    if (s.dev) ITEXB_RETURN_IF_ERROR(itexb_rt_deallocate(ordinal, s.dev));
+    s.pinned = nullptr;
+    s.dev = nullptr;
+    s.cap = 0;
+    ITEXB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&s.pinned), n * sizeof(float), cudaHostAllocDefault));
+    void* d = nullptr;
+    ITEXB_RETURN_IF_ERROR(itexb_rt_allocate(ordinal, n * sizeof(float), &d));
+    s.dev = static_cast<float*>(d);
+    s.cap = n;
+  }
+  if (s.ev == nullptr) ITEXB_CUDA(cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming));
+  std::memcpy(s.pinned, host, n * sizeof(float));
+  ITEXB_CUDA(cudaMemcpyAsync(s.dev, s.pinned, n * sizeof(float), cudaMemcpyHostToDevice, stream));
+  ITEXB_CUDA(cudaEventRecord(s.ev, stream));
+  s.used = true;
+  cur_ = next;
+  last_.assign(host, host + n);
+  *dev = s.dev;
+  return ITEXB_OK;
+}
+
+// ---- DeviceBuffer -----------------------------------------------------------------------
+int DeviceBuffer::Ensure(int ordinal, size_t bytes) {
+  if (ptr_ != nullptr && bytes_ >= bytes && ordinal_ == ordinal) return ITEXB_OK;
+  Release();
+  ITEXB_RETURN_IF_ERROR(itexb_rt_allocate(ordinal, bytes, &ptr_));
+  bytes_ = bytes;
+  ordinal_ = ordinal;
+  return ITEXB_OK;
+}
+void DeviceBuffer::Release() {
+  if (ptr_ != nullptr) (void)itexb_rt_deallocate(ordinal_, ptr_);
+  ptr_ = nullptr;
+  bytes_ = 0;
+}
+
+}  // namespace itexb
+
+using namespace itexb;
+
+struct itexb_op {
+  std::unique_ptr<OpKernel> kernel;
+};
+
+// The default context: outputs and temporaries from the runtime allocator.
+struct itexb_simple_context {
+  itexb_op_context_t ctx;
+  int ordinal;
+  std::vector<itexb_tensor_t> outputs;
+  std::vector<std::pair<void*, bool>> owned;  // (pointer, on_host)
+  std::vector<std::pair<void*, bool>> temps;
+};
+
+namespace {
+
+int SimpleAlloc(itexb_simple_context* c, size_t bytes, bool on_host, void** ptr) {
+  if (on_host) return itexb_rt_host_allocate(bytes, ptr);
+  return itexb_rt_allocate(c->ordinal, bytes, ptr);
+}
+void SimpleFree(itexb_simple_context* c, void* p, bool on_host) {
+  if (on_host) (void)itexb_rt_host_deallocate(p);
+  else (void)itexb_rt_deallocate(c->ordinal, p);
+}
+
+int SimpleAllocateOutput(void* user, int index, itexb_tensor_t* out) {
+  auto* c = static_cast<itexb_simple_context*>(user);
+  ITEXB_REQUIRE(index >= 0 && index < 64, ITEXB_INVALID_ARGUMENT, "output index %d out of range", index);
+  const size_t bytes = size_t(std::max<int64_t>(NumElements(*out), 0)) * DtypeSize(out->dtype);
+  void* p = nullptr;
+  ITEXB_RETURN_IF_ERROR(SimpleAlloc(c, std::max<size_t>(bytes, 1), out->on_host != 0, &p));
+  out->data = p;
+  c->owned.emplace_back(p, out->on_host != 0);
+  if (int(c->outputs.size()) <= index) c->outputs.resize(index + 1, itexb_tensor_t{});
+  c->outputs[index] = *out;
+  return ITEXB_OK;
+}
+
+int SimpleAllocateTemp(void* user, size_t bytes, int on_host, void** ptr) {
+  auto* c = static_cast<itexb_simple_context*>(user);
+  ITEXB_RETURN_IF_ERROR(SimpleAlloc(c, std::max<size_t>(bytes, 1), on_host != 0, ptr));
+  c->temps.emplace_back(*ptr, on_host != 0);
+  return ITEXB_OK;
+}
+
+void ReleaseList(itexb_simple_context* c, std::vector<std::pair<void*, bool>>* l) {
+  for (auto& p : *l) SimpleFree(c, p.first, p.second);
+  l->clear();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* const* itexb_op_list(void) {
+  static std::vector<const char*>* names = [] {
+    auto* v = new std::vector<const char*>();
+    for (auto& kv : Registry()) v->push_back(kv.first.c_str());
+    v->push_back(nullptr);
+    return v;
+  }();
+  return names->data();
+}
+
+int itexb_op_signature(const char* op_name, int* num_inputs, int* num_outputs, uint32_t* host_input_mask,
+                       uint32_t* host_output_mask) {
+  ITEXB_REQUIRE(op_name != nullptr, ITEXB_INVALID_ARGUMENT, "op_signature: op_name is NULL");
+  auto it = Registry().find(op_name);
+  ITEXB_REQUIRE(it != Registry().end(), ITEXB_NOT_FOUND, "Op type not registered '%s'", op_name);
+  if (num_inputs) *num_inputs = it->second.sig.num_inputs;
+  if (num_outputs) *num_outputs = it->second.sig.num_outputs;
+  if (host_input_mask) *host_input_mask = it->second.sig.host_input_mask;
+  if (host_output_mask) *host_output_mask = it->second.sig.host_output_mask;
+  return ITEXB_OK;
+}
+
+int itexb_op_create(const char* op_name, const itexb_attr_t* attrs, int num_attrs, itexb_op_t** op) {
+  ITEXB_REQUIRE(op_name != nullptr && op != nullptr, ITEXB_INVALID_ARGUMENT, "op_create: NULL argument");
+  *op = nullptr;
+  auto it = Registry().find(op_name);
+  ITEXB_REQUIRE(it != Registry().end(), ITEXB_NOT_FOUND, "Op type not registered '%s'", op_name);
+  std::unique_ptr<OpKernel> k(it->second.factory());
+  k->set_name(op_name);
+  AttrMap am(attrs, attrs == nullptr ? 0 : num_attrs);
+  int st = k->Init(am);
+  if (st != ITEXB_OK) return st;
+  *op = new itexb_op{std::move(k)};
+  return ITEXB_OK;
+}
+
+int itexb_op_compute(itexb_op_t* op, itexb_op_context_t* ctx) {
+  ITEXB_REQUIRE(op != nullptr && ctx != nullptr, ITEXB_INVALID_ARGUMENT, "op_compute: NULL argument");
+  std::lock_guard<std::mutex> lock(op->kernel->mu());
+  // Without a usable device the op still runs its host-side checks (and then fails at
+  // its first launch), so argument errors are reported the same way everywhere.
+  int prev = ctx->device_ordinal;
+  if (cudaGetDevice(&prev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    prev = ctx->device_ordinal;
+  }
+  if (prev != ctx->device_ordinal) ITEXB_CUDA(cudaSetDevice(ctx->device_ordinal));
+  int st = op->kernel->Compute(ctx);
+  if (st == ITEXB_OK && std::getenv("ITEXB_SYNC_EXEC") != nullptr) st = CudaStatus(cudaStreamSynchronize(AsCuda(ctx->stream)), "ITEXB_SYNC_EXEC");
+  if (prev != ctx->device_ordinal) (void)cudaSetDevice(prev);
+  return st;
+}
+
+void itexb_op_delete(itexb_op_t* op) { delete op; }
+
+int itexb_simple_context_create(int device_ordinal, itexb_stream_t stream, itexb_simple_context_t** c) {
+  ITEXB_REQUIRE(c != nullptr, ITEXB_INVALID_ARGUMENT, "simple_context_create: NULL argument");
+  auto* s = new itexb_simple_context();
+  s->ordinal = device_ordinal;
+  std::memset(&s->ctx, 0, sizeof(s->ctx));
+  s->ctx.user = s;
+  s->ctx.device_ordinal = device_ordinal;
+  s->ctx.stream = stream;
+  s->ctx.allocate_output = SimpleAllocateOutput;
+  s->ctx.allocate_temp = SimpleAllocateTemp;
+  *c = s;
+  return ITEXB_OK;
+}
+
+itexb_op_context_t* itexb_simple_context_begin(itexb_simple_context_t* c, const itexb_tensor_t* inputs, int num_inputs) {
+  if (c == nullptr) return nullptr;
+  c->ctx.inputs = inputs;
+  c->ctx.num_inputs = num_inputs;
+  c->outputs.clear();
+  return &c->ctx;
+}
+
+int itexb_simple_context_num_outputs(itexb_simple_context_t* c) { return c == nullptr ? 0 : int(c->outputs.size()); }
+
+const itexb_tensor_t* itexb_simple_context_output(itexb_simple_context_t* c, int index) {
+  if (c == nullptr || index < 0 || index >= int(c->outputs.size())) return nullptr;
+  return &c->outputs[index];
+}
+
+int itexb_simple_context_reset(itexb_simple_context_t* c) {
+  ITEXB_REQUIRE(c != nullptr, ITEXB_INVALID_ARGUMENT, "simple_context_reset: NULL argument");
+  // Temporaries and outputs may still be read by work queued on the stream.
+  ITEXB_CUDA(cudaStreamSynchronize(AsCuda(c->ctx.stream)));
+  ReleaseList(c, &c->temps);
+  ReleaseList(c, &c->owned);
+  c->outputs.clear();
+  return ITEXB_OK;
+}
+
+void itexb_simple_context_destroy(itexb_simple_context_t* c) {
+  if (c == nullptr) return;
+  (void)cudaStreamSynchronize(AsCuda(c->ctx.stream));
+  ReleaseList(c, &c->temps);
+  ReleaseList(c, &c->owned);
+  delete c;
+}
+
+}  // extern "C"

@@ -1,0 +1,235 @@
+// [_ITEX]QuantizedConv2DWithBias[AndRelu]AndRequantize and the Sum-fused variants
+// (old-API quantized Conv2D ops), NHWC.
+//
+// Attrs, input order (input, filter, bias, min_input, max_input, min_filter, max_filter,
+// min_freezed_output, max_freezed_output[, summand, min_summand, max_summand]), the
+// HostMemory lists and the checks follow LegacyQuantizedConvOpBase
+// (itex/core/kernels/common/quantized_conv_ops.h:71-729) over ConvOpBase
+// (itex/core/kernels/common/conv_ops.h:612-1133), registrations
+// itex/core/kernels/gpu/quantized_conv_ops.cc:72-160.  Where the reference builds a
+// dnnl::convolution_forward with per-channel scales on the weights argument, this op
+// packs the filter once to [co][kh*kw*c], prepares the scaled bias on the device and
+// launches the implicit-GEMM convolution with the fused epilogue.
+#include "hostmath.h"
+#include "op_kernel.h"
+
+namespace itexb {
+namespace {
+
+class QuantizedConv2DOp : public OpKernel {
+ public:
+  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum) : relu_(relu), sum_(sum), signed_sum_(signed_sum) {}
+
+  int Init(const AttrMap& attrs) override {
+    const char* op = name().c_str();
+    std::vector<int64_t> strides, dilations = {1, 1, 1, 1};
+    ITEXB_RETURN_IF_ERROR(attrs.GetIntList("strides", &strides));
+    if (attrs.Has("dilations")) ITEXB_RETURN_IF_ERROR(attrs.GetIntList("dilations", &dilations));
+    std::string data_format = "NHWC";
+    if (attrs.Has("data_format")) ITEXB_RETURN_IF_ERROR(attrs.GetString("data_format", &data_format));
+    ITEXB_REQUIRE(data_format == "NHWC" || data_format == "NCHW", ITEXB_INVALID_ARGUMENT, "Invalid data format");
+    ITEXB_REQUIRE(data_format == "NHWC", ITEXB_UNIMPLEMENTED, "%s: only data_format NHWC is implemented", op);
+    ITEXB_REQUIRE(strides.size() == 4, ITEXB_INVALID_ARGUMENT, "Sliding window strides field must specify 4 dimensions");
+    ITEXB_REQUIRE(dilations.size() == 4, ITEXB_INVALID_ARGUMENT, "Sliding window dilations field must specify 4 dimensions");
+    ITEXB_REQUIRE(strides[0] == 1 && strides[3] == 1, ITEXB_UNIMPLEMENTED,
+                  "Current implementation does not yet support strides in the batch and depth dimensions.");
+    ITEXB_REQUIRE(dilations[0] == 1 && dilations[3] == 1, ITEXB_INVALID_ARGUMENT,
+                  "Current implementation does not yet support dilations in the batch and depth dimensions.");
+    ITEXB_REQUIRE(strides[1] > 0 && strides[2] > 0, ITEXB_INVALID_ARGUMENT, "Row and column strides should be larger than 0.");
+    ITEXB_REQUIRE(dilations[1] > 0 && dilations[2] > 0, ITEXB_INVALID_ARGUMENT, "Dilated rates should be larger than 0.");
+    stride_h_ = int(strides[1]); stride_w_ = int(strides[2]);
+    dil_h_ = int(dilations[1]); dil_w_ = int(dilations[2]);
+    std::string padding;
+    ITEXB_RETURN_IF_ERROR(attrs.GetString("padding", &padding));
+    if (padding == "VALID") padding_ = 0;
+    else if (padding == "SAME") padding_ = 1;
+    else if (padding == "EXPLICIT") padding_ = 2;
+    else return SetError(ITEXB_INVALID_ARGUMENT, "%s: unknown padding '%s'", op, padding.c_str());
+    if (attrs.Has("explicit_paddings")) ITEXB_RETURN_IF_ERROR(attrs.GetIntList("explicit_paddings", &explicit_paddings_));
+    // legacy int8 graphs carry the pads in padding_list (quantized_conv_ops.h:122-126)
+    if (attrs.Has("padding_list")) {
+      std::vector<int64_t> pl;
+      ITEXB_RETURN_IF_ERROR(attrs.GetIntList("padding_list", &pl));
+      if (!pl.empty()) explicit_paddings_ = pl;
+    }
+    if (padding_ == 2)
+      ITEXB_REQUIRE(explicit_paddings_.size() == 8, ITEXB_INVALID_ARGUMENT, "%s: EXPLICIT padding needs 8 explicit_paddings values", op);
+    is_filter_const_ = true;
+    is_bias_const_ = true;
+    if (attrs.Has("is_filter_const")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("is_filter_const", &is_filter_const_));
+    if (attrs.Has("is_bias_const")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("is_bias_const", &is_bias_const_));
+    tinput_ = ITEXB_DT_QUINT8;
+    if (attrs.Has("Tinput")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tinput", &tinput_));
+    ITEXB_REQUIRE(tinput_ == ITEXB_DT_QUINT8 || tinput_ == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT,
+                  "%s: no kernel registered for Tinput=%s", op, DtypeName(tinput_));
+    int tfilter = ITEXB_DT_QINT8;
+    if (attrs.Has("Tfilter")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tfilter", &tfilter));
+    ITEXB_REQUIRE(tfilter == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT, "%s: no kernel registered for Tfilter=%s", op, DtypeName(tfilter));
+    tbias_ = ITEXB_DT_FLOAT;
+    if (attrs.Has("Tbias")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tbias", &tbias_));
+    ITEXB_REQUIRE(tbias_ == ITEXB_DT_FLOAT || tbias_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT,
+                  "%s: no kernel registered for Tbias=%s", op, DtypeName(tbias_));
+    out_type_ = ITEXB_DT_QUINT8;
+    if (attrs.Has("out_type")) ITEXB_RETURN_IF_ERROR(attrs.GetType("out_type", &out_type_));
+    if (relu_)
+      ITEXB_REQUIRE(out_type_ == ITEXB_DT_QUINT8, ITEXB_INVALID_ARGUMENT,
+                    "%s: no kernel registered for out_type=%s (quint8 is)", op, DtypeName(out_type_));
+    else
+      ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT8 || out_type_ == ITEXB_DT_QUINT8, ITEXB_INVALID_ARGUMENT,
+                    "%s: no kernel registered for out_type=%s (qint8 and quint8 are)", op, DtypeName(out_type_));
+    return ITEXB_OK;
+  }
+
+  int Compute(itexb_op_context_t* ctx) override {
+    const char* op = name().c_str();
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, sum_ ? 12 : 9, op));
+    ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 0, op, "input"));
+    ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 1, op, "filter"));
+    ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 2, op, "bias"));
+    const itexb_tensor_t& x = ctx->inputs[0];
+    const itexb_tensor_t& f = ctx->inputs[1];
+    const itexb_tensor_t& bias = ctx->inputs[2];
+    ITEXB_REQUIRE(x.rank == 4, ITEXB_INVALID_ARGUMENT, "input must be 4-dimensional");
+    ITEXB_REQUIRE(f.rank == 4, ITEXB_INVALID_ARGUMENT, "filter must be 4-dimensional");
+    ITEXB_REQUIRE(x.dtype == tinput_, ITEXB_INVALID_ARGUMENT, "%s: input has type %s, Tinput is %s", op, DtypeName(x.dtype),
+                  DtypeName(tinput_));
+    ITEXB_REQUIRE(f.dtype == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT, "%s: filter must be qint8", op);
+    ITEXB_REQUIRE(bias.dtype == tbias_, ITEXB_INVALID_ARGUMENT, "%s: bias has type %s, Tbias is %s", op, DtypeName(bias.dtype),
+                  DtypeName(tbias_));
+    const int64_t n = x.dims[0], h = x.dims[1], w = x.dims[2], c = x.dims[3];
+    const int64_t kh = f.dims[0], kw = f.dims[1], co = f.dims[3];
+    ITEXB_REQUIRE(f.dims[2] == c, ITEXB_INVALID_ARGUMENT, "input and filter must have the same depth: %lld vs %lld", (long long)c,
+                  (long long)f.dims[2]);
+    ITEXB_REQUIRE(bias.rank == 1 && bias.dims[0] == co, ITEXB_INVALID_ARGUMENT, "%s: bias must be a vector of %lld elements", op,
+                  (long long)co);
+    int64_t oh, ow, pt = 0, pb = 0, pl = 0, pr = 0;
+    if (padding_ == 2) { pt = explicit_paddings_[2]; pb = explicit_paddings_[3]; pl = explicit_paddings_[4]; pr = explicit_paddings_[5]; }
+    ITEXB_REQUIRE(hostmath::WindowedOutputSize(h, kh, dil_h_, stride_h_, padding_, &oh, &pt, &pb) &&
+                      hostmath::WindowedOutputSize(w, kw, dil_w_, stride_w_, padding_, &ow, &pl, &pr),
+                  ITEXB_INVALID_ARGUMENT, "%s: computed output size would be negative", op);
+    const float *pmin_in, *pmax_in, *pmin_f, *pmax_f, *pmin_o, *pmax_o;
+    int64_t c1, c2, nf1, nf2;
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 3, op, "min_input", &pmin_in, &c1));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 4, op, "max_input", &pmax_in, &c2));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 5, op, "min_filter", &pmin_f, &nf1));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 6, op, "max_filter", &pmax_f, &nf2));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 7, op, "min_freezed_output", &pmin_o, &c1));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 8, op, "max_freezed_output", &pmax_o, &c2));
+    ITEXB_REQUIRE(nf1 == nf2 && (nf1 == 1 || nf1 == co), ITEXB_INVALID_ARGUMENT,
+                  "%s: min_filter/max_filter must be scalars or vectors of %lld elements", op, (long long)co);
+    const float min_in = pmin_in[0], max_in = pmax_in[0], min_o = pmin_o[0], max_o = pmax_o[0];
+    float sum_scale = 1.f;
+    const itexb_tensor_t* summand = nullptr;
+    if (sum_) {
+      ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 9, op, "summand"));
+      summand = &ctx->inputs[9];
+      ITEXB_REQUIRE(summand->dtype == ITEXB_DT_QUINT8 || summand->dtype == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT,
+                    "%s: summand must be quint8 or qint8", op);
+      ITEXB_REQUIRE(summand->rank == 4 && summand->dims[0] == n && summand->dims[1] == oh && summand->dims[2] == ow &&
+                        summand->dims[3] == co,
+                    ITEXB_INVALID_ARGUMENT, "%s: summand must have the shape of the output", op);
+      const float *ps1, *ps2;
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 10, op, "min_summand", &ps1, &c1));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 11, op, "max_summand", &ps2, &c2));
+      sum_scale = hostmath::ConvSumScale(min_o, max_o, ps1[0], ps2[0], out_type_, summand->dtype);
+    }
+
+    itexb_tensor_t dst, omin, omax;
+    const int64_t out_dims[4] = {n, oh, ow, co};
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 0, out_type_, out_dims, 4, false, &dst));
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, ITEXB_DT_FLOAT, nullptr, 0, true, &omin));
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 2, ITEXB_DT_FLOAT, nullptr, 0, true, &omax));
+    *static_cast<float*>(omin.data) = min_o;
+    *static_cast<float*>(omax.data) = max_o;
+    if (n == 0 || oh == 0 || ow == 0) return ITEXB_OK;
+
+    cudaStream_t st = AsCuda(ctx->stream);
+    const int ord = ctx->device_ordinal;
+    const int c_pad = int((c + 15) / 16 * 16);
+    const int64_t kp = kh * kw * c_pad;
+
+    // ---- filter: [co][kh*kw][c_pad], packed once when constant
+    const bool hit = is_filter_const_ && packed_from_ == f.data && packed_.data() != nullptr && packed_bytes_ == size_t(co) * kp;
+    if (!hit) {
+      ITEXB_RETURN_IF_ERROR(packed_.Ensure(ord, size_t(co) * kp));
+      ITEXB_RETURN_IF_ERROR(itexb_pack_filter_hwio(f.data, packed_.data(), int(kh), int(kw), int(c), int(co), c_pad, ctx->stream));
+      packed_from_ = f.data;
+      packed_bytes_ = size_t(co) * kp;
+      bias_valid_ = false;
+    }
+
+    // ---- per-output-channel scale (ExtendInt8PostOps) and scaled bias (GetBiasHandle)
+    std::vector<float> scales, factors;
+    hostmath::ConvOutputScales(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, out_type_, min_o, max_o, &scales);
+    const float* d_scale = nullptr;
+    ITEXB_RETURN_IF_ERROR(scale_cache_.Get(ord, st, scales.data(), scales.size(), &d_scale));
+    if (tbias_ == ITEXB_DT_QINT32) factors = scales;  // float(b32) * scale[o]
+    else hostmath::ConvFloatBiasFactors(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, scales, &factors);
+    const bool reuse_bias = bias_valid_ && is_bias_const_ && bias_from_ == bias.data && factors == saved_factors_;
+    if (!reuse_bias) {
+      ITEXB_RETURN_IF_ERROR(scaled_bias_.Ensure(ord, size_t(co) * sizeof(float)));
+      const float* d_f = nullptr;
+      ITEXB_RETURN_IF_ERROR(factor_cache_.Get(ord, st, factors.data(), factors.size(), &d_f));
+      ITEXB_RETURN_IF_ERROR(LaunchBiasPrep(kBiasMul, bias.data, tbias_, nullptr, d_f, int(factors.size()), nullptr, 0, 0.f,
+                                           static_cast<float*>(scaled_bias_.data()), int(co), st));
+      bias_valid_ = true;
+      bias_from_ = bias.data;
+      saved_factors_ = factors;
+    }
+
+    itexb_conv_params_t p{};
+    p.n = int(n); p.h = int(h); p.w = int(w); p.c = int(c);
+    p.kh = int(kh); p.kw = int(kw); p.co = int(co);
+    p.stride_h = stride_h_; p.stride_w = stride_w_; p.dil_h = dil_h_; p.dil_w = dil_w_;
+    p.pad_top = int(pt); p.pad_left = int(pl);
+    p.oh = int(oh); p.ow = int(ow);
+    p.c_pad = c_pad;
+    p.x_dtype = tinput_; p.out_dtype = out_type_;
+    p.x = x.data; p.filter_packed = packed_.data(); p.out = dst.data;
+    p.ep.scale = d_scale;
+    p.ep.scale_count = int(scales.size());
+    p.ep.bias = static_cast<const float*>(scaled_bias_.data());
+    p.ep.relu = relu_ ? 1 : 0;
+    if (summand != nullptr) {
+      p.ep.summand = summand->data;
+      p.ep.summand_dtype = summand->dtype;
+      p.ep.ld_summand = co;
+      p.ep.sum_scale = sum_scale;
+    }
+    const size_t ws = itexb_conv2d_workspace_bytes(&p);
+    if (ws > 0) ITEXB_RETURN_IF_ERROR(AllocateTemp(ctx, ws, false, &p.workspace));
+    return itexb_conv2d(&p, ctx->stream);
+  }
+
+ private:
+  const bool relu_, sum_, signed_sum_;
+  int stride_h_ = 1, stride_w_ = 1, dil_h_ = 1, dil_w_ = 1, padding_ = 1;
+  std::vector<int64_t> explicit_paddings_;
+  bool is_filter_const_ = true, is_bias_const_ = true;
+  int tinput_ = ITEXB_DT_QUINT8, tbias_ = ITEXB_DT_FLOAT, out_type_ = ITEXB_DT_QUINT8;
+  DeviceBuffer packed_, scaled_bias_;
+  const void* packed_from_ = nullptr;
+  size_t packed_bytes_ = 0;
+  bool bias_valid_ = false;
+  const void* bias_from_ = nullptr;
+  std::vector<float> saved_factors_;
+  DeviceVectorCache scale_cache_, factor_cache_;
+};
+
+struct ConvBiasReluReq : QuantizedConv2DOp { ConvBiasReluReq() : QuantizedConv2DOp(true, false, false) {} };
+struct ConvBiasReq : QuantizedConv2DOp { ConvBiasReq() : QuantizedConv2DOp(false, false, false) {} };
+struct ConvBiasSumReluReq : QuantizedConv2DOp { ConvBiasSumReluReq() : QuantizedConv2DOp(true, true, false) {} };
+struct ConvBiasSignedSumReluReq : QuantizedConv2DOp { ConvBiasSignedSumReluReq() : QuantizedConv2DOp(true, true, true) {} };
+
+// HostMemory: inputs 3..8 (and 10, 11), outputs 1, 2.
+ITEXB_REGISTER_OP("QuantizedConv2DWithBiasAndReluAndRequantize", ConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", ConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DWithBiasAndRequantize", ConvBiasReq, 9, 3, 0x1f8u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasAndRequantize", ConvBiasReq, 9, 3, 0x1f8u, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DWithBiasSumAndReluAndRequantize", ConvBiasSumReluReq, 12, 3, 0xdf8u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize", ConvBiasSumReluReq, 12, 3, 0xdf8u, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DWithBiasSignedSumAndReluAndRequantize", ConvBiasSignedSumReluReq, 12, 3, 0xdf8u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasSignedSumAndReluAndRequantize", ConvBiasSignedSumReluReq, 12, 3, 0xdf8u, 0x6u);
+
+}  // namespace
+}  // namespace itexb

@@ -1,0 +1,331 @@
+"""Op-level Python face of libitexb200: ITEX's op names, attrs and argument order.
+
+An `Op` is one graph node: created once from the op name and attrs (like the reference's
+kernel constructor), computed many times.  Device arguments are torch CUDA tensors;
+HostMemory arguments (every min_*/max_* range) are Python floats, sequences or NumPy
+arrays and HostMemory outputs come back as NumPy.  Outputs and temporaries are allocated
+through callbacks, the way a TensorFlow shim would answer TF_AllocateOutput /
+TF_AllocateTemp - here with torch's allocator, so results are ordinary torch tensors.
+
+The module-level functions mirror the generated Python wrappers the reference's tests
+call (`load_ops_library._ITEXQuantizeV2(input=..., min_range=..., T=...)`, see
+itex/python/ops/load_ops_library.py:29-72).
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from .kernels import torch_dtype
+
+_NAME_TO_DT = {
+    "float": L.DT_FLOAT, "float32": L.DT_FLOAT, "bfloat16": L.DT_BFLOAT16, "half": L.DT_HALF, "float16": L.DT_HALF,
+    "qint8": L.DT_QINT8, "quint8": L.DT_QUINT8, "qint32": L.DT_QINT32, "int8": L.DT_INT8, "int32": L.DT_INT32,
+}
+_TORCH_TO_DT = {torch.float32: L.DT_FLOAT, torch.bfloat16: L.DT_BFLOAT16, torch.float16: L.DT_HALF,
+                torch.int8: L.DT_QINT8, torch.uint8: L.DT_QUINT8, torch.int32: L.DT_QINT32}
+_TYPE_ATTRS = {"T", "T1", "T2", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype",
+               "in_dtype", "Tsummand"}
+
+
+def as_dtype(v):
+    """Accepts an itexb_dtype_t number, a TF-style name ('qint8') or a torch dtype."""
+    if isinstance(v, int):
+        return v
+    if isinstance(v, torch.dtype):
+        return _TORCH_TO_DT[v]
+    return _NAME_TO_DT[str(v)]
+
+
+def _setup(lib):
+    if getattr(lib, "_ops_ready", False):
+        return
+    lib.itexb_op_list.restype = C.POINTER(C.c_char_p)
+    lib.itexb_op_delete.restype = None
+    lib.itexb_op_create.argtypes = [C.c_char_p, C.POINTER(L.Attr), C.c_int, C.POINTER(C.c_void_p)]
+    lib.itexb_op_compute.argtypes = [C.c_void_p, C.POINTER(L.OpContext)]
+    lib.itexb_op_delete.argtypes = [C.c_void_p]
+    lib._ops_ready = True
+
+
+def op_list():
+    lib = L.load()
+    _setup(lib)
+    names, p, i = [], lib.itexb_op_list(), 0
+    while p[i]:
+        names.append(p[i].decode())
+        i += 1
+    return names
+
+
+def op_signature(name):
+    lib = L.load()
+    nin, nout, hin, hout = C.c_int(), C.c_int(), C.c_uint32(), C.c_uint32()
+    L.check(lib.itexb_op_signature(name.encode(), C.byref(nin), C.byref(nout), C.byref(hin), C.byref(hout)))
+    return nin.value, nout.value, hin.value, hout.value
+
+
+def _make_attrs(attrs):
+    arr = (L.Attr * max(1, len(attrs)))()
+    keep = []
+    for i, (k, v) in enumerate(attrs.items()):
+        a = arr[i]
+        kb = k.encode()
+        keep.append(kb)
+        a.name = kb
+        if k in _TYPE_ATTRS:
+            a.type, a.i = 4, as_dtype(v)
+        elif isinstance(v, bool):
+            a.type, a.i = 2, int(v)
+        elif isinstance(v, int):
+            a.type, a.i = 0, v
+        elif isinstance(v, float):
+            a.type, a.f = 1, v
+        elif isinstance(v, str):
+            sb = v.encode()
+            keep.append(sb)
+            a.type, a.s = 3, sb
+        elif isinstance(v, (list, tuple)) and all(isinstance(e, str) for e in v) and len(v) > 0:
+            bs = [e.encode() for e in v]
+            sl = (C.c_char_p * len(bs))(*bs)
+            keep += [bs, sl]
+            a.type, a.list_s, a.list_len = 6, sl, len(bs)
+        elif isinstance(v, (list, tuple)):
+            il = (C.c_int64 * max(1, len(v)))(*[int(e) for e in v])
+            keep.append(il)
+            a.type, a.list_i, a.list_len = 5, il, len(v)
+        else:
+            raise TypeError("attr %s: unsupported value %r" % (k, v))
+    return arr, len(attrs), keep
+
+
+class Op:
+    """One kernel instance (itexb_op_t)."""
+
+    def __init__(self, op_name, **attrs):
+        self.lib = L.load()
+        _setup(self.lib)
+        self.name = op_name
+        self.nin, self.nout, self.host_in, self.host_out = op_signature(op_name)
+        arr, n, keep = _make_attrs(attrs)
+        h = C.c_void_p()
+        L.check(self.lib.itexb_op_create(op_name.encode(), arr, n, C.byref(h)))
+        self._h = h
+        self._outputs = {}
+        self._temps = []
+        self._alloc_out_cb = L.ALLOC_OUTPUT_FN(self._allocate_output)
+        self._alloc_tmp_cb = L.ALLOC_TEMP_FN(self._allocate_temp)
+        self._device = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self.lib.itexb_op_delete(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    # -- callbacks (the role of TF_AllocateOutput / TF_AllocateTemp) --------------------
+    def _allocate_output(self, user, index, tp):
+        try:
+            t = tp.contents
+            shape = [t.dims[i] for i in range(t.rank)]
+            if t.on_host:
+                arr = np.empty(shape, dtype=np.float32 if t.dtype == L.DT_FLOAT else np.uint8)
+                t.data = arr.ctypes.data
+                self._outputs[index] = arr
+            else:
+                ten = torch.empty(shape, dtype=torch_dtype(t.dtype), device=self._device)
+                t.data = ten.data_ptr()
+                self._outputs[index] = ten
+            return L.OK
+        except Exception:  # allocation failure surfaces as a status, never as an exception in C
+            return L.RESOURCE_EXHAUSTED
+
+    def _allocate_temp(self, user, nbytes, on_host, pp):
+        try:
+            if on_host:
+                buf = np.empty(max(1, nbytes), dtype=np.uint8)
+                pp[0] = buf.ctypes.data
+            else:
+                buf = torch.empty(max(1, nbytes), dtype=torch.uint8, device=self._device)
+                pp[0] = buf.data_ptr()
+            self._temps.append(buf)
+            return L.OK
+        except Exception:
+            return L.RESOURCE_EXHAUSTED
+
+    def __call__(self, *inputs, device=None, dtypes=None):
+        """Runs Compute.  `dtypes` optionally overrides the itexb dtype of tensor inputs
+        (e.g. DT_INT8 for FP8 bytes held in a torch.int8/uint8 tensor)."""
+        keep = []
+        tens = (L.Tensor * max(1, len(inputs)))()
+        dev = device
+        for i, x in enumerate(inputs):
+            t = tens[i]
+            if isinstance(x, torch.Tensor) and x.is_cuda:
+                x = x.contiguous()
+                dev = dev or x.device
+                t.dtype = (dtypes or {}).get(i, _TORCH_TO_DT[x.dtype])
+                t.rank = x.dim()
+                for d in range(x.dim()):
+                    t.dims[d] = x.shape[d]
+                t.data = x.data_ptr()
+                t.on_host = 0
+                keep.append(x)
+            else:
+                if isinstance(x, torch.Tensor):
+                    x = x.numpy()
+                arr = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+                t.dtype = L.DT_FLOAT
+                t.rank = arr.ndim
+                for d in range(arr.ndim):
+                    t.dims[d] = arr.shape[d]
+                t.data = arr.ctypes.data
+                t.on_host = 1
+                keep.append(arr)
+        self._device = dev or torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+        self._outputs = {}
+        ctx = L.OpContext()
+        ctx.user = None
+        ctx.num_inputs = len(inputs)
+        ctx.inputs = tens
+        ctx.device_ordinal = self._device.index or 0
+        ctx.stream = torch.cuda.current_stream(self._device).cuda_stream if torch.cuda.is_available() else None
+        ctx.allocate_output = self._alloc_out_cb
+        ctx.allocate_temp = self._alloc_tmp_cb
+        try:
+            L.check(self.lib.itexb_op_compute(self._h, C.byref(ctx)))
+        finally:
+            self._temps = []  # torch's allocator is stream-ordered: safe to release after enqueue
+        outs = [self._outputs.get(i) for i in range(self.nout)]
+        outs = [o.reshape(()).item() if isinstance(o, np.ndarray) and o.ndim == 0 else o for o in outs]
+        return outs[0] if self.nout == 1 else tuple(outs)
+
+
+_op_cache = {}
+
+
+def _cached(op_name, attrs):
+    key = (op_name, tuple(sorted((k, tuple(v) if isinstance(v, (list, tuple)) else v) for k, v in attrs.items())))
+    op = _op_cache.get(key)
+    if op is None:
+        op = _op_cache[key] = Op(op_name, **attrs)
+    return op
+
+
+def _ITEXQuantizeV2(input, min_range, max_range, T="qint8", mode="SCALED", round_mode="HALF_AWAY_FROM_ZERO",
+                    narrow_range=False, axis=-1, ensure_minimum_range=0.01, dtype="float",
+                    classic_asymmetric_algorithm=False, op_name="_ITEXQuantizeV2"):
+    """-> (output, output_min, output_max)"""
+    attrs = dict(T=T, mode=mode, round_mode=round_mode, narrow_range=bool(narrow_range), axis=-1 if axis is None else int(axis),
+                 ensure_minimum_range=float(ensure_minimum_range), dtype=dtype,
+                 classic_asymmetric_algorithm=bool(classic_asymmetric_algorithm))
+    return _cached(op_name, attrs)(input, min_range, max_range)
+
+
+def _ITEXDequantize(input, min_range, max_range, mode="SCALED", narrow_range=False, axis=-1, dtype="float",
+                    op_name="_ITEXDequantize"):
+    attrs = dict(T=_TORCH_TO_DT[input.dtype], mode=mode, narrow_range=bool(narrow_range),
+                 axis=-1 if axis is None else int(axis), dtype=dtype)
+    return _cached(op_name, attrs)(input, min_range, max_range)
+
+
+def _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, freezed, attrs):
+    args = [a, b, bias, min_a, max_a, min_b, max_b] + list(freezed)
+    dtypes = {2: L.DT_QINT32} if bias.dtype == torch.int32 else None
+    return _cached(op_name, attrs)(*args, dtypes=dtypes)
+
+
+def _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const, scaled_bias_mode, with_tbias=True):
+    attrs = dict(T1="quint8", T2="qint8", Toutput=Toutput, transpose_a=bool(transpose_a), transpose_b=bool(transpose_b),
+                 input_quant_mode=input_quant_mode, is_weight_const=bool(is_weight_const))
+    if with_tbias:
+        attrs["Tbias"] = "qint32" if bias.dtype == torch.int32 else _TORCH_TO_DT[bias.dtype]
+    if scaled_bias_mode is not None:
+        attrs["_scaled_bias_mode"] = scaled_bias_mode
+    return attrs
+
+
+def _ITEXQuantizedMatMulWithBias(a, b, bias, min_a, max_a, min_b, max_b, Toutput="qint32", transpose_a=False,
+                                 transpose_b=False, input_quant_mode="MIN_FIRST", is_weight_const=True,
+                                 scaled_bias_mode=None, op_name="_ITEXQuantizedMatMulWithBias"):
+    """-> (out, min_out, max_out)"""
+    return _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, (),
+                             _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const, scaled_bias_mode))
+
+
+def _ITEXQuantizedMatMulWithBiasAndRelu(a, b, bias, min_a, max_a, min_b, max_b, Toutput="qint32", transpose_a=False,
+                                        transpose_b=False, input_quant_mode="MIN_FIRST", is_weight_const=True,
+                                        scaled_bias_mode=None, op_name="_ITEXQuantizedMatMulWithBiasAndRelu"):
+    return _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, (),
+                             _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const,
+                                       scaled_bias_mode, with_tbias=False))
+
+
+def _ITEXQuantizedMatMulWithBiasAndRequantize(a, b, bias, min_a, max_a, min_b, max_b, min_freezed_output, max_freezed_output,
+                                              Toutput="quint8", transpose_a=False, transpose_b=False,
+                                              input_quant_mode="MIN_FIRST", is_weight_const=True, scaled_bias_mode=None,
+                                              op_name="_ITEXQuantizedMatMulWithBiasAndRequantize"):
+    return _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, (min_freezed_output, max_freezed_output),
+                             _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const, scaled_bias_mode))
+
+
+def _ITEXQuantizedMatMulWithBiasAndReluAndRequantize(a, b, bias, min_a, max_a, min_b, max_b, min_freezed_output,
+                                                     max_freezed_output, Toutput="quint8", transpose_a=False, transpose_b=False,
+                                                     input_quant_mode="MIN_FIRST", is_weight_const=True, scaled_bias_mode=None,
+                                                     op_name="_ITEXQuantizedMatMulWithBiasAndReluAndRequantize"):
+    return _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, (min_freezed_output, max_freezed_output),
+                             _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const, scaled_bias_mode))
+
+
+def _ITEXQuantizedMatMulWithBiasAndDequantize(a, b, bias, min_a, max_a, min_b, max_b, min_freezed_output, max_freezed_output,
+                                              Toutput="float", transpose_a=False, transpose_b=False,
+                                              input_quant_mode="MIN_FIRST", is_weight_const=True, scaled_bias_mode=None,
+                                              op_name="_ITEXQuantizedMatMulWithBiasAndDequantize"):
+    """-> out"""
+    return _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, (min_freezed_output, max_freezed_output),
+                             _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const, scaled_bias_mode))
+
+
+def _ITEXQuantizedConv2DWithBiasAndReluAndRequantize(input, filter, bias, min_input, max_input, min_filter, max_filter,
+                                                     min_freezed_output, max_freezed_output, strides=(1, 1, 1, 1),
+                                                     padding="SAME", dilations=(1, 1, 1, 1), out_type="quint8",
+                                                     padding_list=(), is_filter_const=True, is_bias_const=True,
+                                                     summand=None, min_summand=None, max_summand=None,
+                                                     op_name="_ITEXQuantizedConv2DWithBiasAndReluAndRequantize"):
+    """-> (output, min_output, max_output).  With `summand` the Sum-fused op names apply."""
+    attrs = dict(Tinput=_TORCH_TO_DT[input.dtype], Tfilter="qint8",
+                 Tbias="qint32" if bias.dtype == torch.int32 else _TORCH_TO_DT[bias.dtype], out_type=out_type,
+                 strides=list(strides), padding=padding, dilations=list(dilations), data_format="NHWC",
+                 is_filter_const=bool(is_filter_const), is_bias_const=bool(is_bias_const))
+    if padding_list:
+        attrs["padding_list"] = list(padding_list)
+    args = [input, filter, bias, min_input, max_input, min_filter, max_filter, min_freezed_output, max_freezed_output]
+    if summand is not None:
+        args += [summand, min_summand, max_summand]
+    dtypes = {2: L.DT_QINT32} if bias.dtype == torch.int32 else None
+    return _cached(op_name, attrs)(*args, dtypes=dtypes)
+
+
+def Fp8Quantize(x, x_amax, x_scale, fp8_meta_index, fp8_dtype="E4M3"):
+    """-> y (int8 tensor holding fp8 bytes); x_amax[fp8_meta_index] is raised in place."""
+    op = _cached("Fp8Quantize", dict(in_dtype=_TORCH_TO_DT[x.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
+    return op(x, x_amax, x_scale)
+
+
+def Fp8Dequantize(x, x_scale_inv, fp8_meta_index, fp8_dtype="E4M3", out_dtype="float"):
+    op = _cached("Fp8Dequantize", dict(out_dtype=out_dtype, fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
+    return op(x, x_scale_inv, dtypes={0: L.DT_INT8})
+
+
+def Fp8Matmul(src, weight, bias, post_add, a_scale_inv, b_scale_inv, c_amax, c_scale, fp8_meta_index_a, fp8_meta_index_b,
+              fp8_meta_index_c=-1, transpose_a=False, transpose_b=False, use_bias=False, has_post_add=False,
+              sum_dtype="float", out_dtype="float", fp8_dtype_a="E4M3", fp8_dtype_b="E4M3", fp8_dtype_c=""):
+    op = _cached("Fp8Matmul", dict(fp8_meta_index_a=int(fp8_meta_index_a), fp8_meta_index_b=int(fp8_meta_index_b),
+                                   fp8_meta_index_c=int(fp8_meta_index_c), transpose_a=bool(transpose_a),
+                                   transpose_b=bool(transpose_b), use_bias=bool(use_bias), has_post_add=bool(has_post_add),
+                                   sum_dtype=sum_dtype, out_dtype=out_dtype, fp8_dtype_a=fp8_dtype_a, fp8_dtype_b=fp8_dtype_b,
+                                   fp8_dtype_c=fp8_dtype_c))
+    return op(src, weight, bias, post_add, a_scale_inv, b_scale_inv, c_amax, c_scale, dtypes={0: L.DT_INT8, 1: L.DT_INT8})

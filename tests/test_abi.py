@@ -1,0 +1,113 @@
+"""CPU checks of the C-ABI boundary: the library loads without a GPU, exports every
+function include/itexb200.h declares, and the op layer reproduces the reference's
+construction-time errors (OP_REQUIRES in the kernel constructors)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "itexb200.h")).read()
+    return sorted(set(re.findall(r"ITEXB_API\s+[^;(]*?\b(itexb_\w+)\s*\(", text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol(itex):
+    lib = itex.load()
+    names = declared_symbols()
+    assert len(names) >= 55
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    assert b"sm_100a" in lib.itexb_version()
+
+
+def test_no_device_is_reported_not_hidden(itex):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    lib = itex.load()
+    n = ctypes.c_int(-1)
+    st = lib.itexb_rt_device_count(ctypes.byref(n))
+    assert st == itex._lib.FAILED_PRECONDITION and n.value == 0
+    assert b"CUDA" in lib.itexb_last_error()
+
+
+def test_op_registry_names_and_host_memory_masks(itex):
+    import importlib
+    ops = importlib.import_module("itex_b200.ops")
+    names = set(ops.op_list())
+    for base in ("QuantizeV2", "Dequantize", "QuantizedMatMulWithBias", "QuantizedMatMulWithBiasAndRelu",
+                 "QuantizedMatMulWithBiasAndRequantize", "QuantizedMatMulWithBiasAndReluAndRequantize",
+                 "QuantizedMatMulWithBiasAndDequantize", "QuantizedConv2DWithBiasAndReluAndRequantize"):
+        assert base in names and "_ITEX" + base in names  # stock and _ITEX names, like the reference GPU build
+    for n in ("Fp8Quantize", "Fp8Dequantize", "Fp8Matmul"):
+        assert n in names
+    # min_range/max_range and output_min/output_max are HostMemory (gpu/quantize_op.cc:25-31)
+    assert ops.op_signature("_ITEXQuantizeV2") == (3, 3, 0b110, 0b110)
+    assert ops.op_signature("_ITEXDequantize") == (3, 1, 0b110, 0)
+    # min_a..max_b, min/max_freezed_output host; min_out/max_out host (gpu/quantized_matmul.cc:53-102)
+    assert ops.op_signature("_ITEXQuantizedMatMulWithBias") == (7, 3, 0b1111000, 0b110)
+    assert ops.op_signature("_ITEXQuantizedMatMulWithBiasAndDequantize") == (9, 1, 0b111111000, 0)
+    assert ops.op_signature("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize") == (9, 3, 0b111111000, 0b110)
+    with pytest.raises(itex.ItexError) as e:
+        ops.op_signature("NoSuchOp")
+    assert e.value.code == itex._lib.NOT_FOUND
+
+
+@pytest.mark.parametrize("attrs,fragment", [
+    (dict(T="qint8", mode="MIN_COMBINED"), "only supports SCALED and MIN_FIRST MODE"),
+    (dict(T="qint8", mode="BOGUS"), "Mode string must be 'MIN_COMBINED', 'MIN_FIRST', or 'SCALED', is 'BOGUS'"),
+    (dict(T="qint8", mode="SCALED", round_mode="UP"), "Round mode string must be"),
+    (dict(T="qint8", mode="MIN_FIRST", round_mode="HALF_TO_EVEN"), "only supported for mode 'SCALED'"),
+    (dict(T="qint32", mode="SCALED"), "no kernel registered for T=qint32"),
+])
+def test_quantize_constructor_errors(itex, attrs, fragment):
+    import importlib
+    ops = importlib.import_module("itex_b200.ops")
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op("_ITEXQuantizeV2", **attrs)
+    assert e.value.code == itex._lib.INVALID_ARGUMENT and fragment in str(e.value)
+
+
+def test_matmul_and_conv_constructor_errors(itex):
+    import importlib
+    ops = importlib.import_module("itex_b200.ops")
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op("_ITEXQuantizedMatMulWithBias", T1="quint8", T2="qint8", Toutput="qint32", input_quant_mode="SYMMETRIC")
+    assert "Quantization mode must be either MIN_FIRST or SCALED, but received SYMMETRIC" in str(e.value)
+    with pytest.raises(itex.ItexError) as e:  # T1 is quint8-only on these ops (cpu/quantized_matmul.cc:27)
+        ops.Op("_ITEXQuantizedMatMulWithBias", T1="qint8", T2="qint8", Toutput="qint32")
+    assert "no kernel registered" in str(e.value)
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op("_ITEXQuantizedMatMulWithBiasAndDequantize", Toutput="quint8")
+    assert "no kernel registered for Toutput=quint8" in str(e.value)
+    conv = "_ITEXQuantizedConv2DWithBiasAndReluAndRequantize"
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op(conv, strides=[1, 1, 1], padding="SAME")
+    assert "Sliding window strides field must specify 4 dimensions" in str(e.value)
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op(conv, strides=[2, 1, 1, 1], padding="SAME")
+    assert e.value.code == itex._lib.UNIMPLEMENTED and "strides in the batch and depth dimensions" in str(e.value)
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op(conv, strides=[1, 0, 1, 1], padding="SAME")
+    assert "Row and column strides should be larger than 0." in str(e.value)
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op(conv, strides=[1, 1, 1, 1], padding="SAME", dilations=[1, 0, 1, 1])
+    assert "Dilated rates should be larger than 0." in str(e.value)
+    with pytest.raises(itex.ItexError) as e:
+        ops.Op("Fp8Quantize", fp8_meta_index=0, fp8_dtype="E3M4")
+    assert "Unsupported fp8_dtype" in str(e.value)
+    ops.Op(conv, strides=[1, 1, 1, 1], padding="SAME")  # defaults as in the op def
+
+
+def test_fp8_recipe_rejects_what_the_reference_rejects(itex):
+    import importlib
+    fp8 = importlib.import_module("itex_b200.fp8")
+    fp8.DelayedScaling(margin=0, amax_history_len=16, amax_compute_algo="most_recent")
+    with pytest.raises(ValueError):
+        fp8.DelayedScaling(amax_compute_algo=lambda h: h)
+    with pytest.raises(ValueError):
+        fp8.DelayedScaling(scaling_factor_compute_algo=lambda *a: a)
