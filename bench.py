@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
+                    help="keep warming up at least this long so the clock sampler sees the load (0 for profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     m, n, k = WORKLOADS[args.workload]
@@ -221,7 +223,7 @@ def main():
     sampler.start()
     t_warm = time.perf_counter()
     n_warm = 0
-    while n_warm < args.warmup or time.perf_counter() - t_warm < 1.0:
+    while n_warm < args.warmup or time.perf_counter() - t_warm < args.min_warmup_seconds:
         out, q, qmin, qmax = step(x)
         n_warm += 1
         if n_warm % 50 == 0:
