@@ -139,7 +139,5 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   if (g.ep.summand != nullptr && g.ep.ld_summand == 0) g.ep.ld_summand = p->co;
   g.status_word = p->status_word;
   g.idesc = MakeInstrDesc(p->x_dtype, ITEXB_DT_QINT8, bn);
-  const int osz = p->ep.raw_acc ? 4 : DtypeSize(p->out_dtype);
-  g.vec_store = ((reinterpret_cast<uintptr_t>(p->out) & 15) == 0 && ((long long)p->co * osz) % 16 == 0) ? 1 : 0;
   return LaunchGemm(ta, tb, g, bn, false, st);
 }

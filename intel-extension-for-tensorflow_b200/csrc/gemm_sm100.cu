@@ -1,18 +1,25 @@
 // int8 / FP8 GEMM for sm_100a: out[m][n] = epilogue(sum_k a[m][k] * b[n][k]).
 //
-// One persistent CTA per SM, warp-specialised:
-//   warp 0   TMA producer   cp.async.bulk.tensor (2-D tiled, 128-byte swizzle) -> smem ring
-//   warp 1   MMA issuer     tcgen05.mma.cta_group::1.kind::i8 | kind::f8f6f4, 128 x BN x 32 per
-//                           instruction, operands read from smem through UMMA descriptors,
-//                           accumulators (s32 | f32) in tensor memory
-//   warp 2   TMEM allocator (2 accumulator stages of BN columns, so the epilogue of tile i
-//                           overlaps the main loop of tile i+1)
-//   warps 4-7 epilogue      tcgen05.ld 32 lanes x 32 columns per warp, scale/bias/sum/ReLU,
-//                           conversion, 16-byte stores
+// One persistent CTA per SM (384 threads), warp-specialised:
+//   warp 0    TMA producer   cp.async.bulk.tensor (2-D tiled, 128-byte swizzle) -> smem ring of
+//                            128 x 128-byte A tiles and BN x 128-byte B tiles
+//   warp 1    MMA issuer     tcgen05.mma.cta_group::1.kind::i8 | kind::f8f6f4, 128 x BN x 32 per
+//                            instruction, operands read from smem through UMMA descriptors,
+//                            accumulators (s32 | f32) in tensor memory
+//   warp 2    TMEM allocator (2 accumulator stages of BN columns, so the epilogue of tile i
+//                            overlaps the main loop of tile i+1)
+//   warps 4-11 epilogue      two warps per TMEM lane quarter; each takes every other 32-column
+//                            block: tcgen05.ld (32 lanes x 32 columns) -> scale / bias / sum /
+//                            ReLU -> conversion -> swizzled staging tile in smem -> one TMA
+//                            store per 32 x 32 block (direct stores when rows are unaligned)
 // Pipelines are mbarrier based: full[s]/empty[s] between producer and MMA issuer
 // (tcgen05.commit releases a stage), tmem_full[a]/tmem_empty[a] between MMA issuer and
 // epilogue.  Every wait is bounded: on expiry the kernel raises a status word, all roles
 // leave their loops, TMEM is released and the kernel returns.
+//
+// Epilogue arithmetic avoids the conversion instructions (int<->float on the multi-function
+// unit is the slowest pipe of this part and was the measured bottleneck): both directions use
+// the exact 1.5*2^23 adder trick, with the real conversion kept for accumulators beyond 2^22.
 //
 // No cluster launch and no multicast loads are used, so the same code runs unchanged in
 // single- and multi-GPU jobs.
@@ -33,8 +40,9 @@ namespace {
 constexpr int kBM = 128;          // rows of a per tile = TMEM lanes
 constexpr int kBK = 128;          // bytes of K per pipeline stage (one 128-byte swizzle row)
 constexpr int kUmmaK = 32;        // bytes of K per tcgen05.mma
-constexpr int kThreads = 256;
-constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = 384;          // 4 control warps + 8 epilogue warps
+constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter: their instruction streams hide each other's latencies
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kGroupM = 16;       // tile rasterisation: m-tiles per L2 super-group
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 
@@ -46,9 +54,9 @@ template <int BN> struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128), 8 (64)
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two >= 32
-  static constexpr int kParamBytes = 2 * 2 * BN * 4;           // scale + bias, per accumulator stage
   static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kParamBytes + kBarrierBytes;
+  static constexpr int kStagingBytes = kEpilogueWarps * 4096;  // one 32 x 128-byte output block per epilogue warp
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -147,7 +155,17 @@ __device__ __forceinline__ void TmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void TmemLdWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Waits for this thread's outstanding tcgen05.ld.  The registers are listed as in/out
+// operands so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void TmemLdWait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 
 // K-major operand tile whose rows are 128 bytes, stored with the 128-byte swizzle TMA
 // writes: 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
@@ -156,15 +174,25 @@ __device__ __forceinline__ uint64_t UmmaDescSw128(uint32_t smem_addr) {
          (uint64_t(2) << 61);
 }
 
-__device__ __forceinline__ void EpilogueBarrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------
 // Epilogue math and stores
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ int SatRneInt(float f, float lo, float hi) {
-  f = f < lo ? lo : (f > hi ? hi : f);
-  return __float2int_rn(f);
+// Conversions run on the multi-function unit, which is more than an order of magnitude
+// slower than the fp32/int pipes on this part and becomes the epilogue's bottleneck.  Both
+// directions are therefore done with the 1.5*2^23 trick on the fp32 adder, which rounds to
+// nearest even exactly like the conversion instructions do.
+constexpr float kMagic = 12582912.f;        // 1.5 * 2^23
+constexpr int kMagicBits = 0x4B400000;
+
+// Low byte of rne(clamp(f, lo, hi)) for -128 <= lo, hi <= 255 (NaN converts like lo).
+__device__ __forceinline__ uint32_t SatRneByte(float f, float lo, float hi) {
+  f = fminf(fmaxf(f, lo), hi);
+  return uint32_t(__float_as_int(__fadd_rn(f, kMagic))) & 0xffu;
 }
+
+// float(a), exact, valid when |a| <= 2^22.
+__device__ __forceinline__ float SmallIntToFloat(int a) { return __fsub_rn(__int_as_float(a + kMagicBits), kMagic); }
 
 __device__ __forceinline__ float LoadSummand(const void* p, int dt, long long idx) {
   switch (dt) {
@@ -180,120 +208,265 @@ __device__ __forceinline__ uint32_t Pack4(int a, int b, int c, int d) {
   return uint32_t(a & 0xff) | (uint32_t(b & 0xff) << 8) | (uint32_t(c & 0xff) << 16) | (uint32_t(d & 0xff) << 24);
 }
 
-// Converts and stores 32 consecutive outputs of one row.  `ncols` (<= 32) columns are in
-// range; `vec` says the row segment is 16-byte aligned and complete.
-__device__ __forceinline__ void StoreRow32(const GemmArgs& g, const float (&v)[32], long long row, int col0, int ncols,
-                                           bool vec, float* thread_amax, float out_scale) {
-  const long long base = row * g.ldo + col0;
-  switch (g.out_dtype) {
-    case ITEXB_DT_FLOAT: {
-      float* o = static_cast<float*>(g.out) + base;
-      if (vec) {
+// Converts 32 consecutive outputs of one row to the output type and packs them into
+// 32-bit words: 32 words for 4-byte types, 16 for 2-byte, 8 for 1-byte.
+__device__ __forceinline__ void ConvertRow32(int out_dtype, const float (&v)[32], int ncols, uint32_t (&w)[32],
+                                             float* thread_amax, float out_scale) {
+  switch (out_dtype) {
+    case ITEXB_DT_FLOAT:
 #pragma unroll
-        for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-      } else {
-        for (int j = 0; j < ncols; ++j) o[j] = v[j];
+      for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
+      break;
+    case ITEXB_DT_BFLOAT16:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
       }
       break;
-    }
-    case ITEXB_DT_BFLOAT16: {
-      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + base;
-      if (vec) {
+    case ITEXB_DT_HALF:
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t w[4];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
-            w[t] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          reinterpret_cast<uint4*>(o)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      } else {
-        for (int j = 0; j < ncols; ++j) o[j] = __float2bfloat16_rn(v[j]);
+      for (int j = 0; j < 16; ++j) {
+        __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
       }
       break;
-    }
-    case ITEXB_DT_HALF: {
-      __half* o = static_cast<__half*>(g.out) + base;
-      if (vec) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t w[4];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            __half2 h = __floats2half2_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
-            w[t] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          reinterpret_cast<uint4*>(o)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      } else {
-        for (int j = 0; j < ncols; ++j) o[j] = __float2half_rn(v[j]);
-      }
-      break;
-    }
-    case ITEXB_DT_QINT32: case ITEXB_DT_INT32: {
+    case ITEXB_DT_QINT32: case ITEXB_DT_INT32:
       // oneDNN converts the fp32 tail to s32 with saturation and RNE.
-      int* o = static_cast<int*>(g.out) + base;
-      int q[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        float f = v[j];
-        q[j] = f >= 2147483648.f ? 2147483647 : (f <= -2147483648.f ? (-2147483647 - 1) : __float2int_rn(f));
-      }
-      if (vec) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) reinterpret_cast<int4*>(o)[j] = make_int4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
-      } else {
-        for (int j = 0; j < ncols; ++j) o[j] = q[j];
+        const float f = v[j];
+        w[j] = uint32_t(f >= 2147483648.f ? 2147483647 : (f <= -2147483648.f ? (-2147483647 - 1) : __float2int_rn(f)));
       }
       break;
-    }
     case ITEXB_DT_QUINT8: case ITEXB_DT_UINT8: case ITEXB_DT_QINT8: case ITEXB_DT_INT8: {
-      const bool sg = (g.out_dtype == ITEXB_DT_QINT8 || g.out_dtype == ITEXB_DT_INT8);
+      const bool sg = (out_dtype == ITEXB_DT_QINT8 || out_dtype == ITEXB_DT_INT8);
       const float lo = sg ? -128.f : 0.f, hi = sg ? 127.f : 255.f;
-      uint8_t* o = static_cast<uint8_t*>(g.out) + base;
-      int q[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) q[j] = SatRneInt(v[j], lo, hi);
-      if (vec) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-          reinterpret_cast<uint4*>(o)[j] =
-              make_uint4(Pack4(q[16 * j], q[16 * j + 1], q[16 * j + 2], q[16 * j + 3]),
-                         Pack4(q[16 * j + 4], q[16 * j + 5], q[16 * j + 6], q[16 * j + 7]),
-                         Pack4(q[16 * j + 8], q[16 * j + 9], q[16 * j + 10], q[16 * j + 11]),
-                         Pack4(q[16 * j + 12], q[16 * j + 13], q[16 * j + 14], q[16 * j + 15]));
-      } else {
-        for (int j = 0; j < ncols; ++j) o[j] = uint8_t(q[j]);
-      }
+      for (int j = 0; j < 8; ++j)
+        w[j] = SatRneByte(v[4 * j], lo, hi) | (SatRneByte(v[4 * j + 1], lo, hi) << 8) | (SatRneByte(v[4 * j + 2], lo, hi) << 16) |
+               (SatRneByte(v[4 * j + 3], lo, hi) << 24);
       break;
     }
     case ITEXB_DT_FP8_E4M3: case ITEXB_DT_FP8_E5M2: {
-      const __nv_fp8_interpretation_t kind = g.out_dtype == ITEXB_DT_FP8_E4M3 ? __NV_E4M3 : __NV_E5M2;
-      uint8_t* o = static_cast<uint8_t*>(g.out) + base;
-      int q[32];
+      const __nv_fp8_interpretation_t kind = out_dtype == ITEXB_DT_FP8_E4M3 ? __NV_E4M3 : __NV_E5M2;
       float m = *thread_amax;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < 32; ++j)
         if (j < ncols) m = fmaxf(m, fabsf(v[j]));
-        q[j] = (int)__nv_cvt_float_to_fp8(__fmul_rn(v[j], out_scale), __NV_SATFINITE, kind);
-      }
       *thread_amax = m;
-      if (vec) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          reinterpret_cast<uint4*>(o)[j] =
-              make_uint4(Pack4(q[16 * j], q[16 * j + 1], q[16 * j + 2], q[16 * j + 3]),
-                         Pack4(q[16 * j + 4], q[16 * j + 5], q[16 * j + 6], q[16 * j + 7]),
-                         Pack4(q[16 * j + 8], q[16 * j + 9], q[16 * j + 10], q[16 * j + 11]),
-                         Pack4(q[16 * j + 12], q[16 * j + 13], q[16 * j + 14], q[16 * j + 15]));
-      } else {
-        for (int j = 0; j < ncols; ++j) o[j] = uint8_t(q[j]);
+      for (int j = 0; j < 8; ++j) {
+        int q[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) q[t] = (int)__nv_cvt_float_to_fp8(__fmul_rn(v[4 * j + t], out_scale), __NV_SATFINITE, kind);
+        w[j] = Pack4(q[0], q[1], q[2], q[3]);
       }
       break;
     }
     default: break;
+  }
+}
+
+// Writes the packed words of one row segment straight to global memory.  `esz` is the
+// output element size, `vec` says the segment is complete and 16-byte aligned.  All
+// indices are compile-time constants so that `w` stays in registers.
+__device__ __forceinline__ void StoreRowDirect(void* out, long long elem_index, int esz, const uint32_t (&w)[32], int ncols, bool vec) {
+  uint8_t* o = static_cast<uint8_t*>(out) + elem_index * esz;
+  if (vec) {
+    const int units = 2 * esz;  // 16-byte units in 32 elements
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < units) reinterpret_cast<uint4*>(o)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  } else if (esz == 4) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) reinterpret_cast<uint32_t*>(o)[j] = w[j];
+  } else if (esz == 2) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) reinterpret_cast<uint16_t*>(o)[j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) o[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+  }
+}
+
+// Writes the packed words of lane `lane`'s row into the warp's staging tile (32 rows of
+// 32*esz bytes) in the swizzled order a TMA store with SWIZZLE_{128,64,32}B expects:
+// 16-byte unit j of row r lives at unit j ^ ((r / (8/units)) % units).
+__device__ __forceinline__ void StoreRowStaged(uint8_t* stage, int lane, int esz, const uint32_t (&w)[32]) {
+  const int units = 2 * esz;                 // 8, 4 or 2 units per row
+  const int x = (lane / (8 / units)) % units;
+  uint8_t* row = stage + lane * (32 * esz);
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (j < units) *reinterpret_cast<uint4*>(row + ((j ^ x) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+
+__device__ __forceinline__ void TmaStore2d(const void* tmap, uint32_t src_smem, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src_smem), "r"(c0),
+               "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void TmaStoreCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Blocks until at most `pending` of this thread's store groups are still reading shared memory.
+__device__ __forceinline__ void TmaStoreWaitRead(int pending) {
+  if (pending >= 3) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+  else if (pending == 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+  else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void TmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Per-warp state of the epilogue that does not change from chunk to chunk.
+struct EpilogueCtx {
+  bool has_scale, has_bias;
+  int mode;           // (0 no scale | 1 scalar scale | 2 scale vector) + 3 * has_bias
+  bool vec_params;    // scale / bias vectors are 16-byte aligned: fetch them as float4
+  float scalar_scale; // the scale when it is one value for the whole matrix
+  const float* scale; // per-column scale vector or nullptr
+  const float* bias;  // per-column bias vector or nullptr
+  int esz;            // bytes per output element
+  int nbuf;           // staging buffers per warp: 4096 / (1024 * esz)
+  uint8_t* stage;     // this warp's 4 KiB of staging
+  float out_scale;
+};
+
+// v[j] = float(acc[j]) * scale + bias for the 32 columns starting at col0, specialised at
+// compile time on where scale and bias come from so that the executed code is one short
+// straight line.  SMODE: 0 no scale, 1 one scale for the matrix, 2 per-column vector.
+// Per-column values are fetched 16 columns at a time as float4 loads of an address all
+// lanes share (one broadcast transaction each, served by L1), issued together so their
+// latencies overlap.
+template <bool F8, int SMODE, bool BIAS>
+__device__ __forceinline__ void ScaleBias32(const uint32_t (&r)[32], float (&v)[32], const float* __restrict__ scale,
+                                            const float* __restrict__ bias, float scalar_scale, int col0) {
+  // int32 -> fp32: exact adder trick when every accumulator of the row segment is within
+  // +-2^22 (the usual case), the conversion instruction otherwise.
+  if (F8) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  } else {
+    uint32_t big = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) big |= (r[j] + 0x400000u) & 0xff800000u;
+    if (big == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = SmallIntToFloat(int(r[j]));
+    } else {
+      // volatile: keeps the slow conversions inside this branch (the compiler would
+      // otherwise execute them speculatively on every block and select afterwards)
+#pragma unroll
+      for (int j = 0; j < 32; ++j) asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(v[j]) : "r"(r[j]));
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float4 s4[4], b4[4];
+    if (SMODE == 2) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s4[i] = __ldg(reinterpret_cast<const float4*>(scale + col0) + 4 * h + i);
+    }
+    if (BIAS) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) b4[i] = __ldg(reinterpret_cast<const float4*>(bias + col0) + 4 * h + i);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = 16 * h + 4 * i;
+      if (SMODE == 2) {
+        v[j] = __fmul_rn(v[j], s4[i].x); v[j + 1] = __fmul_rn(v[j + 1], s4[i].y);
+        v[j + 2] = __fmul_rn(v[j + 2], s4[i].z); v[j + 3] = __fmul_rn(v[j + 3], s4[i].w);
+      } else if (SMODE == 1) {
+        v[j] = __fmul_rn(v[j], scalar_scale); v[j + 1] = __fmul_rn(v[j + 1], scalar_scale);
+        v[j + 2] = __fmul_rn(v[j + 2], scalar_scale); v[j + 3] = __fmul_rn(v[j + 3], scalar_scale);
+      }
+      if (BIAS) {
+        v[j] = __fadd_rn(v[j], b4[i].x); v[j + 1] = __fadd_rn(v[j + 1], b4[i].y);
+        v[j + 2] = __fadd_rn(v[j + 2], b4[i].z); v[j + 3] = __fadd_rn(v[j + 3], b4[i].w);
+      }
+    }
+  }
+}
+
+// The same arithmetic for a block that is cut by the matrix edge or whose parameter
+// vectors are not 16-byte aligned: element-wise guarded loads.
+template <bool F8>
+__device__ __forceinline__ void ScaleBias32Edge(const uint32_t (&r)[32], float (&v)[32], const float* scale, const float* bias,
+                                                bool has_scale, float scalar_scale, int col0, int n) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float f;
+    if (F8) f = __uint_as_float(r[j]);
+    else asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(f) : "r"(r[j]));
+    const int c = col0 + j;
+    if (has_scale) f = __fmul_rn(f, (scale != nullptr && c < n) ? __ldg(scale + c) : scalar_scale);
+    if (bias != nullptr && c < n) f = __fadd_rn(f, __ldg(bias + c));
+    v[j] = f;
+  }
+}
+
+// One 32-row x 32-column block of a tile: accumulators `r` (one row per lane) -> scale, bias,
+// sum, ReLU, conversion -> staged TMA store (or direct stores).  `seq` counts the blocks
+// this warp has stored, which selects the staging buffer.
+template <bool F8>
+__device__ __forceinline__ void EpilogueChunk(const GemmArgs& g, const EpilogueCtx& e, const CUtensorMap* tma_out,
+                                              const uint32_t (&r)[32], int lane, int row0, long long row, bool row_ok, int col0,
+                                              int ncols, uint32_t& seq, float* thread_amax) {
+  uint32_t w[32];
+  if (g.ep.raw_acc) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = r[j];
+  } else {
+    float v[32];
+    if (e.vec_params && ncols == 32) {
+      switch (e.mode) {
+        case 0: ScaleBias32<F8, 0, false>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+        case 1: ScaleBias32<F8, 1, false>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+        case 2: ScaleBias32<F8, 2, false>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+        case 3: ScaleBias32<F8, 0, true>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+        case 4: ScaleBias32<F8, 1, true>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+        default: ScaleBias32<F8, 2, true>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+      }
+    } else {
+      ScaleBias32Edge<F8>(r, v, e.scale, e.bias, e.has_scale, e.scalar_scale, col0, g.n);
+    }
+    if (g.ep.summand != nullptr && row_ok) {
+      const long long sb = row * g.ep.ld_summand + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) v[j] = __fadd_rn(v[j], __fmul_rn(g.ep.sum_scale, LoadSummand(g.ep.summand, g.ep.summand_dtype, sb + j)));
+    }
+    if (g.ep.relu) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    }
+    if (g.ep.mid_dtype == ITEXB_DT_BFLOAT16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+    } else if (g.ep.mid_dtype == ITEXB_DT_HALF) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __half2float(__float2half_rn(v[j]));
+    }
+    ConvertRow32(g.out_dtype, v, row_ok ? ncols : 0, w, thread_amax, e.out_scale);
+  }
+  if (g.tma_store) {
+    // The store that last used this staging buffer must have finished reading it.
+    if (lane == 0) TmaStoreWaitRead(e.nbuf - 1);
+    __syncwarp();
+    uint8_t* buf = e.stage + (seq & uint32_t(e.nbuf - 1)) * (1024 * e.esz);  // nbuf is 1, 2 or 4
+    StoreRowStaged(buf, lane, e.esz, w);
+    FenceProxyAsyncShared();
+    __syncwarp();
+    if (lane == 0) {
+      TmaStore2d(tma_out, SmemAddr(buf), col0 * e.esz, row0);  // rows >= m and columns >= n are clipped
+      TmaStoreCommit();
+    }
+    ++seq;
+  } else if (row_ok) {
+    StoreRowDirect(g.out, row * g.ldo + col0, e.esz, w, ncols, g.vec_store && ncols == 32);
   }
 }
 
@@ -313,20 +486,19 @@ __device__ __forceinline__ void TileCoords(int t, int tiles_m, int tiles_n, int*
 // ---------------------------------------------------------------------------------------
 template <int BN, bool F8>
 __global__ void __launch_bounds__(kThreads, 1)
-GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmArgs g) {
+GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+           const __grid_constant__ CUtensorMap tma_out, const GemmArgs g) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_scale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);  // [2][BN]
-  float* s_bias = s_scale + 2 * BN;                                              // [2][BN]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + 2 * BN);
+  uint8_t* s_stage = smem + C::kStages * C::kStageBytes;  // 8 warps x 4 KiB, 1024-aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stage + C::kStagingBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + C::kStages;
   uint64_t* tmem_full_bar = bars + 2 * C::kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* ep_decision = abort_flag + 1;  // [2]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -415,86 +587,50 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
   } else if (warp >= 4) {
     // ---------------- epilogue ----------------
-    const int et = threadIdx.x - 4 * 32;  // 0..127
-    const int q = warp & 3;               // TMEM lane quarter this warp may read
+    // Warp (q, half): TMEM lanes 32q..32q+31 (the quarter its warp id allows it to read),
+    // 32-column blocks half, half+2, ... of every tile.  Warps are independent of each other.
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     float thread_amax = 0.f;
-    float alpha = 1.f;
+    EpilogueCtx ectx;
     const bool has_alpha = g.ep.alpha_a != nullptr && g.ep.alpha_b != nullptr;
-    if (has_alpha) alpha = __fmul_rn(__ldg(g.ep.alpha_a), __ldg(g.ep.alpha_b));
-    const bool has_scale = has_alpha || g.ep.scale_count > 0;
-    const float out_scale = g.ep.out_scale != nullptr ? __ldg(g.ep.out_scale) : 1.f;
+    ectx.scalar_scale = 1.f;
+    ectx.scale = nullptr;
+    if (has_alpha) ectx.scalar_scale = __fmul_rn(__ldg(g.ep.alpha_a), __ldg(g.ep.alpha_b));
+    else if (g.ep.scale_count == 1) ectx.scalar_scale = __ldg(g.ep.scale);
+    else if (g.ep.scale_count > 1) ectx.scale = g.ep.scale;
+    ectx.has_scale = has_alpha || g.ep.scale_count > 0;
+    ectx.bias = g.ep.bias;
+    ectx.has_bias = g.ep.bias != nullptr;
+    ectx.mode = (ectx.scale != nullptr ? 2 : (ectx.has_scale ? 1 : 0)) + (ectx.has_bias ? 3 : 0);
+    ectx.vec_params = ((reinterpret_cast<uintptr_t>(ectx.scale) | reinterpret_cast<uintptr_t>(ectx.bias)) & 15) == 0;
+    ectx.esz = g.out_esz;
+    ectx.nbuf = 4 / g.out_esz;  // 1 (4-byte outputs), 2 (2-byte), 4 (1-byte)
+    ectx.stage = s_stage + (warp - 4) * 4096;
+    ectx.out_scale = g.ep.out_scale != nullptr ? __ldg(g.ep.out_scale) : 1.f;
+    uint32_t seq = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int tm, tn;
       TileCoords(t, tiles_m, tiles_n, &tm, &tn);
-      float* sc = s_scale + acc * BN;
-      float* bi = s_bias + acc * BN;
-      for (int i = et; i < BN; i += kEpilogueThreads) {
-        const int n = tn * BN + i;
-        float s = 1.f, b = 0.f;
-        if (n < g.n) {
-          if (has_alpha) s = alpha;
-          else if (g.ep.scale_count > 1) s = __ldg(g.ep.scale + n);
-          else if (g.ep.scale_count == 1) s = __ldg(g.ep.scale);
-          if (g.ep.bias != nullptr) b = __ldg(g.ep.bias + n);
-        }
-        sc[i] = s;
-        bi[i] = b;
-      }
-      MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
-      // One thread samples the abort flag so that all 128 take the same branch.
-      if (et == 0) ep_decision[acc] = *abort_flag;
-      EpilogueBarrier();  // scale/bias and the decision are visible
-      if (ep_decision[acc]) break;
+      const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
+      if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
       TcFenceAfter();
-      const long long row = (long long)tm * kBM + q * 32 + lane;
+      const int row0 = tm * kBM + q * 32;            // first row of this warp's 32-row block
+      const long long row = (long long)row0 + lane;
+      const bool row_ok = row < g.m;
       const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
+      // number of 32-column blocks of this tile that hold real columns
+      const int nchunks = min(BN / 32, (g.n - tn * BN + 31) / 32);
+      if (row0 < g.m) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        TmemLd32(taddr + uint32_t(c * 32), r);
-        TmemLdWait();
-        const int col0 = tn * BN + c * 32;
-        const int ncols = min(32, g.n - col0);
-        if (row < g.m && ncols > 0) {
-          const bool vec = g.vec_store && ncols == 32;
-          if (g.ep.raw_acc) {
-            int* o = static_cast<int*>(g.out) + row * g.ldo + col0;
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<int4*>(o)[j] = make_int4(int(r[4 * j]), int(r[4 * j + 1]), int(r[4 * j + 2]), int(r[4 * j + 3]));
-            } else {
-              for (int j = 0; j < ncols; ++j) o[j] = int(r[j]);
-            }
-          } else {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float f = F8 ? __uint_as_float(r[j]) : float(int(r[j]));
-              if (has_scale) f = __fmul_rn(f, sc[c * 32 + j]);
-              if (g.ep.bias != nullptr) f = __fadd_rn(f, bi[c * 32 + j]);
-              v[j] = f;
-            }
-            if (g.ep.summand != nullptr) {
-              const long long sb = row * g.ep.ld_summand + col0;
-              for (int j = 0; j < ncols; ++j)
-                v[j] = __fadd_rn(v[j], __fmul_rn(g.ep.sum_scale, LoadSummand(g.ep.summand, g.ep.summand_dtype, sb + j)));
-            }
-            if (g.ep.relu) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-            }
-            if (g.ep.mid_dtype == ITEXB_DT_BFLOAT16) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
-            } else if (g.ep.mid_dtype == ITEXB_DT_HALF) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __half2float(__float2half_rn(v[j]));
-            }
-            StoreRow32(g, v, row, col0, ncols, vec, &thread_amax, out_scale);
-          }
+        for (int c = half; c < nchunks; c += 2) {
+          uint32_t r[32];
+          TmemLd32(taddr + uint32_t(c * 32), r);
+          TmemLdWait(r);
+          const int col0 = tn * BN + c * 32;
+          EpilogueChunk<F8>(g, ectx, &tma_out, r, lane, row0, row, row_ok, col0, min(32, g.n - col0), seq, &thread_amax);
         }
       }
       TcFenceBefore();
@@ -502,6 +638,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (g.tma_store && lane == 0) TmaStoreWaitAll();  // staging memory stays valid until the last store has read it
     if (g.ep.amax != nullptr) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) thread_amax = fmaxf(thread_amax, __shfl_xor_sync(0xffffffffu, thread_amax, o));
@@ -540,7 +677,7 @@ EncodeTiledFn GetEncodeTiled() {
 }
 
 template <int BN, bool F8>
-int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t st) {
+int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -558,7 +695,7 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cuda
   ITEXB_CUDA(attr_err);
   const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN);
   const int grid = std::max(1, std::min(tiles, SmCount()));
-  GemmKernel<BN, F8><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, g);
+  GemmKernel<BN, F8><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
   return CheckLaunch("GemmKernel");
 }
 
@@ -576,6 +713,23 @@ int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld k=%lld ld=%lld)",
                 int(r), (long long)rows, (long long)k, (long long)ld);
+  return ITEXB_OK;
+}
+
+// Tensor map for the epilogue's TMA stores: the output as a byte matrix {n*esz, m} with
+// row pitch ldo*esz, box = one warp block of 32 rows x 32 elements, swizzle matching the
+// staging tile's row width (128, 64 or 32 bytes).
+static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz) {
+  EncodeTiledFn enc = GetEncodeTiled();
+  ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  const cuuint64_t dims[2] = {cuuint64_t(n) * esz, cuuint64_t(m)};
+  const cuuint64_t strides[1] = {cuuint64_t(ldo) * esz};
+  const cuuint32_t box[2] = {cuuint32_t(32 * esz), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = esz == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : (esz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled (output) failed with CUresult %d", int(r));
   return ITEXB_OK;
 }
 
@@ -599,14 +753,22 @@ uint32_t MakeInstrDesc(int a_dtype, int b_dtype, int bn) {
 int PickBN(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
 int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st) {
+  // Output addressing: TMA stores from a staged tile when the rows are 16-byte aligned,
+  // otherwise per-thread stores straight from registers.
+  g.out_esz = g.ep.raw_acc ? 4 : DtypeSize(g.out_dtype);
+  g.vec_store = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (g.ldo * g.out_esz) % 16 == 0) ? 1 : 0;
+  g.tma_store = g.vec_store;
+  CUtensorMap to;
+  if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz));
+  else to = ta;  // unused by the kernel
   if (f8) {
-    if (bn == 256) return Launch<256, true>(ta, tb, g, st);
-    if (bn == 128) return Launch<128, true>(ta, tb, g, st);
-    return Launch<64, true>(ta, tb, g, st);
+    if (bn == 256) return Launch<256, true>(ta, tb, to, g, st);
+    if (bn == 128) return Launch<128, true>(ta, tb, to, g, st);
+    return Launch<64, true>(ta, tb, to, g, st);
   }
-  if (bn == 256) return Launch<256, false>(ta, tb, g, st);
-  if (bn == 128) return Launch<128, false>(ta, tb, g, st);
-  return Launch<64, false>(ta, tb, g, st);
+  if (bn == 256) return Launch<256, false>(ta, tb, to, g, st);
+  if (bn == 128) return Launch<128, false>(ta, tb, to, g, st);
+  return Launch<64, false>(ta, tb, to, g, st);
 }
 
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n) {
@@ -668,7 +830,5 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   g.ep = p->ep;
   g.status_word = p->status_word;
   g.idesc = MakeInstrDesc(p->a_dtype, p->b_dtype, bn);
-  const int osz = (p->ep.raw_acc ? 4 : DtypeSize(p->out_dtype));
-  g.vec_store = ((reinterpret_cast<uintptr_t>(p->out) & 15) == 0 && (p->ldo * osz) % 16 == 0) ? 1 : 0;
   return LaunchGemm(ta, tb, g, bn, f8, AsCuda(stream));
 }

@@ -18,7 +18,9 @@ struct GemmArgs {
   itexb_epilogue_t ep;
   int* status_word;     // set non-zero when a bounded wait expired
   unsigned idesc;       // tcgen05 instruction descriptor
-  int vec_store;        // output rows are 16-byte aligned
+  int vec_store;        // output rows are 16-byte aligned (set by LaunchGemm)
+  int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)
+  int out_esz;          // bytes per output element (set by LaunchGemm)
   // Implicit-GEMM convolution (conv_taps > 0): row m of A is output pixel m of an NHWC
   // tensor, k-block kb reads filter tap kb / kb_per_tap, channel block kb % kb_per_tap.
   int conv_taps, kb_per_tap, kw, oh, ow;

@@ -33,13 +33,20 @@ template <> __device__ __forceinline__ float FromFloat<float>(float v) { return 
 template <> __device__ __forceinline__ __nv_bfloat16 FromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half FromFloat<__half>(float v) { return __float2half_rn(v); }
 
-// Saturate to [lo, hi] then round to nearest even.  NaN converts to 0.
+// Saturate to [lo, hi] then round to nearest even; NaN converts to 0.  The rounding is done
+// on the fp32 adder (x + 1.5*2^23 rounds to nearest even at integer granularity) because
+// the conversion instructions run on the slow multi-function unit.  Only the low byte of
+// the result is meaningful.
 template <bool SIGNED> __device__ __forceinline__ int SatRne8(float f) {
   constexpr float lo = SIGNED ? -128.f : 0.f;
   constexpr float hi = SIGNED ? 127.f : 255.f;
   f = f < lo ? lo : (f > hi ? hi : f);
-  return __float2int_rn(f);
+  f = (f != f) ? 0.f : f;
+  return __float_as_int(__fadd_rn(f, 12582912.f)) & 0xff;
 }
+
+// float(v) for -2^22 <= v <= 2^22, exact, without a conversion instruction.
+__device__ __forceinline__ float SmallIntToFloat(int v) { return __fsub_rn(__int_as_float(v + 0x4B400000), 12582912.f); }
 
 // ---- 16-element vector load / store -----------------------------------------------
 template <typename T> struct Vec16 { float v[kVec]; };
@@ -132,7 +139,7 @@ template <bool SIGNED> __device__ __forceinline__ void LoadBytes16(const void* p
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
       const uint32_t byte = (w[j] >> (8 * b)) & 0xff;
-      out[4 * j + b] = SIGNED ? float(int(int8_t(byte))) : float(byte);
+      out[4 * j + b] = SmallIntToFloat(SIGNED ? int(int8_t(byte)) : int(byte));
     }
 }
 
@@ -239,7 +246,7 @@ __global__ void __launch_bounds__(kThreads) DequantizeKernel(const uint8_t* __re
     for (long long i = i0; i < n; ++i) {
       float s, zp;
       SliceConsts(a, i, &s, &zp);
-      const float f = SIGNED ? float(int(int8_t(q[i]))) : float(q[i]);
+      const float f = SmallIntToFloat(SIGNED ? int(int8_t(q[i])) : int(q[i]));
       y[i] = FromFloat<TY>(__fmul_rn(__fsub_rn(f, zp), s));
     }
   }
