@@ -245,6 +245,26 @@ ITEXB_API int itexb_pack_filter_hwio(const void* f_hwio, void* f_packed, int32_t
 ITEXB_API size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p);
 ITEXB_API int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream);
 
+/* itexb_conv2d for callers that cannot allocate: same arguments, results and checks, but
+ * p->workspace is ignored and the patch matrix goes into an array built into the library's
+ * device image.  It exists for hosts that may not call cudaMalloc when the convolution is
+ * due - a plugin inside another framework's memory arena, code between the begin and end of
+ * a stream capture, an allocation-free serving loop.  It has no counterpart in the
+ * reference (whose kernels take scratch from the framework's allocator).
+ *   - Limit: convolutions whose itexb_conv2d_workspace_bytes() exceeds
+ *     ITEXB_STATIC_SCRATCH_BYTES (16 MiB, held by every GPU that loads the library until the
+ *     process exits) are refused with ITEXB_RESOURCE_EXHAUSTED.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any
+ *     stream capture begins.
+ *   - All calls share the one array, which keeps the previous call's contents (each call
+ *     overwrites every byte it uses, padding zeros included).  Two calls whose kernels can
+ *     overlap on the GPU - different streams, or different host threads - race on it:
+ *     serialise them.                                                                       */
+#define ITEXB_STATIC_SCRATCH_BYTES (16u << 20)
+ITEXB_API int itexb_conv2d_static_scratch(const itexb_conv_params_t* p, itexb_stream_t stream);
+
 /* FP8 pointwise ops.  Replace the SYCL PointWiseKernel launched by
  * functor::Fp8Quantize / Fp8Dequantize (itex/core/kernels/gpu/fp8/fp8_quantize_gpu.h:36-72,
  * vectorized_pointwise.h:27-88).  scale / scale_inv / amax point at the meta element

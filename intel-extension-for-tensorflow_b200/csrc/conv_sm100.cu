@@ -8,6 +8,7 @@
 //     on it.  Scratch traffic is kh*kw times the input; the caller sizes it with
 //     itexb_conv2d_workspace_bytes().
 #include <algorithm>
+#include <mutex>
 
 #include "common.h"
 #include "gemm_sm100.h"
@@ -140,4 +141,67 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   g.status_word = p->status_word;
   g.idesc = MakeInstrDesc(p->x_dtype, ITEXB_DT_QINT8, bn);
   return LaunchGemm(ta, tb, g, bn, false, st);
+}
+
+// ---------------------------------------------------------------------------------------
+// Convolution for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at the moment they need a convolution:
+// a plugin running inside another framework's memory arena (every byte on the device is
+// already owned by that framework's allocator and a second allocator would fragment or
+// exhaust it), code running between the begin and end of a stream capture (allocation is
+// illegal there), or a latency-critical serving loop that has to be allocation-free by
+// policy.  For them the patch matrix of the general lowering lives in a fixed array inside
+// the library's own device image instead of in caller-provided scratch.
+//
+// The array costs ITEXB_STATIC_SCRATCH_BYTES on every GPU that loads the library, for the
+// life of the process, so it is kept modest; convolutions that need more are refused with
+// a clear status and must use itexb_conv2d with caller scratch.
+//
+// In host code `g_conv_scratch` is only a stand-in symbol, not a device address: handing it
+// to a kernel would fault (or, where the GPU can reach host memory, silently use the wrong
+// memory).  The real address is asked from the runtime once per device, with that device
+// current, by cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------------------
+namespace itexb {
+namespace {
+
+static __device__ __align__(256) unsigned char g_conv_scratch[ITEXB_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mu;
+void* g_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device (looked up on first use).
+int StaticScratchAddress(void** ptr) {
+  int dev = 0;
+  ITEXB_CUDA(cudaGetDevice(&dev));
+  ITEXB_REQUIRE(dev >= 0 && dev < kMaxDevices, ITEXB_INVALID_ARGUMENT, "conv2d_static_scratch: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    ITEXB_CUDA(cudaGetSymbolAddress(&p, g_conv_scratch));
+    ITEXB_REQUIRE(p != nullptr, ITEXB_INTERNAL, "conv2d_static_scratch: cudaGetSymbolAddress returned a null address");
+    g_scratch_ptr[dev] = p;
+  }
+  *ptr = g_scratch_ptr[dev];
+  return ITEXB_OK;
+}
+
+}  // namespace
+}  // namespace itexb
+
+extern "C" int itexb_conv2d_static_scratch(const itexb_conv_params_t* p, itexb_stream_t stream) {
+  ITEXB_REQUIRE(p != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d_static_scratch: params is NULL");
+  const size_t need = itexb_conv2d_workspace_bytes(p);
+  ITEXB_REQUIRE(need <= size_t(ITEXB_STATIC_SCRATCH_BYTES), ITEXB_RESOURCE_EXHAUSTED,
+                "conv2d_static_scratch: this convolution needs %zu bytes of scratch, the built-in array holds %zu; "
+                "use itexb_conv2d with caller-provided scratch",
+                need, size_t(ITEXB_STATIC_SCRATCH_BYTES));
+  itexb_conv_params_t q = *p;
+  q.workspace = nullptr;
+  if (need > 0) ITEXB_RETURN_IF_ERROR(StaticScratchAddress(&q.workspace));
+  // The gather kernel writes every byte of the region it uses (zeros where the window hangs
+  // over the border), so nothing left by an earlier call can leak into this one.
+  return itexb_conv2d(&q, stream);
 }

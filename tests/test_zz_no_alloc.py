@@ -1,0 +1,77 @@
+"""The allocation-free convolution entry point gives the bytes the ordinary one gives.
+
+itexb_conv2d_static_scratch serves hosts that cannot call cudaMalloc when the convolution is
+due (a plugin inside another framework's memory arena, code inside a stream capture, an
+allocation-free serving loop): its scratch is an array inside the library's device image.
+The test calls it through the C-ABI twice in a row - the second call finds the first call's
+leftovers in the shared array - and compares with itexb_conv2d run on caller scratch; it
+also checks the size limit is enforced with a clear status.  The file name sorts last so
+that a run stopping at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, host, modules
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(L, x, fpk, out, scale, bias, n, h, w, c, kh, kw, co, stride, pad, oh, ow, workspace=None):
+    p = L.ConvParams()
+    p.n, p.h, p.w, p.c, p.kh, p.kw, p.co = n, h, w, c, kh, kw, co
+    p.stride_h = p.stride_w = stride
+    p.dil_h = p.dil_w = 1
+    p.pad_top = p.pad_left = pad
+    p.oh, p.ow, p.c_pad = oh, ow, (c + 15) // 16 * 16
+    p.x_dtype, p.out_dtype = L.DT_QUINT8, L.DT_QUINT8
+    p.x, p.filter_packed, p.out = x.data_ptr(), fpk.data_ptr(), out.data_ptr()
+    p.ep.scale, p.ep.scale_count, p.ep.bias, p.ep.relu = scale.data_ptr(), co, bias.data_ptr(), 1
+    p.workspace = 0 if workspace is None else workspace.data_ptr()
+    return p
+
+
+def _run_case(itex, seed, n, h, w, c, kh, co, stride):
+    lib, L = itex.load(), itex._lib
+    lib.itexb_conv2d_workspace_bytes.restype = C.c_size_t
+    rng = np.random.default_rng(seed)
+    pad = kh // 2
+    oh, ow = (h + stride - 1) // stride, (w + stride - 1) // stride
+    x = dev(rng.integers(0, 256, (n, h, w, c), dtype=np.uint8))
+    f = dev(rng.integers(-127, 128, (kh, kh, c, co)).astype(np.int8))
+    scale = dev(rng.uniform(2e-4, 6e-4, co).astype(np.float32))
+    bias = dev(rng.standard_normal(co).astype(np.float32))
+    c_pad = (c + 15) // 16 * 16
+    fpk = torch.empty((co, kh * kh * c_pad), dtype=torch.int8, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    L.check(lib.itexb_pack_filter_hwio(C.c_void_p(f.data_ptr()), C.c_void_p(fpk.data_ptr()), kh, kh, c, co, c_pad, stream))
+    ref = torch.empty((n, oh, ow, co), dtype=torch.uint8, device="cuda")
+    p = _params(L, x, fpk, ref, scale, bias, n, h, w, c, kh, kh, co, stride, pad, oh, ow)
+    ws = torch.empty(max(1, lib.itexb_conv2d_workspace_bytes(C.byref(p))), dtype=torch.uint8, device="cuda")
+    p.workspace = ws.data_ptr()
+    L.check(lib.itexb_conv2d(C.byref(p), stream))
+    out = torch.full((n, oh, ow, co), 77, dtype=torch.uint8, device="cuda")
+    q = _params(L, x, fpk, out, scale, bias, n, h, w, c, kh, kh, co, stride, pad, oh, ow)  # workspace left NULL
+    L.check(lib.itexb_conv2d_static_scratch(C.byref(q), stream))
+    torch.cuda.synchronize()
+    assert int(ref.max()) > 0
+    np.testing.assert_array_equal(host(out), host(ref))  # integer output: identical bytes are the tolerance
+
+
+def test_static_scratch_conv_matches_caller_scratch_conv_twice_in_a_row():
+    itex, K, ops = modules()
+    _run_case(itex, 1, 2, 28, 28, 64, 3, 64, 1)   # 2*28*28 x 576 patch matrix = 0.9 MB
+    _run_case(itex, 2, 1, 17, 17, 32, 3, 48, 2)   # smaller: runs over the first call's leftovers
+
+
+def test_static_scratch_limit_is_enforced():
+    itex, K, ops = modules()
+    lib, L = itex.load(), itex._lib
+    x = torch.zeros(1, dtype=torch.uint8, device="cuda")
+    p = _params(L, x, x, x, x, x, 32, 56, 56, 64, 3, 3, 64, 1, 1, 56, 56)  # needs 57.8 MB of scratch
+    st = lib.itexb_conv2d_static_scratch(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == L.RESOURCE_EXHAUSTED
+    msg = lib.itexb_last_error().decode()
+    assert "57802752" in msg and "16777216" in msg and "itexb_conv2d" in msg
