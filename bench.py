@@ -93,6 +93,27 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.samples)}
 
 
+def shard_seed(base_seed, rank):
+    """Every rank owns its own batch shard (rows of the activation matrix): same distribution, its own seed."""
+    return base_seed + rank
+
+
+def max_over_ranks(ms, world, device=None):
+    """Slowest rank's time in ms (all-reduce MAX); the job is as fast as its slowest shard."""
+    if world <= 1:
+        return float(ms)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_tops(m, n, k, world, ms_step):
+    """Weak scaling: every rank does 2*m*n*k operations per step; value is the sum over ranks per unit time."""
+    return 2.0 * m * n * k * world / (ms_step * 1e-3) / 1e12
+
+
 def synth_weights(n, k, seed):
     """int8 weights [K,N] from N(0, 0.02), symmetric per-tensor (the named op honours one weight range)."""
     rng = np.random.default_rng(seed)
@@ -197,7 +218,7 @@ def main():
 
     # ---- synthetic inputs, resident in HBM (seed depends on the rank: each GPU has its own batch shard)
     gen = torch.Generator(device=dev)
-    gen.manual_seed(1234 + rank)
+    gen.manual_seed(shard_seed(1234, rank))
     x = torch.rand((m, k), device=dev, generator=gen) * 2 - 1
     qw, wmin, wmax, bias_h = synth_weights(n, k, 1235)
     w = torch.from_numpy(qw).to(dev)
@@ -249,12 +270,8 @@ def main():
     sampler.join()
     ms_total = e0.elapsed_time(e1)
     gemm_ms = sum(a.elapsed_time(b) for a, b in zip(g0, g1)) / args.steps
-    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
-    ops_per_step = 2.0 * m * n * k * world
-    value = ops_per_step / (ms_step * 1e-3) / 1e12
+    ms_step = max_over_ranks(ms_total, world, dev) / args.steps
+    value = whole_job_tops(m, n, k, world, ms_step)
 
     # ---- end to end through the public op API with host buffers (pinned), every step H2D in, D2H out
     x_host = torch.empty((m, k), dtype=torch.float32, pin_memory=True)
@@ -276,11 +293,8 @@ def main():
         e2e_step()
     t1.record()
     barrier()
-    te = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te.item()) / args.e2e_steps
-    e2e_value = ops_per_step / (e2e_ms * 1e-3) / 1e12
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world, dev) / args.e2e_steps
+    e2e_value = whole_job_tops(m, n, k, world, e2e_ms)
     checksum = float(out_host[::997, ::991].double().sum())
 
     if rank == 0:
