@@ -265,6 +265,20 @@ ITEXB_API int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream);
 #define ITEXB_STATIC_SCRATCH_BYTES (16u << 20)
 ITEXB_API int itexb_conv2d_static_scratch(const itexb_conv_params_t* p, itexb_stream_t stream);
 
+/* NHWC 8-bit pooling: max, or average over the window cells that lie inside the image
+ * (rne(float(sum)/float(count)), saturated).  Replaces the dnnl::pooling_forward behind the
+ * reference's quantized pooling kernels (itex/core/kernels/cpu/maxpooling_op.cc:43-52,
+ * cpu/avgpooling_op.cc:50-58 over kernels/common/pooling_ops_common.h).                      */
+typedef struct itexb_pool_params {
+  int32_t n, h, w, c;
+  int32_t kh, kw, stride_h, stride_w, pad_top, pad_left, oh, ow;
+  int32_t dtype;           /* QUINT8 | QINT8 */
+  int32_t is_avg;          /* 0 max, 1 average (padding excluded) */
+  const void* x;
+  void* out;
+} itexb_pool_params_t;
+ITEXB_API int itexb_pool2d(const itexb_pool_params_t* p, itexb_stream_t stream);
+
 /* FP8 pointwise ops.  Replace the SYCL PointWiseKernel launched by
  * functor::Fp8Quantize / Fp8Dequantize (itex/core/kernels/gpu/fp8/fp8_quantize_gpu.h:36-72,
  * vectorized_pointwise.h:27-88).  scale / scale_inv / amax point at the meta element

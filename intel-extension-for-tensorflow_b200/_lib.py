@@ -57,6 +57,13 @@ class ConvParams(C.Structure):
                 ("status_word", C.c_void_p), ("workspace", C.c_void_p)]
 
 
+class PoolParams(C.Structure):
+    _fields_ = [("n", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("c", C.c_int32), ("kh", C.c_int32), ("kw", C.c_int32),
+                ("stride_h", C.c_int32), ("stride_w", C.c_int32), ("pad_top", C.c_int32), ("pad_left", C.c_int32),
+                ("oh", C.c_int32), ("ow", C.c_int32), ("dtype", C.c_int32), ("is_avg", C.c_int32), ("x", C.c_void_p),
+                ("out", C.c_void_p)]
+
+
 class Tensor(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("rank", C.c_int32), ("dims", C.c_int64 * MAX_DIMS),
                 ("data", C.c_void_p), ("on_host", C.c_int32), ("reserved", C.c_int32)]

@@ -591,3 +591,35 @@ def fp8_amax_and_scale_update(amax_history, scale, fp8_max: float = 448.0, margi
     nh = np.roll(h, -1, axis=0)
     nh[0] = 0
     return nh, sf, (f32(1.0) / sf).astype(np.float32)
+
+
+# --------------------------------------------------------------------------
+# quantized pooling (row (f)-1: what an un-decomposed int8 ResNet graph also needs)
+# --------------------------------------------------------------------------
+def quantized_pool2d(x, ksize, strides, padding="SAME", avg=False):
+    """[_ITEX]QuantizedMaxPool / QuantizedAvgPool on NHWC u8|s8 (itex/core/kernels/cpu/maxpooling_op.cc:43-52,
+    cpu/avgpooling_op.cc:50-58): max, or rne(float(sum)/float(count)) over the window cells inside the
+    image (padding excluded); the min/max range passes through unchanged."""
+    x = np.asarray(x)
+    n, h, w, c = x.shape
+    kh, kw = ksize[1], ksize[2]
+    sh, sw = strides[1], strides[2]
+    if padding == "SAME":
+        oh, pt, _ = same_padding(h, kh, sh)
+        ow, pl, _ = same_padding(w, kw, sw)
+    else:
+        oh, pt, _ = valid_padding(h, kh, sh)
+        ow, pl, _ = valid_padding(w, kw, sw)
+    T = QUINT8 if x.dtype == np.uint8 else QINT8
+    out = np.empty((n, oh, ow, c), x.dtype)
+    xi = x.astype(np.int32)
+    for oy in range(oh):
+        y0, y1 = max(0, oy * sh - pt), min(h, oy * sh - pt + kh)
+        for ox in range(ow):
+            x0, x1 = max(0, ox * sw - pl), min(w, ox * sw - pl + kw)
+            win = xi[:, y0:y1, x0:x1, :].reshape(n, -1, c)
+            if avg:
+                out[:, oy, ox, :] = sat_rne((win.sum(axis=1).astype(np.float32) / f32(win.shape[1])).astype(np.float32), T)
+            else:
+                out[:, oy, ox, :] = win.max(axis=1).astype(x.dtype)
+    return out
