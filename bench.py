@@ -183,20 +183,105 @@ def run_reference(args, m, n, k):
     print(json.dumps(line), flush=True)
 
 
+def run_resnet50(args, rank, world, local, dev, K):
+    """INT8 ResNet-50 v1.5 inference, batch 128 per GPU (batch-sharded replicas, no collective): images/s.
+    A step is one forward pass of the captured graph over one batch of synthetic uint8 images."""
+    import torch
+    rn = importlib.import_module("itex_b200.resnet50")
+    batch = args.batch
+    net = rn.ResNet50Int8(device=dev, seed=1237)           # same weights on every rank
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(shard_seed(1236, rank))
+    x = torch.randint(0, 256, (batch, 224, 224, 3), dtype=torch.uint8, device=dev, generator=gen)
+    calib = torch.randint(0, 256, (16, 224, 224, 3), dtype=torch.uint8, device=dev, generator=torch.Generator(device=dev).manual_seed(99))
+    net.forward(calib, calibrate=True)                     # ranges frozen from one seeded batch, identical on all ranks
+    graph, logits = net.capture(x)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_warm, n_warm = time.perf_counter(), 0
+    while n_warm < args.warmup or time.perf_counter() - t_warm < args.min_warmup_seconds:
+        graph.replay()
+        n_warm += 1
+        if n_warm % 20 == 0:
+            torch.cuda.synchronize()
+    barrier()
+    launches0 = K.launch_count()
+    net.forward(x)                                         # eager pass: counts this library's launches per step
+    torch.cuda.synchronize()
+    launches_per_step = K.launch_count() - launches0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    sampler.stop_flag.set()
+    sampler.join()
+    ms_step = max_over_ranks(e0.elapsed_time(e1), world, dev) / args.steps
+    value = batch * world / (ms_step * 1e-3)
+    # end to end: pinned host images in, logits out, every step
+    x_host = torch.empty((batch, 224, 224, 3), dtype=torch.uint8, pin_memory=True)
+    x_host.copy_(x.cpu())
+    out_host = torch.empty(tuple(logits.shape), dtype=torch.float32, pin_memory=True)
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        graph.replay()
+        out_host.copy_(logits, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world, dev) / args.e2e_steps
+    if rank == 0:
+        peaks = measured_peaks()
+        macs = net.macs_per_image(224)
+        tops = 2.0 * macs * batch / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": "resnet50_int8_images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8xs8->s32", "data": "synthetic",
+            "config": {"workload": "resnet50_int8", "batch_per_gpu": batch, "image": 224, "graph": "53 fused quantized convs + maxpool + avgpool + fc, CUDA graph",
+                       "gmacs_per_image": macs / 1e9, "l2": "activations larger than L2 (batch %d)" % batch,
+                       "parallelism": "batch-sharded x%d, no collective" % world},
+            "roofline": {"bound": "tensor", "kernel": "whole graph (GemmKernel int8 dominates)", "achieved": tops, "peak": 2.0 * peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": tops / (2.0 * peaks["bf16_tflops"]), "traffic": None,
+                         "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s)" % peaks["source"]},
+            "e2e": {"value": batch * world / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": batch * 224 * 224 * 3 * world, "d2h_bytes_per_step": int(logits.numel()) * 4 * world,
+                    "checksum": float(out_host.double().sum())},
+            "gpu_launches": int(launches_per_step * args.steps), "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS) + ["resnet50_int8"])
+    ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
                     help="keep warming up at least this long so the clock sampler sees the load (0 for profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    m, n, k = WORKLOADS[args.workload]
+    m, n, k = WORKLOADS.get(args.workload, WORKLOADS["int8_gemm_8192"])
     if args.impl == "reference":
         run_reference(args, m, n, k)
         return
@@ -210,11 +295,17 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = os.environ.get("ITEXB_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     itex = load_package()
     ops = importlib.import_module("itex_b200.ops")
     K = importlib.import_module("itex_b200.kernels")
     dev = torch.device("cuda", local)
+    if args.workload == "resnet50_int8":
+        run_resnet50(args, rank, world, local, dev, K)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- synthetic inputs, resident in HBM (seed depends on the rank: each GPU has its own batch shard)
     gen = torch.Generator(device=dev)

@@ -222,8 +222,8 @@ ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
 
 /* NHWC x (packed) HWIO convolution as an implicit GEMM with the same epilogue.
  * Replaces dnnl::convolution_forward (itex/core/kernels/common/conv_ops.h:953-957,801).
- * x: [n,h,w,c] QUINT8|QINT8; filter packed by itexb_pack_filter_hwio to
- * [co][kh*kw*c_pad]; out: [n,oh,ow,co].  Padding is zero fill; pad_top/pad_left as
+ * x: [n,h,w,c] QUINT8|QINT8; filter packed by itexb_pack_filter_hwio to [co][k_pad],
+ * k_pad = kh*kw*c rounded up to 16; out: [n,oh,ow,co].  Padding is zero fill; pad_top/pad_left as
  * computed by GetWindowedOutputSizeVerboseV2 (itex/core/utils/common_shape_fns.cc:42-81). */
 typedef struct itexb_conv_params {
   int32_t n, h, w, c;
@@ -231,7 +231,7 @@ typedef struct itexb_conv_params {
   int32_t stride_h, stride_w, dil_h, dil_w;
   int32_t pad_top, pad_left;
   int32_t oh, ow;
-  int32_t c_pad;           /* channels per tap in the packed filter (multiple of 16) */
+  int32_t c_pad;           /* channels per tap in the packed filter: must equal c (dense rows) */
   int32_t x_dtype, out_dtype;
   const void* x;
   const void* filter_packed;

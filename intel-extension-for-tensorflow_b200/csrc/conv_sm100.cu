@@ -3,9 +3,9 @@
 // Two lowerings share the MMA main loop and the fused epilogue:
 //   * pointwise (1x1, stride 1, no padding, channels a multiple of 16): the input IS the
 //     [n*h*w, c] A operand; nothing is staged.
-//   * general: a gather kernel writes the [n*oh*ow, kh*kw*c_pad] patch matrix (zero fill
-//     for padding) into caller-provided scratch, 16 bytes per thread, then the GEMM runs
-//     on it.  Scratch traffic is kh*kw times the input; the caller sizes it with
+//   * general: a gather kernel writes the [n*oh*ow, round_up(kh*kw*c, 16)] patch matrix (zero
+//     fill for padding) into caller-provided scratch - 16 bytes per thread when c is a multiple
+//     of 16, one contiguous filter-row run per thread otherwise - then the GEMM runs on it.  Scratch traffic is kh*kw times the input; the caller sizes it with
 //     itexb_conv2d_workspace_bytes().
 #include <algorithm>
 #include <mutex>
@@ -46,23 +46,81 @@ __global__ void __launch_bounds__(256) GatherPatchesVecKernel(GatherArgs a) {
   }
 }
 
-// One thread per byte: any channel count (e.g. 3), channels >= c are zero.
-__global__ void __launch_bounds__(256) GatherPatchesScalarKernel(GatherArgs a) {
+// Any channel count (e.g. 3 for an RGB stem) with the dense layout c_pad == c: one thread per
+// (pixel, filter row).  With dilation 1 the kw*c bytes of one filter row are contiguous in the NHWC
+// input, so the thread copies one run (clipped at the left/right border, zeros elsewhere); the last
+// filter row's thread also zeroes the row tail up to the 16-byte multiple.
+__global__ void __launch_bounds__(256) GatherPatchesRowKernel(GatherArgs a) {
   const long long kp = (long long)a.chunks * 16;
-  const long long total = a.m * kp;
+  const int run = a.kw * a.c;
+  const long long total = a.m * a.kh;
   for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
-    const long long pix = i / kp;
-    const int kk = int(i - pix * kp);
-    const int tap = kk / a.c_pad, ci = kk - tap * a.c_pad;
-    const int ky = tap / a.kw, kx = tap - ky * a.kw;
+    const long long pix = i / a.kh;
+    const int ky = int(i - pix * a.kh);
     const int ox = int(pix % a.ow);
     const int oy = int((pix / a.ow) % a.oh);
     const int b = int(pix / ((long long)a.ow * a.oh));
     const int iy = oy * a.stride_h + ky * a.dil_h - a.pad_top;
-    const int ix = ox * a.stride_w + kx * a.dil_w - a.pad_left;
+    uint8_t* dst = a.ws + pix * kp + (long long)ky * run;
+    const bool row_in = iy >= 0 && iy < a.h;
+    const uint8_t* src_row = a.x + ((long long)b * a.h + (row_in ? iy : 0)) * a.w * a.c;
+    for (int kx = 0; kx < a.kw; ++kx) {
+      const int ix = ox * a.stride_w + kx * a.dil_w - a.pad_left;
+      const bool in = row_in && ix >= 0 && ix < a.w;
+      for (int ci = 0; ci < a.c; ++ci) dst[kx * a.c + ci] = in ? __ldg(src_row + (long long)ix * a.c + ci) : uint8_t(0);
+    }
+    if (ky == a.kh - 1)
+      for (long long t = (long long)a.kh * run; t < kp; ++t) a.ws[pix * kp + t] = 0;
+  }
+}
+
+// Few-channel stem convolutions (e.g. 7x7x3, stride 2): the filter shape is a template parameter,
+// so every byte position of the 16-byte-aligned patch row is a compile-time offset into a
+// shared-memory copy of the input window.  A block builds TP consecutive output pixels of one
+// output row: it loads the KH input rows they touch once (coalesced), then each thread assembles
+// its patch row in registers and writes it as 16-byte vectors.  Dilation 1.
+template <int KH, int KW, int C, int TP>
+__global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a) {
+  constexpr int kRun = KW * C;                         // bytes of one filter row
+  constexpr int kRowPitch = (KH * kRun + 15) / 16 * 16;  // patch-matrix pitch
+  extern __shared__ uint8_t s_in[];                    // [KH][span * C]
+  const int tiles_x = (a.ow + TP - 1) / TP;
+  const int tile = blockIdx.x % tiles_x;
+  const int oy = (blockIdx.x / tiles_x) % a.oh;
+  const int b = blockIdx.x / (tiles_x * a.oh);
+  const int ox0 = tile * TP;
+  const int span = (TP - 1) * a.stride_w + KW;         // input columns the tile touches
+  const int ix0 = ox0 * a.stride_w - a.pad_left;
+  const int row_bytes = span * C;
+  for (int i = threadIdx.x; i < KH * row_bytes; i += TP) {
+    const int ky = i / row_bytes, r = i - ky * row_bytes;
+    const int ix = ix0 + r / C, ci = r % C;
+    const int iy = oy * a.stride_h + ky - a.pad_top;
     uint8_t v = 0;
-    if (ci < a.c && iy >= 0 && iy < a.h && ix >= 0 && ix < a.w) v = a.x[(((long long)b * a.h + iy) * a.w + ix) * a.c + ci];
-    a.ws[i] = v;
+    if (iy >= 0 && iy < a.h && ix >= 0 && ix < a.w) v = __ldg(a.x + (((long long)b * a.h + iy) * a.w + ix) * C + ci);
+    s_in[i] = v;
+  }
+  __syncthreads();
+  const int ox = ox0 + threadIdx.x;
+  if (ox >= a.ow) return;
+  const uint8_t* base = s_in + threadIdx.x * a.stride_w * C;
+  uint4* dst = reinterpret_cast<uint4*>(a.ws + (((long long)b * a.oh + oy) * a.ow + ox) * kRowPitch);
+#pragma unroll
+  for (int u = 0; u < kRowPitch / 16; ++u) {
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        constexpr int dummy = 0;
+        const int k = u * 16 + q * 4 + t;               // compile-time after unrolling
+        if (k < KH * kRun) word |= uint32_t(base[(k / kRun) * row_bytes + (k % kRun)]) << (8 * t);
+        (void)dummy;
+      }
+      w[q] = word;
+    }
+    dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -77,8 +135,8 @@ int Validate(const itexb_conv_params_t& p) {
   ITEXB_REQUIRE(p.stride_h > 0 && p.stride_w > 0 && p.dil_h > 0 && p.dil_w > 0, ITEXB_INVALID_ARGUMENT,
                 "conv2d: strides and dilations must be positive");
   ITEXB_REQUIRE(p.oh > 0 && p.ow > 0, ITEXB_INVALID_ARGUMENT, "conv2d: empty output");
-  ITEXB_REQUIRE(p.c_pad >= p.c && p.c_pad % 16 == 0, ITEXB_INVALID_ARGUMENT,
-                "conv2d: c_pad must be a multiple of 16 and >= c (got %d for c=%d)", p.c_pad, p.c);
+  ITEXB_REQUIRE(p.c_pad == p.c, ITEXB_INVALID_ARGUMENT,
+                "conv2d: c_pad must equal c (dense packed filter), got %d for c=%d", p.c_pad, p.c);
   ITEXB_REQUIRE(IsInt8(p.x_dtype), ITEXB_INVALID_ARGUMENT, "conv2d: input type %s is not qint8/quint8", DtypeName(p.x_dtype));
   return ValidateEpilogue("conv2d", p.ep, p.out_dtype, false, p.co);
 }
@@ -90,7 +148,7 @@ using namespace itexb;
 
 extern "C" size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p) {
   if (p == nullptr || IsPointwise(*p)) return 0;
-  return size_t(p->n) * p->oh * p->ow * size_t(p->kh) * p->kw * p->c_pad;
+  return size_t(p->n) * p->oh * p->ow * ((size_t(p->kh) * p->kw * p->c_pad + 15) / 16 * 16);
 }
 
 extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream) {
@@ -101,7 +159,7 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   cudaStream_t st = AsCuda(stream);
   const long long m = (long long)p->n * p->oh * p->ow;
   ITEXB_REQUIRE(m < (1ll << 31), ITEXB_INVALID_ARGUMENT, "conv2d: more than 2^31 output pixels");
-  const int kp = p->kh * p->kw * p->c_pad;
+  const int kp = (p->kh * p->kw * p->c_pad + 15) / 16 * 16;  // patch-matrix / packed-filter row pitch
   const void* a_ptr = p->x;
   if (!IsPointwise(*p)) {
     ITEXB_REQUIRE(p->workspace != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d: workspace of %zu bytes is required",
@@ -117,10 +175,18 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
     a.m = m;
     a.chunks = kp / 16;
     const bool vec = p->c % 16 == 0 && p->c_pad == p->c && (reinterpret_cast<uintptr_t>(p->x) & 15) == 0;
-    const long long work = vec ? m * a.chunks : m * (long long)kp;
+    const long long work = vec ? m * a.chunks : m * (long long)p->kh;
     const int blocks = int(std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)SmCount() * 32)));
-    if (vec) GatherPatchesVecKernel<<<blocks, 256, 0, st>>>(a);
-    else GatherPatchesScalarKernel<<<blocks, 256, 0, st>>>(a);
+    if (vec) {
+      GatherPatchesVecKernel<<<blocks, 256, 0, st>>>(a);
+    } else if (p->kh == 7 && p->kw == 7 && p->c == 3 && p->dil_h == 1 && p->dil_w == 1 && p->stride_w <= 4) {
+      constexpr int kTP = 64;
+      const int tiles_x = (p->ow + kTP - 1) / kTP;
+      const size_t smem = size_t(7) * ((kTP - 1) * p->stride_w + 7) * 3;
+      GatherPatchesStemKernel<7, 7, 3, kTP><<<unsigned(p->n) * p->oh * tiles_x, kTP, smem, st>>>(a);
+    } else {
+      GatherPatchesRowKernel<<<blocks, 256, 0, st>>>(a);
+    }
     ITEXB_RETURN_IF_ERROR(CheckLaunch("GatherPatchesKernel"));
     a_ptr = p->workspace;
   } else {

@@ -142,31 +142,6 @@ __device__ __forceinline__ void UmmaSS(uint32_t d_tmem, uint64_t a_desc, uint64_
   }
 }
 
-// 32 lanes x 32 consecutive 32-bit columns: register j of lane l = D[lane_base + l][col + j].
-__device__ __forceinline__ void TmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-// Waits for this thread's outstanding tcgen05.ld.  The registers are listed as in/out
-// operands so that no use of them can be scheduled ahead of the wait.
-__device__ __forceinline__ void TmemLdWait(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
-                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
-                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
-                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
 // K-major operand tile whose rows are 128 bytes, stored with the 128-byte swizzle TMA
 // writes: 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
 __device__ __forceinline__ uint64_t UmmaDescSw128(uint32_t smem_addr) {
@@ -175,24 +150,45 @@ __device__ __forceinline__ uint64_t UmmaDescSw128(uint32_t smem_addr) {
 }
 
 
+__device__ __forceinline__ void TileCoords(int t, int tiles_m, int tiles_n, int* tm, int* tn) {
+  const int per_group = kGroupM * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM;
+  const int rows = min(kGroupM, tiles_m - first_m);
+  const int r = t - g * per_group;
+  *tm = first_m + r % rows;
+  *tn = r / rows;
+}
+
 // ---------------------------------------------------------------------------------------
-// Epilogue math and stores
+// Epilogue.  The unit of work is a slice: 32 rows (one per lane) x 16 columns.  The slice
+// code is one short loop body that every slice of every tile re-executes, so it stays in the
+// instruction cache (a fully unrolled 32-column body executed once per block was measured to
+// be fetch-bound: ~3000 cycles per block for a few hundred instructions).  The output type
+// is a template parameter, chosen once per launch; everything else is a uniform run-time flag.
 // ---------------------------------------------------------------------------------------
-// Conversions run on the multi-function unit, which is more than an order of magnitude
-// slower than the fp32/int pipes on this part and becomes the epilogue's bottleneck.  Both
-// directions are therefore done with the 1.5*2^23 trick on the fp32 adder, which rounds to
-// nearest even exactly like the conversion instructions do.
 constexpr float kMagic = 12582912.f;        // 1.5 * 2^23
 constexpr int kMagicBits = 0x4B400000;
 
-// Low byte of rne(clamp(f, lo, hi)) for -128 <= lo, hi <= 255 (NaN converts like lo).
-__device__ __forceinline__ uint32_t SatRneByte(float f, float lo, float hi) {
-  f = fminf(fmaxf(f, lo), hi);
-  return uint32_t(__float_as_int(__fadd_rn(f, kMagic))) & 0xffu;
-}
-
+// Conversions between int and float are done on the fp32 adder with the 1.5*2^23 trick, which
+// rounds to nearest even exactly like the conversion instructions do; those run on the
+// multi-function unit, the slowest pipe of this part (measured 71 % busy, everything else idle).
 // float(a), exact, valid when |a| <= 2^22.
 __device__ __forceinline__ float SmallIntToFloat(int a) { return __fsub_rn(__int_as_float(a + kMagicBits), kMagic); }
+// rne(clamp(f, lo, hi)) for -128 <= lo, hi <= 255 in the low byte of the result; the upper
+// bytes are junk (NaN converts like lo).
+__device__ __forceinline__ uint32_t SatRneLowByte(float f, float lo, float hi) {
+  f = fminf(fmaxf(f, lo), hi);
+  return uint32_t(__float_as_int(__fadd_rn(f, kMagic)));
+}
+// Low bytes of a, b, c, d -> one word (byte-permute unit: 3 instructions per 4 outputs).
+__device__ __forceinline__ uint32_t PackLowBytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+__device__ __forceinline__ bool DtypeIs8(int dt) {
+  return dt == ITEXB_DT_QUINT8 || dt == ITEXB_DT_UINT8 || dt == ITEXB_DT_QINT8 || dt == ITEXB_DT_INT8;
+}
 
 __device__ __forceinline__ float LoadSummand(const void* p, int dt, long long idx) {
   switch (dt) {
@@ -204,105 +200,89 @@ __device__ __forceinline__ float LoadSummand(const void* p, int dt, long long id
   }
 }
 
-__device__ __forceinline__ uint32_t Pack4(int a, int b, int c, int d) {
-  return uint32_t(a & 0xff) | (uint32_t(b & 0xff) << 8) | (uint32_t(c & 0xff) << 16) | (uint32_t(d & 0xff) << 24);
-}
+// Output kinds (template parameter of the epilogue).
+enum : int { kOutRaw = 0, kOutF32, kOutBF16, kOutF16, kOutS32, kOutU8, kOutS8, kOutFP8 };
+template <int OK> struct OutBytes { static constexpr int v = (OK == kOutRaw || OK == kOutF32 || OK == kOutS32) ? 4 : ((OK == kOutBF16 || OK == kOutF16) ? 2 : 1); };
 
-// Converts 32 consecutive outputs of one row to the output type and packs them into
-// 32-bit words: 32 words for 4-byte types, 16 for 2-byte, 8 for 1-byte.
-__device__ __forceinline__ void ConvertRow32(int out_dtype, const float (&v)[32], int ncols, uint32_t (&w)[32],
-                                             float* thread_amax, float out_scale) {
-  switch (out_dtype) {
-    case ITEXB_DT_FLOAT:
+// 16 consecutive outputs of one row -> packed words (16, 8 or 4 of them).
+template <int OK>
+__device__ __forceinline__ void Convert16(const float (&v)[16], uint32_t (&w)[16], bool e4m3, float out_scale) {
+  if (OK == kOutF32) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
-      break;
-    case ITEXB_DT_BFLOAT16:
+    for (int j = 0; j < 16; ++j) w[j] = __float_as_uint(v[j]);
+  } else if (OK == kOutBF16) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      break;
-    case ITEXB_DT_HALF:
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      break;
-    case ITEXB_DT_QINT32: case ITEXB_DT_INT32:
-      // oneDNN converts the fp32 tail to s32 with saturation and RNE.
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float f = v[j];
-        w[j] = uint32_t(f >= 2147483648.f ? 2147483647 : (f <= -2147483648.f ? (-2147483647 - 1) : __float2int_rn(f)));
-      }
-      break;
-    case ITEXB_DT_QUINT8: case ITEXB_DT_UINT8: case ITEXB_DT_QINT8: case ITEXB_DT_INT8: {
-      const bool sg = (out_dtype == ITEXB_DT_QINT8 || out_dtype == ITEXB_DT_INT8);
-      const float lo = sg ? -128.f : 0.f, hi = sg ? 127.f : 255.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        w[j] = SatRneByte(v[4 * j], lo, hi) | (SatRneByte(v[4 * j + 1], lo, hi) << 8) | (SatRneByte(v[4 * j + 2], lo, hi) << 16) |
-               (SatRneByte(v[4 * j + 3], lo, hi) << 24);
-      break;
+    for (int j = 0; j < 8; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
     }
-    case ITEXB_DT_FP8_E4M3: case ITEXB_DT_FP8_E5M2: {
-      const __nv_fp8_interpretation_t kind = out_dtype == ITEXB_DT_FP8_E4M3 ? __NV_E4M3 : __NV_E5M2;
-      float m = *thread_amax;
+  } else if (OK == kOutF16) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) m = fmaxf(m, fabsf(v[j]));
-      *thread_amax = m;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        int q[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) q[t] = (int)__nv_cvt_float_to_fp8(__fmul_rn(v[4 * j + t], out_scale), __NV_SATFINITE, kind);
-        w[j] = Pack4(q[0], q[1], q[2], q[3]);
-      }
-      break;
+    for (int j = 0; j < 8; ++j) {
+      __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
     }
-    default: break;
+  } else if (OK == kOutS32) {
+    // oneDNN converts the fp32 tail to s32 with saturation and RNE (rare output type: conversion unit).
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float f = v[j];
+      w[j] = uint32_t(f >= 2147483648.f ? 2147483647 : (f <= -2147483648.f ? (-2147483647 - 1) : __float2int_rn(f)));
+    }
+  } else if (OK == kOutU8 || OK == kOutS8) {
+    constexpr float lo = OK == kOutS8 ? -128.f : 0.f, hi = OK == kOutS8 ? 127.f : 255.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w[j] = PackLowBytes(SatRneLowByte(v[4 * j], lo, hi), SatRneLowByte(v[4 * j + 1], lo, hi), SatRneLowByte(v[4 * j + 2], lo, hi),
+                          SatRneLowByte(v[4 * j + 3], lo, hi));
+  } else if (OK == kOutFP8) {
+    const __nv_fp8_interpretation_t kind = e4m3 ? __NV_E4M3 : __NV_E5M2;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t q[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) q[t] = (uint32_t)__nv_cvt_float_to_fp8(__fmul_rn(v[4 * j + t], out_scale), __NV_SATFINITE, kind);
+      w[j] = PackLowBytes(q[0], q[1], q[2], q[3]);
+    }
   }
 }
 
-// Writes the packed words of one row segment straight to global memory.  `esz` is the
-// output element size, `vec` says the segment is complete and 16-byte aligned.  All
-// indices are compile-time constants so that `w` stays in registers.
-__device__ __forceinline__ void StoreRowDirect(void* out, long long elem_index, int esz, const uint32_t (&w)[32], int ncols, bool vec) {
-  uint8_t* o = static_cast<uint8_t*>(out) + elem_index * esz;
-  if (vec) {
-    const int units = 2 * esz;  // 16-byte units in 32 elements
+// 16 per-column parameters starting at column `col`: four 16-byte loads of an address all lanes
+// share (one broadcast transaction each, served by L1) when the vector is aligned and the slice
+// is complete, guarded element loads otherwise.
+__device__ __forceinline__ void LoadParams16(const float* __restrict__ p, int col, int n, bool vec, float fill, float (&out)[16]) {
+  if (p == nullptr) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (j < units) reinterpret_cast<uint4*>(o)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-  } else if (esz == 4) {
+    for (int j = 0; j < 16; ++j) out[j] = fill;
+  } else if (vec && col + 16 <= n) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols) reinterpret_cast<uint32_t*>(o)[j] = w[j];
-  } else if (esz == 2) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols) reinterpret_cast<uint16_t*>(o)[j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+    for (int i = 0; i < 4; ++i) {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(p + col) + i);
+      out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w;
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols) o[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+    for (int j = 0; j < 16; ++j) out[j] = col + j < n ? __ldg(p + col + j) : fill;
   }
 }
 
-// Writes the packed words of lane `lane`'s row into the warp's staging tile (32 rows of
-// 32*esz bytes) in the swizzled order a TMA store with SWIZZLE_{128,64,32}B expects:
-// 16-byte unit j of row r lives at unit j ^ ((r / (8/units)) % units).
-__device__ __forceinline__ void StoreRowStaged(uint8_t* stage, int lane, int esz, const uint32_t (&w)[32]) {
-  const int units = 2 * esz;                 // 8, 4 or 2 units per row
-  const int x = (lane / (8 / units)) % units;
-  uint8_t* row = stage + lane * (32 * esz);
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    if (j < units) *reinterpret_cast<uint4*>(row + ((j ^ x) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+__device__ __forceinline__ void TmemLd16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Waits for this thread's outstanding tcgen05.ld.  The registers are listed as in/out
+// operands so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void TmemLdWait16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
 }
 
 __device__ __forceinline__ void TmaStore2d(const void* tmap, uint32_t src_smem, int c0, int c1) {
@@ -320,164 +300,199 @@ __device__ __forceinline__ void TmaStoreWaitRead(int pending) {
 __device__ __forceinline__ void TmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Per-warp state of the epilogue that does not change from chunk to chunk.
+// What an epilogue warp needs to know; filled once per launch.
 struct EpilogueCtx {
-  bool has_scale, has_bias;
-  int mode;           // (0 no scale | 1 scalar scale | 2 scale vector) + 3 * has_bias
-  bool vec_params;    // scale / bias vectors are 16-byte aligned: fetch them as float4
-  float scalar_scale; // the scale when it is one value for the whole matrix
-  const float* scale; // per-column scale vector or nullptr
-  const float* bias;  // per-column bias vector or nullptr
-  int esz;            // bytes per output element
-  int nbuf;           // staging buffers per warp: 4096 / (1024 * esz)
-  uint8_t* stage;     // this warp's 4 KiB of staging
-  float out_scale;
+  const float* scale;   // per-column scale vector or nullptr
+  const float* bias;    // per-column bias vector or nullptr
+  float scalar_scale;   // used when scale == nullptr (1 when there is no scale at all)
+  bool vec_params;      // scale / bias vectors are 16-byte aligned
+  bool acc_small;       // |accumulator| <= 2^22 follows from k alone
+  bool relu;            // apply max(f, 0) (skipped when an unsigned clamp does it anyway)
+  bool sum_bytes_vec;   // summand is 1-byte with 16-byte aligned rows: one 16-byte load per slice
+  bool e4m3;            // FP8 output format
+  float out_scale;      // FP8 output scale
+  uint8_t* stage;       // this warp's 4 KiB of staging
 };
 
-// v[j] = float(acc[j]) * scale + bias for the 32 columns starting at col0, specialised at
-// compile time on where scale and bias come from so that the executed code is one short
-// straight line.  SMODE: 0 no scale, 1 one scale for the matrix, 2 per-column vector.
-// Per-column values are fetched 16 columns at a time as float4 loads of an address all
-// lanes share (one broadcast transaction each, served by L1), issued together so their
-// latencies overlap.
-template <bool F8, int SMODE, bool BIAS>
-__device__ __forceinline__ void ScaleBias32(const uint32_t (&r)[32], float (&v)[32], const float* __restrict__ scale,
-                                            const float* __restrict__ bias, float scalar_scale, int col0) {
-  // int32 -> fp32: exact adder trick when every accumulator of the row segment is within
-  // +-2^22 (the usual case), the conversion instruction otherwise.
-  if (F8) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-  } else {
-    uint32_t big = 0;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) big |= (r[j] + 0x400000u) & 0xff800000u;
-    if (big == 0) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = SmallIntToFloat(int(r[j]));
-    } else {
-      // volatile: keeps the slow conversions inside this branch (the compiler would
-      // otherwise execute them speculatively on every block and select afterwards)
-#pragma unroll
-      for (int j = 0; j < 32; ++j) asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(v[j]) : "r"(r[j]));
-    }
-  }
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    float4 s4[4], b4[4];
-    if (SMODE == 2) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s4[i] = __ldg(reinterpret_cast<const float4*>(scale + col0) + 4 * h + i);
-    }
-    if (BIAS) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) b4[i] = __ldg(reinterpret_cast<const float4*>(bias + col0) + 4 * h + i);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int j = 16 * h + 4 * i;
-      if (SMODE == 2) {
-        v[j] = __fmul_rn(v[j], s4[i].x); v[j + 1] = __fmul_rn(v[j + 1], s4[i].y);
-        v[j + 2] = __fmul_rn(v[j + 2], s4[i].z); v[j + 3] = __fmul_rn(v[j + 3], s4[i].w);
-      } else if (SMODE == 1) {
-        v[j] = __fmul_rn(v[j], scalar_scale); v[j + 1] = __fmul_rn(v[j + 1], scalar_scale);
-        v[j + 2] = __fmul_rn(v[j + 2], scalar_scale); v[j + 3] = __fmul_rn(v[j + 3], scalar_scale);
-      }
-      if (BIAS) {
-        v[j] = __fadd_rn(v[j], b4[i].x); v[j + 1] = __fadd_rn(v[j + 1], b4[i].y);
-        v[j + 2] = __fadd_rn(v[j + 2], b4[i].z); v[j + 3] = __fadd_rn(v[j + 3], b4[i].w);
-      }
-    }
-  }
-}
+// The persistent loop of one epilogue warp.  Warp (q, half) owns TMEM lanes 32q..32q+31 (the
+// quarter its warp id may read) and the 32-column blocks half, half+2, ... of every tile.
+// A block is produced as two 16-column slices into a swizzled staging tile (32 rows x 32
+// elements) that one TMA store then writes; edges are clipped by the tensor map.  Without
+// TMA-legal output rows the slices go straight to global memory.
+template <int BN, bool F8, int OK>
+__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, uint8_t* s_stage, uint64_t* tmem_full_bar,
+                                             uint64_t* tmem_empty_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane,
+                                             int tiles_m, int tiles_n, int num_tiles) {
+  constexpr int esz = OutBytes<OK>::v;
+  constexpr int units = esz;                 // 16-byte units per 16-column slice
+  constexpr int row_units = 2 * esz;         // ... per 32-column staging row
+  constexpr int nbuf = 4 / esz;              // staging buffers per warp: 1 (4-byte), 2 (2-byte), 4 (1-byte)
+  const int q = warp & 3;
+  const int half = (warp - 4) >> 2;
+  EpilogueCtx e;
+  const bool has_alpha = g.ep.alpha_a != nullptr && g.ep.alpha_b != nullptr;
+  e.scalar_scale = 1.f;
+  e.scale = nullptr;
+  if (has_alpha) e.scalar_scale = __fmul_rn(__ldg(g.ep.alpha_a), __ldg(g.ep.alpha_b));
+  else if (g.ep.scale_count == 1) e.scalar_scale = __ldg(g.ep.scale);
+  else if (g.ep.scale_count > 1) e.scale = g.ep.scale;
+  e.bias = g.ep.bias;
+  e.vec_params = ((reinterpret_cast<uintptr_t>(e.scale) | reinterpret_cast<uintptr_t>(e.bias)) & 15) == 0;
+  e.acc_small = !F8 && (long long)g.k * 255 * 128 < (1ll << 22);
+  e.relu = g.ep.relu && !(g.ep.mid_dtype == 0 && OK == kOutU8);  // max(f, 0) is implied by the clamp to [0, 255]
+  e.sum_bytes_vec = g.ep.summand != nullptr && DtypeIs8(g.ep.summand_dtype) && g.ep.ld_summand % 16 == 0 &&
+                    (reinterpret_cast<uintptr_t>(g.ep.summand) & 15) == 0;
+  e.e4m3 = g.out_dtype == ITEXB_DT_FP8_E4M3;
+  e.out_scale = g.ep.out_scale != nullptr ? __ldg(g.ep.out_scale) : 1.f;
+  e.stage = s_stage + (warp - 4) * 4096;
+  const bool sum_signed = g.ep.summand_dtype == ITEXB_DT_QINT8 || g.ep.summand_dtype == ITEXB_DT_INT8;
+  const int swz = (lane / (8 / row_units)) % row_units;  // this lane's XOR term of the staging swizzle
+  int acc = 0;
+  uint32_t acc_phase = 0, seq = 0;
+  float thread_amax = 0.f;
 
-// The same arithmetic for a block that is cut by the matrix edge or whose parameter
-// vectors are not 16-byte aligned: element-wise guarded loads.
-template <bool F8>
-__device__ __forceinline__ void ScaleBias32Edge(const uint32_t (&r)[32], float (&v)[32], const float* scale, const float* bias,
-                                                bool has_scale, float scalar_scale, int col0, int n) {
+  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    int tm, tn;
+    TileCoords(t, tiles_m, tiles_n, &tm, &tn);
+    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
+    if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
+    TcFenceAfter();
+    const int row0 = tm * kBM + q * 32;  // first row of this warp's 32-row block
+    const long long row = (long long)row0 + lane;
+    const bool row_ok = row < g.m;
+    const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
+    const int nblocks = min(BN / 32, (g.n - tn * BN + 31) / 32);  // 32-column blocks holding real columns
+    if (row0 < g.m) {
+#pragma unroll 1
+      for (int c = half; c < nblocks; c += 2) {
+        const int col0 = tn * BN + c * 32;
+        uint8_t* buf = e.stage + (seq & uint32_t(nbuf - 1)) * (1024 * esz);
+        if (g.tma_store) {
+          // the store that last used this staging buffer must have finished reading it
+          if (lane == 0) TmaStoreWaitRead(nbuf - 1);
+          __syncwarp();
+        }
+#pragma unroll 1
+        for (int sl = 0; sl < 2; ++sl) {
+          const int col = col0 + 16 * sl;
+          if (col >= g.n) break;
+          uint32_t r[16];
+          TmemLd16(taddr + uint32_t(c * 32 + 16 * sl), r);
+          uint32_t w[16];
+          if (OK == kOutRaw) {
+            TmemLdWait16(r);
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float f;
-    if (F8) f = __uint_as_float(r[j]);
-    else asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(f) : "r"(r[j]));
-    const int c = col0 + j;
-    if (has_scale) f = __fmul_rn(f, (scale != nullptr && c < n) ? __ldg(scale + c) : scalar_scale);
-    if (bias != nullptr && c < n) f = __fadd_rn(f, __ldg(bias + c));
-    v[j] = f;
-  }
-}
-
-// One 32-row x 32-column block of a tile: accumulators `r` (one row per lane) -> scale, bias,
-// sum, ReLU, conversion -> staged TMA store (or direct stores).  `seq` counts the blocks
-// this warp has stored, which selects the staging buffer.
-template <bool F8>
-__device__ __forceinline__ void EpilogueChunk(const GemmArgs& g, const EpilogueCtx& e, const CUtensorMap* tma_out,
-                                              const uint32_t (&r)[32], int lane, int row0, long long row, bool row_ok, int col0,
-                                              int ncols, uint32_t& seq, float* thread_amax) {
-  uint32_t w[32];
-  if (g.ep.raw_acc) {
+            for (int j = 0; j < 16; ++j) w[j] = r[j];
+          } else {
+            float sc[16], bi[16];
+            LoadParams16(e.scale, col, g.n, e.vec_params, e.scalar_scale, sc);  // in flight together with the TMEM load
+            LoadParams16(e.bias, col, g.n, e.vec_params, 0.f, bi);
+            TmemLdWait16(r);
+            float v[16];
+            if (F8) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) w[j] = r[j];
-  } else {
-    float v[32];
-    if (e.vec_params && ncols == 32) {
-      switch (e.mode) {
-        case 0: ScaleBias32<F8, 0, false>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
-        case 1: ScaleBias32<F8, 1, false>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
-        case 2: ScaleBias32<F8, 2, false>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
-        case 3: ScaleBias32<F8, 0, true>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
-        case 4: ScaleBias32<F8, 1, true>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
-        default: ScaleBias32<F8, 2, true>(r, v, e.scale, e.bias, e.scalar_scale, col0); break;
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            } else {
+              // int32 -> fp32: exact adder trick when every accumulator is within +-2^22 (always
+              // true when k is small enough, otherwise checked), the conversion instruction otherwise
+              uint32_t big = 0;
+              if (!e.acc_small) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) big |= (r[j] + 0x400000u) & 0xff800000u;
+              }
+              if (big == 0) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = SmallIntToFloat(int(r[j]));
+              } else {
+                // volatile keeps the slow conversions inside this branch
+#pragma unroll
+                for (int j = 0; j < 16; ++j) asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(v[j]) : "r"(r[j]));
+              }
+            }
+            // separate multiply and add: the order and rounding of oneDNN's scale-then-bias tail.
+            // A missing scale multiplies by 1 and a missing bias adds 0, both exact.
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(__fmul_rn(v[j], sc[j]), bi[j]);
+            if (g.ep.summand != nullptr && row_ok) {
+              const long long sb = row * g.ep.ld_summand + col;
+              if (e.sum_bytes_vec && col + 16 <= g.n) {
+                const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.ep.summand) + sb));
+                const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const uint32_t byte = (sw[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                  v[j] = __fadd_rn(v[j], __fmul_rn(g.ep.sum_scale, SmallIntToFloat(sum_signed ? int(int8_t(byte)) : int(byte))));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (col + j < g.n) v[j] = __fadd_rn(v[j], __fmul_rn(g.ep.sum_scale, LoadSummand(g.ep.summand, g.ep.summand_dtype, sb + j)));
+              }
+            }
+            if (e.relu) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            if (g.ep.mid_dtype == ITEXB_DT_BFLOAT16) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+            } else if (g.ep.mid_dtype == ITEXB_DT_HALF) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __half2float(__float2half_rn(v[j]));
+            }
+            if (OK == kOutFP8 && row_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (col + j < g.n) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
+            }
+            Convert16<OK>(v, w, e.e4m3, e.out_scale);
+          }
+          if (g.tma_store) {
+            // 16-byte unit j of staging row r lives at unit j ^ ((r / (8/row_units)) % row_units): the
+            // layout a TMA store with a 128/64/32-byte swizzle reads (row width 32 * esz bytes)
+            uint8_t* srow = buf + lane * (32 * esz);
+#pragma unroll
+            for (int u = 0; u < units; ++u)
+              *reinterpret_cast<uint4*>(srow + (((sl * units + u) ^ swz) << 4)) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+          } else if (row_ok) {
+            uint8_t* o = static_cast<uint8_t*>(g.out) + (row * g.ldo + col) * esz;
+            if (g.vec_store && col + 16 <= g.n) {
+#pragma unroll
+              for (int u = 0; u < units; ++u) reinterpret_cast<uint4*>(o)[u] = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (col + j < g.n) {
+                  if (esz == 4) reinterpret_cast<uint32_t*>(o)[j] = w[j];
+                  else if (esz == 2) reinterpret_cast<uint16_t*>(o)[j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+                  else o[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+                }
+              }
+            }
+          }
+        }
+        if (g.tma_store) {
+          FenceProxyAsyncShared();
+          __syncwarp();
+          if (lane == 0) {
+            TmaStore2d(tma_out, SmemAddr(buf), col0 * esz, row0);  // rows >= m and columns >= n are clipped
+            TmaStoreCommit();
+          }
+          ++seq;
+        }
       }
-    } else {
-      ScaleBias32Edge<F8>(r, v, e.scale, e.bias, e.has_scale, e.scalar_scale, col0, g.n);
     }
-    if (g.ep.summand != nullptr && row_ok) {
-      const long long sb = row * g.ep.ld_summand + col0;
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) v[j] = __fadd_rn(v[j], __fmul_rn(g.ep.sum_scale, LoadSummand(g.ep.summand, g.ep.summand_dtype, sb + j)));
-    }
-    if (g.ep.relu) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-    }
-    if (g.ep.mid_dtype == ITEXB_DT_BFLOAT16) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
-    } else if (g.ep.mid_dtype == ITEXB_DT_HALF) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __half2float(__float2half_rn(v[j]));
-    }
-    ConvertRow32(g.out_dtype, v, row_ok ? ncols : 0, w, thread_amax, e.out_scale);
+    TcFenceBefore();
+    MbarArrive(SmemAddr(&tmem_empty_bar[acc]));
+    acc ^= 1;
+    if (acc == 0) acc_phase ^= 1;
   }
-  if (g.tma_store) {
-    // The store that last used this staging buffer must have finished reading it.
-    if (lane == 0) TmaStoreWaitRead(e.nbuf - 1);
-    __syncwarp();
-    uint8_t* buf = e.stage + (seq & uint32_t(e.nbuf - 1)) * (1024 * e.esz);  // nbuf is 1, 2 or 4
-    StoreRowStaged(buf, lane, e.esz, w);
-    FenceProxyAsyncShared();
-    __syncwarp();
-    if (lane == 0) {
-      TmaStore2d(tma_out, SmemAddr(buf), col0 * e.esz, row0);  // rows >= m and columns >= n are clipped
-      TmaStoreCommit();
-    }
-    ++seq;
-  } else if (row_ok) {
-    StoreRowDirect(g.out, row * g.ldo + col0, e.esz, w, ncols, g.vec_store && ncols == 32);
+  if (g.tma_store && lane == 0) TmaStoreWaitAll();  // staging memory stays valid until the last store has read it
+  if (OK == kOutFP8 && g.ep.amax != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) thread_amax = fmaxf(thread_amax, __shfl_xor_sync(0xffffffffu, thread_amax, o));
+    if (lane == 0 && thread_amax > 0.f) atomicMax(reinterpret_cast<int*>(g.ep.amax), __float_as_int(thread_amax));
   }
-}
-
-__device__ __forceinline__ void TileCoords(int t, int tiles_m, int tiles_n, int* tm, int* tn) {
-  const int per_group = kGroupM * tiles_n;
-  const int g = t / per_group;
-  const int first_m = g * kGroupM;
-  const int rows = min(kGroupM, tiles_m - first_m);
-  const int r = t - g * per_group;
-  *tm = first_m + r % rows;
-  *tn = r / rows;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -587,62 +602,15 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
   } else if (warp >= 4) {
     // ---------------- epilogue ----------------
-    // Warp (q, half): TMEM lanes 32q..32q+31 (the quarter its warp id allows it to read),
-    // 32-column blocks half, half+2, ... of every tile.  Warps are independent of each other.
-    const int q = warp & 3;
-    const int half = (warp - 4) >> 2;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    float thread_amax = 0.f;
-    EpilogueCtx ectx;
-    const bool has_alpha = g.ep.alpha_a != nullptr && g.ep.alpha_b != nullptr;
-    ectx.scalar_scale = 1.f;
-    ectx.scale = nullptr;
-    if (has_alpha) ectx.scalar_scale = __fmul_rn(__ldg(g.ep.alpha_a), __ldg(g.ep.alpha_b));
-    else if (g.ep.scale_count == 1) ectx.scalar_scale = __ldg(g.ep.scale);
-    else if (g.ep.scale_count > 1) ectx.scale = g.ep.scale;
-    ectx.has_scale = has_alpha || g.ep.scale_count > 0;
-    ectx.bias = g.ep.bias;
-    ectx.has_bias = g.ep.bias != nullptr;
-    ectx.mode = (ectx.scale != nullptr ? 2 : (ectx.has_scale ? 1 : 0)) + (ectx.has_bias ? 3 : 0);
-    ectx.vec_params = ((reinterpret_cast<uintptr_t>(ectx.scale) | reinterpret_cast<uintptr_t>(ectx.bias)) & 15) == 0;
-    ectx.esz = g.out_esz;
-    ectx.nbuf = 4 / g.out_esz;  // 1 (4-byte outputs), 2 (2-byte), 4 (1-byte)
-    ectx.stage = s_stage + (warp - 4) * 4096;
-    ectx.out_scale = g.ep.out_scale != nullptr ? __ldg(g.ep.out_scale) : 1.f;
-    uint32_t seq = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      int tm, tn;
-      TileCoords(t, tiles_m, tiles_n, &tm, &tn);
-      const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
-      if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
-      TcFenceAfter();
-      const int row0 = tm * kBM + q * 32;            // first row of this warp's 32-row block
-      const long long row = (long long)row0 + lane;
-      const bool row_ok = row < g.m;
-      const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
-      // number of 32-column blocks of this tile that hold real columns
-      const int nchunks = min(BN / 32, (g.n - tn * BN + 31) / 32);
-      if (row0 < g.m) {
-#pragma unroll 1
-        for (int c = half; c < nchunks; c += 2) {
-          uint32_t r[32];
-          TmemLd32(taddr + uint32_t(c * 32), r);
-          TmemLdWait(r);
-          const int col0 = tn * BN + c * 32;
-          EpilogueChunk<F8>(g, ectx, &tma_out, r, lane, row0, row, row_ok, col0, min(32, g.n - col0), seq, &thread_amax);
-        }
-      }
-      TcFenceBefore();
-      MbarArrive(SmemAddr(&tmem_empty_bar[acc]));
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
-    }
-    if (g.tma_store && lane == 0) TmaStoreWaitAll();  // staging memory stays valid until the last store has read it
-    if (g.ep.amax != nullptr) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) thread_amax = fmaxf(thread_amax, __shfl_xor_sync(0xffffffffu, thread_amax, o));
-      if (lane == 0 && thread_amax > 0.f) atomicMax(reinterpret_cast<int*>(g.ep.amax), __float_as_int(thread_amax));
+    switch (g.out_kind) {
+      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutF32: EpilogueLoop<BN, F8, kOutF32>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutBF16: EpilogueLoop<BN, F8, kOutBF16>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutF16: EpilogueLoop<BN, F8, kOutF16>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutS32: EpilogueLoop<BN, F8, kOutS32>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutU8: EpilogueLoop<BN, F8, kOutU8>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutS8: EpilogueLoop<BN, F8, kOutS8>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      default: EpilogueLoop<BN, F8, kOutFP8>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
     }
   }
 
@@ -756,6 +724,16 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   // Output addressing: TMA stores from a staged tile when the rows are 16-byte aligned,
   // otherwise per-thread stores straight from registers.
   g.out_esz = g.ep.raw_acc ? 4 : DtypeSize(g.out_dtype);
+  if (g.ep.raw_acc) g.out_kind = kOutRaw;
+  else switch (g.out_dtype) {
+    case ITEXB_DT_FLOAT: g.out_kind = kOutF32; break;
+    case ITEXB_DT_BFLOAT16: g.out_kind = kOutBF16; break;
+    case ITEXB_DT_HALF: g.out_kind = kOutF16; break;
+    case ITEXB_DT_QINT32: case ITEXB_DT_INT32: g.out_kind = kOutS32; break;
+    case ITEXB_DT_QUINT8: case ITEXB_DT_UINT8: g.out_kind = kOutU8; break;
+    case ITEXB_DT_QINT8: case ITEXB_DT_INT8: g.out_kind = kOutS8; break;
+    default: g.out_kind = kOutFP8; break;
+  }
   g.vec_store = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (g.ldo * g.out_esz) % 16 == 0) ? 1 : 0;
   g.tma_store = g.vec_store;
   CUtensorMap to;

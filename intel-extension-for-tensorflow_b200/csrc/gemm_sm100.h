@@ -21,6 +21,7 @@ struct GemmArgs {
   int vec_store;        // output rows are 16-byte aligned (set by LaunchGemm)
   int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)
   int out_esz;          // bytes per output element (set by LaunchGemm)
+  int out_kind;         // epilogue instantiation (set by LaunchGemm)
   // Implicit-GEMM convolution (conv_taps > 0): row m of A is output pixel m of an NHWC
   // tensor, k-block kb reads filter tap kb / kb_per_tap, channel block kb % kb_per_tap.
   int conv_taps, kb_per_tap, kw, oh, ow;

@@ -145,8 +145,8 @@ class QuantizedConv2DOp : public OpKernel {
 
     cudaStream_t st = AsCuda(ctx->stream);
     const int ord = ctx->device_ordinal;
-    const int c_pad = int((c + 15) / 16 * 16);
-    const int64_t kp = kh * kw * c_pad;
+    const int c_pad = int(c);                              // dense [co][kh*kw*c] rows ...
+    const int64_t kp = (kh * kw * c_pad + 15) / 16 * 16;   // ... padded to the 16-byte pitch TMA needs
 
     // ---- filter: [co][kh*kw][c_pad], packed once when constant
     const bool hit = is_filter_const_ && packed_from_ == f.data && packed_.data() != nullptr && packed_bytes_ == size_t(co) * kp;

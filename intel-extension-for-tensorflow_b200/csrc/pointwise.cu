@@ -550,14 +550,16 @@ __global__ void ColsumS8Kernel(const int8_t* __restrict__ b, int32_t* __restrict
   colsum[j] = s;
 }
 
-// HWIO [kh,kw,c,co] -> [co][kh*kw][c_pad]
-__global__ void PackFilterKernel(const uint8_t* __restrict__ f, uint8_t* __restrict__ dst, int taps, int c, int co, int c_pad) {
-  const long long total = (long long)co * taps * c_pad;
+// HWIO [kh,kw,c,co] -> [co][k_pad]: k = (tap * c_pad + channel), zero padded per tap (c_pad > c) and
+// at the row end (k_pad = kh*kw*c_pad rounded up to 16).
+__global__ void PackFilterKernel(const uint8_t* __restrict__ f, uint8_t* __restrict__ dst, int taps, int c, int co, int c_pad,
+                                 int k_pad) {
+  const long long total = (long long)co * k_pad;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int ci = int(i % c_pad);
-    const int t = int((i / c_pad) % taps);
-    const int o = int(i / ((long long)c_pad * taps));
-    dst[i] = ci < c ? f[((long long)t * c + ci) * co + o] : uint8_t(0);
+    const int kk = int(i % k_pad);
+    const int o = int(i / k_pad);
+    const int t = kk / c_pad, ci = kk - t * c_pad;
+    dst[i] = (t < taps && ci < c) ? f[((long long)t * c + ci) * co + o] : uint8_t(0);
   }
 }
 
@@ -676,10 +678,11 @@ int itexb_pack_filter_hwio(const void* f_hwio, void* f_packed, int32_t kh, int32
                            itexb_stream_t stream) {
   ITEXB_REQUIRE(f_hwio != nullptr && f_packed != nullptr && kh > 0 && kw > 0 && c > 0 && co > 0 && c_pad >= c,
                 ITEXB_INVALID_ARGUMENT, "pack_filter_hwio: bad arguments");
-  const long long total = (long long)co * kh * kw * c_pad;
+  const int k_pad = (kh * kw * c_pad + 15) / 16 * 16;
+  const long long total = (long long)co * k_pad;
   const int blocks = int(std::min<long long>((total + 255) / 256, (long long)SmCount() * 8));
   PackFilterKernel<<<blocks, 256, 0, AsCuda(stream)>>>(static_cast<const uint8_t*>(f_hwio), static_cast<uint8_t*>(f_packed),
-                                                      kh * kw, c, co, c_pad);
+                                                      kh * kw, c, co, c_pad, k_pad);
   return CheckLaunch("PackFilterKernel");
 }
 

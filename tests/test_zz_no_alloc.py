@@ -25,7 +25,7 @@ def _params(L, x, fpk, out, scale, bias, n, h, w, c, kh, kw, co, stride, pad, oh
     p.stride_h = p.stride_w = stride
     p.dil_h = p.dil_w = 1
     p.pad_top = p.pad_left = pad
-    p.oh, p.ow, p.c_pad = oh, ow, (c + 15) // 16 * 16
+    p.oh, p.ow, p.c_pad = oh, ow, c
     p.x_dtype, p.out_dtype = L.DT_QUINT8, L.DT_QUINT8
     p.x, p.filter_packed, p.out = x.data_ptr(), fpk.data_ptr(), out.data_ptr()
     p.ep.scale, p.ep.scale_count, p.ep.bias, p.ep.relu = scale.data_ptr(), co, bias.data_ptr(), 1
@@ -43,8 +43,8 @@ def _run_case(itex, seed, n, h, w, c, kh, co, stride):
     f = dev(rng.integers(-127, 128, (kh, kh, c, co)).astype(np.int8))
     scale = dev(rng.uniform(2e-4, 6e-4, co).astype(np.float32))
     bias = dev(rng.standard_normal(co).astype(np.float32))
-    c_pad = (c + 15) // 16 * 16
-    fpk = torch.empty((co, kh * kh * c_pad), dtype=torch.int8, device="cuda")
+    c_pad = c
+    fpk = torch.empty((co, (kh * kh * c_pad + 15) // 16 * 16), dtype=torch.int8, device="cuda")
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     L.check(lib.itexb_pack_filter_hwio(C.c_void_p(f.data_ptr()), C.c_void_p(fpk.data_ptr()), kh, kh, c, co, c_pad, stream))
     ref = torch.empty((n, oh, ow, co), dtype=torch.uint8, device="cuda")
