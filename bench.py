@@ -267,13 +267,146 @@ def run_resnet50(args, rank, world, local, dev, K):
         print(json.dumps(line), flush=True)
 
 
+FP8_LINEARS = ((4096, 4096), (4096, 14336), (14336, 4096))  # (K, N) of the Llama-3-8B-shaped linears, M = 4096 tokens
+
+
+def run_fp8_linears(args, rank, world, local, dev, K):
+    """FP8 e4m3 linears with delayed scaling, column-parallel: rank r holds rows [r*N/g, (r+1)*N/g) of each
+    [N,K] weight, activations are replicated, each rank computes [M, N/g] in bf16 and an NCCL all-gather
+    assembles [g, M, N/g] (shard-major; the consumer reads that layout).  A step is the three linears:
+    scale update, Fp8Quantize(activations), Fp8Quantize(weight shard), Fp8Matmul, all-gather.  Per-shard
+    weight amax values are combined with an all-reduce(max) so every rank keeps the same scaling state."""
+    import torch
+    import torch.distributed as dist
+    fp8 = importlib.import_module("itex_b200.fp8")
+    m = 4096
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1238)                                   # activations are replicated: same seed on every rank
+    layers = []
+    for (k, n) in FP8_LINEARS:
+        assert n % world == 0
+        wgen = torch.Generator(device=dev)
+        wgen.manual_seed(shard_seed(1239 + k + n, rank))
+        w = (torch.randn((n // world, k), generator=wgen, device=dev) * 0.02).to(torch.bfloat16)
+        a = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+        layer = fp8.Fp8Dense(w, recipe=fp8.DelayedScaling(margin=0, amax_history_len=16, amax_compute_algo="max"),
+                             out_dtype="bfloat16", weight_layout="nk")
+        gathered = torch.empty((world, m, n // world), dtype=torch.bfloat16, device=dev)
+        layers.append((layer, a, gathered, k, n))
+
+    comm = torch.cuda.Stream(device=dev)
+
+    def step():
+        # The all-gather of linear i runs on a second stream under the quantize + GEMM of linear i+1.
+        main = torch.cuda.current_stream(dev)
+        comm.wait_stream(main)
+        keep = []
+        for layer, a, gathered, k, n in layers:
+            y = layer(a)
+            keep.append(y)
+            if world > 1:
+                comm.wait_stream(main)
+                with torch.cuda.stream(comm):
+                    # 12 bytes; the state only has to agree before the next step's scale update
+                    dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
+                    dist.all_gather_into_tensor(gathered, y)
+                    y.record_stream(comm)
+            else:
+                gathered[0].copy_(y)
+        main.wait_stream(comm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    # A fixed number of warm-up steps: every step holds collectives, so all ranks must run the same count
+    # (a time-based loop would let ranks disagree and dead-lock).  >= 17 steps fill the 16-deep amax history.
+    n_warm = max(args.warmup, 17, int(args.min_warmup_seconds * 600))
+    for _ in range(n_warm):
+        step()
+    barrier()
+    # One CUDA graph per step (kernels and NCCL collectives): removes ~20 host-side op calls per step,
+    # which otherwise bound the step once the per-GPU GEMMs shrink with the shard count.
+    eager_step = step
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        eager_step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    barrier()
+    with torch.cuda.graph(graph):
+        eager_step()
+    step = graph.replay
+    for _ in range(3):
+        step()
+    barrier()
+    launches0 = K.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    sampler.stop_flag.set()
+    sampler.join()
+    eager_step()                                            # graph replays do not pass through the library's launch counter
+    torch.cuda.synchronize()
+    launches = (K.launch_count() - launches0) * args.steps
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1), world, dev) / args.steps
+    flops = sum(2.0 * m * k * n for k, n in FP8_LINEARS)
+    # end to end: activations from pinned host memory, gathered outputs back to the host
+    hosts = [(torch.empty_like(a, device="cpu").pin_memory().copy_(a), torch.empty(tuple(g_.shape), dtype=torch.bfloat16, pin_memory=True))
+             for _, a, g_, _, _ in layers]
+
+    def e2e_step():
+        for (layer, a, gathered, k, n), (ah, oh) in zip(layers, hosts):
+            a.copy_(ah, non_blocking=True)
+        step()
+        for (layer, a, gathered, k, n), (ah, oh) in zip(layers, hosts):
+            oh.copy_(gathered, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world, dev) / args.e2e_steps
+    if rank == 0:
+        peaks = measured_peaks()
+        tflops = flops / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": "fp8_llama_linears_tokens_per_s", "value": m / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": n_warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "e4m3xe4m3->f32", "data": "synthetic",
+            "config": {"workload": "fp8_llama_linears", "tokens": m, "linears_k_n": FP8_LINEARS, "delayed_scaling": "margin 0, history 16, max",
+                       "output": "bfloat16 [g, M, N/g] after all-gather", "l2": "weights + activations larger than L2",
+                       "parallelism": "column-parallel x%d, NCCL all-gather of outputs" % world, "tflops": tflops},
+            "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,fp8> (tcgen05.mma kind::f8f6f4)", "achieved": tflops,
+                         "peak": 2.0 * peaks["bf16_tflops"] * world, "unit": "TFLOP/s", "frac": tflops / (2.0 * peaks["bf16_tflops"] * world),
+                         "traffic": None, "peak_source": "2 x bf16_tflops (burst) x GPUs, whole step incl. quantize passes and all-gather"},
+            "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": sum(m * k * 2 for k, _ in FP8_LINEARS), "d2h_bytes_per_step": sum(m * n * 2 for _, n in FP8_LINEARS)},
+            "gpu_launches": int(launches), "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS) + ["resnet50_int8"])
+    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears"])
     ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -295,12 +428,22 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = os.environ.get("ITEXB_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if "ITEXB_NCCL_DEBUG" in os.environ:
+            os.environ["NCCL_DEBUG"] = os.environ["ITEXB_NCCL_DEBUG"]
+        else:
+            os.environ["NCCL_DEBUG_FILE"] = os.devnull              # keep stdout to the one JSON line
+        import datetime
+        # a short timeout turns any mismatch between ranks into a quick error instead of a long hang
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     itex = load_package()
     ops = importlib.import_module("itex_b200.ops")
     K = importlib.import_module("itex_b200.kernels")
     dev = torch.device("cuda", local)
+    if args.workload == "fp8_llama_linears":
+        run_fp8_linears(args, rank, world, local, dev, K)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "resnet50_int8":
         run_resnet50(args, rank, world, local, dev, K)
         if world > 1:

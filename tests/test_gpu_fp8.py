@@ -124,3 +124,26 @@ def test_delayed_scaling_20_steps_matches_oracle():
         np.testing.assert_array_equal(host(dh), rh)
         np.testing.assert_array_equal(host(ds), rs)
         np.testing.assert_array_equal(host(dsi), rsi)
+
+
+def test_column_parallel_shards_reassemble_the_full_product():
+    """Column-parallel FP8 linear: the [M, N/g] results of g weight shards (each with the shared, max-combined
+    scaling state) concatenated along N equal the unsharded [M, N] result bit for bit."""
+    itex, K, ops = modules()
+    fp8 = importlib.import_module("itex_b200.fp8")
+    rng = np.random.default_rng(5)
+    m, k, n, g = 128, 256, 384, 4
+    W = torch.from_numpy((rng.standard_normal((n, k)) * 0.02).astype(np.float32)).to(torch.bfloat16).cuda()   # [N, K]
+    full = fp8.Fp8Dense(W, recipe=fp8.DelayedScaling(amax_history_len=4), out_dtype="bfloat16", weight_layout="nk")
+    shards = [fp8.Fp8Dense(W[r * (n // g):(r + 1) * (n // g)].contiguous(), recipe=fp8.DelayedScaling(amax_history_len=4),
+                           out_dtype="bfloat16", weight_layout="nk") for r in range(g)]
+    for step in range(6):
+        A = torch.from_numpy((rng.standard_normal((m, k)) * (1 + step)).astype(np.float32)).to(torch.bfloat16).cuda()
+        ref = full(A)
+        outs = [sh(A) for sh in shards]
+        amax = torch.stack([sh.meta.amax_history[0] for sh in shards]).amax(dim=0)   # what all_reduce(MAX) leaves on every rank
+        for sh in shards:
+            sh.meta.amax_history[0].copy_(amax)
+        assert bool((torch.cat(outs, dim=1) == ref).all())
+        assert bool((shards[0].meta.amax_history == full.meta.amax_history).all())
+        assert bool((shards[-1].meta.scale == full.meta.scale).all())
