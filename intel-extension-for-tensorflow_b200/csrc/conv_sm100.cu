@@ -1,9 +1,12 @@
 // NHWC x HWIO int8 convolution for sm_100a, lowered onto the tcgen05 GEMM kernel.
 //
-// Two lowerings share the MMA main loop and the fused epilogue:
+// Three lowerings share the MMA main loop and the fused epilogue:
 //   * pointwise (1x1, stride 1, no padding, channels a multiple of 16): the input IS the
 //     [n*h*w, c] A operand; nothing is staged.
-//   * general: a gather kernel writes the [n*oh*ow, round_up(kh*kw*c, 16)] patch matrix (zero
+//   * implicit GEMM (channels a multiple of 16): four extra warps of the GEMM kernel gather the A
+//     tile of each k-block straight from the NHWC input with 16-byte cp.async copies (zero fill for
+//     padding) into the swizzled shared-memory layout; nothing is staged in global memory.
+//   * other channel counts (e.g. an RGB stem): a gather kernel writes the [n*oh*ow, round_up(kh*kw*c, 16)] patch matrix (zero
 //     fill for padding) into caller-provided scratch - 16 bytes per thread when c is a multiple
 //     of 16, one contiguous filter-row run per thread otherwise - then the GEMM runs on it.  Scratch traffic is kh*kw times the input; the caller sizes it with
 //     itexb_conv2d_workspace_bytes().
@@ -146,8 +149,12 @@ int Validate(const itexb_conv_params_t& p) {
 
 using namespace itexb;
 
+// Channel counts that are a multiple of 16 are gathered inside the GEMM kernel (16-byte runs);
+// nothing is staged in global memory for them.
+static bool IsImplicit(const itexb_conv_params_t& p) { return p.c % 16 == 0 && p.c_pad == p.c; }
+
 extern "C" size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p) {
-  if (p == nullptr || IsPointwise(*p)) return 0;
+  if (p == nullptr || IsPointwise(*p) || IsImplicit(*p)) return 0;
   return size_t(p->n) * p->oh * p->ow * ((size_t(p->kh) * p->kw * p->c_pad + 15) / 16 * 16);
 }
 
@@ -161,7 +168,10 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   ITEXB_REQUIRE(m < (1ll << 31), ITEXB_INVALID_ARGUMENT, "conv2d: more than 2^31 output pixels");
   const int kp = (p->kh * p->kw * p->c_pad + 15) / 16 * 16;  // patch-matrix / packed-filter row pitch
   const void* a_ptr = p->x;
-  if (!IsPointwise(*p)) {
+  const bool implicit = !IsPointwise(*p) && IsImplicit(*p);
+  if (implicit) {
+    ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->x) & 15) == 0, ITEXB_INVALID_ARGUMENT, "conv2d: input must be 16-byte aligned");
+  } else if (!IsPointwise(*p)) {
     ITEXB_REQUIRE(p->workspace != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d: workspace of %zu bytes is required",
                   itexb_conv2d_workspace_bytes(p));
     ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0, ITEXB_INVALID_ARGUMENT,
@@ -196,9 +206,16 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
                 "conv2d: packed filter must be 16-byte aligned");
   CUtensorMap ta, tb;
   const int bn = PickBN(p->co);
-  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, kp, kp, 128));
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->filter_packed, p->co, kp, kp, bn));
+  if (implicit) ta = tb;  // unused: the kernel gathers A itself
+  else ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, kp, kp, 128));
   GemmArgs g{};
+  if (implicit) {
+    g.conv_taps = p->kh * p->kw; g.conv_kh = p->kh; g.conv_c = p->c; g.conv_h = p->h; g.conv_w = p->w; g.kw = p->kw; g.oh = p->oh; g.ow = p->ow;
+    g.stride_h = p->stride_h; g.stride_w = p->stride_w; g.dil_h = p->dil_h; g.dil_w = p->dil_w;
+    g.pad_top = p->pad_top; g.pad_left = p->pad_left;
+    g.conv_x = p->x;
+  }
   g.m = int(m); g.n = p->co; g.k = kp;
   g.out_dtype = p->out_dtype;
   g.out = p->out; g.ldo = p->co;

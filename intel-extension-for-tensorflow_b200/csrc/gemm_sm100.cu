@@ -41,6 +41,8 @@ constexpr int kBM = 128;          // rows of a per tile = TMEM lanes
 constexpr int kBK = 128;          // bytes of K per pipeline stage (one 128-byte swizzle row)
 constexpr int kUmmaK = 32;        // bytes of K per tcgen05.mma
 constexpr int kThreads = 384;          // 4 control warps + 8 epilogue warps
+constexpr int kThreadsConv = 512;      // ... + 4 warps that gather the convolution's A operand (one thread per tile row)
+constexpr int kGatherThreads = 128;
 constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter: their instruction streams hide each other's latencies
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kGroupM = 16;       // tile rasterisation: m-tiles per L2 super-group
@@ -102,6 +104,8 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile
     }
   }
 }
+
+template <int N> __device__ __forceinline__ void CpAsyncWaitGroup() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void TmaLoad2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -499,8 +503,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 // The kernel.  CONV selects how the producer addresses the A operand: a plain [m,k]
 // matrix (2-D map) or NHWC pixels gathered per filter tap (see conv section below).
 // ---------------------------------------------------------------------------------------
-template <int BN, bool F8>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, bool F8, bool CONV>
+__global__ void __launch_bounds__(CONV ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const GemmArgs g) {
   using C = Cfg<BN>;
@@ -524,7 +528,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
-      MbarInit(SmemAddr(&full_bar[s]), 1);
+      MbarInit(SmemAddr(&full_bar[s]), CONV ? 1 + kGatherThreads : 1);  // B's TMA arrival (+ one per gather thread)
       MbarInit(SmemAddr(&empty_bar[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -557,8 +561,12 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         if (!ok) break;
         const uint32_t fb = SmemAddr(&full_bar[stage]);
         uint8_t* sa = smem + stage * C::kStageBytes;
-        MbarArriveExpectTx(fb, C::kStageBytes);
-        TmaLoad2d(SmemAddr(sa), &tma_a, fb, kb * kBK, tm * kBM);
+        if (CONV) {
+          MbarArriveExpectTx(fb, C::kBBytes);  // the A tile is gathered by warps 12-15
+        } else {
+          MbarArriveExpectTx(fb, C::kStageBytes);
+          TmaLoad2d(SmemAddr(sa), &tma_a, fb, kb * kBK, tm * kBM);
+        }
         TmaLoad2d(SmemAddr(sa + C::kABytes), &tma_b, fb, kb * kBK, tn * BN);
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
@@ -600,7 +608,80 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-  } else if (warp >= 4) {
+  } else if (CONV && warp >= 12) {
+    // ---------------- implicit-GEMM A producer (convolution) ----------------
+    // Thread r owns row r of every A tile = output pixel tm*128 + r.  Per k-block it copies the
+    // eight 16-byte channel runs of that pixel's receptive field straight from the NHWC input
+    // into the position the 128-byte swizzle gives them (what a TMA load would have written),
+    // with cp.async zero fill for padding, rows past the end and the K tail.  Completion is
+    // tracked per thread: once the group issued kStages-2 stages ago has landed, a proxy fence
+    // makes it visible to the tensor core's reads and the thread arrives on that stage's barrier.
+    const int r = threadIdx.x - 12 * 32;
+    const uint32_t swz = uint32_t(r & 7);
+    const uint8_t* __restrict__ x = static_cast<const uint8_t*>(g.conv_x);
+    constexpr int kLag = C::kStages - 2;  // groups a thread keeps in flight before it signals the oldest stage
+    int stage = 0, sig_stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0, signaled = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int tm, tn;
+      TileCoords(t, tiles_m, tiles_n, &tm, &tn);
+      const long long pix = (long long)tm * kBM + r;
+      const bool row_valid = pix < g.m;
+      int iy0 = 0, ix0 = 0;
+      const uint8_t* img = x;
+      if (row_valid) {
+        const int ox = int(pix % g.ow);
+        const int oy = int((pix / g.ow) % g.oh);
+        const long long b = pix / ((long long)g.ow * g.oh);
+        iy0 = oy * g.stride_h - g.pad_top;
+        ix0 = ox * g.stride_w - g.pad_left;
+        img = x + b * g.conv_h * g.conv_w * g.conv_c;
+      }
+      // Running position in the K dimension: channel offset ci inside filter tap (ky, kx).  It advances by
+      // 16 bytes per copy with carries, so no division is needed (channels are a multiple of 16).
+      int ci = 0, kx = 0, ky = 0;
+      int iy = iy0, ix = ix0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer);
+        if (!ok) break;
+        const uint32_t dst_row = SmemAddr(smem + stage * C::kStageBytes) + uint32_t(r) * 128u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const bool in = row_valid && ky < g.conv_kh && iy >= 0 && iy < g.conv_h && ix >= 0 && ix < g.conv_w;
+          const uint8_t* src = in ? img + ((long long)iy * g.conv_w + ix) * g.conv_c + ci : x;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_row + ((uint32_t(j) ^ swz) << 4)), "l"(src),
+                       "r"(in ? 16u : 0u)
+                       : "memory");
+          ci += 16;
+          if (ci == g.conv_c) {
+            ci = 0;
+            ++kx;
+            ix += g.dil_w;
+            if (kx == g.kw) { kx = 0; ix = ix0; ++ky; iy += g.dil_h; }
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        ++issued;
+        if (issued - signaled > kLag) {
+          CpAsyncWaitGroup<kLag>();
+          FenceProxyAsyncShared();
+          MbarArrive(SmemAddr(&full_bar[sig_stage]));
+          ++signaled;
+          if (++sig_stage == C::kStages) sig_stage = 0;
+        }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+    CpAsyncWaitGroup<0>();
+    FenceProxyAsyncShared();
+    while (signaled < issued) {
+      MbarArrive(SmemAddr(&full_bar[sig_stage]));
+      ++signaled;
+      if (++sig_stage == C::kStages) sig_stage = 0;
+    }
+  } else if (warp >= 4 && warp < 12) {
     // ---------------- epilogue ----------------
     switch (g.out_kind) {
       case kOutRaw: EpilogueLoop<BN, F8, kOutRaw>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
@@ -644,26 +725,20 @@ EncodeTiledFn GetEncodeTiled() {
   return fn;
 }
 
-template <int BN, bool F8>
+template <int BN, bool F8, bool CONV>
 int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(GemmKernel<BN, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  });
-  // The attribute is per device; set it again when the current device changed (cheap).
+  // The opt-in shared-memory size is a per-device function attribute; set it when the device changes.
   static thread_local int last_dev = -1;
   int dev = 0;
   ITEXB_CUDA(cudaGetDevice(&dev));
   if (dev != last_dev) {
-    ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     last_dev = dev;
   }
-  ITEXB_CUDA(attr_err);
   const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN);
   const int grid = std::max(1, std::min(tiles, SmCount()));
-  GemmKernel<BN, F8><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
+  GemmKernel<BN, F8, CONV><<<grid, CONV ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
   return CheckLaunch("GemmKernel");
 }
 
@@ -739,14 +814,19 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   CUtensorMap to;
   if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz));
   else to = ta;  // unused by the kernel
-  if (f8) {
-    if (bn == 256) return Launch<256, true>(ta, tb, to, g, st);
-    if (bn == 128) return Launch<128, true>(ta, tb, to, g, st);
-    return Launch<64, true>(ta, tb, to, g, st);
+  if (g.conv_taps > 0) {
+    if (bn == 256) return Launch<256, false, true>(ta, tb, to, g, st);
+    if (bn == 128) return Launch<128, false, true>(ta, tb, to, g, st);
+    return Launch<64, false, true>(ta, tb, to, g, st);
   }
-  if (bn == 256) return Launch<256, false>(ta, tb, to, g, st);
-  if (bn == 128) return Launch<128, false>(ta, tb, to, g, st);
-  return Launch<64, false>(ta, tb, to, g, st);
+  if (f8) {
+    if (bn == 256) return Launch<256, true, false>(ta, tb, to, g, st);
+    if (bn == 128) return Launch<128, true, false>(ta, tb, to, g, st);
+    return Launch<64, true, false>(ta, tb, to, g, st);
+  }
+  if (bn == 256) return Launch<256, false, false>(ta, tb, to, g, st);
+  if (bn == 128) return Launch<128, false, false>(ta, tb, to, g, st);
+  return Launch<64, false, false>(ta, tb, to, g, st);
 }
 
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n) {

@@ -22,10 +22,11 @@ struct GemmArgs {
   int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)
   int out_esz;          // bytes per output element (set by LaunchGemm)
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
-  // Implicit-GEMM convolution (conv_taps > 0): row m of A is output pixel m of an NHWC
-  // tensor, k-block kb reads filter tap kb / kb_per_tap, channel block kb % kb_per_tap.
-  int conv_taps, kb_per_tap, kw, oh, ow;
+  // Implicit-GEMM convolution (conv_taps > 0): row m of A is output pixel m of the NHWC tensor conv_x;
+  // column k = (tap * conv_c + channel), tap = ky * kw + kx.  The A tile is gathered by the kernel.
+  int conv_taps, conv_c, conv_h, conv_w, conv_kh, kw, oh, ow;
   int stride_h, stride_w, dil_h, dil_w, pad_top, pad_left;
+  const void* conv_x;
 };
 
 // 2-D tiled tensor map over a K-major 8-bit operand: dims {k, rows}, row pitch `ld` bytes,

@@ -62,16 +62,17 @@ def _run_case(itex, seed, n, h, w, c, kh, co, stride):
 
 def test_static_scratch_conv_matches_caller_scratch_conv_twice_in_a_row():
     itex, K, ops = modules()
-    _run_case(itex, 1, 2, 28, 28, 64, 3, 64, 1)   # 2*28*28 x 576 patch matrix = 0.9 MB
-    _run_case(itex, 2, 1, 17, 17, 32, 3, 48, 2)   # smaller: runs over the first call's leftovers
+    # channel counts that are not a multiple of 16 are the ones whose patch matrix is staged in scratch
+    _run_case(itex, 1, 2, 28, 28, 24, 3, 64, 1)   # 2*28*28 x 224 patch matrix = 0.35 MB
+    _run_case(itex, 2, 4, 32, 32, 3, 7, 48, 2)    # an RGB stem: runs over the first call's leftovers
 
 
 def test_static_scratch_limit_is_enforced():
     itex, K, ops = modules()
     lib, L = itex.load(), itex._lib
     x = torch.zeros(1, dtype=torch.uint8, device="cuda")
-    p = _params(L, x, x, x, x, x, 32, 56, 56, 64, 3, 3, 64, 1, 1, 56, 56)  # needs 57.8 MB of scratch
+    p = _params(L, x, x, x, x, x, 32, 112, 112, 24, 3, 3, 64, 1, 1, 112, 112)  # needs 32*112*112*224 B = 89.9 MB of scratch
     st = lib.itexb_conv2d_static_scratch(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st == L.RESOURCE_EXHAUSTED
     msg = lib.itexb_last_error().decode()
-    assert "57802752" in msg and "16777216" in msg and "itexb_conv2d" in msg
+    assert "89915392" in msg and "16777216" in msg and "itexb_conv2d" in msg
