@@ -223,15 +223,19 @@ ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
 /* NHWC x (packed) HWIO convolution as an implicit GEMM with the same epilogue.
  * Replaces dnnl::convolution_forward (itex/core/kernels/common/conv_ops.h:953-957,801).
  * x: [n,h,w,c] QUINT8|QINT8; filter packed by itexb_pack_filter_hwio to [co][k_pad],
- * k_pad = kh*kw*c rounded up to 16; out: [n,oh,ow,co].  Padding is zero fill; pad_top/pad_left as
- * computed by GetWindowedOutputSizeVerboseV2 (itex/core/utils/common_shape_fns.cc:42-81). */
+ * k_pad = kh*kw*c_pad rounded up to 16; out: [n,oh,ow,co].  Padding is zero fill; pad_top/pad_left as
+ * computed by GetWindowedOutputSizeVerboseV2 (itex/core/utils/common_shape_fns.cc:42-81).
+ * c_pad is the channel pitch of one filter tap in the packed filter; itexb_conv2d_filter_c_pad
+ * returns the value to use for a geometry (it reads n,h,w,c,kh,kw,strides,dilations,padding,oh,ow):
+ * c rounded up to 128 when the input can be read by TMA im2col loads (c a multiple of 16, strides
+ * up to 8, padding up to 128), otherwise c.  c_pad == c is always accepted. */
 typedef struct itexb_conv_params {
   int32_t n, h, w, c;
   int32_t kh, kw, co;
   int32_t stride_h, stride_w, dil_h, dil_w;
   int32_t pad_top, pad_left;
   int32_t oh, ow;
-  int32_t c_pad;           /* channels per tap in the packed filter: must equal c (dense rows) */
+  int32_t c_pad;           /* channels per tap in the packed filter: itexb_conv2d_filter_c_pad(), or c */
   int32_t x_dtype, out_dtype;
   const void* x;
   const void* filter_packed;
@@ -242,6 +246,7 @@ typedef struct itexb_conv_params {
 } itexb_conv_params_t;
 ITEXB_API int itexb_pack_filter_hwio(const void* f_hwio, void* f_packed, int32_t kh, int32_t kw, int32_t c,
                                      int32_t co, int32_t c_pad, itexb_stream_t stream);
+ITEXB_API int32_t itexb_conv2d_filter_c_pad(const itexb_conv_params_t* p);
 ITEXB_API size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p);
 ITEXB_API int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream);
 

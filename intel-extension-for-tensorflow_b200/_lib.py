@@ -106,6 +106,7 @@ def load():
     lib.itexb_version.restype = C.c_char_p
     lib.itexb_launch_count.restype = C.c_uint64
     lib.itexb_conv2d_workspace_bytes.restype = C.c_size_t
+    lib.itexb_conv2d_filter_c_pad.restype = C.c_int32
     _lib = lib
     return lib
 

@@ -132,14 +132,30 @@ bool IsPointwise(const itexb_conv_params_t& p) {
          p.oh == p.h && p.ow == p.w && p.c % 16 == 0 && p.c_pad == p.c;
 }
 
+// Geometry the TMA im2col path can express: 16-byte channel runs, traversal strides up to 8, box
+// corners and tap offsets within the signed 8-bit fields of the tensor map and the instruction.
+bool Im2colGeometryOk(const itexb_conv_params_t& p) {
+  if (IsPointwise(p) || p.c % 16 != 0 || p.stride_h > 8 || p.stride_w > 8) return false;
+  const int up_w = (p.ow - 1) * p.stride_w - p.pad_left - p.w + 1, up_h = (p.oh - 1) * p.stride_h - p.pad_top - p.h + 1;
+  const auto in8 = [](int v) { return v >= -128 && v <= 127; };
+  return in8(-p.pad_left) && in8(-p.pad_top) && in8(up_w) && in8(up_h) && (p.kw - 1) * p.dil_w <= 127 && (p.kh - 1) * p.dil_h <= 127 &&
+         p.w + up_w + p.pad_left > 0 && p.h + up_h + p.pad_top > 0 && (long long)p.h * p.w * p.c < (1ll << 40);
+}
+
+// Channels per tap the packed filter should have: c rounded up to the 128 bytes of a k-block when
+// the TMA im2col path will run (each k-block is then one tap), c otherwise.
+int FilterCPad(const itexb_conv_params_t& p) { return Im2colGeometryOk(p) ? (p.c + 127) / 128 * 128 : p.c; }
+
+bool IsIm2col(const itexb_conv_params_t& p) { return Im2colGeometryOk(p) && p.c_pad == (p.c + 127) / 128 * 128; }
+
 int Validate(const itexb_conv_params_t& p) {
   ITEXB_REQUIRE(p.n >= 0 && p.h > 0 && p.w > 0 && p.c > 0 && p.kh > 0 && p.kw > 0 && p.co > 0, ITEXB_INVALID_ARGUMENT,
                 "conv2d: bad tensor dimensions");
   ITEXB_REQUIRE(p.stride_h > 0 && p.stride_w > 0 && p.dil_h > 0 && p.dil_w > 0, ITEXB_INVALID_ARGUMENT,
                 "conv2d: strides and dilations must be positive");
   ITEXB_REQUIRE(p.oh > 0 && p.ow > 0, ITEXB_INVALID_ARGUMENT, "conv2d: empty output");
-  ITEXB_REQUIRE(p.c_pad == p.c, ITEXB_INVALID_ARGUMENT,
-                "conv2d: c_pad must equal c (dense packed filter), got %d for c=%d", p.c_pad, p.c);
+  ITEXB_REQUIRE(p.c_pad == p.c || (p.c_pad == (p.c + 127) / 128 * 128 && Im2colGeometryOk(p)), ITEXB_INVALID_ARGUMENT,
+                "conv2d: c_pad must be what itexb_conv2d_filter_c_pad returns (%d or c=%d), got %d", FilterCPad(p), p.c, p.c_pad);
   ITEXB_REQUIRE(IsInt8(p.x_dtype), ITEXB_INVALID_ARGUMENT, "conv2d: input type %s is not qint8/quint8", DtypeName(p.x_dtype));
   return ValidateEpilogue("conv2d", p.ep, p.out_dtype, false, p.co);
 }
@@ -150,11 +166,17 @@ int Validate(const itexb_conv_params_t& p) {
 using namespace itexb;
 
 // Channel counts that are a multiple of 16 are gathered inside the GEMM kernel (16-byte runs);
-// nothing is staged in global memory for them.
-static bool IsImplicit(const itexb_conv_params_t& p) { return p.c % 16 == 0 && p.c_pad == p.c; }
+// nothing is staged in global memory for them.  That kernel keeps 32-bit byte offsets into the
+// input and 15-bit tap masks per axis, hence the size limits.
+static bool IsImplicit(const itexb_conv_params_t& p) {
+  return p.c % 16 == 0 && p.c_pad == p.c && p.kh <= 15 && p.kw <= 15 &&
+         (long long)p.n * p.h * p.w * p.c < (1ll << 31);
+}
+
+extern "C" int32_t itexb_conv2d_filter_c_pad(const itexb_conv_params_t* p) { return p == nullptr ? 0 : FilterCPad(*p); }
 
 extern "C" size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p) {
-  if (p == nullptr || IsPointwise(*p) || IsImplicit(*p)) return 0;
+  if (p == nullptr || IsPointwise(*p) || IsIm2col(*p) || IsImplicit(*p)) return 0;
   return size_t(p->n) * p->oh * p->ow * ((size_t(p->kh) * p->kw * p->c_pad + 15) / 16 * 16);
 }
 
@@ -168,8 +190,9 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   ITEXB_REQUIRE(m < (1ll << 31), ITEXB_INVALID_ARGUMENT, "conv2d: more than 2^31 output pixels");
   const int kp = (p->kh * p->kw * p->c_pad + 15) / 16 * 16;  // patch-matrix / packed-filter row pitch
   const void* a_ptr = p->x;
-  const bool implicit = !IsPointwise(*p) && IsImplicit(*p);
-  if (implicit) {
+  const bool im2col = IsIm2col(*p);
+  const bool implicit = !im2col && !IsPointwise(*p) && IsImplicit(*p);
+  if (implicit || im2col) {
     ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->x) & 15) == 0, ITEXB_INVALID_ARGUMENT, "conv2d: input must be 16-byte aligned");
   } else if (!IsPointwise(*p)) {
     ITEXB_REQUIRE(p->workspace != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d: workspace of %zu bytes is required",
@@ -208,10 +231,11 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   const int bn = PickBN(p->co);
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->filter_packed, p->co, kp, kp, bn));
   if (implicit) ta = tb;  // unused: the kernel gathers A itself
+  else if (im2col) ITEXB_RETURN_IF_ERROR(EncodeIm2colMap(&ta, *p));
   else ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, kp, kp, 128));
   GemmArgs g{};
-  if (implicit) {
-    g.conv_taps = p->kh * p->kw; g.conv_kh = p->kh; g.conv_c = p->c; g.conv_h = p->h; g.conv_w = p->w; g.kw = p->kw; g.oh = p->oh; g.ow = p->ow;
+  if (implicit || im2col) {
+    g.conv_mode = im2col ? kConvIm2col : kConvGather; g.conv_cpad = p->c_pad; g.conv_kh = p->kh; g.conv_c = p->c; g.conv_h = p->h; g.conv_w = p->w; g.kw = p->kw; g.oh = p->oh; g.ow = p->ow;
     g.stride_h = p->stride_h; g.stride_w = p->stride_w; g.dil_h = p->dil_h; g.dil_w = p->dil_w;
     g.pad_top = p->pad_top; g.pad_left = p->pad_left;
     g.conv_x = p->x;

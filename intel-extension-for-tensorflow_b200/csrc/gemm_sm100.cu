@@ -40,10 +40,12 @@ namespace {
 constexpr int kBM = 128;          // rows of a per tile = TMEM lanes
 constexpr int kBK = 128;          // bytes of K per pipeline stage (one 128-byte swizzle row)
 constexpr int kUmmaK = 32;        // bytes of K per tcgen05.mma
-constexpr int kThreads = 384;          // 4 control warps + 8 epilogue warps
-constexpr int kThreadsConv = 512;      // ... + 4 warps that gather the convolution's A operand (one thread per tile row)
+constexpr int kEpilogueWarps = 16;     // four per TMEM lane quarter = four per scheduler: their instruction streams hide each other's latencies
+constexpr int kFirstGatherWarp = 4 + kEpilogueWarps;
+constexpr int kThreads = 32 * kFirstGatherWarp;          // 4 control warps + the epilogue warps
+constexpr int kThreadsConv = kThreads + 128;            // ... + 4 warps that gather the convolution's A operand (one thread per tile row)
 constexpr int kGatherThreads = 128;
-constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter: their instruction streams hide each other's latencies
+constexpr int kStagingPerWarp = 2048;  // bytes of output staging each epilogue warp owns
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kGroupM = 16;       // tile rasterisation: m-tiles per L2 super-group
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
@@ -57,7 +59,7 @@ template <int BN> struct Cfg {
   static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128), 8 (64)
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two >= 32
   static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-  static constexpr int kStagingBytes = kEpilogueWarps * 4096;  // one 32 x 128-byte output block per epilogue warp
+  static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
 };
 
@@ -111,6 +113,16 @@ __device__ __forceinline__ void TmaLoad2d(uint32_t dst, const void* tmap, uint32
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// One k-block of a convolution's A operand: 128 channels from c0 of the pixels that start at
+// base position (w, h, n) and follow the map's traversal strides, displaced by the filter tap's
+// offset (off_w, off_h); positions outside the image read zeros.
+__device__ __forceinline__ void TmaLoadIm2col(uint32_t dst, const void* tmap, uint32_t bar, int c0, int w, int h, int n, int off_w, int off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(w), "r"(h), "r"(n), "h"(uint16_t(off_w)), "h"(uint16_t(off_h))
       : "memory");
 }
 
@@ -297,8 +309,7 @@ __device__ __forceinline__ void TmaStore2d(const void* tmap, uint32_t src_smem, 
 __device__ __forceinline__ void TmaStoreCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Blocks until at most `pending` of this thread's store groups are still reading shared memory.
 __device__ __forceinline__ void TmaStoreWaitRead(int pending) {
-  if (pending >= 3) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
-  else if (pending == 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+  if (pending == 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
   else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void TmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -315,24 +326,29 @@ struct EpilogueCtx {
   bool sum_bytes_vec;   // summand is 1-byte with 16-byte aligned rows: one 16-byte load per slice
   bool e4m3;            // FP8 output format
   float out_scale;      // FP8 output scale
-  uint8_t* stage;       // this warp's 4 KiB of staging
+  uint8_t* stage;       // this warp's staging memory
 };
 
-// The persistent loop of one epilogue warp.  Warp (q, half) owns TMEM lanes 32q..32q+31 (the
-// quarter its warp id may read) and the 32-column blocks half, half+2, ... of every tile.
-// A block is produced as two 16-column slices into a swizzled staging tile (32 rows x 32
-// elements) that one TMA store then writes; edges are clipped by the tensor map.  Without
-// TMA-legal output rows the slices go straight to global memory.
+// The persistent loop of one epilogue warp.  Warp (q, sub) owns TMEM lanes 32q..32q+31 (the
+// quarter its warp id may read) and the column blocks sub, sub+4, ... of every tile.  A block
+// is 16 columns of a 4-byte output or 32 columns of a narrower one; it is produced as 16-column
+// slices into a swizzled staging tile (32 rows of 64 or 32 bytes) that one TMA store then
+// writes; edges are clipped by the tensor map.  Without TMA-legal output rows the slices go
+// straight to global memory.
 template <int BN, bool F8, int OK>
 __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, uint8_t* s_stage, uint64_t* tmem_full_bar,
                                              uint64_t* tmem_empty_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane,
                                              int tiles_m, int tiles_n, int num_tiles) {
   constexpr int esz = OutBytes<OK>::v;
-  constexpr int units = esz;                 // 16-byte units per 16-column slice
-  constexpr int row_units = 2 * esz;         // ... per 32-column staging row
-  constexpr int nbuf = 4 / esz;              // staging buffers per warp: 1 (4-byte), 2 (2-byte), 4 (1-byte)
+  constexpr int units = esz;                          // 16-byte units per 16-column slice
+  constexpr int bcols = esz == 4 ? 16 : 32;           // columns per block
+  constexpr int slices = bcols / 16;
+  constexpr int row_bytes = bcols * esz;              // 64, 64, 32
+  constexpr int row_units = row_bytes / 16;
+  constexpr int buf_bytes = 32 * row_bytes;
+  constexpr int nbuf = kStagingPerWarp / buf_bytes;   // staging buffers per warp: 1 (4- and 2-byte outputs), 2 (1-byte)
   const int q = warp & 3;
-  const int half = (warp - 4) >> 2;
+  const int sub = (warp - 4) >> 2;
   EpilogueCtx e;
   const bool has_alpha = g.ep.alpha_a != nullptr && g.ep.alpha_b != nullptr;
   e.scalar_scale = 1.f;
@@ -348,7 +364,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                     (reinterpret_cast<uintptr_t>(g.ep.summand) & 15) == 0;
   e.e4m3 = g.out_dtype == ITEXB_DT_FP8_E4M3;
   e.out_scale = g.ep.out_scale != nullptr ? __ldg(g.ep.out_scale) : 1.f;
-  e.stage = s_stage + (warp - 4) * 4096;
+  e.stage = s_stage + (warp - 4) * kStagingPerWarp;
   const bool sum_signed = g.ep.summand_dtype == ITEXB_DT_QINT8 || g.ep.summand_dtype == ITEXB_DT_INT8;
   const int swz = (lane / (8 / row_units)) % row_units;  // this lane's XOR term of the staging swizzle
   int acc = 0;
@@ -365,23 +381,18 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     const long long row = (long long)row0 + lane;
     const bool row_ok = row < g.m;
     const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
-    const int nblocks = min(BN / 32, (g.n - tn * BN + 31) / 32);  // 32-column blocks holding real columns
+    const int nblocks = min(BN / bcols, (g.n - tn * BN + bcols - 1) / bcols);  // blocks holding real columns
     if (row0 < g.m) {
 #pragma unroll 1
-      for (int c = half; c < nblocks; c += 2) {
-        const int col0 = tn * BN + c * 32;
-        uint8_t* buf = e.stage + (seq & uint32_t(nbuf - 1)) * (1024 * esz);
-        if (g.tma_store) {
-          // the store that last used this staging buffer must have finished reading it
-          if (lane == 0) TmaStoreWaitRead(nbuf - 1);
-          __syncwarp();
-        }
+      for (int c = sub; c < nblocks; c += kEpilogueWarps / 4) {
+        const int col0 = tn * BN + c * bcols;
+        uint8_t* buf = e.stage + (seq & uint32_t(nbuf - 1)) * buf_bytes;
 #pragma unroll 1
-        for (int sl = 0; sl < 2; ++sl) {
+        for (int sl = 0; sl < slices; ++sl) {
           const int col = col0 + 16 * sl;
           if (col >= g.n) break;
           uint32_t r[16];
-          TmemLd16(taddr + uint32_t(c * 32 + 16 * sl), r);
+          TmemLd16(taddr + uint32_t(c * bcols + 16 * sl), r);
           uint32_t w[16];
           if (OK == kOutRaw) {
             TmemLdWait16(r);
@@ -452,9 +463,14 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             Convert16<OK>(v, w, e.e4m3, e.out_scale);
           }
           if (g.tma_store) {
+            if (sl == 0) {
+              // the store that last used this staging buffer must have finished reading it
+              if (lane == 0) TmaStoreWaitRead(nbuf - 1);
+              __syncwarp();
+            }
             // 16-byte unit j of staging row r lives at unit j ^ ((r / (8/row_units)) % row_units): the
-            // layout a TMA store with a 128/64/32-byte swizzle reads (row width 32 * esz bytes)
-            uint8_t* srow = buf + lane * (32 * esz);
+            // layout a TMA store with a 64/32-byte swizzle reads
+            uint8_t* srow = buf + lane * row_bytes;
 #pragma unroll
             for (int u = 0; u < units; ++u)
               *reinterpret_cast<uint4*>(srow + (((sl * units + u) ^ swz) << 4)) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
@@ -503,14 +519,14 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 // The kernel.  CONV selects how the producer addresses the A operand: a plain [m,k]
 // matrix (2-D map) or NHWC pixels gathered per filter tap (see conv section below).
 // ---------------------------------------------------------------------------------------
-template <int BN, bool F8, bool CONV>
-__global__ void __launch_bounds__(CONV ? kThreadsConv : kThreads, 1)
+template <int BN, bool F8, int CONV>
+__global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const GemmArgs g) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* s_stage = smem + C::kStages * C::kStageBytes;  // 8 warps x 4 KiB, 1024-aligned
+  uint8_t* s_stage = smem + C::kStages * C::kStageBytes;  // the epilogue warps' staging tiles, 1024-aligned
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_stage + C::kStagingBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + C::kStages;
@@ -528,7 +544,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
-      MbarInit(SmemAddr(&full_bar[s]), CONV ? 1 + kGatherThreads : 1);  // B's TMA arrival (+ one per gather thread)
+      MbarInit(SmemAddr(&full_bar[s]), CONV == kConvGather ? 1 + kGatherThreads : 1);  // B's TMA arrival (+ one per gather thread)
       MbarInit(SmemAddr(&empty_bar[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -556,13 +572,26 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
       TileCoords(t, tiles_m, tiles_n, &tm, &tn);
+      int w0 = 0, h0 = 0, n0 = 0, c0 = 0, kx = 0, ky = 0;  // im2col: base position of the tile's first pixel, position in K
+      if (CONV == kConvIm2col) {
+        const int pix = tm * kBM;
+        const int rest = pix / g.ow;
+        w0 = (pix - rest * g.ow) * g.stride_w - g.pad_left;
+        n0 = rest / g.oh;
+        h0 = (rest - n0 * g.oh) * g.stride_h - g.pad_top;
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer);
         if (!ok) break;
         const uint32_t fb = SmemAddr(&full_bar[stage]);
         uint8_t* sa = smem + stage * C::kStageBytes;
-        if (CONV) {
-          MbarArriveExpectTx(fb, C::kBBytes);  // the A tile is gathered by warps 12-15
+        if (CONV == kConvGather) {
+          MbarArriveExpectTx(fb, C::kBBytes);  // the A tile is gathered by the last four warps
+        } else if (CONV == kConvIm2col) {
+          MbarArriveExpectTx(fb, C::kStageBytes);
+          TmaLoadIm2col(SmemAddr(sa), &tma_a, fb, c0, w0, h0, n0, kx * g.dil_w, ky * g.dil_h);
+          c0 += kBK;
+          if (c0 >= g.conv_cpad) { c0 = 0; if (++kx == g.kw) { kx = 0; ++ky; } }
         } else {
           MbarArriveExpectTx(fb, C::kStageBytes);
           TmaLoad2d(SmemAddr(sa), &tma_a, fb, kb * kBK, tm * kBM);
@@ -608,16 +637,20 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-  } else if (CONV && warp >= 12) {
+  } else if (CONV == kConvGather && warp >= kFirstGatherWarp) {
     // ---------------- implicit-GEMM A producer (convolution) ----------------
-    // Thread r owns row r of every A tile = output pixel tm*128 + r.  Per k-block it copies the
-    // eight 16-byte channel runs of that pixel's receptive field straight from the NHWC input
-    // into the position the 128-byte swizzle gives them (what a TMA load would have written),
-    // with cp.async zero fill for padding, rows past the end and the K tail.  Completion is
-    // tracked per thread: once the group issued kStages-2 stages ago has landed, a proxy fence
-    // makes it visible to the tensor core's reads and the thread arrives on that stage's barrier.
-    const int r = threadIdx.x - 12 * 32;
-    const uint32_t swz = uint32_t(r & 7);
+    // Every k-block these 128 threads copy the 128 x 128-byte A tile straight from the NHWC input
+    // into the positions the 128-byte swizzle gives them (what a TMA load would have written),
+    // 16 bytes per cp.async, zero-filled for padding, rows past the end and the K tail.  Thread g
+    // owns 16-byte column g%8 of rows g/8, g/8+16, ..., so a warp reads four whole 128-byte runs
+    // and the position in K (filter tap and channel) is the same for all eight of its copies.
+    // Per tile each thread keeps, for its eight rows, the byte offset of the receptive field's
+    // corner and a bit mask of the taps that fall inside the image (bits 0-14: kx, 16-30: ky).
+    // Completion is tracked per thread: once the group issued kStages-2 stages ago has landed, a
+    // proxy fence makes it visible to the tensor core and the thread arrives on that stage's barrier.
+    const int gi = threadIdx.x - kFirstGatherWarp * 32;
+    const int j = gi & 7, rbase = gi >> 3;
+    const uint32_t dst_off = uint32_t(rbase) * 128u + (uint32_t(j ^ (rbase & 7)) << 4);
     const uint8_t* __restrict__ x = static_cast<const uint8_t*>(g.conv_x);
     constexpr int kLag = C::kStages - 2;  // groups a thread keeps in flight before it signals the oldest stage
     int stage = 0, sig_stage = 0;
@@ -627,40 +660,42 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
       TileCoords(t, tiles_m, tiles_n, &tm, &tn);
-      const long long pix = (long long)tm * kBM + r;
-      const bool row_valid = pix < g.m;
-      int iy0 = 0, ix0 = 0;
-      const uint8_t* img = x;
-      if (row_valid) {
-        const int ox = int(pix % g.ow);
-        const int oy = int((pix / g.ow) % g.oh);
-        const long long b = pix / ((long long)g.ow * g.oh);
-        iy0 = oy * g.stride_h - g.pad_top;
-        ix0 = ox * g.stride_w - g.pad_left;
-        img = x + b * g.conv_h * g.conv_w * g.conv_c;
+      uint32_t msk[8], off[8];
+      {
+        int pix = tm * kBM + rbase;  // m < 2^31 is checked by the host
+        int ox = pix % g.ow;
+        const int rest = pix / g.ow;
+        int oy = rest % g.oh;
+        int b = rest / g.oh;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int iy0 = oy * g.stride_h - g.pad_top, ix0 = ox * g.stride_w - g.pad_left;
+          uint32_t ym = 0, xm = 0;
+          for (int ky = 0; ky < g.conv_kh; ++ky) ym |= uint32_t(uint32_t(iy0 + ky * g.dil_h) < uint32_t(g.conv_h)) << ky;
+          for (int kx = 0; kx < g.kw; ++kx) xm |= uint32_t(uint32_t(ix0 + kx * g.dil_w) < uint32_t(g.conv_w)) << kx;
+          msk[i] = pix < g.m ? (ym << 16) | xm : 0u;
+          // modulo 2^32; exact once a valid tap's offset is added (the host bounds the input size)
+          off[i] = uint32_t((b * g.conv_h + iy0) * g.conv_w + ix0) * uint32_t(g.conv_c);
+          pix += 16;
+          ox += 16;
+          while (ox >= g.ow) { ox -= g.ow; if (++oy == g.oh) { oy = 0; ++b; } }
+        }
       }
-      // Running position in the K dimension: channel offset ci inside filter tap (ky, kx).  It advances by
-      // 16 bytes per copy with carries, so no division is needed (channels are a multiple of 16).
-      int ci = 0, kx = 0, ky = 0;
-      int iy = iy0, ix = ix0;
+      // Position in K of this thread's column: channel ci inside tap (ky, kx); 128 bytes further per k-block.
+      int ci = j * 16, kx = 0, ky = 0;
+      while (ci >= g.conv_c) { ci -= g.conv_c; if (++kx == g.kw) { kx = 0; ++ky; } }
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer);
         if (!ok) break;
-        const uint32_t dst_row = SmemAddr(smem + stage * C::kStageBytes) + uint32_t(r) * 128u;
+        const uint32_t dst = SmemAddr(smem + stage * C::kStageBytes) + dst_off;
+        const uint32_t tap_off = uint32_t((ky * g.dil_h * g.conv_w + kx * g.dil_w) * g.conv_c + ci);
+        const uint32_t shx = ky < g.conv_kh ? uint32_t(kx) : 31u, shy = ky < g.conv_kh ? uint32_t(16 + ky) : 31u;  // bit 31 is never set
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const bool in = row_valid && ky < g.conv_kh && iy >= 0 && iy < g.conv_h && ix >= 0 && ix < g.conv_w;
-          const uint8_t* src = in ? img + ((long long)iy * g.conv_w + ix) * g.conv_c + ci : x;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_row + ((uint32_t(j) ^ swz) << 4)), "l"(src),
-                       "r"(in ? 16u : 0u)
+        for (int i = 0; i < 8; ++i) {
+          const bool in = ((msk[i] >> shx) & (msk[i] >> shy) & 1u) != 0;
+          const uint8_t* src = x + (in ? uint32_t(off[i] + tap_off) : 0u);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + uint32_t(i) * 2048u), "l"(src), "r"(in ? 16u : 0u)
                        : "memory");
-          ci += 16;
-          if (ci == g.conv_c) {
-            ci = 0;
-            ++kx;
-            ix += g.dil_w;
-            if (kx == g.kw) { kx = 0; ix = ix0; ++ky; iy += g.dil_h; }
-          }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         ++issued;
@@ -672,6 +707,8 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
           if (++sig_stage == C::kStages) sig_stage = 0;
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        ci += kBK;
+        while (ci >= g.conv_c) { ci -= g.conv_c; if (++kx == g.kw) { kx = 0; ++ky; } }
       }
     }
     CpAsyncWaitGroup<0>();
@@ -681,7 +718,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       ++signaled;
       if (++sig_stage == C::kStages) sig_stage = 0;
     }
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < kFirstGatherWarp) {
     // ---------------- epilogue ----------------
     switch (g.out_kind) {
       case kOutRaw: EpilogueLoop<BN, F8, kOutRaw>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
@@ -725,7 +762,7 @@ EncodeTiledFn GetEncodeTiled() {
   return fn;
 }
 
-template <int BN, bool F8, bool CONV>
+template <int BN, bool F8, int CONV>
 int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
   // The opt-in shared-memory size is a per-device function attribute; set it when the device changes.
@@ -738,7 +775,7 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   }
   const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN);
   const int grid = std::max(1, std::min(tiles, SmCount()));
-  GemmKernel<BN, F8, CONV><<<grid, CONV ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
+  GemmKernel<BN, F8, CONV><<<grid, CONV == kConvGather ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
   return CheckLaunch("GemmKernel");
 }
 
@@ -759,17 +796,49 @@ int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k
   return ITEXB_OK;
 }
 
+using EncodeIm2colFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
+                                    const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p) {
+  static EncodeIm2colFn enc = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &f, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      enc = reinterpret_cast<EncodeIm2colFn>(f);
+    else
+      (void)cudaGetLastError();
+  });
+  ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeIm2col is not available from the CUDA driver");
+  const cuuint64_t dims[4] = {cuuint64_t(p.c), cuuint64_t(p.w), cuuint64_t(p.h), cuuint64_t(p.n)};
+  const cuuint64_t strides[3] = {cuuint64_t(p.c), cuuint64_t(p.w) * p.c, cuuint64_t(p.h) * p.w * p.c};
+  // The base position of output pixel (oy, ox) is (oy*stride - pad_top, ox*stride - pad_left); the box
+  // corners bound it to the oh x ow positions of one image so that a run of pixels wraps like the output.
+  const int lower[2] = {-p.pad_left, -p.pad_top};
+  const int upper[2] = {(p.ow - 1) * p.stride_w - p.pad_left - p.w + 1, (p.oh - 1) * p.stride_h - p.pad_top - p.h + 1};
+  const cuuint32_t estr[4] = {1, cuuint32_t(p.stride_w), cuuint32_t(p.stride_h), 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(p.x), dims, strides, lower, upper, cuuint32_t(kBK),
+                   cuuint32_t(kBM), estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL,
+                "cuTensorMapEncodeIm2col failed with CUresult %d (n=%d h=%d w=%d c=%d corners [%d,%d] [%d,%d] strides %d,%d)", int(r), p.n,
+                p.h, p.w, p.c, lower[0], lower[1], upper[0], upper[1], p.stride_w, p.stride_h);
+  return ITEXB_OK;
+}
+
 // Tensor map for the epilogue's TMA stores: the output as a byte matrix {n*esz, m} with
-// row pitch ldo*esz, box = one warp block of 32 rows x 32 elements, swizzle matching the
-// staging tile's row width (128, 64 or 32 bytes).
+// row pitch ldo*esz, box = one warp block of 32 rows x 16 (4-byte) or 32 (narrower) elements,
+// swizzle matching the staging tile's row width (64 or 32 bytes).
 static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz) {
   EncodeTiledFn enc = GetEncodeTiled();
   ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   const cuuint64_t dims[2] = {cuuint64_t(n) * esz, cuuint64_t(m)};
   const cuuint64_t strides[1] = {cuuint64_t(ldo) * esz};
-  const cuuint32_t box[2] = {cuuint32_t(32 * esz), 32};
+  const cuuint32_t box[2] = {cuuint32_t(esz == 1 ? 32 : 64), 32};
   const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapSwizzle sw = esz == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : (esz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  const CUtensorMapSwizzle sw = esz == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled (output) failed with CUresult %d", int(r));
@@ -814,19 +883,24 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   CUtensorMap to;
   if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz));
   else to = ta;  // unused by the kernel
-  if (g.conv_taps > 0) {
-    if (bn == 256) return Launch<256, false, true>(ta, tb, to, g, st);
-    if (bn == 128) return Launch<128, false, true>(ta, tb, to, g, st);
-    return Launch<64, false, true>(ta, tb, to, g, st);
+  if (g.conv_mode == kConvGather) {
+    if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, g, st);
+    if (bn == 128) return Launch<128, false, kConvGather>(ta, tb, to, g, st);
+    return Launch<64, false, kConvGather>(ta, tb, to, g, st);
+  }
+  if (g.conv_mode == kConvIm2col) {
+    if (bn == 256) return Launch<256, false, kConvIm2col>(ta, tb, to, g, st);
+    if (bn == 128) return Launch<128, false, kConvIm2col>(ta, tb, to, g, st);
+    return Launch<64, false, kConvIm2col>(ta, tb, to, g, st);
   }
   if (f8) {
-    if (bn == 256) return Launch<256, true, false>(ta, tb, to, g, st);
-    if (bn == 128) return Launch<128, true, false>(ta, tb, to, g, st);
-    return Launch<64, true, false>(ta, tb, to, g, st);
+    if (bn == 256) return Launch<256, true, kConvNone>(ta, tb, to, g, st);
+    if (bn == 128) return Launch<128, true, kConvNone>(ta, tb, to, g, st);
+    return Launch<64, true, kConvNone>(ta, tb, to, g, st);
   }
-  if (bn == 256) return Launch<256, false, false>(ta, tb, to, g, st);
-  if (bn == 128) return Launch<128, false, false>(ta, tb, to, g, st);
-  return Launch<64, false, false>(ta, tb, to, g, st);
+  if (bn == 256) return Launch<256, false, kConvNone>(ta, tb, to, g, st);
+  if (bn == 128) return Launch<128, false, kConvNone>(ta, tb, to, g, st);
+  return Launch<64, false, kConvNone>(ta, tb, to, g, st);
 }
 
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n) {

@@ -22,13 +22,21 @@ struct GemmArgs {
   int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)
   int out_esz;          // bytes per output element (set by LaunchGemm)
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
-  // Implicit-GEMM convolution (conv_taps > 0): row m of A is output pixel m of the NHWC tensor conv_x;
-  // column k = (tap * conv_c + channel), tap = ky * kw + kx.  The A tile is gathered by the kernel.
-  int conv_taps, conv_c, conv_h, conv_w, conv_kh, kw, oh, ow;
+  // Implicit-GEMM convolution (conv_mode != kConvNone): row m of A is output pixel m of the NHWC tensor
+  // conv_x; column k = tap * conv_cpad + channel, tap = ky * kw + kx.  kConvGather: conv_cpad == conv_c and
+  // four extra warps gather the A tile with cp.async.  kConvIm2col: conv_cpad is conv_c rounded up to 128
+  // and the A tile of a k-block (one tap, 128 channels) is one TMA im2col load through the map `ta`.
+  int conv_mode, conv_cpad;
+  int conv_c, conv_h, conv_w, conv_kh, kw, oh, ow;
   int stride_h, stride_w, dil_h, dil_w, pad_top, pad_left;
   const void* conv_x;
 };
 
+enum : int { kConvNone = 0, kConvGather = 1, kConvIm2col = 2 };
+
+// 4-D im2col tensor map over an NHWC 8-bit tensor: box = 128 channels x 128 pixels, 128-byte swizzle,
+// zero fill outside; the pixel bounding box and traversal strides describe the convolution.
+int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p);
 // 2-D tiled tensor map over a K-major 8-bit operand: dims {k, rows}, row pitch `ld` bytes,
 // box {128 bytes, box_rows}, 128-byte swizzle, zero fill outside.
 int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);

@@ -145,8 +145,14 @@ class QuantizedConv2DOp : public OpKernel {
 
     cudaStream_t st = AsCuda(ctx->stream);
     const int ord = ctx->device_ordinal;
-    const int c_pad = int(c);                              // dense [co][kh*kw*c] rows ...
-    const int64_t kp = (kh * kw * c_pad + 15) / 16 * 16;   // ... padded to the 16-byte pitch TMA needs
+    itexb_conv_params_t p{};
+    p.n = int(n); p.h = int(h); p.w = int(w); p.c = int(c);
+    p.kh = int(kh); p.kw = int(kw); p.co = int(co);
+    p.stride_h = stride_h_; p.stride_w = stride_w_; p.dil_h = dil_h_; p.dil_w = dil_w_;
+    p.pad_top = int(pt); p.pad_left = int(pl);
+    p.oh = int(oh); p.ow = int(ow);
+    const int c_pad = itexb_conv2d_filter_c_pad(&p);       // channels per tap of the packed filter: c, or c rounded up to 128 ...
+    const int64_t kp = (kh * kw * c_pad + 15) / 16 * 16;   // ... rows padded to the 16-byte pitch TMA needs
 
     // ---- filter: [co][kh*kw][c_pad], packed once when constant
     const bool hit = is_filter_const_ && packed_from_ == f.data && packed_.data() != nullptr && packed_bytes_ == size_t(co) * kp;
@@ -177,12 +183,6 @@ class QuantizedConv2DOp : public OpKernel {
       saved_factors_ = factors;
     }
 
-    itexb_conv_params_t p{};
-    p.n = int(n); p.h = int(h); p.w = int(w); p.c = int(c);
-    p.kh = int(kh); p.kw = int(kw); p.co = int(co);
-    p.stride_h = stride_h_; p.stride_w = stride_w_; p.dil_h = dil_h_; p.dil_w = dil_w_;
-    p.pad_top = int(pt); p.pad_left = int(pl);
-    p.oh = int(oh); p.ow = int(ow);
     p.c_pad = c_pad;
     p.x_dtype = tinput_; p.out_dtype = out_type_;
     p.x = x.data; p.filter_packed = packed_.data(); p.out = dst.data;

@@ -128,3 +128,83 @@ def test_conv_argument_errors():
     with pytest.raises(itex.ItexError) as e:
         ops._ITEXQuantizedConv2DWithBiasAndReluAndRequantize(x, f, b, 0.0, 1.0, -1.0, 1.0, 0.0, 1.0)
     assert "input and filter must have the same depth" in str(e.value)
+
+
+def _abi_conv(itex, x, f, scale, bias, stride, dil, pad, oh, ow, c_pad, out_dtype=None):
+    """One convolution through the C-ABI with the packed filter's tap pitch chosen by the caller."""
+    import ctypes as C
+    lib, L = itex.load(), itex._lib
+    n, h, w, c = x.shape
+    kh, kw, _, co = f.shape
+    p = L.ConvParams()
+    p.n, p.h, p.w, p.c, p.kh, p.kw, p.co = n, h, w, c, kh, kw, co
+    p.stride_h = p.stride_w = stride
+    p.dil_h = p.dil_w = dil
+    p.pad_top = p.pad_left = pad
+    p.oh, p.ow = oh, ow
+    if c_pad == "preferred":
+        c_pad = lib.itexb_conv2d_filter_c_pad(C.byref(p))
+    p.c_pad = c_pad
+    p.x_dtype, p.out_dtype = L.DT_QUINT8, L.DT_QUINT8
+    fpk = torch.empty((co, (kh * kw * c_pad + 15) // 16 * 16), dtype=torch.int8, device="cuda")
+    out = torch.full((n, oh, ow, co), 99, dtype=torch.uint8, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    L.check(lib.itexb_pack_filter_hwio(C.c_void_p(f.data_ptr()), C.c_void_p(fpk.data_ptr()), kh, kw, c, co, c_pad, stream))
+    p.x, p.filter_packed, p.out = x.data_ptr(), fpk.data_ptr(), out.data_ptr()
+    p.ep.scale, p.ep.scale_count, p.ep.bias, p.ep.relu = scale.data_ptr(), co, bias.data_ptr(), 1
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    p.status_word = status.data_ptr()
+    ws_bytes = lib.itexb_conv2d_workspace_bytes(C.byref(p))
+    ws = torch.empty(max(1, ws_bytes), dtype=torch.uint8, device="cuda")
+    p.workspace = ws.data_ptr()
+    L.check(lib.itexb_conv2d(C.byref(p), stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return host(out), c_pad, ws_bytes
+
+
+@pytest.mark.parametrize("case", [
+    # n, h, w, c, k, co, stride, dilation
+    (2, 14, 14, 64, 3, 64, 1, 1),      # c < 128: the TMA im2col path pads each tap to 128 channels
+    (3, 9, 11, 32, 3, 40, 2, 1),       # ragged: 3*5*6 = 90 pixels in one tile, stride 2, odd sizes
+    (2, 17, 17, 128, 3, 96, 1, 2),     # dilation 2
+    (2, 12, 12, 192, 3, 272, 2, 1),    # c = 128 + 64: second k-block of a tap is half outside the tensor
+    (1, 7, 7, 256, 1, 64, 2, 1),       # strided 1x1 (projection shortcut)
+    (5, 20, 20, 16, 5, 24, 1, 1),      # 5x5, smallest channel run, several tiles per image row group
+])
+def test_lowerings_agree(case):
+    """The three ways the A operand is produced (patch matrix in scratch, cp.async gather inside the GEMM,
+    TMA im2col loads) give identical bytes, and those equal the oracle's."""
+    itex, K, ops = modules()
+    n, h, w, c, k, co, stride, dil = case
+    rng = np.random.default_rng(sum(case))
+    eff = (k - 1) * dil + 1
+    oh, ow = (h + stride - 1) // stride, (w + stride - 1) // stride
+    pad_h = max(0, (oh - 1) * stride + eff - h) // 2
+    x = rng.integers(0, 256, (n, h, w, c), dtype=np.uint8)
+    f = rng.integers(-127, 128, (k, k, c, co)).astype(np.int8)
+    scale = rng.uniform(2e-5, 6e-5, co).astype(np.float32)
+    bias = rng.standard_normal(co).astype(np.float32)
+    xd, fd, sd, bd = dev(x), dev(f), dev(scale), dev(bias)
+    im2col, c_pad, ws0 = _abi_conv(itex, xd, fd, sd, bd, stride, dil, pad_h, oh, ow, "preferred")
+    assert c_pad == (c + 127) // 128 * 128 and ws0 == 0
+    dense, _, ws1 = _abi_conv(itex, xd, fd, sd, bd, stride, dil, pad_h, oh, ow, c)
+    if c % 128 != 0:
+        assert ws1 == 0                      # cp.async gather: no scratch either
+    # explicit lowering: shift the problem to a channel count that is not a multiple of 16 by appending a zero channel
+    x1 = np.concatenate([x, np.zeros((n, h, w, 1), np.uint8)], axis=3)
+    f1 = np.concatenate([f, np.zeros((k, k, 1, co), np.int8)], axis=2)
+    explicit, _, ws2 = _abi_conv(itex, dev(x1), dev(f1), sd, bd, stride, dil, pad_h, oh, ow, c + 1)
+    assert ws2 > 0
+    # oracle: int32 accumulation, then scale, bias, relu, saturating round to uint8
+    xp = np.pad(x.astype(np.int32), ((0, 0), (pad_h, eff), (pad_h, eff), (0, 0)))
+    acc = np.zeros((n, oh, ow, co), np.int64)
+    for ky in range(k):
+        for kx in range(k):
+            patch = xp[:, ky * dil: ky * dil + (oh - 1) * stride + 1: stride, kx * dil: kx * dil + (ow - 1) * stride + 1: stride, :]
+            acc += np.tensordot(patch, f[ky, kx].astype(np.int64), axes=([3], [0]))
+    v = acc.astype(np.float32) * scale + bias
+    want = np.clip(np.rint(np.maximum(v, 0)), 0, 255).astype(np.uint8)
+    np.testing.assert_array_equal(im2col, want)
+    np.testing.assert_array_equal(dense, want)
+    np.testing.assert_array_equal(explicit, want)
