@@ -197,9 +197,35 @@ __device__ __forceinline__ uint32_t SatRneLowByte(float f, float lo, float hi) {
   f = fminf(fmaxf(f, lo), hi);
   return uint32_t(__float_as_int(__fadd_rn(f, kMagic)));
 }
+// Saturating round-to-nearest-even conversion to an 8-bit integer in the low byte (one
+// instruction on the conversion unit; the clamp-and-add form costs three on the main pipes).
+template <bool SIGNED> __device__ __forceinline__ uint32_t SatRne8(float f) {
+  uint32_t r;
+  if (SIGNED) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(f));
+  else asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(f));
+  return r;
+}
 // Low bytes of a, b, c, d -> one word (byte-permute unit: 3 instructions per 4 outputs).
 __device__ __forceinline__ uint32_t PackLowBytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// Packed fp32 pairs: one instruction rounds both lanes exactly like the scalar operation.
+__device__ __forceinline__ uint64_t Pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void Unpack2(uint64_t p, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p)); }
+__device__ __forceinline__ uint64_t Mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t Add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
 }
 
 __device__ __forceinline__ bool DtypeIs8(int dt) {
@@ -246,11 +272,10 @@ __device__ __forceinline__ void Convert16(const float (&v)[16], uint32_t (&w)[16
       w[j] = uint32_t(f >= 2147483648.f ? 2147483647 : (f <= -2147483648.f ? (-2147483647 - 1) : __float2int_rn(f)));
     }
   } else if (OK == kOutU8 || OK == kOutS8) {
-    constexpr float lo = OK == kOutS8 ? -128.f : 0.f, hi = OK == kOutS8 ? 127.f : 255.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
-      w[j] = PackLowBytes(SatRneLowByte(v[4 * j], lo, hi), SatRneLowByte(v[4 * j + 1], lo, hi), SatRneLowByte(v[4 * j + 2], lo, hi),
-                          SatRneLowByte(v[4 * j + 3], lo, hi));
+      w[j] = PackLowBytes(SatRne8<OK == kOutS8>(v[4 * j]), SatRne8<OK == kOutS8>(v[4 * j + 1]), SatRne8<OK == kOutS8>(v[4 * j + 2]),
+                          SatRne8<OK == kOutS8>(v[4 * j + 3]));
   } else if (OK == kOutFP8) {
     const __nv_fp8_interpretation_t kind = e4m3 ? __NV_E4M3 : __NV_E5M2;
 #pragma unroll
@@ -404,6 +429,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             LoadParams16(e.bias, col, g.n, e.vec_params, 0.f, bi);
             TmemLdWait16(r);
             float v[16];
+            bool shifted = false;  // v still carries the +1.5*2^23 of the adder trick
             if (F8) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
@@ -416,8 +442,9 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                 for (int j = 0; j < 16; ++j) big |= (r[j] + 0x400000u) & 0xff800000u;
               }
               if (big == 0) {
+                shifted = true;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = SmallIntToFloat(int(r[j]));
+                for (int j = 0; j < 16; ++j) v[j] = __int_as_float(int(r[j]) + kMagicBits);
               } else {
                 // volatile keeps the slow conversions inside this branch
 #pragma unroll
@@ -426,8 +453,20 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             }
             // separate multiply and add: the order and rounding of oneDNN's scale-then-bias tail.
             // A missing scale multiplies by 1 and a missing bias adds 0, both exact.
+            // Two columns per instruction for the un-shift and the multiply (packed fp32).
+            const uint64_t unshift = shifted ? Pack2(-kMagic, -kMagic) : Pack2(-0.f, -0.f);  // x + (-0) == x for every x
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(__fmul_rn(v[j], sc[j]), bi[j]);
+            for (int j = 0; j < 8; ++j) {
+              uint64_t p = Pack2(v[2 * j], v[2 * j + 1]);
+              if (!F8) p = Add2(p, unshift);
+              p = Mul2(p, Pack2(sc[2 * j], sc[2 * j + 1]));
+              Unpack2(p, v[2 * j], v[2 * j + 1]);
+              // The bias is added with scalar instructions: a packed multiply feeding a packed add is
+              // contracted into a packed fused multiply-add by the assembler even with .rn on both
+              // (measured: 25 % of results differ in the last bit), which would break bit-exactness.
+              v[2 * j] = __fadd_rn(v[2 * j], bi[2 * j]);
+              v[2 * j + 1] = __fadd_rn(v[2 * j + 1], bi[2 * j + 1]);
+            }
             if (g.ep.summand != nullptr && row_ok) {
               const long long sb = row * g.ep.ld_summand + col;
               if (e.sum_bytes_vec && col + 16 <= g.n) {
@@ -503,7 +542,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
       }
     }
     TcFenceBefore();
-    MbarArrive(SmemAddr(&tmem_empty_bar[acc]));
+    __syncwarp();
+    if (lane == 0) MbarArrive(SmemAddr(&tmem_empty_bar[acc]));  // one arrival per warp: all its lanes have read their rows
     acc ^= 1;
     if (acc == 0) acc_phase ^= 1;
   }
@@ -549,7 +589,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
     for (int a = 0; a < 2; ++a) {
       MbarInit(SmemAddr(&tmem_full_bar[a]), 1);
-      MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueThreads);
+      MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueWarps);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
