@@ -31,6 +31,10 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
+# DRAM bytes (read + write) of one GemmKernel launch, from the ncu captures summarised in
+# profiles/int8_gemm_quantize_matmul.md; null for shapes that were not captured.
+GEMM_DRAM_TRAFFIC = {"int8_gemm_8192": 574.4e6, "int8_gemm_4096": 56.4e6}
+
 WORKLOADS = {
     # name: (M per GPU, N, K)
     "int8_gemm_8192": (8192, 8192, 8192),
@@ -545,7 +549,8 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,int8> (tcgen05.mma kind::i8)", "achieved": gemm_tops,
                          "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
                          "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s); int8 MMA rate is twice bf16" % peaks["source"],
-                         "gemm_ms": gemm_ms, "traffic": None},
+                         "gemm_ms": gemm_ms, "traffic": GEMM_DRAM_TRAFFIC.get(args.workload),
+                         "algorithmic_bytes": m * k + n * k + m * n * 4},
             "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k * 4 * world,
                     "d2h_bytes_per_step": m * n * 4 * world, "checksum": checksum},
             "gpu_launches": int(launches), "clocks": sampler.summary(),
