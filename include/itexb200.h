@@ -175,6 +175,7 @@ ITEXB_API int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, in
  *   f = f + bias[n]                    (bias != NULL)
  *   f = f + sum_scale * float(summand[m][n])   (summand != NULL)
  *   f = max(f, 0)                      (relu)
+ *   f = activation(f) * post_scale     (activation != ITEXB_ACT_NONE; post_scale 0 means 1)
  *   f = float(mid_dtype(f))            (mid_dtype != 0)
  *   out = convert(f): QUINT8/QINT8/QINT32 saturate then round-to-nearest-even;
  *         FLOAT/BFLOAT16/HALF plain conversion; FP8_E4M3 saturating RNE of f*out_scale[0]
@@ -182,6 +183,23 @@ ITEXB_API int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, in
  * Separate fp32 multiply and add (no FMA), the order oneDNN's int8 primitives use for
  * "scale on DNNL_ARG_WEIGHTS, bias after" (itex/core/utils/onednn/onednn_post_op_util.cc:283-295).
  * raw_acc = 1 with out_dtype QINT32 stores the exact int32 accumulator instead.        */
+/* Element-wise post-ops of the fused matmul ops, named after the oneDNN algorithms the reference maps
+ * them to (itex/core/utils/onednn/onednn_post_op_util.cc:22-71): relu with negative slope act_alpha
+ * (Relu: 0, LeakyRelu), clip to [act_alpha, act_beta] (Relu6), gelu_erf, gelu_tanh, logistic, tanh,
+ * elu(act_alpha), swish(act_alpha), linear act_alpha*f + act_beta. */
+typedef enum itexb_activation {
+  ITEXB_ACT_NONE = 0,
+  ITEXB_ACT_RELU = 1,
+  ITEXB_ACT_CLIP = 2,
+  ITEXB_ACT_GELU_ERF = 3,
+  ITEXB_ACT_GELU_TANH = 4,
+  ITEXB_ACT_SIGMOID = 5,
+  ITEXB_ACT_TANH = 6,
+  ITEXB_ACT_ELU = 7,
+  ITEXB_ACT_SWISH = 8,
+  ITEXB_ACT_LINEAR = 9
+} itexb_activation_t;
+
 typedef struct itexb_epilogue {
   const float* scale;      /* device, scale_count entries */
   int32_t scale_count;     /* 0, 1 or n */
@@ -198,6 +216,9 @@ typedef struct itexb_epilogue {
   float* amax;             /* FP8 output only: device scalar, atomically maxed */
   int32_t mid_dtype;       /* 0, or BFLOAT16 | HALF: round f to that type before the final
                               conversion (FP8 output of a matmul whose sum type is 16-bit) */
+  int32_t activation;      /* itexb_activation_t, applied after summand and relu */
+  float act_alpha, act_beta;
+  float post_scale;        /* multiplies the activation's result; 0 is read as 1 */
 } itexb_epilogue_t;
 
 /* out[m][n] = epilogue( sum_k a[m][k] * b[n][k] ).
@@ -357,7 +378,11 @@ typedef struct itexb_op_context {
 ITEXB_API const char* const* itexb_op_list(void);
 /* Input names and which inputs/outputs are HostMemory for an op (the lists of
  * itex/core/kernels/gpu/quantize_op.cc:25-46, gpu/quantized_matmul.cc:53-102,
- * gpu/quantized_conv_ops.cc:72-140).  Bit i of the masks = argument i.             */
+ * gpu/quantized_conv_ops.cc:72-140).  Bit i of the masks = argument i.  The fused matmul ops
+ * (_QuantizedFusedMatMul*, _QuantizedMatMul) take list-typed arguments whose length depends on
+ * fused_ops: they report -1 counts and an input mask of 0, and every range tensor
+ * (min_*, max_*) must be in host memory - the HostMemoryList arguments of
+ * gpu/quantized_matmul.cc:137-182.                                                  */
 ITEXB_API int itexb_op_signature(const char* op_name, int* num_inputs, int* num_outputs,
                                  uint32_t* host_input_mask, uint32_t* host_output_mask);
 ITEXB_API int itexb_op_create(const char* op_name, const itexb_attr_t* attrs, int num_attrs, itexb_op_t** op);

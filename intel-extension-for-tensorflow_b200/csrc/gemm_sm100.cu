@@ -340,6 +340,41 @@ __device__ __forceinline__ void TmaStoreWaitRead(int pending) {
 __device__ __forceinline__ void TmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Element-wise post-op on 16 values, out of line so that the slice loop every launch executes stays
+// short.  The switch is on a launch-uniform value and sits outside the unrolled loops, so a launch
+// executes one short straight-line case.  The transcendental cases use the hardware exponential and reciprocal: a few ulp,
+// inside the 1e-5 the parity tests allow.
+#define ITEXB_ACT_CASE(KIND, EXPR)                                     \
+  case KIND:                                                           \
+    _Pragma("unroll") for (int j = 0; j < 16; ++j) {                   \
+      const float x = v[j];                                            \
+      v[j] = __fmul_rn((EXPR), post_scale);                            \
+    }                                                                  \
+    break;
+__device__ __forceinline__ float GeluTanh(float x) {
+  // 0.5 x (1 + tanh(u)) = x / (1 + exp(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3)
+  const float u = __fmul_rn(__fmul_rn(0.7978845608028654f, x), __fmaf_rn(0.044715f, __fmul_rn(x, x), 1.f));
+  return __fdividef(x, __fadd_rn(1.f, __expf(__fmul_rn(-2.f, u))));
+}
+struct Float16 { float v[16]; };
+__device__ __noinline__ Float16 ApplyActivation16(Float16 in, int kind, float alpha, float beta, float post_scale) {
+  float (&v)[16] = in.v;
+  switch (kind) {
+    ITEXB_ACT_CASE(ITEXB_ACT_RELU, x > 0.f ? x : __fmul_rn(x, alpha))
+    ITEXB_ACT_CASE(ITEXB_ACT_CLIP, fminf(fmaxf(x, alpha), beta))
+    ITEXB_ACT_CASE(ITEXB_ACT_GELU_ERF, __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.f, erff(__fmul_rn(x, 0.70710678118654752f)))))
+    ITEXB_ACT_CASE(ITEXB_ACT_GELU_TANH, GeluTanh(x))
+    ITEXB_ACT_CASE(ITEXB_ACT_SIGMOID, __fdividef(1.f, __fadd_rn(1.f, __expf(-x))))
+    ITEXB_ACT_CASE(ITEXB_ACT_TANH, tanhf(x))
+    ITEXB_ACT_CASE(ITEXB_ACT_ELU, x > 0.f ? x : __fmul_rn(alpha, expm1f(x)))
+    ITEXB_ACT_CASE(ITEXB_ACT_SWISH, __fdividef(x, __fadd_rn(1.f, __expf(__fmul_rn(-alpha, x)))))
+    ITEXB_ACT_CASE(ITEXB_ACT_LINEAR, __fadd_rn(__fmul_rn(alpha, x), beta))
+    default: break;
+  }
+  return in;
+}
+#undef ITEXB_ACT_CASE
+
 // What an epilogue warp needs to know; filled once per launch.
 struct EpilogueCtx {
   const float* scale;   // per-column scale vector or nullptr
@@ -351,6 +386,7 @@ struct EpilogueCtx {
   bool sum_bytes_vec;   // summand is 1-byte with 16-byte aligned rows: one 16-byte load per slice
   bool e4m3;            // FP8 output format
   float out_scale;      // FP8 output scale
+  float post_scale;     // multiplier after the activation
   uint8_t* stage;       // this warp's staging memory
 };
 
@@ -389,6 +425,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                     (reinterpret_cast<uintptr_t>(g.ep.summand) & 15) == 0;
   e.e4m3 = g.out_dtype == ITEXB_DT_FP8_E4M3;
   e.out_scale = g.ep.out_scale != nullptr ? __ldg(g.ep.out_scale) : 1.f;
+  e.post_scale = g.ep.post_scale == 0.f ? 1.f : g.ep.post_scale;
   e.stage = s_stage + (warp - 4) * kStagingPerWarp;
   const bool sum_signed = g.ep.summand_dtype == ITEXB_DT_QINT8 || g.ep.summand_dtype == ITEXB_DT_INT8;
   const int swz = (lane / (8 / row_units)) % row_units;  // this lane's XOR term of the staging swizzle
@@ -486,6 +523,14 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             if (e.relu) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            if (g.ep.activation != ITEXB_ACT_NONE) {
+              Float16 t;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t.v[j] = v[j];
+              t = ApplyActivation16(t, g.ep.activation, g.ep.act_alpha, g.ep.act_beta, e.post_scale);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = t.v[j];
             }
             if (g.ep.mid_dtype == ITEXB_DT_BFLOAT16) {
 #pragma unroll

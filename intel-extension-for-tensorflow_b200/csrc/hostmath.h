@@ -85,6 +85,20 @@ inline float MatMulOutputScale(float min_a, float max_a, float min_b0, float max
   return scale_int32 / scale_eightbit / static_cast<float>(1u << 24);
 }
 
+// QuantizedFusedMatMulOp::ExtendInt8PostOps / QuantizedFusedMatMulV2Op::ExtendInt8PostOps,
+// itex/core/kernels/common/quantized_matmul_common.h:1610-1650, 1817-1842: the dequantize scale of every
+// weight range, range_input * range_weight[i] / (max_int8_input * 127).
+inline void FusedMatMulOutputScales(float min_a, float max_a, const float* min_b, const float* max_b, size_t count, bool min_first,
+                                    int t1, std::vector<float>* scales) {
+  const float max_int8_input = MaxIntOf(t1), max_int8_weight = 127.0f;
+  const float range_input = min_first ? max_a - min_a : std::max(std::abs(min_a), std::abs(max_a));
+  scales->resize(count);
+  for (size_t i = 0; i < count; ++i) {
+    const float range_weight = std::max(std::abs(min_b[i]), std::abs(max_b[i]));
+    (*scales)[i] = (range_input * range_weight) / (max_int8_input * max_int8_weight);
+  }
+}
+
 // LegacyQuantizedConvOpBase::ExtendInt8PostOps, itex/core/kernels/common/quantized_conv_ops.h:329-395.
 inline void ConvOutputScales(float min_input, float max_input, const float* min_filter, const float* max_filter, size_t depth,
                              int tinput, int toutput, float min_freezed, float max_freezed, std::vector<float>* scales) {

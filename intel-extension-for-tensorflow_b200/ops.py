@@ -26,7 +26,7 @@ _NAME_TO_DT = {
 _TORCH_TO_DT = {torch.float32: L.DT_FLOAT, torch.bfloat16: L.DT_BFLOAT16, torch.float16: L.DT_HALF,
                 torch.int8: L.DT_QINT8, torch.uint8: L.DT_QUINT8, torch.int32: L.DT_QINT32}
 _TYPE_ATTRS = {"T", "T1", "T2", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype",
-               "in_dtype", "Tsummand"}
+               "in_dtype", "Tsummand", "Targs", "Tout", "U"}
 
 
 def as_dtype(v):
@@ -199,9 +199,10 @@ class Op:
             L.check(self.lib.itexb_op_compute(self._h, C.byref(ctx)))
         finally:
             self._temps = []  # torch's allocator is stream-ordered: safe to release after enqueue
-        outs = [self._outputs.get(i) for i in range(self.nout)]
+        nout = self.nout if self.nout >= 0 else (max(self._outputs) + 1 if self._outputs else 0)  # -1: decided per call
+        outs = [self._outputs.get(i) for i in range(nout)]
         outs = [o.reshape(()).item() if isinstance(o, np.ndarray) and o.ndim == 0 else o for o in outs]
-        return outs[0] if self.nout == 1 else tuple(outs)
+        return outs[0] if nout == 1 else tuple(outs)
 
 
 _op_cache = {}
@@ -287,6 +288,60 @@ def _ITEXQuantizedMatMulWithBiasAndDequantize(a, b, bias, min_a, max_a, min_b, m
     """-> out"""
     return _quantized_matmul(op_name, a, b, bias, min_a, max_a, min_b, max_b, (min_freezed_output, max_freezed_output),
                              _mm_attrs(bias, Toutput, transpose_a, transpose_b, input_quant_mode, is_weight_const, scaled_bias_mode))
+
+
+def _bias_attr(t):
+    return "qint32" if t.dtype == torch.int32 else _TORCH_TO_DT[t.dtype]
+
+
+def _QuantizedFusedMatMul(a, b, args, min_a, max_a, min_b, max_b, min_freezed_output=None, max_freezed_output=None,
+                          Toutput="qint32", fused_ops=(), transpose_a=False, transpose_b=False, input_quant_mode="SCALED",
+                          is_filter_const=True, is_bias_const=True, leakyrelu_alpha=0.2, scaled_bias_mode=None,
+                          postop_scale_mode=None, op_name=None):
+    """_[ITEX]QuantizedFusedMatMul / ...AndRequantize / ...AndDequantize (the op name follows from Toutput unless
+    given).  `args` = [bias] or [bias, addend] as fused_ops says.  -> (product, min_product, max_product) or product."""
+    tout = Toutput if isinstance(Toutput, str) else {L.DT_FLOAT: "float", L.DT_BFLOAT16: "bfloat16", L.DT_HALF: "half",
+                                                     L.DT_QINT8: "qint8", L.DT_QUINT8: "quint8", L.DT_QINT32: "qint32"}[as_dtype(Toutput)]
+    if op_name is None:
+        op_name = "_QuantizedFusedMatMul" + ("" if tout == "qint32" else ("AndRequantize" if tout in ("qint8", "quint8") else "AndDequantize"))
+    attrs = dict(T1=_TORCH_TO_DT[a.dtype], T2="qint8", Toutput=tout, num_args=len(args), transpose_a=bool(transpose_a),
+                 transpose_b=bool(transpose_b), input_quant_mode=input_quant_mode, is_filter_const=bool(is_filter_const),
+                 is_bias_const=bool(is_bias_const), leakyrelu_alpha=float(leakyrelu_alpha))
+    if len(args) > 0:
+        attrs["Targs"] = _bias_attr(args[0])
+    if len(fused_ops) > 0:
+        attrs["fused_ops"] = list(fused_ops)
+    if scaled_bias_mode is not None:
+        attrs["_scaled_bias_mode"] = scaled_bias_mode
+    if postop_scale_mode is not None:
+        attrs["_postop_scale_mode"] = postop_scale_mode
+    inputs = [a, b] + list(args) + [min_a, max_a, min_b, max_b]
+    if tout in ("qint8", "quint8"):
+        inputs += [min_freezed_output, max_freezed_output]
+    dtypes = {2: L.DT_QINT32} if len(args) > 0 and args[0].dtype == torch.int32 else None
+    return _cached(op_name, attrs)(*inputs, dtypes=dtypes)
+
+
+def _QuantizedMatMul(device_inputs, host_inputs, T1=None, T2="qint8", Tbias=None, Tout=None, Tdevice_outputs=None,
+                     fused_ops=(), transpose_a=False, transpose_b=False, input_quant_mode="SCALED", output_quant_mode="SCALED",
+                     is_weight_const=True, is_bias_const=True, leakyrelu_alpha=0.2, scaled_bias_mode=None,
+                     postop_scale_mode=None, op_name="_QuantizedMatMul"):
+    """_[ITEX]QuantizedMatMul (V2): device_inputs = [a, b, bias(, addend)], host_inputs = [min_a, max_a, min_b, max_b
+    (, min_out, max_out)].  -> tuple of the device outputs followed by the host outputs (one element for float outputs)."""
+    if Tout is None:
+        Tout = Tdevice_outputs[0] if Tdevice_outputs else "float"
+    attrs = dict(T1=T1 if T1 is not None else _TORCH_TO_DT[device_inputs[0].dtype], T2=T2, Tout=Tout,
+                 transpose_a=bool(transpose_a), transpose_b=bool(transpose_b), input_quant_mode=input_quant_mode,
+                 output_quant_mode=output_quant_mode, is_weight_const=bool(is_weight_const), is_bias_const=bool(is_bias_const),
+                 leakyrelu_alpha=float(leakyrelu_alpha), fused_ops=list(fused_ops))
+    if len(device_inputs) > 2:
+        attrs["Tbias"] = Tbias if Tbias is not None else _bias_attr(device_inputs[2])
+    if scaled_bias_mode is not None:
+        attrs["_scaled_bias_mode"] = scaled_bias_mode
+    if postop_scale_mode is not None:
+        attrs["_postop_scale_mode"] = postop_scale_mode
+    dtypes = {2: L.DT_QINT32} if len(device_inputs) > 2 and device_inputs[2].dtype == torch.int32 else None
+    return _cached(op_name, attrs)(*(list(device_inputs) + list(host_inputs)), dtypes=dtypes)
 
 
 def _ITEXQuantizedConv2DWithBiasAndReluAndRequantize(input, filter, bias, min_input, max_input, min_filter, max_filter,

@@ -251,15 +251,18 @@ def matmul_output_scale(min_a, max_a, min_b0, max_b0, toutput: str,
 
 
 def matmul_scaled_bias(bias, b_kn, min_a, max_a, min_b, max_b, mode: str, toutput: str,
-                       out_scale, tbias: str = "float", scaled_bias_mode: str = "literal"
-                       ) -> np.ndarray:
+                       out_scale, tbias: str = "float", scaled_bias_mode: str = "literal",
+                       t1: str = QUINT8) -> np.ndarray:
     """GetScaledBias: float bias quantized_matmul_common.h:466-660; qint32 bias :1153-1334.
 
     scaled_bias_mode selects how the SCALED-mode float bias is treated:
       "literal"  - bias * 255*127/(ri*rw)  (what the cited lines compute)
-      "intended" - bias unchanged (real units, what the primitive's y = scale*acc + b needs)
+      "intended" - the bias expressed in the units of the value it is added to (what the primitive's
+                   y = scale*acc + b needs): unchanged for float outputs, times the requantize factor for 8-bit
+                   outputs, times 255*127/(ri*rw) for qint32 outputs
     """
     n = b_kn.shape[1]
+    lim = f32(255.0) if t1 == QUINT8 else f32(127.0)   # max_int8_input, :509-510
     min_a, max_a = f32(min_a), f32(max_a)
     min_b = np.atleast_1d(np.asarray(min_b, np.float32))
     max_b = np.atleast_1d(np.asarray(max_b, np.float32))
@@ -269,7 +272,7 @@ def matmul_scaled_bias(bias, b_kn, min_a, max_a, min_b, max_b, mode: str, toutpu
         if np.size(out_scale) in (1, n) else None
     if tbias == QINT32:
         bf = np.asarray(bias).astype(np.int32).astype(np.float32)
-        s = (f32(ri) * rw / f32(255.0 * 127.0)).astype(np.float32)
+        s = (f32(ri) * rw / f32(lim * f32(127.0))).astype(np.float32)
         s = np.broadcast_to(s, (n,)) if s.size == 1 else s
         if mode == "MIN_FIRST":
             if toutput in ("float", "bfloat16", "half"):
@@ -279,11 +282,11 @@ def matmul_scaled_bias(bias, b_kn, min_a, max_a, min_b, max_b, mode: str, toutpu
             return bf
         return (bf * s).astype(np.float32)
     bias = _as_f32(bias)
-    s = (f32(255.0 * 127.0) / (f32(ri) * rw)).astype(np.float32)
+    s = (f32(lim * f32(127.0)) / (f32(ri) * rw)).astype(np.float32)
     s = np.broadcast_to(s, (n,)) if s.size == 1 else s
     if mode == "MIN_FIRST":
         colsum = b_kn.astype(np.int32).sum(axis=0, dtype=np.int32)
-        qmin = f32(f32(255.0) * min_a / ri)
+        qmin = f32(lim * min_a / ri)
         cs = colsum.astype(np.float32)  # `sum * q_min_input` promotes the int to float
         if toutput in ("float", "bfloat16", "half"):
             return (bias + (cs * qmin / s)).astype(np.float32)
@@ -291,7 +294,12 @@ def matmul_scaled_bias(bias, b_kn, min_a, max_a, min_b, max_b, mode: str, toutpu
             return (bias * s * os_ + (cs * qmin * os_)).astype(np.float32)
         return (bias * s + (cs * qmin)).astype(np.float32)
     if scaled_bias_mode == "intended":
-        return bias.astype(np.float32).copy()
+        # the bias in the units of the value it is added to, i.e. the MIN_FIRST formulas without compensation
+        if toutput in ("float", "bfloat16", "half"):
+            return bias.astype(np.float32).copy()
+        if toutput in (QUINT8, QINT8):
+            return (bias * s * os_).astype(np.float32)
+        return (bias * s).astype(np.float32)
     return (bias * s).astype(np.float32)
 
 
@@ -354,16 +362,121 @@ def quantized_matmul_with_bias(a, b, bias, min_a, max_a, min_b, max_b,
     return out, None, None
 
 
-def fused_matmul_output_scale(min_a, max_a, min_b, max_b, t1: str, n: int) -> np.ndarray:
+def fused_matmul_output_scale(min_a, max_a, min_b, max_b, t1: str, n: int, mode: str = "SCALED") -> np.ndarray:
     """Per-channel dequantize scale of QuantizedFusedMatMulOp / V2,
-    quantized_matmul_common.h:1610-1702, 1809-1908: ri*rw[j]/(max_int8_in*127)."""
+    quantized_matmul_common.h:1610-1650, 1817-1842: ri*rw[j]/(max_int8_in*127)."""
     min_a, max_a = f32(min_a), f32(max_a)
     lim = f32(255.0) if t1 == QUINT8 else f32(127.0)
-    ri = f32(max(abs(min_a), abs(max_a)))
+    ri = f32(max_a - min_a) if mode == "MIN_FIRST" else f32(max(abs(min_a), abs(max_a)))
     rw = np.maximum(np.abs(np.atleast_1d(np.asarray(min_b, np.float32))),
                     np.abs(np.atleast_1d(np.asarray(max_b, np.float32)))).astype(np.float32)
-    sc = (ri * rw / f32(lim * f32(127.0))).astype(np.float32)
+    sc = ((ri * rw).astype(np.float32) / f32(lim * f32(127.0))).astype(np.float32)
     return np.broadcast_to(sc, (n,)).copy() if sc.size == 1 else sc
+
+
+ACTIVATIONS = ("Relu", "LeakyRelu", "Relu6", "GeluExact", "GeluApproximate", "Sigmoid", "Tanh", "Elu", "_ITEXSwish")
+
+
+def activation(f: np.ndarray, name: str, leakyrelu_alpha: float = 0.2) -> np.ndarray:
+    """Element-wise post-ops by their fused_ops names, with the oneDNN algorithms and alpha/beta of
+    PostOpUtil::GetAllPostOpInfo (itex/core/utils/onednn/onednn_post_op_util.cc:22-71).  Evaluated in
+    float64 and rounded once to fp32 (oneDNN's own kernels use polynomial approximations; the GPU
+    tests compare at 1e-5)."""
+    x = f.astype(np.float64)
+    if name == "Relu":
+        y = np.maximum(x, 0.0)
+    elif name == "LeakyRelu":
+        y = np.where(x > 0, x, x * np.float64(f32(leakyrelu_alpha)))
+    elif name == "Relu6":
+        y = np.clip(x, 0.0, 6.0)
+    elif name == "GeluExact":
+        from math import erf
+        y = 0.5 * x * (1.0 + np.vectorize(erf)(x / np.sqrt(2.0)))
+    elif name == "GeluApproximate":
+        y = 0.5 * x * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (x + 0.044715 * x ** 3)))
+    elif name == "Sigmoid":
+        y = 1.0 / (1.0 + np.exp(-x))
+    elif name == "Tanh":
+        y = np.tanh(x)
+    elif name == "Elu":
+        y = np.where(x > 0, x, np.expm1(x))
+    elif name == "_ITEXSwish":
+        y = x / (1.0 + np.exp(-x))
+    else:
+        raise ValueError("Found unsupported fusion: " + name)
+    return y.astype(np.float32)
+
+
+def quantized_fused_matmul(a, b, bias, min_a, max_a, min_b, max_b, min_freezed_output=None, max_freezed_output=None, *,
+                           fused_ops=("BiasAdd",), t1: str = QUINT8, toutput: str = "float", tbias: str = "float",
+                           input_quant_mode: str = "SCALED", addend=None, transpose_a: bool = False,
+                           transpose_b: bool = False, leakyrelu_alpha: float = 0.2,
+                           scaled_bias_mode: str = "literal", postop_scale_mode: str = "intended"):
+    """_[ITEX]QuantizedFusedMatMul[AndRequantize|AndDequantize] and _[ITEX]QuantizedMatMul (V2):
+    QuantizedFusedMatMulOp / QuantizedFusedMatMulV2Op, quantized_matmul_common.h:1534-1908, over the
+    same base class as the WithBias ops (bias scaling :466-660, output ranges quantized_ops.h:142-203).
+
+    fused_ops: BiasAdd, then optionally "Add" (sum post-op, scale 1, float outputs only) and/or one
+    activation; "Dequantize"/"Requantize" entries (V2 spelling) are accepted and ignored - the output kind
+    is given by `toutput`.  postop_scale_mode: "intended" multiplies the activation's result by
+    max_int8_output/range_output when requantizing after an activation (what :1669-1700, 1866-1884 compute);
+    "literal" drops it, as oneDNN 3 eltwise post-ops take no scale (onednn_post_op_util.cc:255).
+    Returns (out, min_out, max_out) like quantized_matmul_with_bias."""
+    a = np.asarray(a)
+    b = np.asarray(b)
+    a_mk = a.T if transpose_a else a
+    b_kn = b.T if transpose_b else b
+    n = b_kn.shape[1]
+    acts = [f for f in fused_ops if f in ACTIVATIONS]
+    if len(acts) > 1:
+        raise ValueError("more than one activation in fused_ops")
+    act = acts[0] if acts else None
+    has_bias = "BiasAdd" in fused_ops
+    has_add = "Add" in fused_ops
+    if has_add and toutput not in ("float", "bfloat16", "half"):
+        raise NotImplementedError("Quantized addend tensor is not implemented yet.")
+    acc = int_matmul(a_mk, b_kn)
+    scale, post = None, f32(1.0)
+    if toutput != QINT32:
+        scale = fused_matmul_output_scale(min_a, max_a, min_b, max_b, t1, np.size(min_b), input_quant_mode)
+        if toutput in (QUINT8, QINT8):
+            ro = f32(max(abs(f32(min_freezed_output)), abs(f32(max_freezed_output))))
+            factor = f32((f32(255.0) if toutput == QUINT8 else f32(127.0)) / ro)
+            if act is None:
+                scale = (scale * factor).astype(np.float32)
+            elif postop_scale_mode == "intended":
+                post = factor
+    bias_s = None
+    if has_bias:
+        bias_s = matmul_scaled_bias(bias, b_kn, min_a, max_a, min_b, max_b, input_quant_mode, toutput, scale, tbias,
+                                    scaled_bias_mode, t1)
+    f = acc.astype(np.float32)
+    if scale is not None:
+        f = (f * (scale if scale.size > 1 else scale[0])).astype(np.float32)
+    if bias_s is not None:
+        f = (f + bias_s).astype(np.float32)
+    if has_add:
+        f = (f + np.asarray(addend).astype(np.float32)).astype(np.float32)
+    if act is not None:
+        f = (activation(f, act, leakyrelu_alpha) * post).astype(np.float32)
+    if toutput == "float":
+        out = f
+    elif toutput == "bfloat16":
+        out = to_bf16_rne(f)
+    elif toutput == "half":
+        out = f.astype(np.float16)
+    else:
+        out = sat_rne(f, toutput)
+    if toutput in (QUINT8, QINT8):
+        return out, f32(min_freezed_output), f32(max_freezed_output)
+    if toutput == QINT32:
+        mbv = np.atleast_1d(np.asarray(min_b, np.float32))
+        xbv = np.atleast_1d(np.asarray(max_b, np.float32))
+        r = [quantization_range_for_multiplication(min_a, max_a, mbv[i], xbv[i], t1) for i in range(mbv.size)]
+        if np.ndim(min_b) == 0:
+            return out, r[0][0], r[0][1]
+        return out, np.array([x[0] for x in r], np.float32), np.array([x[1] for x in r], np.float32)
+    return out, None, None
 
 
 # --------------------------------------------------------------------------

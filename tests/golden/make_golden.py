@@ -82,6 +82,20 @@ def write_reference_kat():
             "y_quant": {"T": "qint8", "mode": "SCALED", "round_mode": "HALF_TO_EVEN"},
             "input_quant_mode": "MIN_FIRST", "rtol": 0.2, "atol": 0.2,
         },
+        "fused_matmul_min_first": {  # kernel_tests/native_quantized_fused_matmul_test.py:46-203 (fp32 math at rtol=atol=0.2)
+            "x_f32": [[1.51, 1.13, -0.66], [0.79, 0.98, 1.88]],
+            "y_f32": [[-1.71, 3.05, 2.05, 0.64], [0.73, 0.23, 1.42, 3.57], [-0.61, 2.24, 2.69, 2.90]],
+            "bias_f32": [-1.42, 2.05, -1.00, 0.94],
+            "z_f32": [[0.92, 1.43, 1.84, -1.01], [-1.83, -1.39, -0.50, 0.32]],  # the test feeds z + z as the addend
+            "x_quant": {"T": "quint8", "mode": "MIN_FIRST"},
+            "y_quant": {"T": "qint8", "mode": "SCALED", "round_mode": "HALF_TO_EVEN", "narrow_range": True},
+            "cases": [
+                {"fused_ops": ["BiasAdd", "GeluApproximate"], "per_channel": False},
+                {"fused_ops": ["BiasAdd", "GeluApproximate"], "per_channel": True},
+                {"fused_ops": ["BiasAdd", "Add"], "per_channel": False},
+            ],
+            "input_quant_mode": "MIN_FIRST", "Toutput": "float", "rtol": 0.2, "atol": 0.2,
+        },
     }
     with open(os.path.join(HERE, "reference_kat.json"), "w") as f:
         json.dump(kat, f, indent=1)

@@ -192,3 +192,56 @@ def test_fp8_cast_and_delayed_scaling():
     np.testing.assert_array_equal(sf, [64.0, 1.0, 0.25])
     np.testing.assert_array_equal(sfi, [1 / 64.0, 1.0, 4.0])
     assert (nh[0] == 0).all() and (nh[15] == hist[0]).all()
+
+
+def test_fused_matmul_reference_cases(kat):
+    """native_quantized_fused_matmul_test.py: _QuantizedFusedMatMulAndDequantize / _QuantizedMatMul with
+    BiasAdd + GeluApproximate (per-tensor and per-channel weights) and BiasAdd + Add, vs fp32 math at 0.2."""
+    k = kat["fused_matmul_min_first"]
+    x = np.array(k["x_f32"], np.float32)
+    y = np.array(k["y_f32"], np.float32)
+    b = np.array(k["bias_f32"], np.float32)
+    z = np.array(k["z_f32"], np.float32) * 2
+    qx, xmin, xmax = o.quantize_v2(x, x.min(), x.max(), T="quint8", mode="MIN_FIRST", round_mode="HALF_AWAY_FROM_ZERO")
+    tol = dict(rtol=k["rtol"], atol=k["atol"])
+    for case in k["cases"]:
+        if case["per_channel"]:
+            qy, ymin, ymax = o.quantize_v2(y, y.min(axis=0), y.max(axis=0), T="qint8", mode="SCALED", narrow_range=True, axis=1)
+        else:
+            qy, ymin, ymax = o.quantize_v2(y, y.min(), y.max(), T="qint8", mode="SCALED", narrow_range=True)
+        f = x @ y + b
+        if "Add" in case["fused_ops"]:
+            want = f + z
+        else:
+            want = o.activation(f, "GeluApproximate")
+        out, _, _ = o.quantized_fused_matmul(qx, qy, b, xmin, xmax, ymin, ymax, fused_ops=case["fused_ops"], t1="quint8",
+                                             toutput="float", input_quant_mode="MIN_FIRST", addend=z)
+        np.testing.assert_allclose(out, want, **tol)
+        # V2 spelling of the same fusion
+        out2, _, _ = o.quantized_fused_matmul(qx, qy, b, xmin, xmax, ymin, ymax, fused_ops=case["fused_ops"] + ["Dequantize"],
+                                              t1="quint8", toutput="float", input_quant_mode="MIN_FIRST", addend=z)
+        np.testing.assert_array_equal(out, out2)
+
+
+def test_fused_matmul_scale_rules():
+    """Requantize folds 255|127 / range into the per-channel scale when no activation follows, and into the
+    activation's post scale otherwise (quantized_matmul_common.h:1651-1700); s8 activations use 127 (H3)."""
+    rng = np.random.default_rng(7)
+    a = rng.integers(-127, 128, (5, 32)).astype(np.int8)
+    w = rng.integers(-127, 128, (32, 6)).astype(np.int8)
+    bias = rng.standard_normal(6).astype(np.float32)
+    mnb, mxb = -np.linspace(0.5, 1.5, 6).astype(np.float32), np.linspace(0.5, 1.5, 6).astype(np.float32)
+    sc = o.fused_matmul_output_scale(-2.0, 2.0, mnb, mxb, "qint8", 6)
+    np.testing.assert_allclose(sc, 2.0 * mxb / (127.0 * 127.0), rtol=1e-6)
+    deq, _, _ = o.quantized_fused_matmul(a, w, bias, -2.0, 2.0, mnb, mxb, fused_ops=["BiasAdd"], t1="qint8", toutput="float",
+                                         scaled_bias_mode="intended")
+    np.testing.assert_allclose(deq, (a.astype(np.int64) @ w.astype(np.int64)) * sc + bias, rtol=1e-5, atol=1e-5)
+    q, mn, mx = o.quantized_fused_matmul(a, w, bias, -2.0, 2.0, mnb, mxb, -40.0, 40.0, fused_ops=["BiasAdd"], t1="qint8",
+                                         toutput="qint8", scaled_bias_mode="intended")
+    np.testing.assert_allclose(q, np.clip(np.rint(deq * (127.0 / 40.0)), -128, 127), atol=1)
+    qr, _, _ = o.quantized_fused_matmul(a, w, bias, -2.0, 2.0, mnb, mxb, 0.0, 40.0, fused_ops=["BiasAdd", "Relu"], t1="qint8",
+                                        toutput="quint8", scaled_bias_mode="intended")
+    np.testing.assert_allclose(qr, np.clip(np.rint(np.maximum(deq, 0) * (255.0 / 40.0)), 0, 255), atol=1)
+    lit, _, _ = o.quantized_fused_matmul(a, w, bias, -2.0, 2.0, mnb, mxb, 0.0, 40.0, fused_ops=["BiasAdd", "Relu"], t1="qint8",
+                                         toutput="quint8", scaled_bias_mode="intended", postop_scale_mode="literal")
+    np.testing.assert_array_equal(lit, np.clip(np.rint(np.maximum(deq, 0)), 0, 255).astype(np.uint8))
