@@ -271,6 +271,104 @@ def run_resnet50(args, rank, world, local, dev, K):
         print(json.dumps(line), flush=True)
 
 
+def run_bert(args, rank, world, local, dev, K):
+    """INT8 BERT-large-shaped encoder forward (24 layers, hidden 1024, 16 heads, FFN 4096) on 32 x 384 = 12288
+    tokens per GPU (batch-sharded replicas, no collective): tokens/s.  A step is one forward pass replayed as a
+    CUDA graph.  The int8 nodes (dynamic-range quantize + fused int8 matmul) are also timed alone."""
+    import torch
+    bert = importlib.import_module("itex_b200.bert_int8")
+    batch, seq = 32, 384
+    tokens = batch * seq
+    enc = bert.BertInt8Encoder(device=dev, seed=1238)      # same weights on every rank
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(shard_seed(1238, rank))
+    x = torch.randn((tokens, enc.hidden), generator=gen, device=dev).to(torch.bfloat16)
+    ctx = torch.randn((tokens, enc.hidden), generator=gen, device=dev).to(torch.bfloat16)
+    mid = torch.randn((tokens, enc.ffn), generator=gen, device=dev).to(torch.bfloat16)
+    graph, y = enc.capture(enc.forward, x, batch, seq)
+    graph8, _ = enc.capture(enc.forward_int8_only, x, ctx, mid)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_warm, n_warm = time.perf_counter(), 0
+    while n_warm < args.warmup or time.perf_counter() - t_warm < args.min_warmup_seconds:
+        graph.replay()
+        n_warm += 1
+        if n_warm % 5 == 0:
+            torch.cuda.synchronize()
+    barrier()
+    launches0 = K.launch_count()
+    enc.forward(x, batch, seq)                             # eager pass: counts this library's launches per step
+    torch.cuda.synchronize()
+    launches_per_step = K.launch_count() - launches0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1), world, dev) / args.steps
+    i0, i1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(2):
+        graph8.replay()
+    barrier()
+    i0.record()
+    for _ in range(args.steps):
+        graph8.replay()
+    i1.record()
+    barrier()
+    sampler.stop_flag.set()
+    sampler.join()
+    int8_ms = max_over_ranks(i0.elapsed_time(i1), world, dev) / args.steps
+    # end to end: pinned host embeddings in, hidden states out, every step
+    x_host = torch.empty((tokens, enc.hidden), dtype=torch.bfloat16, pin_memory=True)
+    x_host.copy_(x.cpu())
+    out_host = torch.empty((tokens, enc.hidden), dtype=torch.bfloat16, pin_memory=True)
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        graph.replay()
+        out_host.copy_(y, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world, dev) / args.e2e_steps
+    if rank == 0:
+        peaks = measured_peaks()
+        ops_step = enc.int8_ops_per_token() * tokens
+        tops = ops_step / (int8_ms * 1e-3) / 1e12
+        line = {
+            "metric": "bert_large_int8_tokens_per_s", "value": tokens * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "s8xs8->s32", "data": "synthetic",
+            "config": {"workload": "bert_large_int8", "tokens_per_gpu": tokens, "batch": batch, "seq_len": seq, "layers": enc.layers,
+                       "hidden": enc.hidden, "heads": enc.heads, "ffn": enc.ffn,
+                       "graph": "per layer 4 x (min/max, quantize, scale, int8 matmul) + bf16 attention, LayerNorm, residuals in PyTorch; CUDA graph",
+                       "int8_path_ms": int8_ms, "int8_tops_per_forward": ops_step / 1e12, "l2": "activations larger than L2",
+                       "parallelism": "batch-sharded x%d, no collective" % world},
+            "roofline": {"bound": "tensor", "kernel": "int8 nodes of the forward pass (GemmKernel int8 + quantize passes)", "achieved": tops,
+                         "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tops / (2.0 * peaks["bf16_tflops"]), "traffic": None,
+                         "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s)" % peaks["source"]},
+            "e2e": {"value": tokens * world / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": tokens * enc.hidden * 2 * world, "d2h_bytes_per_step": tokens * enc.hidden * 2 * world,
+                    "checksum": float(out_host.double().sum())},
+            "gpu_launches": int(launches_per_step * args.steps), "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+
+
 FP8_LINEARS = ((4096, 4096), (4096, 14336), (14336, 4096))  # (K, N) of the Llama-3-8B-shaped linears, M = 4096 tokens
 
 
@@ -410,7 +508,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears"])
+    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears", "bert_large_int8"])
     ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -445,6 +543,11 @@ def main():
     dev = torch.device("cuda", local)
     if args.workload == "fp8_llama_linears":
         run_fp8_linears(args, rank, world, local, dev, K)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "bert_large_int8":
+        run_bert(args, rank, world, local, dev, K)
         if world > 1:
             dist.destroy_process_group()
         return

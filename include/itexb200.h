@@ -160,6 +160,15 @@ ITEXB_API int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_
                                      const float* minmax, float ensure_minimum_range, float* out3,
                                      itexb_stream_t stream);
 
+/* Per-output-channel scale of the fused matmul ops, computed on the device from a device-resident
+ * activation range: scales[j] = (max(|out_min|,|out_max|) * weight_range[j]) / (max_int8(a_dtype) * 127),
+ * range3 = the {scale, out_min, out_max} itexb_quantize_dynamic wrote, weight_range[j] =
+ * max(|min_b[j]|, |max_b[j]|).  The formula of QuantizedFusedMatMulOp::ExtendInt8PostOps
+ * (itex/core/kernels/common/quantized_matmul_common.h:1627-1650); there it runs on the host after a
+ * blocking copy of the range (HostDataCache, kernels/common/host_data_cache.h:36-97). */
+ITEXB_API int itexb_matmul_scales_dynamic(const float* range3, const float* weight_range, int32_t n, int a_dtype,
+                                          float* scales, itexb_stream_t stream);
+
 /* Weight pre-pack: [k,n] row-major (the TF layout of `b`) -> [n,k_pad] row-major with k
  * padded by zeros to a multiple of 16, the K-major layout the MMA kernel stages with TMA.
  * Plays the role of the cached weight reorder of

@@ -15,6 +15,9 @@ MAX_DIMS = 8
 DT_FLOAT, DT_INT32, DT_UINT8, DT_INT8 = 1, 3, 4, 6
 DT_QINT8, DT_QUINT8, DT_QINT32, DT_BFLOAT16, DT_HALF = 11, 12, 13, 14, 19
 DT_FP8_E4M3, DT_FP8_E5M2 = 101, 102
+# itexb_activation_t
+(ACT_NONE, ACT_RELU, ACT_CLIP, ACT_GELU_ERF, ACT_GELU_TANH, ACT_SIGMOID, ACT_TANH, ACT_ELU, ACT_SWISH,
+ ACT_LINEAR) = range(10)
 
 # itexb_status_t
 OK, INVALID_ARGUMENT, NOT_FOUND, RESOURCE_EXHAUSTED = 0, 3, 5, 8

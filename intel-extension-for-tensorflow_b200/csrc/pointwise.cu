@@ -419,6 +419,16 @@ __global__ void __launch_bounds__(kThreads) QuantizeDynamicKernel(const TX* __re
   }
 }
 
+// scales[j] = (range_input * range_weight[j]) / (max_int8_input * 127): the per-channel output scale of the
+// fused matmul ops with the activation range read on the device (range3 = what QuantizeDynamicKernel wrote).
+__global__ void MatMulScalesDynamicKernel(const float* __restrict__ range3, const float* __restrict__ weight_range, int n,
+                                          float max_int8_input, float* __restrict__ scales) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const float range_input = fmaxf(fabsf(range3[1]), fabsf(range3[2]));
+  scales[j] = __fdiv_rn(__fmul_rn(range_input, weight_range[j]), __fmul_rn(max_int8_input, 127.f));
+}
+
 // ---- FP8 ----------------------------------------------------------------------------
 template <bool E4M3> __device__ __forceinline__ uint8_t FloatToFp8Sat(float f) {
   return (uint8_t)__nv_cvt_float_to_fp8(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
@@ -658,6 +668,15 @@ int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_dtype, int
     return SetError(ITEXB_INVALID_ARGUMENT, "quantize_dynamic: input type %s is not float/bfloat16", DtypeName(x_dtype));
   }
   return CheckLaunch("QuantizeDynamicKernel");
+}
+
+int itexb_matmul_scales_dynamic(const float* range3, const float* weight_range, int32_t n, int a_dtype, float* scales,
+                                itexb_stream_t stream) {
+  ITEXB_REQUIRE(range3 != nullptr && weight_range != nullptr && scales != nullptr && n > 0, ITEXB_INVALID_ARGUMENT,
+                "matmul_scales_dynamic: bad arguments");
+  ITEXB_REQUIRE(IsInt8(a_dtype), ITEXB_INVALID_ARGUMENT, "matmul_scales_dynamic: activation type %s is not 8-bit", DtypeName(a_dtype));
+  MatMulScalesDynamicKernel<<<(n + 127) / 128, 128, 0, AsCuda(stream)>>>(range3, weight_range, n, IsSigned8(a_dtype) ? 127.f : 255.f, scales);
+  return CheckLaunch("MatMulScalesDynamicKernel");
 }
 
 int itexb_pack_weights_kn(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad, itexb_stream_t stream) {

@@ -78,7 +78,8 @@ def pack_weights_kn(b_kn, k_pad=None):
 
 
 def make_epilogue(scale=None, bias=None, relu=False, raw_acc=False, summand=None, sum_scale=1.0,
-                  alpha_a=None, alpha_b=None, out_scale=None, amax=None, summand_dtype=None):
+                  alpha_a=None, alpha_b=None, out_scale=None, amax=None, summand_dtype=None,
+                  activation=0, act_alpha=0.0, act_beta=0.0, post_scale=0.0):
     ep = L.Epilogue()
     keep = [scale, bias, summand, alpha_a, alpha_b, out_scale, amax]
     if scale is not None:
@@ -93,6 +94,7 @@ def make_epilogue(scale=None, bias=None, relu=False, raw_acc=False, summand=None
     ep.sum_scale = float(sum_scale)
     ep.relu = int(bool(relu))
     ep.raw_acc = int(bool(raw_acc))
+    ep.activation, ep.act_alpha, ep.act_beta, ep.post_scale = int(activation), float(act_alpha), float(act_beta), float(post_scale)
     for name, t in (("alpha_a", alpha_a), ("alpha_b", alpha_b), ("out_scale", out_scale), ("amax", amax)):
         if t is not None:
             setattr(ep, name, t.data_ptr())
@@ -168,6 +170,15 @@ def quantize_dynamic(x, q_dtype, mm, ensure_minimum_range=0.01):
     L.check(L.load().itexb_quantize_dynamic(_ptr(x), dt_of(x), _ptr(q), q_dtype, C.c_int64(x.numel()), _ptr(mm),
                                             C.c_float(ensure_minimum_range), _ptr(out3), stream_ptr()))
     return q, out3
+
+
+def matmul_scales_dynamic(range3, weight_range, a_dtype, out=None):
+    """Per-channel output scales from a device-resident activation range (see itexb_matmul_scales_dynamic)."""
+    _require_cuda(range3, weight_range, out)
+    n = weight_range.numel()
+    sc = out if out is not None else torch.empty(n, dtype=torch.float32, device=weight_range.device)
+    L.check(L.load().itexb_matmul_scales_dynamic(_ptr(range3), _ptr(weight_range), n, a_dtype, _ptr(sc), stream_ptr()))
+    return sc
 
 
 def launch_count() -> int:
