@@ -668,6 +668,25 @@ def main():
     e2e_value = whole_job_tops(m, n, k, world, e2e_ms)
     checksum = float(out_host[::997, ::991].double().sum())
 
+    # cuBLAS int8 -> int32 on the same shape (no epilogue): a library ceiling to read the fraction against
+    lib_tops = None
+    if rank == 0:
+        try:
+            a8 = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+            b8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev).t()
+            best = float("inf")
+            for i in range(13):
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record()
+                torch._int_mm(a8, b8)
+                c1.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    best = min(best, c0.elapsed_time(c1))
+            lib_tops = 2.0 * m * n * k / (best * 1e-3) / 1e12
+            del a8, b8
+        except Exception:  # noqa: BLE001 - the figure is informative only
+            lib_tops = None
     if rank == 0:
         peaks = measured_peaks()
         gemm_tops = 2.0 * m * n * k / (gemm_ms * 1e-3) / 1e12
@@ -684,7 +703,8 @@ def main():
                          "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
                          "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s); int8 MMA rate is twice bf16" % peaks["source"],
                          "gemm_ms": gemm_ms, "traffic": GEMM_DRAM_TRAFFIC.get(args.workload),
-                         "algorithmic_bytes": m * k + n * k + m * n * 4},
+                         "algorithmic_bytes": m * k + n * k + m * n * 4,
+                         "library_int_mm_tops": lib_tops, "frac_of_library": None if not lib_tops else gemm_tops / lib_tops},
             "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k * 4 * world,
                     "d2h_bytes_per_step": m * n * 4 * world, "checksum": checksum},
             "gpu_launches": int(launches), "clocks": sampler.summary(),
