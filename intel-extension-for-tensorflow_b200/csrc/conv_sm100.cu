@@ -86,7 +86,7 @@ template <int KH, int KW, int C, int TP>
 __global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a) {
   constexpr int kRun = KW * C;                         // bytes of one filter row
   constexpr int kRowPitch = (KH * kRun + 15) / 16 * 16;  // patch-matrix pitch
-  extern __shared__ uint8_t s_in[];                    // [KH][span * C]
+  extern __shared__ __align__(16) uint8_t s_in[];      // [KH][span * C], then the staged patch rows
   const int tiles_x = (a.ow + TP - 1) / TP;
   const int tile = blockIdx.x % tiles_x;
   const int oy = (blockIdx.x / tiles_x) % a.oh;
@@ -104,10 +104,13 @@ __global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a) {
     s_in[i] = v;
   }
   __syncthreads();
-  const int ox = ox0 + threadIdx.x;
-  if (ox >= a.ow) return;
+  // Each thread assembles the patch row of one pixel into the shared staging tile; the block then
+  // writes the tile - TP consecutive patch rows are one contiguous run of the patch matrix - with
+  // consecutive threads on consecutive 16-byte units, so that every store instruction fills whole
+  // sectors (a thread storing its own row would write 16 bytes every kRowPitch bytes).
+  uint4* s_out = reinterpret_cast<uint4*>(s_in + ((KH * row_bytes + 15) / 16) * 16);
   const uint8_t* base = s_in + threadIdx.x * a.stride_w * C;
-  uint4* dst = reinterpret_cast<uint4*>(a.ws + (((long long)b * a.oh + oy) * a.ow + ox) * kRowPitch);
+  uint4* dst = s_out + threadIdx.x * (kRowPitch / 16);
 #pragma unroll
   for (int u = 0; u < kRowPitch / 16; ++u) {
     uint32_t w[4];
@@ -125,6 +128,10 @@ __global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a) {
     }
     dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
   }
+  __syncthreads();
+  const int pixels = min(TP, a.ow - ox0);
+  uint4* out = reinterpret_cast<uint4*>(a.ws + (((long long)b * a.oh + oy) * a.ow + ox0) * kRowPitch);
+  for (int i = threadIdx.x; i < pixels * (kRowPitch / 16); i += TP) out[i] = s_out[i];
 }
 
 bool IsPointwise(const itexb_conv_params_t& p) {
@@ -215,7 +222,7 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
     } else if (p->kh == 7 && p->kw == 7 && p->c == 3 && p->dil_h == 1 && p->dil_w == 1 && p->stride_w <= 4) {
       constexpr int kTP = 64;
       const int tiles_x = (p->ow + kTP - 1) / kTP;
-      const size_t smem = size_t(7) * ((kTP - 1) * p->stride_w + 7) * 3;
+      const size_t smem = (size_t(7) * ((kTP - 1) * p->stride_w + 7) * 3 + 15) / 16 * 16 + size_t(kTP) * 160;  // input window + staged patch rows
       GatherPatchesStemKernel<7, 7, 3, kTP><<<unsigned(p->n) * p->oh * tiles_x, kTP, smem, st>>>(a);
     } else {
       GatherPatchesRowKernel<<<blocks, 256, 0, st>>>(a);

@@ -50,7 +50,7 @@ constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kGroupM = 16;       // tile rasterisation: m-tiles per L2 super-group
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 
-enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3 };
+enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrSmemAlign = 4 };
 
 template <int BN> struct Cfg {
   static constexpr int kABytes = kBM * kBK;
@@ -58,9 +58,12 @@ template <int BN> struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128), 8 (64)
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two >= 32
-  static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kBarrierBytes = (2 * kStages + 6) * 8 + 16;
+  static constexpr int kParamBytes = 2 * BN * 4;               // the tile's per-column scales and biases
   static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
+  // No slack for aligning the base: dynamic shared memory is declared 1024-byte aligned and the kernel checks it.
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kParamBytes + kBarrierBytes;
+  static_assert(kSmemBytes <= 232448, "over the 227 KB a block may have");
 };
 
 // ---------------------------------------------------------------------------------------
@@ -272,6 +275,8 @@ __device__ __forceinline__ void Convert16(const float (&v)[16], uint32_t (&w)[16
       w[j] = uint32_t(f >= 2147483648.f ? 2147483647 : (f <= -2147483648.f ? (-2147483647 - 1) : __float2int_rn(f)));
     }
   } else if (OK == kOutU8 || OK == kOutS8) {
+    // One saturating conversion instruction per element.  Sending half of them through the main pipes instead
+    // (clamp, clamp, magic add) to relieve the conversion unit was measured slower: issue slots, not that unit, limit.
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       w[j] = PackLowBytes(SatRne8<OK == kOutS8>(v[4 * j]), SatRne8<OK == kOutS8>(v[4 * j + 1]), SatRne8<OK == kOutS8>(v[4 * j + 2]),
@@ -288,22 +293,13 @@ __device__ __forceinline__ void Convert16(const float (&v)[16], uint32_t (&w)[16
   }
 }
 
-// 16 per-column parameters starting at column `col`: four 16-byte loads of an address all lanes
-// share (one broadcast transaction each, served by L1) when the vector is aligned and the slice
-// is complete, guarded element loads otherwise.
-__device__ __forceinline__ void LoadParams16(const float* __restrict__ p, int col, int n, bool vec, float fill, float (&out)[16]) {
-  if (p == nullptr) {
+// 16 per-column parameters from the tile's staged copy in shared memory (all lanes read the same
+// address: broadcast, no bank conflict).
+__device__ __forceinline__ void LoadStaged16(const float* __restrict__ p, float (&out)[16]) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) out[j] = fill;
-  } else if (vec && col + 16 <= n) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 t = __ldg(reinterpret_cast<const float4*>(p + col) + i);
-      out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) out[j] = col + j < n ? __ldg(p + col + j) : fill;
+  for (int i = 0; i < 4; ++i) {
+    const float4 t = reinterpret_cast<const float4*>(p)[i];
+    out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w;
   }
 }
 
@@ -380,7 +376,6 @@ struct EpilogueCtx {
   const float* scale;   // per-column scale vector or nullptr
   const float* bias;    // per-column bias vector or nullptr
   float scalar_scale;   // used when scale == nullptr (1 when there is no scale at all)
-  bool vec_params;      // scale / bias vectors are 16-byte aligned
   bool acc_small;       // |accumulator| <= 2^22 follows from k alone
   bool relu;            // apply max(f, 0) (skipped when an unsigned clamp does it anyway)
   bool sum_bytes_vec;   // summand is 1-byte with 16-byte aligned rows: one 16-byte load per slice
@@ -397,9 +392,10 @@ struct EpilogueCtx {
 // writes; edges are clipped by the tensor map.  Without TMA-legal output rows the slices go
 // straight to global memory.
 template <int BN, bool F8, int OK>
-__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, uint8_t* s_stage, uint64_t* tmem_full_bar,
-                                             uint64_t* tmem_empty_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane,
-                                             int tiles_m, int tiles_n, int num_tiles) {
+__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, uint8_t* s_stage, float* s_par,
+                                             uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint64_t* par_bar,
+                                             volatile int* abort_flag, uint32_t tmem_base, int warp, int lane, int tiles_m,
+                                             int tiles_n, int num_tiles) {
   constexpr int esz = OutBytes<OK>::v;
   constexpr int units = esz;                          // 16-byte units per 16-column slice
   constexpr int bcols = esz == 4 ? 16 : 32;           // columns per block
@@ -418,7 +414,6 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   else if (g.ep.scale_count == 1) e.scalar_scale = __ldg(g.ep.scale);
   else if (g.ep.scale_count > 1) e.scale = g.ep.scale;
   e.bias = g.ep.bias;
-  e.vec_params = ((reinterpret_cast<uintptr_t>(e.scale) | reinterpret_cast<uintptr_t>(e.bias)) & 15) == 0;
   e.acc_small = !F8 && (long long)g.k * 255 * 128 < (1ll << 22);
   e.relu = g.ep.relu && !(g.ep.mid_dtype == 0 && OK == kOutU8);  // max(f, 0) is implied by the clamp to [0, 255]
   e.sum_bytes_vec = g.ep.summand != nullptr && DtypeIs8(g.ep.summand_dtype) && g.ep.ld_summand % 16 == 0 &&
@@ -432,10 +427,38 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   int acc = 0;
   uint32_t acc_phase = 0, seq = 0;
   float thread_amax = 0.f;
+  // Per-column scale and bias of the current tile column live in shared memory (s_par[0..BN) scales,
+  // s_par[BN..2BN) biases): fetched from global memory once per change of tile column by the 512
+  // epilogue threads together, instead of once per slice by every warp (that global-load latency,
+  // ~480 cycles per slice, was the largest single item of the epilogue).  par_bar[0] counts the warps
+  // that have written their part, par_bar[1] the warps that are done reading the old contents.
+  const bool staged = OK != kOutRaw;
+  const int et = threadIdx.x - 4 * 32;      // 0..511 among the epilogue threads
+  int last_tn = -1;
+  uint32_t reloads = 0;
 
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     int tm, tn;
     TileCoords(t, tiles_m, tiles_n, &tm, &tn);
+    if (staged && tn != last_tn) {
+      bool pok = true;
+      if (reloads > 0) pok = MbarWait(SmemAddr(&par_bar[1]), (reloads - 1) & 1, abort_flag, g.status_word, kErrEpilogue);
+      if (!__all_sync(0xffffffffu, pok)) break;
+      if (et < 2 * BN) {
+        const int j = et < BN ? et : et - BN;
+        const int col = tn * BN + j;
+        float v;
+        if (et < BN) v = (e.scale != nullptr && col < g.n) ? __ldg(e.scale + col) : e.scalar_scale;
+        else v = (e.bias != nullptr && col < g.n) ? __ldg(e.bias + col) : 0.f;
+        s_par[et] = v;
+      }
+      __syncwarp();
+      if (lane == 0) MbarArrive(SmemAddr(&par_bar[0]));
+      pok = MbarWait(SmemAddr(&par_bar[0]), reloads & 1, abort_flag, g.status_word, kErrEpilogue);
+      if (!__all_sync(0xffffffffu, pok)) break;
+      ++reloads;
+      last_tn = tn;
+    }
     const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
     if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
     TcFenceAfter();
@@ -462,8 +485,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             for (int j = 0; j < 16; ++j) w[j] = r[j];
           } else {
             float sc[16], bi[16];
-            LoadParams16(e.scale, col, g.n, e.vec_params, e.scalar_scale, sc);  // in flight together with the TMEM load
-            LoadParams16(e.bias, col, g.n, e.vec_params, 0.f, bi);
+            LoadStaged16(s_par + (c * bcols + 16 * sl), sc);  // in flight together with the TMEM load
+            LoadStaged16(s_par + BN + (c * bcols + 16 * sl), bi);
             TmemLdWait16(r);
             float v[16];
             bool shifted = false;  // v still carries the +1.5*2^23 of the adder trick
@@ -588,7 +611,14 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     }
     TcFenceBefore();
     __syncwarp();
-    if (lane == 0) MbarArrive(SmemAddr(&tmem_empty_bar[acc]));  // one arrival per warp: all its lanes have read their rows
+    if (lane == 0) {
+      MbarArrive(SmemAddr(&tmem_empty_bar[acc]));  // one arrival per warp: all its lanes have read their rows
+      if (staged && t + int(gridDim.x) < num_tiles) {
+        int ntm, ntn;
+        TileCoords(t + int(gridDim.x), tiles_m, tiles_n, &ntm, &ntn);
+        if (ntn != tn) MbarArrive(SmemAddr(&par_bar[1]));  // this warp is done with the staged parameters
+      }
+    }
     acc ^= 1;
     if (acc == 0) acc_phase ^= 1;
   }
@@ -609,15 +639,21 @@ __global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads,
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const GemmArgs g) {
   using C = Cfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((SmemAddr(smem) & 1023u) != 0) {
+    // the swizzled operand tiles need a 1024-byte aligned base; refuse rather than compute garbage
+    if (threadIdx.x == 0 && g.status_word != nullptr) atomicCAS(g.status_word, 0, kErrSmemAlign);
+    return;
+  }
   uint8_t* s_stage = smem + C::kStages * C::kStageBytes;  // the epilogue warps' staging tiles, 1024-aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stage + C::kStagingBytes);
+  float* s_par = reinterpret_cast<float*>(s_stage + C::kStagingBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_par) + C::kParamBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + C::kStages;
   uint64_t* tmem_full_bar = bars + 2 * C::kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint64_t* par_bar = tmem_empty_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(par_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -635,6 +671,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     for (int a = 0; a < 2; ++a) {
       MbarInit(SmemAddr(&tmem_full_bar[a]), 1);
       MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueWarps);
+      MbarInit(SmemAddr(&par_bar[a]), kEpilogueWarps);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -806,14 +843,14 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   } else if (warp >= 4 && warp < kFirstGatherWarp) {
     // ---------------- epilogue ----------------
     switch (g.out_kind) {
-      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      case kOutF32: EpilogueLoop<BN, F8, kOutF32>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      case kOutBF16: EpilogueLoop<BN, F8, kOutBF16>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      case kOutF16: EpilogueLoop<BN, F8, kOutF16>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      case kOutS32: EpilogueLoop<BN, F8, kOutS32>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      case kOutU8: EpilogueLoop<BN, F8, kOutU8>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      case kOutS8: EpilogueLoop<BN, F8, kOutS8>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
-      default: EpilogueLoop<BN, F8, kOutFP8>(g, &tma_out, s_stage, tmem_full_bar, tmem_empty_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutF32: EpilogueLoop<BN, F8, kOutF32>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutBF16: EpilogueLoop<BN, F8, kOutBF16>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutF16: EpilogueLoop<BN, F8, kOutF16>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutS32: EpilogueLoop<BN, F8, kOutS32>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutU8: EpilogueLoop<BN, F8, kOutU8>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      case kOutS8: EpilogueLoop<BN, F8, kOutS8>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
+      default: EpilogueLoop<BN, F8, kOutFP8>(g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles); break;
     }
   }
 
