@@ -32,7 +32,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
 # DRAM bytes (read + write) of one GemmKernel launch, from the ncu captures summarised in
-# profiles/int8_gemm_quantize_matmul.md; null for shapes that were not captured.
+# the ncu summaries kept under profiles/; null for shapes that were not captured.
 GEMM_DRAM_TRAFFIC = {"int8_gemm_8192": 574.4e6, "int8_gemm_4096": 56.4e6}
 
 WORKLOADS = {
