@@ -1,8 +1,9 @@
-// [_ITEX]QuantizedConv2DWithBias[AndRelu]AndRequantize and the Sum-fused variants
-// (old-API quantized Conv2D ops), NHWC.
+// The old-API quantized Conv2D ops, NHWC: [_ITEX]QuantizedConv2D, ...PerChannel, ...WithBias, ...WithBiasAndRelu
+// (qint32 outputs), ...AndRequantize, ...AndReluAndRequantize, ...WithBias[AndRelu]AndRequantize and the Sum-fused
+// variants (8-bit outputs).
 //
-// Attrs, input order (input, filter, bias, min_input, max_input, min_filter, max_filter,
-// min_freezed_output, max_freezed_output[, summand, min_summand, max_summand]), the
+// Attrs, input order (input, filter, [bias,] min_input, max_input, min_filter, max_filter
+// [, min_freezed_output, max_freezed_output][, summand, min_summand, max_summand]), the
 // HostMemory lists and the checks follow LegacyQuantizedConvOpBase
 // (itex/core/kernels/common/quantized_conv_ops.h:71-729) over ConvOpBase
 // (itex/core/kernels/common/conv_ops.h:612-1133), registrations
@@ -18,7 +19,8 @@ namespace {
 
 class QuantizedConv2DOp : public OpKernel {
  public:
-  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum) : relu_(relu), sum_(sum), signed_sum_(signed_sum) {}
+  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum, bool has_bias = true, bool requantize = true)
+      : relu_(relu), sum_(sum), signed_sum_(signed_sum), has_bias_(has_bias), requantize_(requantize) {}
 
   int Init(const AttrMap& attrs) override {
     const char* op = name().c_str();
@@ -69,9 +71,12 @@ class QuantizedConv2DOp : public OpKernel {
     if (attrs.Has("Tbias")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tbias", &tbias_));
     ITEXB_REQUIRE(tbias_ == ITEXB_DT_FLOAT || tbias_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT,
                   "%s: no kernel registered for Tbias=%s", op, DtypeName(tbias_));
-    out_type_ = ITEXB_DT_QUINT8;
+    out_type_ = requantize_ ? ITEXB_DT_QUINT8 : ITEXB_DT_QINT32;
     if (attrs.Has("out_type")) ITEXB_RETURN_IF_ERROR(attrs.GetType("out_type", &out_type_));
-    if (relu_)
+    if (!requantize_)
+      ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT, "%s: no kernel registered for out_type=%s (qint32 is)", op,
+                    DtypeName(out_type_));
+    else if (relu_)
       ITEXB_REQUIRE(out_type_ == ITEXB_DT_QUINT8, ITEXB_INVALID_ARGUMENT,
                     "%s: no kernel registered for out_type=%s (quint8 is)", op, DtypeName(out_type_));
     else
@@ -82,26 +87,29 @@ class QuantizedConv2DOp : public OpKernel {
 
   int Compute(itexb_op_context_t* ctx) override {
     const char* op = name().c_str();
-    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, sum_ ? 12 : 9, op));
+    const int i_rng = has_bias_ ? 3 : 2;                       // first of min_input, max_input, min_filter, max_filter
+    const int i_sum = i_rng + 4 + (requantize_ ? 2 : 0);       // summand, min_summand, max_summand
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, i_sum + (sum_ ? 3 : 0), op));
     ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 0, op, "input"));
     ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 1, op, "filter"));
-    ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 2, op, "bias"));
+    if (has_bias_) ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 2, op, "bias"));
     const itexb_tensor_t& x = ctx->inputs[0];
     const itexb_tensor_t& f = ctx->inputs[1];
-    const itexb_tensor_t& bias = ctx->inputs[2];
+    static const itexb_tensor_t kNoTensor{};
+    const itexb_tensor_t& bias = has_bias_ ? ctx->inputs[2] : kNoTensor;
     ITEXB_REQUIRE(x.rank == 4, ITEXB_INVALID_ARGUMENT, "input must be 4-dimensional");
     ITEXB_REQUIRE(f.rank == 4, ITEXB_INVALID_ARGUMENT, "filter must be 4-dimensional");
     ITEXB_REQUIRE(x.dtype == tinput_, ITEXB_INVALID_ARGUMENT, "%s: input has type %s, Tinput is %s", op, DtypeName(x.dtype),
                   DtypeName(tinput_));
     ITEXB_REQUIRE(f.dtype == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT, "%s: filter must be qint8", op);
-    ITEXB_REQUIRE(bias.dtype == tbias_, ITEXB_INVALID_ARGUMENT, "%s: bias has type %s, Tbias is %s", op, DtypeName(bias.dtype),
-                  DtypeName(tbias_));
+    ITEXB_REQUIRE(!has_bias_ || bias.dtype == tbias_, ITEXB_INVALID_ARGUMENT, "%s: bias has type %s, Tbias is %s", op,
+                  DtypeName(bias.dtype), DtypeName(tbias_));
     const int64_t n = x.dims[0], h = x.dims[1], w = x.dims[2], c = x.dims[3];
     const int64_t kh = f.dims[0], kw = f.dims[1], co = f.dims[3];
     ITEXB_REQUIRE(f.dims[2] == c, ITEXB_INVALID_ARGUMENT, "input and filter must have the same depth: %lld vs %lld", (long long)c,
                   (long long)f.dims[2]);
-    ITEXB_REQUIRE(bias.rank == 1 && bias.dims[0] == co, ITEXB_INVALID_ARGUMENT, "%s: bias must be a vector of %lld elements", op,
-                  (long long)co);
+    ITEXB_REQUIRE(!has_bias_ || (bias.rank == 1 && bias.dims[0] == co), ITEXB_INVALID_ARGUMENT,
+                  "%s: bias must be a vector of %lld elements", op, (long long)co);
     int64_t oh, ow, pt = 0, pb = 0, pl = 0, pr = 0;
     if (padding_ == 2) { pt = explicit_paddings_[2]; pb = explicit_paddings_[3]; pl = explicit_paddings_[4]; pr = explicit_paddings_[5]; }
     ITEXB_REQUIRE(hostmath::WindowedOutputSize(h, kh, dil_h_, stride_h_, padding_, &oh, &pt, &pb) &&
@@ -109,38 +117,54 @@ class QuantizedConv2DOp : public OpKernel {
                   ITEXB_INVALID_ARGUMENT, "%s: computed output size would be negative", op);
     const float *pmin_in, *pmax_in, *pmin_f, *pmax_f, *pmin_o, *pmax_o;
     int64_t c1, c2, nf1, nf2;
-    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 3, op, "min_input", &pmin_in, &c1));
-    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 4, op, "max_input", &pmax_in, &c2));
-    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 5, op, "min_filter", &pmin_f, &nf1));
-    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 6, op, "max_filter", &pmax_f, &nf2));
-    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 7, op, "min_freezed_output", &pmin_o, &c1));
-    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 8, op, "max_freezed_output", &pmax_o, &c2));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng, op, "min_input", &pmin_in, &c1));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 1, op, "max_input", &pmax_in, &c2));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 2, op, "min_filter", &pmin_f, &nf1));
+    ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 3, op, "max_filter", &pmax_f, &nf2));
+    static const float kZero = 0.f;
+    pmin_o = pmax_o = &kZero;
+    if (requantize_) {
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 4, op, "min_freezed_output", &pmin_o, &c1));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 5, op, "max_freezed_output", &pmax_o, &c2));
+    }
     ITEXB_REQUIRE(nf1 == nf2 && (nf1 == 1 || nf1 == co), ITEXB_INVALID_ARGUMENT,
                   "%s: min_filter/max_filter must be scalars or vectors of %lld elements", op, (long long)co);
     const float min_in = pmin_in[0], max_in = pmax_in[0], min_o = pmin_o[0], max_o = pmax_o[0];
     float sum_scale = 1.f;
     const itexb_tensor_t* summand = nullptr;
     if (sum_) {
-      ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 9, op, "summand"));
-      summand = &ctx->inputs[9];
+      ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, i_sum, op, "summand"));
+      summand = &ctx->inputs[i_sum];
       ITEXB_REQUIRE(summand->dtype == ITEXB_DT_QUINT8 || summand->dtype == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT,
                     "%s: summand must be quint8 or qint8", op);
       ITEXB_REQUIRE(summand->rank == 4 && summand->dims[0] == n && summand->dims[1] == oh && summand->dims[2] == ow &&
                         summand->dims[3] == co,
                     ITEXB_INVALID_ARGUMENT, "%s: summand must have the shape of the output", op);
       const float *ps1, *ps2;
-      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 10, op, "min_summand", &ps1, &c1));
-      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, 11, op, "max_summand", &ps2, &c2));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_sum + 1, op, "min_summand", &ps1, &c1));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_sum + 2, op, "max_summand", &ps2, &c2));
       sum_scale = hostmath::ConvSumScale(min_o, max_o, ps1[0], ps2[0], out_type_, summand->dtype);
     }
 
     itexb_tensor_t dst, omin, omax;
     const int64_t out_dims[4] = {n, oh, ow, co};
     ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 0, out_type_, out_dims, 4, false, &dst));
-    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, ITEXB_DT_FLOAT, nullptr, 0, true, &omin));
-    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 2, ITEXB_DT_FLOAT, nullptr, 0, true, &omax));
-    *static_cast<float*>(omin.data) = min_o;
-    *static_cast<float*>(omax.data) = max_o;
+    if (requantize_) {
+      ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, ITEXB_DT_FLOAT, nullptr, 0, true, &omin));
+      ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 2, ITEXB_DT_FLOAT, nullptr, 0, true, &omax));
+      *static_cast<float*>(omin.data) = min_o;
+      *static_cast<float*>(omax.data) = max_o;
+    } else {
+      // qint32 output: the range one accumulator level spans, per filter range
+      // (AllocateNativeOutputMinMax, itex/core/kernels/onednn/block/quantized_ops.h:166-195)
+      const bool per_channel = ctx->inputs[i_rng + 2].rank != 0;
+      const int64_t vec_dims[1] = {nf1};
+      ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, ITEXB_DT_FLOAT, vec_dims, per_channel ? 1 : 0, true, &omin));
+      ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 2, ITEXB_DT_FLOAT, vec_dims, per_channel ? 1 : 0, true, &omax));
+      for (int64_t i = 0; i < (per_channel ? nf1 : 1); ++i)
+        hostmath::QuantizationRangeForMultiplication(min_in, max_in, pmin_f[i], pmax_f[i], tinput_, ITEXB_DT_QINT8,
+                                                     &static_cast<float*>(omin.data)[i], &static_cast<float*>(omax.data)[i]);
+    }
     if (n == 0 || oh == 0 || ow == 0) return ITEXB_OK;
 
     cudaStream_t st = AsCuda(ctx->stream);
@@ -172,7 +196,7 @@ class QuantizedConv2DOp : public OpKernel {
     if (tbias_ == ITEXB_DT_QINT32) factors = scales;  // float(b32) * scale[o]
     else hostmath::ConvFloatBiasFactors(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, scales, &factors);
     const bool reuse_bias = bias_valid_ && is_bias_const_ && bias_from_ == bias.data && factors == saved_factors_;
-    if (!reuse_bias) {
+    if (has_bias_ && !reuse_bias) {
       ITEXB_RETURN_IF_ERROR(scaled_bias_.Ensure(ord, size_t(co) * sizeof(float)));
       const float* d_f = nullptr;
       ITEXB_RETURN_IF_ERROR(factor_cache_.Get(ord, st, factors.data(), factors.size(), &d_f));
@@ -186,10 +210,13 @@ class QuantizedConv2DOp : public OpKernel {
     p.c_pad = c_pad;
     p.x_dtype = tinput_; p.out_dtype = out_type_;
     p.x = x.data; p.filter_packed = packed_.data(); p.out = dst.data;
-    p.ep.scale = d_scale;
-    p.ep.scale_count = int(scales.size());
-    p.ep.bias = static_cast<const float*>(scaled_bias_.data());
+    if (out_type_ != ITEXB_DT_QINT32) {
+      p.ep.scale = d_scale;
+      p.ep.scale_count = int(scales.size());
+    }
+    p.ep.bias = has_bias_ ? static_cast<const float*>(scaled_bias_.data()) : nullptr;
     p.ep.relu = relu_ ? 1 : 0;
+    p.ep.raw_acc = (out_type_ == ITEXB_DT_QINT32 && !has_bias_ && !relu_ && summand == nullptr) ? 1 : 0;  // the exact accumulators
     if (summand != nullptr) {
       p.ep.summand = summand->data;
       p.ep.summand_dtype = summand->dtype;
@@ -202,7 +229,7 @@ class QuantizedConv2DOp : public OpKernel {
   }
 
  private:
-  const bool relu_, sum_, signed_sum_;
+  const bool relu_, sum_, signed_sum_, has_bias_, requantize_;
   int stride_h_ = 1, stride_w_ = 1, dil_h_ = 1, dil_w_ = 1, padding_ = 1;
   std::vector<int64_t> explicit_paddings_;
   bool is_filter_const_ = true, is_bias_const_ = true;
@@ -221,6 +248,29 @@ struct ConvBiasReq : QuantizedConv2DOp { ConvBiasReq() : QuantizedConv2DOp(false
 struct ConvBiasSumReluReq : QuantizedConv2DOp { ConvBiasSumReluReq() : QuantizedConv2DOp(true, true, false) {} };
 struct ConvBiasSignedSumReluReq : QuantizedConv2DOp { ConvBiasSignedSumReluReq() : QuantizedConv2DOp(true, true, true) {} };
 
+struct ConvS32 : QuantizedConv2DOp { ConvS32() : QuantizedConv2DOp(false, false, false, false, false) {} };
+struct ConvReluS32 : QuantizedConv2DOp { ConvReluS32() : QuantizedConv2DOp(true, false, false, false, false) {} };
+struct ConvBiasS32 : QuantizedConv2DOp { ConvBiasS32() : QuantizedConv2DOp(false, false, false, true, false) {} };
+struct ConvBiasReluS32 : QuantizedConv2DOp { ConvBiasReluS32() : QuantizedConv2DOp(true, false, false, true, false) {} };
+struct ConvReq : QuantizedConv2DOp { ConvReq() : QuantizedConv2DOp(false, false, false, false, true) {} };
+struct ConvReluReq : QuantizedConv2DOp { ConvReluReq() : QuantizedConv2DOp(true, false, false, false, true) {} };
+
+// qint32-output members (itex/core/kernels/gpu/quantized_conv_ops.cc:72-100): HostMemory inputs 2..5 (3..6 with a bias)
+ITEXB_REGISTER_OP("QuantizedConv2D", ConvS32, 6, 3, 0x3cu, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2D", ConvS32, 6, 3, 0x3cu, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DPerChannel", ConvS32, 6, 3, 0x3cu, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DPerChannel", ConvS32, 6, 3, 0x3cu, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DAndRelu", ConvReluS32, 6, 3, 0x3cu, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndRelu", ConvReluS32, 6, 3, 0x3cu, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DWithBias", ConvBiasS32, 7, 3, 0x78u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBias", ConvBiasS32, 7, 3, 0x78u, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DWithBiasAndRelu", ConvBiasReluS32, 7, 3, 0x78u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasAndRelu", ConvBiasReluS32, 7, 3, 0x78u, 0x6u);
+// requantizing members without a bias (:104-110): HostMemory inputs 2..7
+ITEXB_REGISTER_OP("QuantizedConv2DAndRequantize", ConvReq, 8, 3, 0xfcu, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndRequantize", ConvReq, 8, 3, 0xfcu, 0x6u);
+ITEXB_REGISTER_OP("QuantizedConv2DAndReluAndRequantize", ConvReluReq, 8, 3, 0xfcu, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndReluAndRequantize", ConvReluReq, 8, 3, 0xfcu, 0x6u);
 // HostMemory: inputs 3..8 (and 10, 11), outputs 1, 2.
 ITEXB_REGISTER_OP("QuantizedConv2DWithBiasAndReluAndRequantize", ConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);
 ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", ConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);

@@ -364,6 +364,27 @@ def _ITEXQuantizedConv2DWithBiasAndReluAndRequantize(input, filter, bias, min_in
     return _cached(op_name, attrs)(*args, dtypes=dtypes)
 
 
+def QuantizedConv2D(op_name, input, filter, bias, min_input, max_input, min_filter, max_filter, min_freezed_output=None,
+                    max_freezed_output=None, strides=(1, 1, 1, 1), padding="SAME", dilations=(1, 1, 1, 1), out_type="qint32",
+                    is_filter_const=True, is_bias_const=True):
+    """The other members of the legacy conv family by name: QuantizedConv2D, ...PerChannel, ...AndRelu, ...WithBias,
+    ...WithBiasAndRelu (qint32 outputs; `bias` None for the first three) and ...AndRequantize, ...AndReluAndRequantize
+    (no bias, frozen output range).  -> (output, min_output, max_output)"""
+    attrs = dict(Tinput=_TORCH_TO_DT[input.dtype], Tfilter="qint8", out_type=out_type, strides=list(strides), padding=padding,
+                 dilations=list(dilations), data_format="NHWC", is_filter_const=bool(is_filter_const),
+                 is_bias_const=bool(is_bias_const))
+    args = [input, filter]
+    dtypes = None
+    if bias is not None:
+        attrs["Tbias"] = _bias_attr(bias)
+        args.append(bias)
+        dtypes = {2: L.DT_QINT32} if bias.dtype == torch.int32 else None
+    args += [min_input, max_input, min_filter, max_filter]
+    if min_freezed_output is not None:
+        args += [min_freezed_output, max_freezed_output]
+    return _cached(op_name, attrs)(*args, dtypes=dtypes)
+
+
 def Fp8Quantize(x, x_amax, x_scale, fp8_meta_index, fp8_dtype="E4M3"):
     """-> y (int8 tensor holding fp8 bytes); x_amax[fp8_meta_index] is raised in place."""
     op = _cached("Fp8Quantize", dict(in_dtype=_TORCH_TO_DT[x.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))

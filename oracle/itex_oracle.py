@@ -603,9 +603,20 @@ def quantized_conv2d(x, filt, bias, min_input, max_input, min_filter, max_filter
             sum_scale = f32(f32(f32(255.0) * ss) / f32(so * f32(127.0)))
         else:
             sum_scale = f32(ss / so)
-    out = epilogue(acc, scales if out_type != QINT32 else None, b, relu, out_type, summand, sum_scale)
+    if out_type == QINT32 and b is None and not relu and summand is None:
+        out = acc.astype(np.int32)   # no post-op at all: the accumulators themselves
+    else:
+        out = epilogue(acc, scales if out_type != QINT32 else None, b, relu, out_type, summand, sum_scale)
     if out_type in (QUINT8, QINT8):
         return out, f32(min_freezed_output), f32(max_freezed_output)
+    if out_type == QINT32:
+        # AllocateNativeOutputMinMax, onednn/block/quantized_ops.h:166-195: per filter range
+        mf = np.atleast_1d(np.asarray(min_filter, np.float32))
+        xf = np.atleast_1d(np.asarray(max_filter, np.float32))
+        r = [quantization_range_for_multiplication(min_input, max_input, mf[i], xf[i], tinput) for i in range(mf.size)]
+        if np.ndim(min_filter) == 0:
+            return out, r[0][0], r[0][1]
+        return out, np.array([v[0] for v in r], np.float32), np.array([v[1] for v in r], np.float32)
     return out, None, None
 
 

@@ -208,3 +208,41 @@ def test_lowerings_agree(case):
     np.testing.assert_array_equal(im2col, want)
     np.testing.assert_array_equal(dense, want)
     np.testing.assert_array_equal(explicit, want)
+
+
+@pytest.mark.parametrize("tin", ["quint8", "qint8"])
+def test_legacy_family_qint32_and_no_bias(tin):
+    """QuantizedConv2D / PerChannel (exact accumulators), WithBias[AndRelu] (qint32 with the bias brought to
+    accumulator units), AndRequantize / AndReluAndRequantize (no bias): bit-exact against the oracle, output
+    ranges included."""
+    itex, K, ops = modules()
+    rng = np.random.default_rng(31)
+    n, h, w, c, co = 3, 13, 15, 32, 48
+    x = rng.integers(0, 256, (n, h, w, c)).astype(np.uint8) if tin == "quint8" else rng.integers(-127, 128, (n, h, w, c)).astype(np.int8)
+    f32, qf, mnf, mxf = _filter(rng, 3, 3, c, co)
+    bias = (rng.standard_normal(co) * 0.5).astype(np.float32)
+    mni, mxi = (0.0, 6.0) if tin == "quint8" else (-3.0, 3.0)
+    X, F, B = dev(x), dev(qf), dev(bias)
+    kw = dict(strides=(1, 2, 2, 1), padding="SAME")
+    # accumulators, per-channel and per-tensor filter ranges
+    for name, mn, mx in (("_ITEXQuantizedConv2DPerChannel", mnf, mxf), ("QuantizedConv2D", float(mnf.min()), float(mxf.max()))):
+        ref, rmn, rmx = o.quantized_conv2d(x, qf, None, mni, mxi, mn, mx, out_type="qint32", relu=False, strides=(1, 2, 2, 1))
+        got, gmn, gmx = ops.QuantizedConv2D(name, X, F, None, mni, mxi, mn, mx, **kw)
+        np.testing.assert_array_equal(host(got), ref)
+        np.testing.assert_array_equal(np.asarray(gmn), np.asarray(rmn))
+        np.testing.assert_array_equal(np.asarray(gmx), np.asarray(rmx))
+    for name, relu in (("_ITEXQuantizedConv2DWithBias", False), ("QuantizedConv2DWithBiasAndRelu", True)):
+        ref, rmn, rmx = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, out_type="qint32", relu=relu, strides=(1, 2, 2, 1))
+        got, gmn, gmx = ops.QuantizedConv2D(name, X, F, B, mni, mxi, mnf, mxf, **kw)
+        np.testing.assert_array_equal(host(got), ref)
+        np.testing.assert_array_equal(gmx, rmx)
+    acc, _, _ = o.quantized_conv2d(x, qf, None, mni, mxi, mnf, mxf, out_type="qint32", relu=False, strides=(1, 2, 2, 1))
+    real = acc.astype(np.float64) * (max(abs(mni), abs(mxi)) / (255.0 if tin == "quint8" else 127.0)) * (mxf / 127.0)
+    hi = float(np.abs(real).max())
+    ref, _, _ = o.quantized_conv2d(x, qf, None, mni, mxi, mnf, mxf, -hi, hi, out_type="qint8", relu=False, strides=(1, 2, 2, 1))
+    got, gmn, gmx = ops.QuantizedConv2D("_ITEXQuantizedConv2DAndRequantize", X, F, None, mni, mxi, mnf, mxf, -hi, hi, out_type="qint8", **kw)
+    np.testing.assert_array_equal(host(got), ref)
+    assert (gmn, gmx) == (np.float32(-hi), np.float32(hi))
+    ref, _, _ = o.quantized_conv2d(x, qf, None, mni, mxi, mnf, mxf, 0.0, hi, out_type="quint8", relu=True, strides=(1, 2, 2, 1))
+    got, _, _ = ops.QuantizedConv2D("QuantizedConv2DAndReluAndRequantize", X, F, None, mni, mxi, mnf, mxf, 0.0, hi, out_type="quint8", **kw)
+    np.testing.assert_array_equal(host(got), ref)
