@@ -19,8 +19,37 @@ namespace {
 
 class QuantizedConv2DOp : public OpKernel {
  public:
-  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum, bool has_bias = true, bool requantize = true)
-      : relu_(relu), sum_(sum), signed_sum_(signed_sum), has_bias_(has_bias), requantize_(requantize) {}
+  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum, bool has_bias = true, bool requantize = true, bool new_api = false)
+      : relu_(relu), sum_(sum), signed_sum_(signed_sum), has_bias_(has_bias), requantize_(requantize), new_api_(new_api) {}
+
+  // New API (_QuantizedConv2D / _ITEXQuantizedConv2DV2): the fusion comes from the fused_ops attr
+  // (LegacyQuantizedConvOpBase constructor, itex/core/kernels/common/quantized_conv_ops.h:76-312).
+  int InitFusedOps(const AttrMap& attrs) {
+    const char* op = name().c_str();
+    std::vector<std::string> fused;
+    if (attrs.Has("fused_ops")) ITEXB_RETURN_IF_ERROR(attrs.GetStringList("fused_ops", &fused));
+    float alpha = 0.f;
+    if (attrs.Has("alpha")) ITEXB_RETURN_IF_ERROR(attrs.GetFloat("alpha", &alpha));
+    has_bias_ = relu_ = sum_ = requantize_ = dequantize_ = false;
+    int pos = 0, act_at = -1, sum_at = -1;
+    for (const std::string& f : fused) {
+      if (f == "BiasAdd") has_bias_ = true;
+      else if (f == "Requantize") requantize_ = true;
+      else if (f == "Dequantize") dequantize_ = true;
+      else if (f == "Sum") { sum_ = true; sum_at = pos++; }
+      else if (f == "Relu") { relu_ = true; act_at = pos++; }
+      else if (f == "LeakyRelu") { act_ = ITEXB_ACT_RELU; act_alpha_ = alpha; act_at = pos++; }
+      else if (f == "Elu") { act_ = ITEXB_ACT_ELU; act_alpha_ = 1.f; act_at = pos++; }
+      else if (f == "Sigmoid") { act_ = ITEXB_ACT_SIGMOID; act_at = pos++; }
+      else if (f == "_FusedSwish") { act_ = ITEXB_ACT_SWISH; act_alpha_ = 1.f; act_at = pos++; }
+      else return SetError(ITEXB_INVALID_ARGUMENT, "%s: unsupported fusion %s", op, f.c_str());
+    }
+    ITEXB_REQUIRE(!(requantize_ && dequantize_), ITEXB_INVALID_ARGUMENT, "%s: Requantize and Dequantize cannot both be fused", op);
+    ITEXB_REQUIRE(!(sum_ && act_at >= 0 && act_at < sum_at), ITEXB_UNIMPLEMENTED,
+                  "%s: an activation before Sum is not implemented (Sum, then activation is)", op);
+    ITEXB_REQUIRE(!sum_ || requantize_, ITEXB_UNIMPLEMENTED, "%s: Sum is implemented with Requantize (8-bit summand) only", op);
+    return ITEXB_OK;
+  }
 
   int Init(const AttrMap& attrs) override {
     const char* op = name().c_str();
@@ -71,9 +100,19 @@ class QuantizedConv2DOp : public OpKernel {
     if (attrs.Has("Tbias")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tbias", &tbias_));
     ITEXB_REQUIRE(tbias_ == ITEXB_DT_FLOAT || tbias_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT,
                   "%s: no kernel registered for Tbias=%s", op, DtypeName(tbias_));
-    out_type_ = requantize_ ? ITEXB_DT_QUINT8 : ITEXB_DT_QINT32;
+    if (new_api_) ITEXB_RETURN_IF_ERROR(InitFusedOps(attrs));
+    out_type_ = requantize_ ? ITEXB_DT_QUINT8 : (dequantize_ ? ITEXB_DT_FLOAT : ITEXB_DT_QINT32);
     if (attrs.Has("out_type")) ITEXB_RETURN_IF_ERROR(attrs.GetType("out_type", &out_type_));
-    if (!requantize_)
+    if (new_api_) {
+      if (requantize_)
+        ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT8 || out_type_ == ITEXB_DT_QUINT8, ITEXB_INVALID_ARGUMENT,
+                      "QuantizedConv: unsupported output type when Requantize is fused.");
+      else if (dequantize_)
+        ITEXB_REQUIRE(out_type_ == ITEXB_DT_FLOAT || out_type_ == ITEXB_DT_BFLOAT16, ITEXB_INVALID_ARGUMENT,
+                      "QuantizedConv: unsupported output type when Dequantize is fused.");
+      else
+        ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT, "%s: out_type must be qint32 without Requantize / Dequantize", op);
+    } else if (!requantize_)
       ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT, "%s: no kernel registered for out_type=%s (qint32 is)", op,
                     DtypeName(out_type_));
     else if (relu_)
@@ -87,9 +126,13 @@ class QuantizedConv2DOp : public OpKernel {
 
   int Compute(itexb_op_context_t* ctx) override {
     const char* op = name().c_str();
-    const int i_rng = has_bias_ ? 3 : 2;                       // first of min_input, max_input, min_filter, max_filter
-    const int i_sum = i_rng + 4 + (requantize_ ? 2 : 0);       // summand, min_summand, max_summand
-    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, i_sum + (sum_ ? 3 : 0), op));
+    // Old API: input, filter, [bias], 4 ranges, [2 frozen output ranges], [summand, 2 summand ranges].
+    // New API: input, filter, [bias], [summand], 4 ranges, [2 summand ranges], [2 frozen output ranges].
+    const int i_rng = 2 + (has_bias_ ? 1 : 0) + (new_api_ && sum_ ? 1 : 0);  // first of min_input, max_input, min_filter, max_filter
+    const int i_sum = new_api_ ? 2 + (has_bias_ ? 1 : 0) : i_rng + 4 + (requantize_ ? 2 : 0);   // summand
+    const int i_sum_rng = new_api_ ? i_rng + 4 : i_sum + 1;                    // min_summand, max_summand
+    const int i_frz = new_api_ ? i_rng + 4 + (sum_ ? 2 : 0) : i_rng + 4;       // min/max_freezed_output
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, i_rng + 4 + (requantize_ ? 2 : 0) + (sum_ ? (new_api_ ? 2 : 3) : 0), op));
     ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 0, op, "input"));
     ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 1, op, "filter"));
     if (has_bias_) ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 2, op, "bias"));
@@ -124,8 +167,8 @@ class QuantizedConv2DOp : public OpKernel {
     static const float kZero = 0.f;
     pmin_o = pmax_o = &kZero;
     if (requantize_) {
-      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 4, op, "min_freezed_output", &pmin_o, &c1));
-      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_rng + 5, op, "max_freezed_output", &pmax_o, &c2));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_frz, op, "min_freezed_output", &pmin_o, &c1));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_frz + 1, op, "max_freezed_output", &pmax_o, &c2));
     }
     ITEXB_REQUIRE(nf1 == nf2 && (nf1 == 1 || nf1 == co), ITEXB_INVALID_ARGUMENT,
                   "%s: min_filter/max_filter must be scalars or vectors of %lld elements", op, (long long)co);
@@ -141,15 +184,17 @@ class QuantizedConv2DOp : public OpKernel {
                         summand->dims[3] == co,
                     ITEXB_INVALID_ARGUMENT, "%s: summand must have the shape of the output", op);
       const float *ps1, *ps2;
-      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_sum + 1, op, "min_summand", &ps1, &c1));
-      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_sum + 2, op, "max_summand", &ps2, &c2));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_sum_rng, op, "min_summand", &ps1, &c1));
+      ITEXB_RETURN_IF_ERROR(HostFloats(ctx, i_sum_rng + 1, op, "max_summand", &ps2, &c2));
       sum_scale = hostmath::ConvSumScale(min_o, max_o, ps1[0], ps2[0], out_type_, summand->dtype);
     }
 
     itexb_tensor_t dst, omin, omax;
     const int64_t out_dims[4] = {n, oh, ow, co};
     ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 0, out_type_, out_dims, 4, false, &dst));
-    if (requantize_) {
+    if (dequantize_) {
+      // a real-valued output carries no range
+    } else if (requantize_) {
       ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, ITEXB_DT_FLOAT, nullptr, 0, true, &omin));
       ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 2, ITEXB_DT_FLOAT, nullptr, 0, true, &omax));
       *static_cast<float*>(omin.data) = min_o;
@@ -193,7 +238,9 @@ class QuantizedConv2DOp : public OpKernel {
     hostmath::ConvOutputScales(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, out_type_, min_o, max_o, &scales);
     const float* d_scale = nullptr;
     ITEXB_RETURN_IF_ERROR(scale_cache_.Get(ord, st, scales.data(), scales.size(), &d_scale));
-    if (tbias_ == ITEXB_DT_QINT32) factors = scales;  // float(b32) * scale[o]
+    if (tbias_ == ITEXB_DT_QINT32 && dequantize_)
+      hostmath::ConvInt32BiasDequantFactors(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, &factors);
+    else if (tbias_ == ITEXB_DT_QINT32) factors = scales;  // float(b32) * scale[o]
     else hostmath::ConvFloatBiasFactors(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, scales, &factors);
     const bool reuse_bias = bias_valid_ && is_bias_const_ && bias_from_ == bias.data && factors == saved_factors_;
     if (has_bias_ && !reuse_bias) {
@@ -216,7 +263,10 @@ class QuantizedConv2DOp : public OpKernel {
     }
     p.ep.bias = has_bias_ ? static_cast<const float*>(scaled_bias_.data()) : nullptr;
     p.ep.relu = relu_ ? 1 : 0;
-    p.ep.raw_acc = (out_type_ == ITEXB_DT_QINT32 && !has_bias_ && !relu_ && summand == nullptr) ? 1 : 0;  // the exact accumulators
+    p.ep.raw_acc = (out_type_ == ITEXB_DT_QINT32 && !has_bias_ && !relu_ && summand == nullptr && act_ == ITEXB_ACT_NONE) ? 1 : 0;  // the exact accumulators
+    // Element-wise post-ops run on the scaled value with post-op scale 1 (quantized_conv_ops.h:437-445)
+    p.ep.activation = act_;
+    p.ep.act_alpha = act_alpha_;
     if (summand != nullptr) {
       p.ep.summand = summand->data;
       p.ep.summand_dtype = summand->dtype;
@@ -229,7 +279,11 @@ class QuantizedConv2DOp : public OpKernel {
   }
 
  private:
-  const bool relu_, sum_, signed_sum_, has_bias_, requantize_;
+  bool relu_, sum_, signed_sum_, has_bias_, requantize_;
+  const bool new_api_;
+  bool dequantize_ = false;
+  int act_ = ITEXB_ACT_NONE;
+  float act_alpha_ = 0.f;
   int stride_h_ = 1, stride_w_ = 1, dil_h_ = 1, dil_w_ = 1, padding_ = 1;
   std::vector<int64_t> explicit_paddings_;
   bool is_filter_const_ = true, is_bias_const_ = true;
@@ -271,6 +325,11 @@ ITEXB_REGISTER_OP("QuantizedConv2DAndRequantize", ConvReq, 8, 3, 0xfcu, 0x6u);
 ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndRequantize", ConvReq, 8, 3, 0xfcu, 0x6u);
 ITEXB_REGISTER_OP("QuantizedConv2DAndReluAndRequantize", ConvReluReq, 8, 3, 0xfcu, 0x6u);
 ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndReluAndRequantize", ConvReluReq, 8, 3, 0xfcu, 0x6u);
+struct ConvV2 : QuantizedConv2DOp { ConvV2() : QuantizedConv2DOp(false, false, false, false, false, true) {} };
+// New API: list-typed arguments (counts depend on fused_ops), every range in host memory
+// (HostMemoryList2("host_inputs", "host_outputs"), itex/core/kernels/gpu/quantized_conv_ops.cc:171-200)
+ITEXB_REGISTER_OP("_QuantizedConv2D", ConvV2, -1, -1, 0u, 0x6u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DV2", ConvV2, -1, -1, 0u, 0x6u);
 // HostMemory: inputs 3..8 (and 10, 11), outputs 1, 2.
 ITEXB_REGISTER_OP("QuantizedConv2DWithBiasAndReluAndRequantize", ConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);
 ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", ConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);

@@ -385,6 +385,26 @@ def QuantizedConv2D(op_name, input, filter, bias, min_input, max_input, min_filt
     return _cached(op_name, attrs)(*args, dtypes=dtypes)
 
 
+def _QuantizedConv2D(device_inputs, host_inputs, fused_ops=(), out_type="qint32", Tbias=None, Tsummand=None, strides=(1, 1, 1, 1),
+                     padding="SAME", dilations=(1, 1, 1, 1), alpha=0.0, is_filter_const=True, is_bias_const=True,
+                     op_name="_QuantizedConv2D"):
+    """New-API quantized conv (_QuantizedConv2D / _ITEXQuantizedConv2DV2): device_inputs = [input, filter(, bias)(, summand)],
+    host_inputs = [min_input, max_input, min_filter, max_filter(, min_summand, max_summand)(, min_freezed_output,
+    max_freezed_output)].  -> the device output followed by the host outputs (one element for a float output)."""
+    attrs = dict(Tinput=_TORCH_TO_DT[device_inputs[0].dtype], Tfilter="qint8", out_type=out_type, strides=list(strides), padding=padding,
+                 dilations=list(dilations), data_format="NHWC", is_filter_const=bool(is_filter_const),
+                 is_bias_const=bool(is_bias_const), alpha=float(alpha))
+    if len(fused_ops) > 0:
+        attrs["fused_ops"] = list(fused_ops)
+    dtypes = None
+    if "BiasAdd" in fused_ops:
+        attrs["Tbias"] = Tbias if Tbias is not None else _bias_attr(device_inputs[2])
+        dtypes = {2: L.DT_QINT32} if device_inputs[2].dtype == torch.int32 else None
+    if Tsummand is not None:
+        attrs["Tsummand"] = Tsummand
+    return _cached(op_name, attrs)(*(list(device_inputs) + list(host_inputs)), dtypes=dtypes)
+
+
 def Fp8Quantize(x, x_amax, x_scale, fp8_meta_index, fp8_dtype="E4M3"):
     """-> y (int8 tensor holding fp8 bytes); x_amax[fp8_meta_index] is raised in place."""
     op = _cached("Fp8Quantize", dict(in_dtype=_TORCH_TO_DT[x.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))

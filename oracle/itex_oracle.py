@@ -582,7 +582,7 @@ def quantized_conv2d(x, filt, bias, min_input, max_input, min_filter, max_filter
                      min_freezed_output=None, max_freezed_output=None, *, strides=(1, 1, 1, 1),
                      padding="SAME", dilations=(1, 1, 1, 1), explicit_pads=None, out_type: str = QUINT8,
                      relu: bool = True, tbias: str = "float", summand=None, min_summand=None,
-                     max_summand=None):
+                     max_summand=None, activation_name: Optional[str] = None, alpha: float = 0.0):
     """_ITEXQuantizedConv2DWithBias[AndRelu]AndRequantize (+ Sum variants, + Dequantize-fused
     variant when out_type is a float type).  LegacyQuantizedConvOpBase,
     itex/core/kernels/common/quantized_conv_ops.h:71-729 over ConvOpBase
@@ -603,10 +603,15 @@ def quantized_conv2d(x, filt, bias, min_input, max_input, min_filter, max_filter
             sum_scale = f32(f32(f32(255.0) * ss) / f32(so * f32(127.0)))
         else:
             sum_scale = f32(ss / so)
-    if out_type == QINT32 and b is None and not relu and summand is None:
+    if out_type == QINT32 and b is None and not relu and summand is None and activation_name is None:
         out = acc.astype(np.int32)   # no post-op at all: the accumulators themselves
-    else:
+    elif activation_name is None:
         out = epilogue(acc, scales if out_type != QINT32 else None, b, relu, out_type, summand, sum_scale)
+    else:
+        # new-API element-wise post-ops run on the scaled value with post-op scale 1 (quantized_conv_ops.h:437-445)
+        f = epilogue(acc, scales if out_type != QINT32 else None, b, relu, "float", summand, sum_scale)
+        f = activation(f, activation_name, alpha)
+        out = f if out_type == "float" else (to_bf16_rne(f) if out_type == "bfloat16" else sat_rne(f, out_type))
     if out_type in (QUINT8, QINT8):
         return out, f32(min_freezed_output), f32(max_freezed_output)
     if out_type == QINT32:

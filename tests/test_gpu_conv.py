@@ -246,3 +246,49 @@ def test_legacy_family_qint32_and_no_bias(tin):
     ref, _, _ = o.quantized_conv2d(x, qf, None, mni, mxi, mnf, mxf, 0.0, hi, out_type="quint8", relu=True, strides=(1, 2, 2, 1))
     got, _, _ = ops.QuantizedConv2D("QuantizedConv2DAndReluAndRequantize", X, F, None, mni, mxi, mnf, mxf, 0.0, hi, out_type="quint8", **kw)
     np.testing.assert_array_equal(host(got), ref)
+
+
+def test_new_api_fused_ops():
+    """_QuantizedConv2D / _ITEXQuantizedConv2DV2: fusion given by the fused_ops attr, list-typed arguments in the new order
+    (summand before the ranges, frozen output range last).  Bit-exact for integer outputs and algebraic post-ops."""
+    itex, K, ops = modules()
+    rng = np.random.default_rng(41)
+    n, h, w, c, co = 2, 14, 14, 64, 64
+    x = rng.integers(0, 256, (n, h, w, c)).astype(np.uint8)
+    f32, qf, mnf, mxf = _filter(rng, 3, 3, c, co)
+    bias = (rng.standard_normal(co) * 0.5).astype(np.float32)
+    mni, mxi = 0.0, 5.1
+    X, F, B = dev(x), dev(qf), dev(bias)
+    rng4 = [mni, mxi, mnf, mxf]
+    # Dequantize: real-valued output, no ranges
+    for tout in ("float", "bfloat16"):
+        ref, _, _ = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, out_type=tout, relu=False)
+        got = ops._QuantizedConv2D([X, F, B], rng4, fused_ops=["BiasAdd", "Dequantize"], out_type=tout)
+        np.testing.assert_array_equal(host(got), ref.astype(np.float32))
+    real, _, _ = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, out_type="float", relu=False)
+    hi = float(np.abs(real).max())
+    # Relu + Requantize = the legacy op
+    ref, _, _ = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, 0.0, hi, out_type="quint8", relu=True)
+    got, gmn, gmx = ops._QuantizedConv2D([X, F, B], rng4 + [0.0, hi], fused_ops=["BiasAdd", "Relu", "Requantize"], out_type="quint8",
+                                         op_name="_ITEXQuantizedConv2DV2")
+    np.testing.assert_array_equal(host(got), ref)
+    assert (gmn, gmx) == (np.float32(0.0), np.float32(hi))
+    # LeakyRelu + Requantize to qint8
+    ref, _, _ = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, -hi, hi, out_type="qint8", relu=False, activation_name="LeakyRelu", alpha=0.25)
+    got, _, _ = ops._QuantizedConv2D([X, F, B], rng4 + [-hi, hi], fused_ops=["BiasAdd", "LeakyRelu", "Requantize"], out_type="qint8", alpha=0.25)
+    np.testing.assert_array_equal(host(got), ref)
+    # Sum + Relu + Requantize: summand right after the bias, its range before the frozen output range
+    sq = rng.integers(0, 256, ref.shape).astype(np.uint8)
+    ref, _, _ = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, 0.0, hi, out_type="quint8", relu=True, summand=sq, min_summand=0.0,
+                                   max_summand=hi * 0.5)
+    got, _, _ = ops._QuantizedConv2D([X, F, B, dev(sq)], rng4 + [0.0, hi * 0.5, 0.0, hi], fused_ops=["BiasAdd", "Sum", "Relu", "Requantize"],
+                                     out_type="quint8", Tsummand="quint8")
+    np.testing.assert_array_equal(host(got), ref)
+    # nothing fused: accumulators and their per-channel ranges
+    ref, rmn, rmx = o.quantized_conv2d(x, qf, None, mni, mxi, mnf, mxf, out_type="qint32", relu=False)
+    got, gmn, gmx = ops._QuantizedConv2D([X, F], rng4, fused_ops=[], out_type="qint32")
+    np.testing.assert_array_equal(host(got), ref)
+    np.testing.assert_array_equal(gmx, rmx)
+    with pytest.raises(itex._lib.ItexError) as e:
+        ops._QuantizedConv2D([X, F, B], rng4, fused_ops=["BiasAdd", "Mish"], out_type="qint32")
+    assert "unsupported fusion" in str(e.value)
