@@ -323,6 +323,17 @@ ITEXB_API int itexb_fp8_quantize(const void* x, int x_dtype, void* y, int fp8_dt
                                  const float* scale, float* amax, itexb_stream_t stream);
 ITEXB_API int itexb_fp8_dequantize(const void* x, int fp8_dtype, void* y, int y_dtype, int64_t n,
                                    const float* scale_inv, itexb_stream_t stream);
+/* y = fp8(gelu(x) * scale[0]), amax[0] raised to max|gelu(x)|; gelu(v) = v*(0.5 + 0.5*tanh(v*(0.79788456 + 0.03567741*v*v))).
+ * Replaces functor::Fp8Gelu (itex/core/kernels/gpu/fp8/fp8_gelu_gpu.h:29-58). */
+ITEXB_API int itexb_fp8_gelu(const void* x, int x_dtype, void* y, int fp8_dtype, int64_t n, const float* scale,
+                             float* amax, itexb_stream_t stream);
+/* Layer normalisation over the columns of x [rows, cols] with an FP8 (z_dtype FP8_E4M3|FP8_E5M2: z = fp8(v * z_scale[0]),
+ * z_amax[0] raised to max|v|) or real-valued (FLOAT|BFLOAT16|HALF, z_scale / z_amax unused) output;
+ * v = gamma * (x - mu) * rsigma + beta, mu[rows] and rsigma[rows] = rsqrt(var + epsilon) are returned.
+ * Replaces functor::Fp8LayerNormFwd (itex/core/kernels/gpu/fp8/fp8_layernorm_gpu.h:108-257). */
+ITEXB_API int itexb_fp8_layernorm(const void* x, int x_dtype, const void* gamma, const void* beta, int w_dtype, void* z,
+                                  int z_dtype, float* mu, float* rsigma, int64_t rows, int64_t cols, float epsilon,
+                                  const float* z_scale, float* z_amax, itexb_stream_t stream);
 /* Delayed-scaling update of itex/python/fp8/autocast.py:44-121 for `n` meta slots on the
  * device: amax = max over the `history_len` rows (algo 0 "max") or row 0 (algo 1
  * "most_recent"); scale from amax; roll rows by -1 and zero row 0; scale_inv = 1/scale. */

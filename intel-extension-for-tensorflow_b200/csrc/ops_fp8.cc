@@ -1,4 +1,4 @@
-// Fp8Quantize, Fp8Dequantize and Fp8Matmul.
+// Fp8Quantize, Fp8Dequantize, Fp8Matmul, Fp8Gelu and Fp8LayerNorm (forward).
 //
 // Op signatures follow itex/core/ops/fp8_ops.cc:22-61,192-226; kernels follow
 // Fp8QuantizeOp / Fp8DequantizeOp (itex/core/kernels/gpu/fp8/fp8_quantize_op.cc:24-83)
@@ -60,6 +60,80 @@ class Fp8QuantizeOp : public OpKernel {
 
  private:
   int index_ = 0, fp8_dtype_ = ITEXB_DT_FP8_E4M3;
+};
+
+// Fp8Gelu(inp, amax, scale) -> gelu_out: GELU fused with the FP8 cast (itex/core/kernels/gpu/fp8/fp8_gelu_op.cc:25-64,
+// op definition itex/core/ops/fp8_ops.cc:124-141).
+class Fp8GeluOp : public OpKernel {
+ public:
+  int Init(const AttrMap& attrs) override {
+    int64_t idx;
+    ITEXB_RETURN_IF_ERROR(attrs.GetInt("fp8_meta_index", &idx));
+    index_ = int(idx);
+    return ParseFp8Dtype(attrs, "fp8_dtype", false, &fp8_dtype_);
+  }
+  int Compute(itexb_op_context_t* ctx) override {
+    const char* op = name().c_str();
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, 3, op));
+    const itexb_tensor_t& x = ctx->inputs[0];
+    ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 0, op, "inp"));
+    ITEXB_REQUIRE(IsFloatType(x.dtype), ITEXB_INVALID_ARGUMENT, "%s: inp must be float, bfloat16 or half", op);
+    float *amax, *scale;
+    ITEXB_RETURN_IF_ERROR(MetaPointer(ctx, 1, index_, op, "amax", &amax));
+    ITEXB_RETURN_IF_ERROR(MetaPointer(ctx, 2, index_, op, "scale", &scale));
+    itexb_tensor_t y;
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 0, ITEXB_DT_INT8, x.dims, x.rank, false, &y));
+    return itexb_fp8_gelu(x.data, x.dtype, y.data, fp8_dtype_, NumElements(x), scale, amax, ctx->stream);
+  }
+
+ private:
+  int index_ = 0, fp8_dtype_ = ITEXB_DT_FP8_E4M3;
+};
+
+// Fp8LayerNorm(x, gamma, beta, z_amax, z_scale) -> z, mu, rsigma (itex/core/kernels/gpu/fp8/fp8_layernorm_op.cc:24-83,
+// op definition itex/core/ops/fp8_ops.cc:63-88).  out_dtype int8 = FP8 bytes in the fp8_dtype format; a real out_dtype
+// gives the plain normalisation and ignores z_amax / z_scale.
+class Fp8LayerNormOp : public OpKernel {
+ public:
+  int Init(const AttrMap& attrs) override {
+    int64_t idx;
+    ITEXB_RETURN_IF_ERROR(attrs.GetInt("fp8_meta_index", &idx));
+    index_ = int(idx);
+    epsilon_ = 1e-4f;
+    if (attrs.Has("epsilon")) ITEXB_RETURN_IF_ERROR(attrs.GetFloat("epsilon", &epsilon_));
+    out_dtype_ = ITEXB_DT_INT8;
+    if (attrs.Has("out_dtype")) ITEXB_RETURN_IF_ERROR(attrs.GetType("out_dtype", &out_dtype_));
+    ITEXB_REQUIRE(out_dtype_ == ITEXB_DT_INT8 || IsFloatType(out_dtype_), ITEXB_INVALID_ARGUMENT,
+                  "%s: out_dtype must be int8 (FP8 bytes), float, bfloat16 or half", name().c_str());
+    return ParseFp8Dtype(attrs, "fp8_dtype", false, &fp8_dtype_);
+  }
+  int Compute(itexb_op_context_t* ctx) override {
+    const char* op = name().c_str();
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, 5, op));
+    for (int i = 0; i < 3; ++i) ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, i, op, i == 0 ? "x" : (i == 1 ? "gamma" : "beta")));
+    const itexb_tensor_t& x = ctx->inputs[0];
+    const itexb_tensor_t& gamma = ctx->inputs[1];
+    const itexb_tensor_t& beta = ctx->inputs[2];
+    ITEXB_REQUIRE(x.rank == 2 && IsFloatType(x.dtype), ITEXB_INVALID_ARGUMENT, "%s: x must be a float, bfloat16 or half matrix", op);
+    ITEXB_REQUIRE(gamma.dtype == beta.dtype && IsFloatType(gamma.dtype) && NumElements(gamma) == x.dims[1] && NumElements(beta) == x.dims[1],
+                  ITEXB_INVALID_ARGUMENT, "%s: gamma and beta must be vectors of %lld elements of one real type", op, (long long)x.dims[1]);
+    float *amax = nullptr, *scale = nullptr;
+    if (out_dtype_ == ITEXB_DT_INT8) {
+      ITEXB_RETURN_IF_ERROR(MetaPointer(ctx, 3, index_, op, "z_amax", &amax));
+      ITEXB_RETURN_IF_ERROR(MetaPointer(ctx, 4, index_, op, "z_scale", &scale));
+    }
+    itexb_tensor_t z, mu, rs;
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 0, out_dtype_, x.dims, 2, false, &z));
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, ITEXB_DT_FLOAT, x.dims, 1, false, &mu));
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 2, ITEXB_DT_FLOAT, x.dims, 1, false, &rs));
+    return itexb_fp8_layernorm(x.data, x.dtype, gamma.data, beta.data, gamma.dtype, z.data,
+                               out_dtype_ == ITEXB_DT_INT8 ? fp8_dtype_ : out_dtype_, static_cast<float*>(mu.data),
+                               static_cast<float*>(rs.data), x.dims[0], x.dims[1], epsilon_, scale, amax, ctx->stream);
+  }
+
+ private:
+  int index_ = 0, fp8_dtype_ = ITEXB_DT_FP8_E4M3, out_dtype_ = ITEXB_DT_INT8;
+  float epsilon_ = 1e-4f;
 };
 
 class Fp8DequantizeOp : public OpKernel {
@@ -235,6 +309,8 @@ class Fp8MatmulOp : public OpKernel {
 ITEXB_REGISTER_OP("Fp8Quantize", Fp8QuantizeOp, 3, 1, 0x0u, 0x0u);
 ITEXB_REGISTER_OP("Fp8Dequantize", Fp8DequantizeOp, 2, 1, 0x0u, 0x0u);
 ITEXB_REGISTER_OP("Fp8Matmul", Fp8MatmulOp, 8, 1, 0x0u, 0x0u);
+ITEXB_REGISTER_OP("Fp8Gelu", Fp8GeluOp, 3, 1, 0x0u, 0x0u);
+ITEXB_REGISTER_OP("Fp8LayerNorm", Fp8LayerNormOp, 5, 3, 0x0u, 0x0u);
 
 }  // namespace
 }  // namespace itexb

@@ -459,7 +459,13 @@ template <bool E4M3> __device__ __forceinline__ float Fp8ToFloat(uint8_t b) {
 }
 
 // y = fp8(float(x) * scale[0]); amax[0] = max(amax[0], max|x|)
-template <typename TX, bool E4M3>
+// GELU of the FP8 path, the formula of itex/core/kernels/gpu/fp8/fp8_gelu_gpu.h:29-34.
+__device__ __forceinline__ float Fp8PathGelu(float v) {
+  return __fmul_rn(v, __fadd_rn(0.5f, __fmul_rn(0.5f, tanhf(__fmul_rn(v, __fadd_rn(0.79788456f, __fmul_rn(__fmul_rn(0.03567741f, v), v)))))));
+}
+
+// GELU = false: y = fp8(x * scale); GELU = true: y = fp8(gelu(x) * scale).  amax is raised to max|x| resp. max|gelu(x)|.
+template <typename TX, bool E4M3, bool GELU = false>
 __global__ void __launch_bounds__(kThreads) Fp8QuantizeKernel(const TX* __restrict__ x, uint8_t* __restrict__ y, long long n,
                                                               const float* __restrict__ scale, float* __restrict__ amax,
                                                               bool vec) {
@@ -474,19 +480,20 @@ __global__ void __launch_bounds__(kThreads) Fp8QuantizeKernel(const TX* __restri
       Load16<TX>(x + g * kVec, v);
 #pragma unroll
       for (int j = 0; j < kVec; ++j) {
-        m = fmaxf(m, fabsf(v[j]));
-        r[j] = FloatToFp8Sat<E4M3>(__fmul_rn(v[j], s));
+        const float f = GELU ? Fp8PathGelu(v[j]) : v[j];
+        m = fmaxf(m, fabsf(f));
+        r[j] = FloatToFp8Sat<E4M3>(__fmul_rn(f, s));
       }
       StoreBytes16(y + g * kVec, r);
     }
     for (long long i = groups * kVec + (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-      const float f = ToFloat<TX>(x[i]);
+      const float f = GELU ? Fp8PathGelu(ToFloat<TX>(x[i])) : ToFloat<TX>(x[i]);
       m = fmaxf(m, fabsf(f));
       y[i] = FloatToFp8Sat<E4M3>(__fmul_rn(f, s));
     }
   } else {
     for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-      const float f = ToFloat<TX>(x[i]);
+      const float f = GELU ? Fp8PathGelu(ToFloat<TX>(x[i])) : ToFloat<TX>(x[i]);
       m = fmaxf(m, fabsf(f));
       y[i] = FloatToFp8Sat<E4M3>(__fmul_rn(f, s));
     }
@@ -747,6 +754,30 @@ int itexb_fp8_quantize(const void* x, int x_dtype, void* y, int fp8_dtype, int64
   else return SetError(ITEXB_INVALID_ARGUMENT, "fp8_quantize: input type %s is not float/bfloat16/half", DtypeName(x_dtype));
 #undef ITEXB_FP8Q
   return CheckLaunch("Fp8QuantizeKernel");
+}
+
+int itexb_fp8_gelu(const void* x, int x_dtype, void* y, int fp8_dtype, int64_t n, const float* scale, float* amax,
+                   itexb_stream_t stream) {
+  ITEXB_REQUIRE(IsFp8(fp8_dtype), ITEXB_INVALID_ARGUMENT, "fp8_gelu: fp8_dtype must be E4M3 or E5M2");
+  ITEXB_REQUIRE(scale != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "fp8_gelu: bad arguments");
+  if (n == 0) return ITEXB_OK;
+  const bool vec = Aligned16(x) && Aligned16(y);
+  const long long work = vec ? (n + kVec - 1) / kVec : n;
+  const int blocks = int(std::max<long long>(1, std::min<long long>((work + kThreads - 1) / kThreads, (long long)SmCount() * 16)));
+  cudaStream_t st = AsCuda(stream);
+  uint8_t* yp = static_cast<uint8_t*>(y);
+  const bool e4 = fp8_dtype == ITEXB_DT_FP8_E4M3;
+#define ITEXB_FP8G(TX)                                                                                                  \
+  do {                                                                                                                  \
+    if (e4) Fp8QuantizeKernel<TX, true, true><<<blocks, kThreads, 0, st>>>(static_cast<const TX*>(x), yp, n, scale, amax, vec); \
+    else Fp8QuantizeKernel<TX, false, true><<<blocks, kThreads, 0, st>>>(static_cast<const TX*>(x), yp, n, scale, amax, vec);   \
+  } while (0)
+  if (x_dtype == ITEXB_DT_FLOAT) ITEXB_FP8G(float);
+  else if (x_dtype == ITEXB_DT_BFLOAT16) ITEXB_FP8G(__nv_bfloat16);
+  else if (x_dtype == ITEXB_DT_HALF) ITEXB_FP8G(__half);
+  else return SetError(ITEXB_INVALID_ARGUMENT, "fp8_gelu: input type %s is not float/bfloat16/half", DtypeName(x_dtype));
+#undef ITEXB_FP8G
+  return CheckLaunch("Fp8GeluKernel");
 }
 
 int itexb_fp8_dequantize(const void* x, int fp8_dtype, void* y, int y_dtype, int64_t n, const float* scale_inv,

@@ -26,7 +26,7 @@ _NAME_TO_DT = {
 _TORCH_TO_DT = {torch.float32: L.DT_FLOAT, torch.bfloat16: L.DT_BFLOAT16, torch.float16: L.DT_HALF,
                 torch.int8: L.DT_QINT8, torch.uint8: L.DT_QUINT8, torch.int32: L.DT_QINT32}
 _TYPE_ATTRS = {"T", "T1", "T2", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype",
-               "in_dtype", "Tsummand", "Targs", "Tout", "U"}
+               "in_dtype", "Tsummand", "Targs", "Tout", "U", "weight_dtype"}
 
 
 def as_dtype(v):
@@ -409,6 +409,19 @@ def Fp8Quantize(x, x_amax, x_scale, fp8_meta_index, fp8_dtype="E4M3"):
     """-> y (int8 tensor holding fp8 bytes); x_amax[fp8_meta_index] is raised in place."""
     op = _cached("Fp8Quantize", dict(in_dtype=_TORCH_TO_DT[x.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
     return op(x, x_amax, x_scale)
+
+
+def Fp8Gelu(inp, amax, scale, fp8_meta_index, fp8_dtype="E4M3"):
+    """-> gelu_out (int8 tensor holding fp8 bytes of gelu(inp) * scale); amax[fp8_meta_index] is raised in place."""
+    op = _cached("Fp8Gelu", dict(in_dtype=_TORCH_TO_DT[inp.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
+    return op(inp, amax, scale)
+
+
+def Fp8LayerNorm(x, gamma, beta, z_amax, z_scale, fp8_meta_index, epsilon=1e-4, fp8_dtype="E4M3", out_dtype="int8"):
+    """-> (z, mu, rsigma); z is FP8 bytes (out_dtype int8) or a real tensor."""
+    op = _cached("Fp8LayerNorm", dict(in_dtype=_TORCH_TO_DT[x.dtype], weight_dtype=_TORCH_TO_DT[gamma.dtype], out_dtype=out_dtype,
+                                      fp8_meta_index=int(fp8_meta_index), epsilon=float(epsilon), fp8_dtype=fp8_dtype))
+    return op(x, gamma, beta, z_amax, z_scale)
 
 
 def Fp8Dequantize(x, x_scale_inv, fp8_meta_index, fp8_dtype="E4M3", out_dtype="float"):

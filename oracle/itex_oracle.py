@@ -660,6 +660,38 @@ def fp8_quantize(x, amax_row0: np.ndarray, scale: np.ndarray, fp8_meta_index: in
     return fp8_cast_sat((t * f32(scale[fp8_meta_index])).astype(np.float32), fp8_dtype)
 
 
+def fp8_gelu(x, amax_row0: np.ndarray, scale: np.ndarray, fp8_meta_index: int, fp8_dtype: str = "E4M3") -> np.ndarray:
+    """Fp8Gelu: functor::Fp8Gelu over PointWiseKernel (itex/core/kernels/gpu/fp8/fp8_gelu_gpu.h:29-58,
+    vectorized_pointwise.h:43-77): g = gelu(x) in fp32, amax raised to max|g|, y = fp8(g * scale).  Parity unpinned."""
+    v = _as_f32(x).astype(np.float64)
+    g = (v * (0.5 + 0.5 * np.tanh(v * (0.79788456 + 0.03567741 * v * v)))).astype(np.float32)
+    amax_row0[fp8_meta_index] = max(f32(amax_row0[fp8_meta_index]), f32(np.abs(g).max())) if g.size else amax_row0[fp8_meta_index]
+    return fp8_cast_sat((g * f32(scale[fp8_meta_index])).astype(np.float32), fp8_dtype)
+
+
+def fp8_layernorm(x, gamma, beta, amax_row0: Optional[np.ndarray], scale: Optional[np.ndarray], fp8_meta_index: int, *,
+                  epsilon: float = 1e-4, fp8_dtype: str = "E4M3", out_dtype: str = "int8"):
+    """Fp8LayerNorm forward (itex/core/kernels/gpu/fp8/fp8_layernorm_gpu.h:108-257): per row mu = mean(x),
+    rsigma = rsqrt(mean((x - mu)^2) + epsilon), v = gamma * (rsigma * (x - mu)) + beta; FP8 output: amax raised to
+    max|v|, z = fp8(v * scale); real output: z = v.  Sums in float64 then rounded (the device sums fp32 in tree order).
+    Returns (z, mu, rsigma).  Parity unpinned."""
+    xf = _as_f32(x).astype(np.float64)
+    mu = xf.mean(axis=1)
+    var = ((xf - mu[:, None]) ** 2).mean(axis=1)
+    rs = 1.0 / np.sqrt(var + np.float64(f32(epsilon)))
+    v = (_as_f32(gamma).astype(np.float64) * (rs[:, None] * (xf - mu[:, None])) + _as_f32(beta).astype(np.float64)).astype(np.float32)
+    if out_dtype == "int8":
+        amax_row0[fp8_meta_index] = max(f32(amax_row0[fp8_meta_index]), f32(np.abs(v).max()))
+        z = fp8_cast_sat((v * f32(scale[fp8_meta_index])).astype(np.float32), fp8_dtype)
+    elif out_dtype == "bfloat16":
+        z = to_bf16_rne(v)
+    elif out_dtype == "half":
+        z = v.astype(np.float16)
+    else:
+        z = v
+    return z, mu.astype(np.float32), rs.astype(np.float32)
+
+
 def fp8_dequantize(q, scale_inv: np.ndarray, fp8_meta_index: int, fp8_dtype: str = "E4M3",
                    out_dtype: str = "float") -> np.ndarray:
     """Fp8Dequantize (fp8_quantize_op.cc:53-83): y = out_dtype(float(q)*scale_inv[i])."""

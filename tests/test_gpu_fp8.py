@@ -147,3 +147,40 @@ def test_column_parallel_shards_reassemble_the_full_product():
         assert bool((torch.cat(outs, dim=1) == ref).all())
         assert bool((shards[0].meta.amax_history == full.meta.amax_history).all())
         assert bool((shards[-1].meta.scale == full.meta.scale).all())
+
+
+def test_fp8_gelu_and_layernorm():
+    """Fp8Gelu and Fp8LayerNorm against the restatement: FP8 outputs within one FP8 step (1e-2 relative is the bar; the
+    device's tanh / rsqrt and fp32 summation order differ from the float64 restatement in the last bits, which can move a
+    value across an FP8 rounding boundary), real outputs and the row statistics at 1e-5."""
+    itex, K, ops = modules()
+    rng = np.random.default_rng(33)
+    x = (rng.standard_normal((300, 1000)) * 2).astype(np.float32)
+    for dt in (torch.float32, torch.bfloat16):
+        X = torch.from_numpy(x).to(dt).cuda()
+        amax = torch.zeros(3, device="cuda")
+        scale = torch.tensor([1.0, 16.0, 0.5], device="cuda")
+        y = ops.Fp8Gelu(X, amax, scale, 1, "E4M3")
+        ref_amax = np.zeros(3, np.float32)
+        ref = o.fp8_gelu(host(X), ref_amax, host(scale), 1, "E4M3")
+        got_f, ref_f = o.fp8_to_f32(host(y).view(np.uint8), "E4M3"), o.fp8_to_f32(ref, "E4M3")
+        assert (host(y).view(np.uint8) != ref).mean() < 2e-3
+        np.testing.assert_allclose(got_f, ref_f, rtol=0.13, atol=2e-3)        # at most the neighbouring FP8 value
+        np.testing.assert_allclose(float(amax[1]), float(ref_amax[1]), rtol=1e-6)
+        assert float(amax[0]) == 0.0 and float(amax[2]) == 0.0
+    gamma = (1 + 0.1 * rng.standard_normal(1000)).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(1000)).astype(np.float32)
+    X, G, B = dev(x), dev(gamma), dev(beta)
+    z, mu, rs = ops.Fp8LayerNorm(X, G, B, torch.zeros(1, device="cuda"), torch.ones(1, device="cuda"), 0, epsilon=1e-5, out_dtype="float")
+    zr, mur, rsr = o.fp8_layernorm(x, gamma, beta, None, None, 0, epsilon=1e-5, out_dtype="float")
+    np.testing.assert_allclose(host(mu), mur, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(host(rs), rsr, rtol=1e-5)
+    np.testing.assert_allclose(host(z), zr, rtol=1e-5, atol=1e-5)
+    amax = torch.zeros(2, device="cuda")
+    scale = torch.tensor([1.0, 32.0], device="cuda")
+    z8, mu, rs = ops.Fp8LayerNorm(X.to(torch.bfloat16), G, B, amax, scale, 1, epsilon=1e-5, fp8_dtype="E4M3")
+    ref_amax = np.zeros(2, np.float32)
+    z8r, _, _ = o.fp8_layernorm(host(X.to(torch.bfloat16)), gamma, beta, ref_amax, host(scale), 1, epsilon=1e-5)
+    assert z8.dtype == torch.int8 and (host(z8).view(np.uint8) != z8r).mean() < 2e-3
+    np.testing.assert_allclose(o.fp8_to_f32(host(z8).view(np.uint8), "E4M3"), o.fp8_to_f32(z8r, "E4M3"), rtol=0.13, atol=2e-3)
+    np.testing.assert_allclose(float(amax[1]), float(ref_amax[1]), rtol=1e-5)
