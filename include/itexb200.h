@@ -160,6 +160,13 @@ ITEXB_API int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_
                                      const float* minmax, float ensure_minimum_range, float* out3,
                                      itexb_stream_t stream);
 
+/* itexb_quantize_dynamic that also writes the consuming matmul's per-output-channel scales (what
+ * itexb_matmul_scales_dynamic computes: scales[j] for j < n_scales from weight_range[j]), saving a launch. */
+ITEXB_API int itexb_quantize_dynamic_scales(const void* x, int x_dtype, void* q, int q_dtype, int64_t n,
+                                            const float* minmax, float ensure_minimum_range, float* out3,
+                                            const float* weight_range, int32_t n_scales, float* scales,
+                                            itexb_stream_t stream);
+
 /* Per-output-channel scale of the fused matmul ops, computed on the device from a device-resident
  * activation range: scales[j] = (max(|out_min|,|out_max|) * weight_range[j]) / (max_int8(a_dtype) * 127),
  * range3 = the {scale, out_min, out_max} itexb_quantize_dynamic wrote, weight_range[j] =

@@ -4,9 +4,9 @@ What an INC-quantized, ITEX-rewritten BERT contains per layer is four fused int8
 per-tensor activation ranges (QKV, attention output, FFN up with GELU, FFN down): in the reference each is
 a Min/Max reduction, a copy of the two scalars to the host (the ranges are HostMemory inputs), `_ITEXQuantizeV2`
 and `_ITEXQuantizedMatMul` (fused_ops BiasAdd [+ GeluApproximate] + Dequantize, per-channel int8 weights,
-int8 activations).  Here the range stays on the device: `itexb_minmax`, `itexb_quantize_dynamic`,
-`itexb_matmul_scales_dynamic` and the GEMM are four stream-ordered launches with no host round trip, so a
-whole forward pass can be replayed as one CUDA graph.  The arithmetic is the reference's
+int8 activations).  Here the range stays on the device: `itexb_minmax`, `itexb_quantize_dynamic_scales` (which
+also derives the matmul's per-channel scales) and the GEMM are stream-ordered launches with no host round trip,
+so a whole forward pass can be replayed as one CUDA graph.  The arithmetic is the reference's
 (QuantizeV2 SCALED, per-channel scale range_input*range_weight/(127*127), bias added after scaling in real
 units); the per-node tests compare every int8 node with the oracle.
 
@@ -36,8 +36,7 @@ class Int8Linear:
     def __call__(self, x, trace=None):
         """x: [tokens, k] float32 or bfloat16 on the device -> [tokens, n] in out_dtype."""
         mm = K.minmax(x, out=self.minmax)
-        q, range3 = K.quantize_dynamic(x, L.DT_QINT8, mm)
-        sc = K.matmul_scales_dynamic(range3, self.weight_range, L.DT_QINT8, out=self.scales)
+        q, range3, sc = K.quantize_dynamic(x, L.DT_QINT8, mm, weight_range=self.weight_range, scales=self.scales)
         ep = K.make_epilogue(scale=sc, bias=self.bias, activation=L.ACT_GELU_TANH if self.gelu else L.ACT_NONE)
         y = K.gemm(q, self.w_nk, self.out_dtype, ep=ep, k=self.k)
         if trace is not None:

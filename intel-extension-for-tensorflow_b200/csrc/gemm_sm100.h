@@ -22,6 +22,7 @@ struct GemmArgs {
   int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)
   int out_esz;          // bytes per output element (set by LaunchGemm)
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
+  int group_m;          // tile rows per rasterisation group (set by LaunchGemm)
   // Implicit-GEMM convolution (conv_mode != kConvNone): row m of A is output pixel m of the NHWC tensor
   // conv_x; column k = tap * conv_cpad + channel, tap = ky * kw + kx.  kConvGather: conv_cpad == conv_c and
   // four extra warps gather the A tile with cp.async.  kConvIm2col: conv_cpad is conv_c rounded up to 128

@@ -421,10 +421,17 @@ __device__ __forceinline__ void DynamicScale(const float* mm, float emr, bool is
 template <typename TX, bool SIGNED>
 __global__ void __launch_bounds__(kThreads) QuantizeDynamicKernel(const TX* __restrict__ x, uint8_t* __restrict__ q,
                                                                   long long n, const float* __restrict__ mm, float emr,
-                                                                  float* __restrict__ out3) {
+                                                                  float* __restrict__ out3, const float* __restrict__ weight_range,
+                                                                  int n_scales, float* __restrict__ scales) {
   float s, omin, omax;
   DynamicScale(mm, emr, SIGNED, &s, &omin, &omax);
   if (blockIdx.x == 0 && threadIdx.x == 0 && out3 != nullptr) { out3[0] = s; out3[1] = omin; out3[2] = omax; }
+  if (blockIdx.x == 0 && scales != nullptr) {
+    // the consuming matmul's per-channel output scales (same formula as MatMulScalesDynamicKernel)
+    const float range_input = fmaxf(fabsf(omin), fabsf(omax));
+    const float denom = __fmul_rn(SIGNED ? 127.f : 255.f, 127.f);
+    for (int j = threadIdx.x; j < n_scales; j += kThreads) scales[j] = __fdiv_rn(__fmul_rn(range_input, weight_range[j]), denom);
+  }
   const long long i0 = ((long long)blockIdx.x * kThreads + threadIdx.x) * kVec;
   if (i0 >= n) return;
   if (i0 + kVec <= n) {
@@ -674,6 +681,14 @@ int itexb_minmax(const void* x, int x_dtype, int64_t n, float* minmax, itexb_str
 
 int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_dtype, int64_t n, const float* minmax,
                            float ensure_minimum_range, float* out3, itexb_stream_t stream) {
+  return itexb_quantize_dynamic_scales(x, x_dtype, q, q_dtype, n, minmax, ensure_minimum_range, out3, nullptr, 0, nullptr, stream);
+}
+
+int itexb_quantize_dynamic_scales(const void* x, int x_dtype, void* q, int q_dtype, int64_t n, const float* minmax,
+                                  float ensure_minimum_range, float* out3, const float* weight_range, int32_t n_scales,
+                                  float* scales, itexb_stream_t stream) {
+  ITEXB_REQUIRE(scales == nullptr || (weight_range != nullptr && n_scales > 0), ITEXB_INVALID_ARGUMENT,
+                "quantize_dynamic_scales: scales needs weight_range and a positive count");
   ITEXB_REQUIRE(IsInt8(q_dtype), ITEXB_INVALID_ARGUMENT, "quantize_dynamic: output type %s is not qint8/quint8",
                 DtypeName(q_dtype));
   ITEXB_REQUIRE(minmax != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "quantize_dynamic: bad arguments");
@@ -685,12 +700,12 @@ int itexb_quantize_dynamic(const void* x, int x_dtype, void* q, int q_dtype, int
   uint8_t* qp = static_cast<uint8_t*>(q);
   if (x_dtype == ITEXB_DT_FLOAT) {
     auto xp = static_cast<const float*>(x);
-    if (sg) QuantizeDynamicKernel<float, true><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
-    else QuantizeDynamicKernel<float, false><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
+    if (sg) QuantizeDynamicKernel<float, true><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3, weight_range, n_scales, scales);
+    else QuantizeDynamicKernel<float, false><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3, weight_range, n_scales, scales);
   } else if (x_dtype == ITEXB_DT_BFLOAT16) {
     auto xp = static_cast<const __nv_bfloat16*>(x);
-    if (sg) QuantizeDynamicKernel<__nv_bfloat16, true><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
-    else QuantizeDynamicKernel<__nv_bfloat16, false><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3);
+    if (sg) QuantizeDynamicKernel<__nv_bfloat16, true><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3, weight_range, n_scales, scales);
+    else QuantizeDynamicKernel<__nv_bfloat16, false><<<grid, kThreads, 0, st>>>(xp, qp, n, minmax, ensure_minimum_range, out3, weight_range, n_scales, scales);
   } else {
     return SetError(ITEXB_INVALID_ARGUMENT, "quantize_dynamic: input type %s is not float/bfloat16", DtypeName(x_dtype));
   }

@@ -162,14 +162,19 @@ def minmax(x, out=None):
     return mm
 
 
-def quantize_dynamic(x, q_dtype, mm, ensure_minimum_range=0.01):
-    _require_cuda(x, mm)
+def quantize_dynamic(x, q_dtype, mm, ensure_minimum_range=0.01, weight_range=None, scales=None):
+    """QuantizeV2 SCALED with the range read from the device tensor mm; -> (q, {scale, out_min, out_max}).  With
+    weight_range (and optionally a preallocated scales) the consuming matmul's per-channel scales are written too."""
+    _require_cuda(x, mm, weight_range, scales)
     x = x.contiguous()
     q = torch.empty(x.shape, dtype=torch_dtype(q_dtype), device=x.device)
     out3 = torch.empty(3, dtype=torch.float32, device=x.device)
-    L.check(L.load().itexb_quantize_dynamic(_ptr(x), dt_of(x), _ptr(q), q_dtype, C.c_int64(x.numel()), _ptr(mm),
-                                            C.c_float(ensure_minimum_range), _ptr(out3), stream_ptr()))
-    return q, out3
+    if weight_range is not None and scales is None:
+        scales = torch.empty(weight_range.numel(), dtype=torch.float32, device=x.device)
+    L.check(L.load().itexb_quantize_dynamic_scales(_ptr(x), dt_of(x), _ptr(q), q_dtype, C.c_int64(x.numel()), _ptr(mm),
+                                                   C.c_float(ensure_minimum_range), _ptr(out3), _ptr(weight_range),
+                                                   0 if weight_range is None else weight_range.numel(), _ptr(scales), stream_ptr()))
+    return (q, out3) if weight_range is None else (q, out3, scales)
 
 
 def matmul_scales_dynamic(range3, weight_range, a_dtype, out=None):
