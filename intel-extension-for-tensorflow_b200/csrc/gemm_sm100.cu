@@ -1,25 +1,30 @@
 // int8 / FP8 GEMM for sm_100a: out[m][n] = epilogue(sum_k a[m][k] * b[n][k]).
 //
-// One persistent CTA per SM (384 threads), warp-specialised:
-//   warp 0    TMA producer   cp.async.bulk.tensor (2-D tiled, 128-byte swizzle) -> smem ring of
-//                            128 x 128-byte A tiles and BN x 128-byte B tiles
-//   warp 1    MMA issuer     tcgen05.mma.cta_group::1.kind::i8 | kind::f8f6f4, 128 x BN x 32 per
-//                            instruction, operands read from smem through UMMA descriptors,
-//                            accumulators (s32 | f32) in tensor memory
-//   warp 2    TMEM allocator (2 accumulator stages of BN columns, so the epilogue of tile i
-//                            overlaps the main loop of tile i+1)
-//   warps 4-11 epilogue      two warps per TMEM lane quarter; each takes every other 32-column
-//                            block: tcgen05.ld (32 lanes x 32 columns) -> scale / bias / sum /
-//                            ReLU -> conversion -> swizzled staging tile in smem -> one TMA
-//                            store per 32 x 32 block (direct stores when rows are unaligned)
+// One persistent CTA per SM (640 threads; 768 in the cp.async convolution variant), warp-specialised:
+//   warp 0      TMA producer   cp.async.bulk.tensor -> smem ring of 128 x 128-byte A tiles and BN x 128-byte
+//                              B tiles (128-byte swizzle).  A is a 2-D tiled load of a matrix or, for
+//                              convolutions, a 4-D im2col load of the NHWC input (one filter tap x 128
+//                              channels per k-block)
+//   warp 1      MMA issuer     tcgen05.mma.cta_group::1.kind::i8 | kind::f8f6f4, 128 x BN x 32 per
+//                              instruction, operands read from smem through UMMA descriptors,
+//                              accumulators (s32 | f32) in tensor memory
+//   warp 2      TMEM allocator (2 accumulator stages of BN columns, so the epilogue of tile i
+//                              overlaps the main loop of tile i+1)
+//   warps 4-19  epilogue       four warps per TMEM lane quarter (= four per scheduler); each takes every
+//                              fourth column block: tcgen05.ld (32 lanes x 16 columns) -> scale / bias
+//                              (staged in smem per tile column) / sum / ReLU / activation -> conversion ->
+//                              swizzled staging tile in smem -> one TMA store per block (direct stores
+//                              when rows are unaligned)
+//   warps 20-23 (convolutions with densely packed filters only) gather the A tile with cp.async
 // Pipelines are mbarrier based: full[s]/empty[s] between producer and MMA issuer
 // (tcgen05.commit releases a stage), tmem_full[a]/tmem_empty[a] between MMA issuer and
 // epilogue.  Every wait is bounded: on expiry the kernel raises a status word, all roles
 // leave their loops, TMEM is released and the kernel returns.
 //
-// Epilogue arithmetic avoids the conversion instructions (int<->float on the multi-function
-// unit is the slowest pipe of this part and was the measured bottleneck): both directions use
-// the exact 1.5*2^23 adder trick, with the real conversion kept for accumulators beyond 2^22.
+// Epilogue arithmetic: int->float uses the exact 1.5*2^23 adder trick (the conversion instructions
+// run on the multi-function unit, the slowest pipe of this part and the first measured bottleneck),
+// with the real conversion kept for accumulators beyond 2^22; float->8-bit is one saturating
+// conversion per element.  Multiply and add stay separate roundings (bit-exactness with oneDNN).
 //
 // No cluster launch and no multicast loads are used, so the same code runs unchanged in
 // single- and multi-GPU jobs.
