@@ -1,15 +1,19 @@
 // NHWC x HWIO int8 convolution for sm_100a, lowered onto the tcgen05 GEMM kernel.
 //
-// Three lowerings share the MMA main loop and the fused epilogue:
+// Four lowerings share the MMA main loop and the fused epilogue; itexb_conv2d picks one from the geometry
+// and the channel pitch of the packed filter:
 //   * pointwise (1x1, stride 1, no padding, channels a multiple of 16): the input IS the
 //     [n*h*w, c] A operand; nothing is staged.
-//   * implicit GEMM (channels a multiple of 16): four extra warps of the GEMM kernel gather the A
-//     tile of each k-block straight from the NHWC input with 16-byte cp.async copies (zero fill for
-//     padding) into the swizzled shared-memory layout; nothing is staged in global memory.
-//   * other channel counts (e.g. an RGB stem): a gather kernel writes the [n*oh*ow, round_up(kh*kw*c, 16)] patch matrix (zero
-//     fill for padding) into caller-provided scratch - 16 bytes per thread when c is a multiple
-//     of 16, one contiguous filter-row run per thread otherwise - then the GEMM runs on it.  Scratch traffic is kh*kw times the input; the caller sizes it with
-//     itexb_conv2d_workspace_bytes().
+//   * TMA im2col (channels a multiple of 16, filter taps packed at a pitch of c rounded up to 128): the
+//     producer thread issues one 4-D im2col tensor load per k-block - 128 output pixels x 128 channels of one
+//     filter tap - from a tensor map whose pixel bounding box and traversal strides describe the convolution;
+//     padding, rows past the end and channels past c read as zeros.  No scratch, no gather instructions.
+//   * cp.async gather (channels a multiple of 16, densely packed filter): four extra warps of the GEMM
+//     kernel copy the A tile of each k-block from the NHWC input in 16-byte pieces (zero fill for padding)
+//     into the swizzled shared-memory layout.  No scratch either.
+//   * other channel counts (e.g. an RGB stem): a gather kernel writes the [n*oh*ow, round_up(kh*kw*c, 16)]
+//     patch matrix (zero fill for padding) into caller-provided scratch, then the GEMM runs on it.  Scratch
+//     traffic is kh*kw times the input; the caller sizes it with itexb_conv2d_workspace_bytes().
 #include <algorithm>
 #include <mutex>
 
