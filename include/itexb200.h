@@ -254,6 +254,12 @@ typedef struct itexb_gemm_params {
   void* out;     int64_t ldo;
   itexb_epilogue_t ep;
   int32_t* status_word;
+  /* Batched form (0 or 1 = a single GEMM): `batch` independent products with the same m, n, k and epilogue;
+   * batch i reads a + i*stride_a, b + i*stride_b (elements = bytes; positive multiples of 16) and
+   * writes out + i*stride_out elements (a multiple of ldo, at least m*ldo).  A summand follows out's layout.
+   * Replaces the batched dnnl::matmul of BatchMatMulOp (itex/core/kernels/common/batch_matmul_op.h). */
+  int32_t batch;
+  int64_t stride_a, stride_b, stride_out;
 } itexb_gemm_params_t;
 ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
 

@@ -48,7 +48,8 @@ class GemmParams(C.Structure):
     _fields_ = [("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("a_dtype", C.c_int32),
                 ("b_dtype", C.c_int32), ("out_dtype", C.c_int32), ("a", C.c_void_p), ("lda", C.c_int64),
                 ("b", C.c_void_p), ("ldb", C.c_int64), ("out", C.c_void_p), ("ldo", C.c_int64),
-                ("ep", Epilogue), ("status_word", C.c_void_p)]
+                ("ep", Epilogue), ("status_word", C.c_void_p), ("batch", C.c_int32), ("stride_a", C.c_int64),
+                ("stride_b", C.c_int64), ("stride_out", C.c_int64)]
 
 
 class ConvParams(C.Structure):

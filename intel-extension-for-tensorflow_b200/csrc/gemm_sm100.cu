@@ -116,6 +116,12 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile
 
 template <int N> __device__ __forceinline__ void CpAsyncWaitGroup() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+__device__ __forceinline__ void TmaLoad3d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void TmaLoad2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
@@ -175,7 +181,13 @@ __device__ __forceinline__ uint64_t UmmaDescSw128(uint32_t smem_addr) {
 
 // Tile rasterisation: the tile grid is walked in super-groups of group_m tile rows, column by column inside a
 // group, so that the 148 tiles in flight share operand panels in L2.
-__device__ __forceinline__ void TileCoords(int t, int tiles_m, int tiles_n, int group_m, int* tm, int* tn) {
+// A batched launch lays the batches' tile grids one after the other.
+__device__ __forceinline__ void TileCoords(int t, int tiles_m, int tiles_n, int group_m, int* tm, int* tn, int* batch = nullptr) {
+  if (batch != nullptr) {
+    const int per_batch = tiles_m * tiles_n;
+    *batch = t / per_batch;
+    t -= *batch * per_batch;
+  }
   const int per_group = group_m * tiles_n;
   const int g = t / per_group;
   const int first_m = g * group_m;
@@ -328,6 +340,11 @@ __device__ __forceinline__ void TmemLdWait16(uint32_t (&r)[16]) {
                : "memory");
 }
 
+__device__ __forceinline__ void TmaStore3d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap), "r"(src_smem), "r"(c0),
+               "r"(c1), "r"(c2)
+               : "memory");
+}
 __device__ __forceinline__ void TmaStore2d(const void* tmap, uint32_t src_smem, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src_smem), "r"(c0),
                "r"(c1)
@@ -444,8 +461,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   uint32_t reloads = 0;
 
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-    int tm, tn;
-    TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn);
+    int tm, tn, bt;
+    TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn, &bt);
     if (staged && tn != last_tn) {
       bool pok = true;
       if (reloads > 0) pok = MbarWait(SmemAddr(&par_bar[1]), (reloads - 1) & 1, abort_flag, g.status_word, kErrEpilogue);
@@ -469,8 +486,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
     TcFenceAfter();
     const int row0 = tm * kBM + q * 32;  // first row of this warp's 32-row block
-    const long long row = (long long)row0 + lane;
-    const bool row_ok = row < g.m;
+    const bool row_ok = row0 + lane < g.m;
+    const long long row = (long long)bt * g.batch_rows_out + row0 + lane;  // row of `out` / the summand across batches
     const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
     const int nblocks = min(BN / bcols, (g.n - tn * BN + bcols - 1) / bcols);  // blocks holding real columns
     if (row0 < g.m) {
@@ -608,7 +625,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
           FenceProxyAsyncShared();
           __syncwarp();
           if (lane == 0) {
-            TmaStore2d(tma_out, SmemAddr(buf), col0 * esz, row0);  // rows >= m and columns >= n are clipped
+            TmaStore3d(tma_out, SmemAddr(buf), col0 * esz, row0, bt);  // rows >= m and columns >= n are clipped
             TmaStoreCommit();
           }
           ++seq;
@@ -666,7 +683,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   const int lane = threadIdx.x & 31;
   const int tiles_m = (g.m + kBM - 1) / kBM;
   const int tiles_n = (g.n + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = tiles_m * tiles_n * g.batch;
   const int num_kb = (g.k + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
@@ -698,8 +715,8 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     uint32_t phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int tm, tn;
-      TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn);
+      int tm, tn, bt;
+      TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn, &bt);
       int w0 = 0, h0 = 0, n0 = 0, c0 = 0, kx = 0, ky = 0;  // im2col: base position of the tile's first pixel, position in K
       if (CONV == kConvIm2col) {
         const int pix = tm * kBM;
@@ -722,9 +739,9 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
           if (c0 >= g.conv_cpad) { c0 = 0; if (++kx == g.kw) { kx = 0; ++ky; } }
         } else {
           MbarArriveExpectTx(fb, C::kStageBytes);
-          TmaLoad2d(SmemAddr(sa), &tma_a, fb, kb * kBK, tm * kBM);
+          TmaLoad3d(SmemAddr(sa), &tma_a, fb, kb * kBK, tm * kBM, bt);
         }
-        TmaLoad2d(SmemAddr(sa + C::kABytes), &tma_b, fb, kb * kBK, tn * BN);
+        TmaLoad3d(SmemAddr(sa + C::kABytes), &tma_b, fb, kb * kBK, tn * BN, bt);
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -901,7 +918,7 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
     ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     last_dev = dev;
   }
-  const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN);
+  const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN) * g.batch;
   const int grid = std::max(1, std::min(tiles, SmCount()));
   GemmKernel<BN, F8, CONV><<<grid, CONV == kConvGather ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
   return CheckLaunch("GemmKernel");
@@ -909,14 +926,16 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
 
 }  // namespace
 
-int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows, int64_t batch,
+                     int64_t batch_stride) {
   EncodeTiledFn enc = GetEncodeTiled();
   ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
-  const cuuint64_t strides[1] = {cuuint64_t(ld)};
-  const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(box_rows)};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+  if (batch <= 1) { batch = 1; batch_stride = rows * ld; }
+  const cuuint64_t dims[3] = {cuuint64_t(k), cuuint64_t(rows), cuuint64_t(batch)};
+  const cuuint64_t strides[2] = {cuuint64_t(ld), cuuint64_t(batch_stride)};
+  const cuuint32_t box[3] = {cuuint32_t(kBK), cuuint32_t(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld k=%lld ld=%lld)",
@@ -959,15 +978,15 @@ int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p) {
 // Tensor map for the epilogue's TMA stores: the output as a byte matrix {n*esz, m} with
 // row pitch ldo*esz, box = one warp block of 32 rows x 16 (4-byte) or 32 (narrower) elements,
 // swizzle matching the staging tile's row width (64 or 32 bytes).
-static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz) {
+static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz, int64_t batch, int64_t batch_rows) {
   EncodeTiledFn enc = GetEncodeTiled();
   ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  const cuuint64_t dims[2] = {cuuint64_t(n) * esz, cuuint64_t(m)};
-  const cuuint64_t strides[1] = {cuuint64_t(ldo) * esz};
-  const cuuint32_t box[2] = {cuuint32_t(esz == 1 ? 32 : 64), 32};
-  const cuuint32_t estr[2] = {1, 1};
+  const cuuint64_t dims[3] = {cuuint64_t(n) * esz, cuuint64_t(m), cuuint64_t(batch)};
+  const cuuint64_t strides[2] = {cuuint64_t(ldo) * esz, cuuint64_t(batch_rows) * ldo * esz};
+  const cuuint32_t box[3] = {cuuint32_t(esz == 1 ? 32 : 64), 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapSwizzle sw = esz == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B;
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled (output) failed with CUresult %d", int(r));
   return ITEXB_OK;
@@ -1013,7 +1032,8 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   g.vec_store = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (g.ldo * g.out_esz) % 16 == 0) ? 1 : 0;
   g.tma_store = g.vec_store;
   CUtensorMap to;
-  if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz));
+  if (g.batch <= 1) { g.batch = 1; g.batch_rows_out = g.m; }
+  if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, g.batch, g.batch_rows_out));
   else to = ta;  // unused by the kernel
   if (g.conv_mode == kConvGather) {
     if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, g, st);
@@ -1083,11 +1103,21 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   ITEXB_REQUIRE(p->lda % 16 == 0 && p->ldb % 16 == 0 && (reinterpret_cast<uintptr_t>(p->a) & 15) == 0 &&
                     (reinterpret_cast<uintptr_t>(p->b) & 15) == 0,
                 ITEXB_INVALID_ARGUMENT, "gemm: a and b must be 16-byte aligned with lda/ldb multiples of 16 (TMA rule)");
+  const int64_t batch = p->batch > 1 ? p->batch : 1;
+  if (batch > 1) {
+    ITEXB_REQUIRE(p->stride_a % 16 == 0 && p->stride_b % 16 == 0 && p->stride_a > 0 && p->stride_b > 0, ITEXB_INVALID_ARGUMENT,
+                  "gemm: batch strides of a and b must be positive multiples of 16 bytes");
+    ITEXB_REQUIRE(p->stride_out >= int64_t(p->m) * p->ldo && p->stride_out % p->ldo == 0, ITEXB_INVALID_ARGUMENT,
+                  "gemm: stride_out must be a multiple of ldo and at least m*ldo");
+    ITEXB_REQUIRE(batch * ((p->m + kBM - 1) / kBM) * ((p->n + 63) / 64) < (1ll << 31), ITEXB_INVALID_ARGUMENT, "gemm: too many tiles");
+  }
   CUtensorMap ta, tb;
   const int bn = PickBN(p->n);
-  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, p->a, p->m, p->k, p->lda, kBM));
-  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->b, p->n, p->k, p->ldb, bn));
+  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, p->a, p->m, p->k, p->lda, kBM, batch, p->stride_a));
+  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->b, p->n, p->k, p->ldb, bn, batch, p->stride_b));
   GemmArgs g{};
+  g.batch = int(batch);
+  g.batch_rows_out = batch > 1 ? p->stride_out / p->ldo : p->m;
   g.m = p->m; g.n = p->n; g.k = p->k;
   g.out_dtype = p->out_dtype;
   g.out = p->out; g.ldo = p->ldo;

@@ -23,6 +23,8 @@ struct GemmArgs {
   int out_esz;          // bytes per output element (set by LaunchGemm)
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
   int group_m;          // tile rows per rasterisation group (set by LaunchGemm)
+  int batch;            // independent GEMMs in this launch (third coordinate of the tensor maps); 0 is read as 1
+  long long batch_rows_out;  // rows of `out` (and of the summand) from one batch to the next
   // Implicit-GEMM convolution (conv_mode != kConvNone): row m of A is output pixel m of the NHWC tensor
   // conv_x; column k = tap * conv_cpad + channel, tap = ky * kw + kx.  kConvGather: conv_cpad == conv_c and
   // four extra warps gather the A tile with cp.async.  kConvIm2col: conv_cpad is conv_c rounded up to 128
@@ -38,9 +40,11 @@ enum : int { kConvNone = 0, kConvGather = 1, kConvIm2col = 2 };
 // 4-D im2col tensor map over an NHWC 8-bit tensor: box = 128 channels x 128 pixels, 128-byte swizzle,
 // zero fill outside; the pixel bounding box and traversal strides describe the convolution.
 int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p);
-// 2-D tiled tensor map over a K-major 8-bit operand: dims {k, rows}, row pitch `ld` bytes,
-// box {128 bytes, box_rows}, 128-byte swizzle, zero fill outside.
-int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
+// 3-D tiled tensor map over a (batched) K-major 8-bit operand: dims {k, rows, batch}, row pitch `ld` bytes, batch pitch
+// batch_stride bytes, box {128 bytes, box_rows, 1}, 128-byte
+// swizzle, zero fill outside.
+int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows, int64_t batch = 1,
+                     int64_t batch_stride = 0);
 unsigned MakeInstrDesc(int a_dtype, int b_dtype, int bn);
 int PickBN(int n);
 int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st);

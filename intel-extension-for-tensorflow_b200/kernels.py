@@ -103,22 +103,27 @@ def make_epilogue(scale=None, bias=None, relu=False, raw_acc=False, summand=None
 
 
 def gemm(a, b_nk, out_dtype, *, a_dtype=None, b_dtype=None, ep=None, out=None, status_word=None, n=None, k=None):
-    """out[m,n] = epilogue(sum_k a[m,k] * b_nk[n,k]); a and b_nk are 8-bit CUDA tensors."""
+    """out[m,n] = epilogue(sum_k a[m,k] * b_nk[n,k]); a and b_nk are 8-bit CUDA tensors.  Three-dimensional a [batch,m,k]
+    and b_nk [batch,n,k] give a batched product out [batch,m,n]."""
     _require_cuda(a, b_nk, out)
-    m = a.shape[0]
-    k = k or a.shape[1]
-    n = n or b_nk.shape[0]
+    batched = a.dim() == 3
+    m = a.shape[-2]
+    k = k or a.shape[-1]
+    n = n or b_nk.shape[-2]
     ep = ep or make_epilogue()
     tdt = torch.int32 if ep.raw_acc else torch_dtype(out_dtype)
-    o = out if out is not None else torch.empty((m, n), dtype=tdt, device=a.device)
+    shape = (a.shape[0], m, n) if batched else (m, n)
+    o = out if out is not None else torch.empty(shape, dtype=tdt, device=a.device)
     p = L.GemmParams()
     p.m, p.n, p.k = m, n, k
     p.a_dtype = a_dtype or dt_of(a)
     p.b_dtype = b_dtype or dt_of(b_nk)
     p.out_dtype = out_dtype
-    p.a, p.lda = a.data_ptr(), a.stride(0)
-    p.b, p.ldb = b_nk.data_ptr(), b_nk.stride(0)
-    p.out, p.ldo = o.data_ptr(), o.stride(0)
+    p.a, p.lda = a.data_ptr(), a.stride(-2)
+    p.b, p.ldb = b_nk.data_ptr(), b_nk.stride(-2)
+    p.out, p.ldo = o.data_ptr(), o.stride(-2)
+    if batched:
+        p.batch, p.stride_a, p.stride_b, p.stride_out = a.shape[0], a.stride(0), b_nk.stride(0), o.stride(0)
     p.ep = ep
     p.status_word = 0 if status_word is None else status_word.data_ptr()
     L.check(L.load().itexb_gemm(C.byref(p), stream_ptr()))

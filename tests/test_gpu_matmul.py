@@ -210,3 +210,29 @@ def test_kernel_level_argument_errors():
     assert "scale_count" in str(e.value)
     with pytest.raises(itex.ItexError):
         K.gemm(a, b, L.DT_FLOAT, ep=K.make_epilogue(raw_acc=True))
+
+
+@pytest.mark.parametrize("shape", [(5, 100, 72, 64), (16, 384, 384, 64), (3, 130, 300, 272)])
+def test_batched_gemm(shape):
+    """Batched products through the third tensor-map coordinate: every batch is an exact int32 product, rows past m and
+    columns past n of one batch never reach the next one (ragged m, n, k included)."""
+    itex, K, ops = modules()
+    L = itex._lib
+    bsz, m, n, k = shape
+    rng = np.random.default_rng(sum(shape))
+    kp = (k + 15) // 16 * 16
+    a = np.zeros((bsz, m, kp), np.int8)
+    b = np.zeros((bsz, n, kp), np.int8)
+    a[:, :, :k] = rng.integers(-127, 128, (bsz, m, k))
+    b[:, :, :k] = rng.integers(-127, 128, (bsz, n, k))
+    want = np.einsum("bmk,bnk->bmn", a.astype(np.int64), b.astype(np.int64)).astype(np.int32)
+    guard = Canary(bsz * m * n * 4)
+    out = guard.view(torch.int32, (bsz, m, n))
+    K.gemm(dev(a), dev(b), L.DT_QINT32, ep=K.make_epilogue(raw_acc=True), out=out, k=k)
+    np.testing.assert_array_equal(host(out), want)
+    guard.check()
+    scale = rng.uniform(1e-4, 3e-4, n).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    got = K.gemm(dev(a), dev(b), L.DT_FLOAT, ep=K.make_epilogue(scale=dev(scale), bias=dev(bias)), k=k)
+    ref = (want.astype(np.float32) * scale).astype(np.float32) + bias
+    np.testing.assert_array_equal(host(got), ref)
