@@ -182,6 +182,11 @@ ITEXB_API int itexb_matmul_scales_dynamic(const float* range3, const float* weig
  * itex/core/kernels/common/quantized_matmul_common.h:241-275.  1-byte elements.        */
 ITEXB_API int itexb_pack_weights_kn(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad,
                                     itexb_stream_t stream);
+/* The same for `batch` matrices: matrix i is read at b_kn + i*src_stride and written at b_nk + i*dst_stride
+ * (bytes).  Used where a batched matmul receives its right operand as [.., k, n]
+ * (adj_y = false, itex/core/kernels/common/batch_matmul_op.h:112-121).  batch <= 65535. */
+ITEXB_API int itexb_pack_weights_kn_batched(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad, int64_t batch,
+                                            int64_t src_stride, int64_t dst_stride, itexb_stream_t stream);
 /* Column sums of an int8 [k,n] weight (MIN_FIRST compensation,
  * quantized_matmul_common.h:569-574). */
 ITEXB_API int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, int64_t n, itexb_stream_t stream);

@@ -138,6 +138,10 @@ enum BiasPrepMode : int {
 int LaunchBiasPrep(int mode, const void* bias, int bias_dtype, const int32_t* colsum, const float* f, int f_count, const float* g,
                    int g_count, float qmin, float* out, int n, cudaStream_t stream);
 
+// out = in broadcast to out_dims (numpy rules, trailing dims aligned); 2- or 4-byte elements (pointwise.cu).
+int LaunchBroadcast(const void* in, const int64_t* in_dims, int in_rank, void* out, const int64_t* out_dims, int out_rank,
+                    int elem_bytes, cudaStream_t stream);
+
 }  // namespace itexb
 
 #define ITEXB_REGISTER_OP(op_name, cls, nin, nout, hin, hout) \

@@ -568,21 +568,70 @@ __global__ void Fp8AmaxScaleUpdateKernel(float* __restrict__ hist, float* __rest
 }
 
 // ---- one-time packers ---------------------------------------------------------------
-// [k,n] -> [n,k_pad] through a 64x64 shared tile (+4 bytes of row padding against bank conflicts).
+// [batch][k,n] -> [batch][n,k_pad] through a 64x64 shared tile (+4 bytes of row padding against bank conflicts).
+// vec_load / vec_store: 4 bytes per thread along n (source) and along k (destination) when pitch and base allow.
 __global__ void __launch_bounds__(256) PackWeightsKnKernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                                                           long long k, long long n, long long k_pad) {
-  __shared__ uint8_t tile[64][68];
+                                                           long long k, long long n, long long k_pad, long long src_stride,
+                                                           long long dst_stride, bool vec_load, bool vec_store) {
+  __shared__ __align__(16) uint8_t tile[64][68];
+  src += (long long)blockIdx.z * src_stride;
+  dst += (long long)blockIdx.z * dst_stride;
   const long long k0 = (long long)blockIdx.y * 64, n0 = (long long)blockIdx.x * 64;
-  for (int t = threadIdx.x; t < 64 * 64; t += 256) {
-    const int r = t >> 6, c = t & 63;  // r: k, c: n (coalesced along n)
-    const long long kk = k0 + r, nn = n0 + c;
-    tile[r][c] = (kk < k && nn < n) ? src[kk * n + nn] : uint8_t(0);
+  if (vec_load) {
+    for (int t = threadIdx.x; t < 64 * 16; t += 256) {
+      const int r = t >> 4, c = (t & 15) * 4;  // r: k, c: n
+      const long long kk = k0 + r, nn = n0 + c;
+      uint32_t v = 0;
+      if (kk < k && nn < n) v = __ldg(reinterpret_cast<const uint32_t*>(src + kk * n + nn));  // n % 4 == 0: nn + 3 < n
+      *reinterpret_cast<uint32_t*>(&tile[r][c]) = v;
+    }
+  } else {
+    for (int t = threadIdx.x; t < 64 * 64; t += 256) {
+      const int r = t >> 6, c = t & 63;  // r: k, c: n (coalesced along n)
+      const long long kk = k0 + r, nn = n0 + c;
+      tile[r][c] = (kk < k && nn < n) ? src[kk * n + nn] : uint8_t(0);
+    }
   }
   __syncthreads();
-  for (int t = threadIdx.x; t < 64 * 64; t += 256) {
-    const int r = t >> 6, c = t & 63;  // r: n, c: k (coalesced along k)
-    const long long nn = n0 + r, kk = k0 + c;
-    if (nn < n && kk < k_pad) dst[nn * k_pad + kk] = tile[c][r];
+  if (vec_store) {
+    for (int t = threadIdx.x; t < 64 * 16; t += 256) {
+      const int r = t >> 4, c = (t & 15) * 4;  // r: n, c: k
+      const long long nn = n0 + r, kk = k0 + c;
+      if (nn < n && kk < k_pad) {  // k_pad % 4 == 0: kk + 3 < k_pad
+        const uint32_t v = uint32_t(tile[c][r]) | (uint32_t(tile[c + 1][r]) << 8) | (uint32_t(tile[c + 2][r]) << 16) |
+                           (uint32_t(tile[c + 3][r]) << 24);
+        *reinterpret_cast<uint32_t*>(dst + nn * k_pad + kk) = v;
+      }
+    }
+  } else {
+    for (int t = threadIdx.x; t < 64 * 64; t += 256) {
+      const int r = t >> 6, c = t & 63;  // r: n, c: k (coalesced along k)
+      const long long nn = n0 + r, kk = k0 + c;
+      if (nn < n && kk < k_pad) dst[nn * k_pad + kk] = tile[c][r];
+    }
+  }
+}
+
+// out[i] = in[broadcast index of i]: `rank` output dims (outermost first) with the input's element strides,
+// 0 where the input has extent 1.  One element per thread; T is the 2- or 4-byte storage type.
+struct BroadcastShape {
+  int rank;
+  long long dims[ITEXB_MAX_DIMS];
+  long long strides[ITEXB_MAX_DIMS];
+};
+template <typename T>
+__global__ void BroadcastKernel(const T* __restrict__ in, T* __restrict__ out, long long total, BroadcastShape s) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    long long rem = i, src = 0;
+#pragma unroll
+    for (int d = ITEXB_MAX_DIMS - 1; d >= 0; --d) {
+      if (d < s.rank) {
+        const long long q = rem / s.dims[d];
+        src += (rem - q * s.dims[d]) * s.strides[d];
+        rem = q;
+      }
+    }
+    out[i] = __ldg(in + src);
   }
 }
 
@@ -608,6 +657,31 @@ __global__ void PackFilterKernel(const uint8_t* __restrict__ f, uint8_t* __restr
 }
 
 }  // namespace
+
+int LaunchBroadcast(const void* in, const int64_t* in_dims, int in_rank, void* out, const int64_t* out_dims, int out_rank,
+                    int elem_bytes, cudaStream_t stream) {
+  ITEXB_REQUIRE(in != nullptr && out != nullptr && in_rank <= out_rank && out_rank <= ITEXB_MAX_DIMS && (elem_bytes == 2 || elem_bytes == 4),
+                ITEXB_INVALID_ARGUMENT, "broadcast: bad arguments");
+  BroadcastShape s{};
+  s.rank = out_rank;
+  long long total = 1, stride = 1;
+  for (int d = out_rank - 1; d >= 0; --d) {
+    const int id = d - (out_rank - in_rank);
+    const long long extent = id >= 0 ? in_dims[id] : 1;
+    ITEXB_REQUIRE(extent == out_dims[d] || extent == 1, ITEXB_INVALID_ARGUMENT, "broadcast: extent %lld does not broadcast to %lld",
+                  extent, (long long)out_dims[d]);
+    s.dims[d] = out_dims[d];
+    s.strides[d] = extent == 1 ? 0 : stride;
+    stride *= extent;
+    total *= out_dims[d];
+  }
+  if (total == 0) return ITEXB_OK;
+  const int blocks = int(std::max<long long>(1, std::min<long long>((total + 255) / 256, (long long)SmCount() * 16)));
+  if (elem_bytes == 4) BroadcastKernel<uint32_t><<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), total, s);
+  else BroadcastKernel<uint16_t><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), total, s);
+  return CheckLaunch("BroadcastKernel");
+}
+
 }  // namespace itexb
 
 using namespace itexb;
@@ -721,12 +795,21 @@ int itexb_matmul_scales_dynamic(const float* range3, const float* weight_range, 
   return CheckLaunch("MatMulScalesDynamicKernel");
 }
 
-int itexb_pack_weights_kn(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad, itexb_stream_t stream) {
-  ITEXB_REQUIRE(b_kn != nullptr && b_nk != nullptr && k > 0 && n > 0 && k_pad >= k, ITEXB_INVALID_ARGUMENT,
-                "pack_weights_kn: bad arguments");
-  dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k_pad + 63) / 64));
-  PackWeightsKnKernel<<<grid, 256, 0, AsCuda(stream)>>>(static_cast<const uint8_t*>(b_kn), static_cast<uint8_t*>(b_nk), k, n, k_pad);
+int itexb_pack_weights_kn_batched(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad, int64_t batch,
+                                  int64_t src_stride, int64_t dst_stride, itexb_stream_t stream) {
+  ITEXB_REQUIRE(b_kn != nullptr && b_nk != nullptr && k > 0 && n > 0 && k_pad >= k && batch > 0 && batch <= 65535 && src_stride >= 0 &&
+                    dst_stride >= 0,
+                ITEXB_INVALID_ARGUMENT, "pack_weights_kn: bad arguments");
+  const bool vec_load = n % 4 == 0 && src_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(b_kn) & 3) == 0;
+  const bool vec_store = k_pad % 4 == 0 && dst_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(b_nk) & 3) == 0;
+  dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k_pad + 63) / 64), (unsigned)batch);
+  PackWeightsKnKernel<<<grid, 256, 0, AsCuda(stream)>>>(static_cast<const uint8_t*>(b_kn), static_cast<uint8_t*>(b_nk), k, n, k_pad,
+                                                        src_stride, dst_stride, vec_load, vec_store);
   return CheckLaunch("PackWeightsKnKernel");
+}
+
+int itexb_pack_weights_kn(const void* b_kn, void* b_nk, int64_t k, int64_t n, int64_t k_pad, itexb_stream_t stream) {
+  return itexb_pack_weights_kn_batched(b_kn, b_nk, k, n, k_pad, 1, 0, 0, stream);
 }
 
 int itexb_colsum_s8(const int8_t* b_kn, int32_t* colsum, int64_t k, int64_t n, itexb_stream_t stream) {

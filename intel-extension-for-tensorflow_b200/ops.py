@@ -344,6 +344,38 @@ def _QuantizedMatMul(device_inputs, host_inputs, T1=None, T2="qint8", Tbias=None
     return _cached(op_name, attrs)(*(list(device_inputs) + list(host_inputs)), dtypes=dtypes)
 
 
+def _QuantizedBatchMatMulV2AndDequantize(x, y, min_x, max_x, min_y, max_y, Toutput="float", adj_x=False, adj_y=False,
+                                         is_filter_const=False, op_name="_QuantizedBatchMatMulV2AndDequantize"):
+    """-> output [..., m, n] (batch dims broadcast)."""
+    attrs = dict(T1=_TORCH_TO_DT[x.dtype], T2=_TORCH_TO_DT[y.dtype], Toutput=Toutput, adj_x=bool(adj_x), adj_y=bool(adj_y),
+                 is_filter_const=bool(is_filter_const))
+    return _cached(op_name, attrs)(x, y, min_x, max_x, min_y, max_y)
+
+
+def _QuantizedFusedBatchMatMulV2AndDequantize(x, y, args, min_x, max_x, min_y, max_y, fused_ops=(), Toutput="float", T=None,
+                                              adj_x=False, adj_y=False, is_filter_const=False,
+                                              op_name="_QuantizedFusedBatchMatMulV2AndDequantize"):
+    """`args` = one device tensor per fused op ("Mul": a scalar tensor, "Add": broadcasts to the output)."""
+    attrs = dict(T1=_TORCH_TO_DT[x.dtype], T2=_TORCH_TO_DT[y.dtype], Toutput=Toutput, adj_x=bool(adj_x), adj_y=bool(adj_y),
+                 is_filter_const=bool(is_filter_const), num_args=len(args), fused_ops=list(fused_ops))
+    if T is not None or len(args) > 0:
+        attrs["T"] = T if T is not None else _TORCH_TO_DT[args[0].dtype]
+    return _cached(op_name, attrs)(*([x, y] + list(args) + [min_x, max_x, min_y, max_y]))
+
+
+def _QuantizedBatchMatMul(device_inputs, host_inputs, T1="qint8", T2="qint8", U=None, Tout=None, Tdevice_outputs=None,
+                          fused_ops=("Dequantize",), adj_x=False, adj_y=False, input_quant_mode="SCALED",
+                          output_quant_mode="SCALED", op_name="_QuantizedBatchMatMul"):
+    """V2: device_inputs = [x, y, args...], host_inputs = [min_x, max_x, min_y, max_y]; fused_ops ends in "Dequantize"."""
+    if Tout is None:
+        Tout = Tdevice_outputs[0] if Tdevice_outputs else "float"
+    attrs = dict(T1=T1, T2=T2, Tout=Tout, adj_x=bool(adj_x), adj_y=bool(adj_y), fused_ops=list(fused_ops),
+                 input_quant_mode=input_quant_mode, output_quant_mode=output_quant_mode)
+    if U is not None:
+        attrs["U"] = U
+    return _cached(op_name, attrs)(*(list(device_inputs) + list(host_inputs)))
+
+
 def _ITEXQuantizedConv2DWithBiasAndReluAndRequantize(input, filter, bias, min_input, max_input, min_filter, max_filter,
                                                      min_freezed_output, max_freezed_output, strides=(1, 1, 1, 1),
                                                      padding="SAME", dilations=(1, 1, 1, 1), out_type="quint8",

@@ -482,6 +482,40 @@ def quantized_fused_matmul(a, b, bias, min_a, max_a, min_b, max_b, min_freezed_o
 # --------------------------------------------------------------------------
 # int8 conv
 # --------------------------------------------------------------------------
+def quantized_batch_matmul(x, y, min_x, max_x, min_y, max_y, *, fused_ops=(), mul=None, addend=None, adj_x: bool = False,
+                           adj_y: bool = False, toutput: str = "float") -> np.ndarray:
+    """_[ITEX]QuantizedBatchMatMulV2AndDequantize, _[ITEX]QuantizedFusedBatchMatMulV2AndDequantize and
+    _[ITEX]QuantizedBatchMatMul: QuantizedBatchMatMulV2Op, itex/core/kernels/common/batch_matmul_op.h:441-522.
+    qint8 x qint8 (the types registered for the GPU, itex/core/kernels/gpu/matmul_op.cc:612-654), batch dims
+    broadcast (MatMulBCast, :104-128); output = acc * range_x*range_y/(127*127) (AccumulateMulAndInt8Scale
+    :497-514), then the binary post-ops in fused_ops order: "Mul" by `mul` and "Add" of `addend`, both broadcast
+    to the output (:350-377).  "Dequantize" entries (V2 spelling) are ignored."""
+    x = np.asarray(x).astype(np.int64)
+    y = np.asarray(y).astype(np.int64)
+    if adj_x:
+        x = np.swapaxes(x, -1, -2)
+    if adj_y:
+        y = np.swapaxes(y, -1, -2)
+    acc = np.matmul(x, y)
+    assert np.abs(acc).max(initial=0) < 2 ** 31
+    range_lhs = f32(max(abs(f32(min_x)), abs(f32(max_x))))
+    range_rhs = f32(max(abs(f32(min_y)), abs(f32(max_y))))
+    scale_output = f32(f32(range_lhs * range_rhs) / f32(f32(127.0) * f32(127.0)))
+    f = (acc.astype(np.float32) * scale_output).astype(np.float32)
+    for op in fused_ops:
+        if op == "Mul":
+            f = (f * _as_f32(mul)).astype(np.float32)
+        elif op == "Add":
+            f = (f + _as_f32(addend)).astype(np.float32)
+        elif op != "Dequantize":
+            raise NotImplementedError("Fusion is not implemented for QuantizedBatchMatMul: [%s]" % op)
+    if toutput == "bfloat16":
+        return to_bf16_rne(f)
+    if toutput == "half":
+        return f.astype(np.float16)
+    return f
+
+
 def same_padding(in_size: int, k: int, stride: int, dilation: int = 1) -> Tuple[int, int, int]:
     """GetWindowedOutputSizeVerboseV2, SAME branch, itex/core/utils/common_shape_fns.cc:42-81.
     Returns (out_size, pad_before, pad_after); the extra pixel goes after."""

@@ -96,6 +96,15 @@ def write_reference_kat():
             ],
             "input_quant_mode": "MIN_FIRST", "Toutput": "float", "rtol": 0.2, "atol": 0.2,
         },
+        "batch_matmul": {  # test/sanity/array/quantized_batch_matmul_test.py:48-190 (fp32 math at rtol=atol=0.5)
+            "x_f32": [[[-0.33, 1.33, 1.44], [-0.23, 0.60, -0.08]], [[0.97, 0.70, 0.90], [-0.56, -1.84, -1.27]]],
+            "y_f32": [[[0.14, 0.78], [1.51, -1.36], [0.56, -0.29]], [[1.05, 1.82], [1.72, 0.36], [0.16, -0.10]]],
+            "mul": 0.5,
+            "add_f32": [[[0.19, -0.35], [0.03, -0.41]], [[0.72, -0.12], [0.87, -0.84]]],
+            "quant": {"T": "qint8", "mode": "SCALED", "round_mode": "HALF_TO_EVEN", "narrow_range": True},
+            "cases": [[], ["Mul"], ["Mul", "Add"]],
+            "rtol": 0.5, "atol": 0.5,
+        },
     }
     with open(os.path.join(HERE, "reference_kat.json"), "w") as f:
         json.dump(kat, f, indent=1)

@@ -223,6 +223,40 @@ def test_fused_matmul_reference_cases(kat):
         np.testing.assert_array_equal(out, out2)
 
 
+def test_batch_matmul_reference_cases(kat):
+    """test/sanity/array/quantized_batch_matmul_test.py: BMM, BMM + Mul, BMM + Mul + Add on qint8 operands quantized
+    SCALED / HALF_TO_EVEN / narrow_range, vs fp32 math at rtol = atol = 0.5; V1 and V2 spellings agree."""
+    k = kat["batch_matmul"]
+    x = np.array(k["x_f32"], np.float32)
+    y = np.array(k["y_f32"], np.float32)
+    mul = np.float32(k["mul"])
+    add = np.array(k["add_f32"], np.float32)
+    q = dict(T="qint8", mode="SCALED", round_mode="HALF_TO_EVEN", narrow_range=True)
+    qx, xmin, xmax = o.quantize_v2(x, x.min(), x.max(), **q)
+    qy, ymin, ymax = o.quantize_v2(y, y.min(), y.max(), **q)
+    for fused in k["cases"]:
+        want = np.matmul(x, y)
+        if "Mul" in fused:
+            want = want * mul
+        if "Add" in fused:
+            want = want + add
+        out = o.quantized_batch_matmul(qx, qy, xmin, xmax, ymin, ymax, fused_ops=fused, mul=mul, addend=add)
+        assert out.shape == (2, 2, 2) and out.dtype == np.float32
+        np.testing.assert_allclose(out, want, rtol=k["rtol"], atol=k["atol"])
+        np.testing.assert_allclose(out, want, rtol=0, atol=0.03)  # what int8 operands of range 1.84 x 1.82 actually give
+        out2 = o.quantized_batch_matmul(qx, qy, xmin, xmax, ymin, ymax, fused_ops=list(fused) + ["Dequantize"], mul=mul, addend=add)
+        np.testing.assert_array_equal(out, out2)
+    # adjoint flags and broadcast batch dims (MatMulBCast)
+    rng = np.random.default_rng(3)
+    a = rng.integers(-127, 128, (2, 3, 5, 16)).astype(np.int8)
+    b = rng.integers(-127, 128, (3, 7, 16)).astype(np.int8)
+    out = o.quantized_batch_matmul(a, b, -1.0, 1.0, -2.0, 2.0, adj_y=True)
+    want = np.einsum("bhmk,hnk->bhmn", a.astype(np.int64), b.astype(np.int64)).astype(np.float32) * np.float32(np.float32(2.0) / np.float32(127 * 127))
+    np.testing.assert_array_equal(out, want)
+    out_t = o.quantized_batch_matmul(np.swapaxes(a, -1, -2), b, -1.0, 1.0, -2.0, 2.0, adj_x=True, adj_y=True)
+    np.testing.assert_array_equal(out, out_t)
+
+
 def test_fused_matmul_scale_rules():
     """Requantize folds 255|127 / range into the per-channel scale when no activation follows, and into the
     activation's post scale otherwise (quantized_matmul_common.h:1651-1700); s8 activations use 127 (H3)."""
