@@ -22,9 +22,11 @@ struct GemmArgs {
   int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)
   int out_esz;          // bytes per output element (set by LaunchGemm)
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
+  int ep_mode;          // epilogue loop specialisation (set by LaunchGemm)
   int group_m;          // tile rows per rasterisation group (set by LaunchGemm)
   int batch;            // independent GEMMs in this launch (third coordinate of the tensor maps); 0 is read as 1
   long long batch_rows_out;  // rows of `out` (and of the summand) from one batch to the next
+  unsigned long long neg_zero2;  // two fp32 -0 (set by LaunchGemm): a run-time value the assembler cannot fold
   // Implicit-GEMM convolution (conv_mode != kConvNone): row m of A is output pixel m of the NHWC tensor
   // conv_x; column k = tap * conv_cpad + channel, tap = ky * kw + kx.  kConvGather: conv_cpad == conv_c and
   // four extra warps gather the A tile with cp.async.  kConvIm2col: conv_cpad is conv_c rounded up to 128
