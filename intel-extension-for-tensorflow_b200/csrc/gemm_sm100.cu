@@ -182,19 +182,31 @@ __device__ __forceinline__ uint64_t UmmaDescSw128(uint32_t smem_addr) {
 // Tile rasterisation: the tile grid is walked in super-groups of group_m tile rows, column by column inside a
 // group, so that the 148 tiles in flight share operand panels in L2.
 // A batched launch lays the batches' tile grids one after the other.
-__device__ __forceinline__ void TileCoords(int t, int tiles_m, int tiles_n, int group_m, int* tm, int* tn, int* batch = nullptr) {
-  if (batch != nullptr) {
-    const int per_batch = tiles_m * tiles_n;
-    *batch = t / per_batch;
-    t -= *batch * per_batch;
+// Every role walks the tile list once per tile, the sixteen epilogue warps included, and a 64-column tile is
+// only one slice of work per warp: the four divisions here were a third of a narrow tile's instructions, so
+// the three whose divisor is fixed for the launch use a multiplier prepared on the host (the fourth only
+// differs in the last, shorter group).
+__device__ __forceinline__ int DivBy(int x, const FastDiv& d) {  // x >= 0
+  return d.mul == 0u ? x : int(__umulhi(uint32_t(x), d.mul) >> d.shift);
+}
+__device__ __forceinline__ void TileCoords(int t, const GemmArgs& g, int tiles_m, int tiles_n, int* tm, int* tn, int* batch) {
+  const int per_batch = tiles_m * tiles_n;
+  const int b = DivBy(t, g.div_per_batch);
+  t -= b * per_batch;
+  *batch = b;
+  const int per_group = g.group_m * tiles_n;
+  const int grp = DivBy(t, g.div_per_group);
+  const int first_m = grp * g.group_m;
+  const int r = t - grp * per_group;
+  if (first_m + g.group_m <= tiles_m) {
+    const int c = DivBy(r, g.div_group_m);
+    *tn = c;
+    *tm = first_m + (r - c * g.group_m);
+  } else {
+    const int rows = tiles_m - first_m;
+    *tn = r / rows;
+    *tm = first_m + r % rows;
   }
-  const int per_group = group_m * tiles_n;
-  const int g = t / per_group;
-  const int first_m = g * group_m;
-  const int rows = min(group_m, tiles_m - first_m);
-  const int r = t - g * per_group;
-  *tm = first_m + r % rows;
-  *tn = r / rows;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -287,6 +299,10 @@ __device__ __forceinline__ float LoadSummand(const void* p, int dt, long long id
   }
 }
 
+// Columns of one epilogue block (the unit one warp converts, stages and stores): 16 columns of a 4-byte output,
+// 32 of a narrower one - but 16 for every type when the tile is 64 columns wide, so that the tile still has four
+// blocks, one for each of the four warps that share a row quarter (with two blocks half the epilogue warps idle).
+__host__ __device__ constexpr int OutBlockCols(int bn, int esz) { return (esz == 4 || bn == 64) ? 16 : 32; }
 // Epilogue loop specialisations (template parameter, chosen per launch by LaunchGemm).
 enum : int { kEpGeneral = 0, kEpPlain = 1, kEpSum8 = 2 };
 // Output kinds (template parameter of the epilogue).
@@ -365,6 +381,15 @@ __device__ __forceinline__ void TmemLdWait16(uint32_t (&r)[16]) {
                : "memory");
 }
 
+// Writes `value` to 16 consecutive TMEM columns of this warp's 32 lanes, and the wait for such stores.
+__device__ __forceinline__ void TmemSt16Same(uint32_t taddr, uint32_t value) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
+      "r"(value)
+      : "memory");
+}
+__device__ __forceinline__ void TmemStWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void TmaStore3d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap), "r"(src_smem), "r"(c0),
                "r"(c1), "r"(c2)
@@ -431,6 +456,9 @@ struct EpilogueCtx {
   float out_scale;      // FP8 output scale
   float post_scale;     // multiplier after the activation
   uint8_t* stage;       // this warp's staging memory
+  uint32_t sum_flip;    // 8-bit summand: XOR mask (0x80 per byte when signed), the float bit pattern the bytes are
+  uint32_t sum_base_bits;  //   dropped into, and the packed constant that takes the pattern's value off again
+  uint64_t sum_off2;
 };
 
 // The persistent loop of one epilogue warp.  Warp (q, sub) owns TMEM lanes 32q..32q+31 (the
@@ -446,12 +474,12 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                                              int tiles_n, int num_tiles) {
   constexpr int esz = OutBytes<OK>::v;
   constexpr int units = esz;                          // 16-byte units per 16-column slice
-  constexpr int bcols = esz == 4 ? 16 : 32;           // columns per block
+  constexpr int bcols = OutBlockCols(BN, esz);        // columns per block
   constexpr int slices = bcols / 16;
-  constexpr int row_bytes = bcols * esz;              // 64, 64, 32
+  constexpr int row_bytes = bcols * esz;              // 64, 64, 32 (BN = 64: 64, 32, 16)
   constexpr int row_units = row_bytes / 16;
   constexpr int buf_bytes = 32 * row_bytes;
-  constexpr int nbuf = kStagingPerWarp / buf_bytes;   // staging buffers per warp: 1 (4- and 2-byte outputs), 2 (1-byte)
+  constexpr int nbuf = kStagingPerWarp / buf_bytes;   // staging buffers per warp: 1 (64-byte rows), 2 or 4
   const int q = warp & 3;
   const int sub = (warp - 4) >> 2;
   constexpr bool PLAIN = MODE == kEpPlain, SUM8 = MODE == kEpSum8;
@@ -473,6 +501,12 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   e.post_scale = g.ep.post_scale == 0.f ? 1.f : g.ep.post_scale;
   e.stage = s_stage + (warp - 4) * kStagingPerWarp;
   const bool sum_signed = g.ep.summand_dtype == ITEXB_DT_QINT8 || g.ep.summand_dtype == ITEXB_DT_INT8;
+  e.sum_flip = sum_signed ? 0x80808080u : 0u;
+  e.sum_base_bits = sum_signed ? uint32_t(kMagicBits) : 0x4B000000u;  // 1.5 * 2^23 | 2^23
+  {
+    const float off = sum_signed ? -(kMagic + 128.f) : __fmul_rn(-8388608.f, g.ep.sum_scale);
+    e.sum_off2 = Pack2(off, off);
+  }
   const int swz = (lane / (8 / row_units)) % row_units;  // this lane's XOR term of the staging swizzle
   int acc = 0;
   uint32_t acc_phase = 0, seq = 0;
@@ -487,9 +521,28 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   int last_tn = -1;
   uint32_t reloads = 0;
 
+  // Preset accumulators (int8 kinds with a converting epilogue): both TMEM stages start out holding the bit
+  // pattern of 1.5 * 2^23 in every column instead of zero and the MMA always accumulates, so what the epilogue
+  // reads is already the float 1.5 * 2^23 + acc of the adder trick - the integer add per element is done by the
+  // tensor core.  Each warp re-arms the columns it has read with one TMEM store per slice; the first arming
+  // happens here and is published through the accumulator-empty barriers the MMA warp waits on.
+  constexpr bool preset = !F8 && OK != kOutRaw && MODE == kEpPlain;  // == g.preset, known at compile time here
+  if (preset) {
+#pragma unroll 1
+    for (int c = sub * 16; c < 2 * BN; c += 16 * (kEpilogueWarps / 4))
+      TmemSt16Same(tmem_base + uint32_t(c) + (uint32_t(q * 32) << 16), uint32_t(kMagicBits));
+    TmemStWait();
+    TcFenceBefore();
+    __syncwarp();
+    if (lane == 0) {
+      MbarArrive(SmemAddr(&tmem_empty_bar[0]));
+      MbarArrive(SmemAddr(&tmem_empty_bar[1]));
+    }
+  }
+
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     int tm, tn, bt;
-    TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn, &bt);
+    TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
     if (staged && tn != last_tn) {
       bool pok = true;
       if (reloads > 0) pok = MbarWait(SmemAddr(&par_bar[1]), (reloads - 1) & 1, abort_flag, g.status_word, kErrEpilogue);
@@ -509,15 +562,24 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
       ++reloads;
       last_tn = tn;
     }
-    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
-    if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
-    TcFenceAfter();
     const int row0 = tm * kBM + q * 32;  // first row of this warp's 32-row block
     const bool row_ok = row0 + lane < g.m;
     const long long row = (long long)bt * g.batch_rows_out + row0 + lane;  // row of `out` / the summand across batches
-    const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
     const int nblocks = min(BN / bcols, (g.n - tn * BN + bcols - 1) / bcols);  // blocks holding real columns
-    if (row0 < g.m) {
+    const uint8_t* sum_row = SUM8 ? static_cast<const uint8_t*>(g.ep.summand) + row * g.ep.ld_summand : nullptr;
+    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
+    if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
+    TcFenceAfter();
+    const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
+    if (row0 >= g.m) {
+      // No row of this warp is stored, but the MMA still accumulated onto its lanes: re-arm them too.
+      if (preset) {
+#pragma unroll 1
+        for (int c = sub * bcols; c < BN; c += bcols * (kEpilogueWarps / 4))
+#pragma unroll 1
+          for (int sl = 0; sl < slices; ++sl) TmemSt16Same(taddr + uint32_t(c + 16 * sl), uint32_t(kMagicBits));
+      }
+    } else {
 #pragma unroll 1
       for (int c = sub; c < nblocks; c += kEpilogueWarps / 4) {
         const int col0 = tn * BN + c * bcols;
@@ -535,13 +597,19 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             for (int j = 0; j < 16; ++j) w[j] = r[j];
           } else {
             // the 16 summand bytes of this slice are requested first: their latency (L2 or DRAM) is the longest
-            const bool sum_vec = SUM8 ? row_ok : (!PLAIN && e.sum_bytes_vec && row_ok && col + 16 <= g.n);
+            // (requesting them a whole slice ahead gained 3 % and cost the four registers that made this loop spill)
+            const bool sum_vec = MODE == kEpGeneral && e.sum_bytes_vec && row_ok && col + 16 <= g.n;
             uint4 s4 = make_uint4(0u, 0u, 0u, 0u);
-            if (sum_vec) s4 = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.ep.summand) + (row * g.ep.ld_summand + col)));
+            if (SUM8) {
+              if (row_ok) s4 = __ldg(reinterpret_cast<const uint4*>(sum_row + col));
+            } else if (sum_vec) {
+              s4 = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.ep.summand) + (row * g.ep.ld_summand + col)));
+            }
             float sc[16], bi[16];
             LoadStaged16(s_par + (c * bcols + 16 * sl), sc);  // in flight together with the TMEM load
             LoadStaged16(s_par + BN + (c * bcols + 16 * sl), bi);
             TmemLdWait16(r);
+            if (preset) TmemSt16Same(taddr + uint32_t(c * bcols + 16 * sl), uint32_t(kMagicBits));  // re-arm what was just read
             float v[16];
             bool shifted = false;  // v still carries the +1.5*2^23 of the adder trick
             if (F8) {
@@ -561,16 +629,24 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                 }
                 mx = max(mx, int(r[15]));
                 mn = min(mn, int(r[15]));
-                big = mx >= (1 << 22) || mn < -(1 << 22);
+                const int base = preset ? kMagicBits : 0;  // preset accumulators carry the pattern already
+                big = mx >= base + (1 << 22) || mn < base - (1 << 22);
               }
               if (!big) {
                 shifted = true;
+                if (preset) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = __int_as_float(int(r[j]) + kMagicBits);
+                  for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] = __int_as_float(int(r[j]) + kMagicBits);
+                }
               } else {
-                // volatile keeps the slow conversions inside this branch
+                // volatile keeps the slow conversions inside this branch (a preset accumulator that wrapped
+                // around wraps back in the subtraction)
+                const uint32_t base = preset ? uint32_t(kMagicBits) : 0u;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(v[j]) : "r"(r[j]));
+                for (int j = 0; j < 16; ++j) asm volatile("cvt.rn.f32.s32 %0, %1;" : "=f"(v[j]) : "r"(r[j] - base));
               }
             }
             // separate multiply and add: the order and rounding of oneDNN's scale-then-bias tail.
@@ -595,21 +671,25 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
               const long long sb = row * g.ep.ld_summand + col;
               if (SUM8 || sum_vec) {  // SUM8: rows past m carry zero bytes and are never stored
                 // 16 summand bytes -> fp32 without conversion instructions: the byte permute drops each byte into
-                // the low byte of the bit pattern of 1.5*2^23, i.e. builds the float 1.5*2^23 + byte directly
-                // (signed bytes are first offset by 128: b ^ 0x80 = b + 128).  Then, two columns per instruction,
-                // the offset is taken off (exact), the result multiplied by the summand scale (fused multiply-add
-                // with the hidden -0, see above) and added.
-                const uint32_t flip = sum_signed ? 0x80808080u : 0u;
-                const uint32_t sw[4] = {s4.x ^ flip, s4.y ^ flip, s4.z ^ flip, s4.w ^ flip};
-                const float off = sum_signed ? -(kMagic + 128.f) : -kMagic;
-                const uint64_t off2 = Pack2(off, off), ss2 = Pack2(g.ep.sum_scale, g.ep.sum_scale);
+                // the low byte of the bit pattern of a power of two P >= 2^23, i.e. builds the float P + byte.
+                // Unsigned bytes, P = 2^23: one fused multiply-add gives byte * s = (P + byte) * s - P * s with a
+                // single rounding, because P * s is exact (computed once per launch), then one add; two columns
+                // per instruction.  Signed bytes are offset by 128 first (b ^ 0x80 = b + 128) on 1.5 * 2^23, the
+                // offset is taken off exactly, then multiply (fused multiply-add with the hidden -0, see above) and add.
+                const uint32_t sw[4] = {s4.x ^ e.sum_flip, s4.y ^ e.sum_flip, s4.z ^ e.sum_flip, s4.w ^ e.sum_flip};
+                const uint64_t ss2 = Pack2(g.ep.sum_scale, g.ep.sum_scale);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                   const uint32_t word = sw[j >> 1];
-                  const float f0 = __uint_as_float(__byte_perm(word, uint32_t(kMagicBits), (j & 1) ? 0x7652 : 0x7650));
-                  const float f1 = __uint_as_float(__byte_perm(word, uint32_t(kMagicBits), (j & 1) ? 0x7653 : 0x7651));
-                  uint64_t t = Add2(Pack2(f0, f1), off2);
-                  t = Fma2(t, ss2, g.neg_zero2);
+                  const float f0 = __uint_as_float(__byte_perm(word, e.sum_base_bits, (j & 1) ? 0x7652 : 0x7650));
+                  const float f1 = __uint_as_float(__byte_perm(word, e.sum_base_bits, (j & 1) ? 0x7653 : 0x7651));
+                  uint64_t t = Pack2(f0, f1);
+                  if (sum_signed) {
+                    t = Add2(t, e.sum_off2);
+                    t = Fma2(t, ss2, g.neg_zero2);
+                  } else {
+                    t = Fma2(t, ss2, e.sum_off2);
+                  }
                   t = Add2(Pack2(v[2 * j], v[2 * j + 1]), t);
                   Unpack2(t, v[2 * j], v[2 * j + 1]);
                 }
@@ -685,13 +765,14 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
         }
       }
     }
+    if (preset) TmemStWait();  // the re-armed columns are in place before the MMA warp may accumulate onto them
     TcFenceBefore();
     __syncwarp();
     if (lane == 0) {
       MbarArrive(SmemAddr(&tmem_empty_bar[acc]));  // one arrival per warp: all its lanes have read their rows
-      if (staged && t + int(gridDim.x) < num_tiles) {
-        int ntm, ntn;
-        TileCoords(t + int(gridDim.x), tiles_m, tiles_n, g.group_m, &ntm, &ntn);
+      if (staged && tiles_n > 1 && t + int(gridDim.x) < num_tiles) {  // one tile column: the parameters never change
+        int ntm, ntn, nbt;
+        TileCoords(t + int(gridDim.x), g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
         if (ntn != tn) MbarArrive(SmemAddr(&par_bar[1]));  // this warp is done with the staged parameters
       }
     }
@@ -769,7 +850,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn, bt;
-      TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn, &bt);
+      TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
       int w0 = 0, h0 = 0, n0 = 0, c0 = 0, kx = 0, ky = 0;  // im2col: base position of the tile's first pixel, position in K
       if (CONV == kConvIm2col) {
         const int pix = tm * kBM;
@@ -812,7 +893,9 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      ok = MbarWait(SmemAddr(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, g.status_word, kErrMma);
+      // Without preset the first use of each accumulator stage finds its barrier "already released" (parity trick);
+      // with preset it waits for the epilogue warps' arming of the stage, one phase earlier throughout.
+      ok = MbarWait(SmemAddr(&tmem_empty_bar[acc]), g.preset ? acc_phase : acc_phase ^ 1, abort_flag, g.status_word, kErrMma);
       if (!ok) break;
       TcFenceAfter();
       const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
@@ -826,7 +909,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k)
           UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
-                     (kb | k) != 0 ? 1u : 0u);
+                     ((kb | k) != 0 || g.preset) ? 1u : 0u);
         TcCommit(SmemAddr(&empty_bar[stage]));  // stage reusable once these MMAs have read it
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
@@ -856,8 +939,8 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     long long issued = 0, signaled = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int tm, tn;
-      TileCoords(t, tiles_m, tiles_n, g.group_m, &tm, &tn);
+      int tm, tn, bt_unused;
+      TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt_unused);
       uint32_t msk[8], off[8];
       {
         int pix = tm * kBM + rbase;  // m < 2^31 is checked by the host
@@ -1052,14 +1135,15 @@ int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p) {
 // Tensor map for the epilogue's TMA stores: the output as a byte matrix {n*esz, m} with
 // row pitch ldo*esz, box = one warp block of 32 rows x 16 (4-byte) or 32 (narrower) elements,
 // swizzle matching the staging tile's row width (64 or 32 bytes).
-static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz, int64_t batch, int64_t batch_rows) {
+static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz, int bn, int64_t batch, int64_t batch_rows) {
   EncodeTiledFn enc = GetEncodeTiled();
   ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   const cuuint64_t dims[3] = {cuuint64_t(n) * esz, cuuint64_t(m), cuuint64_t(batch)};
   const cuuint64_t strides[2] = {cuuint64_t(ldo) * esz, cuuint64_t(batch_rows) * ldo * esz};
-  const cuuint32_t box[3] = {cuuint32_t(esz == 1 ? 32 : 64), 32, 1};
+  const int row_bytes = OutBlockCols(bn, esz) * esz;  // staging rows of 64, 32 or 16 bytes, swizzled over their own width
+  const cuuint32_t box[3] = {cuuint32_t(row_bytes), 32, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUtensorMapSwizzle sw = esz == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle sw = row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled (output) failed with CUresult %d", int(r));
@@ -1083,6 +1167,19 @@ uint32_t MakeInstrDesc(int a_dtype, int b_dtype, int bn) {
   return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
 }
 
+// floor(x / d) for 0 <= x < 2^31 as umulhi(x, mul) >> shift, with mul = ceil(2^(32 + shift) / d) and
+// shift = ceil(log2 d) - 1 (d >= 2; mul == 0 marks d == 1).  The rounding error of mul adds less than
+// x / 2^(32 + shift) * d < 1/d to the quotient's fraction, so the floor is exact.
+FastDiv MakeFastDiv(uint32_t d) {
+  FastDiv f{0u, 0u};
+  if (d <= 1u) return f;
+  uint32_t lg = 0;
+  while ((1ull << lg) < d) ++lg;
+  f.shift = lg - 1;
+  f.mul = uint32_t(((1ull << (31 + lg)) + d - 1) / d);
+  return f;
+}
+
 int PickBN(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
 int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st) {
@@ -1102,7 +1199,11 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   // m-tiles per rasterisation group, measured: wide tile grids want tall groups (8192^3: 32 beats 16 by 2 %, 8 loses 3 %),
   // narrow ones short groups (n = 4096: 8 beats 16 by 1-2 %)
   const int tiles_n = (g.n + bn - 1) / bn;
+  const int tiles_m = (g.m + kBM - 1) / kBM;
   g.group_m = tiles_n >= 32 ? 32 : (tiles_n <= 16 ? 8 : 16);
+  g.div_per_batch = MakeFastDiv(uint32_t(tiles_m) * uint32_t(tiles_n));
+  g.div_per_group = MakeFastDiv(uint32_t(g.group_m) * uint32_t(tiles_n));
+  g.div_group_m = MakeFastDiv(uint32_t(g.group_m));
   g.neg_zero2 = 0x8000000080000000ull;
   g.vec_store = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (g.ldo * g.out_esz) % 16 == 0) ? 1 : 0;
   g.tma_store = g.vec_store;
@@ -1119,9 +1220,10 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
              (reinterpret_cast<uintptr_t>(g.ep.summand) & 15) == 0)
       g.ep_mode = kEpSum8;
   }
+  g.preset = (!f8 && g.ep_mode == kEpPlain) ? 1 : 0;
   CUtensorMap to;
   if (g.batch <= 1) { g.batch = 1; g.batch_rows_out = g.m; }
-  if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, g.batch, g.batch_rows_out));
+  if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, bn, g.batch, g.batch_rows_out));
   else to = ta;  // unused by the kernel
   if (g.conv_mode == kConvGather) {
     if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, g, st);

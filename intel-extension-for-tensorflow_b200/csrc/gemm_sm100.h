@@ -10,6 +10,10 @@
 namespace itexb {
 
 // Kernel argument block (by value in parameter space).
+// Division by a divisor fixed per launch: see MakeFastDiv.
+struct FastDiv { unsigned mul, shift; };
+FastDiv MakeFastDiv(unsigned d);
+
 struct GemmArgs {
   int m, n, k;          // k in bytes = elements (8-bit operands)
   int out_dtype;
@@ -23,7 +27,9 @@ struct GemmArgs {
   int out_esz;          // bytes per output element (set by LaunchGemm)
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
   int ep_mode;          // epilogue loop specialisation (set by LaunchGemm)
+  int preset;           // accumulators start from the bit pattern of 1.5 * 2^23 instead of zero (set by LaunchGemm)
   int group_m;          // tile rows per rasterisation group (set by LaunchGemm)
+  FastDiv div_per_batch, div_per_group, div_group_m;  // dividers of the tile walk (set by LaunchGemm)
   int batch;            // independent GEMMs in this launch (third coordinate of the tensor maps); 0 is read as 1
   long long batch_rows_out;  // rows of `out` (and of the summand) from one batch to the next
   unsigned long long neg_zero2;  // two fp32 -0 (set by LaunchGemm): a run-time value the assembler cannot fold
