@@ -81,61 +81,128 @@ __global__ void __launch_bounds__(256) GatherPatchesRowKernel(GatherArgs a) {
   }
 }
 
-// Few-channel stem convolutions (e.g. 7x7x3, stride 2): the filter shape is a template parameter,
-// so every byte position of the 16-byte-aligned patch row is a compile-time offset into a
-// shared-memory copy of the input window.  A block builds TP consecutive output pixels of one
-// output row: it loads the KH input rows they touch once (coalesced), then each thread assembles
-// its patch row in registers and writes it as 16-byte vectors.  Dilation 1.
+// Few-channel stem convolutions (e.g. 7x7x3, stride 2): the filter shape is a template parameter.
+// A block builds TP consecutive output pixels of one output row in three phases:
+//   1. the KH input rows the pixels touch go to shared memory as aligned 32-bit words (a few edge
+//      words byte by byte, zero outside the image);
+//   2. each thread pulls the KH runs of KW*C bytes of its pixel into registers - aligned word reads
+//      plus one byte permute per word for the run's phase inside its first word - and composes the
+//      patch row from them: every word of the row takes its bytes from at most three of those
+//      registers at compile-time positions, i.e. one or two byte permutes;
+//   3. the TP patch rows are written with consecutive threads on consecutive 16-byte units.
+// `pitch` is the distance of patch rows in the workspace: a multiple of 128 bytes, because TMA reads
+// 128-byte boxes whose rows straddle two cache lines at half the rate (measured on the GEMM that
+// consumes this matrix: 148 us at a pitch of 160 bytes, 83 us at 256).  Dilation 1.
 template <int KH, int KW, int C, int TP>
-__global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a) {
-  constexpr int kRun = KW * C;                         // bytes of one filter row
-  constexpr int kRowPitch = (KH * kRun + 15) / 16 * 16;  // patch-matrix pitch
-  extern __shared__ __align__(16) uint8_t s_in[];      // [KH][span * C], then the staged patch rows
+__global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a, int pitch) {
+  constexpr int kRun = KW * C;                            // bytes of one filter row
+  constexpr int kBytes = KH * kRun;                       // bytes of one patch
+  constexpr int kRowBytes = (kBytes + 15) / 16 * 16;      // patch row as written (zero padded)
+  constexpr int kDW = (kRun + 3) / 4;                     // registers holding one run
+  constexpr int kLW = (kRun + 3 + 3) / 4;                 // words read to cover a run at any phase
+  extern __shared__ __align__(16) uint8_t s_mem[];
   const int tiles_x = (a.ow + TP - 1) / TP;
   const int tile = blockIdx.x % tiles_x;
   const int oy = (blockIdx.x / tiles_x) % a.oh;
   const int b = blockIdx.x / (tiles_x * a.oh);
   const int ox0 = tile * TP;
-  const int span = (TP - 1) * a.stride_w + KW;         // input columns the tile touches
-  const int ix0 = ox0 * a.stride_w - a.pad_left;
-  const int row_bytes = span * C;
-  for (int i = threadIdx.x; i < KH * row_bytes; i += TP) {
-    const int ky = i / row_bytes, r = i - ky * row_bytes;
-    const int ix = ix0 + r / C, ci = r % C;
+  const int span = (TP - 1) * a.stride_w + KW;            // input columns the tile touches
+  const int row_words = (span * C + 3) / 4 + 1;           // words per staged input row (any phase)
+  const int start = (ox0 * a.stride_w - a.pad_left) * C;  // byte offset of the window in an image row, may be negative
+  const int phase = ((start % 4) + 4) % 4;
+  const int start_al = start - phase;                     // word-aligned (the image rows are: w*C % 4 == 0, checked by the host)
+  const int image_row_bytes = a.w * C;
+  uint32_t* s_in = reinterpret_cast<uint32_t*>(s_mem);    // [KH][row_words]
+#pragma unroll 1
+  for (int ky = 0; ky < KH; ++ky) {
     const int iy = oy * a.stride_h + ky - a.pad_top;
-    uint8_t v = 0;
-    if (iy >= 0 && iy < a.h && ix >= 0 && ix < a.w) v = __ldg(a.x + (((long long)b * a.h + iy) * a.w + ix) * C + ci);
-    s_in[i] = v;
+    const bool row_in = iy >= 0 && iy < a.h;
+    const uint8_t* g_row = a.x + ((long long)b * a.h + (row_in ? iy : 0)) * image_row_bytes;
+    for (int wi = threadIdx.x; wi < row_words; wi += TP) {
+      const int gb = start_al + 4 * wi;
+      uint32_t word = 0;
+      if (row_in) {
+        if (gb >= 0 && gb + 4 <= image_row_bytes) {
+          word = __ldg(reinterpret_cast<const uint32_t*>(g_row + gb));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (gb + t >= 0 && gb + t < image_row_bytes) word |= uint32_t(__ldg(g_row + gb + t)) << (8 * t);
+        }
+      }
+      s_in[ky * row_words + wi] = word;
+    }
   }
   __syncthreads();
-  // Each thread assembles the patch row of one pixel into the shared staging tile; the block then
-  // writes the tile - TP consecutive patch rows are one contiguous run of the patch matrix - with
-  // consecutive threads on consecutive 16-byte units, so that every store instruction fills whole
-  // sectors (a thread storing its own row would write 16 bytes every kRowPitch bytes).
-  uint4* s_out = reinterpret_cast<uint4*>(s_in + ((KH * row_bytes + 15) / 16) * 16);
-  const uint8_t* base = s_in + threadIdx.x * a.stride_w * C;
-  uint4* dst = s_out + threadIdx.x * (kRowPitch / 16);
+  // phase 2: runs into registers
+  const int o = phase + threadIdx.x * a.stride_w * C;     // byte offset of this pixel's runs in a staged row
+  const int w0 = o >> 2;
+  const uint32_t sel = 0x3210u + 0x1111u * uint32_t(o & 3);
+  uint32_t d[KH * kDW];
 #pragma unroll
-  for (int u = 0; u < kRowPitch / 16; ++u) {
+  for (int r = 0; r < KH; ++r) {
+    uint32_t wv[kLW + 1];
+#pragma unroll
+    for (int i = 0; i < kLW; ++i) wv[i] = s_in[r * row_words + w0 + i];
+    wv[kLW] = 0;
+#pragma unroll
+    for (int i = 0; i < kDW; ++i) d[r * kDW + i] = __byte_perm(wv[i], wv[i + 1], sel);
+  }
+  // compose the patch row; byte k of it is byte (k % kRun) & 3 of register (k / kRun) * kDW + ((k % kRun) >> 2)
+  uint4* s_out = reinterpret_cast<uint4*>(s_mem + ((KH * row_words * 4 + 15) / 16) * 16);
+  uint4* dst = s_out + threadIdx.x * (kRowBytes / 16);
+#pragma unroll
+  for (int u = 0; u < kRowBytes / 16; ++u) {
     uint32_t w[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int qq = 0; qq < 4; ++qq) {
+      const int k0 = (u * 4 + qq) * 4;                    // compile-time after unrolling, like everything derived from it
       uint32_t word = 0;
+      if (k0 < kBytes) {
+        const int r0 = (k0 / kRun) * kDW + ((k0 % kRun) >> 2);
+        int r1 = -1, r2 = -1;
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        constexpr int dummy = 0;
-        const int k = u * 16 + q * 4 + t;               // compile-time after unrolling
-        if (k < KH * kRun) word |= uint32_t(base[(k / kRun) * row_bytes + (k % kRun)]) << (8 * t);
-        (void)dummy;
+        for (int t = 1; t < 4; ++t) {
+          const int k = k0 + t;
+          if (k < kBytes) {
+            const int rg = (k / kRun) * kDW + ((k % kRun) >> 2);
+            if (rg != r0) {
+              if (r1 < 0) r1 = rg;
+              else if (rg != r1 && r2 < 0) r2 = rg;
+            }
+          }
+        }
+        uint32_t sel1 = 0, sel2 = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int k = k0 + t;
+          uint32_t n1 = 0, n2 = uint32_t(t);
+          if (k < kBytes) {
+            const int rg = (k / kRun) * kDW + ((k % kRun) >> 2);
+            const uint32_t sb = uint32_t((k % kRun) & 3);
+            if (rg == r0) n1 = sb;
+            else if (rg == r1) n1 = 4u + sb;
+            else n2 = 4u + sb;
+          }
+          sel1 |= n1 << (4 * t);
+          sel2 |= n2 << (4 * t);
+        }
+        word = __byte_perm(d[r0], d[r1 < 0 ? r0 : r1], sel1);
+        if (r2 >= 0) word = __byte_perm(word, d[r2], sel2);
+        if (k0 + 4 > kBytes) word &= (1u << (8 * (kBytes - k0))) - 1u;  // zero padding after the last patch byte
       }
-      w[q] = word;
+      w[qq] = word;
     }
     dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
   }
   __syncthreads();
   const int pixels = min(TP, a.ow - ox0);
-  uint4* out = reinterpret_cast<uint4*>(a.ws + (((long long)b * a.oh + oy) * a.ow + ox0) * kRowPitch);
-  for (int i = threadIdx.x; i < pixels * (kRowPitch / 16); i += TP) out[i] = s_out[i];
+  uint8_t* out = a.ws + (((long long)b * a.oh + oy) * a.ow + ox0) * pitch;
+  constexpr int kUnits = kRowBytes / 16;
+  for (int i = threadIdx.x; i < pixels * kUnits; i += TP) {
+    const int pix = i / kUnits, u = i - pix * kUnits;
+    *reinterpret_cast<uint4*>(out + (long long)pix * pitch + 16 * u) = s_out[i];
+  }
 }
 
 bool IsPointwise(const itexb_conv_params_t& p) {
@@ -186,9 +253,20 @@ static bool IsImplicit(const itexb_conv_params_t& p) {
 
 extern "C" int32_t itexb_conv2d_filter_c_pad(const itexb_conv_params_t* p) { return p == nullptr ? 0 : FilterCPad(*p); }
 
+// The 7x7x3 stem has its own patch builder (GatherPatchesStemKernel).
+static bool IsStem(const itexb_conv_params_t& p) {
+  return p.kh == 7 && p.kw == 7 && p.c == 3 && p.c_pad == 3 && p.dil_h == 1 && p.dil_w == 1 && p.stride_w <= 4 && (p.w * p.c) % 4 == 0;
+}
+// Distance of patch rows in the workspace: the row length (a multiple of 16 bytes), or for the stem the next
+// multiple of 128, which TMA reads at twice the rate (the padding is never written or read).
+static size_t PatchPitch(const itexb_conv_params_t& p) {
+  const size_t kp = (size_t(p.kh) * p.kw * p.c_pad + 15) / 16 * 16;
+  return IsStem(p) ? (kp + 127) / 128 * 128 : kp;
+}
+
 extern "C" size_t itexb_conv2d_workspace_bytes(const itexb_conv_params_t* p) {
   if (p == nullptr || IsPointwise(*p) || IsIm2col(*p) || IsImplicit(*p)) return 0;
-  return size_t(p->n) * p->oh * p->ow * ((size_t(p->kh) * p->kw * p->c_pad + 15) / 16 * 16);
+  return size_t(p->n) * p->oh * p->ow * PatchPitch(*p);
 }
 
 extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream) {
@@ -199,7 +277,8 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   cudaStream_t st = AsCuda(stream);
   const long long m = (long long)p->n * p->oh * p->ow;
   ITEXB_REQUIRE(m < (1ll << 31), ITEXB_INVALID_ARGUMENT, "conv2d: more than 2^31 output pixels");
-  const int kp = (p->kh * p->kw * p->c_pad + 15) / 16 * 16;  // patch-matrix / packed-filter row pitch
+  const int kp = (p->kh * p->kw * p->c_pad + 15) / 16 * 16;  // patch-matrix row length / packed-filter row pitch
+  long long lda = kp;                                        // patch-matrix row pitch
   const void* a_ptr = p->x;
   const bool im2col = IsIm2col(*p);
   const bool implicit = !im2col && !IsPointwise(*p) && IsImplicit(*p);
@@ -223,11 +302,14 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
     const int blocks = int(std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)SmCount() * 32)));
     if (vec) {
       GatherPatchesVecKernel<<<blocks, 256, 0, st>>>(a);
-    } else if (p->kh == 7 && p->kw == 7 && p->c == 3 && p->dil_h == 1 && p->dil_w == 1 && p->stride_w <= 4) {
+    } else if (IsStem(*p)) {
+      ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->x) & 3) == 0, ITEXB_INVALID_ARGUMENT, "conv2d: input must be 4-byte aligned");
       constexpr int kTP = 64;
       const int tiles_x = (p->ow + kTP - 1) / kTP;
-      const size_t smem = (size_t(7) * ((kTP - 1) * p->stride_w + 7) * 3 + 15) / 16 * 16 + size_t(kTP) * 160;  // input window + staged patch rows
-      GatherPatchesStemKernel<7, 7, 3, kTP><<<unsigned(p->n) * p->oh * tiles_x, kTP, smem, st>>>(a);
+      const int row_words = (((kTP - 1) * p->stride_w + 7) * 3 + 3) / 4 + 1;
+      const size_t smem = (size_t(7) * row_words * 4 + 15) / 16 * 16 + size_t(kTP) * 160;  // input window + staged patch rows
+      lda = (long long)PatchPitch(*p);
+      GatherPatchesStemKernel<7, 7, 3, kTP><<<unsigned(p->n) * p->oh * tiles_x, kTP, smem, st>>>(a, int(lda));
     } else {
       GatherPatchesRowKernel<<<blocks, 256, 0, st>>>(a);
     }
@@ -243,7 +325,10 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->filter_packed, p->co, kp, kp, bn));
   if (implicit) ta = tb;  // unused: the kernel gathers A itself
   else if (im2col) ITEXB_RETURN_IF_ERROR(EncodeIm2colMap(&ta, *p));
-  else ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, kp, kp, 128));
+  // A patch matrix with padded rows is described to TMA as lda bytes wide: boxes that lie partly outside the
+  // tensor are read at half the rate (measured 155 us against 83 us on the stem), and what the padding holds
+  // does not matter - the filter's rows end at kp, so TMA zero-fills the filter bytes it is multiplied with.
+  else ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, lda, lda, 128));
   GemmArgs g{};
   if (implicit || im2col) {
     g.conv_mode = im2col ? kConvIm2col : kConvGather; g.conv_cpad = p->c_pad; g.conv_kh = p->kh; g.conv_c = p->c; g.conv_h = p->h; g.conv_w = p->w; g.kw = p->kw; g.oh = p->oh; g.ow = p->ow;
