@@ -113,15 +113,21 @@ __global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a, int 
   const int start_al = start - phase;                     // word-aligned (the image rows are: w*C % 4 == 0, checked by the host)
   const int image_row_bytes = a.w * C;
   uint32_t* s_in = reinterpret_cast<uint32_t*>(s_mem);    // [KH][row_words]
-#pragma unroll 1
+  // All of a thread's words are requested before the first is stored: with one load in flight per thread the
+  // block's lifetime was a chain of 2*KH memory latencies (the kernel ran at a third of the DRAM rate).
+  constexpr int kPerRow = 2;  // words per thread and input row; the host checks row_words <= kPerRow * TP
+  uint32_t v[KH * kPerRow];
+#pragma unroll
   for (int ky = 0; ky < KH; ++ky) {
     const int iy = oy * a.stride_h + ky - a.pad_top;
     const bool row_in = iy >= 0 && iy < a.h;
     const uint8_t* g_row = a.x + ((long long)b * a.h + (row_in ? iy : 0)) * image_row_bytes;
-    for (int wi = threadIdx.x; wi < row_words; wi += TP) {
+#pragma unroll
+    for (int p = 0; p < kPerRow; ++p) {
+      const int wi = threadIdx.x + p * TP;
       const int gb = start_al + 4 * wi;
       uint32_t word = 0;
-      if (row_in) {
+      if (row_in && wi < row_words) {
         if (gb >= 0 && gb + 4 <= image_row_bytes) {
           word = __ldg(reinterpret_cast<const uint32_t*>(g_row + gb));
         } else {
@@ -130,9 +136,14 @@ __global__ void __launch_bounds__(TP) GatherPatchesStemKernel(GatherArgs a, int 
             if (gb + t >= 0 && gb + t < image_row_bytes) word |= uint32_t(__ldg(g_row + gb + t)) << (8 * t);
         }
       }
-      s_in[ky * row_words + wi] = word;
+      v[ky * kPerRow + p] = word;
     }
   }
+#pragma unroll
+  for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+    for (int p = 0; p < kPerRow; ++p)
+      if (threadIdx.x + p * TP < row_words) s_in[ky * row_words + threadIdx.x + p * TP] = v[ky * kPerRow + p];
   __syncthreads();
   // phase 2: runs into registers
   const int o = phase + threadIdx.x * a.stride_w * C;     // byte offset of this pixel's runs in a staged row
@@ -255,7 +266,7 @@ extern "C" int32_t itexb_conv2d_filter_c_pad(const itexb_conv_params_t* p) { ret
 
 // The 7x7x3 stem has its own patch builder (GatherPatchesStemKernel).
 static bool IsStem(const itexb_conv_params_t& p) {
-  return p.kh == 7 && p.kw == 7 && p.c == 3 && p.c_pad == 3 && p.dil_h == 1 && p.dil_w == 1 && p.stride_w <= 4 && (p.w * p.c) % 4 == 0;
+  return p.kh == 7 && p.kw == 7 && p.c == 3 && p.c_pad == 3 && p.dil_h == 1 && p.dil_w == 1 && p.stride_w <= 2 && (p.w * p.c) % 4 == 0;
 }
 // Distance of patch rows in the workspace: the row length (a multiple of 16 bytes), or for the stem the next
 // multiple of 128, which TMA reads at twice the rate (the padding is never written or read).
@@ -306,7 +317,7 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
       ITEXB_REQUIRE((reinterpret_cast<uintptr_t>(p->x) & 3) == 0, ITEXB_INVALID_ARGUMENT, "conv2d: input must be 4-byte aligned");
       constexpr int kTP = 64;
       const int tiles_x = (p->ow + kTP - 1) / kTP;
-      const int row_words = (((kTP - 1) * p->stride_w + 7) * 3 + 3) / 4 + 1;
+      const int row_words = (((kTP - 1) * p->stride_w + 7) * 3 + 3) / 4 + 1;  // <= 2 * kTP for stride_w <= 2
       const size_t smem = (size_t(7) * row_words * 4 + 15) / 16 * 16 + size_t(kTP) * 160;  // input window + staged patch rows
       lda = (long long)PatchPitch(*p);
       GatherPatchesStemKernel<7, 7, 3, kTP><<<unsigned(p->n) * p->oh * tiles_x, kTP, smem, st>>>(a, int(lda));
@@ -329,6 +340,12 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   // tensor are read at half the rate (measured 155 us against 83 us on the stem), and what the padding holds
   // does not matter - the filter's rows end at kp, so TMA zero-fills the filter bytes it is multiplied with.
   else ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, a_ptr, m, lda, lda, 128));
+  TailMaps tail;
+  tail.box = (implicit || im2col) ? 0 : TailBox(kp);
+  if (tail.box != 0) {
+    ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.a, a_ptr, m, kp, lda, 128, 1, 0, tail.box));
+    ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.b, p->filter_packed, p->co, kp, kp, bn, 1, 0, tail.box));
+  }
   GemmArgs g{};
   if (implicit || im2col) {
     g.conv_mode = im2col ? kConvIm2col : kConvGather; g.conv_cpad = p->c_pad; g.conv_kh = p->kh; g.conv_c = p->c; g.conv_h = p->h; g.conv_w = p->w; g.kw = p->kw; g.oh = p->oh; g.ow = p->ow;
@@ -343,7 +360,7 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
   if (g.ep.summand != nullptr && g.ep.ld_summand == 0) g.ep.ld_summand = p->co;
   g.status_word = p->status_word;
   g.idesc = MakeInstrDesc(p->x_dtype, ITEXB_DT_QINT8, bn);
-  return LaunchGemm(ta, tb, g, bn, false, st);
+  return LaunchGemm(ta, tb, g, bn, false, st, tail.box != 0 ? &tail : nullptr);
 }
 
 // ---------------------------------------------------------------------------------------

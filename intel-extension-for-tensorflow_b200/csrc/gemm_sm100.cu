@@ -177,6 +177,12 @@ __device__ __forceinline__ uint64_t UmmaDescSw128(uint32_t smem_addr) {
   return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
          (uint64_t(2) << 61);
 }
+// The same for a tile whose rows are 64 or 32 bytes (64- / 32-byte swizzle): 8-row groups are 8 * row_bytes
+// apart and the layout field says which swizzle the rows were written with (4: 64 bytes, 6: 32 bytes).
+__device__ __forceinline__ uint64_t UmmaDescNarrow(uint32_t smem_addr, int row_bytes) {
+  return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t((8 * row_bytes) >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(row_bytes == 64 ? 4 : 6) << 61);
+}
 
 
 // Tile rasterisation: the tile grid is walked in super-groups of group_m tile rows, column by column inside a
@@ -794,7 +800,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 template <int BN, bool F8, int CONV>
 __global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-           const __grid_constant__ CUtensorMap tma_out, const GemmArgs g) {
+           const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a_tail,
+           const __grid_constant__ CUtensorMap tma_b_tail, const GemmArgs g) {
   using C = Cfg<BN>;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((SmemAddr(smem) & 1023u) != 0) {
@@ -871,6 +878,14 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
           TmaLoadIm2col(SmemAddr(sa), &tma_a, fb, c0, w0, h0, n0, kx * g.dil_w, ky * g.dil_h);
           c0 += kBK;
           if (c0 >= g.conv_cpad) { c0 = 0; if (++kx == g.kw) { kx = 0; ++ky; } }
+        } else if (g.tail_box != 0 && kb == num_kb - 1) {
+          // the last k-block is 64 or 32 bytes wide: narrower boxes (nothing outside the tensor is touched) into
+          // tiles with the matching narrower swizzle
+          MbarArriveExpectTx(fb, uint32_t((kBM + BN) * g.tail_box));
+          TmaLoad3d(SmemAddr(sa), &tma_a_tail, fb, kb * kBK, tm * kBM, bt);
+          TmaLoad3d(SmemAddr(sa + C::kABytes), &tma_b_tail, fb, kb * kBK, tn * BN, bt);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          continue;
         } else {
           MbarArriveExpectTx(fb, C::kStageBytes);
           TmaLoad3d(SmemAddr(sa), &tma_a, fb, kb * kBK, tm * kBM, bt);
@@ -904,12 +919,20 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         if (!ok) break;
         TcFenceAfter();
         uint8_t* sa = smem + stage * C::kStageBytes;
-        const uint64_t a_desc = UmmaDescSw128(SmemAddr(sa));
-        const uint64_t b_desc = UmmaDescSw128(SmemAddr(sa + C::kABytes));
+        if (CONV == kConvNone && g.tail_box != 0 && kb == num_kb - 1) {
+          const uint64_t a_desc = UmmaDescNarrow(SmemAddr(sa), g.tail_box);
+          const uint64_t b_desc = UmmaDescNarrow(SmemAddr(sa + C::kABytes), g.tail_box);
+          for (int k = 0; k < g.tail_box / kUmmaK; ++k)
+            UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
+                       ((kb | k) != 0 || g.preset) ? 1u : 0u);
+        } else {
+          const uint64_t a_desc = UmmaDescSw128(SmemAddr(sa));
+          const uint64_t b_desc = UmmaDescSw128(SmemAddr(sa + C::kABytes));
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k)
-          UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
-                     ((kb | k) != 0 || g.preset) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
+                       ((kb | k) != 0 || g.preset) ? 1u : 0u);
+        }
         TcCommit(SmemAddr(&empty_bar[stage]));  // stage reusable once these MMAs have read it
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
@@ -1065,7 +1088,8 @@ EncodeTiledFn GetEncodeTiled() {
 }
 
 template <int BN, bool F8, int CONV>
-int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const GemmArgs& g, cudaStream_t st) {
+int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tat, const CUtensorMap& tbt,
+           const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
   // The opt-in shared-memory size is a per-device function attribute; set it when the device changes.
   static thread_local int last_dev = -1;
@@ -1077,24 +1101,29 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   }
   const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN) * g.batch;
   const int grid = std::max(1, std::min(tiles, SmCount()));
-  GemmKernel<BN, F8, CONV><<<grid, CONV == kConvGather ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, g);
+  GemmKernel<BN, F8, CONV><<<grid, CONV == kConvGather ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, tat, tbt, g);
   return CheckLaunch("GemmKernel");
 }
 
 }  // namespace
 
+int TailBox(int64_t k) {
+  const int t = int(k % kBK);
+  return (t == 0 || t > 64) ? 0 : (t <= 32 ? 32 : 64);
+}
+
 int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows, int64_t batch,
-                     int64_t batch_stride) {
+                     int64_t batch_stride, int box_k) {
   EncodeTiledFn enc = GetEncodeTiled();
   ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   if (batch <= 1) { batch = 1; batch_stride = rows * ld; }
   const cuuint64_t dims[3] = {cuuint64_t(k), cuuint64_t(rows), cuuint64_t(batch)};
   const cuuint64_t strides[2] = {cuuint64_t(ld), cuuint64_t(batch_stride)};
-  const cuuint32_t box[3] = {cuuint32_t(kBK), cuuint32_t(box_rows), 1};
+  const cuuint32_t box[3] = {cuuint32_t(box_k), cuuint32_t(box_rows), 1};
   const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapSwizzle sw = box_k == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (box_k == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B);
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld k=%lld ld=%lld)",
                 int(r), (long long)rows, (long long)k, (long long)ld);
   return ITEXB_OK;
@@ -1182,7 +1211,10 @@ FastDiv MakeFastDiv(uint32_t d) {
 
 int PickBN(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
-int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st) {
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail) {
+  const CUtensorMap& tat = tail != nullptr ? tail->a : ta;  // placeholders when there is no narrow last k-block
+  const CUtensorMap& tbt = tail != nullptr ? tail->b : tb;
+  g.tail_box = (tail != nullptr && g.conv_mode == kConvNone) ? tail->box : 0;
   // Output addressing: TMA stores from a staged tile when the rows are 16-byte aligned,
   // otherwise per-thread stores straight from registers.
   g.out_esz = g.ep.raw_acc ? 4 : DtypeSize(g.out_dtype);
@@ -1226,23 +1258,23 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, bn, g.batch, g.batch_rows_out));
   else to = ta;  // unused by the kernel
   if (g.conv_mode == kConvGather) {
-    if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, g, st);
-    if (bn == 128) return Launch<128, false, kConvGather>(ta, tb, to, g, st);
-    return Launch<64, false, kConvGather>(ta, tb, to, g, st);
+    if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, tat, tbt, g, st);
+    if (bn == 128) return Launch<128, false, kConvGather>(ta, tb, to, tat, tbt, g, st);
+    return Launch<64, false, kConvGather>(ta, tb, to, tat, tbt, g, st);
   }
   if (g.conv_mode == kConvIm2col) {
-    if (bn == 256) return Launch<256, false, kConvIm2col>(ta, tb, to, g, st);
-    if (bn == 128) return Launch<128, false, kConvIm2col>(ta, tb, to, g, st);
-    return Launch<64, false, kConvIm2col>(ta, tb, to, g, st);
+    if (bn == 256) return Launch<256, false, kConvIm2col>(ta, tb, to, tat, tbt, g, st);
+    if (bn == 128) return Launch<128, false, kConvIm2col>(ta, tb, to, tat, tbt, g, st);
+    return Launch<64, false, kConvIm2col>(ta, tb, to, tat, tbt, g, st);
   }
   if (f8) {
-    if (bn == 256) return Launch<256, true, kConvNone>(ta, tb, to, g, st);
-    if (bn == 128) return Launch<128, true, kConvNone>(ta, tb, to, g, st);
-    return Launch<64, true, kConvNone>(ta, tb, to, g, st);
+    if (bn == 256) return Launch<256, true, kConvNone>(ta, tb, to, tat, tbt, g, st);
+    if (bn == 128) return Launch<128, true, kConvNone>(ta, tb, to, tat, tbt, g, st);
+    return Launch<64, true, kConvNone>(ta, tb, to, tat, tbt, g, st);
   }
-  if (bn == 256) return Launch<256, false, kConvNone>(ta, tb, to, g, st);
-  if (bn == 128) return Launch<128, false, kConvNone>(ta, tb, to, g, st);
-  return Launch<64, false, kConvNone>(ta, tb, to, g, st);
+  if (bn == 256) return Launch<256, false, kConvNone>(ta, tb, to, tat, tbt, g, st);
+  if (bn == 128) return Launch<128, false, kConvNone>(ta, tb, to, tat, tbt, g, st);
+  return Launch<64, false, kConvNone>(ta, tb, to, tat, tbt, g, st);
 }
 
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n) {
@@ -1305,6 +1337,12 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   const int bn = PickBN(p->n);
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, p->a, p->m, p->k, p->lda, kBM, batch, p->stride_a));
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->b, p->n, p->k, p->ldb, bn, batch, p->stride_b));
+  TailMaps tail;
+  tail.box = TailBox(p->k);
+  if (tail.box != 0) {
+    ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.a, p->a, p->m, p->k, p->lda, kBM, batch, p->stride_a, tail.box));
+    ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.b, p->b, p->n, p->k, p->ldb, bn, batch, p->stride_b, tail.box));
+  }
   GemmArgs g{};
   g.batch = int(batch);
   g.batch_rows_out = batch > 1 ? p->stride_out / p->ldo : p->m;
@@ -1314,5 +1352,5 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   g.ep = p->ep;
   g.status_word = p->status_word;
   g.idesc = MakeInstrDesc(p->a_dtype, p->b_dtype, bn);
-  return LaunchGemm(ta, tb, g, bn, f8, AsCuda(stream));
+  return LaunchGemm(ta, tb, g, bn, f8, AsCuda(stream), tail.box != 0 ? &tail : nullptr);
 }

@@ -28,6 +28,7 @@ struct GemmArgs {
   int out_kind;         // epilogue instantiation (set by LaunchGemm)
   int ep_mode;          // epilogue loop specialisation (set by LaunchGemm)
   int preset;           // accumulators start from the bit pattern of 1.5 * 2^23 instead of zero (set by LaunchGemm)
+  int tail_box;         // 0, or the width (64 | 32 bytes) of a narrower last k-block (set by LaunchGemm)
   int group_m;          // tile rows per rasterisation group (set by LaunchGemm)
   FastDiv div_per_batch, div_per_group, div_group_m;  // dividers of the tile walk (set by LaunchGemm)
   int batch;            // independent GEMMs in this launch (third coordinate of the tensor maps); 0 is read as 1
@@ -51,11 +52,17 @@ int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p);
 // 3-D tiled tensor map over a (batched) K-major 8-bit operand: dims {k, rows, batch}, row pitch `ld` bytes, batch pitch
 // batch_stride bytes, box {128 bytes, box_rows, 1}, 128-byte
 // swizzle, zero fill outside.
+// box_k: bytes of K per box - 128 (128-byte swizzle), or 64 / 32 with the swizzle of that width for a narrow last k-block.
 int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows, int64_t batch = 1,
-                     int64_t batch_stride = 0);
+                     int64_t batch_stride = 0, int box_k = 128);
+// A last k-block of at most 64 bytes (k % 128 in 16..64) is loaded through its own pair of maps with 64- or 32-byte
+// boxes: TMA reads boxes that lie partly outside the tensor at a fraction of its normal rate, and the narrow tile
+// is half or a quarter of the shared-memory fill and MMA work.  TailBox returns 64, 32, or 0 when K has no such tail.
+struct TailMaps { CUtensorMap a, b; int box; };
+int TailBox(int64_t k);
 unsigned MakeInstrDesc(int a_dtype, int b_dtype, int bn);
 int PickBN(int n);
-int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st);
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail = nullptr);
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n);
 
 }  // namespace itexb
