@@ -194,6 +194,35 @@ def test_raw_accumulators_exact_large_and_canaries():
     assert bool((got == ref).all())
 
 
+@pytest.mark.parametrize("summand", [False, True])
+def test_epilogue_bound_shape(summand):
+    """A ResNet-sized 1x1 convolution as a GEMM (200704 pixels x 256 channels, K = 64: one 64-byte k-block per tile, so
+    the epilogue is all there is) with per-channel scale, bias, ReLU[, a u8 summand] and u8 output, three launches.
+    Checked in full against the same arithmetic in separate fp32 steps on the raw accumulators (themselves exact by
+    the test above): multiply, add[, multiply-add of the summand in two roundings], clamp, round half to even."""
+    itex, K, ops = modules()
+    L = itex._lib
+    m, n, k = 200704, 256, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randint(0, 256, (m, k), device="cuda", generator=g).to(torch.uint8)
+    b = torch.randint(-127, 128, (n, k), device="cuda", generator=g).to(torch.int8)
+    scale = (torch.rand(n, device="cuda", generator=g) * 2e-3 + 1e-4).float()
+    bias = (torch.randn(n, device="cuda", generator=g) * 20).float()
+    sm = torch.randint(0, 256, (m, n), device="cuda", generator=g).to(torch.uint8) if summand else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    raw = K.gemm(a, b, L.DT_QINT32, ep=K.make_epilogue(raw_acc=True), status_word=status)
+    want = raw.float() * scale
+    want = want + bias
+    if summand:
+        want = want + sm.float() * 0.37
+    want = torch.round(torch.clamp(want, 0.0, 255.0)).to(torch.uint8)
+    ep = K.make_epilogue(scale=scale, bias=bias, relu=True, summand=sm, sum_scale=0.37)
+    for _ in range(3):
+        out = K.gemm(a, b, L.DT_QUINT8, ep=ep, status_word=status)
+        assert torch.equal(out, want)
+    assert int(status.item()) == 0
+
+
 def test_kernel_level_argument_errors():
     itex, K, ops = modules()
     L = itex._lib
