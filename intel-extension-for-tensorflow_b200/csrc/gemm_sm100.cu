@@ -34,6 +34,7 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.h"
@@ -849,6 +850,11 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   __syncthreads();
   TcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: the set-up above (barriers, TMEM allocation) may run while the previous kernel of
+  // the stream is still finishing; nothing below touches global memory before that kernel's writes are visible.
+  // The kernel after this one may start its own set-up as soon as an SM is free of this grid.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
@@ -1101,7 +1107,23 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   }
   const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN) * g.batch;
   const int grid = std::max(1, std::min(tiles, SmCount()));
-  GemmKernel<BN, F8, CONV><<<grid, CONV == kConvGather ? kThreadsConv : kThreads, C::kSmemBytes, st>>>(ta, tb, to, tat, tbt, g);
+  // Launched with programmatic stream serialization (ITEXB_PDL=0 turns it off): back-to-back GEMM launches of a
+  // layer graph overlap one kernel's set-up with the tail of the one before.
+  static const bool pdl = [] {
+    const char* e = std::getenv("ITEXB_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(unsigned(CONV == kConvGather ? kThreadsConv : kThreads));
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV>, ta, tb, to, tat, tbt, g));
   return CheckLaunch("GemmKernel");
 }
 
