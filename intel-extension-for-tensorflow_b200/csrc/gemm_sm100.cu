@@ -63,7 +63,8 @@ template <int BN> struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128), 8 (64)
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two >= 32
-  static constexpr int kBarrierBytes = (2 * kStages + 6) * 8 + 16;
+  static constexpr int kSumBars = kEpilogueWarps * 4;          // one per epilogue warp and staging buffer (summand loads)
+  static constexpr int kBarrierBytes = (2 * kStages + 6 + kSumBars) * 8 + 16;
   static constexpr int kParamBytes = 2 * BN * 4;               // the tile's per-column scales and biases
   static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
   // No slack for aligning the base: dynamic shared memory is declared 1024-byte aligned and the kernel checks it.
@@ -410,7 +411,9 @@ __device__ __forceinline__ void TmaStore2d(const void* tmap, uint32_t src_smem, 
 __device__ __forceinline__ void TmaStoreCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Blocks until at most `pending` of this thread's store groups are still reading shared memory.
 __device__ __forceinline__ void TmaStoreWaitRead(int pending) {
-  if (pending == 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+  if (pending >= 3) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+  else if (pending == 2) asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
+  else if (pending == 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
   else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void TmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -475,9 +478,9 @@ struct EpilogueCtx {
 // writes; edges are clipped by the tensor map.  Without TMA-legal output rows the slices go
 // straight to global memory.
 template <int BN, bool F8, int OK, int MODE>
-__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, uint8_t* s_stage, float* s_par,
-                                             uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint64_t* par_bar,
-                                             volatile int* abort_flag, uint32_t tmem_base, int warp, int lane, int tiles_m,
+__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, const CUtensorMap* tma_sum, uint8_t* s_stage,
+                                             float* s_par, uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint64_t* par_bar,
+                                             uint64_t* sum_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane, int tiles_m,
                                              int tiles_n, int num_tiles) {
   constexpr int esz = OutBytes<OK>::v;
   constexpr int units = esz;                          // 16-byte units per 16-column slice
@@ -547,6 +550,20 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     }
   }
 
+  // Sum8: the summand block of an output block is brought by TMA into the very staging buffer the block's output
+  // will be written to (same rows, same swizzle), one block ahead, so each lane finds its 16 summand bytes where
+  // it is about to store its 16 output bytes: no per-lane global loads (they touched 32 half-used sectors per
+  // instruction) and no latency on the slice's path.  sum_bar[buffer] completes when the block has landed.
+  uint64_t* my_sum_bar = sum_bar + (warp - 4) * 4;
+  bool give_up = false;
+  bool sum_pref = false;  // the load for block number `seq` (the next one this warp processes) is already on its way
+  auto issue_sum = [&](int col0, int brow0, int bbt, uint32_t s) {
+    const uint32_t b = s & uint32_t(nbuf - 1);
+    const uint32_t bar = SmemAddr(&my_sum_bar[b]);
+    MbarArriveExpectTx(bar, uint32_t(buf_bytes));
+    TmaLoad3d(SmemAddr(e.stage + b * buf_bytes), tma_sum, bar, col0 * esz, brow0, bbt);
+  };
+
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     int tm, tn, bt;
     TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
@@ -573,7 +590,6 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     const bool row_ok = row0 + lane < g.m;
     const long long row = (long long)bt * g.batch_rows_out + row0 + lane;  // row of `out` / the summand across batches
     const int nblocks = min(BN / bcols, (g.n - tn * BN + bcols - 1) / bcols);  // blocks holding real columns
-    const uint8_t* sum_row = SUM8 ? static_cast<const uint8_t*>(g.ep.summand) + row * g.ep.ld_summand : nullptr;
     const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
     if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
     TcFenceAfter();
@@ -591,10 +607,41 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
       for (int c = sub; c < nblocks; c += kEpilogueWarps / 4) {
         const int col0 = tn * BN + c * bcols;
         uint8_t* buf = e.stage + (seq & uint32_t(nbuf - 1)) * buf_bytes;
+        bool sum_pref_next = false;
+        if constexpr (SUM8) {
+          if (!sum_pref) {  // first block of the launch, or the block before could not look ahead
+            if (lane == 0) {
+              TmaStoreWaitRead(nbuf - 1);  // the store that last used this buffer has read it
+              issue_sum(col0, row0, bt, seq);
+            }
+          }
+          const bool sok = MbarWait(SmemAddr(&my_sum_bar[seq & uint32_t(nbuf - 1)]), (seq / uint32_t(nbuf)) & 1u, abort_flag,
+                                    g.status_word, kErrEpilogue);
+          if (!__all_sync(0xffffffffu, sok)) { give_up = true; break; }
+        }
 #pragma unroll 1
         for (int sl = 0; sl < slices; ++sl) {
           const int col = col0 + 16 * sl;
           if (col >= g.n) break;
+          if constexpr (SUM8) if (sl == slices - 1) {
+            // look one block ahead: the next block of this tile, or this warp's first block of its next tile
+            int ncol0 = -1, nrow0 = 0, nbt = 0;
+            if (c + kEpilogueWarps / 4 < nblocks) {
+              ncol0 = col0 + bcols * (kEpilogueWarps / 4); nrow0 = row0; nbt = bt;
+            } else if (t + int(gridDim.x) < num_tiles) {
+              int ntm, ntn;
+              TileCoords(t + int(gridDim.x), g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
+              nrow0 = ntm * kBM + q * 32;
+              if (nrow0 < g.m && ntn * BN + sub * bcols < g.n) ncol0 = ntn * BN + sub * bcols;
+            }
+            if (ncol0 >= 0) {
+              if (lane == 0) {
+                TmaStoreWaitRead(nbuf - 2);  // the next buffer's last store (nbuf - 1 blocks ago) has read it
+                issue_sum(ncol0, nrow0, nbt, seq + 1);
+              }
+              sum_pref_next = true;
+            }
+          }
           uint32_t r[16];
           TmemLd16(taddr + uint32_t(c * bcols + 16 * sl), r);
           uint32_t w[16];
@@ -603,12 +650,11 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 #pragma unroll
             for (int j = 0; j < 16; ++j) w[j] = r[j];
           } else {
-            // the 16 summand bytes of this slice are requested first: their latency (L2 or DRAM) is the longest
-            // (requesting them a whole slice ahead gained 3 % and cost the four registers that made this loop spill)
+            // general loop: the 16 summand bytes of this slice are requested first, their latency is the longest
             const bool sum_vec = MODE == kEpGeneral && e.sum_bytes_vec && row_ok && col + 16 <= g.n;
             uint4 s4 = make_uint4(0u, 0u, 0u, 0u);
             if (SUM8) {
-              if (row_ok) s4 = __ldg(reinterpret_cast<const uint4*>(sum_row + col));
+              s4 = *reinterpret_cast<const uint4*>(buf + lane * row_bytes + ((uint32_t(sl * units) ^ uint32_t(swz)) << 4));
             } else if (sum_vec) {
               s4 = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.ep.summand) + (row * g.ep.ld_summand + col)));
             }
@@ -769,8 +815,10 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             TmaStoreCommit();
           }
           ++seq;
+          sum_pref = sum_pref_next;
         }
       }
+      if (give_up) break;
     }
     if (preset) TmemStWait();  // the re-armed columns are in place before the MMA warp may accumulate onto them
     TcFenceBefore();
@@ -802,7 +850,7 @@ template <int BN, bool F8, int CONV>
 __global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a_tail,
-           const __grid_constant__ CUtensorMap tma_b_tail, const GemmArgs g) {
+           const __grid_constant__ CUtensorMap tma_b_tail, const __grid_constant__ CUtensorMap tma_sum, const GemmArgs g) {
   using C = Cfg<BN>;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((SmemAddr(smem) & 1023u) != 0) {
@@ -818,7 +866,8 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   uint64_t* tmem_full_bar = bars + 2 * C::kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint64_t* par_bar = tmem_empty_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(par_bar + 2);
+  uint64_t* sum_bar = par_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sum_bar + C::kSumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -838,6 +887,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueWarps);
       MbarInit(SmemAddr(&par_bar[a]), kEpilogueWarps);
     }
+    for (int i = 0; i < C::kSumBars; ++i) MbarInit(SmemAddr(&sum_bar[i]), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1030,7 +1080,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
   } else if (warp >= 4 && warp < kFirstGatherWarp) {
     // ---------------- epilogue ----------------
-#define ITEXB_EP_ARGS g, &tma_out, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles
+#define ITEXB_EP_ARGS g, &tma_out, &tma_sum, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, sum_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles
     switch (g.out_kind) {
       case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral>(ITEXB_EP_ARGS); break;
       case kOutF32:
@@ -1095,7 +1145,7 @@ EncodeTiledFn GetEncodeTiled() {
 
 template <int BN, bool F8, int CONV>
 int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tat, const CUtensorMap& tbt,
-           const GemmArgs& g, cudaStream_t st) {
+           const CUtensorMap& ts, const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
   // The opt-in shared-memory size is a per-device function attribute; set it when the device changes.
   static thread_local int last_dev = -1;
@@ -1123,7 +1173,7 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV>, ta, tb, to, tat, tbt, g));
+  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV>, ta, tb, to, tat, tbt, ts, g));
   return CheckLaunch("GemmKernel");
 }
 
@@ -1277,26 +1327,30 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   g.preset = (!f8 && g.ep_mode == kEpPlain) ? 1 : 0;
   CUtensorMap to;
   if (g.batch <= 1) { g.batch = 1; g.batch_rows_out = g.m; }
+  CUtensorMap tsum;  // Sum8: the summand seen through the output's geometry (same boxes, same swizzle)
+  if (g.ep_mode == kEpSum8)
+    ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&tsum, const_cast<void*>(g.ep.summand), g.m, g.n, g.ep.ld_summand, 1, bn, g.batch, g.batch_rows_out));
+  else tsum = ta;  // unused by the kernel
   if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, bn, g.batch, g.batch_rows_out));
   else to = ta;  // unused by the kernel
   if (g.conv_mode == kConvGather) {
-    if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, tat, tbt, g, st);
-    if (bn == 128) return Launch<128, false, kConvGather>(ta, tb, to, tat, tbt, g, st);
-    return Launch<64, false, kConvGather>(ta, tb, to, tat, tbt, g, st);
+    if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 128) return Launch<128, false, kConvGather>(ta, tb, to, tat, tbt, tsum, g, st);
+    return Launch<64, false, kConvGather>(ta, tb, to, tat, tbt, tsum, g, st);
   }
   if (g.conv_mode == kConvIm2col) {
-    if (bn == 256) return Launch<256, false, kConvIm2col>(ta, tb, to, tat, tbt, g, st);
-    if (bn == 128) return Launch<128, false, kConvIm2col>(ta, tb, to, tat, tbt, g, st);
-    return Launch<64, false, kConvIm2col>(ta, tb, to, tat, tbt, g, st);
+    if (bn == 256) return Launch<256, false, kConvIm2col>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 128) return Launch<128, false, kConvIm2col>(ta, tb, to, tat, tbt, tsum, g, st);
+    return Launch<64, false, kConvIm2col>(ta, tb, to, tat, tbt, tsum, g, st);
   }
   if (f8) {
-    if (bn == 256) return Launch<256, true, kConvNone>(ta, tb, to, tat, tbt, g, st);
-    if (bn == 128) return Launch<128, true, kConvNone>(ta, tb, to, tat, tbt, g, st);
-    return Launch<64, true, kConvNone>(ta, tb, to, tat, tbt, g, st);
+    if (bn == 256) return Launch<256, true, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 128) return Launch<128, true, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
+    return Launch<64, true, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
   }
-  if (bn == 256) return Launch<256, false, kConvNone>(ta, tb, to, tat, tbt, g, st);
-  if (bn == 128) return Launch<128, false, kConvNone>(ta, tb, to, tat, tbt, g, st);
-  return Launch<64, false, kConvNone>(ta, tb, to, tat, tbt, g, st);
+  if (bn == 256) return Launch<256, false, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
+  if (bn == 128) return Launch<128, false, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
+  return Launch<64, false, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
 }
 
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n) {
