@@ -275,8 +275,9 @@ ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
  * computed by GetWindowedOutputSizeVerboseV2 (itex/core/utils/common_shape_fns.cc:42-81).
  * c_pad is the channel pitch of one filter tap in the packed filter; itexb_conv2d_filter_c_pad
  * returns the value to use for a geometry (it reads n,h,w,c,kh,kw,strides,dilations,padding,oh,ow):
- * c rounded up to 128 when the input can be read by TMA im2col loads (c a multiple of 16, strides
- * up to 8, padding up to 128), otherwise c.  c_pad == c is always accepted. */
+ * when the input can be read by TMA im2col loads (c a multiple of 16, strides up to 8, padding up to
+ * 128) c rounded up to 32, 64 or a multiple of 128 (one filter tap is then one k-block of the GEMM),
+ * otherwise c.  c_pad == c is always accepted. */
 typedef struct itexb_conv_params {
   int32_t n, h, w, c;
   int32_t kh, kw, co;

@@ -233,9 +233,13 @@ bool Im2colGeometryOk(const itexb_conv_params_t& p) {
 
 // Channels per tap the packed filter should have: c rounded up to the 128 bytes of a k-block when
 // the TMA im2col path will run (each k-block is then one tap), c otherwise.
-int FilterCPad(const itexb_conv_params_t& p) { return Im2colGeometryOk(p) ? (p.c + 127) / 128 * 128 : p.c; }
+// The k-blocks of the im2col path are one tap wide: 128 bytes (128-byte swizzle), or for filters of at most
+// 64 channels 64 or 32 bytes with the swizzle of that width, so that a 64-channel 3x3 layer neither fills shared
+// memory with nor multiplies 64 zero channels per tap.
+int Im2colCPad(int c) { return c <= 32 ? 32 : (c <= 64 ? 64 : (c + 127) / 128 * 128); }
+int FilterCPad(const itexb_conv_params_t& p) { return Im2colGeometryOk(p) ? Im2colCPad(p.c) : p.c; }
 
-bool IsIm2col(const itexb_conv_params_t& p) { return Im2colGeometryOk(p) && p.c_pad == (p.c + 127) / 128 * 128; }
+bool IsIm2col(const itexb_conv_params_t& p) { return Im2colGeometryOk(p) && p.c_pad == Im2colCPad(p.c); }
 
 int Validate(const itexb_conv_params_t& p) {
   ITEXB_REQUIRE(p.n >= 0 && p.h > 0 && p.w > 0 && p.c > 0 && p.kh > 0 && p.kw > 0 && p.co > 0, ITEXB_INVALID_ARGUMENT,
@@ -243,7 +247,7 @@ int Validate(const itexb_conv_params_t& p) {
   ITEXB_REQUIRE(p.stride_h > 0 && p.stride_w > 0 && p.dil_h > 0 && p.dil_w > 0, ITEXB_INVALID_ARGUMENT,
                 "conv2d: strides and dilations must be positive");
   ITEXB_REQUIRE(p.oh > 0 && p.ow > 0, ITEXB_INVALID_ARGUMENT, "conv2d: empty output");
-  ITEXB_REQUIRE(p.c_pad == p.c || (p.c_pad == (p.c + 127) / 128 * 128 && Im2colGeometryOk(p)), ITEXB_INVALID_ARGUMENT,
+  ITEXB_REQUIRE(p.c_pad == p.c || (p.c_pad == Im2colCPad(p.c) && Im2colGeometryOk(p)), ITEXB_INVALID_ARGUMENT,
                 "conv2d: c_pad must be what itexb_conv2d_filter_c_pad returns (%d or c=%d), got %d", FilterCPad(p), p.c, p.c_pad);
   ITEXB_REQUIRE(IsInt8(p.x_dtype), ITEXB_INVALID_ARGUMENT, "conv2d: input type %s is not qint8/quint8", DtypeName(p.x_dtype));
   return ValidateEpilogue("conv2d", p.ep, p.out_dtype, false, p.co);
@@ -333,7 +337,7 @@ extern "C" int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream)
                 "conv2d: packed filter must be 16-byte aligned");
   CUtensorMap ta, tb;
   const int bn = PickBN(p->co);
-  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->filter_packed, p->co, kp, kp, bn));
+  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->filter_packed, p->co, kp, kp, bn, 1, 0, (im2col && p->c_pad < 128) ? p->c_pad : 128));
   if (implicit) ta = tb;  // unused: the kernel gathers A itself
   else if (im2col) ITEXB_RETURN_IF_ERROR(EncodeIm2colMap(&ta, *p));
   // A patch matrix with padded rows is described to TMA as lda bytes wide: boxes that lie partly outside the

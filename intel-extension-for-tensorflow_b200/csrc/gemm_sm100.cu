@@ -2,9 +2,11 @@
 //
 // One persistent CTA per SM (640 threads; 768 in the cp.async convolution variant), warp-specialised:
 //   warp 0      TMA producer   cp.async.bulk.tensor -> smem ring of 128 x 128-byte A tiles and BN x 128-byte
-//                              B tiles (128-byte swizzle).  A is a 2-D tiled load of a matrix or, for
+//                              B tiles (128-byte swizzle).  A is a tiled load of a matrix or, for
 //                              convolutions, a 4-D im2col load of the NHWC input (one filter tap x 128
-//                              channels per k-block)
+//                              channels per k-block).  A last k-block of at most 64 bytes, and every
+//                              k-block of a convolution whose taps have at most 64 channels, is 64 or 32
+//                              bytes wide with the swizzle of that width
 //   warp 1      MMA issuer     tcgen05.mma.cta_group::1.kind::i8 | kind::f8f6f4, 128 x BN x 32 per
 //                              instruction, operands read from smem through UMMA descriptors,
 //                              accumulators (s32 | f32) in tensor memory
@@ -14,7 +16,8 @@
 //                              fourth column block: tcgen05.ld (32 lanes x 16 columns) -> scale / bias
 //                              (staged in smem per tile column) / sum / ReLU / activation -> conversion ->
 //                              swizzled staging tile in smem -> one TMA store per block (direct stores
-//                              when rows are unaligned)
+//                              when rows are unaligned).  The loop is compiled in three forms (plain,
+//                              8-bit summand, general) and chosen per launch
 //   warps 20-23 (convolutions with densely packed filters only) gather the A tile with cp.async
 // Pipelines are mbarrier based: full[s]/empty[s] between producer and MMA issuer
 // (tcgen05.commit releases a stage), tmem_full[a]/tmem_empty[a] between MMA issuer and
@@ -23,8 +26,11 @@
 //
 // Epilogue arithmetic: int->float uses the exact 1.5*2^23 adder trick (the conversion instructions
 // run on the multi-function unit, the slowest pipe of this part and the first measured bottleneck),
-// with the real conversion kept for accumulators beyond 2^22; float->8-bit is one saturating
-// conversion per element.  Multiply and add stay separate roundings (bit-exactness with oneDNN).
+// with the real conversion kept for accumulators beyond 2^22 (in the plain loop the accumulators start
+// from that bit pattern, so the tensor core does the add); float->8-bit is one conversion to s32 per
+// element and a saturating pack per pair.  Multiply and add stay separate roundings (bit-exactness with
+// oneDNN).  The kernel is launched with programmatic stream serialization: everything before
+// griddepcontrol.wait may overlap the previous kernel of the stream.
 //
 // No cluster launch and no multicast loads are used, so the same code runs unchanged in
 // single- and multi-GPU jobs.
@@ -875,7 +881,9 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   const int tiles_m = (g.m + kBM - 1) / kBM;
   const int tiles_n = (g.n + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n * g.batch;
-  const int num_kb = (g.k + kBK - 1) / kBK;
+  // bytes of K per k-block: 128, or in the im2col path 64 / 32 when a filter tap has that many (padded) channels
+  const int kb_bytes = (CONV == kConvIm2col && g.conv_cpad < kBK) ? g.conv_cpad : kBK;
+  const int num_kb = (g.k + kb_bytes - 1) / kb_bytes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -930,10 +938,13 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         if (CONV == kConvGather) {
           MbarArriveExpectTx(fb, C::kBBytes);  // the A tile is gathered by the last four warps
         } else if (CONV == kConvIm2col) {
-          MbarArriveExpectTx(fb, C::kStageBytes);
+          MbarArriveExpectTx(fb, uint32_t((kBM + BN) * kb_bytes));
           TmaLoadIm2col(SmemAddr(sa), &tma_a, fb, c0, w0, h0, n0, kx * g.dil_w, ky * g.dil_h);
-          c0 += kBK;
+          c0 += kb_bytes;
           if (c0 >= g.conv_cpad) { c0 = 0; if (++kx == g.kw) { kx = 0; ++ky; } }
+          TmaLoad3d(SmemAddr(sa + C::kABytes), &tma_b, fb, kb * kb_bytes, tn * BN, bt);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          continue;
         } else if (g.tail_box != 0 && kb == num_kb - 1) {
           // the last k-block is 64 or 32 bytes wide: narrower boxes (nothing outside the tensor is touched) into
           // tiles with the matching narrower swizzle
@@ -975,10 +986,12 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         if (!ok) break;
         TcFenceAfter();
         uint8_t* sa = smem + stage * C::kStageBytes;
-        if (CONV == kConvNone && g.tail_box != 0 && kb == num_kb - 1) {
-          const uint64_t a_desc = UmmaDescNarrow(SmemAddr(sa), g.tail_box);
-          const uint64_t b_desc = UmmaDescNarrow(SmemAddr(sa + C::kABytes), g.tail_box);
-          for (int k = 0; k < g.tail_box / kUmmaK; ++k)
+        const int narrow = (CONV == kConvIm2col && kb_bytes < kBK) ? kb_bytes
+                           : ((CONV == kConvNone && g.tail_box != 0 && kb == num_kb - 1) ? g.tail_box : 0);
+        if (narrow != 0) {
+          const uint64_t a_desc = UmmaDescNarrow(SmemAddr(sa), narrow);
+          const uint64_t b_desc = UmmaDescNarrow(SmemAddr(sa + C::kABytes), narrow);
+          for (int k = 0; k < narrow / kUmmaK; ++k)
             UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
                        ((kb | k) != 0 || g.preset) ? 1u : 0u);
         } else {
@@ -1224,8 +1237,10 @@ int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p) {
   const int lower[2] = {-p.pad_left, -p.pad_top};
   const int upper[2] = {(p.ow - 1) * p.stride_w - p.pad_left - p.w + 1, (p.oh - 1) * p.stride_h - p.pad_top - p.h + 1};
   const cuuint32_t estr[4] = {1, cuuint32_t(p.stride_w), cuuint32_t(p.stride_h), 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(p.x), dims, strides, lower, upper, cuuint32_t(kBK),
-                   cuuint32_t(kBM), estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  const int box_c = p.c_pad < kBK ? p.c_pad : kBK;  // 128 channels per box, or a whole (padded) tap of 64 / 32
+  const CUtensorMapSwizzle sw = box_c == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (box_c == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(p.x), dims, strides, lower, upper, cuuint32_t(box_c),
+                   cuuint32_t(kBM), estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ITEXB_REQUIRE(r == CUDA_SUCCESS, ITEXB_INTERNAL,
                 "cuTensorMapEncodeIm2col failed with CUresult %d (n=%d h=%d w=%d c=%d corners [%d,%d] [%d,%d] strides %d,%d)", int(r), p.n,

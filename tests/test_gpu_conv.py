@@ -165,8 +165,9 @@ def _abi_conv(itex, x, f, scale, bias, stride, dil, pad, oh, ow, c_pad, out_dtyp
 
 @pytest.mark.parametrize("case", [
     # n, h, w, c, k, co, stride, dilation
-    (2, 14, 14, 64, 3, 64, 1, 1),      # c < 128: the TMA im2col path pads each tap to 128 channels
-    (3, 9, 11, 32, 3, 40, 2, 1),       # ragged: 3*5*6 = 90 pixels in one tile, stride 2, odd sizes
+    (2, 14, 14, 64, 3, 64, 1, 1),      # c = 64: the TMA im2col path runs 64-byte k-blocks (one tap each, 64-byte swizzle)
+    (3, 9, 11, 32, 3, 40, 2, 1),       # ragged: 3*5*6 = 90 pixels in one tile, stride 2, odd sizes; 32-byte k-blocks
+    (2, 10, 13, 48, 3, 72, 1, 1),      # c = 48: taps padded to 64 channels, each box a quarter outside the tensor
     (2, 17, 17, 128, 3, 96, 1, 2),     # dilation 2
     (2, 12, 12, 192, 3, 272, 2, 1),    # c = 128 + 64: second k-block of a tap is half outside the tensor
     (1, 7, 7, 256, 1, 64, 2, 1),       # strided 1x1 (projection shortcut)
@@ -174,7 +175,8 @@ def _abi_conv(itex, x, f, scale, bias, stride, dil, pad, oh, ow, c_pad, out_dtyp
 ])
 def test_lowerings_agree(case):
     """The three ways the A operand is produced (patch matrix in scratch, cp.async gather inside the GEMM,
-    TMA im2col loads) give identical bytes, and those equal the oracle's."""
+    TMA im2col loads) give identical bytes, and those equal the oracle's.  (With c_pad = c the dense-filter run
+    takes the cp.async gather unless c is itself a k-block width the im2col path accepts: 32, 64 or a multiple of 128.)"""
     itex, K, ops = modules()
     n, h, w, c, k, co, stride, dil = case
     rng = np.random.default_rng(sum(case))
@@ -187,7 +189,7 @@ def test_lowerings_agree(case):
     bias = rng.standard_normal(co).astype(np.float32)
     xd, fd, sd, bd = dev(x), dev(f), dev(scale), dev(bias)
     im2col, c_pad, ws0 = _abi_conv(itex, xd, fd, sd, bd, stride, dil, pad_h, oh, ow, "preferred")
-    assert c_pad == (c + 127) // 128 * 128 and ws0 == 0
+    assert c_pad == (32 if c <= 32 else (64 if c <= 64 else (c + 127) // 128 * 128)) and ws0 == 0
     dense, _, ws1 = _abi_conv(itex, xd, fd, sd, bd, stride, dil, pad_h, oh, ow, c)
     if c % 128 != 0:
         assert ws1 == 0                      # cp.async gather: no scratch either
