@@ -67,7 +67,10 @@ def test_pooling_ops_match_oracle_on_odd_shapes():
     itex, K, ops = modules()
     rng = np.random.default_rng(4)
     for (n, h, w, c, k, s, pad, avg, dt) in ((2, 11, 9, 32, 3, 2, "SAME", False, np.uint8), (1, 7, 7, 48, 7, 7, "VALID", True, np.uint8),
-                                             (2, 10, 10, 5, 2, 2, "VALID", False, np.int8), (1, 9, 9, 16, 3, 1, "SAME", True, np.int8)):
+                                             (2, 10, 10, 5, 2, 2, "VALID", False, np.int8), (1, 9, 9, 16, 3, 1, "SAME", True, np.int8),
+                                             (2, 8, 12, 32, 3, 2, "SAME", False, np.int8),      # signed max, 16 channels per thread
+                                             (1, 12, 13, 16, 11, 1, "VALID", True, np.uint8),    # window rows longer than one batch of loads
+                                             (1, 12, 13, 16, 11, 2, "SAME", False, np.int8)):
         x = rng.integers(0, 256, (n, h, w, c)).astype(np.uint8) if dt == np.uint8 else rng.integers(-128, 128, (n, h, w, c)).astype(np.int8)
         op = ops.Op("_ITEXQuantizedAvgPool" if avg else "_ITEXQuantizedMaxPool", T="quint8" if dt == np.uint8 else "qint8",
                     ksize=[1, k, k, 1], strides=[1, s, s, 1], padding=pad)
