@@ -194,15 +194,16 @@ def test_raw_accumulators_exact_large_and_canaries():
     assert bool((got == ref).all())
 
 
-@pytest.mark.parametrize("summand", [False, True])
-def test_epilogue_bound_shape(summand):
-    """A ResNet-sized 1x1 convolution as a GEMM (200704 pixels x 256 channels, K = 64: one 64-byte k-block per tile, so
-    the epilogue is all there is) with per-channel scale, bias, ReLU[, a u8 summand] and u8 output, three launches.
+@pytest.mark.parametrize("n,k,summand", [(256, 64, False), (256, 64, True), (64, 256, False)], ids=["n256-plain", "n256-sum", "n64-plain"])
+def test_epilogue_bound_shape(n, k, summand):
+    """ResNet-sized 1x1 convolutions as GEMMs (200704 pixels; 256 channels from K = 64: one 64-byte k-block per tile, so
+    the epilogue is all there is; 64 channels from K = 256: 64-column tiles, one slice per epilogue warp and tile) with
+    per-channel scale, bias, ReLU[, a u8 summand] and u8 output, three launches.
     Checked in full against the same arithmetic in separate fp32 steps on the raw accumulators (themselves exact by
     the test above): multiply, add[, multiply-add of the summand in two roundings], clamp, round half to even."""
     itex, K, ops = modules()
     L = itex._lib
-    m, n, k = 200704, 256, 64
+    m = 200704
     g = torch.Generator(device="cuda").manual_seed(5)
     a = torch.randint(0, 256, (m, k), device="cuda", generator=g).to(torch.uint8)
     b = torch.randint(-127, 128, (n, k), device="cuda", generator=g).to(torch.int8)
