@@ -130,12 +130,6 @@ __device__ __forceinline__ void TmaLoad3d(uint32_t dst, const void* tmap, uint32
       "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
-__device__ __forceinline__ void TmaLoad2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-      "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
 
 // One k-block of a convolution's A operand: 128 channels from c0 of the pixels that start at
 // base position (w, h, n) and follow the map's traversal strides, displaced by the filter tap's
@@ -233,26 +227,11 @@ __device__ __forceinline__ void TileCoords(int t, const GemmArgs& g, int tiles_m
 constexpr float kMagic = 12582912.f;        // 1.5 * 2^23
 constexpr int kMagicBits = 0x4B400000;
 
-// Conversions between int and float are done on the fp32 adder with the 1.5*2^23 trick, which
-// rounds to nearest even exactly like the conversion instructions do; those run on the
-// multi-function unit, the slowest pipe of this part (measured 71 % busy, everything else idle).
-// float(a), exact, valid when |a| <= 2^22.
-__device__ __forceinline__ float SmallIntToFloat(int a) { return __fsub_rn(__int_as_float(a + kMagicBits), kMagic); }
-// rne(clamp(f, lo, hi)) for -128 <= lo, hi <= 255 in the low byte of the result; the upper
-// bytes are junk (NaN converts like lo).
-__device__ __forceinline__ uint32_t SatRneLowByte(float f, float lo, float hi) {
-  f = fminf(fmaxf(f, lo), hi);
-  return uint32_t(__float_as_int(__fadd_rn(f, kMagic)));
-}
-// Saturating round-to-nearest-even conversion to an 8-bit integer in the low byte (one
-// instruction on the conversion unit; the clamp-and-add form costs three on the main pipes).
-template <bool SIGNED> __device__ __forceinline__ uint32_t SatRne8(float f) {
-  uint32_t r;
-  if (SIGNED) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(f));
-  else asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(f));
-  return r;
-}
-// Round-to-nearest-even conversion to s32 (out-of-range values clamp, NaN gives 0) and the saturating pack of
+// int -> float is done on the fp32 adder with the 1.5*2^23 trick (exact for |a| <= 2^22), because the
+// conversion instructions run on the multi-function unit, the slowest pipe of this part (measured
+// 71 % busy, everything else idle, when every conversion went through it).
+//
+// float -> 8-bit: round-to-nearest-even conversion to s32 (out-of-range values clamp, NaN gives 0) and the saturating pack of
 // four s32 into four 8-bit lanes: one conversion-unit instruction per element plus two packs per four,
 // against two conversion-unit instructions per element for a direct float -> 8-bit conversion.
 __device__ __forceinline__ int RneS32(float f) {
@@ -283,11 +262,6 @@ __device__ __forceinline__ uint64_t Pack2(float lo, float hi) {
   return r;
 }
 __device__ __forceinline__ void Unpack2(uint64_t p, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p)); }
-__device__ __forceinline__ uint64_t Mul2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
 __device__ __forceinline__ uint64_t Fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
