@@ -1,6 +1,10 @@
 // The old-API quantized Conv2D ops, NHWC: [_ITEX]QuantizedConv2D, ...PerChannel, ...WithBias, ...WithBiasAndRelu
 // (qint32 outputs), ...AndRequantize, ...AndReluAndRequantize, ...WithBias[AndRelu]AndRequantize and the Sum-fused
-// variants (8-bit outputs).
+// variants (8-bit outputs); and two fusions around them the remapper makes: _ITEXQuantizedConv2DWithDequantize /
+// ...WithCast (a ...WithBiasAndRequantize whose Dequantize or Cast consumer is folded in: real-valued output,
+// itex/core/graph/remapper/remapper.cc:2178-2240, scale rule kernels/onednn/block/conv_ops_impl.h:1928-1963) and
+// _ITEXQuantizeV2WithQuantizedConv2D (a QuantizeV2 folded into the ...WithBiasAndReluAndRequantize it feeds: fp32
+// input, remapper.cc:2099-2123, kernels/onednn/block/conv_ops_impl.h:1238-1420).
 //
 // Attrs, input order (input, filter, [bias,] min_input, max_input, min_filter, max_filter
 // [, min_freezed_output, max_freezed_output][, summand, min_summand, max_summand]), the
@@ -17,10 +21,16 @@
 namespace itexb {
 namespace {
 
+enum class ConvFusion { kNone, kDequantizeTail, kQuantizeHead };
+
 class QuantizedConv2DOp : public OpKernel {
  public:
-  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum, bool has_bias = true, bool requantize = true, bool new_api = false)
-      : relu_(relu), sum_(sum), signed_sum_(signed_sum), has_bias_(has_bias), requantize_(requantize), new_api_(new_api) {}
+  QuantizedConv2DOp(bool relu, bool sum, bool signed_sum, bool has_bias = true, bool requantize = true, bool new_api = false,
+                    ConvFusion fusion = ConvFusion::kNone)
+      : relu_(relu), sum_(sum), signed_sum_(signed_sum), has_bias_(has_bias), requantize_(requantize), new_api_(new_api),
+        fusion_(fusion) {
+    if (fusion == ConvFusion::kDequantizeTail) { requantize_ = false; dequantize_ = true; }
+  }
 
   // New API (_QuantizedConv2D / _ITEXQuantizedConv2DV2): the fusion comes from the fused_ops attr
   // (LegacyQuantizedConvOpBase constructor, itex/core/kernels/common/quantized_conv_ops.h:76-312).
@@ -90,9 +100,29 @@ class QuantizedConv2DOp : public OpKernel {
     if (attrs.Has("is_filter_const")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("is_filter_const", &is_filter_const_));
     if (attrs.Has("is_bias_const")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("is_bias_const", &is_bias_const_));
     tinput_ = ITEXB_DT_QUINT8;
-    if (attrs.Has("Tinput")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tinput", &tinput_));
-    ITEXB_REQUIRE(tinput_ == ITEXB_DT_QUINT8 || tinput_ == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT,
-                  "%s: no kernel registered for Tinput=%s", op, DtypeName(tinput_));
+    if (fusion_ == ConvFusion::kQuantizeHead) {
+      // Tinput is the type of the real-valued data; what the convolution reads is quint8 (the only registration,
+      // itex/core/kernels/onednn/block/conv_ops_impl_gpu.cc:716-773)
+      treal_ = ITEXB_DT_FLOAT;
+      if (attrs.Has("Tinput")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tinput", &treal_));
+      ITEXB_REQUIRE(treal_ == ITEXB_DT_FLOAT || treal_ == ITEXB_DT_BFLOAT16, ITEXB_INVALID_ARGUMENT,
+                    "%s: no kernel registered for Tinput=%s (float and bfloat16 are)", op, DtypeName(treal_));
+      std::string mode = "SCALED";
+      if (attrs.Has("mode")) ITEXB_RETURN_IF_ERROR(attrs.GetString("mode", &mode));
+      ITEXB_REQUIRE(mode == "MIN_COMBINED" || mode == "MIN_FIRST" || mode == "SCALED", ITEXB_INVALID_ARGUMENT,
+                    "Mode string must be 'MIN_COMBINED', 'MIN_FIRST', or 'SCALED', is '%s'", mode.c_str());
+      ITEXB_REQUIRE(mode == "SCALED", ITEXB_UNIMPLEMENTED, "%s: only mode SCALED is implemented", op);
+      std::string round_mode = "HALF_AWAY_FROM_ZERO";
+      if (attrs.Has("round_mode")) ITEXB_RETURN_IF_ERROR(attrs.GetString("round_mode", &round_mode));
+      ITEXB_REQUIRE(round_mode == "HALF_AWAY_FROM_ZERO" || round_mode == "HALF_TO_EVEN", ITEXB_INVALID_ARGUMENT,
+                    "Round mode string must be 'HALF_AWAY_FROM_ZERO' or 'HALF_TO_EVEN', is '%s'", round_mode.c_str());
+      ensure_minimum_range_ = 0.01f;
+      if (attrs.Has("ensure_minimum_range")) ITEXB_RETURN_IF_ERROR(attrs.GetFloat("ensure_minimum_range", &ensure_minimum_range_));
+    } else {
+      if (attrs.Has("Tinput")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tinput", &tinput_));
+      ITEXB_REQUIRE(tinput_ == ITEXB_DT_QUINT8 || tinput_ == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT,
+                    "%s: no kernel registered for Tinput=%s", op, DtypeName(tinput_));
+    }
     int tfilter = ITEXB_DT_QINT8;
     if (attrs.Has("Tfilter")) ITEXB_RETURN_IF_ERROR(attrs.GetType("Tfilter", &tfilter));
     ITEXB_REQUIRE(tfilter == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT, "%s: no kernel registered for Tfilter=%s", op, DtypeName(tfilter));
@@ -112,7 +142,10 @@ class QuantizedConv2DOp : public OpKernel {
                       "QuantizedConv: unsupported output type when Dequantize is fused.");
       else
         ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT, "%s: out_type must be qint32 without Requantize / Dequantize", op);
-    } else if (!requantize_)
+    } else if (fusion_ == ConvFusion::kDequantizeTail)
+      ITEXB_REQUIRE(out_type_ == ITEXB_DT_FLOAT || out_type_ == ITEXB_DT_BFLOAT16 || out_type_ == ITEXB_DT_HALF, ITEXB_INVALID_ARGUMENT,
+                    "%s: no kernel registered for out_type=%s (float, bfloat16 and half are)", op, DtypeName(out_type_));
+    else if (!requantize_)
       ITEXB_REQUIRE(out_type_ == ITEXB_DT_QINT32, ITEXB_INVALID_ARGUMENT, "%s: no kernel registered for out_type=%s (qint32 is)", op,
                     DtypeName(out_type_));
     else if (relu_)
@@ -132,7 +165,9 @@ class QuantizedConv2DOp : public OpKernel {
     const int i_sum = new_api_ ? 2 + (has_bias_ ? 1 : 0) : i_rng + 4 + (requantize_ ? 2 : 0);   // summand
     const int i_sum_rng = new_api_ ? i_rng + 4 : i_sum + 1;                    // min_summand, max_summand
     const int i_frz = new_api_ ? i_rng + 4 + (sum_ ? 2 : 0) : i_rng + 4;       // min/max_freezed_output
-    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, i_rng + 4 + (requantize_ ? 2 : 0) + (sum_ ? (new_api_ ? 2 : 3) : 0), op));
+    // (the Dequantize / Cast fusions keep the frozen output range of the op they replaced as two unused inputs)
+    const bool frozen_inputs = requantize_ || fusion_ == ConvFusion::kDequantizeTail;
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, i_rng + 4 + (frozen_inputs ? 2 : 0) + (sum_ ? (new_api_ ? 2 : 3) : 0), op));
     ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 0, op, "input"));
     ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 1, op, "filter"));
     if (has_bias_) ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 2, op, "bias"));
@@ -142,8 +177,9 @@ class QuantizedConv2DOp : public OpKernel {
     const itexb_tensor_t& bias = has_bias_ ? ctx->inputs[2] : kNoTensor;
     ITEXB_REQUIRE(x.rank == 4, ITEXB_INVALID_ARGUMENT, "input must be 4-dimensional");
     ITEXB_REQUIRE(f.rank == 4, ITEXB_INVALID_ARGUMENT, "filter must be 4-dimensional");
-    ITEXB_REQUIRE(x.dtype == tinput_, ITEXB_INVALID_ARGUMENT, "%s: input has type %s, Tinput is %s", op, DtypeName(x.dtype),
-                  DtypeName(tinput_));
+    const int want_x = fusion_ == ConvFusion::kQuantizeHead ? treal_ : tinput_;
+    ITEXB_REQUIRE(x.dtype == want_x, ITEXB_INVALID_ARGUMENT, "%s: input has type %s, Tinput is %s", op, DtypeName(x.dtype),
+                  DtypeName(want_x));
     ITEXB_REQUIRE(f.dtype == ITEXB_DT_QINT8, ITEXB_INVALID_ARGUMENT, "%s: filter must be qint8", op);
     ITEXB_REQUIRE(!has_bias_ || bias.dtype == tbias_, ITEXB_INVALID_ARGUMENT, "%s: bias has type %s, Tbias is %s", op,
                   DtypeName(bias.dtype), DtypeName(tbias_));
@@ -172,7 +208,18 @@ class QuantizedConv2DOp : public OpKernel {
     }
     ITEXB_REQUIRE(nf1 == nf2 && (nf1 == 1 || nf1 == co), ITEXB_INVALID_ARGUMENT,
                   "%s: min_filter/max_filter must be scalars or vectors of %lld elements", op, (long long)co);
-    const float min_in = pmin_in[0], max_in = pmax_in[0], min_o = pmin_o[0], max_o = pmax_o[0];
+    float min_in = pmin_in[0], max_in = pmax_in[0];
+    const float min_o = pmin_o[0], max_o = pmax_o[0];
+    float quantize_scale = 1.f;
+    if (fusion_ == ConvFusion::kQuantizeHead) {
+      // QuantizeV2 SCALED to quint8 (quantize_op.h:130-152, 397-408): the convolution then sees the range [0, max]
+      float qmin, qmax;
+      ITEXB_REQUIRE(hostmath::AdjustInputMinMaxRange(min_in, max_in, ensure_minimum_range_, &qmin, &qmax), ITEXB_INVALID_ARGUMENT,
+                    "input_max_range must be larger than input_min_range.");
+      quantize_scale = hostmath::ScaledScale(&qmin, &qmax, ITEXB_DT_QUINT8, true);
+      min_in = 0.f;
+      max_in = qmax;
+    }
     float sum_scale = 1.f;
     const itexb_tensor_t* summand = nullptr;
     if (sum_) {
@@ -254,9 +301,17 @@ class QuantizedConv2DOp : public OpKernel {
       saved_factors_ = factors;
     }
 
+    const void* x_data = x.data;
+    if (fusion_ == ConvFusion::kQuantizeHead) {
+      void* q = nullptr;
+      ITEXB_RETURN_IF_ERROR(AllocateTemp(ctx, size_t(n) * h * w * c, false, &q));
+      ITEXB_RETURN_IF_ERROR(itexb_quantize(x.data, x.dtype, q, ITEXB_DT_QUINT8, n * h * w * c, 1, 1, ITEXB_QUANT_SCALED, nullptr, nullptr,
+                                           quantize_scale, 0.f, ctx->stream));
+      x_data = q;
+    }
     p.c_pad = c_pad;
     p.x_dtype = tinput_; p.out_dtype = out_type_;
-    p.x = x.data; p.filter_packed = packed_.data(); p.out = dst.data;
+    p.x = x_data; p.filter_packed = packed_.data(); p.out = dst.data;
     if (out_type_ != ITEXB_DT_QINT32) {
       p.ep.scale = d_scale;
       p.ep.scale_count = int(scales.size());
@@ -281,7 +336,10 @@ class QuantizedConv2DOp : public OpKernel {
  private:
   bool relu_, sum_, signed_sum_, has_bias_, requantize_;
   const bool new_api_;
+  const ConvFusion fusion_;
   bool dequantize_ = false;
+  int treal_ = ITEXB_DT_FLOAT;           // kQuantizeHead: type of the real-valued input
+  float ensure_minimum_range_ = 0.01f;   // kQuantizeHead: QuantizeV2's attr
   int act_ = ITEXB_ACT_NONE;
   float act_alpha_ = 0.f;
   int stride_h_ = 1, stride_w_ = 1, dil_h_ = 1, dil_w_ = 1, padding_ = 1;
@@ -325,6 +383,14 @@ ITEXB_REGISTER_OP("QuantizedConv2DAndRequantize", ConvReq, 8, 3, 0xfcu, 0x6u);
 ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndRequantize", ConvReq, 8, 3, 0xfcu, 0x6u);
 ITEXB_REGISTER_OP("QuantizedConv2DAndReluAndRequantize", ConvReluReq, 8, 3, 0xfcu, 0x6u);
 ITEXB_REGISTER_OP("_ITEXQuantizedConv2DAndReluAndRequantize", ConvReluReq, 8, 3, 0xfcu, 0x6u);
+struct ConvBiasDeq : QuantizedConv2DOp { ConvBiasDeq() : QuantizedConv2DOp(false, false, false, true, false, false, ConvFusion::kDequantizeTail) {} };
+struct QuantConvBiasReluReq : QuantizedConv2DOp {
+  QuantConvBiasReluReq() : QuantizedConv2DOp(true, false, false, true, true, false, ConvFusion::kQuantizeHead) {}
+};
+// HostMemory: the six ranges, inputs 3..8 (conv_ops_impl_gpu.cc:716-1000); outputs 1, 2 of the quantizing op.
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithDequantize", ConvBiasDeq, 9, 1, 0x1f8u, 0x0u);
+ITEXB_REGISTER_OP("_ITEXQuantizedConv2DWithCast", ConvBiasDeq, 9, 1, 0x1f8u, 0x0u);
+ITEXB_REGISTER_OP("_ITEXQuantizeV2WithQuantizedConv2D", QuantConvBiasReluReq, 9, 3, 0x1f8u, 0x6u);
 struct ConvV2 : QuantizedConv2DOp { ConvV2() : QuantizedConv2DOp(false, false, false, false, false, true) {} };
 // New API: list-typed arguments (counts depend on fused_ops), every range in host memory
 // (HostMemoryList2("host_inputs", "host_outputs"), itex/core/kernels/gpu/quantized_conv_ops.cc:171-200)

@@ -398,13 +398,16 @@ def _ITEXQuantizedConv2DWithBiasAndReluAndRequantize(input, filter, bias, min_in
 
 def QuantizedConv2D(op_name, input, filter, bias, min_input, max_input, min_filter, max_filter, min_freezed_output=None,
                     max_freezed_output=None, strides=(1, 1, 1, 1), padding="SAME", dilations=(1, 1, 1, 1), out_type="qint32",
-                    is_filter_const=True, is_bias_const=True):
+                    is_filter_const=True, is_bias_const=True, **extra_attrs):
     """The other members of the legacy conv family by name: QuantizedConv2D, ...PerChannel, ...AndRelu, ...WithBias,
-    ...WithBiasAndRelu (qint32 outputs; `bias` None for the first three) and ...AndRequantize, ...AndReluAndRequantize
-    (no bias, frozen output range).  -> (output, min_output, max_output)"""
+    ...WithBiasAndRelu (qint32 outputs; `bias` None for the first three), ...AndRequantize, ...AndReluAndRequantize
+    (no bias, frozen output range), _ITEXQuantizedConv2DWithDequantize / ...WithCast (real-valued output) and
+    _ITEXQuantizeV2WithQuantizedConv2D (real-valued input; extra_attrs carry the QuantizeV2 attrs mode, round_mode,
+    ensure_minimum_range).  -> (output, min_output, max_output), or output for a real-valued output."""
     attrs = dict(Tinput=_TORCH_TO_DT[input.dtype], Tfilter="qint8", out_type=out_type, strides=list(strides), padding=padding,
                  dilations=list(dilations), data_format="NHWC", is_filter_const=bool(is_filter_const),
                  is_bias_const=bool(is_bias_const))
+    attrs.update(extra_attrs)
     args = [input, filter]
     dtypes = None
     if bias is not None:

@@ -659,6 +659,17 @@ def quantized_conv2d(x, filt, bias, min_input, max_input, min_filter, max_filter
     return out, None, None
 
 
+def quantize_v2_with_quantized_conv2d(x, filt, bias, min_input, max_input, min_filter, max_filter, min_freezed_output,
+                                      max_freezed_output, *, ensure_minimum_range: float = 0.01, **conv_kwargs):
+    """_ITEXQuantizeV2WithQuantizedConv2D: the QuantizeV2 (SCALED, to quint8) the remapper folds into the
+    _ITEXQuantizedConv2DWithBiasAndReluAndRequantize it feeds (itex/core/graph/remapper/remapper.cc:2099-2123; kernel
+    OneDnnQuantizeV2WithQuantizedConv2DOp, itex/core/kernels/onednn/block/conv_ops_impl.h:1238-1420).  min_input /
+    max_input are the QuantizeV2's range inputs; the convolution sees the range the quantize step outputs."""
+    q, qmin, qmax = quantize_v2(x, min_input, max_input, T=QUINT8, mode="SCALED", ensure_minimum_range=ensure_minimum_range)
+    return quantized_conv2d(q, filt, bias, qmin, qmax, min_filter, max_filter, min_freezed_output, max_freezed_output,
+                            out_type=QUINT8, relu=True, **conv_kwargs)
+
+
 # --------------------------------------------------------------------------
 # FP8 (parity unpinned: the reference has no FP8 test)
 # --------------------------------------------------------------------------

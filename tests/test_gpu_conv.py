@@ -250,6 +250,40 @@ def test_legacy_family_qint32_and_no_bias(tin):
     np.testing.assert_array_equal(host(got), ref)
 
 
+def test_remapper_fusions_around_the_requantizing_conv():
+    """_ITEXQuantizedConv2DWithDequantize / ...WithCast (a ...WithBiasAndRequantize with its Dequantize or Cast consumer
+    folded in: real-valued output, the frozen range inputs kept but unused) and _ITEXQuantizeV2WithQuantizedConv2D
+    (a QuantizeV2 folded into the ...WithBiasAndReluAndRequantize it feeds): bit-exact against the oracle, and the
+    quantize fusion identical to running the two ops one after the other."""
+    itex, K, ops = modules()
+    rng = np.random.default_rng(43)
+    n, h, w, c, co = 2, 12, 12, 32, 48
+    f32, qf, mnf, mxf = _filter(rng, 3, 3, c, co)
+    bias = (rng.standard_normal(co) * 0.5).astype(np.float32)
+    F, B = dev(qf), dev(bias)
+    for tin, (mni, mxi) in (("quint8", (0.0, 6.0)), ("qint8", (-3.0, 3.0))):
+        x = rng.integers(0, 256, (n, h, w, c)).astype(np.uint8) if tin == "quint8" else rng.integers(-127, 128, (n, h, w, c)).astype(np.int8)
+        for name, tout in (("_ITEXQuantizedConv2DWithDequantize", "float"), ("_ITEXQuantizedConv2DWithDequantize", "bfloat16"),
+                           ("_ITEXQuantizedConv2DWithCast", "half")):
+            ref, _, _ = o.quantized_conv2d(x, qf, bias, mni, mxi, mnf, mxf, out_type=tout, relu=False, strides=(1, 1, 1, 1))
+            got = ops.QuantizedConv2D(name, dev(x), F, B, mni, mxi, mnf, mxf, -7.0, 7.0, out_type=tout, strides=(1, 1, 1, 1))
+            assert isinstance(got, torch.Tensor) and got.dtype == {"float": torch.float32, "bfloat16": torch.bfloat16, "half": torch.float16}[tout]
+            np.testing.assert_array_equal(host(got), np.asarray(ref, np.float32))
+    # quantize + conv
+    xf = (rng.standard_normal((n, h, w, c)) * 1.5 + 1.0).astype(np.float32)
+    lo, hi = float(xf.min()), float(xf.max())
+    ref, rmn, rmx = o.quantize_v2_with_quantized_conv2d(xf, qf, bias, lo, hi, mnf, mxf, 0.0, 9.0, strides=(1, 2, 2, 1))
+    got, gmn, gmx = ops.QuantizedConv2D("_ITEXQuantizeV2WithQuantizedConv2D", dev(xf), F, B, lo, hi, mnf, mxf, 0.0, 9.0, out_type="quint8",
+                                        strides=(1, 2, 2, 1), mode="SCALED", round_mode="HALF_TO_EVEN")
+    np.testing.assert_array_equal(host(got), ref)
+    assert (gmn, gmx) == (np.float32(0.0), np.float32(9.0))
+    q, qmn, qmx = ops._ITEXQuantizeV2(dev(xf), lo, hi, T="quint8", mode="SCALED", round_mode="HALF_TO_EVEN")
+    two, _, _ = ops._ITEXQuantizedConv2DWithBiasAndReluAndRequantize(q, F, B, qmn, qmx, mnf, mxf, 0.0, 9.0, strides=(1, 2, 2, 1))
+    assert torch.equal(got, two)
+    with pytest.raises(itex.ItexError, match="only mode SCALED"):
+        ops.QuantizedConv2D("_ITEXQuantizeV2WithQuantizedConv2D", dev(xf), F, B, lo, hi, mnf, mxf, 0.0, 9.0, out_type="quint8", mode="MIN_FIRST")
+
+
 def test_new_api_fused_ops():
     """_QuantizedConv2D / _ITEXQuantizedConv2DV2: fusion given by the fused_ops attr, list-typed arguments in the new order
     (summand before the ranges, frozen output range last).  Bit-exact for integer outputs and algebraic post-ops."""
