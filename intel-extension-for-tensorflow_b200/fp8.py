@@ -7,6 +7,7 @@ layer.py:65-100,170-194 (meta layout: slot 0 = input, 1 = weight, 2 = output per
 State lives in three device tensors per direction, updated by one small kernel
 (itexb_fp8_amax_and_scale_update) instead of a chain of TF ops.
 """
+from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Optional
 
@@ -34,6 +35,44 @@ class DelayedScaling:
                 or self.amax_compute_algo not in ("max", "most_recent"):
             raise ValueError("We only support the fp8 recipe with 'max' or 'most_recent' amax_compute_algo and default "
                              "scaling_factor_compute_algo at this moment.")
+
+
+# ---- fp8_autocast (itex/python/fp8/autocast.py:26-68,122-151): a process-wide "FP8 on" flag and recipe that layers
+# consult when they are built and called; nesting restores the outer state on exit.
+_FP8_ENABLED = False
+_FP8_RECIPE = None
+
+
+def get_default_fp8_recipe():
+    """Margin 0, HYBRID format, 'max' over the default history (autocast.py:42-47)."""
+    return DelayedScaling()
+
+
+def get_fp8_dtype(fp8_recipe, fwd=True):
+    """HYBRID: e4m3 forward, e5m2 backward (autocast.py:49-52)."""
+    assert fp8_recipe.fp8_format == "HYBRID"
+    return "E4M3" if fwd else "E5M2"
+
+
+def is_fp8_enabled():
+    return _FP8_ENABLED
+
+
+def get_fp8_recipe():
+    return _FP8_RECIPE
+
+
+@contextmanager
+def fp8_autocast(enabled: bool = False, fp8_recipe: Optional[DelayedScaling] = None):
+    """with fp8_autocast(enabled=True, fp8_recipe=DelayedScaling(...)): y = layer(x)"""
+    global _FP8_ENABLED, _FP8_RECIPE
+    saved = (_FP8_ENABLED, _FP8_RECIPE)
+    try:
+        _FP8_ENABLED = enabled
+        _FP8_RECIPE = get_default_fp8_recipe() if fp8_recipe is None else fp8_recipe
+        yield
+    finally:
+        _FP8_ENABLED, _FP8_RECIPE = saved
 
 
 class Fp8Meta:
@@ -72,7 +111,7 @@ class Fp8Dense:
                  out_dtype="bfloat16", weight_layout="kn"):
         self.kernel = kernel
         self.bias = bias
-        self.recipe = recipe or DelayedScaling()
+        self.recipe = recipe or (get_fp8_recipe() if is_fp8_enabled() else None) or DelayedScaling()  # explicit, autocast's, default
         self.meta = Fp8Meta(self.recipe, 1, kernel.device, fwd=True)
         self.out_dtype = out_dtype
         self.transpose_b = weight_layout == "nk"

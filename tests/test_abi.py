@@ -111,3 +111,24 @@ def test_fp8_recipe_rejects_what_the_reference_rejects(itex):
         fp8.DelayedScaling(amax_compute_algo=lambda h: h)
     with pytest.raises(ValueError):
         fp8.DelayedScaling(scaling_factor_compute_algo=lambda *a: a)
+
+
+def test_fp8_autocast_state_nests_and_restores(itex):
+    """fp8_autocast (itex/python/fp8/autocast.py:122-151): flag and recipe inside the block, outer state back on exit -
+    also when the block raises; the default recipe when none is given."""
+    import importlib
+    fp8 = importlib.import_module("itex_b200.fp8")
+    assert not fp8.is_fp8_enabled() and fp8.get_fp8_recipe() is None
+    outer = fp8.DelayedScaling(margin=1, amax_history_len=16)
+    with fp8.fp8_autocast(enabled=True, fp8_recipe=outer):
+        assert fp8.is_fp8_enabled() and fp8.get_fp8_recipe() is outer
+        with fp8.fp8_autocast(enabled=False):
+            assert not fp8.is_fp8_enabled()
+            assert fp8.get_fp8_recipe() == fp8.get_default_fp8_recipe()
+        assert fp8.is_fp8_enabled() and fp8.get_fp8_recipe() is outer
+        with pytest.raises(RuntimeError):
+            with fp8.fp8_autocast(enabled=True):
+                raise RuntimeError("inside")
+        assert fp8.get_fp8_recipe() is outer
+    assert not fp8.is_fp8_enabled() and fp8.get_fp8_recipe() is None
+    assert fp8.get_fp8_dtype(outer, fwd=True) == "E4M3" and fp8.get_fp8_dtype(outer, fwd=False) == "E5M2"
