@@ -1,7 +1,9 @@
 // Op registry, attribute access, per-instance caches and the C-ABI of the op layer
 // (itexb_op_* and itexb_simple_context_* of include/itexb200.h).
 #include <algorithm>
+#include <chrono>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 
 #include "op_kernel.h"
@@ -280,8 +282,21 @@ int itexb_op_compute(itexb_op_t* op, itexb_op_context_t* ctx) {
     prev = ctx->device_ordinal;
   }
   if (prev != ctx->device_ordinal) ITEXB_CUDA(cudaSetDevice(ctx->device_ordinal));
+  // ITEXB_VERBOSE (the reference's ITEX_VERBOSE, itex/core/utils/op_kernel.h:880-906 and op_kernel.cc:972-980): run the op
+  // to completion and print "type,name,nanoseconds" per call.  A node has no name at this boundary, so the second field is
+  // the kernel instance's address.
+  static const bool verbose = [] {
+    const char* e = std::getenv("ITEXB_VERBOSE");
+    return e != nullptr && std::atoll(e) != 0;
+  }();
+  const auto t0 = std::chrono::steady_clock::now();
   int st = op->kernel->Compute(ctx);
-  if (st == ITEXB_OK && std::getenv("ITEXB_SYNC_EXEC") != nullptr) st = CudaStatus(cudaStreamSynchronize(AsCuda(ctx->stream)), "ITEXB_SYNC_EXEC");
+  if (st == ITEXB_OK && (verbose || std::getenv("ITEXB_SYNC_EXEC") != nullptr))
+    st = CudaStatus(cudaStreamSynchronize(AsCuda(ctx->stream)), verbose ? "ITEXB_VERBOSE" : "ITEXB_SYNC_EXEC");
+  if (verbose) {
+    const long long ns = std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+    std::fprintf(stderr, "%s,%p,%lld\n", op->kernel->name().c_str(), static_cast<void*>(op->kernel.get()), ns);
+  }
   if (prev != ctx->device_ordinal) (void)cudaSetDevice(prev);
   return st;
 }

@@ -117,3 +117,28 @@ def test_simple_context_runs_an_op_without_python_allocation():
     L.check(lib.itexb_simple_context_reset(sctx))
     lib.itexb_simple_context_destroy.restype = None
     lib.itexb_simple_context_destroy(sctx)
+
+
+def test_verbose_prints_one_timing_line_per_op_call():
+    """ITEXB_VERBOSE=1 (the reference's ITEX_VERBOSE): every op call runs to completion and prints
+    "type,instance,nanoseconds" on stderr.  The switch is read once per process, hence the child process."""
+    import os
+    import re
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import importlib, torch\n"
+        "from conftest import load_package\n"
+        "load_package(); ops = importlib.import_module('itex_b200.ops')\n"
+        "x = torch.rand(1000, device='cuda')\n"
+        "for _ in range(2): ops._ITEXQuantizeV2(x, 0.0, 1.0, T='quint8')\n"
+        "print('done')\n" % here)
+    env = dict(os.environ, ITEXB_VERBOSE="1")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and "done" in r.stdout, r.stderr[-2000:]
+    lines = [l for l in r.stderr.splitlines() if l.startswith("_ITEXQuantizeV2,")]
+    assert len(lines) == 2
+    for l in lines:
+        assert re.fullmatch(r"_ITEXQuantizeV2,0x[0-9a-f]+,\d+", l), l
