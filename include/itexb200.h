@@ -240,10 +240,6 @@ typedef struct itexb_epilogue {
   int32_t activation;      /* itexb_activation_t, applied after summand and relu */
   float act_alpha, act_beta;
   float post_scale;        /* multiplies the activation's result; 0 is read as 1 */
-  float* out_minmax;       /* optional device float[2] = {min, max} of the values written (FLOAT | BFLOAT16 | HALF outputs,
-                              as stored, i.e. after rounding to the output type): folded in with atomic min / max, so the
-                              caller initialises it with itexb_minmax_init.  Saves the separate itexb_minmax pass when the
-                              output feeds a dynamically quantized matmul.                                             */
 } itexb_epilogue_t;
 
 /* out[m][n] = epilogue( sum_k a[m][k] * b[n][k] ).

@@ -41,7 +41,7 @@ class Epilogue(C.Structure):
                 ("summand_dtype", C.c_int32), ("ld_summand", C.c_int64), ("sum_scale", C.c_float),
                 ("relu", C.c_int32), ("raw_acc", C.c_int32), ("out_scale", C.c_void_p),
                 ("amax", C.c_void_p), ("mid_dtype", C.c_int32), ("activation", C.c_int32),
-                ("act_alpha", C.c_float), ("act_beta", C.c_float), ("post_scale", C.c_float), ("out_minmax", C.c_void_p)]
+                ("act_alpha", C.c_float), ("act_beta", C.c_float), ("post_scale", C.c_float)]
 
 
 class GemmParams(C.Structure):

@@ -501,10 +501,6 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   int acc = 0;
   uint32_t acc_phase = 0, seq = 0;
   float thread_amax = 0.f;
-  // min / max of the stored values, for a consumer that quantizes this output dynamically (general loop, real-valued outputs)
-  constexpr bool kCanMinMax = MODE == kEpGeneral && (OK == kOutF32 || OK == kOutBF16 || OK == kOutF16);
-  const bool want_minmax = kCanMinMax && g.ep.out_minmax != nullptr;
-  float thread_lo = __int_as_float(0x7f800000), thread_hi = __int_as_float(0xff800000);
   // Per-column scale and bias of the current tile column live in shared memory (s_par[0..BN) scales,
   // s_par[BN..2BN) biases): fetched from global memory once per change of tile column by the 512
   // epilogue threads together, instead of once per slice by every warp (that global-load latency,
@@ -761,16 +757,6 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                 if (col + j < g.n) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
             }
             Convert16<OK>(v, w, e.e4m3, e.out_scale);
-            if (kCanMinMax && want_minmax && row_ok) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float stored;  // the value as the output type holds it
-                if (OK == kOutF32) stored = v[j];
-                else if (OK == kOutBF16) stored = __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
-                else stored = __half2float(__ushort_as_half((unsigned short)(w[j >> 1] >> (16 * (j & 1)))));
-                if (col + j < g.n) { thread_lo = fminf(thread_lo, stored); thread_hi = fmaxf(thread_hi, stored); }
-              }
-            }
           }
           if (tma_store) {
             if (sl == 0) {
@@ -833,23 +819,6 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) thread_amax = fmaxf(thread_amax, __shfl_xor_sync(0xffffffffu, thread_amax, o));
     if (lane == 0 && thread_amax > 0.f) atomicMax(reinterpret_cast<int*>(g.ep.amax), __float_as_int(thread_amax));
-  }
-  if (kCanMinMax && want_minmax) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      thread_lo = fminf(thread_lo, __shfl_xor_sync(0xffffffffu, thread_lo, o));
-      thread_hi = fmaxf(thread_hi, __shfl_xor_sync(0xffffffffu, thread_hi, o));
-    }
-    if (lane == 0) {
-      // float min / max through integer atomics: non-negative floats order like signed ints, negative ones in reverse
-      // like unsigned ints (the target starts at +inf / -inf)
-      int* plo = reinterpret_cast<int*>(g.ep.out_minmax);
-      int* phi = plo + 1;
-      if (thread_lo >= 0.f) atomicMin(plo, __float_as_int(thread_lo));
-      else atomicMax(reinterpret_cast<unsigned*>(plo), __float_as_uint(thread_lo));
-      if (thread_hi >= 0.f) atomicMax(phi, __float_as_int(thread_hi));
-      else atomicMin(reinterpret_cast<unsigned*>(phi), __float_as_uint(thread_hi));
-    }
   }
 }
 
@@ -1336,7 +1305,7 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   // TMA stores.  Sum8: the same plus an 8-bit summand read 16 bytes at a time into an 8-bit output (the
   // residual additions of a quantized ResNet).
   g.ep_mode = kEpGeneral;
-  if (g.tma_store && g.ep.activation == ITEXB_ACT_NONE && g.ep.mid_dtype == 0 && !g.ep.raw_acc && g.ep.out_minmax == nullptr) {
+  if (g.tma_store && g.ep.activation == ITEXB_ACT_NONE && g.ep.mid_dtype == 0 && !g.ep.raw_acc) {
     const int sd = g.ep.summand_dtype;
     const bool sum8 = sd == ITEXB_DT_QUINT8 || sd == ITEXB_DT_UINT8 || sd == ITEXB_DT_QINT8 || sd == ITEXB_DT_INT8;
     if (g.ep.summand == nullptr) g.ep_mode = kEpPlain;
@@ -1379,9 +1348,6 @@ int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype,
   ITEXB_REQUIRE(ep.scale_count == 0 || ep.scale != nullptr, ITEXB_INVALID_ARGUMENT, "%s: scale is NULL", who);
   ITEXB_REQUIRE((ep.alpha_a == nullptr) == (ep.alpha_b == nullptr), ITEXB_INVALID_ARGUMENT,
                 "%s: alpha_a and alpha_b must be given together", who);
-  ITEXB_REQUIRE(ep.out_minmax == nullptr ||
-                    (!ep.raw_acc && (out_dtype == ITEXB_DT_FLOAT || out_dtype == ITEXB_DT_BFLOAT16 || out_dtype == ITEXB_DT_HALF)),
-                ITEXB_INVALID_ARGUMENT, "%s: out_minmax needs a float, bfloat16 or half output", who);
   switch (out_dtype) {
     case ITEXB_DT_FLOAT: case ITEXB_DT_BFLOAT16: case ITEXB_DT_HALF: break;
     case ITEXB_DT_QINT32: case ITEXB_DT_INT32: case ITEXB_DT_QUINT8: case ITEXB_DT_UINT8: case ITEXB_DT_QINT8: case ITEXB_DT_INT8:

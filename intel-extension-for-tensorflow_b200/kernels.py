@@ -79,9 +79,9 @@ def pack_weights_kn(b_kn, k_pad=None):
 
 def make_epilogue(scale=None, bias=None, relu=False, raw_acc=False, summand=None, sum_scale=1.0,
                   alpha_a=None, alpha_b=None, out_scale=None, amax=None, summand_dtype=None,
-                  activation=0, act_alpha=0.0, act_beta=0.0, post_scale=0.0, out_minmax=None):
+                  activation=0, act_alpha=0.0, act_beta=0.0, post_scale=0.0):
     ep = L.Epilogue()
-    keep = [scale, bias, summand, alpha_a, alpha_b, out_scale, amax, out_minmax]
+    keep = [scale, bias, summand, alpha_a, alpha_b, out_scale, amax]
     if scale is not None:
         ep.scale = scale.data_ptr()
         ep.scale_count = scale.numel()
@@ -95,7 +95,7 @@ def make_epilogue(scale=None, bias=None, relu=False, raw_acc=False, summand=None
     ep.relu = int(bool(relu))
     ep.raw_acc = int(bool(raw_acc))
     ep.activation, ep.act_alpha, ep.act_beta, ep.post_scale = int(activation), float(act_alpha), float(act_beta), float(post_scale)
-    for name, t in (("alpha_a", alpha_a), ("alpha_b", alpha_b), ("out_scale", out_scale), ("amax", amax), ("out_minmax", out_minmax)):
+    for name, t in (("alpha_a", alpha_a), ("alpha_b", alpha_b), ("out_scale", out_scale), ("amax", amax)):
         if t is not None:
             setattr(ep, name, t.data_ptr())
     ep._keep = keep
@@ -156,13 +156,6 @@ def fp8_amax_and_scale_update(amax_history, scale, scale_inv, fp8_max=448.0, mar
     L.check(L.load().itexb_fp8_amax_and_scale_update(_ptr(amax_history), _ptr(scale), _ptr(scale_inv), h, n,
                                                      C.c_float(fp8_max), C.c_float(margin),
                                                      {"max": 0, "most_recent": 1}[algo], stream_ptr()))
-
-
-def minmax_init(mm):
-    """mm[0] = +inf, mm[1] = -inf: the state itexb_minmax and a GEMM's out_minmax fold values into."""
-    _require_cuda(mm)
-    L.check(L.load().itexb_minmax_init(_ptr(mm), stream_ptr()))
-    return mm
 
 
 def minmax(x, out=None):

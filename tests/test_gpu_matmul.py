@@ -224,31 +224,6 @@ def test_epilogue_bound_shape(n, k, summand):
     assert int(status.item()) == 0
 
 
-@pytest.mark.parametrize("tout", ["float", "bfloat16", "half"])
-def test_epilogue_reports_min_max_of_what_it_wrote(tout):
-    """out_minmax: the GEMM folds the minimum and maximum of the values it stores (after rounding to the output type)
-    into a device float[2]; ragged tile edges, with and without an activation, accumulating over two launches."""
-    itex, K, ops = modules()
-    L = itex._lib
-    dt = {"float": L.DT_FLOAT, "bfloat16": L.DT_BFLOAT16, "half": L.DT_HALF}[tout]
-    g = torch.Generator(device="cuda").manual_seed(9)
-    outs = []
-    mm = K.minmax_init(torch.empty(2, dtype=torch.float32, device="cuda"))
-    for (m, n, k), act in (((300, 200, 96), L.ACT_GELU_TANH), ((130, 72, 256), L.ACT_NONE)):
-        a = torch.randint(-127, 128, (m, k), device="cuda", generator=g).to(torch.int8)
-        b = torch.randint(-127, 128, (n, k), device="cuda", generator=g).to(torch.int8)
-        scale = (torch.rand(n, device="cuda", generator=g) * 1e-4 + 1e-5).float()
-        bias = torch.randn(n, device="cuda", generator=g).float()
-        ep = K.make_epilogue(scale=scale, bias=bias, activation=act, out_minmax=mm)
-        outs.append(K.gemm(a, b, dt, ep=ep).float().flatten())
-        plain = K.gemm(a, b, dt, ep=K.make_epilogue(scale=scale, bias=bias, activation=act)).float().flatten()
-        assert torch.equal(outs[-1], plain)   # asking for the range does not change the output
-    allv = torch.cat(outs)
-    assert mm.tolist() == [float(allv.min()), float(allv.max())]
-    with pytest.raises(itex.ItexError, match="out_minmax needs"):
-        K.gemm(a, b, L.DT_QINT8, ep=K.make_epilogue(scale=scale, bias=bias, out_minmax=mm))
-
-
 def test_kernel_level_argument_errors():
     itex, K, ops = modules()
     L = itex._lib
