@@ -12,6 +12,13 @@ Multi-GPU (launched by torch.distributed.run): the batch (rows of the activation
 is sharded, weights are replicated, there is no data-path collective; per-GPU work is
 fixed, so scaling is weak and `value` is the sum over ranks.
 
+The default run also measures the other pieces of the path and puts them under "secondary" in
+the same line, each with its own value, ms_per_step, roofline, e2e and (one GPU) cpu_baseline:
+quantize_f32_u8 / dequantize_u8_f32 at the reference benchmark's sizes (102 760 448 and 3 211 264
+elements), conv_cfg2 (the fused int8 3x3 convolution at [32,56,56,64]), resnet50_int8 (images/s,
+batch 128 per GPU, weak scaling) and fp8_llama_linears (tokens/s, column-parallel with an all-gather,
+strong scaling).  --no-secondary skips them; --workload NAME runs one of them as the headline.
+
 --impl reference times the CPU path the reference would run (oneDNN int8 inner product,
 reached through torch.ops.onednn, plus the oracle's quantize) on the host cores, on a
 bounded row sample of the same workload.
@@ -167,14 +174,15 @@ def synth_weights(n, k, seed):
     return q, -amax, amax, bias
 
 
-def cpu_reference_step(x_rows, qw_kn, wmin, wmax, bias, state):
-    """One CPU step on a row sample: quantize + int8 matmul + bias + dequantize.
+def cpu_reference_step(x_rows, qw_kn, wmin, wmax, bias, state, x_range=None):
+    """One CPU step on a row sample: quantize + int8 matmul + bias + dequantize.  x_range: the activation range
+    the graph froze (that of the whole batch); by default the sample's own.
     Returns (fp32 output, label of what ran)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import itex_oracle as o
     import oracle_c as oc
     import torch
-    mn, mx = float(x_rows.min()), float(x_rows.max())
+    mn, mx = (float(x_rows.min()), float(x_rows.max())) if x_range is None else x_range
     amin, amax = o.adjust_input_min_max(mn, mx)
     scale, absr = o.scaled_scale(amin, amax, "quint8", True)
     qa = oc.quantize_scaled(x_rows, scale, False)
@@ -309,7 +317,10 @@ def run_resnet50(args, rank, world, local, dev, K):
                     "checksum": float(out_host.double().sum())},
             "gpu_launches": int(launches_per_step * args.steps), "clocks": sampler.summary(),
         }
-        print(json.dumps(line), flush=True)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_resnet50(net, calib, args)
+        return line
+    return None
 
 
 def run_bert(args, rank, world, local, dev, K):
@@ -408,7 +419,8 @@ def run_bert(args, rank, world, local, dev, K):
                     "checksum": float(out_host.double().sum())},
             "gpu_launches": int(launches_per_step * args.steps), "clocks": sampler.summary(),
         }
-        print(json.dumps(line), flush=True)
+        return line
+    return None
 
 
 FP8_LINEARS = ((4096, 4096), (4096, 14336), (14336, 4096))  # (K, N) of the Llama-3-8B-shaped linears, M = 4096 tokens
@@ -541,64 +553,386 @@ def run_fp8_linears(args, rank, world, local, dev, K):
                     "h2d_bytes_per_step": sum(m * k * 2 for k, _ in FP8_LINEARS), "d2h_bytes_per_step": sum(m * n * 2 for _, n in FP8_LINEARS)},
             "gpu_launches": int(launches), "clocks": sampler.summary(),
         }
-        print(json.dumps(line), flush=True)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_fp8_linears(layers, m)
+        return line
+    return None
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="int8_gemm_8192", choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears", "bert_large_int8"])
-    ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
-    ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
-                    help="keep warming up at least this long so the clock sampler sees the load (0 for profiler runs)")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    m, n, k = WORKLOADS.get(args.workload, WORKLOADS["int8_gemm_8192"])
-    if args.impl == "reference":
-        run_reference(args, m, n, k)
-        return
+def l2_flusher(dev):
+    """Returns a function that overwrites a buffer larger than L2 (126 MB) on the current stream."""
+    import torch
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    return lambda: buf.fill_(1)
 
+
+def timed_us(fn, reps, flush=None):
+    """Mean device time of fn() in microseconds over `reps` launches.  The launches (each preceded by flush(), if given,
+    outside its timing events) are recorded in one CUDA graph with a pair of timing events around each, so that what
+    is measured is the kernel on the device and not the host's launch path (a few microseconds of Python and driver per
+    call, more than the kernels of the small cases take).  Falls back to eager launches where events cannot be
+    recorded into a graph."""
+    import torch
+    dev = torch.cuda.current_device()
+    try:
+        ev = [(torch.cuda.Event(enable_timing=True, external=True), torch.cuda.Event(enable_timing=True, external=True)) for _ in range(reps)]
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for a, b in ev:
+                if flush is not None:
+                    flush()
+                a.record()
+                fn()
+                b.record()
+        graph.replay()
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        return 1e3 * sum(a.elapsed_time(b) for a, b in ev) / reps
+    except Exception as exc:                # noqa: BLE001
+        print("bench.py: graph timing unavailable (%s); timing eager launches" % type(exc).__name__, file=sys.stderr)
+        torch.cuda.synchronize()
+    pairs = []
+    for _ in range(reps):
+        if flush is not None:
+            flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    return 1e3 * sum(a.elapsed_time(b) for a, b in pairs) / reps
+
+
+def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
+    """_ITEXQuantizeV2 (fp32 -> quint8, SCALED, HALF_TO_EVEN) or _ITEXDequantize (quint8 -> fp32, SCALED) over `count`
+    elements through the op layer: achieved GB/s of the 5 algorithmic bytes per element.  The sizes are the reference
+    benchmark's (test/benchmark/test_quantize.py:55-56).  The smaller one fits in L2, so L2 is flushed before every timed
+    launch; the larger one is 4x L2 and runs back to back."""
+    import torch
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(shard_seed(1240, rank))
+    shape = (count // 1024, 1024)
+    if which == "quantize":
+        x = torch.rand(shape, device=dev, generator=gen) * 2 - 1
+        op = ops.Op("_ITEXQuantizeV2", T="quint8", mode="SCALED", round_mode="HALF_TO_EVEN", narrow_range=False, axis=-1,
+                    ensure_minimum_range=0.01, dtype="float")
+        call = lambda t: op(t, -1.0, 1.0)[0]
+        in_b, out_b = 4, 1
+    else:
+        x = torch.randint(0, 256, shape, dtype=torch.uint8, device=dev, generator=gen)
+        op = ops.Op("_ITEXDequantize", T="quint8", mode="SCALED", narrow_range=False, axis=-1, dtype="float")
+        call = lambda t: op(t, 0.0, 6.0)
+        in_b, out_b = 1, 4
+    small = count * 5 < (252 << 20)
+    flush = l2_flusher(dev) if small else None
+    for _ in range(max(args.warmup, 3)):
+        y = call(x)
+    torch.cuda.synchronize()
+    n0 = K.launch_count()
+    reps = 20 if small else 10
+    us = timed_us(lambda: call(x), reps, flush)
+    launches = K.launch_count() - n0
+    us = max_over_ranks(us, world, dev)
+    # end to end: pinned host tensor in, result back to pinned host memory, every step
+    xh = torch.empty(shape, dtype=x.dtype, pin_memory=True)
+    xh.copy_(x.cpu())
+    yh = torch.empty(shape, dtype=y.dtype, pin_memory=True)
+    xd = torch.empty_like(x)
+
+    def e2e_step():
+        xd.copy_(xh, non_blocking=True)
+        yh.copy_(call(xd), non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    e2e_reps = 3
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(e2e_reps):
+        e2e_step()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_us = max_over_ranks(1e3 * t0.elapsed_time(t1) / e2e_reps, world, dev)
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    gbs = count * 5 / (us * 1e-6) / 1e9
+    line = {"metric": "%s_gb_per_s" % which, "value": gbs * world, "unit": "GB/s", "ms_per_step": us * 1e-3, "n_gpus": world, "scaling": "weak",
+            "dtype": "f32->u8" if which == "quantize" else "u8->f32",
+            "config": {"workload": "%s_%d" % ("quantize_f32_u8" if which == "quantize" else "dequantize_u8_f32", count), "elements_per_gpu": count,
+                       "op": "_ITEXQuantizeV2" if which == "quantize" else "_ITEXDequantize",
+                       "l2": "L2 flushed before every timed launch" if small else "input + output larger than L2"},
+            "roofline": {"bound": "hbm", "kernel": "QuantizeKernel" if which == "quantize" else "DequantizeKernel", "achieved": gbs,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "algorithmic_bytes": count * 5, "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peaks["source"]},
+            "e2e": {"value": count * 5 * world / (e2e_us * 1e-6) / 1e9, "unit": "GB/s", "ms_per_step": e2e_us * 1e-3,
+                    "h2d_bytes_per_step": count * in_b * world, "d2h_bytes_per_step": count * out_b * world},
+            "gpu_launches": int(launches)}
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_pointwise(which, x[: min(x.shape[0], 3136)].cpu().numpy())
+    return line
+
+
+def cpu_pointwise(which, sample):
+    """The C/OpenMP oracle's quantize / dequantize on a 3 211 264-element sample, all host threads."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_c as oc
+    fn = (lambda: oc.quantize_scaled(sample, np.float32(255.0), False)) if which == "quantize" else (lambda: oc.dequantize(sample, np.float32(6.0 / 255.0)))
+    fn()
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or (time.perf_counter() - t0 < 2.0 and reps < 200):
+        fn()
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": sample.size * 5 / dt / 1e9, "unit": "GB/s", "cores": oc.num_threads(), "kind": "port",
+            "sample": "%d elements, C/OpenMP oracle (oracle/itex_oracle_c.c), %d reps" % (sample.size, reps)}
+
+
+CONV_CFG2 = dict(n=32, h=56, w=56, c=64, k=3, co=64)
+
+
+def run_conv_cfg2(args, rank, world, local, dev, K, ops):
+    """_ITEXQuantizedConv2DWithBiasAndReluAndRequantize at [32,56,56,64] x 3x3x64x64, stride 1, SAME, u8 -> u8: the
+    fused int8 convolution of the reference's conv configuration.  Input + output + filter (12.9 MB) fit in L2, so L2 is
+    flushed before every timed launch.  Both roofline fractions are given: tensor (2 x measured bf16) and HBM."""
+    import torch
+    c = CONV_CFG2
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(shard_seed(1236, rank))
+    x = torch.randint(0, 256, (c["n"], c["h"], c["w"], c["c"]), dtype=torch.uint8, device=dev, generator=gen)
+    rng = np.random.default_rng(1236)
+    f = (rng.standard_normal((c["k"], c["k"], c["c"], c["co"])) * 0.05).astype(np.float32)
+    amax = np.abs(f).reshape(-1, c["co"]).max(axis=0).astype(np.float32)
+    qf_h = np.clip(np.rint(f * (127.0 / amax)), -127, 127).astype(np.int8)
+    bias_h = (rng.standard_normal(c["co"]) * 0.1).astype(np.float32)
+    qf, bias = torch.from_numpy(qf_h).to(dev), torch.from_numpy(bias_h).to(dev)
+    rng_in, rng_out = (0.0, 12.75), (0.0, 20.0)
+    op = ops.Op("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", Tinput="quint8", Tfilter="qint8", Tbias="float", out_type="quint8",
+                strides=[1, 1, 1, 1], padding="SAME", dilations=[1, 1, 1, 1], data_format="NHWC", is_filter_const=True, is_bias_const=True)
+    call = lambda t: op(t, qf, bias, rng_in[0], rng_in[1], -amax, amax, rng_out[0], rng_out[1])[0]
+    flush = l2_flusher(dev)
+    for _ in range(max(args.warmup, 3)):
+        y = call(x)
+    torch.cuda.synchronize()
+    n0 = K.launch_count()
+    us = timed_us(lambda: call(x), 20, flush)
+    launches = K.launch_count() - n0
+    us = max_over_ranks(us, world, dev)
+    xh = torch.empty(tuple(x.shape), dtype=torch.uint8, pin_memory=True)
+    xh.copy_(x.cpu())
+    yh = torch.empty(tuple(y.shape), dtype=torch.uint8, pin_memory=True)
+    xd = torch.empty_like(x)
+
+    def e2e_step():
+        xd.copy_(xh, non_blocking=True)
+        yh.copy_(call(xd), non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(10):
+        e2e_step()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_us = max_over_ranks(1e3 * t0.elapsed_time(t1) / 10, world, dev)
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    ops_n = 2.0 * c["n"] * c["h"] * c["w"] * c["co"] * c["k"] * c["k"] * c["c"]
+    bytes_n = 2 * c["n"] * c["h"] * c["w"] * c["c"] + c["k"] * c["k"] * c["c"] * c["co"] + 8 * c["co"]
+    tops = ops_n / (us * 1e-6) / 1e12
+    gbs = bytes_n / (us * 1e-6) / 1e9
+    line = {"metric": "conv_cfg2_tops", "value": tops * world, "unit": "TOPS", "ms_per_step": us * 1e-3, "n_gpus": world, "scaling": "weak",
+            "dtype": "u8xs8->s32",
+            "config": {"workload": "conv_cfg2", "input": [c["n"], c["h"], c["w"], c["c"]], "filter": [c["k"], c["k"], c["c"], c["co"]],
+                       "op": "_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", "stride": 1, "padding": "SAME", "output": "quint8",
+                       "l2": "L2 flushed before every timed launch"},
+            "roofline": {"bound": "hbm", "kernel": "GemmKernel<64,int8,im2col> (tcgen05.mma kind::i8, TMA im2col A operand)", "achieved": gbs,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": bytes_n,
+                         "tensor": {"achieved": tops, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tops / (2.0 * peaks["bf16_tflops"])},
+                         "note": "574 op/B: the HBM floor (%.2f us) and the tensor floor (%.2f us) of this layer are within 15 %% of each other"
+                                 % (bytes_n / peaks["hbm_gbs"] / 1e3, ops_n / (2.0 * peaks["bf16_tflops"]) / 1e6),
+                         "peak_source": "hbm_gbs and 2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s)" % peaks["source"]},
+            "e2e": {"value": ops_n * world / (e2e_us * 1e-6) / 1e12, "unit": "TOPS", "ms_per_step": e2e_us * 1e-3,
+                    "h2d_bytes_per_step": int(x.numel()) * world, "d2h_bytes_per_step": int(y.numel()) * world},
+            "gpu_launches": int(launches)}
+    if world == 1 and not args.no_cpu_baseline:
+        import torch
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import itex_oracle as o
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        node = CpuConv(qf_h, bias_h, rng_in, (-amax, amax), rng_out, 1, True, "quint8", o)
+        xc = x.cpu().permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+        ref = node(xc)
+        same = bool((ref.permute(0, 2, 3, 1) == y.cpu()).all())
+        if not same:
+            raise SystemExit("bench.py: conv_cfg2: the GPU output differs from the oneDNN CPU result on the same input")
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t0 < 3.0 and reps < 100):
+            node(xc)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {"value": ops_n / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+                                "sample": "the whole layer, oneDNN int8 convolution via torch.ops.onednn.qconv2d_pointwise, %d host threads, %d reps" % (cores, reps)}
+        line["parity_checked"] = "whole output bit-identical to the CPU result"
+    return line
+
+
+class CpuConv:
+    """One fused quantized convolution on the CPU through real oneDNN (torch.ops.onednn.qconv2d_pointwise), driven the way
+    the reference drives dnnl::convolution_forward: combined per-channel scale on the weights argument, pre-scaled bias,
+    ReLU and the u8 summand as post-ops (quantized_conv_ops.h:329-446).  NCHW channels_last tensors in and out."""
+
+    def __init__(self, qf_hwio, bias, rng_in, rng_filter, rng_out, stride, relu, out_type, o, in_type="quint8"):
+        import torch
+        self.torch = torch
+        kh = qf_hwio.shape[0]
+        co = qf_hwio.shape[3]
+        self.stride, self.relu, self.out_type, self.kh = stride, relu, out_type, kh
+        self.scales = o.conv_output_scale(rng_in[0], rng_in[1], rng_filter[0], rng_filter[1], in_type, out_type, rng_out[0], rng_out[1])
+        self.bias = torch.from_numpy(o.conv_scaled_bias(bias, rng_in[0], rng_in[1], rng_filter[0], rng_filter[1], in_type, out_type, self.scales))
+        self.ws = torch.from_numpy(self.scales.copy())
+        self.wz = torch.zeros(co, dtype=torch.int64)
+        qw = torch.from_numpy(np.ascontiguousarray(qf_hwio.transpose(3, 2, 0, 1)))
+        self.rng_out = rng_out
+        self.o = o
+        self._packed = {}
+        self.qw = qw
+
+    def _pads(self, h, w):
+        oh, pt, pb = self.o.same_padding(h, self.kh, self.stride)
+        ow, pl, pr = self.o.same_padding(w, self.kh, self.stride)
+        return pt, pb, pl, pr
+
+    def __call__(self, x, summand=None, sum_range=None):
+        torch = self.torch
+        pt, pb, pl, pr = self._pads(x.shape[2], x.shape[3])
+        if pt != pb or pl != pr:      # the binding takes symmetric padding only
+            x = torch.nn.functional.pad(x, (pl, pr, pt, pb)).contiguous(memory_format=torch.channels_last)
+            pad = [0, 0]
+        else:
+            pad = [pt, pl]
+        key = tuple(pad)
+        if key not in self._packed:
+            self._packed[key] = torch.ops.onednn.qconv_prepack(self.qw, self.ws, 1.0, 0, [self.stride] * 2, pad, [1, 1], 1, None)
+        pw = self._packed[key]
+        odt = torch.uint8 if self.out_type == "quint8" else torch.int8
+        st = [self.stride] * 2
+        if summand is None:
+            return torch.ops.onednn.qconv2d_pointwise(x, 1.0, 0, pw, self.ws, self.wz, self.bias, st, pad, [1, 1], 1, 1.0, 0, odt,
+                                                      "relu" if self.relu else "none", [], "")
+        so = np.float32(max(abs(np.float32(self.rng_out[0])), abs(np.float32(self.rng_out[1]))))
+        ss = np.float32(max(abs(np.float32(sum_range[0])), abs(np.float32(sum_range[1]))))
+        if summand.dtype == torch.uint8:
+            return torch.ops.onednn.qconv2d_pointwise.binary(x, 1.0, 0, pw, self.ws, self.wz, summand.clone(), self.bias, st, pad, [1, 1], 1, 1.0, 0,
+                                                             odt, float(np.float32(ss / so)), 0, "sum", 1.0, "relu", [], "")
+        # signed summand into an unsigned output: this binding's sum post-op wants one data type, so this node (4 of 53)
+        # takes the convolution in fp32 and does the post-op here: one fused multiply-add like the post-op itself
+        # (formed in float64, where the product of a float and a byte is exact, and rounded once)
+        sum_scale = np.float32(np.float32(np.float32(255.0) * ss) / np.float32(so * np.float32(127.0)))
+        v = torch.ops.onednn.qconv2d_pointwise(x, 1.0, 0, pw, self.ws, self.wz, self.bias, st, pad, [1, 1], 1, 1.0, 0, torch.float32, "none", [], "")
+        v = torch.relu((v.double() + summand.double() * float(sum_scale)).float())
+        return torch.clamp(torch.round(v), 0, 255).to(torch.uint8)
+
+
+def cpu_resnet50(net, calib, args):
+    """INT8 ResNet-50 forward on the host cores through real oneDNN (qconv2d_pointwise per node, pooling and the final
+    int8 matmul in torch), batch 16, with the GPU graph's weights and frozen ranges; its logits must equal the GPU's."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import itex_oracle as o
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x_dev = calib[:16]
+    gpu_logits = net.forward(x_dev).cpu()
+
+    # ranges of each node's input are only known along the graph: build the CPU nodes while walking it once
+    cpu_nodes = {}
+
+    def run(node, q, rng, sm=None, srng=None):
+        key = node.name
+        if key not in cpu_nodes:
+            cpu_nodes[key] = CpuConv(node.filter.cpu().numpy(), node.bias.cpu().numpy(), rng, (node.min_filter, node.max_filter),
+                                     (node.min_out, node.max_out), node.stride, node.relu, node.out_type, o,
+                                     in_type="quint8" if q.dtype == torch.uint8 else "qint8")
+        return cpu_nodes[key](q, sm, srng), (node.min_out, node.max_out)
+
+    fc_w = net.fc_w.cpu().numpy()
+    fc_b = net.fc_b.cpu().numpy()
+
+    def forward(xc):
+        q, r = run(net.stem, xc, net.input_range)
+        # SAME 3x3/2 on 112 rows: one pixel of padding after (zeros never win against uint8 values); torch's CPU max pooling
+        # has no uint8 kernel for this size, so the values pass through fp32 (exact)
+        q = torch.nn.functional.max_pool2d(torch.nn.functional.pad(q, (0, 1, 0, 1)).float(), 3, 2).to(torch.uint8)
+        q = q.contiguous(memory_format=torch.channels_last)
+        for proj, c1, c2, c3 in net.blocks:
+            if proj is not None:
+                s, sr = run(proj, q, r)
+            else:
+                s, sr = q, r
+            a, ar = run(c1, q, r)
+            b, br = run(c2, a, ar)
+            q, r = run(c3, b, br, s, sr)
+        # _ITEXQuantizedAvgPool: integer mean, rounded half away from zero on the fp32 quotient like the op
+        hw = q.shape[2] * q.shape[3]
+        pooled = o.quantized_pool2d(q.permute(0, 2, 3, 1).numpy(), (1, q.shape[2], q.shape[3], 1), (1, q.shape[2], q.shape[3], 1), "VALID", avg=True)
+        feat = pooled.reshape(pooled.shape[0], -1)
+        out, _, _ = o.quantized_matmul_with_bias(feat, fc_w, fc_b, r[0], r[1], net.fc_range[0], net.fc_range[1], 0.0, 0.0, toutput="float",
+                                                 input_quant_mode="SCALED", scaled_bias_mode="intended")
+        return torch.from_numpy(out)
+
+    xc = x_dev.cpu().permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+    logits = forward(xc)
+    same = bool((logits == gpu_logits).all())
+    diff = float((logits - gpu_logits).abs().max())
+    if not same and diff > 0.05 * float(gpu_logits.abs().max()):
+        raise SystemExit("bench.py: resnet50_int8: GPU logits differ from the oneDNN CPU forward on the same 16 images by %g" % diff)
+    reps, t0 = 0, time.perf_counter()
+    while reps < 2 or (time.perf_counter() - t0 < 8.0 and reps < 50):
+        forward(xc)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 16 / dt, "unit": "images/s", "cores": cores, "kind": "port",
+            "parity": "logits of the 16 images bit-identical to the GPU graph's" if same else
+                      "logits differ from the GPU graph's by at most %g (%.2f %% of the largest logit)" % (diff, 100 * diff / float(gpu_logits.abs().max())),
+            "sample": "batch 16 forward, 53 oneDNN int8 convolutions via torch.ops.onednn.qconv2d_pointwise (+ pooling and the "
+                      "final matmul in torch / NumPy), %d host threads, %d reps" % (cores, reps)}
+
+
+def cpu_fp8_linears(layers, m):
+    """The reference registers Fp8Matmul for its GPU only (fp8_matmul_op.cc:100-110), so there is no reference CPU
+    kernel to time: the baseline is the NumPy restatement (dequantize both operands, float64 matmul) on a 64-token sample
+    of the three linears."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import itex_oracle as o
+    rows = 64
+    work = []
+    for layer, a, gathered, k, n in layers:
+        amax = np.zeros(3, np.float32)
+        scale = layer.meta.scale.cpu().numpy()
+        qa = o.fp8_quantize(a[:rows].float().cpu().numpy(), amax, scale, 0)
+        qw = o.fp8_quantize(layer.kernel.float().cpu().numpy(), amax, scale, 1)
+        work.append((qa, qw, (1.0 / scale).astype(np.float32), k, n))
+    t0 = time.perf_counter()
+    for qa, qw, sinv, k, n in work:
+        o.fp8_matmul(qa, qw, None, None, sinv, sinv, None, None, transpose_b=True, sum_dtype="bfloat16", out_dtype="bfloat16")
+    dt = time.perf_counter() - t0
+    return {"value": rows / dt, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": "%d of %d tokens through the three linears, NumPy restatement (oracle/itex_oracle.py fp8_matmul), 1 rep" % (rows, m)}
+
+
+def run_gemm(args, rank, world, local, dev, K, ops, m, n, k):
+    """The headline: _ITEXQuantizeV2 + _ITEXQuantizedMatMulWithBiasAndDequantize at [m,k] x [k,n]."""
     import torch
     import torch.distributed as dist
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
-    torch.cuda.set_device(local)
-    if world > 1:
-        if "ITEXB_NCCL_DEBUG" in os.environ:
-            os.environ["NCCL_DEBUG"] = os.environ["ITEXB_NCCL_DEBUG"]
-        else:
-            os.environ["NCCL_DEBUG_FILE"] = os.devnull              # keep stdout to the one JSON line
-        import datetime
-        # a short timeout turns any mismatch between ranks into a quick error instead of a long hang
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
-    itex = load_package()
-    ops = importlib.import_module("itex_b200.ops")
-    K = importlib.import_module("itex_b200.kernels")
-    dev = torch.device("cuda", local)
-    if args.workload == "fp8_llama_linears":
-        run_fp8_linears(args, rank, world, local, dev, K)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.workload == "bert_large_int8":
-        run_bert(args, rank, world, local, dev, K)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.workload == "resnet50_int8":
-        run_resnet50(args, rank, world, local, dev, K)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
     # ---- synthetic inputs, resident in HBM (seed depends on the rank: each GPU has its own batch shard)
     gen = torch.Generator(device=dev)
     gen.manual_seed(shard_seed(1234, rank))
@@ -727,43 +1061,133 @@ def main():
             del a8, b8
         except Exception:  # noqa: BLE001 - the figure is informative only
             lib_tops = None
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    gemm_tops = 2.0 * m * n * k / (gemm_ms * 1e-3) / 1e12
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": "int8_quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "s8xu8->s32", "data": "synthetic",
+        "config": {"workload": args.workload, "m_per_gpu": m, "n": n, "k": k, "ops": ["_ITEXQuantizeV2", "_ITEXQuantizedMatMulWithBiasAndDequantize"],
+                   "output": "float32", "l2": "inputs larger than L2 (%.0f MB touched per step)" % ((m * k * 5 + n * k + m * n * 4) / 1e6),
+                   "launch": "K steps in one CUDA graph" if graph is not None else "eager",
+                   "parallelism": "batch-sharded x%d, no collective" % world},
+        "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,int8> (tcgen05.mma kind::i8)", "achieved": gemm_tops,
+                     "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
+                     "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s); int8 MMA rate is twice bf16" % peaks["source"],
+                     "gemm_ms": gemm_ms, "traffic": GEMM_DRAM_TRAFFIC.get(args.workload),
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in profiles/int8_gemm_quantize_matmul.md",
+                     "algorithmic_bytes": m * k + n * k + m * n * 4,
+                     "library_int_mm_tops": lib_tops, "frac_of_library": None if not lib_tops else gemm_tops / lib_tops},
+        "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k * 4 * world,
+                "d2h_bytes_per_step": m * n * 4 * world, "checksum": checksum},
+        "gpu_launches": int(launches), "clocks": sampler.summary(),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        m_s = min(m, 512)
+        xs = x[:m_s].cpu().numpy()
+        state = {}
+        # the CPU sample also checks the GPU result of the same rows: quantized with the full batch's range, as the GPU step was
+        ref, label = cpu_reference_step(xs, qw, wmin, wmax, bias_h, state, (xmin, xmax))
+        got = step(x)[0][:m_s].cpu().numpy()
+        bad = int((got != ref).sum())
+        if bad:
+            raise SystemExit("bench.py: %d of %d outputs of the first %d rows differ from the CPU result (%s)" % (bad, ref.size, m_s, label))
+        line["parity_rows_checked"] = m_s
+        reps, t_cpu = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t_cpu < 5.0 and reps < 50):
+            cpu_reference_step(xs, qw, wmin, wmax, bias_h, state, (xmin, xmax))
+            reps += 1
+        dt = (time.perf_counter() - t_cpu) / reps
+        line["cpu_baseline"] = {"value": 2.0 * m_s * n * k / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+                                "sample": "%d of %d rows per step (%s), %d host threads, %d reps" % (m_s, m, label, cores, reps)}
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="int8_gemm_8192",
+                    choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears", "bert_large_int8", "conv_cfg2", "quantize", "dequantize"])
+    ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
+    ap.add_argument("--elements", type=int, default=102760448, help="elements per GPU for --workload quantize / dequantize")
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler runs, quick checks)")
+    ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
+                    help="keep warming up at least this long so the clock sampler sees the load (0 for profiler runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    m, n, k = WORKLOADS.get(args.workload, WORKLOADS["int8_gemm_8192"])
+    if args.impl == "reference":
+        run_reference(args, m, n, k)
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        # NCCL's own log (communicator and ring/tree set-up, "nranks N") goes to stderr; stdout stays the one JSON line
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+        import datetime
+        # a short timeout turns any mismatch between ranks into a quick error instead of a long hang
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
+    load_package()
+    ops = importlib.import_module("itex_b200.ops")
+    K = importlib.import_module("itex_b200.kernels")
+    dev = torch.device("cuda", local)
+    common = (args, rank, world, local, dev, K)
+
+    def release():
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    if args.workload == "fp8_llama_linears":
+        line = run_fp8_linears(*common)
+    elif args.workload == "bert_large_int8":
+        line = run_bert(*common)
+    elif args.workload == "resnet50_int8":
+        line = run_resnet50(*common)
+    elif args.workload == "conv_cfg2":
+        line = run_conv_cfg2(*common, ops)
+    elif args.workload in ("quantize", "dequantize"):
+        line = run_pointwise(*common, ops, args.workload, args.elements)
+    else:
+        line = run_gemm(*common, ops, m, n, k)
+        if args.workload == "int8_gemm_8192" and not args.no_secondary:
+            secondary = {}
+            for name, fn in (
+                    ("quantize_f32_u8_102760448", lambda: run_pointwise(*common, ops, "quantize", 102760448)),
+                    ("quantize_f32_u8_3211264", lambda: run_pointwise(*common, ops, "quantize", 3211264)),
+                    ("dequantize_u8_f32_102760448", lambda: run_pointwise(*common, ops, "dequantize", 102760448)),
+                    ("dequantize_u8_f32_3211264", lambda: run_pointwise(*common, ops, "dequantize", 3211264)),
+                    ("conv_cfg2", lambda: run_conv_cfg2(*common, ops)),
+                    ("resnet50_int8", lambda: run_resnet50(*common)),
+                    ("fp8_llama_linears", lambda: run_fp8_linears(*common))):
+                release()
+                t0 = time.perf_counter()
+                sub = fn()
+                if rank == 0:
+                    sub["bench_seconds"] = round(time.perf_counter() - t0, 1)
+                    secondary[name] = sub
+            if rank == 0:
+                line["secondary"] = secondary
     if rank == 0:
-        peaks = measured_peaks()
-        gemm_tops = 2.0 * m * n * k / (gemm_ms * 1e-3) / 1e12
-        int8_peak = 2.0 * peaks["bf16_tflops"]
-        line = {
-            "metric": "int8_quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "s8xu8->s32", "data": "synthetic",
-            "config": {"workload": args.workload, "m_per_gpu": m, "n": n, "k": k, "ops": ["_ITEXQuantizeV2", "_ITEXQuantizedMatMulWithBiasAndDequantize"],
-                       "output": "float32", "l2": "inputs larger than L2 (%.0f MB touched per step)" % ((m * k * 5 + n * k + m * n * 4) / 1e6),
-                       "launch": "K steps in one CUDA graph" if graph is not None else "eager",
-                       "parallelism": "batch-sharded x%d, no collective" % world},
-            "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,int8> (tcgen05.mma kind::i8)", "achieved": gemm_tops,
-                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
-                         "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s); int8 MMA rate is twice bf16" % peaks["source"],
-                         "gemm_ms": gemm_ms, "traffic": GEMM_DRAM_TRAFFIC.get(args.workload),
-                         "algorithmic_bytes": m * k + n * k + m * n * 4,
-                         "library_int_mm_tops": lib_tops, "frac_of_library": None if not lib_tops else gemm_tops / lib_tops},
-            "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k * 4 * world,
-                    "d2h_bytes_per_step": m * n * 4 * world, "checksum": checksum},
-            "gpu_launches": int(launches), "clocks": sampler.summary(),
-        }
-        if world == 1 and not args.no_cpu_baseline:
-            cores = os.cpu_count() or 1
-            torch.set_num_threads(cores)
-            m_s = min(m, 512)
-            xs = x[:m_s].cpu().numpy()
-            state = {}
-            ref, label = cpu_reference_step(xs, qw, wmin, wmax, bias_h, state)
-            reps, t_cpu = 0, time.perf_counter()
-            while reps < 3 or (time.perf_counter() - t_cpu < 5.0 and reps < 50):
-                cpu_reference_step(xs, qw, wmin, wmax, bias_h, state)
-                reps += 1
-            dt = (time.perf_counter() - t_cpu) / reps
-            # the CPU sample also checks the GPU result of the same rows (range = that of the full batch)
-            line["cpu_baseline"] = {"value": 2.0 * m_s * n * k / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
-                                    "sample": "%d of %d rows per step (%s), %d host threads, %d reps" % (m_s, m, label, cores, reps)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -90,7 +90,13 @@ ITEXB_API int itexb_rt_device_count(int* count);
 ITEXB_API int itexb_rt_set_device(int ordinal);
 ITEXB_API int itexb_rt_device_memory_usage(int ordinal, int64_t* free_bytes, int64_t* total_bytes);
 ITEXB_API int itexb_rt_allocate(int ordinal, size_t bytes, void** ptr);      /* 256-byte aligned */
+/* The block goes back to the free lists at once and may be handed out again by the next allocate: the caller must
+ * know that all device work that reads or writes it has finished (the contract of StreamExecutor's deallocate,
+ * itex/core/devices/gpu/gpu_device_plugin.cc:80-92, where TensorFlow orders frees itself). */
 ITEXB_API int itexb_rt_deallocate(int ordinal, void* ptr);
+/* Stream-ordered free: the block is reused only after the work queued on `stream` so far has finished (an event is
+ * recorded; allocate checks it).  What the op layer uses for its own per-instance buffers. */
+ITEXB_API int itexb_rt_deallocate_after(int ordinal, void* ptr, itexb_stream_t stream);
 ITEXB_API int itexb_rt_host_allocate(size_t bytes, void** ptr);              /* pinned */
 ITEXB_API int itexb_rt_host_deallocate(void* ptr);
 ITEXB_API int itexb_rt_allocator_stats(int ordinal, itexb_allocator_stats_t* stats);
@@ -268,6 +274,16 @@ typedef struct itexb_gemm_params {
 } itexb_gemm_params_t;
 ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
 
+/* Test hooks of the GEMM / convolution kernels' failure path; process-wide, read at every launch.  They have no
+ * counterpart in the reference.  Keys:
+ *   "gemm_wait_limit_cycles"  clock cycles a wait on a pipeline stage may take before the kernel gives up (the wait on a
+ *                             whole accumulator gets twice that); 0 restores the default of 4e9 (about 2 s);
+ *   "gemm_skip_kblock"        the TMA producer of every CTA leaves out this k-block of its first tile - a barrier that
+ *                             nothing completes, made on the host's request, so that a test can watch a wait run out
+ *                             (status word 2, the MMA issuer's role), the kernel return and the next launch work; -1: off.
+ * Unknown keys give ITEXB_NOT_FOUND. */
+ITEXB_API int itexb_debug_set(const char* key, int64_t value);
+
 /* NHWC x (packed) HWIO convolution as an implicit GEMM with the same epilogue.
  * Replaces dnnl::convolution_forward (itex/core/kernels/common/conv_ops.h:953-957,801).
  * x: [n,h,w,c] QUINT8|QINT8; filter packed by itexb_pack_filter_hwio to [co][k_pad],
@@ -424,8 +440,39 @@ ITEXB_API const char* const* itexb_op_list(void);
  * gpu/quantized_matmul.cc:137-182.                                                  */
 ITEXB_API int itexb_op_signature(const char* op_name, int* num_inputs, int* num_outputs,
                                  uint32_t* host_input_mask, uint32_t* host_output_mask);
+/* The op definition a TensorFlow plugin has to register for `op_name` before its kernels can be found: the strings are
+ * the arguments of TF_OpDefinitionBuilderAddInput / AddOutput / AddAttr ("a: T1", "T1: quantizedtype",
+ * "transpose_a: bool = false" ...), as the reference registers them (itex/core/ops/nn_ops.cc:1070-1127,1601-1772,
+ * 3339-3600,4136-4325,4513-4760; itex/core/ops/fp8_ops.cc:22-61,124-143,192-226).  defined_by_plugin = 0 means the name
+ * is an op TensorFlow defines itself (QuantizeV2, QuantizedConv2DWithBias..., _QuantizedMatMul ...) or one the reference
+ * registers kernels for without a definition of its own: only kernels are registered for it.  For such a name the
+ * strings are those of the twin op the reference defines with the same argument list (_ITEXQuantizeV2 for QuantizeV2
+ * ...): the argument names serve TF_KernelBuilder_HostMemory, and an attr is read only if the node has it.
+ * The pointers are to static storage. */
+typedef struct itexb_op_def {
+  const char* name;
+  int32_t defined_by_plugin;
+  int32_t num_inputs;
+  const char* const* inputs;
+  int32_t num_outputs;
+  const char* const* outputs;
+  int32_t num_attrs;
+  const char* const* attrs;
+} itexb_op_def_t;
+ITEXB_API int itexb_op_def(const char* op_name, itexb_op_def_t* def);
 ITEXB_API int itexb_op_create(const char* op_name, const itexb_attr_t* attrs, int num_attrs, itexb_op_t** op);
+/* Compute enqueues on ctx->stream and returns without waiting (kernel_compute of itex/core/utils/op_kernel.h:859-917);
+ * one Compute at a time per instance (mu_compute_, quantized_matmul_common.h:62), and the launches of one instance are
+ * expected on one stream per device (calls from another stream are ordered behind the instance's cached uploads).
+ * Errors a kernel can only report after it ran - a bounded device wait that expired - are kept in a per-instance
+ * device status word and surface as ITEXB_ABORTED from the instance's NEXT itexb_op_compute (which then does not
+ * run), from a Compute under ITEXB_SYNC_EXEC / ITEXB_VERBOSE (same call), or from itexb_op_check. */
 ITEXB_API int itexb_op_compute(itexb_op_t* op, itexb_op_context_t* ctx);
+/* Status of the launches this instance has made so far: ITEXB_OK, or ITEXB_ABORTED with the kernel role that gave up.
+ * wait != 0 blocks until the work queued by the last Compute has finished; wait == 0 only looks at what has landed. */
+ITEXB_API int itexb_op_check(itexb_op_t* op, int wait);
+/* Frees the instance and its device buffers (stream-ordered behind its last launches).  A pending kernel error that
+ * nobody collected is written to stderr. */
 ITEXB_API void itexb_op_delete(itexb_op_t* op);
 
 /* A ready-made context over the runtime above: outputs and temps come from

@@ -85,6 +85,11 @@ class AllocatorStats(C.Structure):
                 ("bytes_reserved", C.c_int64), ("largest_alloc_size", C.c_int64), ("bytes_limit", C.c_int64)]
 
 
+class OpDef(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("defined_by_plugin", C.c_int32), ("num_inputs", C.c_int32), ("inputs", C.POINTER(C.c_char_p)),
+                ("num_outputs", C.c_int32), ("outputs", C.POINTER(C.c_char_p)), ("num_attrs", C.c_int32), ("attrs", C.POINTER(C.c_char_p))]
+
+
 ALLOC_OUTPUT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.POINTER(Tensor))
 ALLOC_TEMP_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_void_p))
 
@@ -112,6 +117,9 @@ def load():
     lib.itexb_launch_count.restype = C.c_uint64
     lib.itexb_conv2d_workspace_bytes.restype = C.c_size_t
     lib.itexb_conv2d_filter_c_pad.restype = C.c_int32
+    lib.itexb_op_check.argtypes = [C.c_void_p, C.c_int]
+    lib.itexb_op_def.argtypes = [C.c_char_p, C.POINTER(OpDef)]
+    lib.itexb_debug_set.argtypes = [C.c_char_p, C.c_int64]
     _lib = lib
     return lib
 

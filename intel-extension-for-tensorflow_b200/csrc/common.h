@@ -84,6 +84,23 @@ inline bool IsFp8(int dt) { return dt == ITEXB_DT_FP8_E4M3 || dt == ITEXB_DT_FP8
 
 inline cudaStream_t AsCuda(itexb_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// While any stream of the process is being captured into a CUDA graph in the default ("global") capture mode, calls
+// that are not stream operations - event queries, host or device allocations - are refused and invalidate the capture.
+// Bookkeeping calls that only concern work outside the capture (has an earlier upload landed? may a freed block be
+// reused?) are made with this guard, which switches the calling thread to the relaxed mode for its lifetime.
+struct RelaxedCaptureMode {
+  cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+  RelaxedCaptureMode() { if (cudaThreadExchangeStreamCaptureMode(&mode) != cudaSuccess) (void)cudaGetLastError(); }
+  ~RelaxedCaptureMode() { if (cudaThreadExchangeStreamCaptureMode(&mode) != cudaSuccess) (void)cudaGetLastError(); }
+  RelaxedCaptureMode(const RelaxedCaptureMode&) = delete;
+  RelaxedCaptureMode& operator=(const RelaxedCaptureMode&) = delete;
+};
+inline bool IsCapturing(cudaStream_t stream) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) (void)cudaGetLastError();
+  return cap != cudaStreamCaptureStatusNone;
+}
+
 // Number of SMs of the current device (cached per device ordinal).
 int SmCount();
 

@@ -417,6 +417,16 @@ int StaticScratchAddress(void** ptr) {
 
 extern "C" int itexb_conv2d_static_scratch(const itexb_conv_params_t* p, itexb_stream_t stream) {
   ITEXB_REQUIRE(p != nullptr, ITEXB_INVALID_ARGUMENT, "conv2d_static_scratch: params is NULL");
+  ITEXB_RETURN_IF_ERROR(Validate(*p));  // bad dimensions are an argument error, not a scratch-size one
+  // The array's address is looked up on the current device, so the stream has to belong to it: a stream of another GPU
+  // would run the kernels there with this GPU's address.
+  int cur = 0, sdev = 0;
+  ITEXB_CUDA(cudaGetDevice(&cur));
+  if (stream != nullptr) {
+    ITEXB_CUDA(cudaStreamGetDevice(AsCuda(stream), &sdev));
+    ITEXB_REQUIRE(sdev == cur, ITEXB_INVALID_ARGUMENT,
+                  "conv2d_static_scratch: the stream belongs to device %d but device %d is current; make the stream's device current", sdev, cur);
+  }
   const size_t need = itexb_conv2d_workspace_bytes(p);
   ITEXB_REQUIRE(need <= size_t(ITEXB_STATIC_SCRATCH_BYTES), ITEXB_RESOURCE_EXHAUSTED,
                 "conv2d_static_scratch: this convolution needs %zu bytes of scratch, the built-in array holds %zu; "

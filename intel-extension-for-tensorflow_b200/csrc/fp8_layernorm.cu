@@ -11,6 +11,7 @@
 #include <cuda_fp8.h>
 
 #include "common.h"
+#include "fp8_cast.h"
 
 namespace itexb {
 namespace {
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(kLnThreads) Fp8LayerNormKernel(const TX* __res
     const float v = LnToFloat<TW>(gamma[c]) * y + LnToFloat<TW>(beta[c]);
     if constexpr (kFp8) {
       amax = fmaxf(amax, fabsf(v));
-      zr[c] = (TZ)__nv_cvt_float_to_fp8(v * scale, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
+      zr[c] = (TZ)FloatToFp8Bits(v * scale, E4M3);
     } else {
       LnStore(zr + c, v);
     }

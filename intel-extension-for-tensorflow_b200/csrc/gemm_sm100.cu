@@ -41,9 +41,12 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
+#include <string>
 
 #include "common.h"
+#include "fp8_cast.h"
 #include "gemm_sm100.h"
 
 namespace itexb {
@@ -59,7 +62,7 @@ constexpr int kThreadsConv = kThreads + 128;            // ... + 4 warps that ga
 constexpr int kGatherThreads = 128;
 constexpr int kStagingPerWarp = 2048;  // bytes of output staging each epilogue warp owns
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz; the default of GemmArgs::wait_limit
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrSmemAlign = 4 };
 
@@ -68,7 +71,8 @@ template <int BN> struct Cfg {
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128), 8 (64)
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two >= 32
+  // Accumulators in tensor memory: 2 stages of SUP sub-tiles of BN columns (a power of two >= 32, at most the 512 there are).
+  template <int SUP> static constexpr int kTmemCols = 2 * BN * SUP < 32 ? 32 : 2 * BN * SUP;
   static constexpr int kSumBars = kEpilogueWarps * 4;          // one per epilogue warp and staging buffer (summand loads)
   static constexpr int kBarrierBytes = (2 * kStages + 6 + kSumBars) * 8 + 16;
   static constexpr int kParamBytes = 2 * BN * 4;               // the tile's per-column scales and biases
@@ -106,14 +110,15 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the wait expired or another role already gave up;
 // in the first case it also publishes `code` to the status word.
-__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int code) {
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int code,
+                                         const long long& limit) {
   if (MbarTryWait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (MbarTryWait(bar, parity)) return true;
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {  // read from the kernel's parameter space only here, every 256 polls
         *abort_flag = 1;
         if (status_word != nullptr) atomicCAS(status_word, 0, code);
         return false;
@@ -287,10 +292,20 @@ __device__ __forceinline__ float LoadSummand(const void* p, int dt, long long id
   }
 }
 
-// Columns of one epilogue block (the unit one warp converts, stages and stores): 16 columns of a 4-byte output,
-// 32 of a narrower one - but 16 for every type when the tile is 64 columns wide, so that the tile still has four
-// blocks, one for each of the four warps that share a row quarter (with two blocks half the epilogue warps idle).
-__host__ __device__ constexpr int OutBlockCols(int bn, int esz) { return (esz == 4 || bn == 64) ? 16 : 32; }
+// Columns of one epilogue block (the unit one warp converts, stages and stores with one TMA store).  The four warps
+// that share a row quarter are spread over the sup sub-tiles of an accumulator stage, 4 / sup warps per sub-tile, and
+// every one of them must find a block there.  Tiles of 128 or more columns: 16 columns of a 4-byte output, 32 of a
+// narrower one.  64-column tiles: the tile's columns divided among its 4 / sup warps, at most 64 bytes per row - a
+// single sub-tile per stage leaves each warp a 16-column block (stores of 16-byte row fragments, which is what
+// stacking four sub-tiles per stage avoids: then one warp owns whole 64-column rows of one sub-tile).  The 8-bit
+// summand loop wants two staging buffers per warp (the summand of the next block lands while this one is
+// converted), which caps its rows at 32 bytes.
+__host__ __device__ constexpr int OutBlockCols(int bn, int esz, int sup, bool sum8) {
+  if (bn != 64) return esz == 4 ? 16 : 32;
+  int cols = bn / (4 / sup);                       // 16, 32 or 64
+  const int max_cols = (sum8 ? 32 : 64) / esz;     // row bytes the staging buffers allow
+  return cols < max_cols ? cols : (max_cols < 16 ? 16 : max_cols);
+}
 // Epilogue loop specialisations (template parameter, chosen per launch by LaunchGemm).
 enum : int { kEpGeneral = 0, kEpPlain = 1, kEpSum8 = 2 };
 // Output kinds (template parameter of the epilogue).
@@ -329,12 +344,11 @@ __device__ __forceinline__ void Convert16(const float (&v)[16], uint32_t (&w)[16
     for (int j = 0; j < 4; ++j)
       w[j] = PackSat8<OK == kOutS8>(RneS32(v[4 * j]), RneS32(v[4 * j + 1]), RneS32(v[4 * j + 2]), RneS32(v[4 * j + 3]));
   } else if (OK == kOutFP8) {
-    const __nv_fp8_interpretation_t kind = e4m3 ? __NV_E4M3 : __NV_E5M2;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint32_t q[4];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) q[t] = (uint32_t)__nv_cvt_float_to_fp8(__fmul_rn(v[4 * j + t], out_scale), __NV_SATFINITE, kind);
+      for (int t = 0; t < 4; ++t) q[t] = (uint32_t)FloatToFp8Bits(__fmul_rn(v[4 * j + t], out_scale), e4m3);
       w[j] = PackLowBytes(q[0], q[1], q[2], q[3]);
     }
   }
@@ -457,14 +471,14 @@ struct EpilogueCtx {
 // slices into a swizzled staging tile (32 rows of 64 or 32 bytes) that one TMA store then
 // writes; edges are clipped by the tensor map.  Without TMA-legal output rows the slices go
 // straight to global memory.
-template <int BN, bool F8, int OK, int MODE>
+template <int BN, bool F8, int OK, int MODE, int SUP>
 __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, const CUtensorMap* tma_sum, uint8_t* s_stage,
                                              float* s_par, uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint64_t* par_bar,
                                              uint64_t* sum_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane, int tiles_m,
                                              int tiles_n, int num_tiles) {
   constexpr int esz = OutBytes<OK>::v;
   constexpr int units = esz;                          // 16-byte units per 16-column slice
-  constexpr int bcols = OutBlockCols(BN, esz);        // columns per block
+  constexpr int bcols = OutBlockCols(BN, esz, SUP, MODE == kEpSum8);  // columns per block
   constexpr int slices = bcols / 16;
   constexpr int row_bytes = bcols * esz;              // 64, 64, 32 (BN = 64: 64, 32, 16)
   constexpr int row_units = row_bytes / 16;
@@ -472,6 +486,10 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   constexpr int nbuf = kStagingPerWarp / buf_bytes;   // staging buffers per warp: 1 (64-byte rows), 2 or 4
   const int q = warp & 3;
   const int sub = (warp - 4) >> 2;
+  constexpr int W = 4 / SUP;            // warps of a row quarter that share one sub-tile
+  const int j = sub / W;                // this warp's sub-tile within every accumulator stage
+  const int c_first = sub % W;          // ... and its first block there; it takes every W-th
+  const int tiles_m_real = (g.m + kBM - 1) / kBM;  // tiles_m counts super rows of SUP tile rows each
   constexpr bool PLAIN = MODE == kEpPlain, SUM8 = MODE == kEpSum8;
   const bool tma_store = MODE != kEpGeneral || g.tma_store;
   EpilogueCtx e;
@@ -494,7 +512,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   e.sum_flip = sum_signed ? 0x80808080u : 0u;
   e.sum_base_bits = sum_signed ? uint32_t(kMagicBits) : 0x4B000000u;  // 1.5 * 2^23 | 2^23
   {
-    const float off = sum_signed ? -(kMagic + 128.f) : __fmul_rn(-8388608.f, g.ep.sum_scale);
+    const float off = sum_signed ? -(kMagic + 128.f) : -8388608.f;
     e.sum_off2 = Pack2(off, off);
   }
   const int swz = (lane / (8 / row_units)) % row_units;  // this lane's XOR term of the staging swizzle
@@ -519,7 +537,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   constexpr bool preset = !F8 && OK != kOutRaw && MODE == kEpPlain;  // == g.preset, known at compile time here
   if (preset) {
 #pragma unroll 1
-    for (int c = sub * 16; c < 2 * BN; c += 16 * (kEpilogueWarps / 4))
+    for (int c = sub * 16; c < 2 * BN * SUP; c += 16 * (kEpilogueWarps / 4))
       TmemSt16Same(tmem_base + uint32_t(c) + (uint32_t(q * 32) << 16), uint32_t(kMagicBits));
     TmemStWait();
     TcFenceBefore();
@@ -549,7 +567,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
     if (staged && tn != last_tn) {
       bool pok = true;
-      if (reloads > 0) pok = MbarWait(SmemAddr(&par_bar[1]), (reloads - 1) & 1, abort_flag, g.status_word, kErrEpilogue);
+      if (reloads > 0) pok = MbarWait(SmemAddr(&par_bar[1]), (reloads - 1) & 1, abort_flag, g.status_word, kErrEpilogue, g.wait_limit);
       if (!__all_sync(0xffffffffu, pok)) break;
       if (et < 2 * BN) {
         const int j = et < BN ? et : et - BN;
@@ -561,30 +579,36 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
       }
       __syncwarp();
       if (lane == 0) MbarArrive(SmemAddr(&par_bar[0]));
-      pok = MbarWait(SmemAddr(&par_bar[0]), reloads & 1, abort_flag, g.status_word, kErrEpilogue);
+      pok = MbarWait(SmemAddr(&par_bar[0]), reloads & 1, abort_flag, g.status_word, kErrEpilogue, g.wait_limit);
       if (!__all_sync(0xffffffffu, pok)) break;
       ++reloads;
       last_tn = tn;
     }
-    const int row0 = tm * kBM + q * 32;  // first row of this warp's 32-row block
-    const bool row_ok = row0 + lane < g.m;
-    const long long row = (long long)bt * g.batch_rows_out + row0 + lane;  // row of `out` / the summand across batches
     const int nblocks = min(BN / bcols, (g.n - tn * BN + bcols - 1) / bcols);  // blocks holding real columns
-    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue);
+    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue, g.wait_limit_acc);
     if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
     TcFenceAfter();
-    const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(q * 32) << 16);
+    // One accumulator stage holds SUP tiles of consecutive tile rows (sub-tile j in columns j*BN ...); each warp works
+    // on one of them.  For 64-column tiles that gives a warp whole rows of its sub-tile (one TMA store of full rows per
+    // warp and stage) where a single tile per stage left it a 16-column fragment.
+    do {
+    const int tmr = tm * SUP + j;
+    if (tmr >= tiles_m_real) break;  // the MMA issuer left these columns untouched (still armed)
+    const int row0 = tmr * kBM + q * 32;  // first row of this warp's 32-row block
+    const bool row_ok = row0 + lane < g.m;
+    const long long row = (long long)bt * g.batch_rows_out + row0 + lane;  // row of `out` / the summand across batches
+    const uint32_t taddr = tmem_base + uint32_t((acc * SUP + j) * BN) + (uint32_t(q * 32) << 16);
     if (row0 >= g.m) {
       // No row of this warp is stored, but the MMA still accumulated onto its lanes: re-arm them too.
       if (preset) {
 #pragma unroll 1
-        for (int c = sub * bcols; c < BN; c += bcols * (kEpilogueWarps / 4))
+        for (int c = c_first * bcols; c < BN; c += bcols * W)
 #pragma unroll 1
           for (int sl = 0; sl < slices; ++sl) TmemSt16Same(taddr + uint32_t(c + 16 * sl), uint32_t(kMagicBits));
       }
     } else {
 #pragma unroll 1
-      for (int c = sub; c < nblocks; c += kEpilogueWarps / 4) {
+      for (int c = c_first; c < nblocks; c += W) {
         const int col0 = tn * BN + c * bcols;
         uint8_t* buf = e.stage + (seq & uint32_t(nbuf - 1)) * buf_bytes;
         bool sum_pref_next = false;
@@ -596,7 +620,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             }
           }
           const bool sok = MbarWait(SmemAddr(&my_sum_bar[seq & uint32_t(nbuf - 1)]), (seq / uint32_t(nbuf)) & 1u, abort_flag,
-                                    g.status_word, kErrEpilogue);
+                                    g.status_word, kErrEpilogue, g.wait_limit);
           if (!__all_sync(0xffffffffu, sok)) { give_up = true; break; }
         }
 #pragma unroll 1
@@ -604,15 +628,17 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
           const int col = col0 + 16 * sl;
           if (col >= g.n) break;
           if constexpr (SUM8) if (sl == slices - 1) {
-            // look one block ahead: the next block of this tile, or this warp's first block of its next tile
+            // look one block ahead: the next block of this sub-tile, or this warp's first block in the next stage it
+            // works on.  A guess of "none" is always safe (the block then fetches its own summand); a
+            // block is only ever announced when it is exactly the one this warp processes next.
             int ncol0 = -1, nrow0 = 0, nbt = 0;
-            if (c + kEpilogueWarps / 4 < nblocks) {
-              ncol0 = col0 + bcols * (kEpilogueWarps / 4); nrow0 = row0; nbt = bt;
+            if (c + W < nblocks) {
+              ncol0 = col0 + bcols * W; nrow0 = row0; nbt = bt;
             } else if (t + int(gridDim.x) < num_tiles) {
               int ntm, ntn;
               TileCoords(t + int(gridDim.x), g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
-              nrow0 = ntm * kBM + q * 32;
-              if (nrow0 < g.m && ntn * BN + sub * bcols < g.n) ncol0 = ntn * BN + sub * bcols;
+              nrow0 = (ntm * SUP + j) * kBM + q * 32;  // < m implies that the tile row exists
+              if (nrow0 < g.m && ntn * BN + c_first * bcols < g.n) ncol0 = ntn * BN + c_first * bcols;
             }
             if (ncol0 >= 0) {
               if (lane == 0) {
@@ -704,11 +730,12 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
               const long long sb = row * g.ep.ld_summand + col;
               if (SUM8 || sum_vec) {  // SUM8: rows past m carry zero bytes and are never stored
                 // 16 summand bytes -> fp32 without conversion instructions: the byte permute drops each byte into
-                // the low byte of the bit pattern of a power of two P >= 2^23, i.e. builds the float P + byte.
-                // Unsigned bytes, P = 2^23: one fused multiply-add gives byte * s = (P + byte) * s - P * s with a
-                // single rounding, because P * s is exact (computed once per launch), then one add; two columns
-                // per instruction.  Signed bytes are offset by 128 first (b ^ 0x80 = b + 128) on 1.5 * 2^23, the
-                // offset is taken off exactly, then multiply (fused multiply-add with the hidden -0, see above) and add.
+                // the low byte of the bit pattern of a power of two P >= 2^23, i.e. builds the float P + byte, and
+                // one exact add takes P off again (unsigned bytes: P = 2^23; signed bytes are offset by 128 first,
+                // b ^ 0x80 = b + 128, on 1.5 * 2^23, and the add takes 1.5 * 2^23 + 128 off).  Then ONE fused
+                // multiply-add  v = summand * sum_scale + v : the sum post-op of oneDNN's kernels is a fused
+                // multiply-add (a single rounding), which shows on rounding ties - a handful of elements in ten
+                // million - and is what the oracle and the real-oneDNN fixture pin.  Two columns per instruction.
                 const uint32_t sw[4] = {s4.x ^ e.sum_flip, s4.y ^ e.sum_flip, s4.z ^ e.sum_flip, s4.w ^ e.sum_flip};
                 const uint64_t ss2 = Pack2(g.ep.sum_scale, g.ep.sum_scale);
 #pragma unroll
@@ -716,20 +743,14 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
                   const uint32_t word = sw[j >> 1];
                   const float f0 = __uint_as_float(__byte_perm(word, e.sum_base_bits, (j & 1) ? 0x7652 : 0x7650));
                   const float f1 = __uint_as_float(__byte_perm(word, e.sum_base_bits, (j & 1) ? 0x7653 : 0x7651));
-                  uint64_t t = Pack2(f0, f1);
-                  if (sum_signed) {
-                    t = Add2(t, e.sum_off2);
-                    t = Fma2(t, ss2, g.neg_zero2);
-                  } else {
-                    t = Fma2(t, ss2, e.sum_off2);
-                  }
-                  t = Add2(Pack2(v[2 * j], v[2 * j + 1]), t);
+                  uint64_t t = Add2(Pack2(f0, f1), e.sum_off2);
+                  t = Fma2(t, ss2, Pack2(v[2 * j], v[2 * j + 1]));
                   Unpack2(t, v[2 * j], v[2 * j + 1]);
                 }
               } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                  if (!SUM8 && col + j < g.n) v[j] = __fadd_rn(v[j], __fmul_rn(g.ep.sum_scale, LoadSummand(g.ep.summand, g.ep.summand_dtype, sb + j)));
+                  if (!SUM8 && col + j < g.n) v[j] = __fmaf_rn(g.ep.sum_scale, LoadSummand(g.ep.summand, g.ep.summand_dtype, sb + j), v[j]);
               }
             }
             if (e.relu) {
@@ -800,6 +821,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
       }
       if (give_up) break;
     }
+    } while (false);  // this warp's sub-tile
+    if (give_up) break;
     if (preset) TmemStWait();  // the re-armed columns are in place before the MMA warp may accumulate onto them
     TcFenceBefore();
     __syncwarp();
@@ -826,7 +849,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 // The kernel.  CONV selects how the producer addresses the A operand: a plain [m,k]
 // matrix (2-D map) or NHWC pixels gathered per filter tap (see conv section below).
 // ---------------------------------------------------------------------------------------
-template <int BN, bool F8, int CONV>
+template <int BN, bool F8, int CONV, int SUP>
 __global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a_tail,
@@ -852,7 +875,11 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_m = (g.m + kBM - 1) / kBM;
+  static_assert(SUP == 1 || SUP == 2 || SUP == 4, "sub-tiles per accumulator stage");
+  static_assert(2 * BN * SUP <= 512, "tensor memory has 512 columns");
+  static_assert(CONV != kConvGather || SUP == 1, "the cp.async gather variant walks single tiles");
+  const int tiles_m_real = (g.m + kBM - 1) / kBM;
+  const int tiles_m = (tiles_m_real + SUP - 1) / SUP;  // super rows: the unit of the tile walk is SUP consecutive tile rows
   const int tiles_n = (g.n + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n * g.batch;
   // bytes of K per k-block: 128, or in the im2col path 64 / 32 when a filter tap has that many (padded) channels
@@ -875,7 +902,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 2) {
-    TmemAlloc(SmemAddr(tmem_slot), C::kTmemCols);
+    TmemAlloc(SmemAddr(tmem_slot), C::template kTmemCols<SUP>);
     TmemRelinquish();
   }
   TcFenceBefore();
@@ -894,8 +921,11 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     uint32_t phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int tm, tn, bt;
-      TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
+      int tms, tn, bt;
+      TileCoords(t, g, tiles_m, tiles_n, &tms, &tn, &bt);
+      for (int j = 0; j < SUP && ok; ++j) {
+      const int tm = tms * SUP + j;
+      if (tm >= tiles_m_real) break;
       int w0 = 0, h0 = 0, n0 = 0, c0 = 0, kx = 0, ky = 0;  // im2col: base position of the tile's first pixel, position in K
       if (CONV == kConvIm2col) {
         const int pix = tm * kBM;
@@ -905,8 +935,18 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         h0 = (rest - n0 * g.oh) * g.stride_h - g.pad_top;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer);
+        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit);
         if (!ok) break;
+        if (kb == g.debug_skip_kb && t == int(blockIdx.x) && j == 0) {
+          // Test hook: this k-block never arrives (neither its expect_tx nor its copies are issued), so the MMA issuer's
+          // wait on it runs out and the kernel has to take its give-up path with nothing of this stage in flight.
+          if (CONV == kConvIm2col) {
+            c0 += kb_bytes;
+            if (c0 >= g.conv_cpad) { c0 = 0; if (++kx == g.kw) { kx = 0; ++ky; } }
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          continue;
+        }
         const uint32_t fb = SmemAddr(&full_bar[stage]);
         uint8_t* sa = smem + stage * C::kStageBytes;
         if (CONV == kConvGather) {
@@ -934,6 +974,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         TmaLoad3d(SmemAddr(sa + C::kABytes), &tma_b, fb, kb * kBK, tn * BN, bt);
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
+      }  // sub-tiles
     }
     if (!ok) {
       // Copies already issued land within microseconds; give them a bounded ~200 us
@@ -951,12 +992,19 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       // Without preset the first use of each accumulator stage finds its barrier "already released" (parity trick);
       // with preset it waits for the epilogue warps' arming of the stage, one phase earlier throughout.
-      ok = MbarWait(SmemAddr(&tmem_empty_bar[acc]), g.preset ? acc_phase : acc_phase ^ 1, abort_flag, g.status_word, kErrMma);
+      ok = MbarWait(SmemAddr(&tmem_empty_bar[acc]), g.preset ? acc_phase : acc_phase ^ 1, abort_flag, g.status_word, kErrMma, g.wait_limit);
       if (!ok) break;
       TcFenceAfter();
-      const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+      int tms = 0;
+      if (SUP > 1) {
+        int tn_unused, bt_unused;
+        TileCoords(t, g, tiles_m, tiles_n, &tms, &tn_unused, &bt_unused);
+      }
+      for (int j = 0; j < SUP && ok; ++j) {
+      if (SUP > 1 && tms * SUP + j >= tiles_m_real) break;
+      const uint32_t d_tmem = tmem_base + uint32_t((acc * SUP + j) * BN);
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = MbarWait(SmemAddr(&full_bar[stage]), phase, abort_flag, g.status_word, kErrMma);
+        ok = MbarWait(SmemAddr(&full_bar[stage]), phase, abort_flag, g.status_word, kErrMma, g.wait_limit);
         if (!ok) break;
         TcFenceAfter();
         uint8_t* sa = smem + stage * C::kStageBytes;
@@ -979,8 +1027,9 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         TcCommit(SmemAddr(&empty_bar[stage]));  // stage reusable once these MMAs have read it
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
+      }  // sub-tiles
       if (!ok) break;
-      TcCommit(SmemAddr(&tmem_full_bar[acc]));  // accumulator complete
+      TcCommit(SmemAddr(&tmem_full_bar[acc]));  // all sub-tile accumulators of this stage complete
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -1032,7 +1081,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       int ci = j * 16, kx = 0, ky = 0;
       while (ci >= g.conv_c) { ci -= g.conv_c; if (++kx == g.kw) { kx = 0; ++ky; } }
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer);
+        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit);
         if (!ok) break;
         const uint32_t dst = SmemAddr(smem + stage * C::kStageBytes) + dst_off;
         const uint32_t tap_off = uint32_t((ky * g.dil_h * g.conv_w + kx * g.dil_w) * g.conv_c + ci);
@@ -1069,34 +1118,34 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     // ---------------- epilogue ----------------
 #define ITEXB_EP_ARGS g, &tma_out, &tma_sum, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, sum_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles
     switch (g.out_kind) {
-      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral>(ITEXB_EP_ARGS); break;
+      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral, SUP>(ITEXB_EP_ARGS); break;
       case kOutF32:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF32, kEpPlain>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutF32, kEpGeneral>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF32, kEpPlain, SUP>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutF32, kEpGeneral, SUP>(ITEXB_EP_ARGS);
         break;
       case kOutBF16:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutBF16, kEpPlain>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutBF16, kEpGeneral>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutBF16, kEpPlain, SUP>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutBF16, kEpGeneral, SUP>(ITEXB_EP_ARGS);
         break;
       case kOutF16:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF16, kEpPlain>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutF16, kEpGeneral>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF16, kEpPlain, SUP>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutF16, kEpGeneral, SUP>(ITEXB_EP_ARGS);
         break;
       case kOutS32:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS32, kEpPlain>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutS32, kEpGeneral>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS32, kEpPlain, SUP>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutS32, kEpGeneral, SUP>(ITEXB_EP_ARGS);
         break;
       case kOutU8:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutU8, kEpPlain>(ITEXB_EP_ARGS);
-        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutU8, kEpSum8>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutU8, kEpGeneral>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutU8, kEpPlain, SUP>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutU8, kEpSum8, SUP>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutU8, kEpGeneral, SUP>(ITEXB_EP_ARGS);
         break;
       case kOutS8:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS8, kEpPlain>(ITEXB_EP_ARGS);
-        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutS8, kEpSum8>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutS8, kEpGeneral>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS8, kEpPlain, SUP>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutS8, kEpSum8, SUP>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutS8, kEpGeneral, SUP>(ITEXB_EP_ARGS);
         break;
-      default: EpilogueLoop<BN, F8, kOutFP8, kEpGeneral>(ITEXB_EP_ARGS); break;
+      default: EpilogueLoop<BN, F8, kOutFP8, kEpGeneral, SUP>(ITEXB_EP_ARGS); break;
     }
   }
 
@@ -1104,7 +1153,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   __syncthreads();
   if (warp == 2) {
     TcFenceAfter();
-    TmemDealloc(tmem_base, C::kTmemCols);
+    TmemDealloc(tmem_base, C::template kTmemCols<SUP>);
   }
 }
 
@@ -1130,7 +1179,7 @@ EncodeTiledFn GetEncodeTiled() {
   return fn;
 }
 
-template <int BN, bool F8, int CONV>
+template <int BN, bool F8, int CONV, int SUP>
 int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tat, const CUtensorMap& tbt,
            const CUtensorMap& ts, const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
@@ -1139,10 +1188,10 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   int dev = 0;
   ITEXB_CUDA(cudaGetDevice(&dev));
   if (dev != last_dev) {
-    ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8, CONV, SUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     last_dev = dev;
   }
-  const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + BN - 1) / BN) * g.batch;
+  const int tiles = (((g.m + kBM - 1) / kBM + SUP - 1) / SUP) * ((g.n + BN - 1) / BN) * g.batch;
   const int grid = std::max(1, std::min(tiles, SmCount()));
   // Launched with programmatic stream serialization (ITEXB_PDL=0 turns it off): back-to-back GEMM launches of a
   // layer graph overlap one kernel's set-up with the tail of the one before.
@@ -1160,7 +1209,7 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV>, ta, tb, to, tat, tbt, ts, g));
+  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV, SUP>, ta, tb, to, tat, tbt, ts, g));
   return CheckLaunch("GemmKernel");
 }
 
@@ -1225,12 +1274,13 @@ int EncodeIm2colMap(CUtensorMap* map, const itexb_conv_params_t& p) {
 // Tensor map for the epilogue's TMA stores: the output as a byte matrix {n*esz, m} with
 // row pitch ldo*esz, box = one warp block of 32 rows x 16 (4-byte) or 32 (narrower) elements,
 // swizzle matching the staging tile's row width (64 or 32 bytes).
-static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz, int bn, int64_t batch, int64_t batch_rows) {
+static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int esz, int bn, int sup, bool sum8, int64_t batch,
+                           int64_t batch_rows) {
   EncodeTiledFn enc = GetEncodeTiled();
   ITEXB_REQUIRE(enc != nullptr, ITEXB_FAILED_PRECONDITION, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   const cuuint64_t dims[3] = {cuuint64_t(n) * esz, cuuint64_t(m), cuuint64_t(batch)};
   const cuuint64_t strides[2] = {cuuint64_t(ldo) * esz, cuuint64_t(batch_rows) * ldo * esz};
-  const int row_bytes = OutBlockCols(bn, esz) * esz;  // staging rows of 64, 32 or 16 bytes, swizzled over their own width
+  const int row_bytes = OutBlockCols(bn, esz, sup, sum8) * esz;  // staging rows of 64, 32 or 16 bytes, swizzled over their own width
   const cuuint32_t box[3] = {cuuint32_t(row_bytes), 32, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapSwizzle sw = row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -1272,6 +1322,36 @@ FastDiv MakeFastDiv(uint32_t d) {
 
 int PickBN(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
+// Sub-tiles per accumulator stage (1, 2 or 4; 2 * bn * sup <= 512 columns of tensor memory).  Narrow tiles carry little
+// epilogue work per barrier round trip, so several consecutive tile rows share one; what that costs is coarser work
+// units, so the largest factor is taken that keeps the last wave of the persistent grid reasonably full.
+// ITEXB_GEMM_SUP forces a value (for measurements).
+static int PickSup(int bn, bool single_only, int tiles_m, int tiles_n, int batch) {
+  const int max_sup = single_only ? 1 : (bn == 64 ? 4 : (bn == 128 ? 2 : 1));
+  static const int forced = [] {
+    const char* e = std::getenv("ITEXB_GEMM_SUP");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  if (forced == 1 || forced == 2 || forced == 4) return std::min(forced, max_sup);
+  const long long sms = SmCount();
+  const long long tiles = (long long)tiles_m * tiles_n * batch;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int sup = max_sup; sup >= 1; sup /= 2) {
+    const long long units = (long long)((tiles_m + sup - 1) / sup) * tiles_n * batch;
+    if (sup > 1 && units < sms) continue;  // not enough units to occupy every SM
+    const long long waves = (units + sms - 1) / sms;
+    const double eff = double(tiles) / double(waves * sms * sup);
+    if (eff >= 0.85) return sup;
+    if (eff > best_eff) { best_eff = eff; best = sup; }
+  }
+  return best;
+}
+
+// Test hooks (itexb_debug_set): process-wide, read at every launch.
+static std::atomic<long long> g_wait_limit_cycles{0};  // 0: the default
+static std::atomic<int> g_debug_skip_kb{-1};
+
 int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail) {
   const CUtensorMap& tat = tail != nullptr ? tail->a : ta;  // placeholders when there is no narrow last k-block
   const CUtensorMap& tbt = tail != nullptr ? tail->b : tb;
@@ -1292,12 +1372,23 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   // m-tiles per rasterisation group, measured: wide tile grids want tall groups (8192^3: 32 beats 16 by 2 %, 8 loses 3 %),
   // narrow ones short groups (n = 4096: 8 beats 16 by 1-2 %)
   const int tiles_n = (g.n + bn - 1) / bn;
-  const int tiles_m = (g.m + kBM - 1) / kBM;
+  const int tiles_m_real = (g.m + kBM - 1) / kBM;
+  if (g.batch <= 1) { g.batch = 1; g.batch_rows_out = g.m; }
+  // Measured (B200, u8 output): stacking sub-tiles pays where a tile is all epilogue - one or two k-blocks: 401408 x 64
+  // with K = 64 26.8 -> 20.6 us, the 7x7x3 stem's GEMM (K = 160) 120.6 -> 99.8 us - and costs a few per cent where the
+  // main loop matters (K = 256: 27.2 -> 28.9 us; 3x3 convolutions of 64 channels, K = 576: 72.7 -> 76.4 us), because the
+  // MMA issuer then waits for a whole stage of sub-tiles to be drained.
+  const int sup = PickSup(bn, f8 || g.conv_mode == kConvGather || g.k > 192, tiles_m_real, tiles_n, g.batch);
+  const int tiles_m = (tiles_m_real + sup - 1) / sup;  // the tile walk's rows are super rows of `sup` tile rows
   g.group_m = tiles_n >= 32 ? 32 : (tiles_n <= 16 ? 8 : 16);
   g.div_per_batch = MakeFastDiv(uint32_t(tiles_m) * uint32_t(tiles_n));
   g.div_per_group = MakeFastDiv(uint32_t(g.group_m) * uint32_t(tiles_n));
   g.div_group_m = MakeFastDiv(uint32_t(g.group_m));
   g.neg_zero2 = 0x8000000080000000ull;
+  const long long limit = g_wait_limit_cycles.load(std::memory_order_relaxed);
+  g.wait_limit = limit > 0 ? limit : kWaitLimitCycles;
+  g.wait_limit_acc = 2 * g.wait_limit;
+  g.debug_skip_kb = g_debug_skip_kb.load(std::memory_order_relaxed);
   g.vec_store = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (g.ldo * g.out_esz) % 16 == 0) ? 1 : 0;
   g.tma_store = g.vec_store;
   // The common epilogues run loops compiled without the rest (the loop is bound by instruction fetch: the same
@@ -1315,31 +1406,36 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   }
   g.preset = (!f8 && g.ep_mode == kEpPlain) ? 1 : 0;
   CUtensorMap to;
-  if (g.batch <= 1) { g.batch = 1; g.batch_rows_out = g.m; }
   CUtensorMap tsum;  // Sum8: the summand seen through the output's geometry (same boxes, same swizzle)
   if (g.ep_mode == kEpSum8)
-    ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&tsum, const_cast<void*>(g.ep.summand), g.m, g.n, g.ep.ld_summand, 1, bn, g.batch, g.batch_rows_out));
+    ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&tsum, const_cast<void*>(g.ep.summand), g.m, g.n, g.ep.ld_summand, 1, bn, sup, true, g.batch, g.batch_rows_out));
   else tsum = ta;  // unused by the kernel
-  if (g.tma_store) ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, bn, g.batch, g.batch_rows_out));
+  if (g.tma_store)
+    ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, bn, sup, g.ep_mode == kEpSum8, g.batch, g.batch_rows_out));
   else to = ta;  // unused by the kernel
   if (g.conv_mode == kConvGather) {
-    if (bn == 256) return Launch<256, false, kConvGather>(ta, tb, to, tat, tbt, tsum, g, st);
-    if (bn == 128) return Launch<128, false, kConvGather>(ta, tb, to, tat, tbt, tsum, g, st);
-    return Launch<64, false, kConvGather>(ta, tb, to, tat, tbt, tsum, g, st);
-  }
-  if (g.conv_mode == kConvIm2col) {
-    if (bn == 256) return Launch<256, false, kConvIm2col>(ta, tb, to, tat, tbt, tsum, g, st);
-    if (bn == 128) return Launch<128, false, kConvIm2col>(ta, tb, to, tat, tbt, tsum, g, st);
-    return Launch<64, false, kConvIm2col>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 256) return Launch<256, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 128) return Launch<128, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
+    return Launch<64, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
   }
   if (f8) {
-    if (bn == 256) return Launch<256, true, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
-    if (bn == 128) return Launch<128, true, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
-    return Launch<64, true, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 256) return Launch<256, true, kConvNone, 1>(ta, tb, to, tat, tbt, tsum, g, st);
+    if (bn == 128) return Launch<128, true, kConvNone, 1>(ta, tb, to, tat, tbt, tsum, g, st);
+    return Launch<64, true, kConvNone, 1>(ta, tb, to, tat, tbt, tsum, g, st);
   }
-  if (bn == 256) return Launch<256, false, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
-  if (bn == 128) return Launch<128, false, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
-  return Launch<64, false, kConvNone>(ta, tb, to, tat, tbt, tsum, g, st);
+  const bool im2col = g.conv_mode == kConvIm2col;
+#define ITEXB_LAUNCH(BN_, SUP_)                                                                     \
+  return im2col ? Launch<BN_, false, kConvIm2col, SUP_>(ta, tb, to, tat, tbt, tsum, g, st)          \
+                : Launch<BN_, false, kConvNone, SUP_>(ta, tb, to, tat, tbt, tsum, g, st)
+  if (bn == 256) { ITEXB_LAUNCH(256, 1); }
+  if (bn == 128) {
+    if (sup == 2) { ITEXB_LAUNCH(128, 2); }
+    ITEXB_LAUNCH(128, 1);
+  }
+  if (sup == 4) { ITEXB_LAUNCH(64, 4); }
+  if (sup == 2) { ITEXB_LAUNCH(64, 2); }
+  ITEXB_LAUNCH(64, 1);
+#undef ITEXB_LAUNCH
 }
 
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n) {
@@ -1372,6 +1468,21 @@ int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype,
 }  // namespace itexb
 
 using namespace itexb;
+
+extern "C" int itexb_debug_set(const char* key, int64_t value) {
+  ITEXB_REQUIRE(key != nullptr, ITEXB_INVALID_ARGUMENT, "debug_set: key is NULL");
+  const std::string k(key);
+  if (k == "gemm_wait_limit_cycles") {
+    ITEXB_REQUIRE(value >= 0, ITEXB_INVALID_ARGUMENT, "debug_set: gemm_wait_limit_cycles must be >= 0 (0 restores the default)");
+    g_wait_limit_cycles.store(value, std::memory_order_relaxed);
+  } else if (k == "gemm_skip_kblock") {
+    ITEXB_REQUIRE(value >= -1 && value < (1ll << 30), ITEXB_INVALID_ARGUMENT, "debug_set: gemm_skip_kblock must be -1 (off) or a k-block index");
+    g_debug_skip_kb.store(int(value), std::memory_order_relaxed);
+  } else {
+    return SetError(ITEXB_NOT_FOUND, "debug_set: unknown key '%s'", key);
+  }
+  return ITEXB_OK;
+}
 
 extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   ITEXB_REQUIRE(p != nullptr, ITEXB_INVALID_ARGUMENT, "gemm: params is NULL");

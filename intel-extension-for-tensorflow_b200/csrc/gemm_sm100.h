@@ -21,6 +21,10 @@ struct GemmArgs {
   long long ldo;        // elements
   itexb_epilogue_t ep;
   int* status_word;     // set non-zero when a bounded wait expired
+  long long wait_limit; // cycles a wait on one pipeline stage may take before the kernel gives up (set by LaunchGemm)
+  long long wait_limit_acc;  // the same for the epilogue's wait on a whole accumulator: twice as long, so that the role
+                             // that is actually starved reports first (set by LaunchGemm)
+  int debug_skip_kb;    // test hook: the producer leaves out this k-block of each CTA's first tile (-1: none; set by LaunchGemm)
   unsigned idesc;       // tcgen05 instruction descriptor
   int vec_store;        // output rows are 16-byte aligned (set by LaunchGemm)
   int tma_store;        // epilogue writes through shared memory + TMA stores (set by LaunchGemm)

@@ -56,9 +56,33 @@ class OpKernel {
   void set_name(const std::string& n) { name_ = n; }
   std::mutex& mu() { return mu_; }
 
+  // ---- device status word ------------------------------------------------------------
+  // Every wait inside the GEMM / convolution kernels is bounded; a wait that runs out makes the kernel abandon its
+  // tiles and write a role code (1 producer, 2 MMA issuer, 3 epilogue, 4 misaligned shared memory) into a status word.
+  // Each op instance owns one such word in device memory and hands it to every launch it makes.  The op layer copies it
+  // to pinned host memory behind the launch (asynchronously, with an event) and looks at the copy at the instance's next
+  // Compute, after the stream synchronization of ITEXB_SYNC_EXEC / ITEXB_VERBOSE, in itexb_op_check and in
+  // itexb_op_delete: a non-zero word becomes ITEXB_ABORTED with the role in the message (the reference turns a failed
+  // primitive into errors::Aborted the same way, itex/core/kernels/common/quantize_op.h:409-416).
+  // Returns the word for this call's launches (allocated and zeroed on first use), or nullptr if that failed.
+  int* StatusWord(int ordinal, cudaStream_t stream);
+  // Enqueues the read-back of the word behind what Compute launched (no-op when no launch took the word, or while the
+  // stream is being captured into a graph: the word is sticky, a later call reads it).
+  void QueueStatusReadback(cudaStream_t stream);
+  // Looks at the last read-back: wait = false returns OK while the copy has not landed yet.
+  int PollStatus(bool wait);
+  void ReleaseStatus();
+
  private:
   std::string name_;
   std::mutex mu_;  // one Compute at a time per instance
+  int* status_dev_ = nullptr;
+  int* status_host_ = nullptr;      // pinned
+  cudaEvent_t status_ev_ = nullptr;
+  cudaStream_t status_stream_ = nullptr;
+  int status_ordinal_ = 0;
+  bool status_taken_ = false;       // a launch of the current Compute took the word
+  bool status_pending_ = false;     // a read-back is in flight or unread
 };
 
 using OpFactory = std::function<OpKernel*()>;
@@ -91,6 +115,8 @@ class DeviceVectorCache {
   ~DeviceVectorCache();
   DeviceVectorCache(const DeviceVectorCache&) = delete;
   DeviceVectorCache& operator=(const DeviceVectorCache&) = delete;
+  // One instance serves one device; calls may come from several streams: a hit from a stream other than the one
+  // that carried the upload first waits (on the device) for that upload's event.
   int Get(int ordinal, cudaStream_t stream, const float* host, size_t n, const float** dev);
 
  private:
@@ -100,7 +126,9 @@ class DeviceVectorCache {
     float* dev = nullptr;
     size_t cap = 0;
     cudaEvent_t ev = nullptr;
+    cudaStream_t stream = nullptr;   // the stream that carried the last upload into this slot
     bool used = false;
+    bool landed = false;             // the upload's event has been seen complete
   };
   Slot slots_[kSlots];
   int cur_ = -1;
@@ -115,7 +143,9 @@ class DeviceBuffer {
   ~DeviceBuffer() { Release(); }
   DeviceBuffer(const DeviceBuffer&) = delete;
   DeviceBuffer& operator=(const DeviceBuffer&) = delete;
-  int Ensure(int ordinal, size_t bytes);
+  // `stream`: the stream the buffer's users run on.  A buffer that has to grow (or move to another device) is returned
+  // to the allocator stream-ordered, so kernels already queued on that stream keep reading valid memory.
+  int Ensure(int ordinal, size_t bytes, cudaStream_t stream);
   void Release();
   void* data() const { return ptr_; }
   size_t size() const { return bytes_; }
@@ -124,6 +154,7 @@ class DeviceBuffer {
   void* ptr_ = nullptr;
   size_t bytes_ = 0;
   int ordinal_ = 0;
+  cudaStream_t stream_ = nullptr;
 };
 
 // ---- device-side bias preparation (bias_prep.cu) --------------------------------------

@@ -6,9 +6,19 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "op_kernel.h"
 
 namespace itexb {
+
+// One NVTX range per op call, named after the op type: what a timeline tool shows in place of the reference's
+// AnnotatedTraceMe around Compute (itex/core/utils/op_kernel.h:970-972).  NVTX 3 is header-only and does nothing
+// unless a tool has injected itself into the process.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 
 // ---- AttrMap --------------------------------------------------------------------------
 const itexb_attr_t* AttrMap::Find(const char* name) const {
@@ -132,17 +142,51 @@ DeviceVectorCache::~DeviceVectorCache() {
 
 int DeviceVectorCache::Get(int ordinal, cudaStream_t stream, const float* host, size_t n, const float** dev) {
   ITEXB_REQUIRE(n > 0, ITEXB_INVALID_ARGUMENT, "DeviceVectorCache: empty vector");
+  if (cur_ >= 0 && ordinal != ordinal_) {
+    // The instance moved to another device: nothing cached here is reachable from there.  The old device's slots are
+    // returned once its queued work is done.
+    for (Slot& s : slots_) {
+      if (s.used) ITEXB_CUDA(cudaEventSynchronize(s.ev));
+      if (s.dev) ITEXB_RETURN_IF_ERROR(itexb_rt_deallocate(ordinal_, s.dev));
+      s.dev = nullptr;
+      if (s.pinned) ITEXB_CUDA(cudaFreeHost(s.pinned));
+      s.pinned = nullptr;
+      s.cap = 0;
+      s.used = false;
+    }
+    cur_ = -1;
+    last_.clear();
+  }
   if (cur_ >= 0 && last_.size() == n && std::memcmp(last_.data(), host, n * sizeof(float)) == 0) {
-    *dev = slots_[cur_].dev;
+    Slot& hit = slots_[cur_];
+    // Another stream than the one that carried the upload: order this stream behind the upload, unless it has landed
+    // already.  A stream that is being captured into a graph may not wait on work outside the capture, so there the
+    // host waits instead (once: afterwards the event reads as complete).
+    if (hit.stream != stream && !hit.landed) {
+      RelaxedCaptureMode relaxed;
+      const cudaError_t q = cudaEventQuery(hit.ev);
+      if (q == cudaErrorNotReady) {
+        if (!IsCapturing(stream)) ITEXB_CUDA(cudaStreamWaitEvent(stream, hit.ev, 0));
+        else ITEXB_CUDA(cudaEventSynchronize(hit.ev));
+      } else {
+        ITEXB_CUDA(q);
+        hit.landed = true;
+      }
+    }
+    *dev = hit.dev;
     return ITEXB_OK;
   }
   ordinal_ = ordinal;
+  ITEXB_REQUIRE(!IsCapturing(stream), ITEXB_FAILED_PRECONDITION,
+                "a scale or range vector changed while the stream is being captured into a CUDA graph: run the op once with these "
+                "values before the capture (the upload's staging memory is reused later and cannot belong to a graph)");
   const int next = (cur_ + 1) % kSlots;
   Slot& s = slots_[next];
   if (s.used) ITEXB_CUDA(cudaEventSynchronize(s.ev));  // only if the host is 4 uploads ahead
   if (s.cap < n) {
     if (s.pinned) ITEXB_CUDA(cudaFreeHost(s.pinned));
-    if (s.dev) ITEXB_RETURN_IF_ERROR(itexb_rt_deallocate(ordinal, s.dev));
+    // kernels queued on the slot's stream four uploads ago may still read the old vector: stream-ordered free
+    if (s.dev) ITEXB_RETURN_IF_ERROR(itexb_rt_deallocate_after(ordinal, s.dev, s.stream));
     s.pinned = nullptr;
     s.dev = nullptr;
     s.cap = 0;
@@ -157,6 +201,8 @@ int DeviceVectorCache::Get(int ordinal, cudaStream_t stream, const float* host, 
   ITEXB_CUDA(cudaMemcpyAsync(s.dev, s.pinned, n * sizeof(float), cudaMemcpyHostToDevice, stream));
   ITEXB_CUDA(cudaEventRecord(s.ev, stream));
   s.used = true;
+  s.landed = false;
+  s.stream = stream;
   cur_ = next;
   last_.assign(host, host + n);
   *dev = s.dev;
@@ -164,18 +210,92 @@ int DeviceVectorCache::Get(int ordinal, cudaStream_t stream, const float* host, 
 }
 
 // ---- DeviceBuffer -----------------------------------------------------------------------
-int DeviceBuffer::Ensure(int ordinal, size_t bytes) {
-  if (ptr_ != nullptr && bytes_ >= bytes && ordinal_ == ordinal) return ITEXB_OK;
+int DeviceBuffer::Ensure(int ordinal, size_t bytes, cudaStream_t stream) {
+  if (ptr_ != nullptr && bytes_ >= bytes && ordinal_ == ordinal) {
+    stream_ = stream;
+    return ITEXB_OK;
+  }
   Release();
   ITEXB_RETURN_IF_ERROR(itexb_rt_allocate(ordinal, bytes, &ptr_));
   bytes_ = bytes;
   ordinal_ = ordinal;
+  stream_ = stream;
   return ITEXB_OK;
 }
 void DeviceBuffer::Release() {
-  if (ptr_ != nullptr) (void)itexb_rt_deallocate(ordinal_, ptr_);
+  // Work queued on the users' stream may still read the buffer (a GEMM launched by the previous Compute).
+  if (ptr_ != nullptr) (void)itexb_rt_deallocate_after(ordinal_, ptr_, stream_);
   ptr_ = nullptr;
   bytes_ = 0;
+}
+
+// ---- OpKernel: device status word -------------------------------------------------------
+int* OpKernel::StatusWord(int ordinal, cudaStream_t stream) {
+  if (status_dev_ != nullptr && status_ordinal_ != ordinal) ReleaseStatus();
+  if (status_dev_ == nullptr) {
+    // First use inside a graph capture: the zeroing below would become a graph node instead of running now.  This
+    // call goes without a status word; the instance gets one at its first Compute outside a capture.
+    if (IsCapturing(stream)) return nullptr;
+    void* d = nullptr;
+    if (itexb_rt_allocate(ordinal, sizeof(int), &d) != ITEXB_OK) return nullptr;
+    if (cudaMemsetAsync(d, 0, sizeof(int), stream) != cudaSuccess ||
+        cudaHostAlloc(reinterpret_cast<void**>(&status_host_), sizeof(int), cudaHostAllocDefault) != cudaSuccess ||
+        cudaEventCreateWithFlags(&status_ev_, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      (void)itexb_rt_deallocate_after(ordinal, d, stream);
+      if (status_host_ != nullptr) (void)cudaFreeHost(status_host_);
+      status_host_ = nullptr;
+      return nullptr;
+    }
+    *status_host_ = 0;
+    status_dev_ = static_cast<int*>(d);
+    status_ordinal_ = ordinal;
+  }
+  status_taken_ = true;
+  status_stream_ = stream;
+  return status_dev_;
+}
+
+void OpKernel::QueueStatusReadback(cudaStream_t stream) {
+  if (!status_taken_ || status_dev_ == nullptr) return;
+  status_taken_ = false;
+  if (IsCapturing(stream)) return;
+  if (cudaMemcpyAsync(status_host_, status_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream) == cudaSuccess &&
+      cudaEventRecord(status_ev_, stream) == cudaSuccess)
+    status_pending_ = true;
+  else
+    (void)cudaGetLastError();
+}
+
+int OpKernel::PollStatus(bool wait) {
+  if (!status_pending_) return ITEXB_OK;
+  RelaxedCaptureMode relaxed;  // the read-back was queued outside any capture
+  if (wait) {
+    ITEXB_CUDA(cudaEventSynchronize(status_ev_));
+  } else {
+    const cudaError_t e = cudaEventQuery(status_ev_);
+    if (e == cudaErrorNotReady) return ITEXB_OK;
+    ITEXB_CUDA(e);
+  }
+  status_pending_ = false;
+  const int code = *status_host_;
+  if (code == 0) return ITEXB_OK;
+  *status_host_ = 0;
+  (void)cudaMemsetAsync(status_dev_, 0, sizeof(int), status_stream_);  // later launches report again
+  static const char* const kRoles[] = {"", "TMA producer", "MMA issuer", "epilogue", "shared-memory alignment check"};
+  return SetError(ITEXB_ABORTED,
+                  "%s: a kernel of an earlier Compute gave up on a bounded wait (status %d, %s) and left its output incomplete",
+                  name_.c_str(), code, code >= 1 && code <= 4 ? kRoles[code] : "unknown role");
+}
+
+void OpKernel::ReleaseStatus() {
+  if (status_ev_ != nullptr) (void)cudaEventDestroy(status_ev_);
+  if (status_host_ != nullptr) (void)cudaFreeHost(status_host_);
+  if (status_dev_ != nullptr) (void)itexb_rt_deallocate_after(status_ordinal_, status_dev_, status_stream_);
+  status_ev_ = nullptr;
+  status_host_ = nullptr;
+  status_dev_ = nullptr;
+  status_pending_ = status_taken_ = false;
 }
 
 }  // namespace itexb
@@ -290,9 +410,18 @@ int itexb_op_compute(itexb_op_t* op, itexb_op_context_t* ctx) {
     return e != nullptr && std::atoll(e) != 0;
   }();
   const auto t0 = std::chrono::steady_clock::now();
-  int st = op->kernel->Compute(ctx);
-  if (st == ITEXB_OK && (verbose || std::getenv("ITEXB_SYNC_EXEC") != nullptr))
+  // A launch of an earlier Compute of this instance that gave up on a bounded wait is reported now (its read-back has
+  // landed by the time the host gets here in all but back-to-back calls; otherwise the call after this one reports it).
+  int st = op->kernel->PollStatus(false);
+  if (st == ITEXB_OK) {
+    NvtxRange range(op->kernel->name().c_str());
+    st = op->kernel->Compute(ctx);
+    op->kernel->QueueStatusReadback(AsCuda(ctx->stream));
+  }
+  if (st == ITEXB_OK && (verbose || std::getenv("ITEXB_SYNC_EXEC") != nullptr)) {
     st = CudaStatus(cudaStreamSynchronize(AsCuda(ctx->stream)), verbose ? "ITEXB_VERBOSE" : "ITEXB_SYNC_EXEC");
+    if (st == ITEXB_OK) st = op->kernel->PollStatus(true);
+  }
   if (verbose) {
     const long long ns = std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
     std::fprintf(stderr, "%s,%p,%lld\n", op->kernel->name().c_str(), static_cast<void*>(op->kernel.get()), ns);
@@ -301,7 +430,20 @@ int itexb_op_compute(itexb_op_t* op, itexb_op_context_t* ctx) {
   return st;
 }
 
-void itexb_op_delete(itexb_op_t* op) { delete op; }
+int itexb_op_check(itexb_op_t* op, int wait) {
+  ITEXB_REQUIRE(op != nullptr, ITEXB_INVALID_ARGUMENT, "op_check: op is NULL");
+  std::lock_guard<std::mutex> lock(op->kernel->mu());
+  return op->kernel->PollStatus(wait != 0);
+}
+
+void itexb_op_delete(itexb_op_t* op) {
+  if (op == nullptr) return;
+  // Last chance to learn that a launch of this instance gave up: there is no status to return, so it is written to
+  // stderr (and left in itexb_last_error for the calling thread).
+  if (op->kernel->PollStatus(true) != ITEXB_OK) std::fprintf(stderr, "itexb_op_delete: %s\n", LastError());
+  op->kernel->ReleaseStatus();
+  delete op;
+}
 
 int itexb_simple_context_create(int device_ordinal, itexb_stream_t stream, itexb_simple_context_t** c) {
   ITEXB_REQUIRE(c != nullptr, ITEXB_INVALID_ARGUMENT, "simple_context_create: NULL argument");

@@ -195,7 +195,7 @@ class QuantizedBatchMatMulOp : public OpKernel {
       if (t.dtype == ITEXB_DT_FLOAT) {
         d_mul = static_cast<const float*>(t.data);
       } else {
-        ITEXB_RETURN_IF_ERROR(mul_f32_.Ensure(ord, sizeof(float)));
+        ITEXB_RETURN_IF_ERROR(mul_f32_.Ensure(ord, sizeof(float), st));
         ITEXB_RETURN_IF_ERROR(LaunchBiasPrep(kBiasCopy, t.data, t.dtype, nullptr, nullptr, 0, nullptr, 0, 0.f,
                                              static_cast<float*>(mul_f32_.data()), 1, st));
         d_mul = static_cast<const float*>(mul_f32_.data());
@@ -224,6 +224,7 @@ class QuantizedBatchMatMulOp : public OpKernel {
 
     // ---- one GEMM launch.  A right operand shared by all batches folds the batch into the rows.
     itexb_gemm_params_t p{};
+    p.status_word = StatusWord(ord, st);
     p.a_dtype = t1_; p.b_dtype = t2_; p.out_dtype = toutput_;
     p.k = int(k); p.n = int(n);
     p.a = a_ptr; p.lda = lda;

@@ -273,7 +273,7 @@ class QuantizedConv2DOp : public OpKernel {
     // ---- filter: [co][kh*kw][c_pad], packed once when constant
     const bool hit = is_filter_const_ && packed_from_ == f.data && packed_.data() != nullptr && packed_bytes_ == size_t(co) * kp;
     if (!hit) {
-      ITEXB_RETURN_IF_ERROR(packed_.Ensure(ord, size_t(co) * kp));
+      ITEXB_RETURN_IF_ERROR(packed_.Ensure(ord, size_t(co) * kp, st));
       ITEXB_RETURN_IF_ERROR(itexb_pack_filter_hwio(f.data, packed_.data(), int(kh), int(kw), int(c), int(co), c_pad, ctx->stream));
       packed_from_ = f.data;
       packed_bytes_ = size_t(co) * kp;
@@ -291,7 +291,7 @@ class QuantizedConv2DOp : public OpKernel {
     else hostmath::ConvFloatBiasFactors(min_in, max_in, pmin_f, pmax_f, size_t(nf1), tinput_, scales, &factors);
     const bool reuse_bias = bias_valid_ && is_bias_const_ && bias_from_ == bias.data && factors == saved_factors_;
     if (has_bias_ && !reuse_bias) {
-      ITEXB_RETURN_IF_ERROR(scaled_bias_.Ensure(ord, size_t(co) * sizeof(float)));
+      ITEXB_RETURN_IF_ERROR(scaled_bias_.Ensure(ord, size_t(co) * sizeof(float), st));
       const float* d_f = nullptr;
       ITEXB_RETURN_IF_ERROR(factor_cache_.Get(ord, st, factors.data(), factors.size(), &d_f));
       ITEXB_RETURN_IF_ERROR(LaunchBiasPrep(kBiasMul, bias.data, tbias_, nullptr, d_f, int(factors.size()), nullptr, 0, 0.f,
@@ -330,6 +330,7 @@ class QuantizedConv2DOp : public OpKernel {
     }
     const size_t ws = itexb_conv2d_workspace_bytes(&p);
     if (ws > 0) ITEXB_RETURN_IF_ERROR(AllocateTemp(ctx, ws, false, &p.workspace));
+    p.status_word = StatusWord(ord, st);
     return itexb_conv2d(&p, ctx->stream);
   }
 

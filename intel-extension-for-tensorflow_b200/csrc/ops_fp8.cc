@@ -296,6 +296,7 @@ class Fp8MatmulOp : public OpKernel {
       p.ep.amax = c_amax;
       p.ep.mid_dtype = sum_dtype_ == ITEXB_DT_FLOAT ? 0 : sum_dtype_;
     }
+    p.status_word = StatusWord(ctx->device_ordinal, st);
     return itexb_gemm(&p, ctx->stream);
   }
 

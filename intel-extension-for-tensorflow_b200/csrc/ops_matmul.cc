@@ -142,6 +142,9 @@ class QuantizedMatMulOp : public OpKernel {
     is_weight_const_ = true;
     const char* wconst = flavor_ == Flavor::kFusedV1 ? "is_filter_const" : "is_weight_const";
     if (attrs.Has(wconst)) ITEXB_RETURN_IF_ERROR(attrs.GetBool(wconst, &is_weight_const_));
+    // The scaled bias is cached only for a constant bias AND a constant weight (quantized_matmul_common.h:459,637,1146).
+    is_bias_const_ = true;
+    if (attrs.Has("is_bias_const")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("is_bias_const", &is_bias_const_));
     transpose_a_ = transpose_b_ = false;
     if (attrs.Has("transpose_a")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("transpose_a", &transpose_a_));
     if (attrs.Has("transpose_b")) ITEXB_RETURN_IF_ERROR(attrs.GetBool("transpose_b", &transpose_b_));
@@ -256,7 +259,7 @@ class QuantizedMatMulOp : public OpKernel {
     } else if (cache_hit) {
       w_ptr = packed_.data();
     } else {
-      ITEXB_RETURN_IF_ERROR(packed_.Ensure(ord, size_t(n) * k_pad));
+      ITEXB_RETURN_IF_ERROR(packed_.Ensure(ord, size_t(n) * k_pad, st));
       if (transpose_b_) {
         ITEXB_CUDA(cudaMemsetAsync(packed_.data(), 0, size_t(n) * k_pad, st));
         ITEXB_CUDA(cudaMemcpy2DAsync(packed_.data(), k_pad, b.data, k, k, n, cudaMemcpyDeviceToDevice, st));
@@ -294,12 +297,14 @@ class QuantizedMatMulOp : public OpKernel {
     const float* d_scale = nullptr;
     int scale_count = 0;
     float out_scale = 1.f, post_scale = 1.f;
+    std::vector<float> scale_key;  // every value the scaled bias depends on besides the bias itself: all output scales
     const float max_in = hostmath::MaxIntOf(t1_);
     if (toutput_ != ITEXB_DT_QINT32) {
       if (flavor_ == Flavor::kWithBias) {
         out_scale = hostmath::MatMulOutputScale(min_a, max_a, pmin_b[0], pmax_b[0], toutput_, min_freezed, max_freezed);
         ITEXB_RETURN_IF_ERROR(scale_cache_.Get(ord, st, &out_scale, 1, &d_scale));
         scale_count = 1;
+        scale_key.assign(1, out_scale);
       } else {
         std::vector<float> sc;
         hostmath::FusedMatMulOutputScales(min_a, max_a, pmin_b, pmax_b, size_t(nb_min), min_first_, t1_, &sc);
@@ -309,18 +314,21 @@ class QuantizedMatMulOp : public OpKernel {
           if (act_ == ITEXB_ACT_NONE) for (float& v : sc) v = v * factor;
           else if (intended_postop_scale_) post_scale = factor;
         }
-        out_scale = sc[0] + float(sc.size());  // cache key for the scaled bias below
         ITEXB_RETURN_IF_ERROR(scale_cache_.Get(ord, st, sc.data(), sc.size(), &d_scale));
         scale_count = int(sc.size());
+        scale_key = sc;
       }
     }
 
     // ---- scaled bias (GetScaledBias), cached like the reference: constant bias and weight,
     //      and an input range within 1e-5 of the one it was computed for
-    const bool reuse_bias = bias_valid_ && is_weight_const_ && bias_from_ == bias.data && std::abs(min_a - saved_min_a_) < 1e-5f &&
-                            std::abs(max_a - saved_max_a_) < 1e-5f && saved_out_scale_ == out_scale;
+    // The weight ranges enter through scale_key (per channel) and, for qint32 outputs, through the bias factors, which
+    // are functions of the same ranges and of (min_a, max_a).
+    for (int64_t i = 0; i < nb_min; ++i) { scale_key.push_back(pmin_b[i]); scale_key.push_back(pmax_b[i]); }
+    const bool reuse_bias = bias_valid_ && is_weight_const_ && is_bias_const_ && bias_from_ == bias.data &&
+                            std::abs(min_a - saved_min_a_) < 1e-5f && std::abs(max_a - saved_max_a_) < 1e-5f && saved_scale_key_ == scale_key;
     if (has_bias_ && !reuse_bias) {
-      ITEXB_RETURN_IF_ERROR(scaled_bias_.Ensure(ord, size_t(n) * sizeof(float)));
+      ITEXB_RETURN_IF_ERROR(scaled_bias_.Ensure(ord, size_t(n) * sizeof(float), st));
       const float range_input = min_first_ ? max_a - min_a : std::max(std::abs(min_a), std::abs(max_a));
       std::vector<float> s(nb_min);
       for (int64_t i = 0; i < nb_min; ++i) {
@@ -349,7 +357,7 @@ class QuantizedMatMulOp : public OpKernel {
         }
       } else if (min_first_) {
         if (!colsum_valid_) {
-          ITEXB_RETURN_IF_ERROR(colsum_.Ensure(ord, size_t(n) * sizeof(int32_t)));
+          ITEXB_RETURN_IF_ERROR(colsum_.Ensure(ord, size_t(n) * sizeof(int32_t), st));
           if (transpose_b_) {
             // column sums of the [k,n] view = row sums of the [n,k] tensor: transpose first
             void* tmp = nullptr;
@@ -382,7 +390,7 @@ class QuantizedMatMulOp : public OpKernel {
       bias_from_ = bias.data;
       saved_min_a_ = min_a;
       saved_max_a_ = max_a;
-      saved_out_scale_ = out_scale;
+      saved_scale_key_ = scale_key;
     }
 
     // ---- the GEMM
@@ -407,6 +415,7 @@ class QuantizedMatMulOp : public OpKernel {
     p.ep.act_alpha = act_alpha_;
     p.ep.act_beta = act_beta_;
     p.ep.post_scale = post_scale;
+    p.status_word = StatusWord(ord, st);
     return itexb_gemm(&p, ctx->stream);
   }
 
@@ -418,14 +427,15 @@ class QuantizedMatMulOp : public OpKernel {
   int act_ = ITEXB_ACT_NONE;
   float act_alpha_ = 0.f, act_beta_ = 0.f;
   int t1_ = ITEXB_DT_QUINT8, t2_ = ITEXB_DT_QINT8, tbias_ = ITEXB_DT_FLOAT, toutput_ = ITEXB_DT_QINT32;
-  bool min_first_ = true, is_weight_const_ = true, transpose_a_ = false, transpose_b_ = false, literal_scaled_bias_ = true;
+  bool min_first_ = true, is_weight_const_ = true, is_bias_const_ = true, transpose_a_ = false, transpose_b_ = false, literal_scaled_bias_ = true;
   // weight cache (plays WeightCacheManager's role) and derived per-weight data
   DeviceBuffer packed_, colsum_, scaled_bias_;
   const void* packed_from_ = nullptr;
   int64_t packed_k_ = 0, packed_n_ = 0;
   bool colsum_valid_ = false, bias_valid_ = false;
   const void* bias_from_ = nullptr;
-  float saved_min_a_ = 0.f, saved_max_a_ = 0.f, saved_out_scale_ = 0.f;
+  float saved_min_a_ = 0.f, saved_max_a_ = 0.f;
+  std::vector<float> saved_scale_key_;
   DeviceVectorCache scale_cache_, bias_scale_cache_;
 };
 

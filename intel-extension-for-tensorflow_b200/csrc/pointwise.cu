@@ -15,6 +15,7 @@
 #include <cfloat>
 
 #include "common.h"
+#include "fp8_cast.h"
 
 namespace itexb {
 namespace {
@@ -457,9 +458,7 @@ __global__ void MatMulScalesDynamicKernel(const float* __restrict__ range3, cons
 }
 
 // ---- FP8 ----------------------------------------------------------------------------
-template <bool E4M3> __device__ __forceinline__ uint8_t FloatToFp8Sat(float f) {
-  return (uint8_t)__nv_cvt_float_to_fp8(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
-}
+template <bool E4M3> __device__ __forceinline__ uint8_t FloatToFp8Sat(float f) { return FloatToFp8Bits(f, E4M3); }
 template <bool E4M3> __device__ __forceinline__ float Fp8ToFloat(uint8_t b) {
   __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, E4M3 ? __NV_E4M3 : __NV_E5M2);
   return __half2float(*reinterpret_cast<__half*>(&h));

@@ -104,7 +104,8 @@ __global__ void __launch_bounds__(256) PoolSmallKernel(itexb_pool_params_t p) {
 // Larger windows (the 7 x 7 global average pooling): a block of 8 warps works on 32 consecutive units (output
 // pixel x 16 channels); warp r takes the window rows r, r+8, ... of all 32 (coalesced: the 32 lanes read 512
 // consecutive bytes of a pixel, or neighbouring pixels), eight taps of a row in flight at a time, and the eight
-// partial results meet in shared memory.  Window sums fit 16 bits for up to 257 taps (the host checks).
+// partial results meet in shared memory.  Window sums fit 16 bits for up to 257 taps of unsigned input (257 * 255 = 65535)
+// and 256 taps of signed input (256 * -128 = -32768): the host checks.
 template <bool SIGNED, bool AVG>
 __global__ void __launch_bounds__(256) PoolRowsKernel(itexb_pool_params_t p) {
   __shared__ uint32_t red[8][32][9];
@@ -204,7 +205,7 @@ extern "C" int itexb_pool2d(const itexb_pool_params_t* p, itexb_stream_t stream)
   if (p->n == 0) return ITEXB_OK;
   ITEXB_REQUIRE(p->x != nullptr && p->out != nullptr, ITEXB_INVALID_ARGUMENT, "pool2d: NULL tensor");
   const bool vec = p->c % 16 == 0 && ((reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->out)) & 15) == 0 &&
-                   (long long)p->kh * p->kw <= 257;  // 16-bit window sums
+                   (long long)p->kh * p->kw <= (IsSigned8(p->dtype) ? 256 : 257);  // 16-bit window sums: 257 * 255, 256 * -128
   const long long work = (long long)p->n * p->oh * p->ow * (vec ? p->c / 16 : p->c);
   const bool small = p->kh <= 3 && p->kw <= 3;
   const long long want_blocks = (vec && !small) ? (work + 31) / 32 : (work + 255) / 256;

@@ -64,6 +64,7 @@ class CachingAllocator {
   int Allocate(size_t bytes, void** ptr) {
     const size_t cls = SizeClass(bytes);
     std::lock_guard<std::mutex> l(mu_);
+    SweepPendingLocked();
     auto it = free_.find(cls);
     void* p = nullptr;
     if (it != free_.end() && !it->second.empty()) {
@@ -114,6 +115,31 @@ class CachingAllocator {
     return ITEXB_OK;
   }
 
+  // The block returns to the free lists only after the work queued on `stream` up to now has finished: an event is
+  // recorded and Allocate looks at it before handing the block out again.  On a capturing stream no event can be
+  // queried later, so the block waits for the next Trim (which synchronizes the device first).
+  int DeallocateAfter(void* p, cudaStream_t stream) {
+    if (p == nullptr) return ITEXB_OK;
+    std::lock_guard<std::mutex> l(mu_);
+    auto it = live_.find(p);
+    if (it == live_.end()) return SetError(ITEXB_INVALID_ARGUMENT, "deallocate: %p was not allocated by device %d", p, ordinal_);
+    Pending pd{p, it->second, nullptr};
+    if (!IsCapturing(stream)) {
+      int prev = 0;
+      const bool switched = cudaGetDevice(&prev) == cudaSuccess && prev != ordinal_ && cudaSetDevice(ordinal_) == cudaSuccess;
+      if (cudaEventCreateWithFlags(&pd.ev, cudaEventDisableTiming) != cudaSuccess || cudaEventRecord(pd.ev, stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (pd.ev != nullptr) (void)cudaEventDestroy(pd.ev);
+        pd.ev = nullptr;
+      }
+      if (switched) (void)cudaSetDevice(prev);
+    }
+    pending_.push_back(pd);
+    stats_.bytes_in_use -= int64_t(it->second);
+    live_.erase(it);
+    return ITEXB_OK;
+  }
+
   int Trim() {
     std::lock_guard<std::mutex> l(mu_);
     TrimLocked();
@@ -126,7 +152,50 @@ class CachingAllocator {
   }
 
  private:
+  struct Pending {
+    void* ptr;
+    size_t cls;
+    cudaEvent_t ev;  // nullptr: no event could be recorded; released by Trim only
+  };
+
+  // Moves the blocks whose event has completed to the free lists.
+  void SweepPendingLocked() {
+    if (pending_.empty()) return;
+    RelaxedCaptureMode relaxed;  // the events belong to work outside any capture
+    size_t keep = 0;
+    for (size_t i = 0; i < pending_.size(); ++i) {
+      Pending& pd = pending_[i];
+      bool done = false;
+      if (pd.ev != nullptr) {
+        const cudaError_t e = cudaEventQuery(pd.ev);
+        if (e == cudaSuccess) done = true;
+        else if (e != cudaErrorNotReady) (void)cudaGetLastError();
+      }
+      if (done) {
+        (void)cudaEventDestroy(pd.ev);
+        free_[pd.cls].push_back(pd.ptr);
+      } else {
+        pending_[keep++] = pd;
+      }
+    }
+    pending_.resize(keep);
+  }
+
   void TrimLocked() {
+    if (!pending_.empty()) {
+      int prev = 0;
+      const bool switched = cudaGetDevice(&prev) == cudaSuccess && prev != ordinal_ && cudaSetDevice(ordinal_) == cudaSuccess;
+      if (cudaDeviceSynchronize() == cudaSuccess) {
+        for (Pending& pd : pending_) {
+          if (pd.ev != nullptr) (void)cudaEventDestroy(pd.ev);
+          free_[pd.cls].push_back(pd.ptr);
+        }
+        pending_.clear();
+      } else {
+        (void)cudaGetLastError();
+      }
+      if (switched) (void)cudaSetDevice(prev);
+    }
     for (auto& kv : free_) {
       for (void* p : kv.second) {
         if (cudaFree(p) == cudaSuccess) stats_.bytes_reserved -= int64_t(kv.first);
@@ -139,6 +208,7 @@ class CachingAllocator {
   std::mutex mu_;
   std::map<size_t, std::vector<void*>> free_;
   std::unordered_map<void*, size_t> live_;
+  std::vector<Pending> pending_;
   itexb_allocator_stats_t stats_{};
 };
 
@@ -202,6 +272,9 @@ int itexb_rt_allocate(int ordinal, size_t bytes, void** ptr) {
   return AllocatorFor(ordinal)->Allocate(bytes, ptr);
 }
 int itexb_rt_deallocate(int ordinal, void* ptr) { return AllocatorFor(ordinal)->Deallocate(ptr); }
+int itexb_rt_deallocate_after(int ordinal, void* ptr, itexb_stream_t stream) {
+  return AllocatorFor(ordinal)->DeallocateAfter(ptr, AsCuda(stream));
+}
 int itexb_rt_host_allocate(size_t bytes, void** ptr) {
   ITEXB_REQUIRE(ptr != nullptr, ITEXB_INVALID_ARGUMENT, "host_allocate: ptr is NULL");
   ITEXB_CUDA(cudaHostAlloc(ptr, bytes ? bytes : 1, cudaHostAllocDefault));

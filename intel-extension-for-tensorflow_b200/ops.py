@@ -46,6 +46,7 @@ def _setup(lib):
     lib.itexb_op_create.argtypes = [C.c_char_p, C.POINTER(L.Attr), C.c_int, C.POINTER(C.c_void_p)]
     lib.itexb_op_compute.argtypes = [C.c_void_p, C.POINTER(L.OpContext)]
     lib.itexb_op_delete.argtypes = [C.c_void_p]
+    lib.itexb_op_check.argtypes = [C.c_void_p, C.c_int]
     lib._ops_ready = True
 
 
@@ -117,6 +118,10 @@ class Op:
         self._alloc_out_cb = L.ALLOC_OUTPUT_FN(self._allocate_output)
         self._alloc_tmp_cb = L.ALLOC_TEMP_FN(self._allocate_temp)
         self._device = None
+
+    def check(self, wait=True):
+        """Raises ItexError (ABORTED) if a kernel launched by this instance gave up on a bounded wait (itexb_op_check)."""
+        L.check(self.lib.itexb_op_check(self._h, 1 if wait else 0))
 
     def __del__(self):
         try:
@@ -205,15 +210,12 @@ class Op:
         return outs[0] if nout == 1 else tuple(outs)
 
 
-_op_cache = {}
-
-
 def _cached(op_name, attrs):
-    key = (op_name, tuple(sorted((k, tuple(v) if isinstance(v, (list, tuple)) else v) for k, v in attrs.items())))
-    op = _op_cache.get(key)
-    if op is None:
-        op = _op_cache[key] = Op(op_name, **attrs)
-    return op
+    """The functional wrappers below run one node once: every call builds its own kernel instance, as every node of a
+    graph has its own (the per-instance caches - packed constant weight, scaled bias, scale vectors - belong to one node;
+    sharing an instance between call sites with equal attrs would serve one site's constants to the other).  Code that
+    runs the same node repeatedly keeps an `Op` and calls it, which is where those caches pay."""
+    return Op(op_name, **attrs)
 
 
 def _ITEXQuantizeV2(input, min_range, max_range, T="qint8", mode="SCALED", round_mode="HALF_AWAY_FROM_ZERO",

@@ -305,15 +305,19 @@ def matmul_scaled_bias(bias, b_kn, min_a, max_a, min_b, max_b, mode: str, toutpu
 
 def epilogue(acc: np.ndarray, scale, bias, relu: bool, toutput: str,
              summand=None, sum_scale: float = 1.0) -> np.ndarray:
-    """oneDNN int8 primitive tail: f=(float)acc; f*=scale[n]; f+=bias[n]; [f+=sum_scale*summand];
-    [relu]; convert (ints: saturate + RNE; floats: cast).  Separate fp32 multiply and add."""
+    """oneDNN int8 primitive tail: f=(float)acc; f*=scale[n]; f+=bias[n]; [f=fma(sum_scale, summand, f)];
+    [relu]; convert (ints: saturate + RNE; floats: cast).  The scale multiply and the bias add are separate fp32
+    roundings; the sum post-op is ONE fused multiply-add, which is what oneDNN's kernels execute: with real oneDNN
+    (tests/golden/onednn_conv_sum.npz) the separate-rounding model is off by one on rounding ties, the fused one is
+    exact.  The fused multiply-add is formed in float64 (the product of a float and an 8- or 16-bit summand is exact
+    there, and so is the sum for all but astronomically distant exponents) and rounded once to float32."""
     f = acc.astype(np.float32)
     if scale is not None:
         f = (f * np.asarray(scale, np.float32)).astype(np.float32)
     if bias is not None:
         f = (f + np.asarray(bias, np.float32)).astype(np.float32)
     if summand is not None:
-        f = (f + (f32(sum_scale) * np.asarray(summand).astype(np.float32)).astype(np.float32)).astype(np.float32)
+        f = (np.float64(f32(sum_scale)) * np.asarray(summand).astype(np.float32).astype(np.float64) + f.astype(np.float64)).astype(np.float32)
     if relu:
         f = np.maximum(f, f32(0.0))
     if toutput == "float":
@@ -682,11 +686,13 @@ def _fp8_np(fp8_dtype: str):
 
 
 def fp8_cast_sat(f: np.ndarray, fp8_dtype: str = "E4M3") -> np.ndarray:
-    """float -> fp8 bits (uint8): RNE, saturating to ±max, NaN stays NaN
-    (itex/core/utils/float8.h:72-74 kSaturate=true, ConvertImpl::run :651-766)."""
+    """float -> fp8 bits (uint8): RNE; finite values beyond the largest finite code saturate to it; NaN stays NaN;
+    an infinite input gives the target's numeric_limits::infinity(), i.e. NaN for e4m3fn and +-inf for e5m2
+    (itex/core/utils/float8.h:72-74 kSaturate=true; ConvertImpl::run :651-766: the infinity test at :665-668
+    comes before the saturating overflow branch at :713-718; infinity() at :313-315 and :400)."""
     f = np.asarray(f, np.float32)
     m = f32(FP8_MAX[fp8_dtype])
-    c = np.clip(f, -m, m)  # clip keeps NaN
+    c = np.where(np.isinf(f), f, np.clip(f, -m, m))  # clip keeps NaN; the cast below maps inf to NaN (e4m3fn) or inf (e5m2)
     return c.astype(_fp8_np(fp8_dtype)).view(np.uint8)
 
 

@@ -198,8 +198,58 @@ def write_onednn_conv():
     np.savez_compressed(os.path.join(HERE, "onednn_conv.npz"), **out)
 
 
+def write_onednn_conv_sum():
+    """The sum post-op (the residual additions of a quantized ResNet: _ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize,
+    quantized_conv_ops.h:398-434) through real oneDNN.  Whether  f + sum_scale * summand  is one rounding or two only
+    shows on rounding ties, a few elements in ten million: a large seeded 1x1 convolution is run once, the pixels where
+    the two models disagree are found, and the fixture keeps exactly those pixels (plus as many ordinary ones) as a
+    [1,1,P,64] input, re-run through oneDNN on its own."""
+    import torch
+    rng = np.random.default_rng(20240503)
+    n, h, w, c, co = 16, 56, 56, 64, 256
+    x = rng.integers(0, 256, (n, h, w, c), dtype=np.uint8)
+    f32f = (rng.standard_normal((1, 1, c, co)) * 0.05).astype(np.float32)
+    amax = np.abs(f32f).reshape(-1, co).max(axis=0).astype(np.float32)
+    qf = np.clip(np.rint(f32f * (127.0 / amax)), -127, 127).astype(np.int8)
+    bias = (rng.standard_normal(co) * 0.1).astype(np.float32)
+    summand = rng.integers(0, 256, (n, h, w, co)).astype(np.uint8)
+    rng_in, rng_out, rng_sum = (np.float32(0.0), np.float32(12.75)), (np.float32(0.0), np.float32(37.3)), (np.float32(0.0), np.float32(5.123))
+    sc = o.conv_output_scale(rng_in[0], rng_in[1], -amax, amax, "quint8", "quint8", rng_out[0], rng_out[1])
+    bp = o.conv_scaled_bias(bias, rng_in[0], rng_in[1], -amax, amax, "quint8", "quint8", sc)
+    sum_scale = np.float32(rng_sum[1] / rng_out[1])
+    qw = torch.from_numpy(np.ascontiguousarray(qf.transpose(3, 2, 0, 1)))
+    ws, wz = torch.from_numpy(sc.copy()), torch.zeros(co, dtype=torch.int64)
+    pw = torch.ops.onednn.qconv_prepack(qw, ws, 1.0, 0, [1, 1], [0, 0], [1, 1], 1, None)
+
+    def nchw(a):
+        return torch.from_numpy(np.ascontiguousarray(a.transpose(0, 3, 1, 2))).contiguous(memory_format=torch.channels_last)
+
+    def run_sum(xa, sa):
+        y = torch.ops.onednn.qconv2d_pointwise.binary(nchw(xa), 1.0, 0, pw, ws, wz, nchw(sa), torch.from_numpy(bp), [1, 1], [0, 0], [1, 1], 1,
+                                                      1.0, 0, torch.uint8, float(sum_scale), 0, "sum", 1.0, "relu", [], "")
+        return np.ascontiguousarray(y.permute(0, 2, 3, 1).numpy())
+
+    yf = torch.ops.onednn.qconv2d_pointwise(nchw(x), 1.0, 0, pw, ws, wz, torch.from_numpy(bp), [1, 1], [0, 0], [1, 1], 1, 1.0, 0,
+                                            torch.float32, "none", [], "").permute(0, 2, 3, 1).numpy()
+    two = np.clip(np.rint(np.maximum(yf + (sum_scale * summand.astype(np.float32)).astype(np.float32), 0)), 0, 255)
+    one = np.clip(np.rint(np.maximum((np.float64(sum_scale) * summand.astype(np.float64) + yf.astype(np.float64)).astype(np.float32), 0)), 0, 255)
+    tie_pix = np.argwhere((two != one).any(axis=3))
+    assert len(tie_pix) >= 3, "no distinguishing element in the sample"
+    pick = [tuple(p) for p in tie_pix[:32]]
+    pick += [(int(a), int(b), int(d)) for a, b, d in zip(rng.integers(0, n, 32), rng.integers(0, h, 32), rng.integers(0, w, 32))]
+    xs = np.stack([x[p] for p in pick])[None, None]                 # [1,1,P,64]
+    ss = np.stack([summand[p] for p in pick])[None, None]           # [1,1,P,256]
+    y = run_sum(xs, ss)
+    full = run_sum(x, summand)
+    assert all(np.array_equal(y[0, 0, i], full[p]) for i, p in enumerate(pick))
+    np.savez_compressed(os.path.join(HERE, "onednn_conv_sum.npz"), x=xs, summand=ss, f=qf, bias=bias, min_f=-amax, max_f=amax,
+                        min_input=rng_in[0], max_input=rng_in[1], min_out=rng_out[0], max_out=rng_out[1],
+                        min_summand=rng_sum[0], max_summand=rng_sum[1], y=y, n_tie_pixels=np.int32(min(32, len(tie_pix))))
+
+
 if __name__ == "__main__":
     write_reference_kat()
     write_onednn_matmul()
     write_onednn_conv()
+    write_onednn_conv_sum()
     print("golden fixtures written to", HERE)

@@ -9,9 +9,6 @@ def modules():
     from conftest import load_package
     itex = load_package()
     ops = importlib.import_module("itex_b200.ops")
-    # Op instances cache constant weights by address (like the reference's kernels); a test must not meet an
-    # instance that an earlier test fed different weights which happened to live at the same address.
-    ops._op_cache.clear()
     return itex, importlib.import_module("itex_b200.kernels"), ops
 
 

@@ -132,3 +132,49 @@ def test_fp8_autocast_state_nests_and_restores(itex):
         assert fp8.get_fp8_recipe() is outer
     assert not fp8.is_fp8_enabled() and fp8.get_fp8_recipe() is None
     assert fp8.get_fp8_dtype(outer, fwd=True) == "E4M3" and fp8.get_fp8_dtype(outer, fwd=False) == "E5M2"
+
+
+def test_op_definitions_match_the_reference_registrations(itex, golden_dir):
+    """itexb_op_def for every registered name: the names the plugin has to define itself carry exactly the input, output
+    and attr specification strings the reference hands to TF_OpDefinitionBuilder (tests/golden/op_defs.json, extracted
+    from itex/core/ops/nn_ops.cc and fp8_ops.cc by tests/golden/make_opdef_fixture.py); the others are TensorFlow's ops."""
+    import importlib
+    import json
+    ops = importlib.import_module("itex_b200.ops")
+    lib, L = itex.load(), itex._lib
+    fixture = json.load(open(os.path.join(golden_dir, "op_defs.json")))
+    assert sorted(ops.op_list()) == json.load(open(os.path.join(golden_dir, "op_names.json")))
+    seen = 0
+    for name in ops.op_list():
+        d = L.OpDef()
+        assert lib.itexb_op_def(name.encode(), ctypes.byref(d)) == L.OK
+        got = {k: [getattr(d, k)[i].decode() for i in range(getattr(d, "num_" + k))] for k in ("inputs", "outputs", "attrs")}
+        if name in fixture["ops"]:
+            want = fixture["ops"][name]
+            assert d.defined_by_plugin == 1 and d.name.decode() == name
+            assert got == {k: want[k] for k in ("inputs", "outputs", "attrs")}, name
+            seen += 1
+        else:
+            # TensorFlow's own op (or a name the reference gives kernels but no definition): the argument names come from
+            # the twin the reference defines, for the HostMemory registration
+            assert name in fixture["defined_by_tensorflow"] and d.defined_by_plugin == 0
+            twin = {"QuantizedAvgPool": "ITEXQuantizedAvgPool", "_ITEXQuantizedAvgPool": "ITEXQuantizedAvgPool"}.get(
+                name, "_ITEX" + (name[1:] if name.startswith("_Quantized") else name))
+            if twin in fixture["ops"]:
+                assert got["inputs"] == fixture["ops"][twin]["inputs"], name
+            assert got["inputs"], name          # every kernel can name its HostMemory arguments
+    assert seen == len(fixture["ops"]) >= 40
+    # what the kernels read is what the definitions declare: every attr the quantized matmul reads exists in its definition
+    mm = fixture["ops"]["_ITEXQuantizedMatMulWithBiasAndDequantize"]
+    assert mm["inputs"][:3] == ["a: T1", "b: T2", "bias: Tbias"] and "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'" in mm["attrs"]
+    d = L.OpDef()
+    assert lib.itexb_op_def(b"NoSuchOp", ctypes.byref(d)) == L.NOT_FOUND
+
+
+def test_debug_hooks_reject_unknown_keys(itex):
+    lib, L = itex.load(), itex._lib
+    assert lib.itexb_debug_set(b"gemm_skip_kblock", ctypes.c_int64(-1)) == L.OK
+    assert lib.itexb_debug_set(b"gemm_wait_limit_cycles", ctypes.c_int64(0)) == L.OK
+    assert lib.itexb_debug_set(b"gemm_wait_limit_cycles", ctypes.c_int64(-5)) == L.INVALID_ARGUMENT
+    assert lib.itexb_debug_set(b"bogus", ctypes.c_int64(1)) == L.NOT_FOUND
+    assert lib.itexb_op_check(None, 1) == L.INVALID_ARGUMENT

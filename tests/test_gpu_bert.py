@@ -45,3 +45,41 @@ def test_encoder_nodes_match_oracle_and_graph_replay_matches_eager():
     torch.cuda.synchronize()
     np.testing.assert_array_equal(host(y_static), host(y))
     assert enc.int8_ops_per_token() == 2 * 2 * (128 * 384 + 128 * 128 + 128 * 512 + 512 * 128)
+
+
+@pytest.mark.parametrize("name,k,n,gelu", [("qkv", 1024, 3072, False), ("attn_out", 1024, 1024, False), ("ffn_up", 1024, 4096, True),
+                                           ("ffn_down", 4096, 1024, False)])
+def test_bert_large_nodes_at_full_size(name, k, n, gelu):
+    """The four int8 matmul nodes of a BERT-large layer at their real sizes (32 x 384 = 12288 tokens, hidden 1024, FFN
+    4096): dynamic per-tensor range over the whole activation, QuantizeV2 to qint8, fused int8 matmul with per-channel
+    scales, bias, (GELU,) bf16 output.  The quantized activation is compared in full, the matmul output on two 128-row
+    slabs (one straddling a tile boundary, one at the end) against the oracle."""
+    itex, K, ops = modules()
+    bert = importlib.import_module("itex_b200.bert_int8")
+    tokens = 32 * 384
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1238 + n)
+    lin = bert.Int8Linear(name, k, n, gen, torch.device("cuda"), gelu=gelu)
+    x = (torch.randn((tokens, k), generator=gen, device="cuda") * (1.5 if k == 4096 else 1.0)).to(torch.bfloat16)
+    trace = []
+    y = lin(x, trace)
+    torch.cuda.synchronize()
+    _, xin, q, range3, out = trace[0]
+    xf = host(xin).astype(np.float32)
+    qr, omin, omax = o.quantize_v2(xf, xf.min(), xf.max(), T="qint8", mode="SCALED", round_mode="HALF_TO_EVEN")
+    r3 = host(range3)
+    assert (r3[1], r3[2]) == (omin, omax)
+    np.testing.assert_array_equal(host(q), qr)
+    rw = host(lin.weight_range)
+    fused = ["BiasAdd", "GeluApproximate"] if gelu else ["BiasAdd"]
+    w_kn, bias = host(lin.w_kn), host(lin.bias)
+    for rows in (slice(4032, 4160), slice(tokens - 128, tokens)):
+        ref, _, _ = o.quantized_fused_matmul(qr[rows], w_kn, bias, omin, omax, -rw, rw, fused_ops=fused, t1="qint8", toutput="bfloat16",
+                                             scaled_bias_mode="intended")
+        got = host(out[rows])
+        if gelu:  # transcendental post-op: a result within an ulp of a bf16 rounding tie may land on the neighbour
+            np.testing.assert_allclose(got, ref, rtol=2.0 ** -7, atol=1e-6)
+            assert (got != ref).mean() < 1e-2
+        else:
+            np.testing.assert_array_equal(got, ref)
+    assert bool(torch.isfinite(y.float()).all())

@@ -328,3 +328,16 @@ def test_new_api_fused_ops():
     with pytest.raises(itex._lib.ItexError) as e:
         ops._QuantizedConv2D([X, F, B], rng4, fused_ops=["BiasAdd", "Mish"], out_type="qint32")
     assert "unsupported fusion" in str(e.value)
+
+
+def test_sum_post_op_matches_real_onednn_on_rounding_ties(golden_dir):
+    """_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize on the real-oneDNN fixture whose pixels sit on rounding ties of
+    the sum post-op: the device epilogue (one fused multiply-add for the summand) gives oneDNN's bytes."""
+    import os
+    itex, K, ops = modules()
+    d = np.load(os.path.join(golden_dir, "onednn_conv_sum.npz"))
+    op = ops.Op("_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize", Tinput="quint8", Tfilter="qint8", Tbias="float", out_type="quint8",
+                strides=[1, 1, 1, 1], padding="SAME", dilations=[1, 1, 1, 1], data_format="NHWC")
+    out, mn, mx = op(dev(d["x"]), dev(d["f"]), dev(d["bias"]), float(d["min_input"]), float(d["max_input"]), d["min_f"], d["max_f"],
+                     float(d["min_out"]), float(d["max_out"]), dev(d["summand"]), float(d["min_summand"]), float(d["max_summand"]))
+    np.testing.assert_array_equal(host(out), d["y"])

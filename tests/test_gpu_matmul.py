@@ -162,6 +162,39 @@ def test_object_cache_second_run_and_changed_range():
     assert "Matrix size-incompatible" in str(e.value)
 
 
+def test_non_const_bias_rewritten_in_place_is_not_served_from_the_cache():
+    """is_bias_const=false: the bias tensor may change between calls while its address stays (an allocator reuses it);
+    the scaled bias is then rebuilt every call, as the reference only caches when bias AND weight are constant
+    (quantized_matmul_common.h:459,637,1146).  Per-channel weight ranges: a change in a range other than element 0
+    rebuilds the cached scaled bias of a constant-bias instance too."""
+    itex, K, ops = modules()
+    x, w, bias, qa, mna, mxa, qb, mnb, mxb = _cfg1(m=64, k=128, n=192, seed=9)
+    A, B, Bi = dev(qa), dev(qb), dev(bias)
+    op = ops.Op("_ITEXQuantizedMatMulWithBiasAndDequantize", T1="quint8", T2="qint8", Tbias="float", Toutput="float",
+                input_quant_mode="MIN_FIRST", is_bias_const=False)
+    for step in range(3):
+        b_now = (bias * (1.0 + step)).astype(np.float32)
+        Bi.copy_(torch.from_numpy(b_now))                      # same address, new values
+        out = op(A, B, Bi, float(mna), float(mxa), float(mnb), float(mxb), 0.0, 0.0)
+        ref, _, _ = o.quantized_matmul_with_bias(qa, qb, b_now, mna, mxa, mnb, mxb, 0.0, 0.0, toutput="float")
+        np.testing.assert_array_equal(host(out), ref)
+    # fused flavour, per-channel ranges: only the LAST channel's range changes between the two calls
+    n = qb.shape[1]
+    rw = np.abs(w).max(axis=0).astype(np.float32)
+    qbc = np.clip(np.rint(w * (127.0 / rw)), -127, 127).astype(np.int8)
+    qs, smn, smx = o.quantize_v2(x, x.min(), x.max(), T="qint8", mode="SCALED", round_mode="HALF_TO_EVEN")
+    fop = ops.Op("_ITEXQuantizedFusedMatMulAndDequantize", T1="qint8", T2="qint8", Targs="float", Toutput="float", fused_ops=["BiasAdd"],
+                 input_quant_mode="SCALED", is_filter_const=True, is_bias_const=True, _scaled_bias_mode="literal")
+    Bc, Bi2 = dev(qbc), dev(bias)
+    for scale_last in (1.0, 3.0):
+        r = rw.copy()
+        r[-1] *= scale_last
+        out = fop(dev(qs), Bc, Bi2, float(smn), float(smx), -r, r)
+        ref, _, _ = o.quantized_fused_matmul(qs, qbc, bias, smn, smx, -r, r, fused_ops=["BiasAdd"], t1="qint8", toutput="float",
+                                             scaled_bias_mode="literal")
+        np.testing.assert_array_equal(host(out), ref)
+
+
 def test_raw_accumulators_exact_large_and_canaries():
     """int32 accumulators bit-exact (u8 x s8 and s8 x s8) at a BERT-sized shape, exact check by f64 matmul on the GPU;
     no write outside the output."""
@@ -200,7 +233,8 @@ def test_epilogue_bound_shape(n, k, summand):
     the epilogue is all there is; 64 channels from K = 256: 64-column tiles, one slice per epilogue warp and tile) with
     per-channel scale, bias, ReLU[, a u8 summand] and u8 output, three launches.
     Checked in full against the same arithmetic in separate fp32 steps on the raw accumulators (themselves exact by
-    the test above): multiply, add[, multiply-add of the summand in two roundings], clamp, round half to even."""
+    the test above): multiply, add[, ONE fused multiply-add of the summand - oneDNN's sum post-op, formed here in float64
+    where byte x float is exact - ], clamp, round half to even."""
     itex, K, ops = modules()
     L = itex._lib
     m = 200704
@@ -215,7 +249,7 @@ def test_epilogue_bound_shape(n, k, summand):
     want = raw.float() * scale
     want = want + bias
     if summand:
-        want = want + sm.float() * 0.37
+        want = (want.double() + sm.double() * float(np.float32(0.37))).float()
     want = torch.round(torch.clamp(want, 0.0, 255.0)).to(torch.uint8)
     ep = K.make_epilogue(scale=scale, bias=bias, relu=True, summand=sm, sum_scale=0.37)
     for _ in range(3):

@@ -12,13 +12,16 @@ from gpu_util import host, modules
 pytestmark = pytest.mark.gpu
 
 
-def test_every_node_matches_the_oracle_and_graph_replay_matches_eager():
+@pytest.mark.parametrize("image", [64, 224])
+def test_every_node_matches_the_oracle_and_graph_replay_matches_eager(image):
+    """image 64: a small case; image 224: the configuration's real resolution (batch 2), where the layers meet the tile
+    counts, the 256-byte-pitch stem patches and the multi-wave tile walk of the full-size graph."""
     itex, K, ops = modules()
     rn = importlib.import_module("itex_b200.resnet50")
     net = rn.ResNet50Int8(device="cuda", seed=1237, num_classes=100)
     assert 4.0e9 < net.macs_per_image(224) < 4.2e9     # from the layer table: 53 convolutions + the classifier
     assert sum(1 for _ in net.conv_nodes()) == 53
-    x = torch.randint(0, 256, (2, 64, 64, 3), dtype=torch.uint8, device="cuda", generator=torch.Generator("cuda").manual_seed(3))
+    x = torch.randint(0, 256, (2, image, image, 3), dtype=torch.uint8, device="cuda", generator=torch.Generator("cuda").manual_seed(3))
     net.forward(x, calibrate=True)
     trace = []
     logits = net.forward(x, trace=trace)

@@ -159,6 +159,25 @@ def test_conv_against_onednn(golden_dir):
                 np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-6)
 
 
+def test_conv_sum_post_op_against_onednn(golden_dir):
+    """The residual-sum convolution against real oneDNN on pixels chosen to sit on rounding ties: the restated tail
+    (scale and bias as separate roundings, the sum post-op as ONE fused multiply-add) reproduces oneDNN on all of them;
+    the model with a separately rounded product does not, which is what the fixture is for."""
+    d = np.load(os.path.join(golden_dir, "onednn_conv_sum.npz"))
+    kw = dict(out_type="quint8", relu=True, summand=d["summand"], min_summand=d["min_summand"], max_summand=d["max_summand"])
+    out, _, _ = o.quantized_conv2d(d["x"], d["f"], d["bias"], d["min_input"], d["max_input"], d["min_f"], d["max_f"], d["min_out"], d["max_out"], **kw)
+    np.testing.assert_array_equal(out, d["y"])
+    # the two-rounding model, spelled out: it must differ on every tie pixel
+    acc = o.int_conv2d_nhwc(d["x"], d["f"])
+    sc = o.conv_output_scale(d["min_input"], d["max_input"], d["min_f"], d["max_f"], "quint8", "quint8", d["min_out"], d["max_out"])
+    b = o.conv_scaled_bias(d["bias"], d["min_input"], d["max_input"], d["min_f"], d["max_f"], "quint8", "quint8", sc)
+    f = (acc.astype(np.float32) * sc + b).astype(np.float32)
+    ss = np.float32(d["max_summand"] / d["max_out"])
+    two = o.sat_rne(np.maximum((f + (ss * d["summand"].astype(np.float32)).astype(np.float32)).astype(np.float32), 0), "quint8")
+    ties = int(d["n_tie_pixels"])
+    assert ((two != d["y"]).any(axis=3)[0, 0, :ties]).all() and not (two != d["y"])[0, 0, ties:].any()
+
+
 def test_conv_reference_style_vs_fp32():
     """native_quantized_conv_test.py:33-198 pattern: random 1x6x6x4 . 3x3x4x4, SAME, SCALED
     inputs, compared with the fp32 convolution at rtol=atol=0.3."""
@@ -279,3 +298,66 @@ def test_fused_matmul_scale_rules():
     lit, _, _ = o.quantized_fused_matmul(a, w, bias, -2.0, 2.0, mnb, mxb, 0.0, 40.0, fused_ops=["BiasAdd", "Relu"], t1="qint8",
                                          toutput="quint8", scaled_bias_mode="intended", postop_scale_mode="literal")
     np.testing.assert_array_equal(lit, np.clip(np.rint(np.maximum(deq, 0)), 0, 255).astype(np.uint8))
+
+
+@pytest.mark.parametrize("fmt", ["E4M3", "E5M2"])
+def test_fp8_cast_pinned_to_the_format_definition(fmt):
+    """The oracle's FP8 cast and decode against the bit layout written out in tests/fp8_format.py (no ml_dtypes): all 256
+    codes decoded; every finite value, every tie between neighbours and its float32 neighbours, overflow, infinities and
+    NaN encoded - round to nearest even, saturation of finite overflow, infinity -> NaN (e4m3fn) / infinity (e5m2), the
+    behaviour itex/core/utils/float8.h:651-766 states."""
+    import fp8_format as F
+    t = F.table(fmt)
+    got = o.fp8_to_f32(np.arange(256, dtype=np.uint8), fmt).astype(np.float64)
+    assert np.array_equal(np.isnan(got), np.isnan(t)) and np.array_equal(got[~np.isnan(t)], t[~np.isnan(t)])
+    assert np.nanmax(np.where(np.isfinite(t), t, np.nan)) == o.FP8_MAX[fmt]
+    xs = F.probe_inputs(fmt)
+    want = F.encode_many(xs, fmt)
+    assert F.same_codes(o.fp8_cast_sat(xs, fmt), want, fmt)
+    # a few decisions spelled out by hand (e4m3: neighbours 1.0 | 1.125, 384 | 416 | 448, subnormal step 2^-9)
+    if fmt == "E4M3":
+        hand = [(1.0625, 0x38), (1.0625 + 2 ** -20, 0x39), (1.1875, 0x3A), (400.0, 0x7C), (432.0, 0x7E), (464.0, 0x7E), (1e9, 0x7E),
+                (-1e9, 0xFE), (2 ** -10, 0x00), (2 ** -10 + 2 ** -30, 0x01), (3 * 2 ** -10, 0x02), (0.0, 0x00), (-0.0, 0x80)]
+        for x, code in hand:
+            assert int(o.fp8_cast_sat(np.array([x], np.float32), fmt)[0]) == code, x
+        assert np.isnan(o.fp8_to_f32(o.fp8_cast_sat(np.array([np.inf, -np.inf], np.float32), fmt), fmt)).all()
+    else:
+        assert list(o.fp8_cast_sat(np.array([np.inf, -np.inf, 57344.0, 61440.0, 1e30], np.float32), fmt)) == [0x7C, 0xFC, 0x7B, 0x7B, 0x7B]
+
+
+def fp8_scale_hand_vectors():
+    """(amax, old scale, fp8_max, margin) -> new scale, worked by hand from _default_sf_compute,
+    itex/python/fp8/autocast.py:44-51: exp = floor(log2(fp8_max / amax)) - margin; sf = round(2^|exp|);
+    amax <= 0 or not finite keeps the old scale; exp < 0 takes the reciprocal (of whatever sf is by then)."""
+    inf, nan = float("inf"), float("nan")
+    return [
+        ((1.0, 7.0, 448.0, 0), 256.0),         # log2(448) = 8.8 -> 8
+        ((1.0, 7.0, 448.0, 2), 64.0),          # margin 2 -> exp 6
+        ((448.0, 7.0, 448.0, 0), 1.0),         # exp 0
+        ((449.0, 7.0, 448.0, 0), 0.5),         # log2(0.9978) -> floor -1 -> 1 / 2
+        ((1000.0, 7.0, 448.0, 0), 0.25),       # log2(0.448) = -1.16 -> -2 -> 1 / 4
+        ((1000.0, 7.0, 448.0, 3), 1.0 / 32),   # exp -2 - 3 = -5
+        ((3.7, 7.0, 448.0, 0), 64.0),          # 121.08 -> 6
+        ((0.0, 7.0, 448.0, 0), 7.0),           # amax 0: old scale (exp = +inf is not < 0)
+        ((-1.0, 7.0, 448.0, 0), 7.0),          # negative amax: log2 of a negative is NaN; old scale
+        ((nan, 7.0, 448.0, 0), 7.0),           # NaN: old scale, exp < 0 is false
+        ((inf, 8.0, 448.0, 0), 0.125),         # inf: old scale is selected, then exp = -inf < 0 takes its reciprocal
+        ((1e-38, 7.0, 448.0, 0), inf),         # 448 / 1e-38 overflows fp32: exp = +inf, 2^inf = inf, kept because amax is finite and > 0
+        ((1.0, 7.0, 57344.0, 0), 32768.0),     # e5m2 range: log2(57344) = 15.8
+        ((2.0 ** -20, 7.0, 448.0, 0), 2.0 ** 28),
+    ]
+
+
+def test_fp8_scale_update_hand_vectors():
+    for (amax, old, fmax, margin), want in fp8_scale_hand_vectors():
+        got = o.fp8_default_sf_compute(np.array([amax], np.float32), np.array([old], np.float32), fmax, margin)
+        assert got.dtype == np.float32 and got.shape == (1,)
+        assert float(got[0]) == want, (amax, old, fmax, margin, float(got[0]), want)
+    # history roll: row 0 zeroed, the other rows move up by one, the old row 0 lands in the last row (autocast.py:53-58)
+    h = np.arange(12, dtype=np.float32).reshape(4, 3) + 1
+    nh, sf, sfi = o.fp8_amax_and_scale_update(h, np.ones(3, np.float32), 448.0, 0, "most_recent")
+    np.testing.assert_array_equal(nh, [[0, 0, 0], [7, 8, 9], [10, 11, 12], [1, 2, 3]])
+    np.testing.assert_array_equal(sf, [256.0, 128.0, 128.0])      # amax = row 0 = 1, 2, 3
+    nh, sf, sfi = o.fp8_amax_and_scale_update(h, np.ones(3, np.float32), 448.0, 0, "max")
+    np.testing.assert_array_equal(sf, [32.0, 32.0, 32.0])         # amax = 10, 11, 12 -> 448/12 = 37.3 -> 5
+    np.testing.assert_array_equal(sfi, [1 / 32.0] * 3)

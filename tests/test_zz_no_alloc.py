@@ -33,7 +33,7 @@ def _params(L, x, fpk, out, scale, bias, n, h, w, c, kh, kw, co, stride, pad, oh
     return p
 
 
-def _run_case(itex, seed, n, h, w, c, kh, co, stride):
+def _run_case(itex, seed, n, h, w, c, kh, co, stride, first_call_on_device=False):
     lib, L = itex.load(), itex._lib
     lib.itexb_conv2d_workspace_bytes.restype = C.c_size_t
     rng = np.random.default_rng(seed)
@@ -54,8 +54,18 @@ def _run_case(itex, seed, n, h, w, c, kh, co, stride):
     L.check(lib.itexb_conv2d(C.byref(p), stream))
     out = torch.full((n, oh, ow, co), 77, dtype=torch.uint8, device="cuda")
     q = _params(L, x, fpk, out, scale, bias, n, h, w, c, kh, kh, co, stride, pad, oh, ow)  # workspace left NULL
+    torch.cuda.synchronize()
+    # "allocates nothing": neither this library's allocator nor the driver's free-memory figure may move across the call
+    st0, st1 = L.AllocatorStats(), L.AllocatorStats()
+    L.check(lib.itexb_rt_allocator_stats(0, C.byref(st0)))
+    free0 = torch.cuda.mem_get_info()[0]
     L.check(lib.itexb_conv2d_static_scratch(C.byref(q), stream))
     torch.cuda.synchronize()
+    free1 = torch.cuda.mem_get_info()[0]
+    L.check(lib.itexb_rt_allocator_stats(0, C.byref(st1)))
+    assert (st1.num_allocs, st1.bytes_in_use, st1.bytes_reserved) == (st0.num_allocs, st0.bytes_in_use, st0.bytes_reserved)
+    if not first_call_on_device:
+        assert free1 == free0, "device free memory changed across an allocation-free call"
     assert int(ref.max()) > 0
     np.testing.assert_array_equal(host(out), host(ref))  # integer output: identical bytes are the tolerance
 
@@ -63,8 +73,20 @@ def _run_case(itex, seed, n, h, w, c, kh, co, stride):
 def test_static_scratch_conv_matches_caller_scratch_conv_twice_in_a_row():
     itex, K, ops = modules()
     # channel counts that are not a multiple of 16 are the ones whose patch matrix is staged in scratch
-    _run_case(itex, 1, 2, 28, 28, 24, 3, 64, 1)   # 2*28*28 x 224 patch matrix = 0.35 MB
+    # (the very first launch of a kernel in a process may make the driver load its code: the free-memory figure is
+    # compared from the second call on)
+    _run_case(itex, 1, 2, 28, 28, 24, 3, 64, 1, first_call_on_device=True)   # 2*28*28 x 224 patch matrix = 0.35 MB
+    _run_case(itex, 1, 2, 28, 28, 24, 3, 64, 1)
     _run_case(itex, 2, 4, 32, 32, 3, 7, 48, 2)    # an RGB stem: runs over the first call's leftovers
+
+
+def test_static_scratch_rejects_bad_dimensions_as_an_argument_error():
+    itex, K, ops = modules()
+    lib, L = itex.load(), itex._lib
+    x = torch.zeros(1, dtype=torch.uint8, device="cuda")
+    p = _params(L, x, x, x, x, x, 1, 8, 8, 24, 3, 3, 64, 0, 1, 8, 8)     # stride 0
+    st = lib.itexb_conv2d_static_scratch(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == L.INVALID_ARGUMENT
 
 
 def test_static_scratch_limit_is_enforced():
