@@ -451,8 +451,17 @@ def run_fp8_linears(args, rank, world, local, dev, K):
         layers.append((layer, a, gathered, k, n))
 
     comm = torch.cuda.Stream(device=dev)
+    fused = world > 1 and args.fp8_gather == "fused"
+    pg = None
+    if fused:
+        def exchange(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+        pg = fp8.PeerGather([(m, n // world) for _, _, _, _, n in layers], torch.bfloat16, rank, world, dev, exchange)
+        layers = [(layer, a, pg.gathered(i), k, n) for i, (layer, a, _, k, n) in enumerate(layers)]
 
-    def step():
+    def step_nccl():
         # The all-gather of linear i runs on a second stream under the quantize + GEMM of linear i+1.
         main = torch.cuda.current_stream(dev)
         comm.wait_stream(main)
@@ -471,6 +480,25 @@ def run_fp8_linears(args, rank, world, local, dev, K):
                 gathered[0].copy_(y)
         main.wait_stream(comm)
 
+    def step_fused():
+        # Every GEMM's epilogue stores its shard into all ranks' gather buffers while the next tiles are computed; the
+        # 12-byte amax all-reduce stays on NCCL, on a second stream.  One publish / finish pair covers the three linears.
+        main = torch.cuda.current_stream(dev)
+        pg.begin()
+        for i, (layer, a, gathered, k, n) in enumerate(layers):
+            layer(a, gather=pg, gather_index=i)
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
+        pg.publish()
+        pg.finish()
+        main.wait_stream(comm)
+
+    step = step_fused if fused else step_nccl
+    # after finish() the gathered buffers are complete and may be read; acknowledge() tells the peers that this rank is
+    # done reading, which is what lets them store the next step's shards (issued after the consumer, outside the graph)
+    consumed = pg.acknowledge if fused else (lambda: None)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -483,6 +511,7 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     n_warm = max(args.warmup, 17, int(args.min_warmup_seconds * 600))
     for _ in range(n_warm):
         step()
+        consumed()
     barrier()
     # One CUDA graph per step (kernels and NCCL collectives): removes ~20 host-side op calls per step,
     # which otherwise bound the step once the per-GPU GEMMs shrink with the shard count.
@@ -492,10 +521,12 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     side.wait_stream(torch.cuda.current_stream(dev))
     with torch.cuda.stream(side):
         eager_step()
+        consumed()
     torch.cuda.current_stream(dev).wait_stream(side)
     barrier()
     with torch.cuda.graph(graph):
         eager_step()
+        consumed()          # the timed loop has no consumer: the step is acknowledged inside the graph
     step = graph.replay
     for _ in range(3):
         step()
@@ -511,6 +542,7 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     sampler.stop_flag.set()
     sampler.join()
     eager_step()                                            # graph replays do not pass through the library's launch counter
+    consumed()
     torch.cuda.synchronize()
     launches = (K.launch_count() - launches0) * args.steps
     barrier()
@@ -545,7 +577,11 @@ def run_fp8_linears(args, rank, world, local, dev, K):
             "vs_baseline": None, "dtype": "e4m3xe4m3->f32", "data": "synthetic",
             "config": {"workload": "fp8_llama_linears", "tokens": m, "linears_k_n": FP8_LINEARS, "delayed_scaling": "margin 0, history 16, max",
                        "output": "bfloat16 [g, M, N/g] after all-gather", "l2": "weights + activations larger than L2",
-                       "parallelism": "column-parallel x%d, NCCL all-gather of outputs" % world, "tflops": tflops},
+                       "parallelism": ("column-parallel x%d, all-gather fused into the GEMM epilogue (stores to peer memory over NVLink)" if fused
+                                       else "column-parallel x%d, NCCL all-gather of outputs") % world,
+                       "gather": "fused" if fused else ("nccl" if world > 1 else "none"), "tflops": tflops,
+                       "nvlink_bytes_sent_per_gpu_per_step": sum(m * (n // world) * 2 * (world - 1) for _, n in FP8_LINEARS) if world > 1 else 0,
+                       "peer_status": int(pg.status.item()) if fused else None},
             "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,fp8> (tcgen05.mma kind::f8f6f4)", "achieved": tflops,
                          "peak": 2.0 * peaks["bf16_tflops"] * world, "unit": "TFLOP/s", "frac": tflops / (2.0 * peaks["bf16_tflops"] * world),
                          "traffic": None, "peak_source": "2 x bf16_tflops (burst) x GPUs, whole step incl. quantize passes and all-gather"},
@@ -555,8 +591,13 @@ def run_fp8_linears(args, rank, world, local, dev, K):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_fp8_linears(layers, m)
-        return line
-    return None
+    if pg is not None:
+        status = int(pg.status.item())
+        del graph
+        pg.close(dist.barrier)
+        if status != 0:
+            raise SystemExit("bench.py: rank %d: the fused all-gather reported status %d (a bounded wait on a peer ran out)" % (rank, status))
+    return line if rank == 0 else None
 
 
 def l2_flusher(dev):
@@ -1119,6 +1160,8 @@ def main():
     ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
     ap.add_argument("--elements", type=int, default=102760448, help="elements per GPU for --workload quantize / dequantize")
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--fp8-gather", default="fused", choices=["fused", "nccl"],
+                    help="fp8_llama_linears on several GPUs: all-gather fused into the GEMM epilogue (peer stores), or NCCL's")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler runs, quick checks)")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0,

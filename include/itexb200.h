@@ -125,6 +125,31 @@ ITEXB_API int itexb_rt_block_host_for_event(itexb_event_t event);
 ITEXB_API int itexb_rt_synchronize_all_activity(int ordinal);
 ITEXB_API int itexb_rt_host_callback(itexb_stream_t stream, void (*fn)(void* arg), void* arg);
 
+/* Peer memory for multi-GPU jobs with one process per GPU (no counterpart in the reference's callback table).
+ * itexb_rt_ipc_export: a 64-byte handle of a block obtained from itexb_rt_allocate, to be sent to the other processes
+ * of the node by any host channel.  itexb_rt_ipc_open (with the opening process's own device current): maps the block
+ * into this process and enables peer access; the pointer may be stored to (and loaded from) by this process's
+ * kernels over NVLink.  itexb_rt_ipc_close unmaps it.  The exporting process must keep the block allocated while
+ * any other process has it open. */
+#define ITEXB_IPC_HANDLE_BYTES 64
+ITEXB_API int itexb_rt_ipc_export(void* dev_ptr, unsigned char handle[ITEXB_IPC_HANDLE_BYTES]);
+ITEXB_API int itexb_rt_ipc_open(const unsigned char handle[ITEXB_IPC_HANDLE_BYTES], void** dev_ptr);
+ITEXB_API int itexb_rt_ipc_close(void* dev_ptr);
+/* Completion flags of the fused all-gather.  Each GPU owns an int32 array `flags[world]` in memory its peers have
+ * opened.  The value written and waited for is  value + *value_ptr  (value_ptr optional): a step counter kept in
+ * device memory and advanced by itexb_peer_advance lets a CUDA graph that holds a whole step be replayed, its kernel
+ * arguments unchanged, with a new value every time.
+ * itexb_peer_signal (on the stream that carried the GEMM): after everything queued before it on `stream` has finished
+ * and been made visible system-wide, stores the value into flag_ptrs[i] for i in [0, n) - normally slot [my_rank] of
+ * every GPU's array.  itexb_peer_wait: one small kernel that polls local_flags[0 .. n) until each is >= the value
+ * (values only grow); the wait is bounded (about a second, or half the "gemm_wait_limit_cycles" hook) and on expiry
+ * writes 5 into *status_word (optional) and returns, so a peer that never signals costs a status, not a hang.
+ * itexb_peer_advance: *counter += 1 on the stream. */
+ITEXB_API int itexb_peer_signal(int32_t* const* flag_ptrs, int32_t n, int32_t value, const int32_t* value_ptr, itexb_stream_t stream);
+ITEXB_API int itexb_peer_wait(const int32_t* local_flags, int32_t n, int32_t value, const int32_t* value_ptr, int32_t* status_word,
+                              itexb_stream_t stream);
+ITEXB_API int itexb_peer_advance(int32_t* counter, itexb_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* 2. Kernel launches (device pointers; asynchronous on `stream`).            */
 /* ------------------------------------------------------------------------- */
@@ -271,7 +296,18 @@ typedef struct itexb_gemm_params {
    * Replaces the batched dnnl::matmul of BatchMatMulOp (itex/core/kernels/common/batch_matmul_op.h). */
   int32_t batch;
   int64_t stride_a, stride_b, stride_out;
+  /* Fused all-gather by peer stores (column-parallel linears: each GPU computes [m, n] = its column shard and every
+   * GPU needs all shards).  With num_peers > 0 the epilogue writes every finished output block not only to `out` but
+   * also, with ordinary 16-byte global stores, to the same offsets of peer_out[0 .. num_peers) - device pointers into
+   * OTHER GPUs' memory (itexb_rt_ipc_open) laid out exactly like `out` (same ldo) - while the tensor cores work on the
+   * next tile.  Nothing is ever loaded from a peer.  Needs 16-byte aligned output rows (n * element size a multiple
+   * of 16) and a single GEMM (batch <= 1); at most ITEXB_MAX_PEERS.  Completion is signalled separately
+   * (itexb_peer_signal after the GEMM on the same stream, itexb_peer_wait on the receiving side).  No counterpart in
+   * the reference, whose only collective call site is an all-reduce (itex/core/kernels/gpu/collective_ops.h:338-430). */
+  int32_t num_peers;
+  void* const* peer_out;   /* host array of num_peers device pointers */
 } itexb_gemm_params_t;
+#define ITEXB_MAX_PEERS 7
 ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
 
 /* Test hooks of the GEMM / convolution kernels' failure path; process-wide, read at every launch.  They have no

@@ -49,7 +49,7 @@ class GemmParams(C.Structure):
                 ("b_dtype", C.c_int32), ("out_dtype", C.c_int32), ("a", C.c_void_p), ("lda", C.c_int64),
                 ("b", C.c_void_p), ("ldb", C.c_int64), ("out", C.c_void_p), ("ldo", C.c_int64),
                 ("ep", Epilogue), ("status_word", C.c_void_p), ("batch", C.c_int32), ("stride_a", C.c_int64),
-                ("stride_b", C.c_int64), ("stride_out", C.c_int64)]
+                ("stride_b", C.c_int64), ("stride_out", C.c_int64), ("num_peers", C.c_int32), ("peer_out", C.POINTER(C.c_void_p))]
 
 
 class ConvParams(C.Structure):
@@ -120,6 +120,14 @@ def load():
     lib.itexb_op_check.argtypes = [C.c_void_p, C.c_int]
     lib.itexb_op_def.argtypes = [C.c_char_p, C.POINTER(OpDef)]
     lib.itexb_debug_set.argtypes = [C.c_char_p, C.c_int64]
+    lib.itexb_rt_allocate.argtypes = [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
+    lib.itexb_rt_deallocate.argtypes = [C.c_int, C.c_void_p]
+    lib.itexb_rt_ipc_export.argtypes = [C.c_void_p, C.c_char_p]
+    lib.itexb_rt_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.itexb_rt_ipc_close.argtypes = [C.c_void_p]
+    lib.itexb_peer_signal.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+    lib.itexb_peer_wait.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.itexb_peer_advance.argtypes = [C.c_void_p, C.c_void_p]
     _lib = lib
     return lib
 

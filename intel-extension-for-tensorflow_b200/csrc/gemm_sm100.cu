@@ -448,6 +448,26 @@ __device__ __noinline__ Float16 ApplyActivation16(Float16 in, int kind, float al
 }
 #undef ITEXB_ACT_CASE
 
+// Fused all-gather: the block a warp has just staged (32 rows of row_bytes, in the swizzled layout of the TMA store)
+// goes to the same place of every peer's output buffer with ordinary 16-byte global stores, four (or two) lanes per
+// row so that a row's bytes leave as one contiguous run.  Rows past m and bytes past the row's end are skipped.
+// Out of line: only multi-GPU launches execute it, and the epilogue loops keep their registers.
+__device__ __noinline__ void PushBlockToPeers(const GemmArgs& g, const uint8_t* buf, int row_bytes, long long row_first, int rows_valid,
+                                              long long col_byte0, int lane) {
+  const int row_units = row_bytes >> 4;
+  const long long pitch = g.ldo * g.out_esz;
+  const long long row_end = (long long)g.n * g.out_esz;
+  for (int u = lane; u < 32 * row_units; u += 32) {
+    const int r = u / row_units, ch = u - r * row_units;
+    const int rswz = (r / (8 / row_units)) % row_units;
+    if (r >= rows_valid || col_byte0 + ch * 16 >= row_end) continue;
+    const uint4 v = *reinterpret_cast<const uint4*>(buf + r * row_bytes + ((ch ^ rswz) << 4));
+    const long long off = (row_first + r) * pitch + col_byte0 + ch * 16;
+#pragma unroll 1
+    for (int p = 0; p < g.num_peers; ++p) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.peer_out[p]) + off) = v;
+  }
+}
+
 // What an epilogue warp needs to know; filled once per launch.
 struct EpilogueCtx {
   const float* scale;   // per-column scale vector or nullptr
@@ -815,6 +835,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             TmaStore3d(tma_out, SmemAddr(buf), col0 * esz, row0, bt);  // rows >= m and columns >= n are clipped
             TmaStoreCommit();
           }
+          if (g.num_peers > 0) PushBlockToPeers(g, buf, row_bytes, row0, min(32, g.m - row0), (long long)col0 * esz, lane);
           ++seq;
           sum_pref = sum_pref_next;
         }
@@ -853,7 +874,7 @@ template <int BN, bool F8, int CONV, int SUP>
 __global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a_tail,
-           const __grid_constant__ CUtensorMap tma_b_tail, const __grid_constant__ CUtensorMap tma_sum, const GemmArgs g) {
+           const __grid_constant__ CUtensorMap tma_b_tail, const __grid_constant__ CUtensorMap tma_sum, const __grid_constant__ GemmArgs g) {
   using C = Cfg<BN>;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((SmemAddr(smem) & 1023u) != 0) {
@@ -1351,6 +1372,10 @@ static int PickSup(int bn, bool single_only, int tiles_m, int tiles_n, int batch
 // Test hooks (itexb_debug_set): process-wide, read at every launch.
 static std::atomic<long long> g_wait_limit_cycles{0};  // 0: the default
 static std::atomic<int> g_debug_skip_kb{-1};
+long long GemmWaitLimitCycles() {
+  const long long limit = g_wait_limit_cycles.load(std::memory_order_relaxed);
+  return limit > 0 ? limit : kWaitLimitCycles;
+}
 
 int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail) {
   const CUtensorMap& tat = tail != nullptr ? tail->a : ta;  // placeholders when there is no narrow last k-block
@@ -1528,5 +1553,18 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   g.ep = p->ep;
   g.status_word = p->status_word;
   g.idesc = MakeInstrDesc(p->a_dtype, p->b_dtype, bn);
+  if (p->num_peers > 0) {
+    ITEXB_REQUIRE(p->num_peers <= ITEXB_MAX_PEERS && p->peer_out != nullptr, ITEXB_INVALID_ARGUMENT, "gemm: num_peers must be at most %d with peer_out given",
+                  ITEXB_MAX_PEERS);
+    const int esz = p->ep.raw_acc ? 4 : DtypeSize(p->out_dtype);
+    ITEXB_REQUIRE(batch == 1 && (int64_t(p->n) * esz) % 16 == 0 && (p->ldo * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p->out) & 15) == 0,
+                  ITEXB_INVALID_ARGUMENT, "gemm: the fused all-gather needs a single GEMM whose output rows are 16-byte aligned multiples of 16 bytes");
+    g.num_peers = p->num_peers;
+    for (int i = 0; i < p->num_peers; ++i) {
+      ITEXB_REQUIRE(p->peer_out[i] != nullptr && (reinterpret_cast<uintptr_t>(p->peer_out[i]) & 15) == 0, ITEXB_INVALID_ARGUMENT,
+                    "gemm: peer_out[%d] must be a 16-byte aligned device pointer", i);
+      g.peer_out[i] = p->peer_out[i];
+    }
+  }
   return LaunchGemm(ta, tb, g, bn, f8, AsCuda(stream), tail.box != 0 ? &tail : nullptr);
 }

@@ -35,6 +35,8 @@ struct GemmArgs {
   int tail_box;         // 0, or the width (64 | 32 bytes) of a narrower last k-block (set by LaunchGemm)
   int group_m;          // tile rows per rasterisation group (set by LaunchGemm)
   FastDiv div_per_batch, div_per_group, div_group_m;  // dividers of the tile walk (set by LaunchGemm)
+  int num_peers;        // fused all-gather: every output block is also stored to the same offset of peer_out[0 .. num_peers)
+  void* peer_out[ITEXB_MAX_PEERS];
   int batch;            // independent GEMMs in this launch (third coordinate of the tensor maps); 0 is read as 1
   long long batch_rows_out;  // rows of `out` (and of the summand) from one batch to the next
   unsigned long long neg_zero2;  // two fp32 -0 (set by LaunchGemm): a run-time value the assembler cannot fold

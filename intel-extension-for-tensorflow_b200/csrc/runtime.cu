@@ -433,4 +433,92 @@ int itexb_rt_host_callback(itexb_stream_t st, void (*fn)(void*), void* arg) {
   return ITEXB_OK;
 }
 
+int itexb_rt_ipc_export(void* dev_ptr, unsigned char handle[ITEXB_IPC_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == ITEXB_IPC_HANDLE_BYTES, "handle size");
+  ITEXB_REQUIRE(dev_ptr != nullptr && handle != nullptr, ITEXB_INVALID_ARGUMENT, "ipc_export: NULL argument");
+  cudaIpcMemHandle_t h;
+  ITEXB_CUDA(cudaIpcGetMemHandle(&h, dev_ptr));
+  std::memcpy(handle, &h, sizeof(h));
+  return ITEXB_OK;
+}
+int itexb_rt_ipc_open(const unsigned char handle[ITEXB_IPC_HANDLE_BYTES], void** dev_ptr) {
+  ITEXB_REQUIRE(dev_ptr != nullptr && handle != nullptr, ITEXB_INVALID_ARGUMENT, "ipc_open: NULL argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  ITEXB_CUDA(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return ITEXB_OK;
+}
+int itexb_rt_ipc_close(void* dev_ptr) {
+  if (dev_ptr != nullptr) ITEXB_CUDA(cudaIpcCloseMemHandle(dev_ptr));
+  return ITEXB_OK;
+}
+
 }  // extern "C"
+
+namespace itexb {
+namespace {
+
+struct FlagPtrs { int* p[ITEXB_MAX_PEERS + 1]; };
+
+// Everything queued before this kernel on its stream has completed; the fence makes those writes (to local and peer
+// memory) visible system-wide before the flags are.
+__global__ void PeerSignalKernel(FlagPtrs f, int n, int value, const int* value_ptr) {
+  if (value_ptr != nullptr) value += *value_ptr;
+  __threadfence_system();
+  const int i = threadIdx.x;
+  if (i < n) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f.p[i]), "r"(value) : "memory");
+  }
+}
+
+// One lane per flag; every wait is bounded.
+__global__ void PeerWaitKernel(const int* flags, int n, int value, const int* value_ptr, int* status_word, long long limit) {
+  if (value_ptr != nullptr) value += *value_ptr;
+  const int i = threadIdx.x;
+  bool ok = true;
+  if (i < n) {
+    const long long t0 = clock64();
+    for (;;) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+      if (v >= value) break;
+      if (clock64() - t0 > limit) { ok = false; break; }
+      __nanosleep(200);
+    }
+  }
+  if (!ok && status_word != nullptr) atomicCAS(status_word, 0, 5);
+  __threadfence_system();
+}
+
+}  // namespace
+long long GemmWaitLimitCycles();
+}  // namespace itexb
+
+__global__ void PeerAdvanceKernel(int* counter) { *counter += 1; }
+
+extern "C" int itexb_peer_advance(int32_t* counter, itexb_stream_t stream) {
+  ITEXB_REQUIRE(counter != nullptr, ITEXB_INVALID_ARGUMENT, "peer_advance: counter is NULL");
+  PeerAdvanceKernel<<<1, 1, 0, AsCuda(stream)>>>(counter);
+  return CheckLaunch("PeerAdvanceKernel");
+}
+
+extern "C" int itexb_peer_signal(int32_t* const* flag_ptrs, int32_t n, int32_t value, const int32_t* value_ptr, itexb_stream_t stream) {
+  ITEXB_REQUIRE(flag_ptrs != nullptr && n >= 0 && n <= ITEXB_MAX_PEERS + 1, ITEXB_INVALID_ARGUMENT, "peer_signal: bad arguments");
+  if (n == 0) return ITEXB_OK;
+  FlagPtrs f{};
+  for (int i = 0; i < n; ++i) {
+    ITEXB_REQUIRE(flag_ptrs[i] != nullptr, ITEXB_INVALID_ARGUMENT, "peer_signal: flag pointer %d is NULL", i);
+    f.p[i] = flag_ptrs[i];
+  }
+  PeerSignalKernel<<<1, 32, 0, AsCuda(stream)>>>(f, n, value, value_ptr);
+  return CheckLaunch("PeerSignalKernel");
+}
+
+extern "C" int itexb_peer_wait(const int32_t* local_flags, int32_t n, int32_t value, const int32_t* value_ptr, int32_t* status_word,
+                               itexb_stream_t stream) {
+  ITEXB_REQUIRE(local_flags != nullptr && n >= 0 && n <= 32, ITEXB_INVALID_ARGUMENT, "peer_wait: bad arguments");
+  if (n == 0) return ITEXB_OK;
+  PeerWaitKernel<<<1, 32, 0, AsCuda(stream)>>>(local_flags, n, value, value_ptr, status_word, itexb::GemmWaitLimitCycles() / 2);
+  return CheckLaunch("PeerWaitKernel");
+}
+

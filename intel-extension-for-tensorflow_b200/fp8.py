@@ -100,6 +100,140 @@ class Fp8Meta:
         self.amax_history.copy_(sd["amax_history"])
 
 
+class _DeviceBlock:
+    """A raw device allocation seen by torch through the CUDA array interface (bytes)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+def peer_gather_layout(world, shard_bytes):
+    """Byte layout of one rank's gather block.  shard_bytes: bytes of one rank's output shard for each linear served.
+    Per linear, `world` slots of that many bytes (slot r receives rank r's shard; sizes must be multiples of 256 so every
+    slot starts on the allocator's alignment), then two int32 flag rows of `world` entries - row "data": rank r's shards
+    of the current step have arrived here; row "ack": rank r has finished reading the previous step's data - then the
+    step counter and a status word.  Returns a dict of offsets; the same on every rank, so a peer's address of anything
+    is that peer's base plus the local offset."""
+    offs, off = [], 0
+    for b in shard_bytes:
+        if b <= 0 or b % 256 != 0:
+            raise ValueError("shard sizes must be positive multiples of 256 bytes, got %d" % b)
+        offs.append(off)
+        off += b * world
+    lay = {"linear": offs, "data_flags": off, "ack_flags": off + 4 * world, "counter": off + 8 * world, "status": off + 8 * world + 4}
+    lay["total"] = (off + 8 * world + 8 + 255) // 256 * 256
+    return lay
+
+
+def peer_slot_offset(layout, shard_bytes, linear, src_rank):
+    """Offset (in every rank's block) of the slot that holds `src_rank`'s shard of linear `linear`."""
+    return layout["linear"][linear] + shard_bytes[linear] * src_rank
+
+
+class PeerGather:
+    """All-gather of column-parallel outputs by peer stores: every rank owns a [world, M, N/world] buffer in memory that all
+    ranks of the node have mapped (CUDA IPC); rank r's GEMM epilogue stores its shard into slot r of EVERY rank's buffer
+    while it is being computed (itexb_gemm with peer_out), so no separate collective runs afterwards.
+
+    Protocol per step, all on the caller's stream (values are a device-side step counter, so a captured step replays):
+      begin()    counter += 1; wait until every peer has acknowledged consuming the previous step (nobody overwrites a
+                 buffer that is still being read);
+      ...GEMMs with out=local(i) and peer_out=peers(i) ...
+      publish()  make the stores visible, tell every rank "my shard of this step is in your buffer";
+      finish()   wait (bounded: a missing peer becomes a status, not a hang) until all shards have arrived here; the
+                 gathered buffers may be read from here on; acknowledge() after the last read.
+    One PeerGather serves several linears: give their shard sizes as `shard_shapes`."""
+
+    def __init__(self, shard_shapes, dtype, rank, world, device, exchange):
+        """exchange(obj) -> list of every rank's obj (e.g. torch.distributed.all_gather_object wrapped); host plumbing only."""
+        import ctypes as C
+        from . import _lib as L
+        assert 2 <= world <= 8, "PeerGather serves the GPUs of one node"
+        self.lib, self.L, self.C = L.load(), L, C
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.ordinal = self.device.index or 0
+        esz = torch.empty(0, dtype=dtype).element_size()
+        self.shapes = [tuple(sh) for sh in shard_shapes]
+        self.shard_bytes = [m * n * esz for (m, n) in self.shapes]
+        self.layout = peer_gather_layout(world, self.shard_bytes)
+        self.data_flags_off, self.ack_flags_off = self.layout["data_flags"], self.layout["ack_flags"]
+        self.counter_off, self.status_off, self.nbytes = self.layout["counter"], self.layout["status"], self.layout["total"]
+        base = C.c_void_p()
+        L.check(self.lib.itexb_rt_allocate(self.ordinal, self.nbytes, C.byref(base)))
+        self.base = base.value
+        self.block = torch.as_tensor(_DeviceBlock(self.base, self.nbytes), device=self.device)
+        self.block.zero_()
+        torch.cuda.synchronize(self.device)
+        handle = C.create_string_buffer(64)
+        L.check(self.lib.itexb_rt_ipc_export(C.c_void_p(self.base), handle))
+        handles = exchange(bytes(handle.raw))
+        self.peer_base = {}
+        for r, h in enumerate(handles):
+            if r == rank:
+                continue
+            p = C.c_void_p()
+            L.check(self.lib.itexb_rt_ipc_open(C.create_string_buffer(h, 64), C.byref(p)))
+            self.peer_base[r] = p.value
+        self.dtype = dtype
+        all_bases = [self.base if r == rank else self.peer_base[r] for r in range(world)]
+        self._data_flag_ptrs = (C.c_void_p * world)(*[b + self.data_flags_off + 4 * rank for b in all_bases])
+        self._ack_flag_ptrs = (C.c_void_p * world)(*[b + self.ack_flags_off + 4 * rank for b in all_bases])
+        exchange(0)   # every rank has opened every block before anyone stores into one
+
+    def gathered(self, i):
+        """[world, M, N/world] view of linear i's gather buffer on this rank."""
+        off, (m, n) = self.layout["linear"][i], self.shapes[i]
+        return self.block[off:off + self.shard_bytes[i] * self.world].view(self.dtype).view(self.world, m, n)
+
+    def local(self, i):
+        """This rank's own slot of linear i: the `out` of its GEMM."""
+        return self.gathered(i)[self.rank]
+
+    def peers(self, i):
+        """Addresses of this rank's slot in every other rank's buffer of linear i: the `peer_out` of its GEMM."""
+        off = peer_slot_offset(self.layout, self.shard_bytes, i, self.rank)
+        return [self.peer_base[r] + off for r in range(self.world) if r != self.rank]
+
+    @property
+    def status(self):
+        return self.block[self.status_off:self.status_off + 4].view(torch.int32)
+
+    def _stream(self):
+        return self.C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def begin(self):
+        self.L.check(self.lib.itexb_peer_advance(self.C.c_void_p(self.base + self.counter_off), self._stream()))
+        # acknowledgements carry the number of the step that was consumed: wait for (this step - 1)
+        self.L.check(self.lib.itexb_peer_wait(self.C.c_void_p(self.base + self.ack_flags_off), self.world, -1,
+                                              self.C.c_void_p(self.base + self.counter_off), self.C.c_void_p(self.base + self.status_off), self._stream()))
+
+    def publish(self):
+        self.L.check(self.lib.itexb_peer_signal(self._data_flag_ptrs, self.world, 0, self.C.c_void_p(self.base + self.counter_off), self._stream()))
+
+    def finish(self):
+        self.L.check(self.lib.itexb_peer_wait(self.C.c_void_p(self.base + self.data_flags_off), self.world, 0,
+                                              self.C.c_void_p(self.base + self.counter_off), self.C.c_void_p(self.base + self.status_off), self._stream()))
+
+    def acknowledge(self):
+        self.L.check(self.lib.itexb_peer_signal(self._ack_flag_ptrs, self.world, 0, self.C.c_void_p(self.base + self.counter_off), self._stream()))
+
+    def close(self, barrier=None):
+        """Unmaps the peers' blocks and frees this rank's; `barrier()` (a host rendezvous) makes sure no rank frees its
+        block while another still has kernels in flight that store into it."""
+        torch.cuda.synchronize(self.device)
+        if barrier is not None:
+            barrier()
+        for p in self.peer_base.values():
+            self.lib.itexb_rt_ipc_close(self.C.c_void_p(p))
+        self.peer_base = {}
+        if barrier is not None:
+            barrier()
+        if self.base:
+            self.block = None
+            self.lib.itexb_rt_deallocate(self.ordinal, self.C.c_void_p(self.base))
+            self.base = 0
+
+
 class Fp8Dense:
     """Forward of the FP8 Dense layer: y = x @ kernel (+ bias), e4m3 operands, `out_dtype` result.
 
@@ -117,13 +251,24 @@ class Fp8Dense:
         self.transpose_b = weight_layout == "nk"
         self._dummy = torch.zeros(1, dtype=torch.bfloat16 if out_dtype == "bfloat16" else torch.float32, device=kernel.device)
 
-    def __call__(self, x: torch.Tensor, update_meta: bool = True) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0) -> torch.Tensor:
+        """gather: a PeerGather (column-parallel layer, kernel kept as [N/world, K]): the product lands in slot `rank` of
+        linear `gather_index`'s buffer on every rank, stored by the GEMM's epilogue; returns this rank's slot.  The
+        arithmetic is that of the Fp8Matmul op (same kernel, same scales)."""
         m = self.meta
         if update_meta:
             m.amax_and_scale_update()
         amax_row0 = m.amax_history[0]
         xq = ops.Fp8Quantize(x, amax_row0, m.scale, 0, "E4M3")
         wq = ops.Fp8Quantize(self.kernel, amax_row0, m.scale, 1, "E4M3")
+        if gather is not None:
+            from . import _lib as L
+            assert self.transpose_b and self.bias is None and self.out_dtype == "bfloat16", "the fused gather path serves [N,K] kernels, bf16 out"
+            ep = K.make_epilogue(alpha_a=m.scale_inv[0:1], alpha_b=m.scale_inv[1:2])
+            out = gather.local(gather_index)
+            K.gemm(xq.view(torch.uint8), wq.view(torch.uint8), L.DT_BFLOAT16, a_dtype=L.DT_FP8_E4M3, b_dtype=L.DT_FP8_E4M3, ep=ep, out=out,
+                   peer_out=gather.peers(gather_index), status_word=gather.status)
+            return out
         bias = self.bias if self.bias is not None else self._dummy
         return ops.Fp8Matmul(xq, wq, bias, self._dummy, m.scale_inv, m.scale_inv, amax_row0, m.scale, 0, 1, -1,
                              transpose_b=self.transpose_b, use_bias=self.bias is not None, sum_dtype=self.out_dtype,

@@ -102,9 +102,10 @@ def make_epilogue(scale=None, bias=None, relu=False, raw_acc=False, summand=None
     return ep
 
 
-def gemm(a, b_nk, out_dtype, *, a_dtype=None, b_dtype=None, ep=None, out=None, status_word=None, n=None, k=None):
+def gemm(a, b_nk, out_dtype, *, a_dtype=None, b_dtype=None, ep=None, out=None, status_word=None, n=None, k=None, peer_out=None):
     """out[m,n] = epilogue(sum_k a[m,k] * b_nk[n,k]); a and b_nk are 8-bit CUDA tensors.  Three-dimensional a [batch,m,k]
-    and b_nk [batch,n,k] give a batched product out [batch,m,n]."""
+    and b_nk [batch,n,k] give a batched product out [batch,m,n].  peer_out: device addresses (ints) of buffers on other
+    GPUs laid out like `out`; every output block is stored there too (the fused all-gather of itexb_gemm)."""
     _require_cuda(a, b_nk, out)
     batched = a.dim() == 3
     m = a.shape[-2]
@@ -126,6 +127,9 @@ def gemm(a, b_nk, out_dtype, *, a_dtype=None, b_dtype=None, ep=None, out=None, s
         p.batch, p.stride_a, p.stride_b, p.stride_out = a.shape[0], a.stride(0), b_nk.stride(0), o.stride(0)
     p.ep = ep
     p.status_word = 0 if status_word is None else status_word.data_ptr()
+    if peer_out:
+        arr = (C.c_void_p * len(peer_out))(*[int(v) for v in peer_out])
+        p.num_peers, p.peer_out = len(peer_out), arr
     L.check(L.load().itexb_gemm(C.byref(p), stream_ptr()))
     return o
 

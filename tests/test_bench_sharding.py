@@ -8,6 +8,7 @@ import sys
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
@@ -59,3 +60,61 @@ def test_reference_arm_runs_on_rank0_only():
     assert line["impl"] == "reference" and line["unit"] == "TOPS" and line["value"] > 0
     assert line["cpu_baseline"]["kind"] in ("port", "reference") and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+def _layout_worker(rank, world, port, out):
+    """Two gloo ranks build the fused all-gather's block layout independently and exchange what they would hand to
+    their GEMMs: every (rank -> peer) store target must be the peer's own address of the same slot, slots must not
+    overlap each other or the flags, and the flag a rank signals in a peer's block must be the one that peer polls."""
+    import importlib
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from conftest import load_package
+    load_package()
+    fp8 = importlib.import_module("itex_b200.fp8")
+    shard_bytes = [4096 * (4096 // world) * 2, 4096 * (14336 // world) * 2]
+    lay = fp8.peer_gather_layout(world, shard_bytes)
+    base = 0x7F0000000000 + rank * (1 << 32)          # pretend device address of this rank's block
+    mine = {"base": base, "layout": lay,
+            "stores": {(i, peer): fp8.peer_slot_offset(lay, shard_bytes, i, rank) for i in range(2) for peer in range(world) if peer != rank},
+            "signals": lay["data_flags"] + 4 * rank}
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    ok = all(e["layout"] == lay for e in everyone)
+    spans = []
+    for i in range(2):
+        for src in range(world):
+            off = fp8.peer_slot_offset(lay, shard_bytes, i, src)
+            spans.append((off, off + shard_bytes[i]))
+    spans.sort()
+    ok = ok and all(a[1] <= b[0] for a, b in zip(spans, spans[1:])) and spans[-1][1] <= lay["data_flags"] and spans[0][0] == 0
+    ok = ok and lay["data_flags"] + 4 * world <= lay["ack_flags"] and lay["ack_flags"] + 4 * world <= lay["counter"] < lay["status"] < lay["total"]
+    # what rank s stores for linear i lands in slot s of the receiver: the receiver reads gathered[i][s] at that same offset
+    for e_rank, e in enumerate(everyone):
+        for (i, peer), off in e["stores"].items():
+            ok = ok and off == lay["linear"][i] + shard_bytes[i] * e_rank
+        ok = ok and e["signals"] == lay["data_flags"] + 4 * e_rank
+    out[rank] = ok
+    dist.destroy_process_group()
+
+
+def test_peer_gather_layout_agrees_between_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = 29600 + os.getpid() % 2000
+    procs = [ctx.Process(target=_layout_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs)
+    assert dict(out) == {0: True, 1: True}
+    import importlib
+    from conftest import load_package
+    load_package()
+    fp8 = importlib.import_module("itex_b200.fp8")
+    with pytest.raises(ValueError):
+        fp8.peer_gather_layout(2, [100])
