@@ -600,59 +600,56 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     return line if rank == 0 else None
 
 
-def l2_flusher(dev):
-    """Returns a function that overwrites a buffer larger than L2 (126 MB) on the current stream."""
-    import torch
-    buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    return lambda: buf.fill_(1)
-
-
-def timed_us(fn, reps, flush=None):
-    """Mean device time of fn() in microseconds over `reps` launches.  The launches (each preceded by flush(), if given,
-    outside its timing events) are recorded in one CUDA graph with a pair of timing events around each, so that what
-    is measured is the kernel on the device and not the host's launch path (a few microseconds of Python and driver per
-    call, more than the kernels of the small cases take).  Falls back to eager launches where events cannot be
-    recorded into a graph."""
+def timed_us(calls, reps):
+    """Mean device time per call in microseconds.  `calls` is a list of zero-argument functions that do the same work on
+    DIFFERENT input buffers; together the buffers are larger than L2 (126 MB), so cycling through them gives every
+    launch cold data without a flush kernel in between.  `reps` rounds over the list are recorded back to back in one
+    CUDA graph between a single pair of timing events: what is measured is the kernels on the device at the rate a
+    serving loop would issue them, not the host's launch path (a few microseconds of Python and driver per call, more
+    than the kernels of the small cases take).  Falls back to eager launches if the capture fails."""
     import torch
     dev = torch.cuda.current_device()
+    n = reps * len(calls)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     try:
-        ev = [(torch.cuda.Event(enable_timing=True, external=True), torch.cuda.Event(enable_timing=True, external=True)) for _ in range(reps)]
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
-            for a, b in ev:
-                if flush is not None:
-                    flush()
-                a.record()
-                fn()
-                b.record()
+            for _ in range(reps):
+                for fn in calls:
+                    fn()
         graph.replay()
         torch.cuda.synchronize()
+        t0.record()
         graph.replay()
+        t1.record()
         torch.cuda.synchronize()
-        return 1e3 * sum(a.elapsed_time(b) for a, b in ev) / reps
+        return 1e3 * t0.elapsed_time(t1) / n
     except Exception as exc:                # noqa: BLE001
         print("bench.py: graph timing unavailable (%s); timing eager launches" % type(exc).__name__, file=sys.stderr)
         torch.cuda.synchronize()
-    pairs = []
+    t0.record()
     for _ in range(reps):
-        if flush is not None:
-            flush()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        pairs.append((a, b))
+        for fn in calls:
+            fn()
+    t1.record()
     torch.cuda.synchronize()
-    return 1e3 * sum(a.elapsed_time(b) for a, b in pairs) / reps
+    return 1e3 * t0.elapsed_time(t1) / n
+
+
+def rotating_inputs(x, bytes_per_call):
+    """Copies of x, enough of them that one round over all touches more than twice the L2 capacity."""
+    import torch
+    copies = max(1, min(64, -(-(256 << 20) // max(1, bytes_per_call))))
+    return [x] + [x.clone() for _ in range(copies - 1)]
 
 
 def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
     """_ITEXQuantizeV2 (fp32 -> quint8, SCALED, HALF_TO_EVEN) or _ITEXDequantize (quint8 -> fp32, SCALED) over `count`
     elements through the op layer: achieved GB/s of the 5 algorithmic bytes per element.  The sizes are the reference
-    benchmark's (test/benchmark/test_quantize.py:55-56).  The smaller one fits in L2, so L2 is flushed before every timed
-    launch; the larger one is 4x L2 and runs back to back."""
+    benchmark's (test/benchmark/test_quantize.py:55-56).  The smaller one fits in L2, so the timed launches cycle over
+    enough copies of the input to exceed it; the larger one is 4x L2 by itself."""
     import torch
     gen = torch.Generator(device=dev)
     gen.manual_seed(shard_seed(1240, rank))
@@ -668,15 +665,14 @@ def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
         op = ops.Op("_ITEXDequantize", T="quint8", mode="SCALED", narrow_range=False, axis=-1, dtype="float")
         call = lambda t: op(t, 0.0, 6.0)
         in_b, out_b = 1, 4
-    small = count * 5 < (252 << 20)
-    flush = l2_flusher(dev) if small else None
+    xs = rotating_inputs(x, count * 5)
     for _ in range(max(args.warmup, 3)):
         y = call(x)
     torch.cuda.synchronize()
     n0 = K.launch_count()
-    reps = 20 if small else 10
-    us = timed_us(lambda: call(x), reps, flush)
+    us = timed_us([(lambda t=t: call(t)) for t in xs], max(3, 40 // len(xs)))
     launches = K.launch_count() - n0
+    del xs
     us = max_over_ranks(us, world, dev)
     # end to end: pinned host tensor in, result back to pinned host memory, every step
     xh = torch.empty(shape, dtype=x.dtype, pin_memory=True)
@@ -706,7 +702,7 @@ def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
             "dtype": "f32->u8" if which == "quantize" else "u8->f32",
             "config": {"workload": "%s_%d" % ("quantize_f32_u8" if which == "quantize" else "dequantize_u8_f32", count), "elements_per_gpu": count,
                        "op": "_ITEXQuantizeV2" if which == "quantize" else "_ITEXDequantize",
-                       "l2": "L2 flushed before every timed launch" if small else "input + output larger than L2"},
+                       "l2": "launches cycle over input copies that together exceed L2; back-to-back launches in one CUDA graph"},
             "roofline": {"bound": "hbm", "kernel": "QuantizeKernel" if which == "quantize" else "DequantizeKernel", "achieved": gbs,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
                          "algorithmic_bytes": count * 5, "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peaks["source"]},
@@ -738,8 +734,9 @@ CONV_CFG2 = dict(n=32, h=56, w=56, c=64, k=3, co=64)
 
 def run_conv_cfg2(args, rank, world, local, dev, K, ops):
     """_ITEXQuantizedConv2DWithBiasAndReluAndRequantize at [32,56,56,64] x 3x3x64x64, stride 1, SAME, u8 -> u8: the
-    fused int8 convolution of the reference's conv configuration.  Input + output + filter (12.9 MB) fit in L2, so L2 is
-    flushed before every timed launch.  Both roofline fractions are given: tensor (2 x measured bf16) and HBM."""
+    fused int8 convolution of the reference's conv configuration.  Input + output + filter (12.9 MB) fit in L2, so the timed
+    launches cycle over enough copies of the input to exceed it.  Both roofline fractions are given: tensor (2 x measured
+    bf16) and HBM."""
     import torch
     c = CONV_CFG2
     gen = torch.Generator(device=dev)
@@ -755,13 +752,14 @@ def run_conv_cfg2(args, rank, world, local, dev, K, ops):
     op = ops.Op("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", Tinput="quint8", Tfilter="qint8", Tbias="float", out_type="quint8",
                 strides=[1, 1, 1, 1], padding="SAME", dilations=[1, 1, 1, 1], data_format="NHWC", is_filter_const=True, is_bias_const=True)
     call = lambda t: op(t, qf, bias, rng_in[0], rng_in[1], -amax, amax, rng_out[0], rng_out[1])[0]
-    flush = l2_flusher(dev)
+    xs = rotating_inputs(x, 2 * int(x.numel()))
     for _ in range(max(args.warmup, 3)):
         y = call(x)
     torch.cuda.synchronize()
     n0 = K.launch_count()
-    us = timed_us(lambda: call(x), 20, flush)
+    us = timed_us([(lambda t=t: call(t)) for t in xs], 3)
     launches = K.launch_count() - n0
+    del xs
     us = max_over_ranks(us, world, dev)
     xh = torch.empty(tuple(x.shape), dtype=torch.uint8, pin_memory=True)
     xh.copy_(x.cpu())
@@ -792,7 +790,7 @@ def run_conv_cfg2(args, rank, world, local, dev, K, ops):
             "dtype": "u8xs8->s32",
             "config": {"workload": "conv_cfg2", "input": [c["n"], c["h"], c["w"], c["c"]], "filter": [c["k"], c["k"], c["c"], c["co"]],
                        "op": "_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", "stride": 1, "padding": "SAME", "output": "quint8",
-                       "l2": "L2 flushed before every timed launch"},
+                       "l2": "launches cycle over input copies that together exceed L2; back-to-back launches in one CUDA graph"},
             "roofline": {"bound": "hbm", "kernel": "GemmKernel<64,int8,im2col> (tcgen05.mma kind::i8, TMA im2col A operand)", "achieved": gbs,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": bytes_n,
                          "tensor": {"achieved": tops, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tops / (2.0 * peaks["bf16_tflops"])},

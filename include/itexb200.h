@@ -104,6 +104,7 @@ ITEXB_API int itexb_rt_trim(int ordinal);                                    /* 
 ITEXB_API int itexb_rt_create_stream(int ordinal, itexb_stream_t* stream);
 ITEXB_API int itexb_rt_destroy_stream(itexb_stream_t stream);
 ITEXB_API int itexb_rt_stream_dependency(itexb_stream_t dependent, itexb_stream_t other);
+ITEXB_API int itexb_rt_stream_device(itexb_stream_t stream, int* ordinal);     /* the device a stream belongs to (NULL stream: the current device) */
 ITEXB_API int itexb_rt_stream_status(itexb_stream_t stream);                 /* OK, or INTERNAL when the stream is in error */
 ITEXB_API int itexb_rt_create_event(itexb_event_t* event);
 ITEXB_API int itexb_rt_destroy_event(itexb_event_t event);
@@ -398,6 +399,27 @@ ITEXB_API int itexb_fp8_dequantize(const void* x, int fp8_dtype, void* y, int y_
  * Replaces functor::Fp8Gelu (itex/core/kernels/gpu/fp8/fp8_gelu_gpu.h:29-58). */
 ITEXB_API int itexb_fp8_gelu(const void* x, int x_dtype, void* y, int fp8_dtype, int64_t n, const float* scale,
                              float* amax, itexb_stream_t stream);
+/* The delayed-scaling state of one layer (amax_history [history_len, n], scale [n], scale_inv [n], device fp32) to and
+ * from one self-describing host blob of itexb_fp8_meta_blob_bytes(history_len, n) bytes: what a checkpoint holds for a
+ * layer.  In the reference the state is three non-trainable tf.Variables per direction
+ * (itex/python/transformer/base.py:60-93) that TensorFlow's own checkpointing saves.  Both calls are ordered after the
+ * work queued on `stream` and return when the copy is complete; load refuses a blob of another shape. */
+ITEXB_API size_t itexb_fp8_meta_blob_bytes(int32_t history_len, int32_t n);
+ITEXB_API int itexb_fp8_meta_save(const float* amax_history, const float* scale, const float* scale_inv, int32_t history_len, int32_t n,
+                                  void* blob, size_t blob_bytes, itexb_stream_t stream);
+ITEXB_API int itexb_fp8_meta_load(float* amax_history, float* scale, float* scale_inv, int32_t history_len, int32_t n, const void* blob,
+                                  size_t blob_bytes, itexb_stream_t stream);
+/* The FP8 cast of a gradient fused with its bias gradient, optionally through the derivative of GELU:
+ *   t = grad (gelu_inp == NULL)  or  t = dgelu(gelu_inp) * grad;   out = fp8(t * scale[0]) [rows, cols];
+ *   dbias[cols] = sum over rows of t (fp32 sums, stored in `dtype`);   amax[0] raised to max|t| (amax may be NULL).
+ * grad, gelu_inp and dbias share `dtype` (FLOAT | BFLOAT16 | HALF).  workspace: device scratch of
+ * itexb_fp8_quantize_dbias_workspace_bytes(rows, cols) bytes (per-block partial sums, added in a fixed order).
+ * Replaces functor::Fp8QuantizeDbiasFused / Fp8QuantizeDbiasDgeluFused
+ * (itex/core/kernels/gpu/fp8/fp8_quantize_fusion_gpu.h:33-300). */
+ITEXB_API size_t itexb_fp8_quantize_dbias_workspace_bytes(int64_t rows, int64_t cols);
+ITEXB_API int itexb_fp8_quantize_dbias(const void* grad, const void* gelu_inp, int dtype, void* out, int fp8_dtype, void* dbias,
+                                       int64_t rows, int64_t cols, const float* scale, float* amax, void* workspace,
+                                       itexb_stream_t stream);
 /* Layer normalisation over the columns of x [rows, cols] with an FP8 (z_dtype FP8_E4M3|FP8_E5M2: z = fp8(v * z_scale[0]),
  * z_amax[0] raised to max|v|) or real-valued (FLOAT|BFLOAT16|HALF, z_scale / z_amax unused) output;
  * v = gamma * (x - mu) * rsigma + beta, mu[rows] and rsigma[rows] = rsqrt(var + epsilon) are returned.
@@ -510,6 +532,30 @@ ITEXB_API int itexb_op_check(itexb_op_t* op, int wait);
 /* Frees the instance and its device buffers (stream-ordered behind its last launches).  A pending kernel error that
  * nobody collected is written to stderr. */
 ITEXB_API void itexb_op_delete(itexb_op_t* op);
+
+/* Graph-side routing (what a TF_InitGraph optimizer needs, free of TensorFlow types): should this stock-TensorFlow
+ * INT8 node be replaced by one of this library's `_ITEX*` ops, and with which extra attrs?  Restates the reference's
+ * rename table (itex/core/graph/native_layout/native_layout.cc:113-199), its predicate RewriteQuantize
+ * (itex/core/graph/utils/layout_utils.cc:315-354: MIN_COMBINED never; MIN_FIRST Dequantize not on the GPU; SCALED only
+ * with HALF_TO_EVEN) and its attr copiers (layout_utils.cc:471-542: data_format = "NHWC" and Tbias for the convolutions,
+ * Tbias for the matmuls, dtype and classic_asymmetric_algorithm for QuantizeV2).  new_op == NULL: leave the node as it
+ * is.  Otherwise the new node takes all attrs of the old one plus added[0 .. num_added) (an added attr replaces one of
+ * the same name).  A node that lacks an attr the rule must read (mode; out_type; Toutput) is an INVALID_ARGUMENT. */
+typedef struct itexb_rewrite_query {
+  const char* op;
+  const itexb_attr_t* attrs;
+  int32_t num_attrs;
+  int32_t on_gpu;                        /* the node is placed on this plugin's device */
+  int32_t all_consumers_are_dequantize;  /* QuantizeV2: every consumer of output 0 is a Dequantize node */
+} itexb_rewrite_query_t;
+typedef struct itexb_rewrite_result {
+  const char* new_op;
+  int32_t num_added;
+  itexb_attr_t added[4];
+} itexb_rewrite_result_t;
+ITEXB_API int itexb_rewrite_node(const itexb_rewrite_query_t* q, itexb_rewrite_result_t* r);
+/* The table itself: rule `index` renames *from to *to; NOT_FOUND past the end. */
+ITEXB_API int itexb_rewrite_rule(int index, const char** from, const char** to);
 
 /* A ready-made context over the runtime above: outputs and temps come from
  * itexb_rt_allocate / itexb_rt_host_allocate.  Outputs stay valid until

@@ -90,6 +90,15 @@ class OpDef(C.Structure):
                 ("num_outputs", C.c_int32), ("outputs", C.POINTER(C.c_char_p)), ("num_attrs", C.c_int32), ("attrs", C.POINTER(C.c_char_p))]
 
 
+class RewriteQuery(C.Structure):
+    _fields_ = [("op", C.c_char_p), ("attrs", C.POINTER(Attr)), ("num_attrs", C.c_int32), ("on_gpu", C.c_int32),
+                ("all_consumers_are_dequantize", C.c_int32)]
+
+
+class RewriteResult(C.Structure):
+    _fields_ = [("new_op", C.c_char_p), ("num_added", C.c_int32), ("added", Attr * 4)]
+
+
 ALLOC_OUTPUT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.POINTER(Tensor))
 ALLOC_TEMP_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_void_p))
 
@@ -120,6 +129,8 @@ def load():
     lib.itexb_op_check.argtypes = [C.c_void_p, C.c_int]
     lib.itexb_op_def.argtypes = [C.c_char_p, C.POINTER(OpDef)]
     lib.itexb_debug_set.argtypes = [C.c_char_p, C.c_int64]
+    lib.itexb_rewrite_node.argtypes = [C.POINTER(RewriteQuery), C.POINTER(RewriteResult)]
+    lib.itexb_rewrite_rule.argtypes = [C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p)]
     lib.itexb_rt_allocate.argtypes = [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
     lib.itexb_rt_deallocate.argtypes = [C.c_int, C.c_void_p]
     lib.itexb_rt_ipc_export.argtypes = [C.c_void_p, C.c_char_p]

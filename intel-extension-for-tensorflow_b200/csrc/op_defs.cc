@@ -94,38 +94,62 @@ const char* const k4_attrs[] = {
     "fp8_meta_index: int",
     "fp8_dtype: {'E4M3', 'E5M2'}"};
 const char* const k5_inputs[] = {
+    "grad: grad_dtype",
+    "amax: float",
+    "scale: float"};
+const char* const k5_outputs[] = {
+    "quantize_out: int8",
+    "dbias: grad_dtype"};
+const char* const k5_attrs[] = {
+    "fp8_meta_index: int",
+    "grad_dtype: {float, bfloat16, half, int8}",
+    "fp8_dtype: {'E4M3', 'E5M2'}"};
+const char* const k6_inputs[] = {
+    "grad: grad_dtype",
+    "gelu_inp: in_dtype",
+    "amax: float",
+    "scale: float"};
+const char* const k6_outputs[] = {
+    "dgelu: int8",
+    "dbias: grad_dtype"};
+const char* const k6_attrs[] = {
+    "fp8_meta_index: int",
+    "in_dtype: {float, bfloat16, half, int8}",
+    "grad_dtype: {float, bfloat16, half, int8}",
+    "fp8_dtype: {'E4M3', 'E5M2'}"};
+const char* const k7_inputs[] = {
     "input: T",
     "min_input: float",
     "max_input: float"};
-const char* const k5_outputs[] = {
+const char* const k7_outputs[] = {
     "output: T",
     "min_output: float",
     "max_output: float"};
-const char* const k5_attrs[] = {
+const char* const k7_attrs[] = {
     "T: quantizedtype",
     "ksize: list(int) >= 4",
     "strides: list(int) >= 4"};
-const char* const k6_inputs[] = {
+const char* const k8_inputs[] = {
     "input: T",
     "min_range: float",
     "max_range: float"};
-const char* const k6_outputs[] = {
+const char* const k8_outputs[] = {
     "output: dtype"};
-const char* const k6_attrs[] = {
+const char* const k8_attrs[] = {
     "T: quantizedtype",
     "mode: {'MIN_COMBINED', 'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "narrow_range: bool = false",
     "axis: int = -1",
     "dtype: {bfloat16, float} = DT_FLOAT"};
-const char* const k7_inputs[] = {
+const char* const k9_inputs[] = {
     "input: dtype",
     "min_range: float",
     "max_range: float"};
-const char* const k7_outputs[] = {
+const char* const k9_outputs[] = {
     "output: T",
     "output_min: float",
     "output_max: float"};
-const char* const k7_attrs[] = {
+const char* const k9_attrs[] = {
     "T: quantizedtype",
     "mode: {'MIN_COMBINED', 'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "round_mode: {'HALF_AWAY_FROM_ZERO', 'HALF_TO_EVEN'} = 'HALF_AWAY_FROM_ZERO'",
@@ -134,7 +158,7 @@ const char* const k7_attrs[] = {
     "ensure_minimum_range: float = 0.01",
     "dtype: {bfloat16, float} = DT_FLOAT",
     "classic_asymmetric_algorithm: bool = false"};
-const char* const k8_inputs[] = {
+const char* const k10_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
     "bias: Tbias",
@@ -144,11 +168,11 @@ const char* const k8_inputs[] = {
     "max_filter: float",
     "min_freezed_output: float",
     "max_freezed_output: float"};
-const char* const k8_outputs[] = {
+const char* const k10_outputs[] = {
     "output: out_type",
     "min_output: float",
     "max_output: float"};
-const char* const k8_attrs[] = {
+const char* const k10_attrs[] = {
     "Tinput: {bfloat16, float} = DT_FLOAT",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
@@ -164,13 +188,13 @@ const char* const k8_attrs[] = {
     "narrow_range: bool = false",
     "axis: int = -1",
     "ensure_minimum_range: float = 0.01"};
-const char* const k9_inputs[] = {
+const char* const k11_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k9_outputs[] = {
+const char* const k11_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k9_attrs[] = {
+const char* const k11_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -184,64 +208,22 @@ const char* const k9_attrs[] = {
     "fused_ops: list(string) = []",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "output_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k10_inputs[] = {
+const char* const k12_inputs[] = {
     "x: T1",
     "y: T2",
     "min_x: float",
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k10_outputs[] = {
+const char* const k12_outputs[] = {
     "output: Toutput"};
-const char* const k10_attrs[] = {
+const char* const k12_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "Toutput: {bfloat16, float} = DT_FLOAT",
     "adj_x: bool = false",
     "adj_y: bool = false",
     "is_filter_const: bool = false"};
-const char* const k11_inputs[] = {
-    "input: Tinput",
-    "filter: Tfilter",
-    "min_input: float",
-    "max_input: float",
-    "min_filter: float",
-    "max_filter: float"};
-const char* const k11_outputs[] = {
-    "output: out_type",
-    "min_output: float",
-    "max_output: float"};
-const char* const k11_attrs[] = {
-    "Tinput: quantizedtype",
-    "Tfilter: quantizedtype",
-    "out_type: quantizedtype = DT_QINT32",
-    "data_format: string = 'NHWC'",
-    "strides: list(int)",
-    "is_filter_const: bool = true",
-    "padding_list: list(int) = []",
-    "dilations: list(int) = [1, 1, 1, 1]"};
-const char* const k12_inputs[] = {
-    "input: Tinput",
-    "filter: Tfilter",
-    "min_input: float",
-    "max_input: float",
-    "min_filter: float",
-    "max_filter: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
-const char* const k12_outputs[] = {
-    "output: out_type",
-    "min_output: float",
-    "max_output: float"};
-const char* const k12_attrs[] = {
-    "Tinput: quantizedtype",
-    "Tfilter: quantizedtype",
-    "out_type: quantizedtype = DT_QINT32",
-    "data_format: string = 'NHWC'",
-    "strides: list(int)",
-    "is_filter_const: bool = true",
-    "padding_list: list(int) = []",
-    "dilations: list(int) = [1, 1, 1, 1]"};
 const char* const k13_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
@@ -263,12 +245,54 @@ const char* const k13_attrs[] = {
     "padding_list: list(int) = []",
     "dilations: list(int) = [1, 1, 1, 1]"};
 const char* const k14_inputs[] = {
+    "input: Tinput",
+    "filter: Tfilter",
+    "min_input: float",
+    "max_input: float",
+    "min_filter: float",
+    "max_filter: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k14_outputs[] = {
+    "output: out_type",
+    "min_output: float",
+    "max_output: float"};
+const char* const k14_attrs[] = {
+    "Tinput: quantizedtype",
+    "Tfilter: quantizedtype",
+    "out_type: quantizedtype = DT_QINT32",
+    "data_format: string = 'NHWC'",
+    "strides: list(int)",
+    "is_filter_const: bool = true",
+    "padding_list: list(int) = []",
+    "dilations: list(int) = [1, 1, 1, 1]"};
+const char* const k15_inputs[] = {
+    "input: Tinput",
+    "filter: Tfilter",
+    "min_input: float",
+    "max_input: float",
+    "min_filter: float",
+    "max_filter: float"};
+const char* const k15_outputs[] = {
+    "output: out_type",
+    "min_output: float",
+    "max_output: float"};
+const char* const k15_attrs[] = {
+    "Tinput: quantizedtype",
+    "Tfilter: quantizedtype",
+    "out_type: quantizedtype = DT_QINT32",
+    "data_format: string = 'NHWC'",
+    "strides: list(int)",
+    "is_filter_const: bool = true",
+    "padding_list: list(int) = []",
+    "dilations: list(int) = [1, 1, 1, 1]"};
+const char* const k16_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k14_outputs[] = {
+const char* const k16_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k14_attrs[] = {
+const char* const k16_attrs[] = {
     "Tinput: quantizedtype = DT_QUINT8",
     "Tfilter: quantizedtype = DT_QINT8",
     "Tbias: {float, qint32} = DT_QINT32",
@@ -285,60 +309,14 @@ const char* const k14_attrs[] = {
     "dilations: list(int) = [1, 1, 1, 1]",
     "fused_ops: list(string) = []",
     "alpha: float = 0.0"};
-const char* const k15_inputs[] = {
-    "input: Tinput",
-    "filter: Tfilter",
-    "bias: float",
-    "min_input: float",
-    "max_input: float",
-    "min_filter: float",
-    "max_filter: float"};
-const char* const k15_outputs[] = {
-    "output: out_type",
-    "min_output: float",
-    "max_output: float"};
-const char* const k15_attrs[] = {
-    "Tinput: quantizedtype",
-    "Tfilter: quantizedtype",
-    "out_type: quantizedtype = DT_QINT32",
-    "data_format: string = 'NHWC'",
-    "strides: list(int)",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "padding_list: list(int) = []",
-    "dilations: list(int) = [1, 1, 1, 1]"};
-const char* const k16_inputs[] = {
-    "input: Tinput",
-    "filter: Tfilter",
-    "bias: float",
-    "min_input: float",
-    "max_input: float",
-    "min_filter: float",
-    "max_filter: float"};
-const char* const k16_outputs[] = {
-    "output: out_type",
-    "min_output: float",
-    "max_output: float"};
-const char* const k16_attrs[] = {
-    "Tinput: quantizedtype",
-    "Tfilter: quantizedtype",
-    "out_type: quantizedtype = DT_QINT32",
-    "data_format: string = 'NHWC'",
-    "strides: list(int)",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "padding_list: list(int) = []",
-    "dilations: list(int) = [1, 1, 1, 1]"};
 const char* const k17_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
-    "bias: Tbias",
+    "bias: float",
     "min_input: float",
     "max_input: float",
     "min_filter: float",
-    "max_filter: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_filter: float"};
 const char* const k17_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -346,7 +324,6 @@ const char* const k17_outputs[] = {
 const char* const k17_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
-    "Tbias: {float, qint32}",
     "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
@@ -357,13 +334,11 @@ const char* const k17_attrs[] = {
 const char* const k18_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
-    "bias: Tbias",
+    "bias: float",
     "min_input: float",
     "max_input: float",
     "min_filter: float",
-    "max_filter: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_filter: float"};
 const char* const k18_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -371,7 +346,6 @@ const char* const k18_outputs[] = {
 const char* const k18_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
-    "Tbias: {float, qint32}",
     "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
@@ -388,10 +362,7 @@ const char* const k19_inputs[] = {
     "min_filter: float",
     "max_filter: float",
     "min_freezed_output: float",
-    "max_freezed_output: float",
-    "summand: Tsummand",
-    "min_summand: float",
-    "max_summand: float"};
+    "max_freezed_output: float"};
 const char* const k19_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -400,7 +371,6 @@ const char* const k19_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
-    "Tsummand: quantizedtype",
     "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
@@ -417,10 +387,7 @@ const char* const k20_inputs[] = {
     "min_filter: float",
     "max_filter: float",
     "min_freezed_output: float",
-    "max_freezed_output: float",
-    "summand: Tsummand",
-    "min_summand: float",
-    "max_summand: float"};
+    "max_freezed_output: float"};
 const char* const k20_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -429,7 +396,6 @@ const char* const k20_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
-    "Tsummand: quantizedtype",
     "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
@@ -446,14 +412,20 @@ const char* const k21_inputs[] = {
     "min_filter: float",
     "max_filter: float",
     "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_freezed_output: float",
+    "summand: Tsummand",
+    "min_summand: float",
+    "max_summand: float"};
 const char* const k21_outputs[] = {
-    "output: out_type"};
+    "output: out_type",
+    "min_output: float",
+    "max_output: float"};
 const char* const k21_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
-    "out_type: {bfloat16, half} = DT_HALF",
+    "Tsummand: quantizedtype",
+    "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
     "is_filter_const: bool = true",
@@ -469,10 +441,62 @@ const char* const k22_inputs[] = {
     "min_filter: float",
     "max_filter: float",
     "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_freezed_output: float",
+    "summand: Tsummand",
+    "min_summand: float",
+    "max_summand: float"};
 const char* const k22_outputs[] = {
-    "output: out_type"};
+    "output: out_type",
+    "min_output: float",
+    "max_output: float"};
 const char* const k22_attrs[] = {
+    "Tinput: quantizedtype",
+    "Tfilter: quantizedtype",
+    "Tbias: {float, qint32}",
+    "Tsummand: quantizedtype",
+    "out_type: quantizedtype = DT_QINT32",
+    "data_format: string = 'NHWC'",
+    "strides: list(int)",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "padding_list: list(int) = []",
+    "dilations: list(int) = [1, 1, 1, 1]"};
+const char* const k23_inputs[] = {
+    "input: Tinput",
+    "filter: Tfilter",
+    "bias: Tbias",
+    "min_input: float",
+    "max_input: float",
+    "min_filter: float",
+    "max_filter: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k23_outputs[] = {
+    "output: out_type"};
+const char* const k23_attrs[] = {
+    "Tinput: quantizedtype",
+    "Tfilter: quantizedtype",
+    "Tbias: {float, qint32}",
+    "out_type: {bfloat16, half} = DT_HALF",
+    "data_format: string = 'NHWC'",
+    "strides: list(int)",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "padding_list: list(int) = []",
+    "dilations: list(int) = [1, 1, 1, 1]"};
+const char* const k24_inputs[] = {
+    "input: Tinput",
+    "filter: Tfilter",
+    "bias: Tbias",
+    "min_input: float",
+    "max_input: float",
+    "min_filter: float",
+    "max_filter: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k24_outputs[] = {
+    "output: out_type"};
+const char* const k24_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
@@ -483,7 +507,7 @@ const char* const k22_attrs[] = {
     "is_bias_const: bool = true",
     "padding_list: list(int) = []",
     "dilations: list(int) = [1, 1, 1, 1]"};
-const char* const k23_inputs[] = {
+const char* const k25_inputs[] = {
     "x: T1",
     "y: T2",
     "args: num_args * T",
@@ -491,9 +515,9 @@ const char* const k23_inputs[] = {
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k23_outputs[] = {
+const char* const k25_outputs[] = {
     "output: Toutput"};
-const char* const k23_attrs[] = {
+const char* const k25_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "T: {bfloat16, float} = DT_FLOAT",
@@ -503,58 +527,6 @@ const char* const k23_attrs[] = {
     "num_args: int >= 0",
     "fused_ops: list(string) = []",
     "is_filter_const: bool = false"};
-const char* const k24_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "args: num_args * Targs",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float"};
-const char* const k24_outputs[] = {
-    "product: Toutput",
-    "min_product: float",
-    "max_product: float"};
-const char* const k24_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "num_args: int >= 0",
-    "Targs: {bfloat16, half, float, quantizedtype}",
-    "Toutput: quantizedtype",
-    "T: numbertype",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "fused_ops: list(string) = []",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "epsilon: float = 0.0001",
-    "leakyrelu_alpha: float = 0.2",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k25_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "args: num_args * Targs",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float"};
-const char* const k25_outputs[] = {
-    "product: Toutput"};
-const char* const k25_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "num_args: int >= 0",
-    "Targs: {bfloat16, half, float, quantizedtype}",
-    "Toutput: {bfloat16, half, float} = DT_FLOAT",
-    "T: numbertype",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "fused_ops: list(string) = []",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "epsilon: float = 0.0001",
-    "leakyrelu_alpha: float = 0.2",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
 const char* const k26_inputs[] = {
     "a: T1",
     "b: T2",
@@ -562,9 +534,7 @@ const char* const k26_inputs[] = {
     "min_a: float",
     "max_a: float",
     "min_b: float",
-    "max_b: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_b: float"};
 const char* const k26_outputs[] = {
     "product: Toutput",
     "min_product: float",
@@ -585,12 +555,66 @@ const char* const k26_attrs[] = {
     "leakyrelu_alpha: float = 0.2",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
 const char* const k27_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "args: num_args * Targs",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float"};
+const char* const k27_outputs[] = {
+    "product: Toutput"};
+const char* const k27_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "num_args: int >= 0",
+    "Targs: {bfloat16, half, float, quantizedtype}",
+    "Toutput: {bfloat16, half, float} = DT_FLOAT",
+    "T: numbertype",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "fused_ops: list(string) = []",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "epsilon: float = 0.0001",
+    "leakyrelu_alpha: float = 0.2",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
+const char* const k28_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "args: num_args * Targs",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k28_outputs[] = {
+    "product: Toutput",
+    "min_product: float",
+    "max_product: float"};
+const char* const k28_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "num_args: int >= 0",
+    "Targs: {bfloat16, half, float, quantizedtype}",
+    "Toutput: quantizedtype",
+    "T: numbertype",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "fused_ops: list(string) = []",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "epsilon: float = 0.0001",
+    "leakyrelu_alpha: float = 0.2",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
+const char* const k29_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k27_outputs[] = {
+const char* const k29_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k27_attrs[] = {
+const char* const k29_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -608,52 +632,10 @@ const char* const k27_attrs[] = {
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "output_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "leakyrelu_alpha: float = 0.2"};
-const char* const k28_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "bias: Tbias",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float"};
-const char* const k28_outputs[] = {
-    "out: Toutput",
-    "min_out: float",
-    "max_out: float"};
-const char* const k28_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "Tbias: {float, qint32}",
-    "Toutput: quantizedtype = DT_QINT32",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
-    "is_weight_const: bool = true"};
-const char* const k29_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "bias: Tbias",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
-const char* const k29_outputs[] = {
-    "out: Toutput"};
-const char* const k29_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "Tbias: {float, bfloat16, qint32}",
-    "Toutput: {float, bfloat16}",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
-    "is_weight_const: bool = true"};
 const char* const k30_inputs[] = {
     "a: T1",
     "b: T2",
-    "bias: float",
+    "bias: Tbias",
     "min_a: float",
     "max_a: float",
     "min_b: float",
@@ -665,6 +647,7 @@ const char* const k30_outputs[] = {
 const char* const k30_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
+    "Tbias: {float, qint32}",
     "Toutput: quantizedtype = DT_QINT32",
     "transpose_a: bool = false",
     "transpose_b: bool = false",
@@ -681,19 +664,37 @@ const char* const k31_inputs[] = {
     "min_freezed_output: float",
     "max_freezed_output: float"};
 const char* const k31_outputs[] = {
-    "out: Toutput",
-    "min_out: float",
-    "max_out: float"};
+    "out: Toutput"};
 const char* const k31_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
-    "Tbias: {float, qint32}",
-    "Toutput: quantizedtype = DT_QUINT8",
+    "Tbias: {float, bfloat16, qint32}",
+    "Toutput: {float, bfloat16}",
     "transpose_a: bool = false",
     "transpose_b: bool = false",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
     "is_weight_const: bool = true"};
 const char* const k32_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "bias: float",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float"};
+const char* const k32_outputs[] = {
+    "out: Toutput",
+    "min_out: float",
+    "max_out: float"};
+const char* const k32_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "Toutput: quantizedtype = DT_QINT32",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
+    "is_weight_const: bool = true"};
+const char* const k33_inputs[] = {
     "a: T1",
     "b: T2",
     "bias: Tbias",
@@ -703,11 +704,11 @@ const char* const k32_inputs[] = {
     "max_b: float",
     "min_freezed_output: float",
     "max_freezed_output: float"};
-const char* const k32_outputs[] = {
+const char* const k33_outputs[] = {
     "out: Toutput",
     "min_out: float",
     "max_out: float"};
-const char* const k32_attrs[] = {
+const char* const k33_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "Tbias: {float, qint32}",
@@ -716,25 +717,48 @@ const char* const k32_attrs[] = {
     "transpose_b: bool = false",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
     "is_weight_const: bool = true"};
-const char* const k33_inputs[] = {
+const char* const k34_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "bias: Tbias",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k34_outputs[] = {
+    "out: Toutput",
+    "min_out: float",
+    "max_out: float"};
+const char* const k34_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "Tbias: {float, qint32}",
+    "Toutput: quantizedtype = DT_QUINT8",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
+    "is_weight_const: bool = true"};
+const char* const k35_inputs[] = {
     "input: T",
     "min_input: float",
     "max_input: float"};
-const char* const k33_outputs[] = {
+const char* const k35_outputs[] = {
     "output: T",
     "min_output: float",
     "max_output: float"};
-const char* const k33_attrs[] = {
+const char* const k35_attrs[] = {
     "T: quantizedtype",
     "ksize: list(int) >= 4",
     "strides: list(int) >= 4"};
-const char* const k34_inputs[] = {
+const char* const k36_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k34_outputs[] = {
+const char* const k36_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k34_attrs[] = {
+const char* const k36_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -748,29 +772,29 @@ const char* const k34_attrs[] = {
     "fused_ops: list(string) = []",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "output_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k35_inputs[] = {
+const char* const k37_inputs[] = {
     "x: T1",
     "y: T2",
     "min_x: float",
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k35_outputs[] = {
+const char* const k37_outputs[] = {
     "output: Toutput"};
-const char* const k35_attrs[] = {
+const char* const k37_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "Toutput: {bfloat16, half, float} = DT_FLOAT",
     "adj_x: bool = false",
     "adj_y: bool = false",
     "is_filter_const: bool = false"};
-const char* const k36_inputs[] = {
+const char* const k38_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k36_outputs[] = {
+const char* const k38_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k36_attrs[] = {
+const char* const k38_attrs[] = {
     "Tinput: quantizedtype = DT_QUINT8",
     "Tfilter: quantizedtype = DT_QINT8",
     "Tbias: {float, qint32} = DT_QINT32",
@@ -787,7 +811,7 @@ const char* const k36_attrs[] = {
     "dilations: list(int) = [1, 1, 1, 1]",
     "fused_ops: list(string) = []",
     "alpha: float = 0.0"};
-const char* const k37_inputs[] = {
+const char* const k39_inputs[] = {
     "x: T1",
     "y: T2",
     "args: num_args * T",
@@ -795,9 +819,9 @@ const char* const k37_inputs[] = {
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k37_outputs[] = {
+const char* const k39_outputs[] = {
     "output: Toutput"};
-const char* const k37_attrs[] = {
+const char* const k39_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "T: {bfloat16, half, float} = DT_FLOAT",
@@ -807,56 +831,6 @@ const char* const k37_attrs[] = {
     "num_args: int >= 0",
     "fused_ops: list(string) = []",
     "is_filter_const: bool = false"};
-const char* const k38_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "args: num_args * Targs",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float"};
-const char* const k38_outputs[] = {
-    "product: Toutput",
-    "min_product: float",
-    "max_product: float"};
-const char* const k38_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "num_args: int >= 0",
-    "Targs: {float, bfloat16, half, quantizedtype}",
-    "Toutput: quantizedtype",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "fused_ops: list(string) = []",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "epsilon: float = 0.0001",
-    "leakyrelu_alpha: float = 0.2",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k39_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "args: num_args * Targs",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float"};
-const char* const k39_outputs[] = {
-    "product: Toutput"};
-const char* const k39_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "num_args: int >= 0",
-    "Targs: {float, bfloat16, half, quantizedtype}",
-    "Toutput: {float, bfloat16, half} = DT_FLOAT",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "fused_ops: list(string) = []",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "epsilon: float = 0.0001",
-    "leakyrelu_alpha: float = 0.2",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
 const char* const k40_inputs[] = {
     "a: T1",
     "b: T2",
@@ -864,9 +838,7 @@ const char* const k40_inputs[] = {
     "min_a: float",
     "max_a: float",
     "min_b: float",
-    "max_b: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_b: float"};
 const char* const k40_outputs[] = {
     "product: Toutput",
     "min_product: float",
@@ -886,12 +858,64 @@ const char* const k40_attrs[] = {
     "leakyrelu_alpha: float = 0.2",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
 const char* const k41_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "args: num_args * Targs",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float"};
+const char* const k41_outputs[] = {
+    "product: Toutput"};
+const char* const k41_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "num_args: int >= 0",
+    "Targs: {float, bfloat16, half, quantizedtype}",
+    "Toutput: {float, bfloat16, half} = DT_FLOAT",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "fused_ops: list(string) = []",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "epsilon: float = 0.0001",
+    "leakyrelu_alpha: float = 0.2",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
+const char* const k42_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "args: num_args * Targs",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k42_outputs[] = {
+    "product: Toutput",
+    "min_product: float",
+    "max_product: float"};
+const char* const k42_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "num_args: int >= 0",
+    "Targs: {float, bfloat16, half, quantizedtype}",
+    "Toutput: quantizedtype",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "fused_ops: list(string) = []",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "epsilon: float = 0.0001",
+    "leakyrelu_alpha: float = 0.2",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
+const char* const k43_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k41_outputs[] = {
+const char* const k43_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k41_attrs[] = {
+const char* const k43_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -916,43 +940,45 @@ const OpDefEntry kOpDefs[] = {
     {"Fp8LayerNorm", k2_inputs, 5, k2_outputs, 3, k2_attrs, 6},
     {"Fp8Matmul", k3_inputs, 8, k3_outputs, 1, k3_attrs, 12},
     {"Fp8Quantize", k4_inputs, 3, k4_outputs, 1, k4_attrs, 3},
-    {"ITEXQuantizedAvgPool", k5_inputs, 3, k5_outputs, 3, k5_attrs, 3},
-    {"_ITEXDequantize", k6_inputs, 3, k6_outputs, 1, k6_attrs, 5},
-    {"_ITEXQuantizeV2", k7_inputs, 3, k7_outputs, 3, k7_attrs, 8},
-    {"_ITEXQuantizeV2WithQuantizedConv2D", k8_inputs, 9, k8_outputs, 3, k8_attrs, 15},
-    {"_ITEXQuantizedBatchMatMul", k9_inputs, 2, k9_outputs, 2, k9_attrs, 13},
-    {"_ITEXQuantizedBatchMatMulV2AndDequantize", k10_inputs, 6, k10_outputs, 1, k10_attrs, 6},
-    {"_ITEXQuantizedConv2D", k11_inputs, 6, k11_outputs, 3, k11_attrs, 8},
-    {"_ITEXQuantizedConv2DAndRequantize", k12_inputs, 8, k12_outputs, 3, k12_attrs, 8},
-    {"_ITEXQuantizedConv2DPerChannel", k13_inputs, 6, k13_outputs, 3, k13_attrs, 8},
-    {"_ITEXQuantizedConv2DV2", k14_inputs, 2, k14_outputs, 2, k14_attrs, 16},
-    {"_ITEXQuantizedConv2DWithBias", k15_inputs, 7, k15_outputs, 3, k15_attrs, 9},
-    {"_ITEXQuantizedConv2DWithBiasAndRelu", k16_inputs, 7, k16_outputs, 3, k16_attrs, 9},
-    {"_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", k17_inputs, 9, k17_outputs, 3, k17_attrs, 10},
-    {"_ITEXQuantizedConv2DWithBiasAndRequantize", k18_inputs, 9, k18_outputs, 3, k18_attrs, 10},
-    {"_ITEXQuantizedConv2DWithBiasSignedSumAndReluAndRequantize", k19_inputs, 12, k19_outputs, 3, k19_attrs, 11},
-    {"_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize", k20_inputs, 12, k20_outputs, 3, k20_attrs, 11},
-    {"_ITEXQuantizedConv2DWithCast", k21_inputs, 9, k21_outputs, 1, k21_attrs, 10},
-    {"_ITEXQuantizedConv2DWithDequantize", k22_inputs, 9, k22_outputs, 1, k22_attrs, 10},
-    {"_ITEXQuantizedFusedBatchMatMulV2AndDequantize", k23_inputs, 7, k23_outputs, 1, k23_attrs, 9},
-    {"_ITEXQuantizedFusedMatMul", k24_inputs, 7, k24_outputs, 3, k24_attrs, 14},
-    {"_ITEXQuantizedFusedMatMulAndDequantize", k25_inputs, 7, k25_outputs, 1, k25_attrs, 14},
-    {"_ITEXQuantizedFusedMatMulAndRequantize", k26_inputs, 9, k26_outputs, 3, k26_attrs, 14},
-    {"_ITEXQuantizedMatMul", k27_inputs, 2, k27_outputs, 2, k27_attrs, 17},
-    {"_ITEXQuantizedMatMulWithBias", k28_inputs, 7, k28_outputs, 3, k28_attrs, 8},
-    {"_ITEXQuantizedMatMulWithBiasAndDequantize", k29_inputs, 9, k29_outputs, 1, k29_attrs, 8},
-    {"_ITEXQuantizedMatMulWithBiasAndRelu", k30_inputs, 7, k30_outputs, 3, k30_attrs, 7},
-    {"_ITEXQuantizedMatMulWithBiasAndReluAndRequantize", k31_inputs, 9, k31_outputs, 3, k31_attrs, 8},
-    {"_ITEXQuantizedMatMulWithBiasAndRequantize", k32_inputs, 9, k32_outputs, 3, k32_attrs, 8},
-    {"_ITEXQuantizedMaxPool", k33_inputs, 3, k33_outputs, 3, k33_attrs, 3},
-    {"_QuantizedBatchMatMul", k34_inputs, 2, k34_outputs, 2, k34_attrs, 13},
-    {"_QuantizedBatchMatMulV2AndDequantize", k35_inputs, 6, k35_outputs, 1, k35_attrs, 6},
-    {"_QuantizedConv2D", k36_inputs, 2, k36_outputs, 2, k36_attrs, 16},
-    {"_QuantizedFusedBatchMatMulV2AndDequantize", k37_inputs, 7, k37_outputs, 1, k37_attrs, 9},
-    {"_QuantizedFusedMatMul", k38_inputs, 7, k38_outputs, 3, k38_attrs, 13},
-    {"_QuantizedFusedMatMulAndDequantize", k39_inputs, 7, k39_outputs, 1, k39_attrs, 13},
-    {"_QuantizedFusedMatMulAndRequantize", k40_inputs, 9, k40_outputs, 3, k40_attrs, 13},
-    {"_QuantizedMatMul", k41_inputs, 2, k41_outputs, 2, k41_attrs, 17},
+    {"Fp8QuantizeDbias", k5_inputs, 3, k5_outputs, 2, k5_attrs, 3},
+    {"Fp8QuantizeDbiasDgelu", k6_inputs, 4, k6_outputs, 2, k6_attrs, 4},
+    {"ITEXQuantizedAvgPool", k7_inputs, 3, k7_outputs, 3, k7_attrs, 3},
+    {"_ITEXDequantize", k8_inputs, 3, k8_outputs, 1, k8_attrs, 5},
+    {"_ITEXQuantizeV2", k9_inputs, 3, k9_outputs, 3, k9_attrs, 8},
+    {"_ITEXQuantizeV2WithQuantizedConv2D", k10_inputs, 9, k10_outputs, 3, k10_attrs, 15},
+    {"_ITEXQuantizedBatchMatMul", k11_inputs, 2, k11_outputs, 2, k11_attrs, 13},
+    {"_ITEXQuantizedBatchMatMulV2AndDequantize", k12_inputs, 6, k12_outputs, 1, k12_attrs, 6},
+    {"_ITEXQuantizedConv2D", k13_inputs, 6, k13_outputs, 3, k13_attrs, 8},
+    {"_ITEXQuantizedConv2DAndRequantize", k14_inputs, 8, k14_outputs, 3, k14_attrs, 8},
+    {"_ITEXQuantizedConv2DPerChannel", k15_inputs, 6, k15_outputs, 3, k15_attrs, 8},
+    {"_ITEXQuantizedConv2DV2", k16_inputs, 2, k16_outputs, 2, k16_attrs, 16},
+    {"_ITEXQuantizedConv2DWithBias", k17_inputs, 7, k17_outputs, 3, k17_attrs, 9},
+    {"_ITEXQuantizedConv2DWithBiasAndRelu", k18_inputs, 7, k18_outputs, 3, k18_attrs, 9},
+    {"_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", k19_inputs, 9, k19_outputs, 3, k19_attrs, 10},
+    {"_ITEXQuantizedConv2DWithBiasAndRequantize", k20_inputs, 9, k20_outputs, 3, k20_attrs, 10},
+    {"_ITEXQuantizedConv2DWithBiasSignedSumAndReluAndRequantize", k21_inputs, 12, k21_outputs, 3, k21_attrs, 11},
+    {"_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize", k22_inputs, 12, k22_outputs, 3, k22_attrs, 11},
+    {"_ITEXQuantizedConv2DWithCast", k23_inputs, 9, k23_outputs, 1, k23_attrs, 10},
+    {"_ITEXQuantizedConv2DWithDequantize", k24_inputs, 9, k24_outputs, 1, k24_attrs, 10},
+    {"_ITEXQuantizedFusedBatchMatMulV2AndDequantize", k25_inputs, 7, k25_outputs, 1, k25_attrs, 9},
+    {"_ITEXQuantizedFusedMatMul", k26_inputs, 7, k26_outputs, 3, k26_attrs, 14},
+    {"_ITEXQuantizedFusedMatMulAndDequantize", k27_inputs, 7, k27_outputs, 1, k27_attrs, 14},
+    {"_ITEXQuantizedFusedMatMulAndRequantize", k28_inputs, 9, k28_outputs, 3, k28_attrs, 14},
+    {"_ITEXQuantizedMatMul", k29_inputs, 2, k29_outputs, 2, k29_attrs, 17},
+    {"_ITEXQuantizedMatMulWithBias", k30_inputs, 7, k30_outputs, 3, k30_attrs, 8},
+    {"_ITEXQuantizedMatMulWithBiasAndDequantize", k31_inputs, 9, k31_outputs, 1, k31_attrs, 8},
+    {"_ITEXQuantizedMatMulWithBiasAndRelu", k32_inputs, 7, k32_outputs, 3, k32_attrs, 7},
+    {"_ITEXQuantizedMatMulWithBiasAndReluAndRequantize", k33_inputs, 9, k33_outputs, 3, k33_attrs, 8},
+    {"_ITEXQuantizedMatMulWithBiasAndRequantize", k34_inputs, 9, k34_outputs, 3, k34_attrs, 8},
+    {"_ITEXQuantizedMaxPool", k35_inputs, 3, k35_outputs, 3, k35_attrs, 3},
+    {"_QuantizedBatchMatMul", k36_inputs, 2, k36_outputs, 2, k36_attrs, 13},
+    {"_QuantizedBatchMatMulV2AndDequantize", k37_inputs, 6, k37_outputs, 1, k37_attrs, 6},
+    {"_QuantizedConv2D", k38_inputs, 2, k38_outputs, 2, k38_attrs, 16},
+    {"_QuantizedFusedBatchMatMulV2AndDequantize", k39_inputs, 7, k39_outputs, 1, k39_attrs, 9},
+    {"_QuantizedFusedMatMul", k40_inputs, 7, k40_outputs, 3, k40_attrs, 13},
+    {"_QuantizedFusedMatMulAndDequantize", k41_inputs, 7, k41_outputs, 1, k41_attrs, 13},
+    {"_QuantizedFusedMatMulAndRequantize", k42_inputs, 9, k42_outputs, 3, k42_attrs, 13},
+    {"_QuantizedMatMul", k43_inputs, 2, k43_outputs, 2, k43_attrs, 17},
 };
 
 }  // namespace

@@ -1,4 +1,4 @@
-// Fp8Quantize, Fp8Dequantize, Fp8Matmul, Fp8Gelu and Fp8LayerNorm (forward).
+// Fp8Quantize, Fp8Dequantize, Fp8Matmul, Fp8Gelu, Fp8LayerNorm (forward), Fp8QuantizeDbias and Fp8QuantizeDbiasDgelu.
 //
 // Op signatures follow itex/core/ops/fp8_ops.cc:22-61,192-226; kernels follow
 // Fp8QuantizeOp / Fp8DequantizeOp (itex/core/kernels/gpu/fp8/fp8_quantize_op.cc:24-83)
@@ -311,6 +311,55 @@ ITEXB_REGISTER_OP("Fp8Quantize", Fp8QuantizeOp, 3, 1, 0x0u, 0x0u);
 ITEXB_REGISTER_OP("Fp8Dequantize", Fp8DequantizeOp, 2, 1, 0x0u, 0x0u);
 ITEXB_REGISTER_OP("Fp8Matmul", Fp8MatmulOp, 8, 1, 0x0u, 0x0u);
 ITEXB_REGISTER_OP("Fp8Gelu", Fp8GeluOp, 3, 1, 0x0u, 0x0u);
+
+// Fp8QuantizeDbias(grad, amax, scale) -> quantize_out, dbias and Fp8QuantizeDbiasDgelu(grad, gelu_inp, amax, scale) ->
+// dgelu, dbias (itex/core/kernels/gpu/fp8/fp8_quantize_fusion_op.cc:24-116; op definitions itex/core/ops/fp8_ops.cc:145-190).
+// The reference registers them for float and bfloat16 gradients; half is accepted here as well.
+class Fp8QuantizeDbiasOp : public OpKernel {
+ public:
+  explicit Fp8QuantizeDbiasOp(bool dgelu) : dgelu_(dgelu) {}
+  int Init(const AttrMap& attrs) override {
+    int64_t idx;
+    ITEXB_RETURN_IF_ERROR(attrs.GetInt("fp8_meta_index", &idx));
+    index_ = int(idx);
+    return ParseFp8Dtype(attrs, "fp8_dtype", false, &fp8_dtype_);
+  }
+  int Compute(itexb_op_context_t* ctx) override {
+    const char* op = name().c_str();
+    const int base = dgelu_ ? 1 : 0;
+    ITEXB_RETURN_IF_ERROR(RequireInputs(ctx, 3 + base, op));
+    const itexb_tensor_t& grad = ctx->inputs[0];
+    ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 0, op, "grad"));
+    ITEXB_REQUIRE(grad.rank == 2 && IsFloatType(grad.dtype), ITEXB_INVALID_ARGUMENT, "%s: grad must be a float, bfloat16 or half matrix", op);
+    const void* gelu_inp = nullptr;
+    if (dgelu_) {
+      const itexb_tensor_t& x = ctx->inputs[1];
+      ITEXB_RETURN_IF_ERROR(RequireDevice(ctx, 1, op, "gelu_inp"));
+      ITEXB_REQUIRE(x.dtype == grad.dtype && x.rank == 2 && x.dims[0] == grad.dims[0] && x.dims[1] == grad.dims[1], ITEXB_INVALID_ARGUMENT,
+                    "%s: gelu_inp must have the type and shape of grad", op);
+      gelu_inp = x.data;
+    }
+    float *amax, *scale;
+    ITEXB_RETURN_IF_ERROR(MetaPointer(ctx, 1 + base, index_, op, "amax", &amax));
+    ITEXB_RETURN_IF_ERROR(MetaPointer(ctx, 2 + base, index_, op, "scale", &scale));
+    itexb_tensor_t out, dbias;
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 0, ITEXB_DT_INT8, grad.dims, 2, false, &out));
+    ITEXB_RETURN_IF_ERROR(AllocateOutput(ctx, 1, grad.dtype, &grad.dims[1], 1, false, &dbias));
+    void* ws = nullptr;
+    const size_t ws_bytes = itexb_fp8_quantize_dbias_workspace_bytes(grad.dims[0], grad.dims[1]);
+    if (ws_bytes > 0) ITEXB_RETURN_IF_ERROR(AllocateTemp(ctx, ws_bytes, false, &ws));
+    return itexb_fp8_quantize_dbias(grad.data, gelu_inp, grad.dtype, out.data, fp8_dtype_, dbias.data, grad.dims[0], grad.dims[1], scale, amax, ws,
+                                    ctx->stream);
+  }
+
+ private:
+  const bool dgelu_;
+  int index_ = 0, fp8_dtype_ = ITEXB_DT_FP8_E5M2;
+};
+struct Fp8QuantizeDbias : Fp8QuantizeDbiasOp { Fp8QuantizeDbias() : Fp8QuantizeDbiasOp(false) {} };
+struct Fp8QuantizeDbiasDgelu : Fp8QuantizeDbiasOp { Fp8QuantizeDbiasDgelu() : Fp8QuantizeDbiasOp(true) {} };
+ITEXB_REGISTER_OP("Fp8QuantizeDbias", Fp8QuantizeDbias, 3, 2, 0x0u, 0x0u);
+ITEXB_REGISTER_OP("Fp8QuantizeDbiasDgelu", Fp8QuantizeDbiasDgelu, 4, 2, 0x0u, 0x0u);
 ITEXB_REGISTER_OP("Fp8LayerNorm", Fp8LayerNormOp, 5, 3, 0x0u, 0x0u);
 
 }  // namespace

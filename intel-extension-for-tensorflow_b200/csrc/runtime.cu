@@ -316,6 +316,15 @@ int itexb_rt_stream_dependency(itexb_stream_t dependent, itexb_stream_t other) {
   ITEXB_CUDA(e);
   return ITEXB_OK;
 }
+int itexb_rt_stream_device(itexb_stream_t stream, int* ordinal) {
+  ITEXB_REQUIRE(ordinal != nullptr, ITEXB_INVALID_ARGUMENT, "stream_device: ordinal is NULL");
+  if (stream == nullptr) {
+    ITEXB_CUDA(cudaGetDevice(ordinal));
+  } else {
+    ITEXB_CUDA(cudaStreamGetDevice(AsCuda(stream), ordinal));
+  }
+  return ITEXB_OK;
+}
 int itexb_rt_stream_status(itexb_stream_t stream) {
   cudaError_t e = cudaStreamQuery(AsCuda(stream));
   if (e == cudaSuccess || e == cudaErrorNotReady) return ITEXB_OK;

@@ -91,6 +91,27 @@ class Fp8Meta:
         K.fp8_amax_and_scale_update(self.amax_history, self.scale, self.scale_inv, self.fp8_max,
                                     float(self.recipe.margin), self.recipe.amax_compute_algo)
 
+    def save_blob(self) -> bytes:
+        """The state as one host blob (itexb_fp8_meta_save): what a checkpoint stores for this layer."""
+        import ctypes as C
+        from . import _lib as L
+        lib = L.load()
+        lib.itexb_fp8_meta_blob_bytes.restype = C.c_size_t
+        h, n = self.amax_history.shape
+        nbytes = lib.itexb_fp8_meta_blob_bytes(h, n)
+        buf = C.create_string_buffer(nbytes)
+        L.check(lib.itexb_fp8_meta_save(C.c_void_p(self.amax_history.data_ptr()), C.c_void_p(self.scale.data_ptr()), C.c_void_p(self.scale_inv.data_ptr()),
+                                        h, n, buf, C.c_size_t(nbytes), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return bytes(buf.raw)
+
+    def load_blob(self, blob: bytes):
+        import ctypes as C
+        from . import _lib as L
+        h, n = self.amax_history.shape
+        L.check(L.load().itexb_fp8_meta_load(C.c_void_p(self.amax_history.data_ptr()), C.c_void_p(self.scale.data_ptr()),
+                                             C.c_void_p(self.scale_inv.data_ptr()), h, n, blob, C.c_size_t(len(blob)),
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
     def state_dict(self):
         return {"scale": self.scale.clone(), "scale_inv": self.scale_inv.clone(), "amax_history": self.amax_history.clone()}
 

@@ -25,7 +25,7 @@ _NAME_TO_DT = {
 }
 _TORCH_TO_DT = {torch.float32: L.DT_FLOAT, torch.bfloat16: L.DT_BFLOAT16, torch.float16: L.DT_HALF,
                 torch.int8: L.DT_QINT8, torch.uint8: L.DT_QUINT8, torch.int32: L.DT_QINT32}
-_TYPE_ATTRS = {"T", "T1", "T2", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype",
+_TYPE_ATTRS = {"T", "T1", "T2", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype", "grad_dtype",
                "in_dtype", "Tsummand", "Targs", "Tout", "U", "weight_dtype"}
 
 
@@ -65,6 +65,12 @@ def op_signature(name):
     nin, nout, hin, hout = C.c_int(), C.c_int(), C.c_uint32(), C.c_uint32()
     L.check(lib.itexb_op_signature(name.encode(), C.byref(nin), C.byref(nout), C.byref(hin), C.byref(hout)))
     return nin.value, nout.value, hin.value, hout.value
+
+
+def make_attrs(attrs):
+    """dict -> (itexb_attr_t array, keep-alive list): the marshalling the Op class uses, for other C-ABI calls that take attrs."""
+    arr, _, keep = _make_attrs(attrs)
+    return arr, keep
 
 
 def _make_attrs(attrs):
@@ -446,6 +452,19 @@ def Fp8Quantize(x, x_amax, x_scale, fp8_meta_index, fp8_dtype="E4M3"):
     """-> y (int8 tensor holding fp8 bytes); x_amax[fp8_meta_index] is raised in place."""
     op = _cached("Fp8Quantize", dict(in_dtype=_TORCH_TO_DT[x.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
     return op(x, x_amax, x_scale)
+
+
+def Fp8QuantizeDbias(grad, amax, scale, fp8_meta_index, fp8_dtype="E5M2"):
+    """-> (quantize_out int8 [rows, cols], dbias [cols])"""
+    op = _cached("Fp8QuantizeDbias", dict(grad_dtype=_TORCH_TO_DT[grad.dtype], fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
+    return op(grad, amax, scale)
+
+
+def Fp8QuantizeDbiasDgelu(grad, gelu_inp, amax, scale, fp8_meta_index, fp8_dtype="E5M2"):
+    """-> (dgelu int8 [rows, cols], dbias [cols])"""
+    op = _cached("Fp8QuantizeDbiasDgelu", dict(grad_dtype=_TORCH_TO_DT[grad.dtype], in_dtype=_TORCH_TO_DT[gelu_inp.dtype],
+                                               fp8_meta_index=int(fp8_meta_index), fp8_dtype=fp8_dtype))
+    return op(grad, gelu_inp, amax, scale)
 
 
 def Fp8Gelu(inp, amax, scale, fp8_meta_index, fp8_dtype="E4M3"):

@@ -720,6 +720,33 @@ def fp8_gelu(x, amax_row0: np.ndarray, scale: np.ndarray, fp8_meta_index: int, f
     return fp8_cast_sat((g * f32(scale[fp8_meta_index])).astype(np.float32), fp8_dtype)
 
 
+def fp8_dgelu(x) -> np.ndarray:
+    """dgelu(), itex/core/kernels/gpu/fp8/fp8_quantize_fusion_gpu.h:33-43 (float64 here, rounded to fp32)."""
+    v = _as_f32(x).astype(np.float64)
+    th = np.tanh(0.79788456 * v * (1.0 + 0.044715 * v * v))
+    return (0.5 * v * ((1.0 - th * th) * (0.79788456 + 0.1070322243 * v * v)) + 0.5 * (1.0 + th)).astype(np.float32)
+
+
+def fp8_quantize_dbias(grad, amax_row0: np.ndarray, scale: np.ndarray, fp8_meta_index: int, fp8_dtype: str = "E5M2", gelu_inp=None,
+                       out_dtype: str = "float"):
+    """Fp8QuantizeDbias / Fp8QuantizeDbiasDgelu (itex/core/kernels/gpu/fp8/fp8_quantize_fusion_op.cc:24-104; kernels
+    fp8_quantize_fusion_gpu.h:45-300): t = grad, or dgelu(gelu_inp) * grad; out = fp8(scale * t); dbias = column sums of
+    t (fp32 in the reference, in its own block order; float64 here); amax raised to max|t|.  Returns (out bits, dbias).
+    Parity unpinned (the reference has no test for these ops)."""
+    t = _as_f32(grad)
+    if gelu_inp is not None:
+        t = (fp8_dgelu(gelu_inp) * t).astype(np.float32)
+    if t.size:
+        amax_row0[fp8_meta_index] = max(f32(amax_row0[fp8_meta_index]), f32(np.abs(t).max()))
+    out = fp8_cast_sat((f32(scale[fp8_meta_index]) * t).astype(np.float32), fp8_dtype)
+    dbias = t.astype(np.float64).sum(axis=0).astype(np.float32)
+    if out_dtype in ("bfloat16", "bf16"):
+        dbias = to_bf16_rne(dbias)
+    elif out_dtype == "half":
+        dbias = dbias.astype(np.float16).astype(np.float32)
+    return out, dbias
+
+
 def fp8_layernorm(x, gamma, beta, amax_row0: Optional[np.ndarray], scale: Optional[np.ndarray], fp8_meta_index: int, *,
                   epsilon: float = 1e-4, fp8_dtype: str = "E4M3", out_dtype: str = "int8"):
     """Fp8LayerNorm forward (itex/core/kernels/gpu/fp8/fp8_layernorm_gpu.h:108-257): per row mu = mean(x),

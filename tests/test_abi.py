@@ -178,3 +178,75 @@ def test_debug_hooks_reject_unknown_keys(itex):
     assert lib.itexb_debug_set(b"gemm_wait_limit_cycles", ctypes.c_int64(-5)) == L.INVALID_ARGUMENT
     assert lib.itexb_debug_set(b"bogus", ctypes.c_int64(1)) == L.NOT_FOUND
     assert lib.itexb_op_check(None, 1) == L.INVALID_ARGUMENT
+
+
+def _rewrite(itex, op, on_gpu=False, all_deq=False, **attrs):
+    import importlib
+    ops = importlib.import_module("itex_b200.ops")
+    lib, L = itex.load(), itex._lib
+    arr, keep = ops.make_attrs(attrs)
+    q = L.RewriteQuery(op.encode(), ctypes.cast(arr, ctypes.POINTER(L.Attr)), len(attrs), int(on_gpu), int(all_deq))
+    r = L.RewriteResult()
+    st = lib.itexb_rewrite_node(ctypes.byref(q), ctypes.byref(r))
+    if st != L.OK:
+        return st, None, None
+    added = {}
+    for i in range(r.num_added):
+        a = r.added[i]
+        added[a.name.decode()] = a.s.decode() if a.type == 3 else int(a.i)
+    return st, (r.new_op.decode() if r.new_op else None), added
+
+
+def test_rewrite_rules_match_the_reference_table(itex, golden_dir):
+    """itexb_rewrite_node against the reference's rename table (tests/golden/rewrite_table.json, extracted from
+    native_layout.cc:113-199) for every entry whose target this library implements, and the predicate / attr-copy rules
+    of layout_utils.cc:315-354,471-542 case by case."""
+    import importlib
+    import json
+    ops = importlib.import_module("itex_b200.ops")
+    lib, L = itex.load(), itex._lib
+    table = json.load(open(os.path.join(golden_dir, "rewrite_table.json")))
+    registered = set(ops.op_list())
+    mine = {}
+    i = 0
+    while True:
+        f, t = ctypes.c_char_p(), ctypes.c_char_p()
+        if lib.itexb_rewrite_rule(i, ctypes.byref(f), ctypes.byref(t)) != L.OK:
+            break
+        mine[f.value.decode()] = t.value.decode()
+        i += 1
+    want = {e["from"]: e for e in table if e["to"] in registered}
+    assert len(want) >= 25 and mine == {k: v["to"] for k, v in want.items()}
+    need = {"CopyAttrsQuantizedConv2D": dict(out_type="qint32"), "CopyAttrsQuantizedMatMul": dict(Toutput="qint32"),
+            "CopyAttrsQuantize": dict(mode="SCALED", round_mode="HALF_TO_EVEN"), "CopyAttrsAll": {}}
+    for f, e in want.items():
+        attrs = dict(need[e["copy"]])
+        if e["rule"] == "RewriteQuantize":
+            attrs.setdefault("mode", "SCALED")
+        st, new_op, added = _rewrite(itex, f, **attrs)
+        assert st == L.OK and new_op == e["to"], f
+        if e["copy"] == "CopyAttrsQuantizedConv2D":
+            assert added == {"data_format": "NHWC"}
+    # ops the table does not hold stay as they are
+    assert _rewrite(itex, "Conv2D") == (L.OK, None, {})
+    assert _rewrite(itex, "QuantizedConcatV2") == (L.OK, None, {})        # disabled in the reference's table
+    # RewriteQuantize
+    assert _rewrite(itex, "QuantizeV2", mode="MIN_COMBINED", round_mode="HALF_AWAY_FROM_ZERO")[1] is None
+    assert _rewrite(itex, "QuantizeV2", mode="SCALED", round_mode="HALF_AWAY_FROM_ZERO")[1] is None
+    assert _rewrite(itex, "QuantizeV2", mode="MIN_FIRST", round_mode="HALF_AWAY_FROM_ZERO")[1] == "_ITEXQuantizeV2"
+    assert _rewrite(itex, "Dequantize", mode="MIN_FIRST", on_gpu=True)[1] is None
+    assert _rewrite(itex, "Dequantize", mode="MIN_FIRST", on_gpu=False)[1] == "_ITEXDequantize"
+    assert _rewrite(itex, "Dequantize", mode="SCALED", on_gpu=True)[1] == "_ITEXDequantize"
+    assert _rewrite(itex, "QuantizeV2")[0] == L.INVALID_ARGUMENT           # no `mode`
+    # CopyAttrsQuantize: dtype defaults to float when absent; classic_asymmetric_algorithm follows the consumers
+    st, new_op, added = _rewrite(itex, "QuantizeV2", mode="SCALED", round_mode="HALF_TO_EVEN", all_deq=True)
+    assert added == {"dtype": L.DT_FLOAT, "classic_asymmetric_algorithm": 1}
+    st, new_op, added = _rewrite(itex, "QuantizeV2", mode="SCALED", round_mode="HALF_TO_EVEN", dtype="bfloat16")
+    assert added == {"classic_asymmetric_algorithm": 0}
+    # CopyAttrsQuantizedConv2D / MatMul: Tbias carried over when present; out_type / Toutput required
+    st, new_op, added = _rewrite(itex, "QuantizedConv2DWithBiasAndReluAndRequantize", out_type="quint8", Tbias="float")
+    assert new_op == "_ITEXQuantizedConv2DWithBiasAndReluAndRequantize" and added == {"data_format": "NHWC", "Tbias": L.DT_FLOAT}
+    assert _rewrite(itex, "QuantizedConv2D")[0] == L.INVALID_ARGUMENT
+    st, new_op, added = _rewrite(itex, "QuantizedMatMulWithBiasAndDequantize", Toutput="float", Tbias="qint32")
+    assert new_op == "_ITEXQuantizedMatMulWithBiasAndDequantize" and added == {"Tbias": L.DT_QINT32}
+    assert _rewrite(itex, "QuantizedMatMulWithBias")[0] == L.INVALID_ARGUMENT

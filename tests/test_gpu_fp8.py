@@ -114,6 +114,19 @@ def test_delayed_scaling_20_steps_matches_oracle():
     layer.meta.amax_history.zero_()
     layer.meta.load_state_dict(sd)
     np.testing.assert_array_equal(host(layer.meta.amax_history), hist)
+    # the same through the C-ABI's checkpoint blob; a blob of another shape is refused
+    blob = layer.meta.save_blob()
+    layer.meta.amax_history.zero_(); layer.meta.scale.fill_(7.0); layer.meta.scale_inv.zero_()
+    layer.meta.load_blob(blob)
+    np.testing.assert_array_equal(host(layer.meta.amax_history), hist)
+    np.testing.assert_array_equal(host(layer.meta.scale), scale)
+    np.testing.assert_array_equal(host(layer.meta.scale_inv), sinv)
+    other = fp8.Fp8Meta(fp8.DelayedScaling(amax_history_len=8), 1, "cuda")
+    with pytest.raises(itex.ItexError) as e:
+        other.load_blob(blob)
+    assert "history 16 x 3" in str(e.value)
+    with pytest.raises(itex.ItexError):
+        layer.meta.load_blob(b"not a blob at all, but long enough for the header")
     for algo in ("max", "most_recent"):
         h = np.abs(rng.standard_normal((16, 5))).astype(np.float32) * np.array([1, 0, 1000, 1e-6, 448], np.float32)
         h[3, 2] = np.inf
@@ -318,3 +331,45 @@ def test_delayed_scaling_20_steps_at_k4096():
         got = host(out)
         assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-2
     assert scale[0] <= 16 and scale[1] >= 2048       # the activation scale fell as the spread grew; the weight scale settled high
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 1000), (4096, 4096), (37, 130), (1, 4)])
+def test_fp8_quantize_dbias_and_dgelu(rows, cols):
+    """Fp8QuantizeDbias / Fp8QuantizeDbiasDgelu against the restatement (the reference has no test for them: unpinned).
+    The FP8 bytes of the plain cast are exact; through dgelu (device tanhf against float64) a value may land on the
+    neighbouring code; the bias gradient is an fp32 sum in another order: 1e-5 of the column's sum of magnitudes."""
+    itex, K, ops = modules()
+    rng = np.random.default_rng(rows + cols)
+    g = (rng.standard_normal((rows, cols)) * 0.7).astype(np.float32)
+    x = (rng.standard_normal((rows, cols)) * 1.5).astype(np.float32)
+    for dt, name in ((torch.float32, "float"), (torch.bfloat16, "bfloat16")):
+        G, X = torch.from_numpy(g).to(dt).cuda(), torch.from_numpy(x).to(dt).cuda()
+        gh, xh = host(G), host(X)
+        for fmt in ("E5M2", "E4M3"):
+            amax = torch.zeros(3, device="cuda")
+            scale = torch.tensor([1.0, 64.0, 0.5], device="cuda")
+            q, db = ops.Fp8QuantizeDbias(G, amax, scale, 1, fmt)
+            ref_amax = np.zeros(3, np.float32)
+            rq, rdb = o.fp8_quantize_dbias(gh, ref_amax, host(scale), 1, fmt, out_dtype=name)
+            assert q.dtype == torch.int8 and tuple(q.shape) == (rows, cols) and tuple(db.shape) == (cols,) and db.dtype == dt
+            np.testing.assert_array_equal(host(q).view(np.uint8), rq)
+            tol = 1e-5 * np.abs(gh).sum(axis=0) + (2.0 ** -8 * np.abs(rdb) if dt == torch.bfloat16 else 0) + 1e-7
+            assert np.all(np.abs(host(db) - rdb) <= tol)
+            assert float(amax[1]) == float(ref_amax[1]) and float(amax[0]) == 0.0
+            amax.zero_()
+            q, db = ops.Fp8QuantizeDbiasDgelu(G, X, amax, scale, 1, fmt)
+            ref_amax = np.zeros(3, np.float32)
+            rq, rdb = o.fp8_quantize_dbias(gh, ref_amax, host(scale), 1, fmt, gelu_inp=xh, out_dtype=name)
+            got_f, ref_f = o.fp8_to_f32(host(q).view(np.uint8), fmt), o.fp8_to_f32(rq, fmt)
+            assert (host(q).view(np.uint8) != rq).mean() < 2e-3
+            np.testing.assert_allclose(got_f, ref_f, rtol=0.26 if fmt == "E5M2" else 0.13, atol=1e-2)    # at most the neighbouring code
+            t = np.abs(o.fp8_dgelu(xh) * gh)
+            tol = 1e-5 * t.sum(axis=0) + (2.0 ** -8 * np.abs(rdb) if dt == torch.bfloat16 else 0) + 1e-6
+            assert np.all(np.abs(host(db) - rdb) <= tol)
+            np.testing.assert_allclose(float(amax[1]), float(ref_amax[1]), rtol=1e-5)
+    # two runs give the same bias gradient bit for bit (fixed summation order, no float atomics)
+    G = dev(g)
+    amax, scale = torch.zeros(1, device="cuda"), torch.ones(1, device="cuda")
+    a = ops.Fp8QuantizeDbias(G, amax, scale, 0, "E5M2")[1]
+    b = ops.Fp8QuantizeDbias(G, amax, scale, 0, "E5M2")[1]
+    assert bool((a == b).all())
