@@ -589,6 +589,28 @@ def run_fp8_linears(args, rank, world, local, dev, K):
                     "h2d_bytes_per_step": sum(m * k * 2 for k, _ in FP8_LINEARS), "d2h_bytes_per_step": sum(m * n * 2 for _, n in FP8_LINEARS)},
             "gpu_launches": int(launches), "clocks": sampler.summary(),
         }
+        if world == 1:
+            # cuBLASLt FP8 on the same three shapes (no quantize passes, no scale update): a library ceiling for the GEMMs alone
+            try:
+                one = torch.ones((), device=dev)
+                best_total = 0.0
+                for k, n in FP8_LINEARS:
+                    a8 = torch.randn((m, k), device=dev).to(torch.float8_e4m3fn)
+                    b8 = torch.randn((n, k), device=dev).to(torch.float8_e4m3fn)
+                    best = float("inf")
+                    for i in range(8):
+                        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        c0.record()
+                        torch._scaled_mm(a8, b8.t(), one, one, out_dtype=torch.bfloat16)
+                        c1.record()
+                        torch.cuda.synchronize()
+                        if i >= 3:
+                            best = min(best, c0.elapsed_time(c1))
+                    best_total += best
+                line["roofline"]["library_scaled_mm_tflops"] = flops / (best_total * 1e-3) / 1e12
+                line["roofline"]["library_scaled_mm_ms"] = best_total
+            except Exception:  # noqa: BLE001 - informative only
+                line["roofline"]["library_scaled_mm_tflops"] = None
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_fp8_linears(layers, m)
     if pg is not None:
@@ -645,7 +667,7 @@ def rotating_inputs(x, bytes_per_call):
     return [x] + [x.clone() for _ in range(copies - 1)]
 
 
-def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
+def run_pointwise(args, rank, world, local, dev, K, ops, which, count, real=None):
     """_ITEXQuantizeV2 (fp32 -> quint8, SCALED, HALF_TO_EVEN) or _ITEXDequantize (quint8 -> fp32, SCALED) over `count`
     elements through the op layer: achieved GB/s of the 5 algorithmic bytes per element.  The sizes are the reference
     benchmark's (test/benchmark/test_quantize.py:55-56).  The smaller one fits in L2, so the timed launches cycle over
@@ -654,18 +676,35 @@ def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
     gen = torch.Generator(device=dev)
     gen.manual_seed(shard_seed(1240, rank))
     shape = (count // 1024, 1024)
+    real = real or getattr(args, "real_dtype", "float")      # the real-valued side: float (the reference benchmark's) or bfloat16
+    tdt, rb = (torch.bfloat16, 2) if real == "bfloat16" else (torch.float32, 4)
+    kernel = {"quantize": "QuantizeKernel", "dequantize": "DequantizeKernel", "fp8_quantize": "Fp8QuantizeKernel",
+              "fp8_dequantize": "Fp8DequantizeKernel"}[which]
     if which == "quantize":
-        x = torch.rand(shape, device=dev, generator=gen) * 2 - 1
+        x = (torch.rand(shape, device=dev, generator=gen) * 2 - 1).to(tdt)
         op = ops.Op("_ITEXQuantizeV2", T="quint8", mode="SCALED", round_mode="HALF_TO_EVEN", narrow_range=False, axis=-1,
-                    ensure_minimum_range=0.01, dtype="float")
+                    ensure_minimum_range=0.01, dtype=real)
         call = lambda t: op(t, -1.0, 1.0)[0]
-        in_b, out_b = 4, 1
-    else:
+        in_b, out_b = rb, 1
+    elif which == "dequantize":
         x = torch.randint(0, 256, shape, dtype=torch.uint8, device=dev, generator=gen)
-        op = ops.Op("_ITEXDequantize", T="quint8", mode="SCALED", narrow_range=False, axis=-1, dtype="float")
+        op = ops.Op("_ITEXDequantize", T="quint8", mode="SCALED", narrow_range=False, axis=-1, dtype=real)
         call = lambda t: op(t, 0.0, 6.0)
-        in_b, out_b = 1, 4
-    xs = rotating_inputs(x, count * 5)
+        in_b, out_b = 1, rb
+    elif which == "fp8_quantize":
+        x = torch.randn(shape, device=dev, generator=gen).to(tdt)
+        amax, scale = torch.zeros(1, device=dev), torch.full((1,), 64.0, device=dev)
+        op = ops.Op("Fp8Quantize", in_dtype=real, fp8_meta_index=0, fp8_dtype="E4M3")
+        call = lambda t: op(t, amax, scale)
+        in_b, out_b = rb, 1
+    else:
+        x = torch.randint(0, 120, shape, dtype=torch.int8, device=dev, generator=gen)
+        sinv = torch.full((1,), 1.0 / 64.0, device=dev)
+        op = ops.Op("Fp8Dequantize", out_dtype=real, fp8_meta_index=0, fp8_dtype="E4M3")
+        call = lambda t: op(t, sinv)
+        in_b, out_b = 1, rb
+    per_elem = in_b + out_b
+    xs = rotating_inputs(x, count * per_elem)
     for _ in range(max(args.warmup, 3)):
         y = call(x)
     torch.cuda.synchronize()
@@ -697,19 +736,22 @@ def run_pointwise(args, rank, world, local, dev, K, ops, which, count):
     if rank != 0:
         return None
     peaks = measured_peaks()
-    gbs = count * 5 / (us * 1e-6) / 1e9
+    gbs = count * per_elem / (us * 1e-6) / 1e9
+    tname = {"float": "f32", "bfloat16": "bf16"}[real]
+    io = {"quantize": "%s->u8" % tname, "dequantize": "u8->%s" % tname, "fp8_quantize": "%s->e4m3" % tname, "fp8_dequantize": "e4m3->%s" % tname}[which]
     line = {"metric": "%s_gb_per_s" % which, "value": gbs * world, "unit": "GB/s", "ms_per_step": us * 1e-3, "n_gpus": world, "scaling": "weak",
-            "dtype": "f32->u8" if which == "quantize" else "u8->f32",
-            "config": {"workload": "%s_%d" % ("quantize_f32_u8" if which == "quantize" else "dequantize_u8_f32", count), "elements_per_gpu": count,
-                       "op": "_ITEXQuantizeV2" if which == "quantize" else "_ITEXDequantize",
+            "dtype": io,
+            "config": {"workload": "%s_%s_%d" % (which, io.replace("->", "_"), count), "elements_per_gpu": count,
+                       "op": {"quantize": "_ITEXQuantizeV2", "dequantize": "_ITEXDequantize", "fp8_quantize": "Fp8Quantize", "fp8_dequantize": "Fp8Dequantize"}[which],
                        "l2": "launches cycle over input copies that together exceed L2; back-to-back launches in one CUDA graph"},
-            "roofline": {"bound": "hbm", "kernel": "QuantizeKernel" if which == "quantize" else "DequantizeKernel", "achieved": gbs,
+            "roofline": {"bound": "hbm", "kernel": kernel, "achieved": gbs,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
-                         "algorithmic_bytes": count * 5, "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peaks["source"]},
-            "e2e": {"value": count * 5 * world / (e2e_us * 1e-6) / 1e9, "unit": "GB/s", "ms_per_step": e2e_us * 1e-3,
+                         "algorithmic_bytes": count * per_elem, "bytes_per_element": per_elem,
+                         "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peaks["source"]},
+            "e2e": {"value": count * per_elem * world / (e2e_us * 1e-6) / 1e9, "unit": "GB/s", "ms_per_step": e2e_us * 1e-3,
                     "h2d_bytes_per_step": count * in_b * world, "d2h_bytes_per_step": count * out_b * world},
             "gpu_launches": int(launches)}
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and which in ("quantize", "dequantize") and real == "float":
         line["cpu_baseline"] = cpu_pointwise(which, x[: min(x.shape[0], 3136)].cpu().numpy())
     return line
 
@@ -1154,9 +1196,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="int8_gemm_8192",
-                    choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears", "bert_large_int8", "conv_cfg2", "quantize", "dequantize"])
+                    choices=sorted(WORKLOADS) + ["resnet50_int8", "fp8_llama_linears", "bert_large_int8", "conv_cfg2", "quantize", "dequantize",
+                                                 "fp8_quantize", "fp8_dequantize"])
     ap.add_argument("--batch", type=int, default=128, help="images per GPU for --workload resnet50_int8")
-    ap.add_argument("--elements", type=int, default=102760448, help="elements per GPU for --workload quantize / dequantize")
+    ap.add_argument("--elements", type=int, default=102760448, help="elements per GPU for --workload [fp8_]quantize / [fp8_]dequantize")
+    ap.add_argument("--real-dtype", default="float", choices=["float", "bfloat16"],
+                    help="type of the real-valued side for --workload [fp8_]quantize / [fp8_]dequantize")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--fp8-gather", default="fused", choices=["fused", "nccl"],
                     help="fp8_llama_linears on several GPUs: all-gather fused into the GEMM epilogue (peer stores), or NCCL's")
@@ -1206,7 +1251,7 @@ def main():
         line = run_resnet50(*common)
     elif args.workload == "conv_cfg2":
         line = run_conv_cfg2(*common, ops)
-    elif args.workload in ("quantize", "dequantize"):
+    elif args.workload in ("quantize", "dequantize", "fp8_quantize", "fp8_dequantize"):
         line = run_pointwise(*common, ops, args.workload, args.elements)
     else:
         line = run_gemm(*common, ops, m, n, k)
@@ -1217,6 +1262,7 @@ def main():
                     ("quantize_f32_u8_3211264", lambda: run_pointwise(*common, ops, "quantize", 3211264)),
                     ("dequantize_u8_f32_102760448", lambda: run_pointwise(*common, ops, "dequantize", 102760448)),
                     ("dequantize_u8_f32_3211264", lambda: run_pointwise(*common, ops, "dequantize", 3211264)),
+                    ("fp8_quantize_bf16_e4m3_58720256", lambda: run_pointwise(*common, ops, "fp8_quantize", 58720256, "bfloat16")),
                     ("conv_cfg2", lambda: run_conv_cfg2(*common, ops)),
                     ("resnet50_int8", lambda: run_resnet50(*common)),
                     ("fp8_llama_linears", lambda: run_fp8_linears(*common))):

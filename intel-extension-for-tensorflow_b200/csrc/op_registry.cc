@@ -230,24 +230,104 @@ void DeviceBuffer::Release() {
 }
 
 // ---- OpKernel: device status word -------------------------------------------------------
+namespace {
+
+// Pinned host words for the status read-backs come from one process-wide pool: a page of them is pinned at a time and
+// never unpinned, so creating and deleting kernel instances pins and unpins nothing (unpinning synchronizes the device
+// and is not allowed while any stream of the thread captures a graph).
+class StatusSlots {
+ public:
+  int* Take() {
+    std::lock_guard<std::mutex> l(mu_);
+    if (free_.empty()) {
+      RelaxedCaptureMode relaxed;
+      int* page = nullptr;
+      constexpr int kWords = 1024;
+      if (cudaHostAlloc(reinterpret_cast<void**>(&page), kWords * sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+      }
+      for (int i = kWords - 1; i >= 0; --i) free_.push_back(page + i);
+    }
+    int* w = free_.back();
+    free_.pop_back();
+    *w = 0;
+    return w;
+  }
+  void Give(int* w) {
+    if (w == nullptr) return;
+    std::lock_guard<std::mutex> l(mu_);
+    free_.push_back(w);
+  }
+
+ private:
+  std::mutex mu_;
+  std::vector<int*> free_;
+};
+
+StatusSlots& Slots() {
+  static StatusSlots* s = new StatusSlots();  // outlives every kernel instance, static destruction order included
+  return *s;
+}
+
+// A deleted instance whose last read-back had not landed yet: its words stay reserved until the event completes, and
+// a give-up they report is written to stderr (nobody is left to return a status to).
+struct Orphan {
+  cudaEvent_t ev;
+  int* host;
+  int* dev;
+  int ordinal;
+  cudaStream_t stream;
+  std::string name;
+};
+std::mutex g_orphan_mu;
+std::vector<Orphan> g_orphans;
+
+void SweepOrphans() {
+  std::lock_guard<std::mutex> l(g_orphan_mu);
+  if (g_orphans.empty()) return;
+  RelaxedCaptureMode relaxed;
+  size_t keep = 0;
+  for (size_t i = 0; i < g_orphans.size(); ++i) {
+    Orphan& o = g_orphans[i];
+    const cudaError_t e = cudaEventQuery(o.ev);
+    if (e == cudaErrorNotReady) {
+      if (keep != i) g_orphans[keep] = std::move(o);
+      ++keep;
+      continue;
+    }
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    if (e == cudaSuccess && *o.host != 0)
+      std::fprintf(stderr, "itexb: %s (deleted): a kernel gave up on a bounded wait (status %d) and left its output incomplete\n",
+                   o.name.c_str(), *o.host);
+    (void)cudaEventDestroy(o.ev);
+    Slots().Give(o.host);
+    (void)itexb_rt_deallocate_after(o.ordinal, o.dev, o.stream);
+  }
+  g_orphans.resize(keep);
+}
+
+}  // namespace
+
 int* OpKernel::StatusWord(int ordinal, cudaStream_t stream) {
   if (status_dev_ != nullptr && status_ordinal_ != ordinal) ReleaseStatus();
   if (status_dev_ == nullptr) {
     // First use inside a graph capture: the zeroing below would become a graph node instead of running now.  This
     // call goes without a status word; the instance gets one at its first Compute outside a capture.
     if (IsCapturing(stream)) return nullptr;
+    SweepOrphans();
     void* d = nullptr;
     if (itexb_rt_allocate(ordinal, sizeof(int), &d) != ITEXB_OK) return nullptr;
-    if (cudaMemsetAsync(d, 0, sizeof(int), stream) != cudaSuccess ||
-        cudaHostAlloc(reinterpret_cast<void**>(&status_host_), sizeof(int), cudaHostAllocDefault) != cudaSuccess ||
+    status_host_ = Slots().Take();
+    if (status_host_ == nullptr || cudaMemsetAsync(d, 0, sizeof(int), stream) != cudaSuccess ||
         cudaEventCreateWithFlags(&status_ev_, cudaEventDisableTiming) != cudaSuccess) {
       (void)cudaGetLastError();
       (void)itexb_rt_deallocate_after(ordinal, d, stream);
-      if (status_host_ != nullptr) (void)cudaFreeHost(status_host_);
+      Slots().Give(status_host_);
       status_host_ = nullptr;
+      status_ev_ = nullptr;
       return nullptr;
     }
-    *status_host_ = 0;
     status_dev_ = static_cast<int*>(d);
     status_ordinal_ = ordinal;
   }
@@ -289,9 +369,18 @@ int OpKernel::PollStatus(bool wait) {
 }
 
 void OpKernel::ReleaseStatus() {
-  if (status_ev_ != nullptr) (void)cudaEventDestroy(status_ev_);
-  if (status_host_ != nullptr) (void)cudaFreeHost(status_host_);
-  if (status_dev_ != nullptr) (void)itexb_rt_deallocate_after(status_ordinal_, status_dev_, status_stream_);
+  if (status_dev_ != nullptr) {
+    if (status_pending_) {
+      // the read-back is still in flight: the words are handed over and released once its event has completed
+      std::lock_guard<std::mutex> l(g_orphan_mu);
+      g_orphans.push_back(Orphan{status_ev_, status_host_, status_dev_, status_ordinal_, status_stream_, name_});
+    } else {
+      RelaxedCaptureMode relaxed;
+      if (status_ev_ != nullptr) (void)cudaEventDestroy(status_ev_);
+      Slots().Give(status_host_);
+      (void)itexb_rt_deallocate_after(status_ordinal_, status_dev_, status_stream_);
+    }
+  }
   status_ev_ = nullptr;
   status_host_ = nullptr;
   status_dev_ = nullptr;
@@ -439,10 +528,12 @@ int itexb_op_check(itexb_op_t* op, int wait) {
 void itexb_op_delete(itexb_op_t* op) {
   if (op == nullptr) return;
   // Last chance to learn that a launch of this instance gave up: there is no status to return, so it is written to
-  // stderr (and left in itexb_last_error for the calling thread).
-  if (op->kernel->PollStatus(true) != ITEXB_OK) std::fprintf(stderr, "itexb_op_delete: %s\n", LastError());
+  // stderr (and left in itexb_last_error for the calling thread).  A read-back still in flight is not waited for: its
+  // words go to the orphan list, which reports the same way once the event has completed.
+  if (op->kernel->PollStatus(false) != ITEXB_OK) std::fprintf(stderr, "itexb_op_delete: %s\n", LastError());
   op->kernel->ReleaseStatus();
   delete op;
+  SweepOrphans();
 }
 
 int itexb_simple_context_create(int device_ordinal, itexb_stream_t stream, itexb_simple_context_t** c) {

@@ -220,48 +220,95 @@ __global__ void __launch_bounds__(kThreads) QuantizeScalarKernel(const TX* __res
 }
 
 // Four consecutive outputs of one thread -> one store (16 bytes of fp32, 8 bytes of a 16-bit type).
-template <typename T> __device__ __forceinline__ void Store4(T* p, const float (&in)[4]);
-template <> __device__ __forceinline__ void Store4<float>(float* p, const float (&in)[4]) {
+// Elements a thread converts per round of the two dequantize kernels: as many as make its store 16 bytes wide.
+template <typename TY> constexpr int kPerRound = 16 / int(sizeof(TY));
+constexpr int kRounds = 4;
+
+template <int PER> struct Words;
+template <> struct Words<4> {
+  uint32_t w[1];
+  __device__ __forceinline__ void Load(const uint8_t* p) { w[0] = __ldcs(reinterpret_cast<const uint32_t*>(p)); }
+};
+template <> struct Words<8> {
+  uint32_t w[2];
+  __device__ __forceinline__ void Load(const uint8_t* p) {
+    const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+    w[0] = t.x;
+    w[1] = t.y;
+  }
+};
+
+template <typename T> __device__ __forceinline__ void StoreRound(T* p, const float (&in)[kPerRound<T>]);
+template <> __device__ __forceinline__ void StoreRound<float>(float* p, const float (&in)[4]) {
   __stcs(reinterpret_cast<float4*>(p), make_float4(in[0], in[1], in[2], in[3]));
 }
-template <> __device__ __forceinline__ void Store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&in)[4]) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(in[0], in[1]), b = __floats2bfloat162_rn(in[2], in[3]);
-  __stcs(reinterpret_cast<uint2*>(p), make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b)));
+template <> __device__ __forceinline__ void StoreRound<__nv_bfloat16>(__nv_bfloat16* p, const float (&in)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * j], in[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
 }
-template <> __device__ __forceinline__ void Store4<__half>(__half* p, const float (&in)[4]) {
-  __half2 a = __floats2half2_rn(in[0], in[1]), b = __floats2half2_rn(in[2], in[3]);
-  __stcs(reinterpret_cast<uint2*>(p), make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b)));
+template <> __device__ __forceinline__ void StoreRound<__half>(__half* p, const float (&in)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __half2 h = __floats2half2_rn(in[2 * j], in[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
 }
 
-// y = T((float(q) - zp) * s).  A block covers kThreads * 16 consecutive elements in four rounds; in a
-// round thread t converts elements 4t .. 4t+3 of a run of kThreads * 4, so every load instruction of a
-// warp reads 128 consecutive bytes and every store instruction writes 512 (fp32) or 256 consecutive
-// bytes - whole 32-byte sectors, which the write-dominated traffic of this kernel needs (a thread
-// writing its own 64 consecutive bytes in four stores half-fills every sector it touches: 0.71 of the
-// copy bandwidth instead of the 0.9 and more of this layout).
+// y = T((float(q) - zp) * s).  A block covers kThreads * PER * 4 consecutive elements in four rounds (PER = 4 for fp32
+// results, 8 for 16-bit ones); in a round thread t converts elements PER*t .. PER*t + PER-1 of a run of kThreads * PER,
+// so every load instruction of a warp reads 128 or 256 consecutive bytes and every store instruction writes 512
+// consecutive bytes, 16 per thread - whole 32-byte sectors, which the write-dominated traffic of this kernel needs (a
+// thread writing its own 64 consecutive bytes in four stores half-fills every sector it touches: 0.71 of the copy
+// bandwidth instead of the 0.9 and more of this layout).
 template <typename TY, bool SIGNED, bool UNIFORM>
 __global__ void __launch_bounds__(kThreads) DequantizeKernel(const uint8_t* __restrict__ q, TY* __restrict__ y, long long n,
                                                              SliceArgs a) {
-  const long long base = (long long)blockIdx.x * (kThreads * kVec) + threadIdx.x * 4;
-  uint32_t w[4];
+  constexpr int PER = kPerRound<TY>;
+  const long long base = (long long)blockIdx.x * (kThreads * PER * kRounds) + threadIdx.x * PER;
+  Words<PER> w[kRounds];
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const long long i = base + (long long)r * (kThreads * 4);
-    w[r] = i + 4 <= n ? __ldcs(reinterpret_cast<const uint32_t*>(q + i)) : 0u;
+  for (int r = 0; r < kRounds; ++r) {
+    const long long i = base + (long long)r * (kThreads * PER);
+    if (i + PER <= n) w[r].Load(q + i);
   }
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const long long i = base + (long long)r * (kThreads * 4);
-    if (i + 4 <= n) {
-      float v[4], s, zp;
-      if (UNIFORM) SliceConsts(a, i, &s, &zp);
+  for (int r = 0; r < kRounds; ++r) {
+    const long long i = base + (long long)r * (kThreads * PER);
+    if (i + PER <= n) {
+      float v[PER], s, zp;
+      if (UNIFORM) {
+        // One scale for the thread's bytes.  byte -> float without a conversion or an integer add: a byte permute drops
+        // the byte into the low byte of the bit pattern of 2^23 (signed bytes are offset by 128 first, b ^ 0x80 = b + 128),
+        // which IS the float 2^23 + b; one exact subtraction takes 2^23 (+ 128) off again.  Then the same two roundings as
+        // everywhere: minus zero point, times scale (a zero point of 0 subtracts exactly, so both cases share the code).
+        SliceConsts(a, i, &s, &zp);
+        const float off = SIGNED ? 8388736.f : 8388608.f;  // 2^23 + 128 | 2^23
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const uint32_t byte = (w[r] >> (8 * b)) & 0xff;
-        if (!UNIFORM) SliceConsts(a, i + b, &s, &zp);
-        v[b] = __fmul_rn(__fsub_rn(SmallIntToFloat(SIGNED ? int(int8_t(byte)) : int(byte)), zp), s);
+        for (int j = 0; j < PER / 4; ++j) {
+          const uint32_t word = SIGNED ? (w[r].w[j] ^ 0x80808080u) : w[r].w[j];
+          v[4 * j + 0] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650));
+          v[4 * j + 1] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7651));
+          v[4 * j + 2] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7652));
+          v[4 * j + 3] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7653));
+        }
+#pragma unroll
+        for (int b = 0; b < PER; ++b) v[b] = __fmul_rn(__fsub_rn(__fsub_rn(v[b], off), zp), s);
+      } else {
+#pragma unroll
+        for (int b = 0; b < PER; ++b) {
+          const uint32_t byte = (w[r].w[b / 4] >> (8 * (b % 4))) & 0xff;
+          SliceConsts(a, i + b, &s, &zp);
+          v[b] = __fmul_rn(__fsub_rn(SmallIntToFloat(SIGNED ? int(int8_t(byte)) : int(byte)), zp), s);
+        }
       }
-      Store4<TY>(y + i, v);
+      StoreRound<TY>(y + i, v);
     } else {
       for (long long e = i; e < n; ++e) {
         float s, zp;
@@ -327,12 +374,13 @@ int LaunchDequantize(const void* q, void* y, long long n, const SliceArgs& a, cu
     DequantizeScalarKernel<TY, SIGNED><<<blocks, kThreads, 0, st>>>(qp, yp, n, a);
     return CheckLaunch("DequantizeScalarKernel");
   }
-  const long long groups = (n + kVec - 1) / kVec;
-  const bool uniform = a.nslice <= 1 || (a.inner % 4) == 0;  // a thread's four elements share a slice
+  constexpr long long kPerBlock = (long long)kThreads * kPerRound<TY> * kRounds;
+  const int grid = int((n + kPerBlock - 1) / kPerBlock);
+  const bool uniform = a.nslice <= 1 || (a.inner % kPerRound<TY>) == 0;  // a thread's elements of a round share a slice
   if (uniform)
-    DequantizeKernel<TY, SIGNED, true><<<GridFor(groups), kThreads, 0, st>>>(qp, yp, n, a);
+    DequantizeKernel<TY, SIGNED, true><<<grid, kThreads, 0, st>>>(qp, yp, n, a);
   else
-    DequantizeKernel<TY, SIGNED, false><<<GridFor(groups), kThreads, 0, st>>>(qp, yp, n, a);
+    DequantizeKernel<TY, SIGNED, false><<<grid, kThreads, 0, st>>>(qp, yp, n, a);
   return CheckLaunch("DequantizeKernel");
 }
 
@@ -516,27 +564,46 @@ __global__ void __launch_bounds__(kThreads) Fp8QuantizeKernel(const TX* __restri
   }
 }
 
+// y = T(float(x) * scale_inv[0]).  The layout of DequantizeKernel: 16-byte stores, whole sectors per warp instruction.
+// Two FP8 bytes convert to a pair of halves in one instruction (exact: every FP8 value is a half), then to fp32.
 template <typename TY, bool E4M3>
 __global__ void __launch_bounds__(kThreads) Fp8DequantizeKernel(const uint8_t* __restrict__ x, TY* __restrict__ y, long long n,
-                                                                const float* __restrict__ scale_inv, bool vec) {
+                                                                const float* __restrict__ scale_inv) {
+  constexpr int PER = kPerRound<TY>;
+  const float s = __ldg(scale_inv);
+  const long long base = (long long)blockIdx.x * (kThreads * PER * kRounds) + threadIdx.x * PER;
+  Words<PER> w[kRounds];
+#pragma unroll
+  for (int r = 0; r < kRounds; ++r) {
+    const long long i = base + (long long)r * (kThreads * PER);
+    if (i + PER <= n) w[r].Load(x + i);
+  }
+#pragma unroll
+  for (int r = 0; r < kRounds; ++r) {
+    const long long i = base + (long long)r * (kThreads * PER);
+    if (i + PER <= n) {
+      float v[PER];
+#pragma unroll
+      for (int j = 0; j < PER / 2; ++j) {
+        const uint32_t pair = (w[r].w[j / 2] >> (16 * (j % 2))) & 0xffffu;
+        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)pair, E4M3 ? __NV_E4M3 : __NV_E5M2);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+        v[2 * j] = __fmul_rn(f.x, s);
+        v[2 * j + 1] = __fmul_rn(f.y, s);
+      }
+      StoreRound<TY>(y + i, v);
+    } else {
+      for (long long e = i; e < n; ++e) y[e] = FromFloat<TY>(__fmul_rn(Fp8ToFloat<E4M3>(x[e]), s));
+    }
+  }
+}
+
+template <typename TY, bool E4M3>
+__global__ void __launch_bounds__(kThreads) Fp8DequantizeScalarKernel(const uint8_t* __restrict__ x, TY* __restrict__ y, long long n,
+                                                                      const float* __restrict__ scale_inv) {
   const float s = __ldg(scale_inv);
   const long long stride = (long long)gridDim.x * kThreads;
-  long long start = 0;
-  if (vec) {
-    const long long groups = n / kVec;
-    for (long long g = (long long)blockIdx.x * kThreads + threadIdx.x; g < groups; g += stride) {
-      uint4 t = __ldcs(reinterpret_cast<const uint4*>(x + g * kVec));
-      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-      float v[kVec];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) v[4 * j + b] = __fmul_rn(Fp8ToFloat<E4M3>(uint8_t((w[j] >> (8 * b)) & 0xff)), s);
-      Store16<TY>(y + g * kVec, v);
-    }
-    start = groups * kVec;
-  }
-  for (long long i = start + (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+  for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
     y[i] = FromFloat<TY>(__fmul_rn(Fp8ToFloat<E4M3>(x[i]), s));
 }
 
@@ -883,15 +950,21 @@ int itexb_fp8_dequantize(const void* x, int fp8_dtype, void* y, int y_dtype, int
   ITEXB_REQUIRE(scale_inv != nullptr && n >= 0, ITEXB_INVALID_ARGUMENT, "fp8_dequantize: bad arguments");
   if (n == 0) return ITEXB_OK;
   const bool vec = Aligned16(x) && Aligned16(y);
-  const long long work = vec ? (n + kVec - 1) / kVec : n;
-  const int blocks = int(std::max<long long>(1, std::min<long long>((work + kThreads - 1) / kThreads, (long long)SmCount() * 16)));
   cudaStream_t st = AsCuda(stream);
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   const bool e4 = fp8_dtype == ITEXB_DT_FP8_E4M3;
-#define ITEXB_FP8D(TY)                                                                                        \
-  do {                                                                                                        \
-    if (e4) Fp8DequantizeKernel<TY, true><<<blocks, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv, vec); \
-    else Fp8DequantizeKernel<TY, false><<<blocks, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv, vec);   \
+#define ITEXB_FP8D(TY)                                                                                                   \
+  do {                                                                                                                   \
+    if (vec) {                                                                                                           \
+      constexpr long long kPerBlock = (long long)kThreads * kPerRound<TY> * kRounds;                                     \
+      const int grid = int((n + kPerBlock - 1) / kPerBlock);                                                             \
+      if (e4) Fp8DequantizeKernel<TY, true><<<grid, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv);           \
+      else Fp8DequantizeKernel<TY, false><<<grid, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv);             \
+    } else {                                                                                                             \
+      const int blocks = int(std::min<long long>((n + kThreads - 1) / kThreads, (long long)SmCount() * 16));             \
+      if (e4) Fp8DequantizeScalarKernel<TY, true><<<blocks, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv);   \
+      else Fp8DequantizeScalarKernel<TY, false><<<blocks, kThreads, 0, st>>>(xp, static_cast<TY*>(y), n, scale_inv);     \
+    }                                                                                                                    \
   } while (0)
   if (y_dtype == ITEXB_DT_FLOAT) ITEXB_FP8D(float);
   else if (y_dtype == ITEXB_DT_BFLOAT16) ITEXB_FP8D(__nv_bfloat16);

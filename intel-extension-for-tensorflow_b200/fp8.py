@@ -271,6 +271,24 @@ class Fp8Dense:
         self.out_dtype = out_dtype
         self.transpose_b = weight_layout == "nk"
         self._dummy = torch.zeros(1, dtype=torch.bfloat16 if out_dtype == "bfloat16" else torch.float32, device=kernel.device)
+        self._nodes = {}    # the layer's kernel instances, one per node of its graph, kept across calls
+
+    def _quantize(self, t: torch.Tensor, index: int) -> torch.Tensor:
+        key = ("q", index, t.dtype)
+        if key not in self._nodes:
+            self._nodes[key] = ops.Op("Fp8Quantize", in_dtype=ops._TORCH_TO_DT[t.dtype], fp8_meta_index=index, fp8_dtype="E4M3")
+        return self._nodes[key](t, self.meta.amax_history[0], self.meta.scale)
+
+    def _matmul(self, xq, wq, bias):
+        from . import _lib as L
+        if "mm" not in self._nodes:
+            self._nodes["mm"] = ops.Op("Fp8Matmul", fp8_meta_index_a=0, fp8_meta_index_b=1, fp8_meta_index_c=-1, transpose_a=False,
+                                       transpose_b=self.transpose_b, use_bias=self.bias is not None, has_post_add=False,
+                                       sum_dtype=self.out_dtype, out_dtype=self.out_dtype, fp8_dtype_a="E4M3", fp8_dtype_b="E4M3",
+                                       fp8_dtype_c="")
+        m = self.meta
+        return self._nodes["mm"](xq, wq, bias, self._dummy, m.scale_inv, m.scale_inv, m.amax_history[0], m.scale,
+                                 dtypes={0: L.DT_INT8, 1: L.DT_INT8})
 
     def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0) -> torch.Tensor:
         """gather: a PeerGather (column-parallel layer, kernel kept as [N/world, K]): the product lands in slot `rank` of
@@ -279,9 +297,8 @@ class Fp8Dense:
         m = self.meta
         if update_meta:
             m.amax_and_scale_update()
-        amax_row0 = m.amax_history[0]
-        xq = ops.Fp8Quantize(x, amax_row0, m.scale, 0, "E4M3")
-        wq = ops.Fp8Quantize(self.kernel, amax_row0, m.scale, 1, "E4M3")
+        xq = self._quantize(x, 0)
+        wq = self._quantize(self.kernel, 1)
         if gather is not None:
             from . import _lib as L
             assert self.transpose_b and self.bias is None and self.out_dtype == "bfloat16", "the fused gather path serves [N,K] kernels, bf16 out"
@@ -291,6 +308,4 @@ class Fp8Dense:
                    peer_out=gather.peers(gather_index), status_word=gather.status)
             return out
         bias = self.bias if self.bias is not None else self._dummy
-        return ops.Fp8Matmul(xq, wq, bias, self._dummy, m.scale_inv, m.scale_inv, amax_row0, m.scale, 0, 1, -1,
-                             transpose_b=self.transpose_b, use_bias=self.bias is not None, sum_dtype=self.out_dtype,
-                             out_dtype=self.out_dtype)
+        return self._matmul(xq, wq, bias)

@@ -12,6 +12,7 @@ call (`load_ops_library._ITEXQuantizeV2(input=..., min_range=..., T=...)`, see
 itex/python/ops/load_ops_library.py:29-72).
 """
 import ctypes as C
+import weakref
 
 import numpy as np
 import torch
@@ -121,8 +122,12 @@ class Op:
         self._h = h
         self._outputs = {}
         self._temps = []
-        self._alloc_out_cb = L.ALLOC_OUTPUT_FN(self._allocate_output)
-        self._alloc_tmp_cb = L.ALLOC_TEMP_FN(self._allocate_temp)
+        # The callbacks reach the instance through a weak reference: a bound method kept on the instance would be a
+        # reference cycle, and the kernel instance would then live until some later garbage collection instead of
+        # being deleted with its last user.
+        ref = weakref.ref(self)
+        self._alloc_out_cb = L.ALLOC_OUTPUT_FN(lambda user, index, tp: ref()._allocate_output(user, index, tp))
+        self._alloc_tmp_cb = L.ALLOC_TEMP_FN(lambda user, nbytes, on_host, pp: ref()._allocate_temp(user, nbytes, on_host, pp))
         self._device = None
 
     def check(self, wait=True):

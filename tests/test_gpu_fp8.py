@@ -229,6 +229,13 @@ def test_fp8_cast_on_the_device_is_pinned_to_the_format_definition(fmt):
     t = F.table(fmt)
     back = host(K.fp8_dequantize(dev(np.arange(256, dtype=np.uint8)), one, L.DT_FLOAT, dt)).astype(np.float64)
     assert np.array_equal(np.isnan(back), np.isnan(t)) and np.array_equal(back[~np.isnan(t)], t[~np.isnan(t)])
+    # every result type, a length that leaves a ragged tail after whole 16-byte stores, an exact scale (every code x 0.5
+    # is a bf16 and a half): the paired conversion and the tail agree with the table
+    codes = np.tile(np.arange(256, dtype=np.uint8), 37)[:9301]
+    want = t[codes] * 0.5
+    for ydt in (L.DT_FLOAT, L.DT_BFLOAT16, L.DT_HALF):
+        back = host(K.fp8_dequantize(dev(codes), torch.full((1,), 0.5, device="cuda"), ydt, dt)).astype(np.float64)
+        assert np.array_equal(np.isnan(back), np.isnan(want)) and np.array_equal(back[~np.isnan(want)], want[~np.isnan(want)])
     # the matmul's FP8 output conversion goes through the same rule: identity weights, inputs chosen on ties
     if fmt == "E4M3":
         _, vals = F.finite_positive_codes(fmt)
