@@ -313,11 +313,15 @@ ITEXB_API int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream);
 
 /* Test hooks of the GEMM / convolution kernels' failure path; process-wide, read at every launch.  They have no
  * counterpart in the reference.  Keys:
- *   "gemm_wait_limit_cycles"  clock cycles a wait on a pipeline stage may take before the kernel gives up (the wait on a
- *                             whole accumulator gets twice that); 0 restores the default of 4e9 (about 2 s);
+ *   "gemm_wait_limit_cycles"  clock cycles the MMA issuer's wait on a pipeline stage may take before the kernel gives up
+ *                             (the waits behind it - a producer's on a stage's release, the epilogue's on a whole
+ *                             accumulator - get twice that); 0 restores the default of 4e9 (about 2 s);
  *   "gemm_skip_kblock"        the TMA producer of every CTA leaves out this k-block of its first tile - a barrier that
  *                             nothing completes, made on the host's request, so that a test can watch a wait run out
- *                             (status word 2, the MMA issuer's role), the kernel return and the next launch work; -1: off.
+ *                             (status word 2, the MMA issuer's role), the kernel return and the next launch work; -1: off;
+ *   "gemm_cta_pair"           1: plain GEMMs with 256-column tiles and an even number of tile rows run as pairs of CTAs
+ *                             (a cluster of two per 256 x 256 tile, each CTA loading half of the B tile); 0: never;
+ *                             -1: the launch decides (the default).  Results are bit-identical either way.
  * Unknown keys give ITEXB_NOT_FOUND. */
 ITEXB_API int itexb_debug_set(const char* key, int64_t value);
 

@@ -66,11 +66,14 @@ constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz; the defa
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrSmemAlign = 4 };
 
-template <int BN> struct Cfg {
+// CG = 2: a pair of CTAs (a cluster of two) works on one 256 x BN tile.  Each CTA holds 128 rows of A, HALF of the B
+// tile and the accumulators of its own 128 rows; the tensor cores of the pair read both halves of B, so a CTA fetches a
+// third less per k-block and the ring is deeper.
+template <int BN, int CG = 1> struct Cfg {
   static constexpr int kABytes = kBM * kBK;
-  static constexpr int kBBytes = BN * kBK;
+  static constexpr int kBBytes = (BN / CG) * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128), 8 (64)
+  static constexpr int kStages = (192 * 1024) / kStageBytes;   // 4 (BN=256), 6 (128; 256 as a pair), 8 (64)
   // Accumulators in tensor memory: 2 stages of SUP sub-tiles of BN columns (a power of two >= 32, at most the 512 there are).
   template <int SUP> static constexpr int kTmemCols = 2 * BN * SUP < 32 ? 32 : 2 * BN * SUP;
   static constexpr int kSumBars = kEpilogueWarps * 4;          // one per epilogue warp and staging buffer (summand loads)
@@ -127,11 +130,43 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile
   }
 }
 
+// ---- CTA pairs (CG = 2) ----
+__device__ __forceinline__ uint32_t ClusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t MapToCta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// Arrival on a barrier of either CTA of the pair.  What it publishes are tensor-memory reads, ordered by the
+// tcgen05 fence before it, so the default semantics do (a cluster-scope release here was measured to cost the
+// epilogue warps about a microsecond per tile).
+__device__ __forceinline__ void MbarArriveCluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void ClusterSync() {
+  __syncwarp();  // the aligned forms want the whole warp at the same instruction
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 template <int N> __device__ __forceinline__ void CpAsyncWaitGroup() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void TmaLoad3d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// The same into this CTA's shared memory, but the bytes are counted on a barrier that may live in the pair's other CTA
+// (`bar` is a shared::cluster address).
+__device__ __forceinline__ void TmaLoad3dPair(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
       "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
@@ -146,23 +181,50 @@ __device__ __forceinline__ void TmaLoadIm2col(uint32_t dst, const void* tmap, ui
       : "memory");
 }
 
-__device__ __forceinline__ void TmemAlloc(uint32_t slot_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+// CG = 2: one warp of EACH CTA of the pair issues these, with the same slot offset and column count.
+template <int CG> __device__ __forceinline__ void TmemAlloc(uint32_t slot_smem, uint32_t cols) {
+  if (CG == 2) asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+  else asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void TmemRelinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+template <int CG> __device__ __forceinline__ void TmemRelinquish() {
+  if (CG == 2) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void TmemDealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+template <int CG> __device__ __forceinline__ void TmemDealloc(uint32_t taddr, uint32_t cols) {
+  if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcCommit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Pair MMAs: one arrival on the barrier at shared::cluster address `bar` (either CTA's) once every MMA issued so far
+// has completed in both CTAs.
+__device__ __forceinline__ void TcCommitPair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 
-template <bool F8>
+template <bool F8, int CG = 1>
 __device__ __forceinline__ void UmmaSS(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (CG == 2) {
+    // 256 x BN x 32 across the pair: rows 0-127 from this CTA's A tile into its tensor memory, rows 128-255 from the
+    // other CTA's into that one's; B's rows 0 .. BN/2-1 from this CTA's shared memory, the rest from the other's.
+    if (F8) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+          "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+          "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+          : "memory");
+    } else {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+          "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+          "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+          : "memory");
+    }
+    return;
+  }
   if (F8) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -491,7 +553,7 @@ struct EpilogueCtx {
 // slices into a swizzled staging tile (32 rows of 64 or 32 bytes) that one TMA store then
 // writes; edges are clipped by the tensor map.  Without TMA-legal output rows the slices go
 // straight to global memory.
-template <int BN, bool F8, int OK, int MODE, int SUP>
+template <int BN, bool F8, int OK, int MODE, int SUP, int CG>
 __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, const CUtensorMap* tma_sum, uint8_t* s_stage,
                                              float* s_par, uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint64_t* par_bar,
                                              uint64_t* sum_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane, int tiles_m,
@@ -509,7 +571,15 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   constexpr int W = 4 / SUP;            // warps of a row quarter that share one sub-tile
   const int j = sub / W;                // this warp's sub-tile within every accumulator stage
   const int c_first = sub % W;          // ... and its first block there; it takes every W-th
-  const int tiles_m_real = (g.m + kBM - 1) / kBM;  // tiles_m counts super rows of SUP tile rows each
+  const int tiles_m_real = (g.m + kBM - 1) / kBM;  // tiles_m counts super rows of SUP * CG tile rows each
+  // CTA pairs: the pair's unit is two consecutive tile rows, this CTA's is number `rank` of them; the accumulator-empty
+  // barriers the MMA issuer waits on are those of the pair's first CTA.
+  const int rank = CG == 2 ? int(ClusterCtaRank()) : 0;
+  const int tfirst = int(blockIdx.x) / CG, tstep = int(gridDim.x) / CG;
+  auto release_acc = [&](int a) {  // one arrival on accumulator stage a's empty barrier (the first CTA's, in a pair)
+    if (CG == 2) MbarArriveCluster(MapToCta(SmemAddr(&tmem_empty_bar[a]), 0));
+    else MbarArrive(SmemAddr(&tmem_empty_bar[a]));
+  };
   constexpr bool PLAIN = MODE == kEpPlain, SUM8 = MODE == kEpSum8;
   const bool tma_store = MODE != kEpGeneral || g.tma_store;
   EpilogueCtx e;
@@ -563,8 +633,8 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     TcFenceBefore();
     __syncwarp();
     if (lane == 0) {
-      MbarArrive(SmemAddr(&tmem_empty_bar[0]));
-      MbarArrive(SmemAddr(&tmem_empty_bar[1]));
+      release_acc(0);
+      release_acc(1);
     }
   }
 
@@ -582,7 +652,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     TmaLoad3d(SmemAddr(e.stage + b * buf_bytes), tma_sum, bar, col0 * esz, brow0, bbt);
   };
 
-  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+  for (int t = tfirst; t < num_tiles; t += tstep) {
     int tm, tn, bt;
     TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
     if (staged && tn != last_tn) {
@@ -612,7 +682,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     // on one of them.  For 64-column tiles that gives a warp whole rows of its sub-tile (one TMA store of full rows per
     // warp and stage) where a single tile per stage left it a 16-column fragment.
     do {
-    const int tmr = tm * SUP + j;
+    const int tmr = (tm * SUP + j) * CG + rank;
     if (tmr >= tiles_m_real) break;  // the MMA issuer left these columns untouched (still armed)
     const int row0 = tmr * kBM + q * 32;  // first row of this warp's 32-row block
     const bool row_ok = row0 + lane < g.m;
@@ -654,10 +724,10 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             int ncol0 = -1, nrow0 = 0, nbt = 0;
             if (c + W < nblocks) {
               ncol0 = col0 + bcols * W; nrow0 = row0; nbt = bt;
-            } else if (t + int(gridDim.x) < num_tiles) {
+            } else if (t + tstep < num_tiles) {
               int ntm, ntn;
-              TileCoords(t + int(gridDim.x), g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
-              nrow0 = (ntm * SUP + j) * kBM + q * 32;  // < m implies that the tile row exists
+              TileCoords(t + tstep, g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
+              nrow0 = ((ntm * SUP + j) * CG + rank) * kBM + q * 32;  // < m implies that the tile row exists
               if (nrow0 < g.m && ntn * BN + c_first * bcols < g.n) ncol0 = ntn * BN + c_first * bcols;
             }
             if (ncol0 >= 0) {
@@ -848,10 +918,11 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     TcFenceBefore();
     __syncwarp();
     if (lane == 0) {
-      MbarArrive(SmemAddr(&tmem_empty_bar[acc]));  // one arrival per warp: all its lanes have read their rows
-      if (staged && tiles_n > 1 && t + int(gridDim.x) < num_tiles) {  // one tile column: the parameters never change
+      // one arrival per warp: all its lanes have read their rows
+      release_acc(acc);
+      if (staged && tiles_n > 1 && t + tstep < num_tiles) {  // one tile column: the parameters never change
         int ntm, ntn, nbt;
-        TileCoords(t + int(gridDim.x), g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
+        TileCoords(t + tstep, g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
         if (ntn != tn) MbarArrive(SmemAddr(&par_bar[1]));  // this warp is done with the staged parameters
       }
     }
@@ -870,15 +941,17 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
 // The kernel.  CONV selects how the producer addresses the A operand: a plain [m,k]
 // matrix (2-D map) or NHWC pixels gathered per filter tap (see conv section below).
 // ---------------------------------------------------------------------------------------
-template <int BN, bool F8, int CONV, int SUP>
+template <int BN, bool F8, int CONV, int SUP, int CG>
 __global__ void __launch_bounds__(CONV == kConvGather ? kThreadsConv : kThreads, 1)
 GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
            const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a_tail,
            const __grid_constant__ CUtensorMap tma_b_tail, const __grid_constant__ CUtensorMap tma_sum, const __grid_constant__ GemmArgs g) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CG>;
+  static_assert(CG == 1 || (CG == 2 && CONV == kConvNone && SUP == 1), "CTA pairs serve plain GEMMs, one tile per accumulator stage");
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((SmemAddr(smem) & 1023u) != 0) {
     // the swizzled operand tiles need a 1024-byte aligned base; refuse rather than compute garbage
+    // (the offset is the same in every CTA of the grid, so a pair leaves together)
     if (threadIdx.x == 0 && g.status_word != nullptr) atomicCAS(g.status_word, 0, kErrSmemAlign);
     return;
   }
@@ -900,7 +973,9 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   static_assert(2 * BN * SUP <= 512, "tensor memory has 512 columns");
   static_assert(CONV != kConvGather || SUP == 1, "the cp.async gather variant walks single tiles");
   const int tiles_m_real = (g.m + kBM - 1) / kBM;
-  const int tiles_m = (tiles_m_real + SUP - 1) / SUP;  // super rows: the unit of the tile walk is SUP consecutive tile rows
+  const int tiles_m = (tiles_m_real + SUP * CG - 1) / (SUP * CG);  // super rows: the unit of the tile walk is SUP (CG) consecutive tile rows
+  const int rank = CG == 2 ? int(ClusterCtaRank()) : 0;  // this CTA's place in its pair
+  const int tfirst = int(blockIdx.x) / CG, tstep = int(gridDim.x) / CG;
   const int tiles_n = (g.n + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n * g.batch;
   // bytes of K per k-block: 128, or in the im2col path 64 / 32 when a filter tap has that many (padded) channels
@@ -914,7 +989,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
     for (int a = 0; a < 2; ++a) {
       MbarInit(SmemAddr(&tmem_full_bar[a]), 1);
-      MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueWarps);
+      MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueWarps * CG);  // a pair's issuer waits for both CTAs' epilogue warps
       MbarInit(SmemAddr(&par_bar[a]), kEpilogueWarps);
     }
     for (int i = 0; i < C::kSumBars; ++i) MbarInit(SmemAddr(&sum_bar[i]), 1);
@@ -923,11 +998,12 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 2) {
-    TmemAlloc(SmemAddr(tmem_slot), C::template kTmemCols<SUP>);
-    TmemRelinquish();
+    TmemAlloc<CG>(SmemAddr(tmem_slot), C::template kTmemCols<SUP>);
+    TmemRelinquish<CG>();
   }
   TcFenceBefore();
   __syncthreads();
+  if (CG == 2) ClusterSync();  // the other CTA's barriers are initialised before anything signals them
   TcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
   // Programmatic dependent launch: the set-up above (barriers, TMEM allocation) may run while the previous kernel of
@@ -941,12 +1017,12 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = tfirst; t < num_tiles && ok; t += tstep) {
       int tms, tn, bt;
       TileCoords(t, g, tiles_m, tiles_n, &tms, &tn, &bt);
       for (int j = 0; j < SUP && ok; ++j) {
-      const int tm = tms * SUP + j;
-      if (tm >= tiles_m_real) break;
+      const int tm = (tms * SUP + j) * CG + rank;
+      if (CG == 1 && tm >= tiles_m_real) break;  // (a pair always loads: rows past the end read as zeros)
       int w0 = 0, h0 = 0, n0 = 0, c0 = 0, kx = 0, ky = 0;  // im2col: base position of the tile's first pixel, position in K
       if (CONV == kConvIm2col) {
         const int pix = tm * kBM;
@@ -956,9 +1032,9 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         h0 = (rest - n0 * g.oh) * g.stride_h - g.pad_top;
       }
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit);
+        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit_acc);
         if (!ok) break;
-        if (kb == g.debug_skip_kb && t == int(blockIdx.x) && j == 0) {
+        if (CG == 1 && kb == g.debug_skip_kb && t == int(blockIdx.x) && j == 0) {
           // Test hook: this k-block never arrives (neither its expect_tx nor its copies are issued), so the MMA issuer's
           // wait on it runs out and the kernel has to take its give-up path with nothing of this stage in flight.
           if (CONV == kConvIm2col) {
@@ -968,8 +1044,18 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
           continue;
         }
-        const uint32_t fb = SmemAddr(&full_bar[stage]);
         uint8_t* sa = smem + stage * C::kStageBytes;
+        if (CG == 2) {
+          // Both CTAs' copies are counted on the first CTA's barrier, which its producer arms for the bytes of both.
+          const uint32_t fb = MapToCta(SmemAddr(&full_bar[stage]), 0);
+          const bool tail = g.tail_box != 0 && kb == num_kb - 1;
+          if (rank == 0) MbarArriveExpectTx(SmemAddr(&full_bar[stage]), tail ? uint32_t(2 * (kBM + BN / 2) * g.tail_box) : uint32_t(2 * C::kStageBytes));
+          TmaLoad3dPair(SmemAddr(sa), tail ? &tma_a_tail : &tma_a, fb, kb * kBK, tm * kBM, bt);
+          TmaLoad3dPair(SmemAddr(sa + C::kABytes), tail ? &tma_b_tail : &tma_b, fb, kb * kBK, tn * BN + rank * (BN / 2), bt);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          continue;
+        }
+        const uint32_t fb = SmemAddr(&full_bar[stage]);
         if (CONV == kConvGather) {
           MbarArriveExpectTx(fb, C::kBBytes);  // the A tile is gathered by the last four warps
         } else if (CONV == kConvIm2col) {
@@ -997,20 +1083,27 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       }
       }  // sub-tiles
     }
+    if (CG == 2 && ok) {
+      // The issuer's releases of the last stages arrive from the other CTA: this CTA's shared memory has to outlive them.
+      for (int i = 0; i < C::kStages && ok; ++i) {
+        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit_acc);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
     if (!ok) {
       // Copies already issued land within microseconds; give them a bounded ~200 us
       // before the CTA tears its shared memory down.
       const long long t0 = clock64();
       while (clock64() - t0 < 400000) {}
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1 && lane == 0 && rank == 0) {
     // ---------------- MMA issuer ----------------
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = tfirst; t < num_tiles && ok; t += tstep) {
       // Without preset the first use of each accumulator stage finds its barrier "already released" (parity trick);
       // with preset it waits for the epilogue warps' arming of the stage, one phase earlier throughout.
       ok = MbarWait(SmemAddr(&tmem_empty_bar[acc]), g.preset ? acc_phase : acc_phase ^ 1, abort_flag, g.status_word, kErrMma, g.wait_limit);
@@ -1035,22 +1128,34 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
           const uint64_t a_desc = UmmaDescNarrow(SmemAddr(sa), narrow);
           const uint64_t b_desc = UmmaDescNarrow(SmemAddr(sa + C::kABytes), narrow);
           for (int k = 0; k < narrow / kUmmaK; ++k)
-            UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
+            UmmaSS<F8, CG>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
                        ((kb | k) != 0 || g.preset) ? 1u : 0u);
         } else {
           const uint64_t a_desc = UmmaDescSw128(SmemAddr(sa));
           const uint64_t b_desc = UmmaDescSw128(SmemAddr(sa + C::kABytes));
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k)
-            UmmaSS<F8>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
+            UmmaSS<F8, CG>(d_tmem, a_desc + uint64_t(k * (kUmmaK >> 4)), b_desc + uint64_t(k * (kUmmaK >> 4)), g.idesc,
                        ((kb | k) != 0 || g.preset) ? 1u : 0u);
         }
-        TcCommit(SmemAddr(&empty_bar[stage]));  // stage reusable once these MMAs have read it
+        // stage reusable once these MMAs have read it (in both CTAs of a pair)
+        if (CG == 2) {
+          TcCommitPair(SmemAddr(&empty_bar[stage]));
+          TcCommitPair(MapToCta(SmemAddr(&empty_bar[stage]), 1));
+        } else {
+          TcCommit(SmemAddr(&empty_bar[stage]));
+        }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
       }  // sub-tiles
       if (!ok) break;
-      TcCommit(SmemAddr(&tmem_full_bar[acc]));  // all sub-tile accumulators of this stage complete
+      // all sub-tile accumulators of this stage complete
+      if (CG == 2) {
+        TcCommitPair(SmemAddr(&tmem_full_bar[acc]));
+        TcCommitPair(MapToCta(SmemAddr(&tmem_full_bar[acc]), 1));
+      } else {
+        TcCommit(SmemAddr(&tmem_full_bar[acc]));
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -1102,7 +1207,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       int ci = j * 16, kx = 0, ky = 0;
       while (ci >= g.conv_c) { ci -= g.conv_c; if (++kx == g.kw) { kx = 0; ++ky; } }
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit);
+        ok = MbarWait(SmemAddr(&empty_bar[stage]), phase ^ 1, abort_flag, g.status_word, kErrProducer, g.wait_limit_acc);
         if (!ok) break;
         const uint32_t dst = SmemAddr(smem + stage * C::kStageBytes) + dst_off;
         const uint32_t tap_off = uint32_t((ky * g.dil_h * g.conv_w + kx * g.dil_w) * g.conv_c + ci);
@@ -1139,42 +1244,45 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     // ---------------- epilogue ----------------
 #define ITEXB_EP_ARGS g, &tma_out, &tma_sum, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, sum_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles
     switch (g.out_kind) {
-      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral, SUP>(ITEXB_EP_ARGS); break;
+      case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS); break;
       case kOutF32:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF32, kEpPlain, SUP>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutF32, kEpGeneral, SUP>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF32, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutF32, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutBF16:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutBF16, kEpPlain, SUP>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutBF16, kEpGeneral, SUP>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutBF16, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutBF16, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutF16:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF16, kEpPlain, SUP>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutF16, kEpGeneral, SUP>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF16, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutF16, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutS32:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS32, kEpPlain, SUP>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutS32, kEpGeneral, SUP>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS32, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutS32, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutU8:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutU8, kEpPlain, SUP>(ITEXB_EP_ARGS);
-        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutU8, kEpSum8, SUP>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutU8, kEpGeneral, SUP>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutU8, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutU8, kEpSum8, SUP, CG>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutU8, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutS8:
-        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS8, kEpPlain, SUP>(ITEXB_EP_ARGS);
-        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutS8, kEpSum8, SUP>(ITEXB_EP_ARGS);
-        else EpilogueLoop<BN, F8, kOutS8, kEpGeneral, SUP>(ITEXB_EP_ARGS);
+        if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS8, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutS8, kEpSum8, SUP, CG>(ITEXB_EP_ARGS);
+        else EpilogueLoop<BN, F8, kOutS8, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
-      default: EpilogueLoop<BN, F8, kOutFP8, kEpGeneral, SUP>(ITEXB_EP_ARGS); break;
+      default: EpilogueLoop<BN, F8, kOutFP8, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS); break;
     }
   }
 
   TcFenceBefore();
   __syncthreads();
+  // A pair leaves together: neither CTA's shared memory or tensor memory goes away while the other may still signal
+  // a barrier in it or have MMAs in flight on it.
+  if (CG == 2) ClusterSync();
   if (warp == 2) {
     TcFenceAfter();
-    TmemDealloc(tmem_base, C::template kTmemCols<SUP>);
+    TmemDealloc<CG>(tmem_base, C::template kTmemCols<SUP>);
   }
 }
 
@@ -1200,20 +1308,39 @@ EncodeTiledFn GetEncodeTiled() {
   return fn;
 }
 
-template <int BN, bool F8, int CONV, int SUP>
+template <int BN, bool F8, int CONV, int SUP, int CG = 1>
 int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tat, const CUtensorMap& tbt,
            const CUtensorMap& ts, const GemmArgs& g, cudaStream_t st) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CG>;
+  const unsigned threads = CONV == kConvGather ? kThreadsConv : kThreads;
   // The opt-in shared-memory size is a per-device function attribute; set it when the device changes.
   static thread_local int last_dev = -1;
+  static thread_local int max_pairs = 0;  // CG = 2: pairs of CTAs the device runs at once
   int dev = 0;
   ITEXB_CUDA(cudaGetDevice(&dev));
   if (dev != last_dev) {
-    ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8, CONV, SUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    ITEXB_CUDA(cudaFuncSetAttribute(GemmKernel<BN, F8, CONV, SUP, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    if (CG == 2) {
+      cudaLaunchConfig_t q{};
+      q.gridDim = dim3(unsigned(SmCount() & ~1));
+      q.blockDim = dim3(threads);
+      q.dynamicSmemBytes = C::kSmemBytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int n = 0;
+      ITEXB_CUDA(cudaOccupancyMaxActiveClusters(&n, GemmKernel<BN, F8, CONV, SUP, CG>, &q));
+      ITEXB_REQUIRE(n >= 1, ITEXB_FAILED_PRECONDITION, "GemmKernel: the device cannot co-schedule a pair of CTAs");
+      max_pairs = n;
+    }
     last_dev = dev;
   }
-  const int tiles = (((g.m + kBM - 1) / kBM + SUP - 1) / SUP) * ((g.n + BN - 1) / BN) * g.batch;
-  const int grid = std::max(1, std::min(tiles, SmCount()));
+  const int tiles = (((g.m + kBM - 1) / kBM + SUP * CG - 1) / (SUP * CG)) * ((g.n + BN - 1) / BN) * g.batch;
+  const int grid = CG == 2 ? 2 * std::max(1, std::min(tiles, max_pairs)) : std::max(1, std::min(tiles, SmCount()));
   // Launched with programmatic stream serialization (ITEXB_PDL=0 turns it off): back-to-back GEMM launches of a
   // layer graph overlap one kernel's set-up with the tail of the one before.
   static const bool pdl = [] {
@@ -1222,15 +1349,26 @@ int Launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   }();
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(unsigned(grid));
-  cfg.blockDim = dim3(unsigned(CONV == kConvGather ? kThreadsConv : kThreads));
+  cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (CG == 2) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV, SUP>, ta, tb, to, tat, tbt, ts, g));
+  cfg.numAttrs = unsigned(na);
+  ITEXB_CUDA(cudaLaunchKernelEx(&cfg, GemmKernel<BN, F8, CONV, SUP, CG>, ta, tb, to, tat, tbt, ts, g));
   return CheckLaunch("GemmKernel");
 }
 
@@ -1311,7 +1449,7 @@ static int EncodeOutputMap(CUtensorMap* map, void* base, int64_t m, int64_t n, i
   return ITEXB_OK;
 }
 
-uint32_t MakeInstrDesc(int a_dtype, int b_dtype, int bn) {
+uint32_t MakeInstrDesc(int a_dtype, int b_dtype, int bn, int rows) {
   const bool f8 = IsFp8(a_dtype);
   uint32_t a_fmt, b_fmt, c_fmt;
   if (f8) {
@@ -1324,8 +1462,8 @@ uint32_t MakeInstrDesc(int a_dtype, int b_dtype, int bn) {
     c_fmt = 2u;  // s32 accumulate
   }
   // [4,6) D format, [7,10) A format, [10,13) B format, bits 15/16 = 0: both operands K-major,
-  // [17,23) N>>3, [24,29) M>>4.
-  return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+  // [17,23) N>>3, [24,29) M>>4 (128 rows, or 256 across a pair of CTAs).
+  return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(rows >> 4) << 24);
 }
 
 // floor(x / d) for 0 <= x < 2^31 as umulhi(x, mul) >> shift, with mul = ceil(2^(32 + shift) / d) and
@@ -1377,7 +1515,33 @@ long long GemmWaitLimitCycles() {
   return limit > 0 ? limit : kWaitLimitCycles;
 }
 
-int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail) {
+// A pair of CTAs per 256 x 256 tile (each loads half of B) for plain GEMMs that have enough such tiles and write 4-byte
+// outputs.  Measured on B200, pair against single: 8192^3 -> f32 0.350-0.358 ms against 0.373-0.395 (1.03 of the
+// library's kernel instead of 0.96-0.98); 12288 x 4096 x 1024 -> f32 59.8 us against 64.0, raw accumulators 57.1
+// against 65.7; but -> u8 53.1 against 49.7 and -> bf16 54.7 against 51.6 (the same 6-7 % at 12288 x 1024 x 4096 and
+// 12288 x 3072 x 1024): the pair's issuer waits for the slower of two epilogues, which only the launches whose
+// epilogue is bound by its stores win back through the third less operand traffic.
+// ITEXB_GEMM_CTA_PAIR=0 (or itexb_debug_set("gemm_cta_pair", 0)) turns it off, 1 takes it wherever the kernel allows
+// (tests and measurements), -1 is this rule.
+static std::atomic<int> g_cta_pair{-2};  // -2: not set through itexb_debug_set, the environment decides
+int PickCtaGroup(int m, int n, int batch, int bn, bool gather, int out_esz) {
+  static const int from_env = [] {
+    const char* e = std::getenv("ITEXB_GEMM_CTA_PAIR");
+    return e != nullptr ? std::atoi(e) : -1;
+  }();
+  const int set = g_cta_pair.load(std::memory_order_relaxed);
+  const int forced = set != -2 ? set : from_env;
+  if (forced == 0 || bn != 256 || gather) return 1;
+  if (g_debug_skip_kb.load(std::memory_order_relaxed) >= 0) return 1;  // the test hook lives in the single-CTA producer
+  const int tiles_m_real = (m + kBM - 1) / kBM;
+  if (tiles_m_real % 2 != 0) return 1;  // every pair gets two real tile rows
+  if (forced == 1) return 2;
+  if (out_esz != 4) return 1;
+  const long long pairs = (long long)(tiles_m_real / 2) * ((n + bn - 1) / bn) * std::max(batch, 1);
+  return pairs >= 2ll * (SmCount() / 2) ? 2 : 1;
+}
+
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail, int cg) {
   const CUtensorMap& tat = tail != nullptr ? tail->a : ta;  // placeholders when there is no narrow last k-block
   const CUtensorMap& tbt = tail != nullptr ? tail->b : tb;
   g.tail_box = (tail != nullptr && g.conv_mode == kConvNone) ? tail->box : 0;
@@ -1403,9 +1567,17 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   // with K = 64 26.8 -> 20.6 us, the 7x7x3 stem's GEMM (K = 160) 120.6 -> 99.8 us - and costs a few per cent where the
   // main loop matters (K = 256: 27.2 -> 28.9 us; 3x3 convolutions of 64 channels, K = 576: 72.7 -> 76.4 us), because the
   // MMA issuer then waits for a whole stage of sub-tiles to be drained.
-  const int sup = PickSup(bn, f8 || g.conv_mode == kConvGather || g.k > 192, tiles_m_real, tiles_n, g.batch);
-  const int tiles_m = (tiles_m_real + sup - 1) / sup;  // the tile walk's rows are super rows of `sup` tile rows
+  const int sup = cg == 2 ? 1 : PickSup(bn, f8 || g.conv_mode == kConvGather || g.k > 192, tiles_m_real, tiles_n, g.batch);
+  const int tiles_m = (tiles_m_real + sup * cg - 1) / (sup * cg);  // the tile walk's rows are super rows of `sup` (`cg`) tile rows
   g.group_m = tiles_n >= 32 ? 32 : (tiles_n <= 16 ? 8 : 16);
+  if (cg == 2) g.group_m = tiles_n >= 32 ? 16 : 8;  // rows of pairs (8192^3: 16 -> 0.350 ms, 8 -> 0.356, 32 -> 0.415, 4 -> 0.377)
+  {
+    static const int forced_group = [] {  // ITEXB_GEMM_GROUP_M: measurements
+      const char* e = std::getenv("ITEXB_GEMM_GROUP_M");
+      return e != nullptr ? std::atoi(e) : 0;
+    }();
+    if (forced_group > 0) g.group_m = forced_group;
+  }
   g.div_per_batch = MakeFastDiv(uint32_t(tiles_m) * uint32_t(tiles_n));
   g.div_per_group = MakeFastDiv(uint32_t(g.group_m) * uint32_t(tiles_n));
   g.div_group_m = MakeFastDiv(uint32_t(g.group_m));
@@ -1442,6 +1614,12 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
     if (bn == 256) return Launch<256, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
     if (bn == 128) return Launch<128, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
     return Launch<64, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
+  }
+  if (cg == 2) {
+    ITEXB_REQUIRE(bn == 256 && g.conv_mode == kConvNone && tiles_m_real % 2 == 0 && g.num_peers == 0, ITEXB_INTERNAL,
+                  "LaunchGemm: a CTA pair was asked for a launch it does not serve");
+    if (f8) return Launch<256, true, kConvNone, 1, 2>(ta, tb, to, tat, tbt, tsum, g, st);
+    return Launch<256, false, kConvNone, 1, 2>(ta, tb, to, tat, tbt, tsum, g, st);
   }
   if (f8) {
     if (bn == 256) return Launch<256, true, kConvNone, 1>(ta, tb, to, tat, tbt, tsum, g, st);
@@ -1500,6 +1678,9 @@ extern "C" int itexb_debug_set(const char* key, int64_t value) {
   if (k == "gemm_wait_limit_cycles") {
     ITEXB_REQUIRE(value >= 0, ITEXB_INVALID_ARGUMENT, "debug_set: gemm_wait_limit_cycles must be >= 0 (0 restores the default)");
     g_wait_limit_cycles.store(value, std::memory_order_relaxed);
+  } else if (k == "gemm_cta_pair") {
+    ITEXB_REQUIRE(value >= -1 && value <= 1, ITEXB_INVALID_ARGUMENT, "debug_set: gemm_cta_pair must be -1 (automatic), 0 (never) or 1 (wherever possible)");
+    g_cta_pair.store(int(value), std::memory_order_relaxed);
   } else if (k == "gemm_skip_kblock") {
     ITEXB_REQUIRE(value >= -1 && value < (1ll << 30), ITEXB_INVALID_ARGUMENT, "debug_set: gemm_skip_kblock must be -1 (off) or a k-block index");
     g_debug_skip_kb.store(int(value), std::memory_order_relaxed);
@@ -1536,13 +1717,14 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   }
   CUtensorMap ta, tb;
   const int bn = PickBN(p->n);
+  const int cg = PickCtaGroup(p->m, p->n, int(batch), bn, p->num_peers > 0, p->ep.raw_acc ? 4 : DtypeSize(p->out_dtype));  // 2: each CTA of a pair loads half of a B tile
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, p->a, p->m, p->k, p->lda, kBM, batch, p->stride_a));
-  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->b, p->n, p->k, p->ldb, bn, batch, p->stride_b));
+  ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->b, p->n, p->k, p->ldb, bn / cg, batch, p->stride_b));
   TailMaps tail;
   tail.box = TailBox(p->k);
   if (tail.box != 0) {
     ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.a, p->a, p->m, p->k, p->lda, kBM, batch, p->stride_a, tail.box));
-    ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.b, p->b, p->n, p->k, p->ldb, bn, batch, p->stride_b, tail.box));
+    ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tail.b, p->b, p->n, p->k, p->ldb, bn / cg, batch, p->stride_b, tail.box));
   }
   GemmArgs g{};
   g.batch = int(batch);
@@ -1552,7 +1734,7 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
   g.out = p->out; g.ldo = p->ldo;
   g.ep = p->ep;
   g.status_word = p->status_word;
-  g.idesc = MakeInstrDesc(p->a_dtype, p->b_dtype, bn);
+  g.idesc = MakeInstrDesc(p->a_dtype, p->b_dtype, bn, kBM * cg);
   if (p->num_peers > 0) {
     ITEXB_REQUIRE(p->num_peers <= ITEXB_MAX_PEERS && p->peer_out != nullptr, ITEXB_INVALID_ARGUMENT, "gemm: num_peers must be at most %d with peer_out given",
                   ITEXB_MAX_PEERS);
@@ -1566,5 +1748,5 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
       g.peer_out[i] = p->peer_out[i];
     }
   }
-  return LaunchGemm(ta, tb, g, bn, f8, AsCuda(stream), tail.box != 0 ? &tail : nullptr);
+  return LaunchGemm(ta, tb, g, bn, f8, AsCuda(stream), tail.box != 0 ? &tail : nullptr, cg);
 }

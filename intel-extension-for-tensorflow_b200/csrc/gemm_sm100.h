@@ -22,8 +22,9 @@ struct GemmArgs {
   itexb_epilogue_t ep;
   int* status_word;     // set non-zero when a bounded wait expired
   long long wait_limit; // cycles a wait on one pipeline stage may take before the kernel gives up (set by LaunchGemm)
-  long long wait_limit_acc;  // the same for the epilogue's wait on a whole accumulator: twice as long, so that the role
-                             // that is actually starved reports first (set by LaunchGemm)
+  long long wait_limit_acc;  // the same for the waits that sit behind the MMA issuer - the epilogue's on a whole accumulator,
+                             // the producers' on a stage's release: twice as long, so that the role that is actually
+                             // starved reports first (set by LaunchGemm)
   int debug_skip_kb;    // test hook: the producer leaves out this k-block of each CTA's first tile (-1: none; set by LaunchGemm)
   unsigned idesc;       // tcgen05 instruction descriptor
   int vec_store;        // output rows are 16-byte aligned (set by LaunchGemm)
@@ -66,9 +67,11 @@ int EncodeOperandMap(CUtensorMap* map, const void* base, int64_t rows, int64_t k
 // is half or a quarter of the shared-memory fill and MMA work.  TailBox returns 64, 32, or 0 when K has no such tail.
 struct TailMaps { CUtensorMap a, b; int box; };
 int TailBox(int64_t k);
-unsigned MakeInstrDesc(int a_dtype, int b_dtype, int bn);
+unsigned MakeInstrDesc(int a_dtype, int b_dtype, int bn, int rows = 128);
 int PickBN(int n);
-int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail = nullptr);
+// cg = 2: a pair of CTAs per 256 x bn tile; `tb` (and the tail's) then has boxes of bn / 2 rows and g.idesc 256 rows.
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn, bool f8, cudaStream_t st, const TailMaps* tail = nullptr,
+               int cg = 1);
 int ValidateEpilogue(const char* who, const itexb_epilogue_t& ep, int out_dtype, bool f8, int n);
 
 }  // namespace itexb

@@ -176,6 +176,8 @@ def test_debug_hooks_reject_unknown_keys(itex):
     assert lib.itexb_debug_set(b"gemm_skip_kblock", ctypes.c_int64(-1)) == L.OK
     assert lib.itexb_debug_set(b"gemm_wait_limit_cycles", ctypes.c_int64(0)) == L.OK
     assert lib.itexb_debug_set(b"gemm_wait_limit_cycles", ctypes.c_int64(-5)) == L.INVALID_ARGUMENT
+    assert lib.itexb_debug_set(b"gemm_cta_pair", ctypes.c_int64(2)) == L.INVALID_ARGUMENT
+    assert lib.itexb_debug_set(b"gemm_cta_pair", ctypes.c_int64(-1)) == L.OK
     assert lib.itexb_debug_set(b"bogus", ctypes.c_int64(1)) == L.NOT_FOUND
     assert lib.itexb_op_check(None, 1) == L.INVALID_ARGUMENT
 

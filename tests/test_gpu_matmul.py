@@ -1,4 +1,5 @@
 """GPU parity of the fused int8 matmul family through the C-ABI op layer."""
+import ctypes as C
 import json
 import os
 
@@ -256,6 +257,38 @@ def test_epilogue_bound_shape(n, k, summand):
         out = K.gemm(a, b, L.DT_QUINT8, ep=ep, status_word=status)
         assert torch.equal(out, want)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 768, 1024), (1024, 300, 400), (2304, 1024, 4096 + 48), (256 * 5, 512, 64)])
+def test_cta_pair_kernel_equals_single_cta_kernel(m, n, k):
+    """The kernel that runs a pair of CTAs per 256-row tile (each loading half of the B tile) against the one-CTA kernel
+    and against exact arithmetic: raw accumulators (u8 x s8), the plain u8 epilogue with preset accumulators, the general
+    bf16 epilogue, a narrow last k-block (k % 128 = 48) and a ragged last tile column (n = 300).  The pair is forced with
+    the debug key; without it only launches with at least two waves of pair tiles take it."""
+    itex, K, ops = modules()
+    L = itex._lib
+    lib = L.load()
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randint(0, 256, (m, k), device="cuda", generator=g).to(torch.uint8)
+    b = torch.randint(-127, 128, (n, k), device="cuda", generator=g).to(torch.int8)
+    scale = (torch.rand(n, device="cuda", generator=g) * 2e-4 + 1e-5).float()
+    bias = (torch.randn(n, device="cuda", generator=g) * 20).float()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    eps = [(L.DT_QINT32, dict(raw_acc=True)), (L.DT_QUINT8, dict(scale=scale, bias=bias, relu=True)),
+           (L.DT_BFLOAT16, dict(scale=scale, bias=bias, activation=L.ACT_GELU_TANH))]
+    results = {}
+    try:
+        for pair in (0, 1):
+            assert lib.itexb_debug_set(b"gemm_cta_pair", C.c_int64(pair)) == 0
+            results[pair] = [K.gemm(a, b, dt, ep=K.make_epilogue(**kw), status_word=status) for dt, kw in eps for _ in range(2)]
+    finally:
+        assert lib.itexb_debug_set(b"gemm_cta_pair", C.c_int64(-1)) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for x, y in zip(results[0], results[1]):
+        assert torch.equal(x, y)
+    ref = (a.double() @ b.double().t()).to(torch.int64)
+    assert bool((results[1][0].to(torch.int64) == ref).all())
 
 
 def test_kernel_level_argument_errors():
