@@ -205,7 +205,7 @@ def cpu_reference_step(x_rows, qw_kn, wmin, wmax, bias, state, x_range=None):
     return oc.gemm_fused(qa, state["w_nk"], out_scale, state["bias_s"], False, "float"), state["label"]
 
 
-def run_reference(args, m, n, k):
+def run_reference(args, m, n, k, emit):
     """The reference arm: CPU only, rank 0 only."""
     import torch
     if int(os.environ.get("RANK", "0")) != 0:
@@ -231,7 +231,7 @@ def run_reference(args, m, n, k):
             "config": {"workload": args.workload, "m_per_gpu": m, "n": n, "k": k, "cpu_sample_rows": m_s},
             "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_resnet50(args, rank, world, local, dev, K):
@@ -1211,10 +1211,20 @@ def main():
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
                     help="keep warming up at least this long so the clock sampler sees the load (0 for profiler runs)")
     args = ap.parse_args()
+    # stdout carries exactly one line, the JSON record: everything else any library writes to file descriptor 1 (NCCL's
+    # version banner ignores NCCL_DEBUG_FILE) is sent to stderr, and the record goes to the saved descriptor at the end
+    sys.stdout.flush()
+    record_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        sys.stdout.flush()
+        os.write(record_fd, (json.dumps(line) + "\n").encode())
+
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     m, n, k = WORKLOADS.get(args.workload, WORKLOADS["int8_gemm_8192"])
     if args.impl == "reference":
-        run_reference(args, m, n, k)
+        run_reference(args, m, n, k, emit)
         return
 
     import torch
@@ -1226,10 +1236,12 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     if world > 1:
-        # NCCL's own log (communicator and ring/tree set-up, "nranks N") goes to stderr; stdout stays the one JSON line
-        os.environ.setdefault("NCCL_DEBUG", "INFO")
-        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
-        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+        # NCCL's own log (communicator and ring/tree set-up, "nranks N") is written to file descriptor 1, which by now is
+        # stderr; stdout stays the one JSON line.  (NCCL_DEBUG_FILE=/dev/stderr would reopen - and truncate - a stderr
+        # that is redirected to a file, once per rank.)
+        if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "INFO"       # an inherited VERSION / WARN would hide the communicator lines
+            os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
         import datetime
         # a short timeout turns any mismatch between ranks into a quick error instead of a long hang
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
@@ -1276,7 +1288,7 @@ def main():
             if rank == 0:
                 line["secondary"] = secondary
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

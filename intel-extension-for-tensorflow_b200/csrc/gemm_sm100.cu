@@ -41,6 +41,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <atomic>
 #include <mutex>
 #include <string>
@@ -510,24 +511,20 @@ __device__ __noinline__ Float16 ApplyActivation16(Float16 in, int kind, float al
 }
 #undef ITEXB_ACT_CASE
 
-// Fused all-gather: the block a warp has just staged (32 rows of row_bytes, in the swizzled layout of the TMA store)
-// goes to the same place of every peer's output buffer with ordinary 16-byte global stores, four (or two) lanes per
-// row so that a row's bytes leave as one contiguous run.  Rows past m and bytes past the row's end are skipped.
-// Out of line: only multi-GPU launches execute it, and the epilogue loops keep their registers.
-__device__ __noinline__ void PushBlockToPeers(const GemmArgs& g, const uint8_t* buf, int row_bytes, long long row_first, int rows_valid,
-                                              long long col_byte0, int lane) {
-  const int row_units = row_bytes >> 4;
-  const long long pitch = g.ldo * g.out_esz;
-  const long long row_end = (long long)g.n * g.out_esz;
-  for (int u = lane; u < 32 * row_units; u += 32) {
-    const int r = u / row_units, ch = u - r * row_units;
-    const int rswz = (r / (8 / row_units)) % row_units;
-    if (r >= rows_valid || col_byte0 + ch * 16 >= row_end) continue;
-    const uint4 v = *reinterpret_cast<const uint4*>(buf + r * row_bytes + ((ch ^ rswz) << 4));
-    const long long off = (row_first + r) * pitch + col_byte0 + ch * 16;
-#pragma unroll 1
-    for (int p = 0; p < g.num_peers; ++p) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.peer_out[p]) + off) = v;
-  }
+// Fused all-gather.  The epilogue warps only store the tile locally (TMA stores, as in every launch).  Two warps that
+// are otherwise idle copy each finished tile from the local output - still in L2 - to the same place of every
+// peer's buffer: one 16-byte load per lane and row, then one 16-byte store per lane and peer, so that every store
+// instruction of the warp writes 512 contiguous bytes of one row (NVLink wants long runs: the same bytes pushed as
+// 64-byte row fragments straight from the epilogue's staging tiles, by per-lane stores or by TMA stores through peer
+// tensor maps, moved at ~300 GB/s and held the epilogue up for as long).  The epilogue warps count a tile in
+// `stored` once their stores of it have completed; the copying warps wait for 16 counts per tile.
+__device__ __forceinline__ uint32_t LdAcquireShared(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(SmemAddr(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void RedReleaseShared(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(SmemAddr(p)), "r"(v) : "memory");
 }
 
 // What an epilogue warp needs to know; filled once per launch.
@@ -554,7 +551,8 @@ struct EpilogueCtx {
 // writes; edges are clipped by the tensor map.  Without TMA-legal output rows the slices go
 // straight to global memory.
 template <int BN, bool F8, int OK, int MODE, int SUP, int CG>
-__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, const CUtensorMap* tma_sum, uint8_t* s_stage,
+__device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMap* tma_out, const CUtensorMap* tma_sum, uint32_t* stored,
+                                             uint8_t* s_stage,
                                              float* s_par, uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint64_t* par_bar,
                                              uint64_t* sum_bar, volatile int* abort_flag, uint32_t tmem_base, int warp, int lane, int tiles_m,
                                              int tiles_n, int num_tiles) {
@@ -655,6 +653,12 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   for (int t = tfirst; t < num_tiles; t += tstep) {
     int tm, tn, bt;
     TileCoords(t, g, tiles_m, tiles_n, &tm, &tn, &bt);
+    if (g.num_peers > 0 && t != tfirst && lane == 0) {
+      // fused all-gather: this warp's stores of the previous tile have completed -> one count for the copying warp.
+      // Done here, where the warp would otherwise only wait for the next accumulator.
+      TmaStoreWaitAll();
+      RedReleaseShared(stored, 1u);
+    }
     if (staged && tn != last_tn) {
       bool pok = true;
       if (reloads > 0) pok = MbarWait(SmemAddr(&par_bar[1]), (reloads - 1) & 1, abort_flag, g.status_word, kErrEpilogue, g.wait_limit);
@@ -905,7 +909,6 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             TmaStore3d(tma_out, SmemAddr(buf), col0 * esz, row0, bt);  // rows >= m and columns >= n are clipped
             TmaStoreCommit();
           }
-          if (g.num_peers > 0) PushBlockToPeers(g, buf, row_bytes, row0, min(32, g.m - row0), (long long)col0 * esz, lane);
           ++seq;
           sum_pref = sum_pref_next;
         }
@@ -930,6 +933,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     if (acc == 0) acc_phase ^= 1;
   }
   if (tma_store && lane == 0) TmaStoreWaitAll();  // staging memory stays valid until the last store has read it
+  if (g.num_peers > 0 && lane == 0 && !give_up && tfirst < num_tiles) RedReleaseShared(stored, 1u);  // the last tile
   if (OK == kOutFP8 && g.ep.amax != nullptr) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) thread_amax = fmaxf(thread_amax, __shfl_xor_sync(0xffffffffu, thread_amax, o));
@@ -966,6 +970,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   uint64_t* sum_bar = par_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sum_bar + C::kSumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* stored = tmem_slot + 2;  // fused all-gather: epilogue warps that have completed their stores, summed over tiles
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -994,6 +999,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
     for (int i = 0; i < C::kSumBars; ++i) MbarInit(SmemAddr(&sum_bar[i]), 1);
     *abort_flag = 0;
+    *stored = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -1159,6 +1165,83 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+  } else if ((warp == 2 || warp == 3) && CONV == kConvNone && g.num_peers > 0) {
+    // ---------------- fused all-gather: copy finished tiles to the peers ----------------
+    // Two warps, half of a tile's rows each; twelve 16-byte loads per lane in flight (12 rows of 512 bytes per round
+    // when the tile is full): what bounds a copying warp is the latency of its loads, not the stores that follow them.
+    const int esz = g.out_esz;
+    const long long pitch = g.ldo * esz;
+    uint8_t* const local = static_cast<uint8_t*>(g.out);
+    const int half = warp - 2;
+    uint32_t want = 0;
+    bool ok = true;
+    for (int t = tfirst; t < num_tiles && ok; t += tstep) {
+      int tms, tn, bt;
+      TileCoords(t, g, tiles_m, tiles_n, &tms, &tn, &bt);
+      want += uint32_t(kEpilogueWarps);
+      if (LdAcquireShared(stored) < want) {
+        const long long t0 = clock64();
+        for (uint32_t it = 1; LdAcquireShared(stored) < want; ++it) {
+          if ((it & 63u) == 0) {
+            if (*abort_flag) { ok = false; break; }
+            if (clock64() - t0 > g.wait_limit_acc) {
+              *abort_flag = 1;
+              if (g.status_word != nullptr) atomicCAS(g.status_word, 0, kErrEpilogue);
+              ok = false;
+              break;
+            }
+          }
+          __nanosleep(100);
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      for (int j = 0; j < SUP * CG; ++j) {
+        if (CG == 2 && j != rank) continue;   // a pair's CTAs copy their own tile rows
+        const int row0 = (tms * SUP * CG + j) * kBM + half * (kBM / 2);
+        if (row0 >= g.m) break;
+        const int rows = min(kBM / 2, g.m - row0);
+        const int cpr = (min(BN, g.n - tn * BN) * esz) >> 4;           // 16-byte chunks per row of this tile (n * esz % 16 == 0)
+        const long long base = ((long long)bt * g.batch_rows_out + row0) * pitch + (long long)tn * BN * esz;
+        const int chunks = rows * cpr;
+        if (cpr == 32) {
+          // full tile rows (512 bytes): twelve rows per round, one row per instruction
+          const uint8_t* src = local + base + lane * 16;
+          for (int r0 = 0; r0 < rows; r0 += 12) {
+            uint4 v[12];
+#pragma unroll
+            for (int u = 0; u < 12; ++u)
+              if (r0 + u < rows) v[u] = __ldcg(reinterpret_cast<const uint4*>(src + (long long)(r0 + u) * pitch));
+#pragma unroll 1
+            for (int p = 0; p < g.num_peers; ++p) {
+              uint8_t* const dst = static_cast<uint8_t*>(g.peer_out[p]) + base + lane * 16;
+#pragma unroll
+              for (int u = 0; u < 12; ++u)
+                if (r0 + u < rows) *reinterpret_cast<uint4*>(dst + (long long)(r0 + u) * pitch) = v[u];
+            }
+          }
+          continue;
+        }
+        for (int c0 = 0; c0 < chunks; c0 += 128) {
+          uint4 v[4];
+          long long off[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * 32 + lane;
+            const int r = c / cpr;
+            off[u] = base + r * pitch + (long long)(c - r * cpr) * 16;
+            if (c < chunks) v[u] = __ldcg(reinterpret_cast<const uint4*>(local + off[u]));
+          }
+#pragma unroll 1
+          for (int p = 0; p < g.num_peers; ++p) {
+            uint8_t* const dst = static_cast<uint8_t*>(g.peer_out[p]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (c0 + u * 32 + lane < chunks) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+          }
+        }
+      }
+    }
   } else if (CONV == kConvGather && warp >= kFirstGatherWarp) {
     // ---------------- implicit-GEMM A producer (convolution) ----------------
     // Every k-block these 128 threads copy the 128 x 128-byte A tile straight from the NHWC input
@@ -1242,7 +1325,7 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     }
   } else if (warp >= 4 && warp < kFirstGatherWarp) {
     // ---------------- epilogue ----------------
-#define ITEXB_EP_ARGS g, &tma_out, &tma_sum, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, sum_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles
+#define ITEXB_EP_ARGS g, &tma_out, &tma_sum, stored, s_stage, s_par, tmem_full_bar, tmem_empty_bar, par_bar, sum_bar, abort_flag, tmem_base, warp, lane, tiles_m, tiles_n, num_tiles
     switch (g.out_kind) {
       case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS); break;
       case kOutF32:
@@ -1610,6 +1693,8 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
   if (g.tma_store)
     ITEXB_RETURN_IF_ERROR(EncodeOutputMap(&to, g.out, g.m, g.n, g.ldo, g.out_esz, bn, sup, g.ep_mode == kEpSum8, g.batch, g.batch_rows_out));
   else to = ta;  // unused by the kernel
+  if (g.num_peers > 0)
+    ITEXB_REQUIRE(g.tma_store, ITEXB_INVALID_ARGUMENT, "gemm: the fused all-gather needs 16-byte aligned output rows");
   if (g.conv_mode == kConvGather) {
     if (bn == 256) return Launch<256, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
     if (bn == 128) return Launch<128, false, kConvGather, 1>(ta, tb, to, tat, tbt, tsum, g, st);
@@ -1716,7 +1801,14 @@ extern "C" int itexb_gemm(const itexb_gemm_params_t* p, itexb_stream_t stream) {
     ITEXB_REQUIRE(batch * ((p->m + kBM - 1) / kBM) * ((p->n + 63) / 64) < (1ll << 31), ITEXB_INVALID_ARGUMENT, "gemm: too many tiles");
   }
   CUtensorMap ta, tb;
-  const int bn = PickBN(p->n);
+  int bn = PickBN(p->n);
+  {
+    static const int forced_bn = [] {  // ITEXB_GEMM_BN: measurements
+      const char* e = std::getenv("ITEXB_GEMM_BN");
+      return e != nullptr ? std::atoi(e) : 0;
+    }();
+    if ((forced_bn == 64 || forced_bn == 128 || forced_bn == 256) && forced_bn < bn) bn = forced_bn;
+  }
   const int cg = PickCtaGroup(p->m, p->n, int(batch), bn, p->num_peers > 0, p->ep.raw_acc ? 4 : DtypeSize(p->out_dtype));  // 2: each CTA of a pair loads half of a B tile
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&ta, p->a, p->m, p->k, p->lda, kBM, batch, p->stride_a));
   ITEXB_RETURN_IF_ERROR(EncodeOperandMap(&tb, p->b, p->n, p->k, p->ldb, bn / cg, batch, p->stride_b));
