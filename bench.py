@@ -40,7 +40,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 
 # DRAM bytes (read + write) of one GemmKernel launch, from the ncu captures whose summaries are
 # kept under profiles/; null for shapes that were not captured.
-GEMM_DRAM_TRAFFIC = {"int8_gemm_8192": 498.8e6, "int8_gemm_4096": 55.4e6}
+GEMM_DRAM_TRAFFIC = {"int8_gemm_8192": 539.4e6, "int8_gemm_4096": 59.1e6}
 
 WORKLOADS = {
     # name: (M per GPU, N, K)

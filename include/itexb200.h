@@ -298,10 +298,10 @@ typedef struct itexb_gemm_params {
   int32_t batch;
   int64_t stride_a, stride_b, stride_out;
   /* Fused all-gather by peer stores (column-parallel linears: each GPU computes [m, n] = its column shard and every
-   * GPU needs all shards).  With num_peers > 0 the epilogue writes every finished output block not only to `out` but
-   * also, with ordinary 16-byte global stores, to the same offsets of peer_out[0 .. num_peers) - device pointers into
-   * OTHER GPUs' memory (itexb_rt_ipc_open) laid out exactly like `out` (same ldo) - while the tensor cores work on the
-   * next tile.  Nothing is ever loaded from a peer.  Needs 16-byte aligned output rows (n * element size a multiple
+   * GPU needs all shards).  With num_peers > 0 every finished output tile is written not only to `out` but also,
+   * by two copying warps of the kernel with ordinary 16-byte global stores (whole 512-byte rows per instruction), to
+   * the same offsets of peer_out[0 .. num_peers) - device pointers into OTHER GPUs' memory (itexb_rt_ipc_open) laid
+   * out exactly like `out` (same ldo) - while the tensor cores work on the next tiles.  Nothing is ever loaded from a peer.  Needs 16-byte aligned output rows (n * element size a multiple
    * of 16) and a single GEMM (batch <= 1); at most ITEXB_MAX_PEERS.  Completion is signalled separately
    * (itexb_peer_signal after the GEMM on the same stream, itexb_peer_wait on the receiving side).  No counterpart in
    * the reference, whose only collective call site is an all-reduce (itex/core/kernels/gpu/collective_ops.h:338-430). */

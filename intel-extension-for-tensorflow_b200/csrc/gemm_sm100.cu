@@ -78,7 +78,8 @@ template <int BN, int CG = 1> struct Cfg {
   // Accumulators in tensor memory: 2 stages of SUP sub-tiles of BN columns (a power of two >= 32, at most the 512 there are).
   template <int SUP> static constexpr int kTmemCols = 2 * BN * SUP < 32 ? 32 : 2 * BN * SUP;
   static constexpr int kSumBars = kEpilogueWarps * 4;          // one per epilogue warp and staging buffer (summand loads)
-  static constexpr int kBarrierBytes = (2 * kStages + 6 + kSumBars) * 8 + 16;
+  static constexpr int kAccBars = 2 * 4;                       // accumulator full / empty barriers: 2 stages x up to 4 sub-tiles
+  static constexpr int kBarrierBytes = (2 * kStages + 2 * kAccBars + 2 + kSumBars) * 8 + 16;
   static constexpr int kParamBytes = 2 * BN * 4;               // the tile's per-column scales and biases
   static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
   // No slack for aligning the base: dynamic shared memory is declared 1024-byte aligned and the kernel checks it.
@@ -624,15 +625,20 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   // happens here and is published through the accumulator-empty barriers the MMA warp waits on.
   constexpr bool preset = !F8 && OK != kOutRaw && MODE == kEpPlain;  // == g.preset, known at compile time here
   if (preset) {
+    // each warp arms what it will read and re-arm later: its blocks of its sub-tile, in both stages
 #pragma unroll 1
-    for (int c = sub * 16; c < 2 * BN * SUP; c += 16 * (kEpilogueWarps / 4))
-      TmemSt16Same(tmem_base + uint32_t(c) + (uint32_t(q * 32) << 16), uint32_t(kMagicBits));
+    for (int a = 0; a < 2; ++a)
+#pragma unroll 1
+      for (int c = c_first * bcols; c < BN; c += bcols * W)
+#pragma unroll 1
+        for (int sl = 0; sl < slices; ++sl)
+          TmemSt16Same(tmem_base + uint32_t((a * SUP + j) * BN + c + 16 * sl) + (uint32_t(q * 32) << 16), uint32_t(kMagicBits));
     TmemStWait();
     TcFenceBefore();
     __syncwarp();
     if (lane == 0) {
-      release_acc(0);
-      release_acc(1);
+      release_acc(j);
+      release_acc(SUP + j);
     }
   }
 
@@ -679,7 +685,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
       last_tn = tn;
     }
     const int nblocks = min(BN / bcols, (g.n - tn * BN + bcols - 1) / bcols);  // blocks holding real columns
-    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc]), acc_phase, abort_flag, g.status_word, kErrEpilogue, g.wait_limit_acc);
+    const bool ok = MbarWait(SmemAddr(&tmem_full_bar[acc * SUP + j]), acc_phase, abort_flag, g.status_word, kErrEpilogue, g.wait_limit_acc);
     if (!__all_sync(0xffffffffu, ok)) break;  // warp-uniform: a lane gave up or saw another role give up
     TcFenceAfter();
     // One accumulator stage holds SUP tiles of consecutive tile rows (sub-tile j in columns j*BN ...); each warp works
@@ -687,7 +693,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     // warp and stage) where a single tile per stage left it a 16-column fragment.
     do {
     const int tmr = (tm * SUP + j) * CG + rank;
-    if (tmr >= tiles_m_real) break;  // the MMA issuer left these columns untouched (still armed)
+    if (tmr >= tiles_m_real) break;  // the MMA issuer left these columns untouched (still armed); the hand-over takes place all the same
     const int row0 = tmr * kBM + q * 32;  // first row of this warp's 32-row block
     const bool row_ok = row0 + lane < g.m;
     const long long row = (long long)bt * g.batch_rows_out + row0 + lane;  // row of `out` / the summand across batches
@@ -922,7 +928,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     __syncwarp();
     if (lane == 0) {
       // one arrival per warp: all its lanes have read their rows
-      release_acc(acc);
+      release_acc(acc * SUP + j);
       if (staged && tiles_n > 1 && t + tstep < num_tiles) {  // one tile column: the parameters never change
         int ntm, ntn, nbt;
         TileCoords(t + tstep, g, tiles_m, tiles_n, &ntm, &ntn, &nbt);
@@ -965,8 +971,8 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + C::kStages;
   uint64_t* tmem_full_bar = bars + 2 * C::kStages;
-  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint64_t* par_bar = tmem_empty_bar + 2;
+  uint64_t* tmem_empty_bar = tmem_full_bar + C::kAccBars;   // [stage * SUP + sub-tile], like tmem_full_bar
+  uint64_t* par_bar = tmem_empty_bar + C::kAccBars;
   uint64_t* sum_bar = par_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sum_bar + C::kSumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -992,11 +998,13 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       MbarInit(SmemAddr(&full_bar[s]), CONV == kConvGather ? 1 + kGatherThreads : 1);  // B's TMA arrival (+ one per gather thread)
       MbarInit(SmemAddr(&empty_bar[s]), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 2 * SUP; ++a) {
+      // every sub-tile of an accumulator stage is handed over by itself: to the kEpilogueWarps / SUP warps that work on
+      // it, and back (a pair's issuer waits for both CTAs' epilogue warps)
       MbarInit(SmemAddr(&tmem_full_bar[a]), 1);
-      MbarInit(SmemAddr(&tmem_empty_bar[a]), kEpilogueWarps * CG);  // a pair's issuer waits for both CTAs' epilogue warps
-      MbarInit(SmemAddr(&par_bar[a]), kEpilogueWarps);
+      MbarInit(SmemAddr(&tmem_empty_bar[a]), (kEpilogueWarps / SUP) * CG);
     }
+    for (int a = 0; a < 2; ++a) MbarInit(SmemAddr(&par_bar[a]), kEpilogueWarps);
     for (int i = 0; i < C::kSumBars; ++i) MbarInit(SmemAddr(&sum_bar[i]), 1);
     *abort_flag = 0;
     *stored = 0u;
@@ -1110,20 +1118,21 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = tfirst; t < num_tiles && ok; t += tstep) {
-      // Without preset the first use of each accumulator stage finds its barrier "already released" (parity trick);
-      // with preset it waits for the epilogue warps' arming of the stage, one phase earlier throughout.
-      ok = MbarWait(SmemAddr(&tmem_empty_bar[acc]), g.preset ? acc_phase : acc_phase ^ 1, abort_flag, g.status_word, kErrMma, g.wait_limit);
-      if (!ok) break;
-      TcFenceAfter();
       int tms = 0;
       if (SUP > 1) {
         int tn_unused, bt_unused;
         TileCoords(t, g, tiles_m, tiles_n, &tms, &tn_unused, &bt_unused);
       }
       for (int j = 0; j < SUP && ok; ++j) {
-      if (SUP > 1 && tms * SUP + j >= tiles_m_real) break;
+      // Without preset the first use of each accumulator finds its barrier "already released" (parity trick);
+      // with preset it waits for the epilogue warps' arming of it, one phase earlier throughout.
+      ok = MbarWait(SmemAddr(&tmem_empty_bar[acc * SUP + j]), g.preset ? acc_phase : acc_phase ^ 1, abort_flag, g.status_word, kErrMma, g.wait_limit);
+      if (!ok) break;
+      TcFenceAfter();
       const uint32_t d_tmem = tmem_base + uint32_t((acc * SUP + j) * BN);
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // a sub-tile past the last tile row gets no MMAs, but its hand-over still takes place: the barriers stay in step
+      const int num_kb_j = (SUP > 1 && tms * SUP + j >= tiles_m_real) ? 0 : num_kb;
+      for (int kb = 0; kb < num_kb_j; ++kb) {
         ok = MbarWait(SmemAddr(&full_bar[stage]), phase, abort_flag, g.status_word, kErrMma, g.wait_limit);
         if (!ok) break;
         TcFenceAfter();
@@ -1153,15 +1162,16 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
+      if (!ok) break;
+      // this sub-tile's accumulator is complete
+      if (CG == 2) {
+        TcCommitPair(SmemAddr(&tmem_full_bar[acc * SUP + j]));
+        TcCommitPair(MapToCta(SmemAddr(&tmem_full_bar[acc * SUP + j]), 1));
+      } else {
+        TcCommit(SmemAddr(&tmem_full_bar[acc * SUP + j]));
+      }
       }  // sub-tiles
       if (!ok) break;
-      // all sub-tile accumulators of this stage complete
-      if (CG == 2) {
-        TcCommitPair(SmemAddr(&tmem_full_bar[acc]));
-        TcCommitPair(MapToCta(SmemAddr(&tmem_full_bar[acc]), 1));
-      } else {
-        TcCommit(SmemAddr(&tmem_full_bar[acc]));
-      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }

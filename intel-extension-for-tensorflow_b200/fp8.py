@@ -153,7 +153,7 @@ def peer_slot_offset(layout, shard_bytes, linear, src_rank):
 
 class PeerGather:
     """All-gather of column-parallel outputs by peer stores: every rank owns a [world, M, N/world] buffer in memory that all
-    ranks of the node have mapped (CUDA IPC); rank r's GEMM epilogue stores its shard into slot r of EVERY rank's buffer
+    ranks of the node have mapped (CUDA IPC); rank r's GEMM kernel copies its shard, tile by tile, into slot r of EVERY rank's buffer
     while it is being computed (itexb_gemm with peer_out), so no separate collective runs afterwards.
 
     Protocol per step, all on the caller's stream (values are a device-side step counter, so a captured step replays):
@@ -292,7 +292,7 @@ class Fp8Dense:
 
     def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0) -> torch.Tensor:
         """gather: a PeerGather (column-parallel layer, kernel kept as [N/world, K]): the product lands in slot `rank` of
-        linear `gather_index`'s buffer on every rank, stored by the GEMM's epilogue; returns this rank's slot.  The
+        linear `gather_index`'s buffer on every rank, stored by the GEMM kernel's copying warps; returns this rank's slot.  The
         arithmetic is that of the Fp8Matmul op (same kernel, same scales)."""
         m = self.meta
         if update_meta:
