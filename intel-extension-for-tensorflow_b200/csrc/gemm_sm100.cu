@@ -623,7 +623,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   // reads is already the float 1.5 * 2^23 + acc of the adder trick - the integer add per element is done by the
   // tensor core.  Each warp re-arms the columns it has read with one TMEM store per slice; the first arming
   // happens here and is published through the accumulator-empty barriers the MMA warp waits on.
-  constexpr bool preset = !F8 && OK != kOutRaw && MODE == kEpPlain;  // == g.preset, known at compile time here
+  constexpr bool preset = !F8 && OK != kOutRaw && (MODE == kEpPlain || MODE == kEpSum8);  // == g.preset, known at compile time here
   if (preset) {
     // each warp arms what it will read and re-arm later: its blocks of its sub-tile, in both stages
 #pragma unroll 1
@@ -1694,7 +1694,7 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
              (reinterpret_cast<uintptr_t>(g.ep.summand) & 15) == 0)
       g.ep_mode = kEpSum8;
   }
-  g.preset = (!f8 && g.ep_mode == kEpPlain) ? 1 : 0;
+  g.preset = (!f8 && (g.ep_mode == kEpPlain || g.ep_mode == kEpSum8)) ? 1 : 0;
   CUtensorMap to;
   CUtensorMap tsum;  // Sum8: the summand seen through the output's geometry (same boxes, same swizzle)
   if (g.ep_mode == kEpSum8)

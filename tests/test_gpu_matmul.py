@@ -291,6 +291,38 @@ def test_cta_pair_kernel_equals_single_cta_kernel(m, n, k):
     assert bool((results[1][0].to(torch.int64) == ref).all())
 
 
+@pytest.mark.parametrize("n,k,summand", [(64, 64, False), (64, 160, True), (128, 128, False)])
+def test_stacked_subtiles_with_a_partial_last_group(n, k, summand):
+    """Narrow tiles with one or two k-blocks run with several consecutive tile rows stacked in one accumulator stage, each
+    handed over through its own barriers.  590 tile rows (the last one ragged) are 147 full groups of four and one group
+    with two tile rows that do not exist: their hand-overs still have to take place and nothing may be stored for them.
+    Checked in full against separate fp32 steps on the raw accumulators; a canary guards the end of the output."""
+    itex, K, ops = modules()
+    L = itex._lib
+    m = 590 * 128 - 57
+    g = torch.Generator(device="cuda").manual_seed(11 + n + k)
+    a = torch.randint(0, 256, (m, k), device="cuda", generator=g).to(torch.uint8)
+    b = torch.randint(-127, 128, (n, k), device="cuda", generator=g).to(torch.int8)
+    scale = (torch.rand(n, device="cuda", generator=g) * 2e-3 + 1e-4).float()
+    bias = (torch.randn(n, device="cuda", generator=g) * 20).float()
+    sm = torch.randint(0, 256, (m, n), device="cuda", generator=g).to(torch.uint8) if summand else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    raw = K.gemm(a, b, L.DT_QINT32, ep=K.make_epilogue(raw_acc=True), status_word=status)
+    assert bool((raw.to(torch.int64) == (a.double() @ b.double().t()).to(torch.int64)).all())
+    want = raw.float() * scale
+    want = want + bias
+    if summand:
+        want = (want.double() + sm.double() * float(np.float32(0.37))).float()
+    want = torch.round(torch.clamp(want, 0.0, 255.0)).to(torch.uint8)
+    ep = K.make_epilogue(scale=scale, bias=bias, relu=True, summand=sm, sum_scale=0.37)
+    c = Canary(m * n)
+    for _ in range(2):
+        out = K.gemm(a, b, L.DT_QUINT8, ep=ep, out=c.view(torch.uint8, (m, n)), status_word=status)
+        assert torch.equal(out, want)
+    c.check()
+    assert int(status.item()) == 0
+
+
 def test_kernel_level_argument_errors():
     itex, K, ops = modules()
     L = itex._lib
