@@ -451,22 +451,26 @@ def run_fp8_linears(args, rank, world, local, dev, K):
         layers.append((layer, a, gathered, k, n))
 
     comm = torch.cuda.Stream(device=dev)
-    fused = world > 1 and args.fp8_gather == "fused"
+    # auto: both ways are warmed up and timed on this node, the faster one runs the timed region (which way wins depends
+    # on the shard count: the copies of a fused launch cannot overlap a main loop that is a single wave of tiles)
+    mode = args.fp8_gather if world > 1 else "nccl"
     pg = None
-    if fused:
+    layers_nccl = layers
+    layers_fused = layers
+    if mode in ("fused", "auto"):
         def exchange(obj):
             out = [None] * world
             dist.all_gather_object(out, obj)
             return out
         pg = fp8.PeerGather([(m, n // world) for _, _, _, _, n in layers], torch.bfloat16, rank, world, dev, exchange)
-        layers = [(layer, a, pg.gathered(i), k, n) for i, (layer, a, _, k, n) in enumerate(layers)]
+        layers_fused = [(layer, a, pg.gathered(i), k, n) for i, (layer, a, _, k, n) in enumerate(layers)]
 
     def step_nccl():
         # The all-gather of linear i runs on a second stream under the quantize + GEMM of linear i+1.
         main = torch.cuda.current_stream(dev)
         comm.wait_stream(main)
         keep = []
-        for layer, a, gathered, k, n in layers:
+        for layer, a, gathered, k, n in layers_nccl:
             y = layer(a)
             keep.append(y)
             if world > 1:
@@ -485,7 +489,7 @@ def run_fp8_linears(args, rank, world, local, dev, K):
         # 12-byte amax all-reduce stays on NCCL, on a second stream.  One publish / finish pair covers the three linears.
         main = torch.cuda.current_stream(dev)
         pg.begin()
-        for i, (layer, a, gathered, k, n) in enumerate(layers):
+        for i, (layer, a, gathered, k, n) in enumerate(layers_fused):
             layer(a, gather=pg, gather_index=i)
             comm.wait_stream(main)
             with torch.cuda.stream(comm):
@@ -493,11 +497,6 @@ def run_fp8_linears(args, rank, world, local, dev, K):
         pg.publish()
         pg.finish()
         main.wait_stream(comm)
-
-    step = step_fused if fused else step_nccl
-    # after finish() the gathered buffers are complete and may be read; acknowledge() tells the peers that this rank is
-    # done reading, which is what lets them store the next step's shards (issued after the consumer, outside the graph)
-    consumed = pg.acknowledge if fused else (lambda: None)
 
     def barrier():
         if world > 1:
@@ -509,28 +508,55 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     # A fixed number of warm-up steps: every step holds collectives, so all ranks must run the same count
     # (a time-based loop would let ranks disagree and dead-lock).  >= 17 steps fill the 16-deep amax history.
     n_warm = max(args.warmup, 17, int(args.min_warmup_seconds * 600))
-    for _ in range(n_warm):
-        step()
-        consumed()
-    barrier()
-    # One CUDA graph per step (kernels and NCCL collectives): removes ~20 host-side op calls per step,
-    # which otherwise bound the step once the per-GPU GEMMs shrink with the shard count.
-    eager_step = step
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream(device=dev)
-    side.wait_stream(torch.cuda.current_stream(dev))
-    with torch.cuda.stream(side):
-        eager_step()
-        consumed()
-    torch.cuda.current_stream(dev).wait_stream(side)
-    barrier()
-    with torch.cuda.graph(graph):
-        eager_step()
-        consumed()          # the timed loop has no consumer: the step is acknowledged inside the graph
+
+    def prepare(fused_way):
+        """Warm-up, then one CUDA graph per step (kernels and NCCL collectives): removes ~20 host-side op calls per step,
+        which otherwise bound the step once the per-GPU GEMMs shrink with the shard count."""
+        eager = step_fused if fused_way else step_nccl
+        # after finish() the gathered buffers are complete and may be read; acknowledge() tells the peers that this rank
+        # is done reading, which is what lets them store the next step's shards
+        ack = pg.acknowledge if fused_way else (lambda: None)
+        for _ in range(n_warm):
+            eager()
+            ack()
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            eager()
+            ack()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        barrier()
+        with torch.cuda.graph(graph):
+            eager()
+            ack()           # the timed loop has no consumer: the step is acknowledged inside the graph
+        for _ in range(3):
+            graph.replay()
+        barrier()
+        return eager, ack, graph
+
+    def trial_ms(graph, reps=10):
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        c0.record()
+        for _ in range(reps):
+            graph.replay()
+        c1.record()
+        barrier()
+        return max_over_ranks(c0.elapsed_time(c1), world, dev) / reps
+
+    trials = None
+    if mode == "auto":
+        ways = {False: prepare(False), True: prepare(True)}
+        trials = {"nccl_ms": trial_ms(ways[False][2]), "fused_ms": trial_ms(ways[True][2])}   # the same on every rank
+        fused = trials["fused_ms"] <= trials["nccl_ms"]
+        eager_step, consumed, graph = ways[fused]
+    else:
+        fused = mode == "fused"
+        eager_step, consumed, graph = prepare(fused)
+    layers = layers_fused if fused else layers_nccl
     step = graph.replay
-    for _ in range(3):
-        step()
-    barrier()
     launches0 = K.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -579,7 +605,7 @@ def run_fp8_linears(args, rank, world, local, dev, K):
                        "output": "bfloat16 [g, M, N/g] after all-gather", "l2": "weights + activations larger than L2",
                        "parallelism": ("column-parallel x%d, all-gather fused into the GEMM epilogue (stores to peer memory over NVLink)" if fused
                                        else "column-parallel x%d, NCCL all-gather of outputs") % world,
-                       "gather": "fused" if fused else ("nccl" if world > 1 else "none"), "tflops": tflops,
+                       "gather": "fused" if fused else ("nccl" if world > 1 else "none"), "gather_trials": trials, "tflops": tflops,
                        "nvlink_bytes_sent_per_gpu_per_step": sum(m * (n // world) * 2 * (world - 1) for _, n in FP8_LINEARS) if world > 1 else 0,
                        "peer_status": int(pg.status.item()) if fused else None},
             "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,fp8> (tcgen05.mma kind::f8f6f4)", "achieved": tflops,
@@ -1204,8 +1230,9 @@ def main():
     ap.add_argument("--real-dtype", default="float", choices=["float", "bfloat16"],
                     help="type of the real-valued side for --workload [fp8_]quantize / [fp8_]dequantize")
     ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--fp8-gather", default="fused", choices=["fused", "nccl"],
-                    help="fp8_llama_linears on several GPUs: all-gather fused into the GEMM epilogue (peer stores), or NCCL's")
+    ap.add_argument("--fp8-gather", default="auto", choices=["auto", "fused", "nccl"],
+                    help="fp8_llama_linears on several GPUs: all-gather fused into the GEMM kernel (copies to peer memory), NCCL's, "
+                         "or whichever of the two is faster in a trial during warm-up")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler runs, quick checks)")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
