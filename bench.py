@@ -550,7 +550,9 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     if mode == "auto":
         ways = {False: prepare(False), True: prepare(True)}
         trials = {"nccl_ms": trial_ms(ways[False][2]), "fused_ms": trial_ms(ways[True][2])}   # the same on every rank
-        fused = trials["fused_ms"] <= trials["nccl_ms"]
+        # a bounded wait that ran out anywhere (a peer that never signalled) disqualifies the fused way
+        trials["fused_status"] = int(max_over_ranks(float(pg.status.item()), world, dev))
+        fused = trials["fused_status"] == 0 and trials["fused_ms"] <= trials["nccl_ms"]
         eager_step, consumed, graph = ways[fused]
     else:
         fused = mode == "fused"
