@@ -51,6 +51,7 @@ typedef enum itexb_dtype {
   ITEXB_DT_INT32 = 3,
   ITEXB_DT_UINT8 = 4,
   ITEXB_DT_INT8 = 6,
+  ITEXB_DT_INT64 = 9,
   ITEXB_DT_QINT8 = 11,
   ITEXB_DT_QUINT8 = 12,
   ITEXB_DT_QINT32 = 13,
@@ -375,6 +376,23 @@ ITEXB_API int itexb_conv2d(const itexb_conv_params_t* p, itexb_stream_t stream);
  *     serialise them.                                                                       */
 #define ITEXB_STATIC_SCRATCH_BYTES (16u << 20)
 ITEXB_API int itexb_conv2d_static_scratch(const itexb_conv_params_t* p, itexb_stream_t stream);
+
+/* y = transpose(x, perm): y.dims[d] = x.dims[perm[d]], elements of elem_size bytes (1: qint8 / quint8, 2, 4: qint32).
+ * The data movement of the reference's QuantizedTransposeOp (itex/core/kernels/common/transpose_op.h:197-236 over its
+ * TransposeOp); the range tensors pass through in the op layer.                                                        */
+#define ITEXB_TRANSPOSE_MAX_RANK 8
+typedef struct itexb_transpose_params {
+  const void* x;
+  void* y;
+  int32_t rank;
+  int32_t elem_size;
+  int64_t dims[ITEXB_TRANSPOSE_MAX_RANK];   /* of x */
+  int32_t perm[ITEXB_TRANSPOSE_MAX_RANK];
+} itexb_transpose_params_t;
+ITEXB_API int itexb_transpose(const itexb_transpose_params_t* p, itexb_stream_t stream);
+/* `outer` dense rows of `width` bytes at src -> rows of `dpitch` bytes at dst, starting at byte `col` of each: one input of
+ * a concatenation along an inner axis (the dnnl::concat of itex/core/kernels/common/quantized_concat_op.cc:196-231).  */
+ITEXB_API int itexb_copy_rows(const void* src, void* dst, int64_t outer, int64_t width, int64_t dpitch, int64_t col, itexb_stream_t stream);
 
 /* NHWC 8-bit pooling: max, or average over the window cells that lie inside the image
  * (rne(float(sum)/float(count)), saturated).  Replaces the dnnl::pooling_forward behind the

@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libitexb200.so")
 MAX_DIMS = 8
 
 # itexb_dtype_t
-DT_FLOAT, DT_INT32, DT_UINT8, DT_INT8 = 1, 3, 4, 6
+DT_FLOAT, DT_INT32, DT_UINT8, DT_INT8, DT_INT64 = 1, 3, 4, 6, 9
 DT_QINT8, DT_QUINT8, DT_QINT32, DT_BFLOAT16, DT_HALF = 11, 12, 13, 14, 19
 DT_FP8_E4M3, DT_FP8_E5M2 = 101, 102
 # itexb_activation_t

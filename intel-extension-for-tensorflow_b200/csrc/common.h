@@ -53,6 +53,7 @@ inline int CheckLaunch(const char* kernel) {
 inline int DtypeSize(int dt) {
   switch (dt) {
     case ITEXB_DT_FLOAT: case ITEXB_DT_INT32: case ITEXB_DT_QINT32: return 4;
+    case ITEXB_DT_INT64: return 8;
     case ITEXB_DT_BFLOAT16: case ITEXB_DT_HALF: return 2;
     case ITEXB_DT_UINT8: case ITEXB_DT_INT8: case ITEXB_DT_QINT8: case ITEXB_DT_QUINT8:
     case ITEXB_DT_FP8_E4M3: case ITEXB_DT_FP8_E5M2: return 1;
@@ -64,6 +65,7 @@ inline const char* DtypeName(int dt) {
   switch (dt) {
     case ITEXB_DT_FLOAT: return "float";
     case ITEXB_DT_INT32: return "int32";
+    case ITEXB_DT_INT64: return "int64";
     case ITEXB_DT_UINT8: return "uint8";
     case ITEXB_DT_INT8: return "int8";
     case ITEXB_DT_QINT8: return "qint8";

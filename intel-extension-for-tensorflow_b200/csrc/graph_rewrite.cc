@@ -2,8 +2,8 @@
 // `_ITEX*` node, under which condition, and which attrs the new node gets besides a copy of the old ones.
 //
 // This is what the reference's layout pass does for these ops (the rename table of
-// itex/core/graph/native_layout/native_layout.cc:113-199; the predicate RewriteQuantize,
-// itex/core/graph/utils/layout_utils.cc:315-354; the attr copiers CopyAttrsQuantizedConv2D / CopyAttrsQuantizedMatMul /
+// itex/core/graph/native_layout/native_layout.cc:113-199; the predicates RewriteQuantize and RewriteQuantizeReshape,
+// itex/core/graph/utils/layout_utils.cc:315-354,392-400; the attr copiers CopyAttrsQuantizedConv2D / CopyAttrsQuantizedMatMul /
 // CopyAttrsQuantize, layout_utils.cc:471-542), restricted to the ops this library implements.  A TF_InitGraph
 // optimizer calls itexb_rewrite_node for every node and, when it answers with a new op name, replaces the node by one
 // of that name with the old node's attrs plus the returned ones - after which the graph dispatches to the kernels of
@@ -17,7 +17,7 @@ namespace itexb {
 namespace {
 
 enum CopyKind { kCopyAll, kCopyConv2D, kCopyMatMul, kCopyQuantize };
-enum Predicate { kAlways, kQuantizeRule };
+enum Predicate { kAlways, kQuantizeRule, kReshapeRule };
 
 struct Rule {
   const char* from;
@@ -32,6 +32,7 @@ const Rule kRules[] = {
     {"QuantizeV2", "_ITEXQuantizeV2", kCopyQuantize, kQuantizeRule},
     {"QuantizedAvgPool", "ITEXQuantizedAvgPool", kCopyAll, kAlways},
     {"QuantizedMaxPool", "_ITEXQuantizedMaxPool", kCopyAll, kAlways},
+    {"QuantizedReshape", "_ITEXQuantizedReshape", kCopyAll, kReshapeRule},
     {"QuantizedConv2D", "_ITEXQuantizedConv2D", kCopyConv2D, kAlways},
     {"QuantizedConv2DAndRequantize", "_ITEXQuantizedConv2DAndRequantize", kCopyConv2D, kAlways},
     {"QuantizedConv2DPerChannel", "_ITEXQuantizedConv2DPerChannel", kCopyConv2D, kAlways},
@@ -55,6 +56,7 @@ const Rule kRules[] = {
     {"_QuantizedFusedMatMulAndDequantize", "_ITEXQuantizedFusedMatMulAndDequantize", kCopyMatMul, kAlways},
     {"_QuantizedFusedMatMulAndRequantize", "_ITEXQuantizedFusedMatMulAndRequantize", kCopyMatMul, kAlways},
     {"_QuantizedMatMul", "_ITEXQuantizedMatMul", kCopyAll, kAlways},
+    {"_QuantizedTranspose", "_ITEXQuantizedTranspose", kCopyAll, kAlways},
 };
 
 // RewriteQuantize: MIN_COMBINED is never rewritten; a MIN_FIRST Dequantize stays on the stock kernel when the node is
@@ -108,6 +110,12 @@ extern "C" int itexb_rewrite_node(const itexb_rewrite_query_t* q, itexb_rewrite_
     const bool yes = QuantizeRule(op, attrs, q->on_gpu != 0, &st);
     if (st != ITEXB_OK) return st;  // a Quantize / Dequantize node without `mode` is malformed (the reference CHECK-fails)
     if (!yes) return ITEXB_OK;
+  }
+  if (rule->when == kReshapeRule) {
+    // RewriteQuantizeReshape: only a qint8 reshape is taken over
+    int t = 0;
+    ITEXB_RETURN_IF_ERROR(attrs.GetType("T", &t));
+    if (t != ITEXB_DT_QINT8) return ITEXB_OK;
   }
   switch (rule->copy) {
     case kCopyAll: break;

@@ -225,34 +225,25 @@ const char* const k12_attrs[] = {
     "adj_y: bool = false",
     "is_filter_const: bool = false"};
 const char* const k13_inputs[] = {
-    "input: Tinput",
-    "filter: Tfilter",
-    "min_input: float",
-    "max_input: float",
-    "min_filter: float",
-    "max_filter: float"};
+    "values: N * T",
+    "axis: Tidx",
+    "input_mins:  N * float",
+    "input_maxes: N * float"};
 const char* const k13_outputs[] = {
-    "output: out_type",
-    "min_output: float",
-    "max_output: float"};
+    "output: T",
+    "output_min: float",
+    "output_max: float"};
 const char* const k13_attrs[] = {
-    "Tinput: quantizedtype",
-    "Tfilter: quantizedtype",
-    "out_type: quantizedtype = DT_QINT32",
-    "data_format: string = 'NHWC'",
-    "strides: list(int)",
-    "is_filter_const: bool = true",
-    "padding_list: list(int) = []",
-    "dilations: list(int) = [1, 1, 1, 1]"};
+    "N: int >= 2",
+    "T: numbertype",
+    "Tidx: {int32, int64} = DT_INT32"};
 const char* const k14_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
     "min_input: float",
     "max_input: float",
     "min_filter: float",
-    "max_filter: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_filter: float"};
 const char* const k14_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -272,7 +263,9 @@ const char* const k15_inputs[] = {
     "min_input: float",
     "max_input: float",
     "min_filter: float",
-    "max_filter: float"};
+    "max_filter: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
 const char* const k15_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -287,12 +280,32 @@ const char* const k15_attrs[] = {
     "padding_list: list(int) = []",
     "dilations: list(int) = [1, 1, 1, 1]"};
 const char* const k16_inputs[] = {
+    "input: Tinput",
+    "filter: Tfilter",
+    "min_input: float",
+    "max_input: float",
+    "min_filter: float",
+    "max_filter: float"};
+const char* const k16_outputs[] = {
+    "output: out_type",
+    "min_output: float",
+    "max_output: float"};
+const char* const k16_attrs[] = {
+    "Tinput: quantizedtype",
+    "Tfilter: quantizedtype",
+    "out_type: quantizedtype = DT_QINT32",
+    "data_format: string = 'NHWC'",
+    "strides: list(int)",
+    "is_filter_const: bool = true",
+    "padding_list: list(int) = []",
+    "dilations: list(int) = [1, 1, 1, 1]"};
+const char* const k17_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k16_outputs[] = {
+const char* const k17_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k16_attrs[] = {
+const char* const k17_attrs[] = {
     "Tinput: quantizedtype = DT_QUINT8",
     "Tfilter: quantizedtype = DT_QINT8",
     "Tbias: {float, qint32} = DT_QINT32",
@@ -309,28 +322,6 @@ const char* const k16_attrs[] = {
     "dilations: list(int) = [1, 1, 1, 1]",
     "fused_ops: list(string) = []",
     "alpha: float = 0.0"};
-const char* const k17_inputs[] = {
-    "input: Tinput",
-    "filter: Tfilter",
-    "bias: float",
-    "min_input: float",
-    "max_input: float",
-    "min_filter: float",
-    "max_filter: float"};
-const char* const k17_outputs[] = {
-    "output: out_type",
-    "min_output: float",
-    "max_output: float"};
-const char* const k17_attrs[] = {
-    "Tinput: quantizedtype",
-    "Tfilter: quantizedtype",
-    "out_type: quantizedtype = DT_QINT32",
-    "data_format: string = 'NHWC'",
-    "strides: list(int)",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "padding_list: list(int) = []",
-    "dilations: list(int) = [1, 1, 1, 1]"};
 const char* const k18_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
@@ -356,13 +347,11 @@ const char* const k18_attrs[] = {
 const char* const k19_inputs[] = {
     "input: Tinput",
     "filter: Tfilter",
-    "bias: Tbias",
+    "bias: float",
     "min_input: float",
     "max_input: float",
     "min_filter: float",
-    "max_filter: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_filter: float"};
 const char* const k19_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -370,7 +359,6 @@ const char* const k19_outputs[] = {
 const char* const k19_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
-    "Tbias: {float, qint32}",
     "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
@@ -412,10 +400,7 @@ const char* const k21_inputs[] = {
     "min_filter: float",
     "max_filter: float",
     "min_freezed_output: float",
-    "max_freezed_output: float",
-    "summand: Tsummand",
-    "min_summand: float",
-    "max_summand: float"};
+    "max_freezed_output: float"};
 const char* const k21_outputs[] = {
     "output: out_type",
     "min_output: float",
@@ -424,7 +409,6 @@ const char* const k21_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
-    "Tsummand: quantizedtype",
     "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
@@ -470,14 +454,20 @@ const char* const k23_inputs[] = {
     "min_filter: float",
     "max_filter: float",
     "min_freezed_output: float",
-    "max_freezed_output: float"};
+    "max_freezed_output: float",
+    "summand: Tsummand",
+    "min_summand: float",
+    "max_summand: float"};
 const char* const k23_outputs[] = {
-    "output: out_type"};
+    "output: out_type",
+    "min_output: float",
+    "max_output: float"};
 const char* const k23_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
-    "out_type: {bfloat16, half} = DT_HALF",
+    "Tsummand: quantizedtype",
+    "out_type: quantizedtype = DT_QINT32",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
     "is_filter_const: bool = true",
@@ -500,7 +490,7 @@ const char* const k24_attrs[] = {
     "Tinput: quantizedtype",
     "Tfilter: quantizedtype",
     "Tbias: {float, qint32}",
-    "out_type: {bfloat16, half, float} = DT_FLOAT",
+    "out_type: {bfloat16, half} = DT_HALF",
     "data_format: string = 'NHWC'",
     "strides: list(int)",
     "is_filter_const: bool = true",
@@ -508,6 +498,29 @@ const char* const k24_attrs[] = {
     "padding_list: list(int) = []",
     "dilations: list(int) = [1, 1, 1, 1]"};
 const char* const k25_inputs[] = {
+    "input: Tinput",
+    "filter: Tfilter",
+    "bias: Tbias",
+    "min_input: float",
+    "max_input: float",
+    "min_filter: float",
+    "max_filter: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k25_outputs[] = {
+    "output: out_type"};
+const char* const k25_attrs[] = {
+    "Tinput: quantizedtype",
+    "Tfilter: quantizedtype",
+    "Tbias: {float, qint32}",
+    "out_type: {bfloat16, half, float} = DT_FLOAT",
+    "data_format: string = 'NHWC'",
+    "strides: list(int)",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "padding_list: list(int) = []",
+    "dilations: list(int) = [1, 1, 1, 1]"};
+const char* const k26_inputs[] = {
     "x: T1",
     "y: T2",
     "args: num_args * T",
@@ -515,9 +528,9 @@ const char* const k25_inputs[] = {
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k25_outputs[] = {
+const char* const k26_outputs[] = {
     "output: Toutput"};
-const char* const k25_attrs[] = {
+const char* const k26_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "T: {bfloat16, float} = DT_FLOAT",
@@ -527,33 +540,6 @@ const char* const k25_attrs[] = {
     "num_args: int >= 0",
     "fused_ops: list(string) = []",
     "is_filter_const: bool = false"};
-const char* const k26_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "args: num_args * Targs",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float"};
-const char* const k26_outputs[] = {
-    "product: Toutput",
-    "min_product: float",
-    "max_product: float"};
-const char* const k26_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "num_args: int >= 0",
-    "Targs: {bfloat16, half, float, quantizedtype}",
-    "Toutput: quantizedtype",
-    "T: numbertype",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "fused_ops: list(string) = []",
-    "is_filter_const: bool = true",
-    "is_bias_const: bool = true",
-    "epsilon: float = 0.0001",
-    "leakyrelu_alpha: float = 0.2",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
 const char* const k27_inputs[] = {
     "a: T1",
     "b: T2",
@@ -563,13 +549,15 @@ const char* const k27_inputs[] = {
     "min_b: float",
     "max_b: float"};
 const char* const k27_outputs[] = {
-    "product: Toutput"};
+    "product: Toutput",
+    "min_product: float",
+    "max_product: float"};
 const char* const k27_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "num_args: int >= 0",
     "Targs: {bfloat16, half, float, quantizedtype}",
-    "Toutput: {bfloat16, half, float} = DT_FLOAT",
+    "Toutput: quantizedtype",
     "T: numbertype",
     "transpose_a: bool = false",
     "transpose_b: bool = false",
@@ -586,14 +574,39 @@ const char* const k28_inputs[] = {
     "min_a: float",
     "max_a: float",
     "min_b: float",
+    "max_b: float"};
+const char* const k28_outputs[] = {
+    "product: Toutput"};
+const char* const k28_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "num_args: int >= 0",
+    "Targs: {bfloat16, half, float, quantizedtype}",
+    "Toutput: {bfloat16, half, float} = DT_FLOAT",
+    "T: numbertype",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "fused_ops: list(string) = []",
+    "is_filter_const: bool = true",
+    "is_bias_const: bool = true",
+    "epsilon: float = 0.0001",
+    "leakyrelu_alpha: float = 0.2",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
+const char* const k29_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "args: num_args * Targs",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
     "max_b: float",
     "min_freezed_output: float",
     "max_freezed_output: float"};
-const char* const k28_outputs[] = {
+const char* const k29_outputs[] = {
     "product: Toutput",
     "min_product: float",
     "max_product: float"};
-const char* const k28_attrs[] = {
+const char* const k29_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "num_args: int >= 0",
@@ -608,13 +621,13 @@ const char* const k28_attrs[] = {
     "epsilon: float = 0.0001",
     "leakyrelu_alpha: float = 0.2",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k29_inputs[] = {
+const char* const k30_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k29_outputs[] = {
+const char* const k30_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k29_attrs[] = {
+const char* const k30_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -632,7 +645,7 @@ const char* const k29_attrs[] = {
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "output_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "leakyrelu_alpha: float = 0.2"};
-const char* const k30_inputs[] = {
+const char* const k31_inputs[] = {
     "a: T1",
     "b: T2",
     "bias: Tbias",
@@ -640,11 +653,11 @@ const char* const k30_inputs[] = {
     "max_a: float",
     "min_b: float",
     "max_b: float"};
-const char* const k30_outputs[] = {
+const char* const k31_outputs[] = {
     "out: Toutput",
     "min_out: float",
     "max_out: float"};
-const char* const k30_attrs[] = {
+const char* const k31_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "Tbias: {float, qint32}",
@@ -653,7 +666,7 @@ const char* const k30_attrs[] = {
     "transpose_b: bool = false",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
     "is_weight_const: bool = true"};
-const char* const k31_inputs[] = {
+const char* const k32_inputs[] = {
     "a: T1",
     "b: T2",
     "bias: Tbias",
@@ -663,9 +676,9 @@ const char* const k31_inputs[] = {
     "max_b: float",
     "min_freezed_output: float",
     "max_freezed_output: float"};
-const char* const k31_outputs[] = {
+const char* const k32_outputs[] = {
     "out: Toutput"};
-const char* const k31_attrs[] = {
+const char* const k32_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "Tbias: {float, bfloat16, qint32}",
@@ -674,7 +687,7 @@ const char* const k31_attrs[] = {
     "transpose_b: bool = false",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
     "is_weight_const: bool = true"};
-const char* const k32_inputs[] = {
+const char* const k33_inputs[] = {
     "a: T1",
     "b: T2",
     "bias: float",
@@ -682,28 +695,6 @@ const char* const k32_inputs[] = {
     "max_a: float",
     "min_b: float",
     "max_b: float"};
-const char* const k32_outputs[] = {
-    "out: Toutput",
-    "min_out: float",
-    "max_out: float"};
-const char* const k32_attrs[] = {
-    "T1: quantizedtype",
-    "T2: quantizedtype",
-    "Toutput: quantizedtype = DT_QINT32",
-    "transpose_a: bool = false",
-    "transpose_b: bool = false",
-    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
-    "is_weight_const: bool = true"};
-const char* const k33_inputs[] = {
-    "a: T1",
-    "b: T2",
-    "bias: Tbias",
-    "min_a: float",
-    "max_a: float",
-    "min_b: float",
-    "max_b: float",
-    "min_freezed_output: float",
-    "max_freezed_output: float"};
 const char* const k33_outputs[] = {
     "out: Toutput",
     "min_out: float",
@@ -711,8 +702,7 @@ const char* const k33_outputs[] = {
 const char* const k33_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
-    "Tbias: {float, qint32}",
-    "Toutput: quantizedtype = DT_QUINT8",
+    "Toutput: quantizedtype = DT_QINT32",
     "transpose_a: bool = false",
     "transpose_b: bool = false",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
@@ -741,24 +731,71 @@ const char* const k34_attrs[] = {
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
     "is_weight_const: bool = true"};
 const char* const k35_inputs[] = {
+    "a: T1",
+    "b: T2",
+    "bias: Tbias",
+    "min_a: float",
+    "max_a: float",
+    "min_b: float",
+    "max_b: float",
+    "min_freezed_output: float",
+    "max_freezed_output: float"};
+const char* const k35_outputs[] = {
+    "out: Toutput",
+    "min_out: float",
+    "max_out: float"};
+const char* const k35_attrs[] = {
+    "T1: quantizedtype",
+    "T2: quantizedtype",
+    "Tbias: {float, qint32}",
+    "Toutput: quantizedtype = DT_QUINT8",
+    "transpose_a: bool = false",
+    "transpose_b: bool = false",
+    "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'MIN_FIRST'",
+    "is_weight_const: bool = true"};
+const char* const k36_inputs[] = {
     "input: T",
     "min_input: float",
     "max_input: float"};
-const char* const k35_outputs[] = {
+const char* const k36_outputs[] = {
     "output: T",
     "min_output: float",
     "max_output: float"};
-const char* const k35_attrs[] = {
+const char* const k36_attrs[] = {
     "T: quantizedtype",
     "ksize: list(int) >= 4",
     "strides: list(int) >= 4"};
-const char* const k36_inputs[] = {
+const char* const k37_inputs[] = {
+    "tensor: T",
+    "shape: Tshape",
+    "input_min: float",
+    "input_max: float"};
+const char* const k37_outputs[] = {
+    "output: T",
+    "output_min: float",
+    "output_max: float"};
+const char* const k37_attrs[] = {
+    "T: type",
+    "Tshape: {int32, int64} = DT_INT32"};
+const char* const k38_inputs[] = {
+    "x: T",
+    "perm: Tperm",
+    "min_x: float",
+    "max_x: float"};
+const char* const k38_outputs[] = {
+    "y: T",
+    "min_y: float",
+    "max_y: float"};
+const char* const k38_attrs[] = {
+    "T: quantizedtype",
+    "Tperm: {int32, int64} = DT_INT32"};
+const char* const k39_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k36_outputs[] = {
+const char* const k39_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k36_attrs[] = {
+const char* const k39_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -772,29 +809,29 @@ const char* const k36_attrs[] = {
     "fused_ops: list(string) = []",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "output_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k37_inputs[] = {
+const char* const k40_inputs[] = {
     "x: T1",
     "y: T2",
     "min_x: float",
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k37_outputs[] = {
+const char* const k40_outputs[] = {
     "output: Toutput"};
-const char* const k37_attrs[] = {
+const char* const k40_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "Toutput: {bfloat16, half, float} = DT_FLOAT",
     "adj_x: bool = false",
     "adj_y: bool = false",
     "is_filter_const: bool = false"};
-const char* const k38_inputs[] = {
+const char* const k41_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k38_outputs[] = {
+const char* const k41_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k38_attrs[] = {
+const char* const k41_attrs[] = {
     "Tinput: quantizedtype = DT_QUINT8",
     "Tfilter: quantizedtype = DT_QINT8",
     "Tbias: {float, qint32} = DT_QINT32",
@@ -811,7 +848,7 @@ const char* const k38_attrs[] = {
     "dilations: list(int) = [1, 1, 1, 1]",
     "fused_ops: list(string) = []",
     "alpha: float = 0.0"};
-const char* const k39_inputs[] = {
+const char* const k42_inputs[] = {
     "x: T1",
     "y: T2",
     "args: num_args * T",
@@ -819,9 +856,9 @@ const char* const k39_inputs[] = {
     "max_x: float",
     "min_y: float",
     "max_y: float"};
-const char* const k39_outputs[] = {
+const char* const k42_outputs[] = {
     "output: Toutput"};
-const char* const k39_attrs[] = {
+const char* const k42_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "T: {bfloat16, half, float} = DT_FLOAT",
@@ -831,7 +868,7 @@ const char* const k39_attrs[] = {
     "num_args: int >= 0",
     "fused_ops: list(string) = []",
     "is_filter_const: bool = false"};
-const char* const k40_inputs[] = {
+const char* const k43_inputs[] = {
     "a: T1",
     "b: T2",
     "args: num_args * Targs",
@@ -839,11 +876,11 @@ const char* const k40_inputs[] = {
     "max_a: float",
     "min_b: float",
     "max_b: float"};
-const char* const k40_outputs[] = {
+const char* const k43_outputs[] = {
     "product: Toutput",
     "min_product: float",
     "max_product: float"};
-const char* const k40_attrs[] = {
+const char* const k43_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "num_args: int >= 0",
@@ -857,7 +894,7 @@ const char* const k40_attrs[] = {
     "epsilon: float = 0.0001",
     "leakyrelu_alpha: float = 0.2",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k41_inputs[] = {
+const char* const k44_inputs[] = {
     "a: T1",
     "b: T2",
     "args: num_args * Targs",
@@ -865,9 +902,9 @@ const char* const k41_inputs[] = {
     "max_a: float",
     "min_b: float",
     "max_b: float"};
-const char* const k41_outputs[] = {
+const char* const k44_outputs[] = {
     "product: Toutput"};
-const char* const k41_attrs[] = {
+const char* const k44_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "num_args: int >= 0",
@@ -881,7 +918,7 @@ const char* const k41_attrs[] = {
     "epsilon: float = 0.0001",
     "leakyrelu_alpha: float = 0.2",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k42_inputs[] = {
+const char* const k45_inputs[] = {
     "a: T1",
     "b: T2",
     "args: num_args * Targs",
@@ -891,11 +928,11 @@ const char* const k42_inputs[] = {
     "max_b: float",
     "min_freezed_output: float",
     "max_freezed_output: float"};
-const char* const k42_outputs[] = {
+const char* const k45_outputs[] = {
     "product: Toutput",
     "min_product: float",
     "max_product: float"};
-const char* const k42_attrs[] = {
+const char* const k45_attrs[] = {
     "T1: quantizedtype",
     "T2: quantizedtype",
     "num_args: int >= 0",
@@ -909,13 +946,13 @@ const char* const k42_attrs[] = {
     "epsilon: float = 0.0001",
     "leakyrelu_alpha: float = 0.2",
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'"};
-const char* const k43_inputs[] = {
+const char* const k46_inputs[] = {
     "device_inputs: Tdevice_inputs",
     "host_inputs: Thost_inputs"};
-const char* const k43_outputs[] = {
+const char* const k46_outputs[] = {
     "device_outputs: Tdevice_outputs",
     "host_outputs: Thost_outputs"};
-const char* const k43_attrs[] = {
+const char* const k46_attrs[] = {
     "Tdevice_inputs: list(type) >= 0 = []",
     "Thost_inputs: list(type) >= 0 = []",
     "Tdevice_outputs: list(type) >= 0 = []",
@@ -933,6 +970,18 @@ const char* const k43_attrs[] = {
     "input_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "output_quant_mode: {'MIN_FIRST', 'SCALED'} = 'SCALED'",
     "leakyrelu_alpha: float = 0.2"};
+const char* const k47_inputs[] = {
+    "x: T",
+    "perm: Tperm",
+    "min_x: float",
+    "max_x: float"};
+const char* const k47_outputs[] = {
+    "y: T",
+    "min_y: float",
+    "max_y: float"};
+const char* const k47_attrs[] = {
+    "T: quantizedtype",
+    "Tperm: {int32, int64} = DT_INT32"};
 
 const OpDefEntry kOpDefs[] = {
     {"Fp8Dequantize", k0_inputs, 2, k0_outputs, 1, k0_attrs, 3},
@@ -948,37 +997,41 @@ const OpDefEntry kOpDefs[] = {
     {"_ITEXQuantizeV2WithQuantizedConv2D", k10_inputs, 9, k10_outputs, 3, k10_attrs, 15},
     {"_ITEXQuantizedBatchMatMul", k11_inputs, 2, k11_outputs, 2, k11_attrs, 13},
     {"_ITEXQuantizedBatchMatMulV2AndDequantize", k12_inputs, 6, k12_outputs, 1, k12_attrs, 6},
-    {"_ITEXQuantizedConv2D", k13_inputs, 6, k13_outputs, 3, k13_attrs, 8},
-    {"_ITEXQuantizedConv2DAndRequantize", k14_inputs, 8, k14_outputs, 3, k14_attrs, 8},
-    {"_ITEXQuantizedConv2DPerChannel", k15_inputs, 6, k15_outputs, 3, k15_attrs, 8},
-    {"_ITEXQuantizedConv2DV2", k16_inputs, 2, k16_outputs, 2, k16_attrs, 16},
-    {"_ITEXQuantizedConv2DWithBias", k17_inputs, 7, k17_outputs, 3, k17_attrs, 9},
-    {"_ITEXQuantizedConv2DWithBiasAndRelu", k18_inputs, 7, k18_outputs, 3, k18_attrs, 9},
-    {"_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", k19_inputs, 9, k19_outputs, 3, k19_attrs, 10},
-    {"_ITEXQuantizedConv2DWithBiasAndRequantize", k20_inputs, 9, k20_outputs, 3, k20_attrs, 10},
-    {"_ITEXQuantizedConv2DWithBiasSignedSumAndReluAndRequantize", k21_inputs, 12, k21_outputs, 3, k21_attrs, 11},
-    {"_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize", k22_inputs, 12, k22_outputs, 3, k22_attrs, 11},
-    {"_ITEXQuantizedConv2DWithCast", k23_inputs, 9, k23_outputs, 1, k23_attrs, 10},
-    {"_ITEXQuantizedConv2DWithDequantize", k24_inputs, 9, k24_outputs, 1, k24_attrs, 10},
-    {"_ITEXQuantizedFusedBatchMatMulV2AndDequantize", k25_inputs, 7, k25_outputs, 1, k25_attrs, 9},
-    {"_ITEXQuantizedFusedMatMul", k26_inputs, 7, k26_outputs, 3, k26_attrs, 14},
-    {"_ITEXQuantizedFusedMatMulAndDequantize", k27_inputs, 7, k27_outputs, 1, k27_attrs, 14},
-    {"_ITEXQuantizedFusedMatMulAndRequantize", k28_inputs, 9, k28_outputs, 3, k28_attrs, 14},
-    {"_ITEXQuantizedMatMul", k29_inputs, 2, k29_outputs, 2, k29_attrs, 17},
-    {"_ITEXQuantizedMatMulWithBias", k30_inputs, 7, k30_outputs, 3, k30_attrs, 8},
-    {"_ITEXQuantizedMatMulWithBiasAndDequantize", k31_inputs, 9, k31_outputs, 1, k31_attrs, 8},
-    {"_ITEXQuantizedMatMulWithBiasAndRelu", k32_inputs, 7, k32_outputs, 3, k32_attrs, 7},
-    {"_ITEXQuantizedMatMulWithBiasAndReluAndRequantize", k33_inputs, 9, k33_outputs, 3, k33_attrs, 8},
-    {"_ITEXQuantizedMatMulWithBiasAndRequantize", k34_inputs, 9, k34_outputs, 3, k34_attrs, 8},
-    {"_ITEXQuantizedMaxPool", k35_inputs, 3, k35_outputs, 3, k35_attrs, 3},
-    {"_QuantizedBatchMatMul", k36_inputs, 2, k36_outputs, 2, k36_attrs, 13},
-    {"_QuantizedBatchMatMulV2AndDequantize", k37_inputs, 6, k37_outputs, 1, k37_attrs, 6},
-    {"_QuantizedConv2D", k38_inputs, 2, k38_outputs, 2, k38_attrs, 16},
-    {"_QuantizedFusedBatchMatMulV2AndDequantize", k39_inputs, 7, k39_outputs, 1, k39_attrs, 9},
-    {"_QuantizedFusedMatMul", k40_inputs, 7, k40_outputs, 3, k40_attrs, 13},
-    {"_QuantizedFusedMatMulAndDequantize", k41_inputs, 7, k41_outputs, 1, k41_attrs, 13},
-    {"_QuantizedFusedMatMulAndRequantize", k42_inputs, 9, k42_outputs, 3, k42_attrs, 13},
-    {"_QuantizedMatMul", k43_inputs, 2, k43_outputs, 2, k43_attrs, 17},
+    {"_ITEXQuantizedConcatV2", k13_inputs, 4, k13_outputs, 3, k13_attrs, 3},
+    {"_ITEXQuantizedConv2D", k14_inputs, 6, k14_outputs, 3, k14_attrs, 8},
+    {"_ITEXQuantizedConv2DAndRequantize", k15_inputs, 8, k15_outputs, 3, k15_attrs, 8},
+    {"_ITEXQuantizedConv2DPerChannel", k16_inputs, 6, k16_outputs, 3, k16_attrs, 8},
+    {"_ITEXQuantizedConv2DV2", k17_inputs, 2, k17_outputs, 2, k17_attrs, 16},
+    {"_ITEXQuantizedConv2DWithBias", k18_inputs, 7, k18_outputs, 3, k18_attrs, 9},
+    {"_ITEXQuantizedConv2DWithBiasAndRelu", k19_inputs, 7, k19_outputs, 3, k19_attrs, 9},
+    {"_ITEXQuantizedConv2DWithBiasAndReluAndRequantize", k20_inputs, 9, k20_outputs, 3, k20_attrs, 10},
+    {"_ITEXQuantizedConv2DWithBiasAndRequantize", k21_inputs, 9, k21_outputs, 3, k21_attrs, 10},
+    {"_ITEXQuantizedConv2DWithBiasSignedSumAndReluAndRequantize", k22_inputs, 12, k22_outputs, 3, k22_attrs, 11},
+    {"_ITEXQuantizedConv2DWithBiasSumAndReluAndRequantize", k23_inputs, 12, k23_outputs, 3, k23_attrs, 11},
+    {"_ITEXQuantizedConv2DWithCast", k24_inputs, 9, k24_outputs, 1, k24_attrs, 10},
+    {"_ITEXQuantizedConv2DWithDequantize", k25_inputs, 9, k25_outputs, 1, k25_attrs, 10},
+    {"_ITEXQuantizedFusedBatchMatMulV2AndDequantize", k26_inputs, 7, k26_outputs, 1, k26_attrs, 9},
+    {"_ITEXQuantizedFusedMatMul", k27_inputs, 7, k27_outputs, 3, k27_attrs, 14},
+    {"_ITEXQuantizedFusedMatMulAndDequantize", k28_inputs, 7, k28_outputs, 1, k28_attrs, 14},
+    {"_ITEXQuantizedFusedMatMulAndRequantize", k29_inputs, 9, k29_outputs, 3, k29_attrs, 14},
+    {"_ITEXQuantizedMatMul", k30_inputs, 2, k30_outputs, 2, k30_attrs, 17},
+    {"_ITEXQuantizedMatMulWithBias", k31_inputs, 7, k31_outputs, 3, k31_attrs, 8},
+    {"_ITEXQuantizedMatMulWithBiasAndDequantize", k32_inputs, 9, k32_outputs, 1, k32_attrs, 8},
+    {"_ITEXQuantizedMatMulWithBiasAndRelu", k33_inputs, 7, k33_outputs, 3, k33_attrs, 7},
+    {"_ITEXQuantizedMatMulWithBiasAndReluAndRequantize", k34_inputs, 9, k34_outputs, 3, k34_attrs, 8},
+    {"_ITEXQuantizedMatMulWithBiasAndRequantize", k35_inputs, 9, k35_outputs, 3, k35_attrs, 8},
+    {"_ITEXQuantizedMaxPool", k36_inputs, 3, k36_outputs, 3, k36_attrs, 3},
+    {"_ITEXQuantizedReshape", k37_inputs, 4, k37_outputs, 3, k37_attrs, 2},
+    {"_ITEXQuantizedTranspose", k38_inputs, 4, k38_outputs, 3, k38_attrs, 2},
+    {"_QuantizedBatchMatMul", k39_inputs, 2, k39_outputs, 2, k39_attrs, 13},
+    {"_QuantizedBatchMatMulV2AndDequantize", k40_inputs, 6, k40_outputs, 1, k40_attrs, 6},
+    {"_QuantizedConv2D", k41_inputs, 2, k41_outputs, 2, k41_attrs, 16},
+    {"_QuantizedFusedBatchMatMulV2AndDequantize", k42_inputs, 7, k42_outputs, 1, k42_attrs, 9},
+    {"_QuantizedFusedMatMul", k43_inputs, 7, k43_outputs, 3, k43_attrs, 13},
+    {"_QuantizedFusedMatMulAndDequantize", k44_inputs, 7, k44_outputs, 1, k44_attrs, 13},
+    {"_QuantizedFusedMatMulAndRequantize", k45_inputs, 9, k45_outputs, 3, k45_attrs, 13},
+    {"_QuantizedMatMul", k46_inputs, 2, k46_outputs, 2, k46_attrs, 17},
+    {"_QuantizedTranspose", k47_inputs, 4, k47_outputs, 3, k47_attrs, 2},
 };
 
 }  // namespace

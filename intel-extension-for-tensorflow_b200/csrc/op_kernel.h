@@ -100,6 +100,8 @@ inline int64_t NumElements(const itexb_tensor_t& t) {
 int RequireInputs(const itexb_op_context_t* ctx, int n, const char* op);
 // Input `i` as host floats (HostMemory argument); fails when the tensor is not on the host.
 int HostFloats(const itexb_op_context_t* ctx, int i, const char* op, const char* arg, const float** data, int64_t* count);
+// Input `i` as host integers (an int32 or int64 HostMemory argument: shape, perm, axis).
+int HostInts(const itexb_op_context_t* ctx, int i, const char* op, const char* arg, std::vector<int64_t>* v);
 int RequireDevice(const itexb_op_context_t* ctx, int i, const char* op, const char* arg);
 int AllocateOutput(itexb_op_context_t* ctx, int index, int dtype, const int64_t* dims, int rank, bool on_host, itexb_tensor_t* out);
 int AllocateTemp(itexb_op_context_t* ctx, size_t bytes, bool on_host, void** ptr);

@@ -105,6 +105,19 @@ int HostFloats(const itexb_op_context_t* ctx, int i, const char* op, const char*
   *data = static_cast<const float*>(t.data);
   return ITEXB_OK;
 }
+int HostInts(const itexb_op_context_t* ctx, int i, const char* op, const char* arg, std::vector<int64_t>* v) {
+  const itexb_tensor_t& t = ctx->inputs[i];
+  ITEXB_REQUIRE(t.on_host, ITEXB_INVALID_ARGUMENT, "%s: input '%s' (#%d) is a HostMemory argument but was passed in device memory",
+                op, arg, i);
+  ITEXB_REQUIRE(t.dtype == ITEXB_DT_INT32 || t.dtype == ITEXB_DT_INT64, ITEXB_INVALID_ARGUMENT, "%s: input '%s' must be int32 or int64, is %s",
+                op, arg, DtypeName(t.dtype));
+  const int64_t n = NumElements(t);
+  ITEXB_REQUIRE(n == 0 || t.data != nullptr, ITEXB_INVALID_ARGUMENT, "%s: input '%s' has no data", op, arg);
+  v->resize(size_t(n));
+  for (int64_t j = 0; j < n; ++j)
+    (*v)[size_t(j)] = t.dtype == ITEXB_DT_INT32 ? int64_t(static_cast<const int32_t*>(t.data)[j]) : static_cast<const int64_t*>(t.data)[j];
+  return ITEXB_OK;
+}
 int RequireDevice(const itexb_op_context_t* ctx, int i, const char* op, const char* arg) {
   ITEXB_REQUIRE(!ctx->inputs[i].on_host, ITEXB_INVALID_ARGUMENT, "%s: input '%s' (#%d) must be in device memory", op, arg, i);
   return ITEXB_OK;

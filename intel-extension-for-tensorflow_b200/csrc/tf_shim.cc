@@ -450,6 +450,7 @@ size_t ElementBytes(int dtype) {
   switch (dtype) {
     case ITEXB_DT_FLOAT: case ITEXB_DT_INT32: case ITEXB_DT_QINT32: return 4;
     case ITEXB_DT_BFLOAT16: case ITEXB_DT_HALF: return 2;
+    case ITEXB_DT_INT64: return 8;
     default: return 1;
   }
 }
@@ -509,7 +510,11 @@ void KernelCompute(void* kernel, TF_OpKernelContext* ctx) {
     // Fixed-arity ops: the registered mask.  List-typed ops (mask 0, count -1): ranges are HostMemory lists, which
     // TensorFlow hands over as host tensors; the op checks per call that what it reads as a range is on the host, and
     // a float tensor of at most one element per output channel in one of the trailing positions is one.
-    x.on_host = nin_decl >= 0 ? int((host_in >> i) & 1u) : int(x.dtype == ITEXB_DT_FLOAT && i >= 2 && i >= nin - 6 && x.rank <= 1);
+    // QuantizedConcatV2 (values x N, axis, input_mins x N, input_maxes x N): everything after the N values.
+    const bool concat = k->type.size() >= 17 && k->type.compare(k->type.size() - 17, 17, "QuantizedConcatV2") == 0;
+    x.on_host = nin_decl >= 0 ? int((host_in >> i) & 1u)
+                : concat      ? int(i >= (nin - 1) / 3)
+                              : int(x.dtype == ITEXB_DT_FLOAT && i >= 2 && i >= nin - 6 && x.rank <= 1);
   }
   if (ok) {
     SP_Stream stream = TF_GetStream(ctx, status);
@@ -567,13 +572,17 @@ void RegisterKernel(int slot, const char* op_name, const itexb_op_def_t& def, TF
     for (int i = 0; i < def.num_outputs && i < 32; ++i)
       if ((host_out >> i) & 1u) TF_KernelBuilder_HostMemory(b, ArgName(def.outputs[i]).c_str());
   } else {
-    // list-typed ops: the whole host_inputs / host_outputs lists (gpu/quantized_matmul.cc:137-182)
+    // list-typed ops: the whole host_inputs / host_outputs lists (gpu/quantized_matmul.cc:137-182); QuantizedConcatV2:
+    // axis, input_mins, input_maxes, output_min, output_max (common/quantized_concat_op.cc:251-268)
+    const auto is_host = [](const std::string& a) {
+      for (const char* prefix : {"host_", "min_", "max_", "input_min", "input_max", "output_min", "output_max"})
+        if (a.rfind(prefix, 0) == 0) return true;
+      return a == "axis";
+    };
     for (int i = 0; i < def.num_inputs; ++i)
-      if (ArgName(def.inputs[i]).rfind("host_", 0) == 0 || ArgName(def.inputs[i]).rfind("min_", 0) == 0 || ArgName(def.inputs[i]).rfind("max_", 0) == 0)
-        TF_KernelBuilder_HostMemory(b, ArgName(def.inputs[i]).c_str());
+      if (is_host(ArgName(def.inputs[i]))) TF_KernelBuilder_HostMemory(b, ArgName(def.inputs[i]).c_str());
     for (int i = 0; i < def.num_outputs; ++i)
-      if (ArgName(def.outputs[i]).rfind("host_", 0) == 0 || ArgName(def.outputs[i]).rfind("min_", 0) == 0 || ArgName(def.outputs[i]).rfind("max_", 0) == 0)
-        TF_KernelBuilder_HostMemory(b, ArgName(def.outputs[i]).c_str());
+      if (is_host(ArgName(def.outputs[i]))) TF_KernelBuilder_HostMemory(b, ArgName(def.outputs[i]).c_str());
   }
   // No TypeConstraint: one kernel object serves every type combination the op layer implements and reports the others
   // at construction ("no kernel registered for T1=..."), which is where the reference's type matrix fails too.

@@ -22,11 +22,11 @@ from .kernels import torch_dtype
 
 _NAME_TO_DT = {
     "float": L.DT_FLOAT, "float32": L.DT_FLOAT, "bfloat16": L.DT_BFLOAT16, "half": L.DT_HALF, "float16": L.DT_HALF,
-    "qint8": L.DT_QINT8, "quint8": L.DT_QUINT8, "qint32": L.DT_QINT32, "int8": L.DT_INT8, "int32": L.DT_INT32,
+    "qint8": L.DT_QINT8, "quint8": L.DT_QUINT8, "qint32": L.DT_QINT32, "int8": L.DT_INT8, "int32": L.DT_INT32, "int64": L.DT_INT64,
 }
 _TORCH_TO_DT = {torch.float32: L.DT_FLOAT, torch.bfloat16: L.DT_BFLOAT16, torch.float16: L.DT_HALF,
                 torch.int8: L.DT_QINT8, torch.uint8: L.DT_QUINT8, torch.int32: L.DT_QINT32}
-_TYPE_ATTRS = {"T", "T1", "T2", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype", "grad_dtype",
+_TYPE_ATTRS = {"T", "T1", "T2", "Tshape", "Tperm", "Tidx", "Tbias", "Toutput", "Tinput", "Tfilter", "out_type", "dtype", "sum_dtype", "out_dtype", "grad_dtype",
                "in_dtype", "Tsummand", "Targs", "Tout", "U", "weight_dtype"}
 
 
@@ -193,8 +193,12 @@ class Op:
             else:
                 if isinstance(x, torch.Tensor):
                     x = x.numpy()
-                arr = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
-                t.dtype = L.DT_FLOAT
+                if isinstance(x, np.ndarray) and x.dtype in (np.int32, np.int64):   # shape / perm / axis arguments
+                    arr = np.ascontiguousarray(x)
+                    t.dtype = L.DT_INT32 if x.dtype == np.int32 else L.DT_INT64
+                else:
+                    arr = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+                    t.dtype = L.DT_FLOAT
                 t.rank = arr.ndim
                 for d in range(arr.ndim):
                     t.dims[d] = arr.shape[d]
@@ -451,6 +455,25 @@ def _QuantizedConv2D(device_inputs, host_inputs, fused_ops=(), out_type="qint32"
     if Tsummand is not None:
         attrs["Tsummand"] = Tsummand
     return _cached(op_name, attrs)(*(list(device_inputs) + list(host_inputs)), dtypes=dtypes)
+
+
+def _ITEXQuantizedReshape(tensor, shape, input_min, input_max, Tshape="int32", op_name="_ITEXQuantizedReshape"):
+    """-> (output, output_min, output_max); one entry of `shape` may be -1."""
+    idt = np.int64 if Tshape == "int64" else np.int32
+    return _cached(op_name, dict(T=_TORCH_TO_DT[tensor.dtype], Tshape=Tshape))(tensor, np.asarray(shape, dtype=idt).reshape(-1), input_min, input_max)
+
+
+def _ITEXQuantizedTranspose(x, perm, min_x, max_x, Tperm="int32", op_name="_ITEXQuantizedTranspose"):
+    """-> (y, min_y, max_y)"""
+    idt = np.int64 if Tperm == "int64" else np.int32
+    return _cached(op_name, dict(T=_TORCH_TO_DT[x.dtype], Tperm=Tperm))(x, np.asarray(perm, dtype=idt).reshape(-1), min_x, max_x)
+
+
+def _ITEXQuantizedConcatV2(values, axis, input_mins, input_maxes, Tidx="int32", op_name="_ITEXQuantizedConcatV2"):
+    """-> (output, output_min, output_max); the reference's GPU kernel (and this one) serves equal input ranges only."""
+    idt = np.int64 if Tidx == "int64" else np.int32
+    args = list(values) + [np.asarray(axis, dtype=idt).reshape(())] + list(input_mins) + list(input_maxes)
+    return _cached(op_name, dict(N=len(values), T=_TORCH_TO_DT[values[0].dtype], Tidx=Tidx))(*args)
 
 
 def Fp8Quantize(x, x_amax, x_scale, fp8_meta_index, fp8_dtype="E4M3"):

@@ -862,3 +862,77 @@ def quantized_pool2d(x, ksize, strides, padding="SAME", avg=False):
             else:
                 out[:, oy, ox, :] = win.max(axis=1).astype(x.dtype)
     return out
+
+
+# --------------------------------------------------------------------------
+# data movement between the quantized ops: reshape, transpose, concat
+# --------------------------------------------------------------------------
+def quantized_reshape(tensor, shape, input_min, input_max):
+    """[_ITEX]QuantizedReshape (itex/core/kernels/common/quantized_reshape_op.h:33-200): the element order is kept, one
+    entry of `shape` may be -1 (zero-sized entries stay out of the product it is inferred from), the range passes
+    through.  -> (output, output_min, output_max); ValueError where the reference raises InvalidArgument."""
+    tensor = np.asarray(tensor)
+    sizes = [int(s) for s in np.asarray(shape).reshape(-1)]
+    if sum(1 for s in sizes if s == -1) > 1:
+        raise ValueError("Only one input size may be -1")
+    if any(s < -1 for s in sizes):
+        raise ValueError("Size must be non-negative")
+    product, has_zero = 1, False
+    for s in sizes:
+        if s == 0:
+            has_zero = True
+        elif s > 0:
+            product *= s
+    dims = [1 if s == -1 else s for s in sizes]
+    if -1 in sizes:
+        elems, input_has_zero = 1, False
+        for d in tensor.shape:
+            if d > 0 or not has_zero:
+                elems *= d
+            else:
+                input_has_zero = True
+        missing = elems // product
+        if not input_has_zero and product * missing != elems:
+            raise ValueError("the requested shape requires a multiple of %d" % product)
+        dims[sizes.index(-1)] = missing
+    if int(np.prod(dims, dtype=np.int64)) != tensor.size:
+        raise ValueError("Input to reshape is a tensor with %d values, but the requested shape has %d" % (tensor.size, int(np.prod(dims, dtype=np.int64))))
+    return tensor.reshape(dims).copy(), f32(input_min), f32(input_max)
+
+
+def quantized_transpose(x, perm, min_x, max_x):
+    """_QuantizedTranspose / _ITEXQuantizedTranspose (itex/core/kernels/common/transpose_op.h:92-236): y.shape[d] =
+    x.shape[perm[d]]; the range passes through."""
+    x = np.asarray(x)
+    perm = [int(p) for p in np.asarray(perm).reshape(-1)]
+    if len(perm) != x.ndim:
+        raise ValueError("transpose expects a vector of size %d" % x.ndim)
+    for p in perm:
+        if not 0 <= p < x.ndim:
+            raise ValueError("%d is out of range [0 .. %d)" % (p, x.ndim))
+    for d in range(x.ndim):
+        if d not in perm:
+            raise ValueError("%d is missing from {%s}." % (d, ",".join(str(p) for p in perm)))
+    return np.ascontiguousarray(np.transpose(x, perm)), f32(min_x), f32(max_x)
+
+
+def quantized_concat_v2(values, axis, input_mins, input_maxes):
+    """QuantizedConcatV2 / _ITEXQuantizedConcatV2 (itex/core/kernels/common/quantized_concat_op.cc:34-247): the bytes are
+    concatenated as they are; the kernel only serves inputs whose ranges agree within 1e-6 (anything else is the
+    reference's Aborted "Not implemented the case unequal input_mins / input_maxes") and hands out input 0's range."""
+    values = [np.asarray(v) for v in values]
+    mins = [f32(m) for m in input_mins]
+    maxes = [f32(m) for m in input_maxes]
+    rank = values[0].ndim
+    ax = int(axis) + rank if int(axis) < 0 else int(axis)
+    if not 0 <= ax < rank:
+        raise ValueError("ConcatOp : Expected concatenating dimensions in the range [%d, %d)" % (-rank, rank))
+    for v in values:
+        if v.ndim != rank:
+            raise ValueError("ConcatOp : Ranks of all input tensors should match")
+        if any(d != ax and v.shape[d] != values[0].shape[d] for d in range(rank)):
+            raise ValueError("ConcatOp : Dimensions of inputs should match")
+    for mn, mx in zip(mins[1:], maxes[1:]):
+        if abs(float(mins[0]) - float(mn)) > 1.0e-6 or abs(float(maxes[0]) - float(mx)) > 1.0e-6:
+            raise NotImplementedError("unequal input_mins / input_maxes")
+    return np.concatenate(values, axis=ax), mins[0], maxes[0]

@@ -225,6 +225,8 @@ def test_rewrite_rules_match_the_reference_table(itex, golden_dir):
         attrs = dict(need[e["copy"]])
         if e["rule"] == "RewriteQuantize":
             attrs.setdefault("mode", "SCALED")
+        if e["rule"] == "RewriteQuantizeReshape":
+            attrs["T"] = "qint8"
         st, new_op, added = _rewrite(itex, f, **attrs)
         assert st == L.OK and new_op == e["to"], f
         if e["copy"] == "CopyAttrsQuantizedConv2D":
@@ -232,6 +234,10 @@ def test_rewrite_rules_match_the_reference_table(itex, golden_dir):
     # ops the table does not hold stay as they are
     assert _rewrite(itex, "Conv2D") == (L.OK, None, {})
     assert _rewrite(itex, "QuantizedConcatV2") == (L.OK, None, {})        # disabled in the reference's table
+    # RewriteQuantizeReshape (layout_utils.cc:392-400): only a qint8 reshape is taken over
+    assert _rewrite(itex, "QuantizedReshape", T="qint8")[1] == "_ITEXQuantizedReshape"
+    assert _rewrite(itex, "QuantizedReshape", T="quint8")[1] is None
+    assert _rewrite(itex, "QuantizedReshape")[0] == L.INVALID_ARGUMENT
     # RewriteQuantize
     assert _rewrite(itex, "QuantizeV2", mode="MIN_COMBINED", round_mode="HALF_AWAY_FROM_ZERO")[1] is None
     assert _rewrite(itex, "QuantizeV2", mode="SCALED", round_mode="HALF_AWAY_FROM_ZERO")[1] is None
