@@ -471,17 +471,14 @@ def run_fp8_linears(args, rank, world, local, dev, K):
         comm.wait_stream(main)
         keep = []
         for layer, a, gathered, k, n in layers_nccl:
-            y = layer(a)
+            y = layer(a, out=gathered[rank])            # the shard is computed in its place of the gather buffer
             keep.append(y)
             if world > 1:
                 comm.wait_stream(main)
                 with torch.cuda.stream(comm):
                     # 12 bytes; the state only has to agree before the next step's scale update
                     dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
-                    dist.all_gather_into_tensor(gathered, y)
-                    y.record_stream(comm)
-            else:
-                gathered[0].copy_(y)
+                    dist.all_gather_into_tensor(gathered, y)    # in place: y is this rank's slice of `gathered`
         main.wait_stream(comm)
 
     def step_fused():

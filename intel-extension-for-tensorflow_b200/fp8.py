@@ -279,7 +279,7 @@ class Fp8Dense:
             self._nodes[key] = ops.Op("Fp8Quantize", in_dtype=ops._TORCH_TO_DT[t.dtype], fp8_meta_index=index, fp8_dtype="E4M3")
         return self._nodes[key](t, self.meta.amax_history[0], self.meta.scale)
 
-    def _matmul(self, xq, wq, bias):
+    def _matmul(self, xq, wq, bias, out=None):
         from . import _lib as L
         if "mm" not in self._nodes:
             self._nodes["mm"] = ops.Op("Fp8Matmul", fp8_meta_index_a=0, fp8_meta_index_b=1, fp8_meta_index_c=-1, transpose_a=False,
@@ -288,9 +288,9 @@ class Fp8Dense:
                                        fp8_dtype_c="")
         m = self.meta
         return self._nodes["mm"](xq, wq, bias, self._dummy, m.scale_inv, m.scale_inv, m.amax_history[0], m.scale,
-                                 dtypes={0: L.DT_INT8, 1: L.DT_INT8})
+                                 dtypes={0: L.DT_INT8, 1: L.DT_INT8}, out=None if out is None else {0: out})
 
-    def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0, out=None) -> torch.Tensor:
         """gather: a PeerGather (column-parallel layer, kernel kept as [N/world, K]): the product lands in slot `rank` of
         linear `gather_index`'s buffer on every rank, stored by the GEMM kernel's copying warps; returns this rank's slot.  The
         arithmetic is that of the Fp8Matmul op (same kernel, same scales)."""
@@ -308,4 +308,4 @@ class Fp8Dense:
                    peer_out=gather.peers(gather_index), status_word=gather.status)
             return out
         bias = self.bias if self.bias is not None else self._dummy
-        return self._matmul(xq, wq, bias)
+        return self._matmul(xq, wq, bias, out)      # out: the product is written into the caller's [M, N] tensor

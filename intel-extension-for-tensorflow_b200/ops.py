@@ -129,6 +129,7 @@ class Op:
         self._alloc_out_cb = L.ALLOC_OUTPUT_FN(lambda user, index, tp: ref()._allocate_output(user, index, tp))
         self._alloc_tmp_cb = L.ALLOC_TEMP_FN(lambda user, nbytes, on_host, pp: ref()._allocate_temp(user, nbytes, on_host, pp))
         self._device = None
+        self._given = None
 
     def check(self, wait=True):
         """Raises ItexError (ABORTED) if a kernel launched by this instance gave up on a bounded wait (itexb_op_check)."""
@@ -152,7 +153,14 @@ class Op:
                 t.data = arr.ctypes.data
                 self._outputs[index] = arr
             else:
-                ten = torch.empty(shape, dtype=torch_dtype(t.dtype), device=self._device)
+                ten = self._given.get(index) if self._given else None
+                if ten is not None:
+                    # the caller's buffer (TensorFlow forwards an input buffer to an output the same way): it has to be what
+                    # the kernel asked for
+                    if list(ten.shape) != shape or ten.dtype != torch_dtype(t.dtype) or not ten.is_contiguous() or ten.device != self._device:
+                        return L.INVALID_ARGUMENT
+                else:
+                    ten = torch.empty(shape, dtype=torch_dtype(t.dtype), device=self._device)
                 t.data = ten.data_ptr()
                 self._outputs[index] = ten
             return L.OK
@@ -172,9 +180,11 @@ class Op:
         except Exception:
             return L.RESOURCE_EXHAUSTED
 
-    def __call__(self, *inputs, device=None, dtypes=None):
+    def __call__(self, *inputs, device=None, dtypes=None, out=None):
         """Runs Compute.  `dtypes` optionally overrides the itexb dtype of tensor inputs
-        (e.g. DT_INT8 for FP8 bytes held in a torch.int8/uint8 tensor)."""
+        (e.g. DT_INT8 for FP8 bytes held in a torch.int8/uint8 tensor).  `out` = {output index: tensor} makes the kernel
+        write those device outputs into the caller's tensors (shape, type and device must be what the kernel produces)."""
+        self._given = out
         keep = []
         tens = (L.Tensor * max(1, len(inputs)))()
         dev = device
@@ -219,6 +229,7 @@ class Op:
             L.check(self.lib.itexb_op_compute(self._h, C.byref(ctx)))
         finally:
             self._temps = []  # torch's allocator is stream-ordered: safe to release after enqueue
+            self._given = None
         nout = self.nout if self.nout >= 0 else (max(self._outputs) + 1 if self._outputs else 0)  # -1: decided per call
         outs = [self._outputs.get(i) for i in range(nout)]
         outs = [o.reshape(()).item() if isinstance(o, np.ndarray) and o.ndim == 0 else o for o in outs]

@@ -162,6 +162,34 @@ def test_column_parallel_shards_reassemble_the_full_product():
         assert bool((shards[-1].meta.scale == full.meta.scale).all())
 
 
+def test_outputs_into_the_callers_buffers():
+    """`out=` makes a kernel instance write a device output into the caller's tensor (a slot of a gather buffer): same
+    bits as the kernel's own allocation; a tensor of another shape or type is refused."""
+    itex, K, ops = modules()
+    fp8 = importlib.import_module("itex_b200.fp8")
+    rng = np.random.default_rng(6)
+    m, k, n = 96, 256, 128
+    W = torch.from_numpy((rng.standard_normal((n, k)) * 0.02).astype(np.float32)).to(torch.bfloat16).cuda()
+    A = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16).cuda()
+    a = fp8.Fp8Dense(W, recipe=fp8.DelayedScaling(amax_history_len=4), out_dtype="bfloat16", weight_layout="nk")
+    b = fp8.Fp8Dense(W, recipe=fp8.DelayedScaling(amax_history_len=4), out_dtype="bfloat16", weight_layout="nk")
+    slots = torch.zeros((3, m, n), dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):
+        want = a(A)
+        got = b(A, out=slots[1])
+        assert got.data_ptr() == slots[1].data_ptr() and bool((got == want).all())
+    assert bool((slots[0] == 0).all()) and bool((slots[2] == 0).all())
+    q = ops.Op("_ITEXQuantizeV2", T="quint8", mode="SCALED", round_mode="HALF_TO_EVEN", narrow_range=False, axis=-1, ensure_minimum_range=0.01,
+               dtype="float")
+    x = torch.rand((8, 32), device="cuda")
+    buf = torch.empty((8, 32), dtype=torch.uint8, device="cuda")
+    y, _, _ = q(x, 0.0, 1.0, out={0: buf})
+    assert y.data_ptr() == buf.data_ptr() and bool((y == q(x, 0.0, 1.0)[0]).all())
+    for bad in (torch.empty((8, 31), dtype=torch.uint8, device="cuda"), torch.empty((8, 32), dtype=torch.int8, device="cuda")):
+        with pytest.raises(itex.ItexError):
+            q(x, 0.0, 1.0, out={0: bad})
+
+
 def test_fp8_gelu_and_layernorm():
     """Fp8Gelu and Fp8LayerNorm against the restatement: FP8 outputs within one FP8 step (1e-2 relative is the bar; the
     device's tanh / rsqrt and fp32 summation order differ from the float64 restatement in the last bits, which can move a
