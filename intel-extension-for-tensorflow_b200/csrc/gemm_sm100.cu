@@ -371,7 +371,7 @@ __host__ __device__ constexpr int OutBlockCols(int bn, int esz, int sup, bool su
   return cols < max_cols ? cols : (max_cols < 16 ? 16 : max_cols);
 }
 // Epilogue loop specialisations (template parameter, chosen per launch by LaunchGemm).
-enum : int { kEpGeneral = 0, kEpPlain = 1, kEpSum8 = 2 };
+enum : int { kEpGeneral = 0, kEpPlain = 1, kEpSum8 = 2, kEpGelu = 3 };
 // Output kinds (template parameter of the epilogue).
 enum : int { kOutRaw = 0, kOutF32, kOutBF16, kOutF16, kOutS32, kOutU8, kOutS8, kOutFP8 };
 template <int OK> struct OutBytes { static constexpr int v = (OK == kOutRaw || OK == kOutF32 || OK == kOutS32) ? 4 : ((OK == kOutBF16 || OK == kOutF16) ? 2 : 1); };
@@ -579,7 +579,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
     if (CG == 2) MbarArriveCluster(MapToCta(SmemAddr(&tmem_empty_bar[a]), 0));
     else MbarArrive(SmemAddr(&tmem_empty_bar[a]));
   };
-  constexpr bool PLAIN = MODE == kEpPlain, SUM8 = MODE == kEpSum8;
+  constexpr bool PLAIN = MODE == kEpPlain || MODE == kEpGelu, SUM8 = MODE == kEpSum8;  // kEpGelu: the plain loop + tanh-GELU
   const bool tma_store = MODE != kEpGeneral || g.tma_store;
   EpilogueCtx e;
   const bool has_alpha = g.ep.alpha_a != nullptr && g.ep.alpha_b != nullptr;
@@ -623,7 +623,7 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
   // reads is already the float 1.5 * 2^23 + acc of the adder trick - the integer add per element is done by the
   // tensor core.  Each warp re-arms the columns it has read with one TMEM store per slice; the first arming
   // happens here and is published through the accumulator-empty barriers the MMA warp waits on.
-  constexpr bool preset = !F8 && OK != kOutRaw && (MODE == kEpPlain || MODE == kEpSum8);  // == g.preset, known at compile time here
+  constexpr bool preset = !F8 && OK != kOutRaw && MODE != kEpGeneral;  // == g.preset, known at compile time here
   if (preset) {
     // each warp arms what it will read and re-arm later: its blocks of its sub-tile, in both stages
 #pragma unroll 1
@@ -856,6 +856,10 @@ __device__ __forceinline__ void EpilogueLoop(const GemmArgs& g, const CUtensorMa
             if (e.relu) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            if constexpr (MODE == kEpGelu) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(GeluTanh(v[j]), e.post_scale);
             }
             if (MODE == kEpGeneral && g.ep.activation != ITEXB_ACT_NONE) {
               Float16 t;
@@ -1340,14 +1344,17 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       case kOutRaw: EpilogueLoop<BN, F8, kOutRaw, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS); break;
       case kOutF32:
         if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF32, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpGelu) EpilogueLoop<BN, F8, kOutF32, kEpGelu, SUP, CG>(ITEXB_EP_ARGS);
         else EpilogueLoop<BN, F8, kOutF32, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutBF16:
         if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutBF16, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpGelu) EpilogueLoop<BN, F8, kOutBF16, kEpGelu, SUP, CG>(ITEXB_EP_ARGS);
         else EpilogueLoop<BN, F8, kOutBF16, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutF16:
         if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutF16, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpGelu) EpilogueLoop<BN, F8, kOutF16, kEpGelu, SUP, CG>(ITEXB_EP_ARGS);
         else EpilogueLoop<BN, F8, kOutF16, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutS32:
@@ -1357,11 +1364,13 @@ GemmKernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CU
       case kOutU8:
         if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutU8, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
         else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutU8, kEpSum8, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpGelu) EpilogueLoop<BN, F8, kOutU8, kEpGelu, SUP, CG>(ITEXB_EP_ARGS);
         else EpilogueLoop<BN, F8, kOutU8, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       case kOutS8:
         if (g.ep_mode == kEpPlain) EpilogueLoop<BN, F8, kOutS8, kEpPlain, SUP, CG>(ITEXB_EP_ARGS);
         else if (g.ep_mode == kEpSum8) EpilogueLoop<BN, F8, kOutS8, kEpSum8, SUP, CG>(ITEXB_EP_ARGS);
+        else if (g.ep_mode == kEpGelu) EpilogueLoop<BN, F8, kOutS8, kEpGelu, SUP, CG>(ITEXB_EP_ARGS);
         else EpilogueLoop<BN, F8, kOutS8, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS);
         break;
       default: EpilogueLoop<BN, F8, kOutFP8, kEpGeneral, SUP, CG>(ITEXB_EP_ARGS); break;
@@ -1694,7 +1703,12 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int bn,
              (reinterpret_cast<uintptr_t>(g.ep.summand) & 15) == 0)
       g.ep_mode = kEpSum8;
   }
-  g.preset = (!f8 && (g.ep_mode == kEpPlain || g.ep_mode == kEpSum8)) ? 1 : 0;
+  // tanh-GELU after scale and bias, nothing else (the FFN-up layer of a transformer): the plain loop with the activation
+  // inlined instead of the general loop's out-of-line activation call (12288 x 4096 x 1024 -> bf16: see the kernel table)
+  if (g.tma_store && g.ep.activation == ITEXB_ACT_GELU_TANH && g.ep.mid_dtype == 0 && !g.ep.raw_acc && g.ep.summand == nullptr && !g.ep.relu &&
+      (g.out_kind == kOutF32 || g.out_kind == kOutBF16 || g.out_kind == kOutF16 || g.out_kind == kOutU8 || g.out_kind == kOutS8))
+    g.ep_mode = kEpGelu;
+  g.preset = (!f8 && g.ep_mode != kEpGeneral) ? 1 : 0;
   CUtensorMap to;
   CUtensorMap tsum;  // Sum8: the summand seen through the output's geometry (same boxes, same swizzle)
   if (g.ep_mode == kEpSum8)
