@@ -90,39 +90,6 @@ template <> __device__ __forceinline__ void Load16<__half>(const __half* p, floa
   }
 }
 
-template <typename T> __device__ __forceinline__ void Store16(T* p, const float (&in)[kVec]);
-template <> __device__ __forceinline__ void Store16<float>(float* p, const float (&in)[kVec]) {
-  float4* p4 = reinterpret_cast<float4*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) __stcs(p4 + i, make_float4(in[4 * i], in[4 * i + 1], in[4 * i + 2], in[4 * i + 3]));
-}
-template <> __device__ __forceinline__ void Store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&in)[kVec]) {
-  uint4* p4 = reinterpret_cast<uint4*>(p);
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(in[8 * i + 2 * j], in[8 * i + 2 * j + 1]);
-      w[j] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    __stcs(p4 + i, make_uint4(w[0], w[1], w[2], w[3]));
-  }
-}
-template <> __device__ __forceinline__ void Store16<__half>(__half* p, const float (&in)[kVec]) {
-  uint4* p4 = reinterpret_cast<uint4*>(p);
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __half2 h = __floats2half2_rn(in[8 * i + 2 * j], in[8 * i + 2 * j + 1]);
-      w[j] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    __stcs(p4 + i, make_uint4(w[0], w[1], w[2], w[3]));
-  }
-}
-
 __device__ __forceinline__ void StoreBytes16(void* p, const int (&q)[kVec]) {
   uint32_t w[4];
 #pragma unroll
