@@ -36,7 +36,9 @@ def extract(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: %s /path/to/reference-checkout" % os.path.basename(sys.argv[0]))
+    root = sys.argv[1]
     wanted = json.load(open(os.path.join(HERE, "op_names.json")))
     defs = extract(root)
     out = {n: defs[n] for n in wanted if n in defs}

@@ -16,7 +16,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: %s /path/to/reference-checkout" % os.path.basename(sys.argv[0]))
+    root = sys.argv[1]
     text = open(os.path.join(root, "itex/core/graph/native_layout/native_layout.cc")).read()
     gpu = text[text.index("GetCPUEigenNativeFormatInfo() {"):text.index("GetCPUNativeFormatInfo() {")]
     gpu = re.sub(r"//[^\n]*", "", gpu)
