@@ -52,9 +52,44 @@ def test_op_registry_names_and_host_memory_masks(itex):
     assert ops.op_signature("_ITEXQuantizedMatMulWithBias") == (7, 3, 0b1111000, 0b110)
     assert ops.op_signature("_ITEXQuantizedMatMulWithBiasAndDequantize") == (9, 1, 0b111111000, 0)
     assert ops.op_signature("_ITEXQuantizedConv2DWithBiasAndReluAndRequantize") == (9, 3, 0b111111000, 0b110)
+    # perm / shape and the ranges are HostMemory (gpu/transpose_op.cc:48-56, gpu/quantized_reshape_op.cc); the concat's
+    # arity depends on N (common/quantized_concat_op.cc:251-268)
+    assert ops.op_signature("_ITEXQuantizedTranspose") == ops.op_signature("_QuantizedTranspose") == (4, 3, 0b1110, 0b110)
+    assert ops.op_signature("_ITEXQuantizedReshape") == ops.op_signature("QuantizedReshape") == (4, 3, 0b1110, 0b110)
+    assert ops.op_signature("_ITEXQuantizedConcatV2") == ops.op_signature("QuantizedConcatV2") == (-1, 3, 0, 0b110)
     with pytest.raises(itex.ItexError) as e:
         ops.op_signature("NoSuchOp")
     assert e.value.code == itex._lib.NOT_FOUND
+
+
+def test_layout_kernels_reject_bad_arguments_before_touching_a_device(itex):
+    """itexb_transpose / itexb_copy_rows validate on the host: these calls return without a CUDA call."""
+    lib, L = itex.load(), itex._lib
+
+    class Transpose(ctypes.Structure):
+        _fields_ = [("x", ctypes.c_void_p), ("y", ctypes.c_void_p), ("rank", ctypes.c_int32), ("elem_size", ctypes.c_int32),
+                    ("dims", ctypes.c_int64 * 8), ("perm", ctypes.c_int32 * 8)]
+
+    def call(rank, dims, perm, esz=1):
+        p = Transpose()
+        p.rank, p.elem_size = rank, esz
+        for i, d in enumerate(dims):
+            p.dims[i] = d
+        for i, a in enumerate(perm):
+            p.perm[i] = a
+        return lib.itexb_transpose(ctypes.byref(p), None)
+
+    assert call(9, [1] * 8, list(range(8))) == L.INVALID_ARGUMENT            # rank above ITEXB_TRANSPOSE_MAX_RANK
+    assert call(3, [2, 3, 4], [0, 1, 1]) == L.INVALID_ARGUMENT                # not a permutation
+    assert call(3, [2, 3, 4], [0, 1, 3]) == L.INVALID_ARGUMENT
+    assert call(2, [2, 3], [1, 0], esz=3) == L.INVALID_ARGUMENT
+    assert call(3, [2, 0, 4], [2, 1, 0]) == L.OK                              # empty: nothing to do
+    assert call(2, [2, 3], [1, 0]) == L.INVALID_ARGUMENT                      # NULL tensors
+    lib.itexb_copy_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+    assert lib.itexb_copy_rows(None, None, 4, 32, 16, 0, None) == L.INVALID_ARGUMENT   # rows longer than the pitch
+    assert lib.itexb_copy_rows(None, None, 4, 16, 32, 24, None) == L.INVALID_ARGUMENT  # past the end of a row
+    assert lib.itexb_copy_rows(None, None, 0, 16, 32, 0, None) == L.OK
+    assert lib.itexb_copy_rows(None, None, 4, 16, 32, 0, None) == L.INVALID_ARGUMENT   # NULL pointers
 
 
 @pytest.mark.parametrize("attrs,fragment", [
