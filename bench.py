@@ -457,7 +457,7 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     pg = None
     layers_nccl = layers
     layers_fused = layers
-    if mode in ("fused", "auto"):
+    if mode != "nccl":
         def exchange(obj):
             out = [None] * world
             dist.all_gather_object(out, obj)
@@ -481,16 +481,30 @@ def run_fp8_linears(args, rank, world, local, dev, K):
                     dist.all_gather_into_tensor(gathered, y)    # in place: y is this rank's slice of `gathered`
         main.wait_stream(comm)
 
-    def step_fused():
-        # Every GEMM's epilogue stores its shard into all ranks' gather buffers while the next tiles are computed; the
+    lanes = [torch.cuda.Stream(device=dev) for _ in layers]
+    # the widest shard first: its GEMM is the one with more tiles than SMs, the other two fill the SMs it leaves
+    lane_order = sorted(range(len(layers)), key=lambda i: -layers[i][4])
+
+    def step_fused(overlap=False):
+        # Every GEMM's copying warps store its shard into all ranks' gather buffers while the next tiles are computed; the
         # 12-byte amax all-reduce stays on NCCL, on a second stream.  One publish / finish pair covers the three linears.
+        # overlap: the three linears are independent, so each runs on a stream of its own between begin() and publish():
+        # one linear's quantize passes and main loop run under another's copies, and NVLink stays busy from the first
+        # finished tile to the last.
         main = torch.cuda.current_stream(dev)
         pg.begin()
-        for i, (layer, a, gathered, k, n) in enumerate(layers_fused):
-            layer(a, gather=pg, gather_index=i)
-            comm.wait_stream(main)
+        for i in (lane_order if overlap else range(len(layers_fused))):
+            layer, a = layers_fused[i][0], layers_fused[i][1]
+            lane = lanes[i] if overlap else main
+            lane.wait_stream(main)
+            with torch.cuda.stream(lane):
+                layer(a, gather=pg, gather_index=i)
+            comm.wait_stream(lane)
             with torch.cuda.stream(comm):
                 dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
+        if overlap:
+            for lane in lanes:
+                main.wait_stream(lane)
         pg.publish()
         pg.finish()
         main.wait_stream(comm)
@@ -506,10 +520,11 @@ def run_fp8_linears(args, rank, world, local, dev, K):
     # (a time-based loop would let ranks disagree and dead-lock).  >= 17 steps fill the 16-deep amax history.
     n_warm = max(args.warmup, 17, int(args.min_warmup_seconds * 600))
 
-    def prepare(fused_way):
+    def prepare(way):
         """Warm-up, then one CUDA graph per step (kernels and NCCL collectives): removes ~20 host-side op calls per step,
         which otherwise bound the step once the per-GPU GEMMs shrink with the shard count."""
-        eager = step_fused if fused_way else step_nccl
+        fused_way = way != "nccl"
+        eager = {"nccl": step_nccl, "fused": step_fused, "fused_streams": lambda: step_fused(True)}[way]
         # after finish() the gathered buffers are complete and may be read; acknowledge() tells the peers that this rank
         # is done reading, which is what lets them store the next step's shards
         ack = pg.acknowledge if fused_way else (lambda: None)
@@ -545,15 +560,20 @@ def run_fp8_linears(args, rank, world, local, dev, K):
 
     trials = None
     if mode == "auto":
-        ways = {False: prepare(False), True: prepare(True)}
-        trials = {"nccl_ms": trial_ms(ways[False][2]), "fused_ms": trial_ms(ways[True][2])}   # the same on every rank
-        # a bounded wait that ran out anywhere (a peer that never signalled) disqualifies the fused way
+        ways = {w: prepare(w) for w in ("nccl", "fused", "fused_streams")}
+        trials = {w + "_ms": trial_ms(ways[w][2]) for w in ways}                   # the same on every rank
+        # a bounded wait that ran out anywhere (a peer that never signalled) disqualifies the fused ways
         trials["fused_status"] = int(max_over_ranks(float(pg.status.item()), world, dev))
-        fused = trials["fused_status"] == 0 and trials["fused_ms"] <= trials["nccl_ms"]
-        eager_step, consumed, graph = ways[fused]
+        # same inputs and, once the amax history is full, the same scales in every step: what the last fused trial left in
+        # the peer-mapped buffers must be what the NCCL trial left in its own, bit for bit, on every rank
+        differs = any(not torch.equal(layers_fused[i][2], layers_nccl[i][2]) for i in range(len(layers)))
+        trials["fused_equals_nccl"] = max_over_ranks(1.0 if differs else 0.0, world, dev) == 0.0
+        ok = trials["fused_status"] == 0 and trials["fused_equals_nccl"]
+        mode = min(ways, key=lambda w: trials[w + "_ms"]) if ok else "nccl"
+        eager_step, consumed, graph = ways[mode]
     else:
-        fused = mode == "fused"
-        eager_step, consumed, graph = prepare(fused)
+        eager_step, consumed, graph = prepare(mode)
+    fused = mode != "nccl"
     layers = layers_fused if fused else layers_nccl
     step = graph.replay
     launches0 = K.launch_count()
@@ -602,9 +622,9 @@ def run_fp8_linears(args, rank, world, local, dev, K):
             "vs_baseline": None, "dtype": "e4m3xe4m3->f32", "data": "synthetic",
             "config": {"workload": "fp8_llama_linears", "tokens": m, "linears_k_n": FP8_LINEARS, "delayed_scaling": "margin 0, history 16, max",
                        "output": "bfloat16 [g, M, N/g] after all-gather", "l2": "weights + activations larger than L2",
-                       "parallelism": ("column-parallel x%d, all-gather fused into the GEMM epilogue (stores to peer memory over NVLink)" if fused
+                       "parallelism": ("column-parallel x%d, all-gather fused into the GEMM kernel (copies to peer memory over NVLink)" if fused
                                        else "column-parallel x%d, NCCL all-gather of outputs") % world,
-                       "gather": "fused" if fused else ("nccl" if world > 1 else "none"), "gather_trials": trials, "tflops": tflops,
+                       "gather": mode if world > 1 else "none", "gather_trials": trials, "tflops": tflops,
                        "nvlink_bytes_sent_per_gpu_per_step": sum(m * (n // world) * 2 * (world - 1) for _, n in FP8_LINEARS) if world > 1 else 0,
                        "peer_status": int(pg.status.item()) if fused else None},
             "roofline": {"bound": "tensor", "kernel": "GemmKernel<256,fp8> (tcgen05.mma kind::f8f6f4)", "achieved": tflops,
@@ -1229,9 +1249,9 @@ def main():
     ap.add_argument("--real-dtype", default="float", choices=["float", "bfloat16"],
                     help="type of the real-valued side for --workload [fp8_]quantize / [fp8_]dequantize")
     ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--fp8-gather", default="auto", choices=["auto", "fused", "nccl"],
-                    help="fp8_llama_linears on several GPUs: all-gather fused into the GEMM kernel (copies to peer memory), NCCL's, "
-                         "or whichever of the two is faster in a trial during warm-up")
+    ap.add_argument("--fp8-gather", default="auto", choices=["auto", "fused", "fused_streams", "nccl"],
+                    help="fp8_llama_linears on several GPUs: all-gather fused into the GEMM kernel (copies to peer memory), the same "
+                         "with each linear on a stream of its own, NCCL's, or whichever is fastest in a trial during warm-up")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler runs, quick checks)")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0,
