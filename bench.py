@@ -499,12 +499,19 @@ def run_fp8_linears(args, rank, world, local, dev, K):
             lane.wait_stream(main)
             with torch.cuda.stream(lane):
                 layer(a, gather=pg, gather_index=i)
-            comm.wait_stream(lane)
-            with torch.cuda.stream(comm):
-                dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
+            if not overlap:
+                comm.wait_stream(lane)
+                with torch.cuda.stream(comm):
+                    dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
         if overlap:
             for lane in lanes:
                 main.wait_stream(lane)
+            # one NCCL launch for the three 12-byte rows: a collective kernel finds no free SM while the GEMMs run, so
+            # each separate launch would add its whole latency to the end of the step
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm), dist._coalescing_manager(device=dev):
+                for layer, *_ in layers_fused:
+                    dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
         pg.publish()
         pg.finish()
         main.wait_stream(comm)
