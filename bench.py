@@ -481,40 +481,17 @@ def run_fp8_linears(args, rank, world, local, dev, K):
                     dist.all_gather_into_tensor(gathered, y)    # in place: y is this rank's slice of `gathered`
         main.wait_stream(comm)
 
-    lanes = [torch.cuda.Stream(device=dev) for _ in layers]
-    # the widest shard first: its GEMM is the one with more tiles than SMs, the other two fill the SMs it leaves
-    lane_order = sorted(range(len(layers)), key=lambda i: -layers[i][4])
+    def reduce_amax(rows):
+        # one NCCL launch for the three 12-byte rows; the state only has to agree before the next step's scale update
+        with dist._coalescing_manager(device=dev):
+            for row in rows:
+                dist.all_reduce(row, op=dist.ReduceOp.MAX)
 
     def step_fused(overlap=False):
-        # Every GEMM's copying warps store its shard into all ranks' gather buffers while the next tiles are computed; the
-        # 12-byte amax all-reduce stays on NCCL, on a second stream.  One publish / finish pair covers the three linears.
-        # overlap: the three linears are independent, so each runs on a stream of its own between begin() and publish():
-        # one linear's quantize passes and main loop run under another's copies, and NVLink stays busy from the first
-        # finished tile to the last.
-        main = torch.cuda.current_stream(dev)
-        pg.begin()
-        for i in (lane_order if overlap else range(len(layers_fused))):
-            layer, a = layers_fused[i][0], layers_fused[i][1]
-            lane = lanes[i] if overlap else main
-            lane.wait_stream(main)
-            with torch.cuda.stream(lane):
-                layer(a, gather=pg, gather_index=i)
-            if not overlap:
-                comm.wait_stream(lane)
-                with torch.cuda.stream(comm):
-                    dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
-        if overlap:
-            for lane in lanes:
-                main.wait_stream(lane)
-            # one NCCL launch for the three 12-byte rows: a collective kernel finds no free SM while the GEMMs run, so
-            # each separate launch would add its whole latency to the end of the step
-            comm.wait_stream(main)
-            with torch.cuda.stream(comm), dist._coalescing_manager(device=dev):
-                for layer, *_ in layers_fused:
-                    dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
-        pg.publish()
-        pg.finish()
-        main.wait_stream(comm)
+        # Every GEMM's copying warps store its shard into all ranks' gather buffers while the next tiles are computed; one
+        # publish / finish pair covers the three linears; the amax all-reduce stays on NCCL, on a second stream.
+        # overlap: the three linears are independent, so each runs on a stream of its own (PeerGather.linears).
+        pg.linears([l[0] for l in layers_fused], [l[1] for l in layers_fused], reduce_amax=reduce_amax, streams=overlap)
 
     def barrier():
         if world > 1:

@@ -238,6 +238,44 @@ class PeerGather:
     def acknowledge(self):
         self.L.check(self.lib.itexb_peer_signal(self._ack_flag_ptrs, self.world, 0, self.C.c_void_p(self.base + self.counter_off), self._stream()))
 
+    def linears(self, layers, inputs, reduce_amax=None, streams=True):
+        """One step of column-parallel Fp8Dense layers that do not depend on one another: begin(), layer i on inputs[i] with
+        its product gathered into buffer i, publish(), finish().  Returns the gathered buffers; the caller reads them and then
+        calls acknowledge().
+
+        streams: every layer runs on a stream of its own (forked from and joined to the caller's), the widest shard launched
+        first, so one layer's quantize passes and main loop run under another's copies and NVLink stays busy from the first
+        finished tile to the last; otherwise all on the caller's stream, in order.
+        reduce_amax(rows): the caller's collective over the layers' newest amax rows (max over the ranks, in place; e.g. one
+        coalesced NCCL all-reduce), so that every rank keeps the same scaling state.  It runs on a side stream after the last
+        layer — a collective kernel finds no free SM while persistent GEMMs hold all of them — and is joined before return.
+        Captures into a CUDA graph like any fork/join of streams."""
+        assert len(layers) == len(inputs) == len(self.shapes)
+        main = torch.cuda.current_stream(self.device)
+        if streams and getattr(self, "_lanes", None) is None:
+            self._lanes = [torch.cuda.Stream(device=self.device) for _ in layers]
+        if reduce_amax is not None and getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        self.begin()
+        order = sorted(range(len(layers)), key=lambda i: -self.shapes[i][1]) if streams else range(len(layers))
+        for i in order:
+            lane = self._lanes[i] if streams else main
+            lane.wait_stream(main)
+            with torch.cuda.stream(lane):
+                layers[i](inputs[i], gather=self, gather_index=i)
+        if streams:
+            for lane in self._lanes:
+                main.wait_stream(lane)
+        if reduce_amax is not None:
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                reduce_amax([layer.meta.amax_history[0] for layer in layers])
+        self.publish()
+        self.finish()
+        if reduce_amax is not None:
+            main.wait_stream(self._side)
+        return [self.gathered(i) for i in range(len(layers))]
+
     def close(self, barrier=None):
         """Unmaps the peers' blocks and frees this rank's; `barrier()` (a host rendezvous) makes sure no rank frees its
         block while another still has kernels in flight that store into it."""

@@ -47,13 +47,19 @@ def _worker(rank, world, port, results):
     ok = True
     for step in range(4):
         scale_up = 1.0 + step
-        pg.begin()
-        for i, (layer, a) in enumerate(zip(layers, acts)):
-            layer(a * scale_up, gather=pg, gather_index=i)
-            dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
-        pg.publish()
-        pg.finish()
-        got = [pg.gathered(i).clone() for i in range(len(layers))]
+        if step % 2 == 0:                     # the protocol spelled out, everything on one stream
+            pg.begin()
+            for i, (layer, a) in enumerate(zip(layers, acts)):
+                layer(a * scale_up, gather=pg, gather_index=i)
+                dist.all_reduce(layer.meta.amax_history[0], op=dist.ReduceOp.MAX)
+            pg.publish()
+            pg.finish()
+            got = [pg.gathered(i).clone() for i in range(len(layers))]
+        else:                                 # the same step through the helper, every linear on a stream of its own
+            def reduce_amax(rows):
+                for row in rows:
+                    dist.all_reduce(row, op=dist.ReduceOp.MAX)
+            got = [g.clone() for g in pg.linears(layers, [a * scale_up for a in acts], reduce_amax=reduce_amax, streams=True)]
         pg.acknowledge()
         # the reference path: the Fp8Matmul op per shard, shards assembled by NCCL
         for i, (layer, a) in enumerate(zip(refs, acts)):
