@@ -247,29 +247,44 @@ class PeerGather:
         first, so one layer's quantize passes and main loop run under another's copies and NVLink stays busy from the first
         finished tile to the last; otherwise all on the caller's stream, in order.
         reduce_amax(rows): the caller's collective over the layers' newest amax rows (max over the ranks, in place; e.g. one
-        coalesced NCCL all-reduce), so that every rank keeps the same scaling state.  It runs on a side stream after the last
-        layer — a collective kernel finds no free SM while persistent GEMMs hold all of them — and is joined before return.
+        coalesced NCCL all-reduce), so that every rank keeps the same scaling state.  It runs on a side stream and is joined
+        before return; with `streams` it is launched between the quantize passes and the GEMMs (a collective kernel launched
+        later finds no free SM while persistent GEMMs hold all of them, and its whole latency lands at the end of the step).
         Captures into a CUDA graph like any fork/join of streams."""
         assert len(layers) == len(inputs) == len(self.shapes)
         main = torch.cuda.current_stream(self.device)
         if streams and getattr(self, "_lanes", None) is None:
             self._lanes = [torch.cuda.Stream(device=self.device) for _ in layers]
         if reduce_amax is not None and getattr(self, "_side", None) is None:
-            self._side = torch.cuda.Stream(device=self.device)
+            self._side = torch.cuda.Stream(device=self.device, priority=-1)
+        rows = [layer.meta.amax_history[0] for layer in layers]
         self.begin()
-        order = sorted(range(len(layers)), key=lambda i: -self.shapes[i][1]) if streams else range(len(layers))
-        for i in order:
-            lane = self._lanes[i] if streams else main
-            lane.wait_stream(main)
-            with torch.cuda.stream(lane):
-                layers[i](inputs[i], gather=self, gather_index=i)
         if streams:
+            order = sorted(range(len(layers)), key=lambda i: -self.shapes[i][1])
+            quantized = {}
+            for i in order:
+                self._lanes[i].wait_stream(main)
+                with torch.cuda.stream(self._lanes[i]):
+                    quantized[i] = layers[i].quantize_inputs(inputs[i])
+                if reduce_amax is not None:
+                    self._side.wait_stream(self._lanes[i])
+            if reduce_amax is not None:
+                # the rows are final once the quantize passes are done: the collective is launched before the GEMMs take
+                # the SMs and runs under them
+                with torch.cuda.stream(self._side):
+                    reduce_amax(rows)
+            for i in order:
+                with torch.cuda.stream(self._lanes[i]):
+                    layers[i].gathered_matmul(*quantized[i], self, i)
             for lane in self._lanes:
                 main.wait_stream(lane)
-        if reduce_amax is not None:
-            self._side.wait_stream(main)
-            with torch.cuda.stream(self._side):
-                reduce_amax([layer.meta.amax_history[0] for layer in layers])
+        else:
+            for i, layer in enumerate(layers):
+                layer(inputs[i], gather=self, gather_index=i)
+            if reduce_amax is not None:
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    reduce_amax(rows)
         self.publish()
         self.finish()
         if reduce_amax is not None:
@@ -328,22 +343,30 @@ class Fp8Dense:
         return self._nodes["mm"](xq, wq, bias, self._dummy, m.scale_inv, m.scale_inv, m.amax_history[0], m.scale,
                                  dtypes={0: L.DT_INT8, 1: L.DT_INT8}, out=None if out is None else {0: out})
 
-    def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0, out=None) -> torch.Tensor:
-        """gather: a PeerGather (column-parallel layer, kernel kept as [N/world, K]): the product lands in slot `rank` of
-        linear `gather_index`'s buffer on every rank, stored by the GEMM kernel's copying warps; returns this rank's slot.  The
-        arithmetic is that of the Fp8Matmul op (same kernel, same scales)."""
-        m = self.meta
+    def quantize_inputs(self, x: torch.Tensor, update_meta: bool = True):
+        """First half of the forward: the scale update and the two Fp8Quantize passes.  Returns (xq, wq); after it the newest
+        amax row holds this call's maxima (a bf16 / f32 product adds none)."""
         if update_meta:
-            m.amax_and_scale_update()
-        xq = self._quantize(x, 0)
-        wq = self._quantize(self.kernel, 1)
+            self.meta.amax_and_scale_update()
+        return self._quantize(x, 0), self._quantize(self.kernel, 1)
+
+    def gathered_matmul(self, xq, wq, gather, gather_index: int = 0) -> torch.Tensor:
+        """Second half for a column-parallel layer (kernel kept as [N/world, K]): the product lands in slot `rank` of linear
+        `gather_index`'s buffer on every rank of the PeerGather, stored by the GEMM kernel's copying warps; returns this
+        rank's slot.  The arithmetic is that of the Fp8Matmul op (same kernel, same scales)."""
+        from . import _lib as L
+        assert self.transpose_b and self.bias is None and self.out_dtype == "bfloat16", "the fused gather path serves [N,K] kernels, bf16 out"
+        m = self.meta
+        ep = K.make_epilogue(alpha_a=m.scale_inv[0:1], alpha_b=m.scale_inv[1:2])
+        out = gather.local(gather_index)
+        K.gemm(xq.view(torch.uint8), wq.view(torch.uint8), L.DT_BFLOAT16, a_dtype=L.DT_FP8_E4M3, b_dtype=L.DT_FP8_E4M3, ep=ep, out=out,
+               peer_out=gather.peers(gather_index), status_word=gather.status)
+        return out
+
+    def __call__(self, x: torch.Tensor, update_meta: bool = True, gather=None, gather_index: int = 0, out=None) -> torch.Tensor:
+        """gather: a PeerGather; see gathered_matmul."""
+        xq, wq = self.quantize_inputs(x, update_meta)
         if gather is not None:
-            from . import _lib as L
-            assert self.transpose_b and self.bias is None and self.out_dtype == "bfloat16", "the fused gather path serves [N,K] kernels, bf16 out"
-            ep = K.make_epilogue(alpha_a=m.scale_inv[0:1], alpha_b=m.scale_inv[1:2])
-            out = gather.local(gather_index)
-            K.gemm(xq.view(torch.uint8), wq.view(torch.uint8), L.DT_BFLOAT16, a_dtype=L.DT_FP8_E4M3, b_dtype=L.DT_FP8_E4M3, ep=ep, out=out,
-                   peer_out=gather.peers(gather_index), status_word=gather.status)
-            return out
+            return self.gathered_matmul(xq, wq, gather, gather_index)
         bias = self.bias if self.bias is not None else self._dummy
         return self._matmul(xq, wq, bias, out)      # out: the product is written into the caller's [M, N] tensor
