@@ -361,3 +361,32 @@ def test_fp8_scale_update_hand_vectors():
     nh, sf, sfi = o.fp8_amax_and_scale_update(h, np.ones(3, np.float32), 448.0, 0, "max")
     np.testing.assert_array_equal(sf, [32.0, 32.0, 32.0])         # amax = 10, 11, 12 -> 448/12 = 37.3 -> 5
     np.testing.assert_array_equal(sfi, [1 / 32.0] * 3)
+
+
+def test_layout_ops_move_elements_and_pass_the_range_through():
+    """QuantizedReshape / _QuantizedTranspose / QuantizedConcatV2 (common/quantized_reshape_op.h:33-200, gpu/transpose_op.cc,
+    common/quantized_concat_op.cc:34-247): element moves only; the range is an output equal to the input's (input 0's for
+    the concat, which refuses unequal ranges)."""
+    rng = np.random.default_rng(11)
+    x = rng.integers(-128, 128, (2, 3, 4, 5)).astype(np.int8)
+    y, mn, mx = o.quantized_transpose(x, [0, 3, 1, 2], -1.5, 2.5)
+    assert np.array_equal(y, np.transpose(x, (0, 3, 1, 2))) and (float(mn), float(mx)) == (-1.5, 2.5)
+    with pytest.raises(ValueError):
+        o.quantized_transpose(x, [0, 1, 1, 2], 0.0, 1.0)          # not a permutation
+    with pytest.raises(ValueError):
+        o.quantized_transpose(x, [0, 1, 2], 0.0, 1.0)             # wrong length
+    y, mn, mx = o.quantized_reshape(x, [-1, 20], 0.0, 6.0)
+    assert y.shape == (6, 20) and np.array_equal(y.reshape(-1), x.reshape(-1)) and (float(mn), float(mx)) == (0.0, 6.0)
+    assert o.quantized_reshape(np.zeros((0, 4), np.uint8), [0, -1], 0.0, 1.0)[0].shape == (0, 4)
+    for bad in ([-1, -1], [7, -1], [-2, 60], [5, 5]):
+        with pytest.raises(ValueError):
+            o.quantized_reshape(x, bad, 0.0, 1.0)
+    a, b = x[:, :, :, :2], x[:, :, :, 2:]
+    y, mn, mx = o.quantized_concat_v2([a, b], -1, [-1.0, -1.0], [1.0, 1.0 + 5e-7])
+    assert np.array_equal(y, x) and (float(mn), float(mx)) == (-1.0, 1.0)
+    with pytest.raises(NotImplementedError):
+        o.quantized_concat_v2([a, b], 3, [-1.0, -1.0], [1.0, 1.5])
+    with pytest.raises(ValueError):
+        o.quantized_concat_v2([a, b], 0, [-1.0, -1.0], [1.0, 1.0])  # sizes differ off the axis
+    with pytest.raises(ValueError):
+        o.quantized_concat_v2([a, b], 4, [-1.0, -1.0], [1.0, 1.0])
